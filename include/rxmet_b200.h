@@ -1,0 +1,305 @@
+/*
+ * rxmet_b200.h - C ABI of the B200-native quantized recurrent hot path.
+ *
+ * Every entry point takes plain pointers, sizes and POD structs; no C++ or
+ * torch types cross this boundary.  "dev" pointers are CUDA device pointers on
+ * the current device, "host" pointers are ordinary host memory.  All tensors
+ * are dense and contiguous in the layouts named per argument.  All entry
+ * points return 0 on success and a negative rxmet_status on failure;
+ * rxmet_last_error() then holds a message for the calling thread.
+ *
+ * Each declaration cites the reference interface it replaces as
+ * <path inside rx-met>:<line>.
+ */
+#ifndef RXMET_B200_H_
+#define RXMET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define RXMET_API
+#else
+#define RXMET_API __attribute__((visibility("default")))
+#endif
+
+typedef enum rxmet_status {
+    RXMET_OK = 0,
+    RXMET_ERR_INVALID_ARGUMENT = -1, /* bad size, null pointer, bad config      */
+    RXMET_ERR_CUDA = -2,             /* a CUDA runtime call or launch failed    */
+    RXMET_ERR_WORKSPACE = -3,        /* caller's workspace is too small         */
+    RXMET_ERR_UNSUPPORTED = -4,      /* shape or bit-width outside this build   */
+    RXMET_ERR_DEVICE_TIMEOUT = -5    /* a bounded device-side wait ran out      */
+} rxmet_status;
+
+/* Message of the last failure on the calling thread ("" if none). */
+RXMET_API const char *rxmet_last_error(void);
+/* Library version string. */
+RXMET_API const char *rxmet_version(void);
+/* Number of kernels this library has launched in this process so far. */
+RXMET_API uint64_t rxmet_kernel_launch_count(void);
+
+/* ------------------------------------------------------------------------ */
+/* QuantGRU: configuration and encodings                                     */
+/* ------------------------------------------------------------------------ */
+
+/* The 17 quantization points of one GRU direction, in the member order of the
+ * reference's OperatorQuantConfig (operators/quant-gru/include/
+ * quantize_bitwidth_config.h:54-83). */
+enum {
+    RXMET_GRU_X = 0,
+    RXMET_GRU_H = 1,
+    RXMET_GRU_W = 2,
+    RXMET_GRU_R = 3,
+    RXMET_GRU_BW = 4,
+    RXMET_GRU_BR = 5,
+    RXMET_GRU_WEIGHT_IH_LINEAR = 6,
+    RXMET_GRU_WEIGHT_HH_LINEAR = 7,
+    RXMET_GRU_UPDATE_GATE_INPUT = 8,
+    RXMET_GRU_UPDATE_GATE_OUTPUT = 9,
+    RXMET_GRU_RESET_GATE_INPUT = 10,
+    RXMET_GRU_RESET_GATE_OUTPUT = 11,
+    RXMET_GRU_NEW_GATE_INPUT = 12,
+    RXMET_GRU_NEW_GATE_OUTPUT = 13,
+    RXMET_GRU_MUL_RESET_HIDDEN = 14,
+    RXMET_GRU_MUL_OLD_CONTRIBUTION = 15,
+    RXMET_GRU_MUL_NEW_CONTRIBUTION = 16,
+    RXMET_GRU_NUM_OPS = 17
+};
+
+/* Granularity of the W / R / bw / br scales (quantize_bitwidth_config.h:56-60). */
+enum { RXMET_PER_TENSOR = 0, RXMET_PER_GATE = 1, RXMET_PER_CHANNEL = 2 };
+/* Power-of-two rounding policy (operators/quant-gru/include/pot_scale_encode.h:37-41). */
+enum { RXMET_POT_ROUND = 0, RXMET_POT_COVER_RANGE = 1, RXMET_POT_FLOOR = 2 };
+
+/* Mirror of OperatorQuantConfig (quantize_bitwidth_config.h:54-122): bit-width
+ * 1..32, signedness and symmetry per quantization point, weight granularities
+ * and the power-of-two switch. */
+typedef struct rxmet_gru_quant_config {
+    int8_t bits[RXMET_GRU_NUM_OPS];
+    uint8_t is_unsigned[RXMET_GRU_NUM_OPS];
+    uint8_t symmetric[RXMET_GRU_NUM_OPS];
+    int32_t W_granularity, R_granularity, bw_granularity, br_granularity;
+    uint8_t use_pot2;
+    int8_t pot_scale_method;
+    float pot_scale_tolerance;
+} rxmet_gru_quant_config;
+
+/* Fills *cfg with the reference defaults: 8 bit everywhere, update/reset gate
+ * outputs unsigned, everything symmetric, per-channel weights, affine
+ * (M * 2^-shift) rescale, CoverRange with tolerance 0.02. */
+RXMET_API void rxmet_gru_default_config(rxmet_gru_quant_config *cfg);
+
+/* Mirror of GRUQuantizationRanges (operators/quant-gru/include/
+ * gru_quantization_ranges.h:20-69).  min/max are indexed by quantization
+ * point; the W/R/bw/br entries of the scalar arrays are unused, their
+ * per-channel ranges live in the eight host arrays of 3*hidden floats. */
+typedef struct rxmet_gru_ranges {
+    int32_t hidden;
+    float min[RXMET_GRU_NUM_OPS];
+    float max[RXMET_GRU_NUM_OPS];
+    float *min_W, *max_W, *min_R, *max_R, *min_bw, *max_bw, *min_br, *max_br;
+} rxmet_gru_ranges;
+
+/* Sets every range to (FLT_MAX, -FLT_MAX) like GRUQuantizationRanges::reset
+ * (gru_quantization_ranges.h:74-118).  The per-channel arrays must be set. */
+RXMET_API int rxmet_gru_ranges_reset(rxmet_gru_ranges *ranges);
+
+/* Mirror of the Python-visible GRUQuantParams (operators/quant-gru/pytorch/lib/
+ * gru_interface_binding.cc:145-193): one (scale, zero point) per point, the
+ * four weight/bias scale arrays always expanded to 3*hidden (zero point 0),
+ * and the configuration.  LUT tables and rescale multipliers are derived
+ * inside the library from these values, as the reference's to_cpp() does
+ * (gru_interface_binding.cc:1261-1316). */
+typedef struct rxmet_gru_quant_params {
+    int32_t hidden;
+    float scale[RXMET_GRU_NUM_OPS];
+    int32_t zero_point[RXMET_GRU_NUM_OPS];
+    float *scale_W, *scale_R, *scale_bw, *scale_br; /* host, 3*hidden each */
+    rxmet_gru_quant_config config;
+} rxmet_gru_quant_params;
+
+/* Ranges -> encodings.  Replaces calculateGRUQuantitativeParameters
+ * (operators/quant-gru/src/gru_host.cc:13-125).  out->scale_* must point to
+ * 3*hidden floats each.  Host only. */
+RXMET_API int rxmet_gru_params_from_ranges(const rxmet_gru_ranges *ranges,
+                                           const rxmet_gru_quant_config *cfg,
+                                           rxmet_gru_quant_params *out);
+
+/* One segment of the 16-segment piecewise-linear activation table
+ * (operators/quant-gru/include/quantize_lut_types.h:32-37). */
+typedef struct rxmet_lut_segment {
+    int32_t q_b;
+    int32_t n_bx_total;
+    int32_t term_c;
+    int32_t threshold;
+} rxmet_lut_segment;
+
+/* Writes the three activation tables (update sigmoid, reset sigmoid, new-gate
+ * tanh; 16 segments each) derived from params.  Replaces
+ * generate_piecewise_linear_lut_to_params (operators/quant-gru/src/
+ * quantize_lut.cc:17-48).  Host only; exposed so that table parity can be
+ * checked on its own. */
+RXMET_API int rxmet_gru_build_luts(const rxmet_gru_quant_params *params,
+                                   rxmet_lut_segment out_segments[3][16]);
+
+/* Effective scale the integer core uses for a stored scale: M*2^-shift with a
+ * 16-bit M (affine) or the power of two itself.  Replaces
+ * decode_effective_scale (gru_interface_binding.cc:1322-1327). */
+RXMET_API int rxmet_gru_decode_effective_scale(float scale, int use_pot2, float *out);
+
+/* ------------------------------------------------------------------------ */
+/* QuantGRU: device entry points                                             */
+/* ------------------------------------------------------------------------ */
+
+/* Weights arrive as the reference's Python hands them over: gate order z,r,n
+ * and transposed, W [I,3H], R [H,3H], bw/br [3H] (operators/quant-gru/pytorch/
+ * quant_gru.py:714-759).  x is time-major [T,B,I]; h is [T+1,B,H] with h[0]
+ * the initial state; v is [T,B,4H] = (z, r, n, (R h + br)_n). */
+
+/* Bytes of device scratch the entry point named by `op` needs for these
+ * sizes.  op: 0 forward_fp / forward_calibrate, 1 forward_quant,
+ * 2 backward_quant / backward_fp. */
+RXMET_API size_t rxmet_gru_workspace_bytes(int op, int T, int B, int I, int H);
+
+/* Float GRU forward.  Replaces forward_fp -> gru::ForwardPass<float>::Run
+ * (gru_interface_binding.cc:656-698, operators/quant-gru/src/
+ * gru_forward_gpu.cu:359-431).  h0_dev may be NULL (zero state). */
+RXMET_API int rxmet_gru_forward_fp(int T, int B, int I, int H,
+                                   const float *W_dev, const float *R_dev,
+                                   const float *bw_dev, const float *br_dev,
+                                   const float *x_dev, const float *h0_dev,
+                                   float *h_dev, float *v_dev,
+                                   void *workspace_dev, size_t workspace_bytes,
+                                   void *stream);
+
+/* Float forward that also folds the min/max of the 13 activation points and
+ * of W/R/bw/br per channel into *ranges (host).  Replaces forward_calibrate
+ * with calib_method "minmax" -> forwardWithCalibrationGPU /
+ * forwardWithCalibrationCPU (gru_interface_binding.cc:710-780, operators/
+ * quant-gru/src/gru_interface.cc:936-1024, src/gru_forward_cpu.cc:58-151).
+ * Only finite values are observed; h[0] is not observed.  Synchronises the
+ * stream before returning because the result lands in host memory. */
+RXMET_API int rxmet_gru_forward_calibrate_minmax(int T, int B, int I, int H,
+                                                 const float *W_dev, const float *R_dev,
+                                                 const float *bw_dev, const float *br_dev,
+                                                 const float *x_dev, const float *h0_dev,
+                                                 float *h_dev, float *v_dev,
+                                                 rxmet_gru_ranges *ranges,
+                                                 void *workspace_dev, size_t workspace_bytes,
+                                                 void *stream);
+
+/* Device-side half of the above for data-parallel calibration: leaves the
+ * packed statistics (see rxmet_gru_stats_floats) in stats_dev as
+ * [mins..., maxs...] without touching the host, so that ranks can all-reduce
+ * them (MIN on the first half, MAX on the second) before folding. */
+RXMET_API size_t rxmet_gru_stats_floats(int H);
+RXMET_API int rxmet_gru_forward_calibrate_stats(int T, int B, int I, int H,
+                                                const float *W_dev, const float *R_dev,
+                                                const float *bw_dev, const float *br_dev,
+                                                const float *x_dev, const float *h0_dev,
+                                                float *h_dev, float *v_dev, float *stats_dev,
+                                                void *workspace_dev, size_t workspace_bytes,
+                                                void *stream);
+/* Folds packed statistics (host copy of stats_dev) into *ranges. */
+RXMET_API int rxmet_gru_ranges_fold_stats(rxmet_gru_ranges *ranges, const float *stats_host);
+
+/* The 11 clamp masks of a training forward (1 = kept, 0 = clamped;
+ * operators/quant-gru/include/quantize_ops_helper.h:272-276), in the order
+ * the reference returns them (gru_interface_binding.cc:310-448).  Each is a
+ * device uint8 array; all NULL for an inference forward. */
+typedef struct rxmet_gru_masks {
+    uint8_t *x;                /* [T,B,I]  */
+    uint8_t *h0;               /* [B,H], NULL when no h0 is given */
+    uint8_t *W;                /* [I,3H]   */
+    uint8_t *R;                /* [H,3H]   */
+    uint8_t *bw;               /* [3H]     */
+    uint8_t *br;               /* [3H]     */
+    uint8_t *weight_ih_linear; /* [T,B,3H] */
+    uint8_t *weight_hh_linear; /* [T,B,3H] */
+    uint8_t *gate_input;       /* [T,B,3H] */
+    uint8_t *gate_output;      /* [T,B,3H] */
+    uint8_t *h;                /* [T,B,H]  */
+} rxmet_gru_masks;
+
+/* Quantized GRU forward with the integer carrier: int32-exact accumulation,
+ * M*2^-shift (or power-of-two) rescale with round-half-even shifts and the
+ * 16-segment integer activation tables.  Replaces forward_quant_int_storage /
+ * forward_quant_float_storage -> quantGRUForwardInt -> ForwardPassQuant::Run
+ * (gru_interface_binding.cc:463-597, operators/quant-gru/src/
+ * gru_interface.cc:430-556, src/gru_forward_gpu_quant.cu:789-841) and the CPU
+ * core ForwardPassQuantCPU::Run (src/gru_forward_cpu_quant.cc:313-348).
+ * h_dev / v_dev receive the dequantized values; the optional *_q_dev outputs
+ * receive the integer codes (int32, NULL to skip): W_q [I,3H], R_q [H,3H],
+ * bw_q/br_q [3H], x_q [T,B,I], h_q [T+1,B,H], v_q [T,B,4H]. */
+RXMET_API int rxmet_gru_forward_quant(int is_training, int T, int B, int I, int H,
+                                      const float *W_dev, const float *R_dev,
+                                      const float *bw_dev, const float *br_dev,
+                                      const float *x_dev, const float *h0_dev,
+                                      const rxmet_gru_quant_params *params,
+                                      float *h_dev, float *v_dev,
+                                      int32_t *W_q_dev, int32_t *R_q_dev,
+                                      int32_t *bw_q_dev, int32_t *br_q_dev,
+                                      int32_t *x_q_dev, int32_t *h_q_dev, int32_t *v_q_dev,
+                                      const rxmet_gru_masks *masks,
+                                      void *workspace_dev, size_t workspace_bytes,
+                                      void *stream);
+
+/* Integer-in / integer-out inference: x_q [T,B,I] and h0_q [B,H] (or NULL)
+ * are already codes on the x / h grids; h_q_dev receives [T+1,B,H] codes.
+ * Replaces forward_quantized_int_io -> quantGRUForwardIntIO
+ * (gru_interface_binding.cc:600-647, gru_interface.cc:566-618). */
+RXMET_API int rxmet_gru_forward_quant_int_io(int T, int B, int I, int H,
+                                             const float *W_dev, const float *R_dev,
+                                             const float *bw_dev, const float *br_dev,
+                                             const int32_t *x_q_dev, const int32_t *h0_q_dev,
+                                             const rxmet_gru_quant_params *params,
+                                             int32_t *h_q_dev,
+                                             void *workspace_dev, size_t workspace_bytes,
+                                             void *stream);
+
+/* QAT backward: BPTT on the dequantized saved values with straight-through
+ * clamp masks.  Replaces backward_quant_int_storage /
+ * backward_quant_float_storage -> quantGRUBackward -> BackwardPassQuant::Run
+ * (gru_interface_binding.cc:790-969, gru_interface.cc:112-153, operators/
+ * quant-gru/src/gru_backward_gpu_quant.cu:93-493).  W_q..x_q are the int32
+ * codes saved by the forward and are left untouched; h [T+1,B,H] and
+ * v [T,B,4H] are the dequantized forward outputs; dh_new is [T+1,B,H].
+ * Outputs: dx [T,B,I], dW [I,3H], dR [H,3H], dbw/dbr [3H], dh0 [B,H].  Bias
+ * gradients are reduced in a fixed order (no atomics), so the result is
+ * reproducible run to run.  masks may be NULL (no clamp anywhere). */
+RXMET_API int rxmet_gru_backward_quant(int T, int B, int I, int H,
+                                       const int32_t *W_q_dev, const int32_t *R_q_dev,
+                                       const int32_t *bw_q_dev, const int32_t *br_q_dev,
+                                       const int32_t *x_q_dev,
+                                       const float *dh_new_dev, const float *h_dev,
+                                       const float *v_dev,
+                                       const rxmet_gru_quant_params *params,
+                                       const rxmet_gru_masks *masks,
+                                       float *dx_dev, float *dW_dev, float *dR_dev,
+                                       float *dbw_dev, float *dbr_dev, float *dh0_dev,
+                                       void *workspace_dev, size_t workspace_bytes,
+                                       void *stream);
+
+/* Float backward.  Replaces backward_fp -> gru::BackwardPass<float>::Run
+ * (gru_interface_binding.cc:975-1046, operators/quant-gru/src/
+ * gru_backward_gpu.cu). */
+RXMET_API int rxmet_gru_backward_fp(int T, int B, int I, int H,
+                                    const float *W_dev, const float *R_dev,
+                                    const float *bw_dev, const float *br_dev,
+                                    const float *x_dev,
+                                    const float *dh_new_dev, const float *h_dev,
+                                    const float *v_dev,
+                                    float *dx_dev, float *dW_dev, float *dR_dev,
+                                    float *dbw_dev, float *dbr_dev, float *dh0_dev,
+                                    void *workspace_dev, size_t workspace_bytes,
+                                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RXMET_B200_H_ */
