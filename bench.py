@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the QuantGRU QAT step (the workload the headline metric is quoted on).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload "gru_qat_step": QuantGRU I=40, H=128, T=100, batch 256 per GPU (weak scaling), W8/A8
+fake-quant with straight-through masks; one step = quantized training forward + MSE gradient +
+BPTT + gradient all-reduce + SGD update.  Synthetic N(0,1) inputs and targets, U(-1/sqrt(H),
+1/sqrt(H)) weights, min/max calibration once before timing.
+
+value : seq-timesteps/s with inputs resident in HBM (preallocated buffers, C ABI called directly).
+e2e   : the same step through the reference-facing module ``rx_met_b200.gru_interface_binding``
+        with host->device copies of x / target from pinned memory and the loss read back.
+The reference arm (--impl reference) times the reference's CPU quantized forward (it has no CPU
+training path) on all host cores over a bounded sample of the same shapes.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+WORKLOAD = dict(T=100, B=256, I=40, H=128)
+METRIC = "QuantGRU QAT seq-timesteps/sec"
+UNIT = "seq-timesteps/s"
+# Algorithmic HBM bytes per sequence-timestep of the two recurrent kernels: the module-boundary
+# fp32 tensors (4*I in or out, 4*H out or in) plus the minimal saved state S = 5 code bytes per
+# hidden unit + the 13H+I mask bits, once written (forward) and once read (backward).
+def _algo_bytes_per_st(I, H):
+    S = 5 * H + (13 * H + I + 7) // 8
+    return 4 * I + 4 * H + S
+
+
+def _peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        if shutil.which("nvidia-smi") is None:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen(
+            ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+             "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for line in Path(self.path).read_text().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        # samples under load = upper half of the observed SM clocks
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# CPU arm: the reference's own CPU quantized path (or its C restatement)
+# --------------------------------------------------------------------------
+
+def cpu_forward_throughput(seconds_target=12.0, shard_batch=8):
+    """Calibration-free timing of the CPU quantized (PTQ) forward at the workload's T/I/H on all
+    host cores: independent batch shards run on a thread pool (ctypes releases the GIL).  Returns
+    (seq-timesteps/s, cores, kind, description)."""
+    import numpy as np
+    import oracle_lib as ol
+    T, I, H = WORKLOAD["T"], WORKLOAD["I"], WORKLOAD["H"]
+    kind = "reference" if ol.ref() is not None else "port"
+    prefix = "ref" if kind == "reference" else "orc"
+    cores = os.cpu_count() or 1
+    W, R, bw, br, x, _ = ol.gru_problem(0, T, shard_batch, I, H)
+    cfg = ol.make_config(bits=8, symmetric=False)
+    ranges = ol.RangesBox(H)
+    ol.forward_calibrate_minmax("orc", W, R, bw, br, x, None, ranges)
+    params = ol.params_from_ranges("orc", ranges, cfg)
+
+    def shard(seed):
+        xs = np.random.default_rng(seed).standard_normal((T, shard_batch, I)).astype(np.float32)
+        ol.forward_quant(prefix, W, R, bw, br, xs, None, params, training=False, want_float=False)
+
+    t0 = time.perf_counter()
+    shard(1)
+    one = time.perf_counter() - t0
+    rounds = max(1, int(seconds_target / max(one, 1e-3)))
+    n_shards = cores * rounds
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=cores) as pool:
+        list(pool.map(shard, range(n_shards)))
+    dt = time.perf_counter() - t0
+    st = n_shards * shard_batch * T
+    desc = (f"{n_shards} shards of {shard_batch} sequences x T={T} (I={I}, H={H}), quantized inference forward only "
+            f"(the reference has no CPU training path), {cores} threads, {dt:.1f} s")
+    return st / dt, cores, kind, desc, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times, values = [], []
+    desc = kind = None
+    cores = 1
+    for i in range(args.warmup + args.steps):
+        v, cores, kind, desc, dt = cpu_forward_throughput(
+            seconds_target=min(3.0, 150.0 / max(1, args.warmup + args.steps)))
+        if i >= args.warmup:
+            values.append(v)
+            times.append(dt)
+    value = statistics.mean(values)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 codes / int64 accumulate",
+        "data": "synthetic", "config": {"workload": "gru_qat_step", **WORKLOAD, "note": "CPU reference arm: forward only"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from rx_met_b200 import _cabi as cabi
+    from rx_met_b200 import gru_interface_binding as ops
+    from rx_met_b200.qat import GruQatStep
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    lib = cabi.load_library()
+    T, B, I, H = (WORKLOAD[k] for k in "TBIH")
+    cfg = ops.OperatorQuantConfig()
+    for name in cabi.OP_NAMES:
+        if name not in ("W", "R", "bw", "br"):
+            setattr(cfg, f"{name}_symmetric_", False)  # W8 symmetric, A8 asymmetric
+    eng = GruQatStep(T, B, I, H, device, cfg, process_group=group, seed=1234)
+    gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    n_sets = 4
+    xs_host = [torch.randn((T, B, I), generator=gen).pin_memory() for _ in range(n_sets)]
+    ys_host = [torch.randn((T, B, H), generator=gen).pin_memory() for _ in range(n_sets)]
+    xs = [t.to(device) for t in xs_host]
+    ys = [t.to(device) for t in ys_host]
+    eng.calibrate(xs[:2])
+    lr = 1e-3
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+            flush.zero_()
+        barrier()
+        timed.launches0 = lib.rxmet_kernel_launch_count()
+        start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            start[i].record()
+            fn(i)
+            stop[i].record()
+            flush.zero_()
+        barrier()
+        timed.launches = lib.rxmet_kernel_launch_count() - timed.launches0
+        ms = sum(s.elapsed_time(e) for s, e in zip(start, stop))
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # --- device-resident leg
+    def resident(i):
+        eng.step(xs[i % n_sets], ys[i % n_sets], lr)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(resident, args.steps, args.warmup)
+    launches = timed.launches
+    clocks = sampler.stop() if rank == 0 else None
+    st_per_step = T * B * world
+    value = st_per_step * args.steps / (total_ms * 1e-3)
+
+    # --- per-kernel durations of the same step (second pass, CUDA events around every kernel)
+    lib.rxmet_reset_kernel_timing()
+    lib.rxmet_set_kernel_timing(1)
+    k_steps = min(args.steps, 10)
+    timed(resident, k_steps, 1)
+    names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "inputGrad",
+             "reduceSplits", "columnSums", "channelPrep", "dequantCodes", "transposeMatrix"]
+    per_kernel = {}
+    for n in names:
+        ms, cnt = C.c_double(), C.c_longlong()
+        lib.rxmet_get_kernel_timing(n.encode(), C.byref(ms), C.byref(cnt))
+        if cnt.value:
+            per_kernel[n] = (ms.value, cnt.value)
+    lib.rxmet_set_kernel_timing(0)
+    top = max(per_kernel, key=lambda n: per_kernel[n][0])
+    top_ms = per_kernel[top][0] / per_kernel[top][1]
+    peak, peak_kind = _peaks()
+    algo = _algo_bytes_per_st(I, H) * T * B
+    achieved = algo / (top_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "kernel_ms": top_ms, "algorithmic_bytes": algo,
+                "kernel_ms_per_step": {n: v[0] / k_steps for n, v in per_kernel.items()}}
+
+    # --- end-to-end leg through the reference-facing module
+    W, R, bw, br = eng.W, eng.R, eng.bw, eng.br
+    qp = eng.params
+    x_dev = torch.empty((T, B, I), device=device)
+    y_dev = torch.empty((T, B, H), device=device)
+    losses = []
+
+    def e2e(i):
+        x_dev.copy_(xs_host[i % n_sets], non_blocking=True)
+        y_dev.copy_(ys_host[i % n_sets], non_blocking=True)
+        out = ops.forward_quant_int_storage(True, T, B, I, H, W, R, bw, br, x_dev, None, qp)
+        h, v = out[0], out[1]
+        diff = h[1:] - y_dev
+        loss = diff.square().mean()
+        dh_new = torch.zeros_like(h)
+        dh_new[1:] = diff * (2.0 / diff.numel())
+        dx, dW, dR, dbw, dbr, _ = ops.backward_quant_int_storage(T, B, I, H, *out[2:7], dh_new, h, v, qp, *out[7:])
+        grads = [dW, dR, dbw, dbr]
+        if world > 1:
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat)
+            flat.div_(world)
+            o = 0
+            for g in grads:
+                g.copy_(flat[o:o + g.numel()].view_as(g)); o += g.numel()
+        for p_, g in zip((W, R, bw, br), grads):
+            p_.add_(g, alpha=-lr)
+        losses.append(float(loss.item()))  # device -> host read of the step's result
+
+    e2e_steps = min(args.steps, 20)
+    e2e_ms = timed(e2e, e2e_steps, min(args.warmup, 3))
+    e2e_value = st_per_step * e2e_steps / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        cpu = None
+        if world == 1:
+            v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
+            cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 codes / int32 accumulate fwd, fp32 bwd",
+            "data": "synthetic",
+            "config": {"workload": "gru_qat_step", **WORKLOAD, "global_batch": B * world, "parallelism": f"dp{world}",
+                       "quant": "W8 symmetric per-channel, A8 asymmetric, integer carrier", "l2": "flushed between steps",
+                       "kernel_timing": "second pass of the same step with CUDA events around every kernel"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
+                    "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
+                    "final_loss": losses[-1] if losses else None},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        if args.warmup < 3:
+            args.warmup = 3
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -43,6 +43,16 @@ RXMET_API const char *rxmet_version(void);
 /* Number of kernels this library has launched in this process so far. */
 RXMET_API uint64_t rxmet_kernel_launch_count(void);
 
+/* Per-kernel timing, off by default.  While enabled every kernel launch of the
+ * library is bracketed by CUDA events on its stream;
+ * rxmet_get_kernel_timing waits for the recorded events and returns the summed
+ * duration and the launch count of the kernel with that name since the last
+ * reset.  Plays the role of the reference's caller-supplied timing events
+ * (operators/quant-lstm/include/lstm/forward_quantized_fp_cuda.h:119-131). */
+RXMET_API int rxmet_set_kernel_timing(int enabled);
+RXMET_API int rxmet_get_kernel_timing(const char *kernel_name, double *total_ms, long long *launches);
+RXMET_API int rxmet_reset_kernel_timing(void);
+
 /* ------------------------------------------------------------------------ */
 /* QuantGRU: configuration and encodings                                     */
 /* ------------------------------------------------------------------------ */

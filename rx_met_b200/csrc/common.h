@@ -1,0 +1,128 @@
+// Shared host-side helpers of the CUDA library: error reporting, launch
+// accounting and CUDA call checking.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+
+#include "rxmet_b200.h"
+
+namespace rxmet {
+
+// Thread-local message returned by rxmet_last_error().
+std::string &lastError();
+// Count of kernels launched by this library in this process.
+std::atomic<uint64_t> &launchCounter();
+
+struct Error : std::runtime_error {
+    int status;
+    Error(int s, const std::string &m) : std::runtime_error(m), status(s) {}
+};
+
+[[noreturn]] inline void fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    throw Error(status, buf);
+}
+
+#define RXMET_CUDA(expr)                                                                   \
+    do {                                                                                   \
+        cudaError_t err__ = (expr);                                                        \
+        if (err__ != cudaSuccess)                                                          \
+            ::rxmet::fail(RXMET_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+    } while (0)
+
+// Called after every kernel launch: counts it and surfaces launch errors.
+inline void afterLaunch(const char *name) {
+    launchCounter().fetch_add(1, std::memory_order_relaxed);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) fail(RXMET_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(err));
+}
+
+#define RXMET_REQUIRE(cond, ...)                                            \
+    do {                                                                    \
+        if (!(cond)) ::rxmet::fail(RXMET_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+// Runs f and converts exceptions into status codes + last-error text.
+template <class F>
+int guarded(F &&f) {
+    try {
+        f();
+        return RXMET_OK;
+    } catch (const Error &e) {
+        lastError() = e.what();
+        return e.status;
+    } catch (const std::exception &e) {
+        lastError() = e.what();
+        return RXMET_ERR_INVALID_ARGUMENT;
+    }
+}
+
+// Optional per-kernel timing (off by default): while enabled, every launcher brackets its kernel
+// with CUDA events on the launching stream; rxmet_get_kernel_timing() resolves and sums them.
+bool kernelTimingEnabled();
+void kernelTimingBegin(const char *name, cudaStream_t stream, cudaEvent_t *start, cudaEvent_t *stop);
+void kernelTimingEnd(const char *name, cudaStream_t stream, cudaEvent_t start, cudaEvent_t stop);
+
+class KernelTimer {
+   public:
+    KernelTimer(const char *name, cudaStream_t stream) : name_(name), stream_(stream) {
+        if (kernelTimingEnabled()) kernelTimingBegin(name_, stream_, &start_, &stop_);
+    }
+    ~KernelTimer() {
+        if (start_) kernelTimingEnd(name_, stream_, start_, stop_);
+    }
+    KernelTimer(const KernelTimer &) = delete;
+    KernelTimer &operator=(const KernelTimer &) = delete;
+
+   private:
+    const char *name_;
+    cudaStream_t stream_;
+    cudaEvent_t start_ = nullptr, stop_ = nullptr;
+};
+
+inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Carves aligned sub-buffers out of a caller-provided device workspace.
+class Workspace {
+   public:
+    Workspace(void *base, size_t bytes) : base_(static_cast<char *>(base)), bytes_(bytes) {}
+    template <class T>
+    T *take(size_t count) {
+        const size_t off = alignUp(used_, 256);
+        const size_t need = off + count * sizeof(T);
+        if (base_ == nullptr || need > bytes_)
+            fail(RXMET_ERR_WORKSPACE, "workspace too small: need at least %zu bytes, have %zu", need, bytes_);
+        used_ = need;
+        return reinterpret_cast<T *>(base_ + off);
+    }
+    size_t used() const { return used_; }
+
+   private:
+    char *base_;
+    size_t bytes_;
+    size_t used_ = 0;
+};
+
+// Same arithmetic without a buffer, for the workspace-size query.
+class WorkspaceSizer {
+   public:
+    template <class T>
+    void take(size_t count) { used_ = alignUp(used_, 256) + count * sizeof(T); }
+    size_t used() const { return alignUp(used_, 256); }
+
+   private:
+    size_t used_ = 0;
+};
+
+}  // namespace rxmet

@@ -1,0 +1,394 @@
+// GRU backward through time (float arithmetic on dequantized saved values, straight-through
+// clamp masks) and the weight / input / bias gradients.
+//
+//   recurrentBackward : ONE launch for all T steps in reverse.  Like the forward, each CTA owns a
+//                       batch tile for the whole sequence (dh is independent per sequence) and
+//                       keeps R resident in shared memory; per step it forms dp/dq with every
+//                       mask applied and then dh += R dq.
+//   gemmTN + reduce   : dW = x^T dp and dR = h^T dq as split-K tile GEMMs whose partial sums are
+//                       added in a fixed order, so gradients are reproducible run to run.
+//   inputGrad         : dx = dp W^T with the input clamp mask.
+//   columnSums        : bias gradients as fixed-order column sums (the reference uses float
+//                       atomics here, gru_backward_gpu_quant.cu:258-264).
+//
+// Reference: operators/quant-gru/src/gru_backward_gpu_quant.cu:93-493 and, for the float path,
+// src/gru_backward_gpu.cu.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.h"
+#include "gru_backward.h"
+
+namespace rxmet {
+namespace gru {
+namespace {
+
+__device__ __forceinline__ float keepOf(const uint8_t *m, size_t i) { return m ? static_cast<float>(m[i]) : 1.0f; }
+
+// out[i] = (codes[i] - zp) * scale, scale per column when channelScale is set
+// (gru_interface_binding.cc:842-856).
+__global__ void dequantCodes(const int32_t *__restrict__ q, size_t n, int cols, const float *__restrict__ channelScale,
+                             float scalarScale, int32_t zp, float *__restrict__ out) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float s = channelScale ? channelScale[i % cols] : scalarScale;
+        out[i] = (static_cast<float>(q[i]) - static_cast<float>(zp)) * s;
+    }
+}
+
+struct BackwardArgs {
+    int T, B, H;
+    int weightsInSmem;
+    int parts;            // the 3H contraction of dh += R dq is split into this many thread groups
+    const float *RT;      // [3H][H] : R transposed
+    const float *h;       // [T+1][B][H]
+    const float *v;       // [T][B][4H]
+    const float *dhNew;   // [T+1][B][H]
+    float *dp, *dq;       // [T][B][3H]
+    float *dh0;           // [B][H]
+    const uint8_t *mIh, *mHh, *mGateIn, *mGateOut, *mH, *mH0;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(768) recurrentBackward(const __grid_constant__ BackwardArgs a) {
+    const int H = a.H, C = 3 * a.H, P = a.parts;
+    extern __shared__ float smemB[];
+    float *dhS = smemB;                   // [BT][H]   gradient flowing to the previous step
+    float *dqS = dhS + BT * H;            // [BT][C]
+    float *partS = dqS + BT * C;          // [P][BT][H]
+    float *RS = partS + P * BT * H;       // [C][H] when resident
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+
+    const float *RT = a.RT;
+    if (a.weightsInSmem) {
+        for (int i = tid; i < C * H; i += nthreads) RS[i] = a.RT[i];
+        RT = RS;
+    }
+    for (int i = tid; i < BT * H; i += nthreads) dhS[i] = 0.0f;
+    for (int i = tid; i < BT * C; i += nthreads) dqS[i] = 0.0f;
+    __syncthreads();
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        // ---- pointwise derivative with masks (gru_backward_gpu_quant.cu:110-240)
+        for (int i = tid; i < nb * H; i += nthreads) {
+            const int b = i / H, j = i % H;
+            const size_t row = rowBase + b;
+            const size_t hi = row * H + j, gi = row * C + j;
+            const float *vRow = a.v + row * 4 * H;
+            float dhTotal = a.dhNew[hi + static_cast<size_t>(a.B) * H] + dhS[b * H + j];
+            dhTotal *= keepOf(a.mH, hi);
+            const float z = vRow[j], r = vRow[H + j], g = vRow[2 * H + j], qg = vRow[3 * H + j];
+            dhS[b * H + j] = z * dhTotal;
+            const float dg = (1.0f - z) * dhTotal;
+            const float dz = (a.h[hi] - g) * dhTotal;
+            float dpG = (1.0f - g * g) * dg;
+            dpG *= keepOf(a.mGateOut, gi + 2 * H);
+            dpG *= keepOf(a.mGateIn, gi + 2 * H);
+            const float dqG = dpG * r;
+            const float dr = dpG * qg;
+            const float dpR = (r * (1.0f - r)) * dr;
+            const float dpZ = (z * (1.0f - z)) * dz;
+            const float kz = keepOf(a.mGateOut, gi) * keepOf(a.mGateIn, gi);
+            const float kr = keepOf(a.mGateOut, gi + H) * keepOf(a.mGateIn, gi + H);
+            const float pz = dpZ * kz * keepOf(a.mIh, gi);
+            const float pr = dpR * kr * keepOf(a.mIh, gi + H);
+            const float pg = dpG * keepOf(a.mIh, gi + 2 * H);
+            const float qz = dpZ * kz * keepOf(a.mHh, gi);
+            const float qr = dpR * kr * keepOf(a.mHh, gi + H);
+            const float qn = dqG * keepOf(a.mHh, gi + 2 * H);
+            a.dp[gi] = pz; a.dp[gi + H] = pr; a.dp[gi + 2 * H] = pg;
+            a.dq[gi] = qz; a.dq[gi + H] = qr; a.dq[gi + 2 * H] = qn;
+            float *dqRow = dqS + b * C;
+            dqRow[j] = qz; dqRow[H + j] = qr; dqRow[2 * H + j] = qn;
+        }
+        __syncthreads();
+        // ---- dh[b,k] += sum_c R[k,c] dq[b,c], contraction split over P thread groups
+        for (int item = tid; item < H * P; item += nthreads) {
+            const int k = item % H, part = item / H;
+            const int c0 = static_cast<int>(static_cast<long long>(C) * part / P);
+            const int c1 = static_cast<int>(static_cast<long long>(C) * (part + 1) / P);
+            float acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+            for (int c = c0; c < c1; ++c) {
+                const float w = RT[static_cast<size_t>(c) * H + k];
+#pragma unroll
+                for (int b = 0; b < BT; ++b) acc[b] = fmaf(w, dqS[b * C + c], acc[b]);
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b) partS[(part * BT + b) * H + k] = acc[b];
+        }
+        __syncthreads();
+        for (int i = tid; i < BT * H; i += nthreads) {
+            float s = dhS[i];
+            for (int p = 0; p < P; ++p) s += partS[p * BT * H + i];
+            dhS[i] = s;
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < nb * H; i += nthreads) {
+        const size_t o = static_cast<size_t>(b0 + i / H) * H + (i % H);
+        a.dh0[o] = dhS[i] * keepOf(a.mH0, o);
+    }
+}
+
+__global__ void transposeMatrix(const float *__restrict__ in, int rows, int cols, float *__restrict__ out) {
+    __shared__ float tile[32][33];
+    const int x = blockIdx.x * 32 + threadIdx.x, y0 = blockIdx.y * 32;
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y)
+        if (x < cols && y0 + dy < rows) tile[dy][threadIdx.x] = in[static_cast<size_t>(y0 + dy) * cols + x];
+    __syncthreads();
+    const int ox = blockIdx.y * 32 + threadIdx.x, oy0 = blockIdx.x * 32;
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y)
+        if (ox < rows && oy0 + dy < cols) out[static_cast<size_t>(oy0 + dy) * rows + ox] = tile[threadIdx.x][dy];
+}
+
+// partial[s][m][n] = sum over the s-th K chunk of A[k][m] * B[k][n].  64x64 tile, 16-deep K
+// steps, 4x4 outputs per thread.
+constexpr int kTile = 64, kDepth = 16;
+__global__ void __launch_bounds__(256) gemmTN(const float *__restrict__ A, const float *__restrict__ Bm, int K, int M,
+                                              int N, int chunk, float *__restrict__ partial) {
+    __shared__ float As[kDepth][kTile + 4];
+    __shared__ float Bs[kDepth][kTile + 4];
+    const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+    const int kBegin = blockIdx.z * chunk, kEnd = min(K, kBegin + chunk);
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4] = {};
+    for (int k0 = kBegin; k0 < kEnd; k0 += kDepth) {
+        for (int i = threadIdx.x; i < kDepth * kTile; i += 256) {
+            const int kk = i / kTile, c = i % kTile;
+            const int k = k0 + kk;
+            As[kk][c] = (k < kEnd && m0 + c < M) ? A[static_cast<size_t>(k) * M + m0 + c] : 0.0f;
+            Bs[kk][c] = (k < kEnd && n0 + c < N) ? Bm[static_cast<size_t>(k) * N + n0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kDepth; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[kk][ty * 4 + i]; bv[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float *out = partial + static_cast<size_t>(blockIdx.z) * M * N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) out[static_cast<size_t>(m) * N + n] = acc[i][j];
+        }
+}
+
+// out[i] = mask[i] * sum_s partial[s][i], s ascending.
+__global__ void reduceSplits(const float *__restrict__ partial, int splits, size_t n, const uint8_t *__restrict__ mask,
+                             float *__restrict__ out) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float s = 0.0f;
+        for (int p = 0; p < splits; ++p) s += partial[static_cast<size_t>(p) * n + i];
+        out[i] = s * keepOf(mask, i);
+    }
+}
+
+// dx[n][i] = mask * sum_c dp[n][c] * W[i][c]
+constexpr int kGradRows = 16;
+__global__ void inputGrad(const float *__restrict__ dp, int rows, int C, const float *__restrict__ W, int I,
+                          const uint8_t *__restrict__ mask, float *__restrict__ dx) {
+    extern __shared__ float smemB[];
+    float *dps = smemB;  // [kGradRows][C + 1]
+    const int row0 = blockIdx.x * kGradRows, nRows = min(kGradRows, rows - row0);
+    for (int i = threadIdx.x; i < kGradRows * C; i += blockDim.x) {
+        const int r = i / C, c = i % C;
+        dps[r * (C + 1) + c] = r < nRows ? dp[static_cast<size_t>(row0 + r) * C + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < nRows * I; o += blockDim.x) {
+        const int r = o / I, i = o % I;
+        const float *w = W + static_cast<size_t>(i) * C;
+        const float *d = dps + r * (C + 1);
+        float acc = 0.0f;
+        for (int c = 0; c < C; ++c) acc = fmaf(d[c], w[c], acc);
+        const size_t out = static_cast<size_t>(row0 + r) * I + i;
+        dx[out] = acc * keepOf(mask, out);
+    }
+}
+
+// partial[s][c] = sum over the s-th row chunk of g[n][c]; blockIdx.y selects dp or dq.
+__global__ void columnSums(const float *__restrict__ dp, const float *__restrict__ dq, int rows, int C, int chunk,
+                           float *__restrict__ partial) {
+    const float *g = blockIdx.y == 0 ? dp : dq;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int n0 = blockIdx.z * chunk, n1 = min(rows, n0 + chunk);
+    float s = 0.0f;
+    for (int n = n0; n < n1; ++n) s += g[static_cast<size_t>(n) * C + c];
+    partial[(static_cast<size_t>(blockIdx.y) * gridDim.z + blockIdx.z) * C + c] = s;
+}
+
+int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
+
+int splitsFor(int K, int tiles) {
+    const int want = std::max(1, (2 * 148 + tiles - 1) / tiles);
+    return std::max(1, std::min(want, (K + 255) / 256));
+}
+
+constexpr int kBiasSplits = 64;
+
+}  // namespace
+
+size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
+    const size_t rows = static_cast<size_t>(T) * B, C = 3 * static_cast<size_t>(H);
+    WorkspaceSizer ws;
+    ws.take<float>(rows * C);          // dp
+    ws.take<float>(rows * C);          // dq
+    ws.take<float>(C * H);             // R transposed
+    ws.take<float>(static_cast<size_t>(I) * C);  // W real-valued
+    ws.take<float>(static_cast<size_t>(H) * C);  // R real-valued
+    ws.take<float>(rows * I);          // x real-valued
+    ws.take<float>(12 * C);            // per-channel block
+    const size_t splitW = splitsFor(static_cast<int>(rows), ((I + kTile - 1) / kTile) * ((static_cast<int>(C) + kTile - 1) / kTile));
+    const size_t splitR = splitsFor(static_cast<int>(rows), ((H + kTile - 1) / kTile) * ((static_cast<int>(C) + kTile - 1) / kTile));
+    ws.take<float>(splitW * I * C);
+    ws.take<float>(splitR * H * C);
+    ws.take<float>(2 * kBiasSplits * C);
+    return ws.used() + 4096;
+}
+
+void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 3 * H;
+    const size_t rows = static_cast<size_t>(T) * B;
+    Workspace ws(workspace, workspaceBytes);
+    float *dp = ws.take<float>(rows * C);
+    float *dq = ws.take<float>(rows * C);
+    float *RT = ws.take<float>(static_cast<size_t>(C) * H);
+    const rxmet_gru_masks none{};
+    const rxmet_gru_masks &mk = call.masks ? *call.masks : none;
+
+    const float *W = call.W, *R = call.R, *x = call.x;
+    if (call.W_q) {  // QAT path: rebuild the real-valued operands from the saved codes
+        RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
+        const Exec &e = *call.exec;
+        float *Wf = ws.take<float>(static_cast<size_t>(I) * C);
+        float *Rf = ws.take<float>(static_cast<size_t>(H) * C);
+        float *xf = ws.take<float>(rows * I);
+        float *chan = ws.take<float>(2 * static_cast<size_t>(C));
+        RXMET_CUDA(cudaMemcpyAsync(chan, e.chan.eff_W.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        RXMET_CUDA(cudaMemcpyAsync(chan + C, e.chan.eff_R.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        {
+            KernelTimer timer__("dequantCodes", st);
+            dequantCodes<<<gridFor(static_cast<size_t>(I) * C, 256), 256, 0, st>>>(call.W_q, static_cast<size_t>(I) * C, C, chan, 0.f, 0, Wf);
+        }
+        afterLaunch("dequantCodes");
+        {
+            KernelTimer timer__("dequantCodes", st);
+            dequantCodes<<<gridFor(static_cast<size_t>(H) * C, 256), 256, 0, st>>>(call.R_q, static_cast<size_t>(H) * C, C, chan + C, 0.f, 0, Rf);
+        }
+        afterLaunch("dequantCodes");
+        {
+            KernelTimer timer__("dequantCodes", st);
+            dequantCodes<<<gridFor(rows * I, 256), 256, 0, st>>>(call.x_q, rows * I, I, nullptr, e.gate.eff[RXMET_GRU_X],
+                                                                e.gate.zp[RXMET_GRU_X], xf);
+        }
+        afterLaunch("dequantCodes");
+        W = Wf; R = Rf; x = xf;
+    }
+
+    {
+        KernelTimer timer__("transposeMatrix", st);
+        transposeMatrix<<<dim3((C + 31) / 32, (H + 31) / 32), dim3(32, 8), 0, st>>>(R, H, C, RT);
+    }
+    afterLaunch("transposeMatrix");
+
+    BackwardArgs a{};
+    a.T = T; a.B = B; a.H = H;
+    a.RT = RT; a.h = call.h; a.v = call.v; a.dhNew = call.dh_new; a.dp = dp; a.dq = dq; a.dh0 = call.dh0;
+    a.mIh = mk.weight_ih_linear; a.mHh = mk.weight_hh_linear; a.mGateIn = mk.gate_input;
+    a.mGateOut = mk.gate_output; a.mH = mk.h; a.mH0 = mk.h0;
+    int device = 0, smemMax = 0, sms = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int block = std::min(std::max((C + 31) / 32 * 32, 128), 768);
+    a.parts = std::max(1, std::min(block / std::max(H, 1), 8));
+    const int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+    auto launch = [&](auto kernel, int BT) {
+        const size_t base = sizeof(float) * (static_cast<size_t>(BT) * H + static_cast<size_t>(BT) * C +
+                                             static_cast<size_t>(a.parts) * BT * H);
+        const size_t full = base + sizeof(float) * static_cast<size_t>(C) * H;
+        a.weightsInSmem = full <= static_cast<size_t>(smemMax) ? 1 : 0;
+        const size_t smem = a.weightsInSmem ? full : base;
+        if (smem > static_cast<size_t>(smemMax))
+            fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
+        RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        {
+            KernelTimer timer__("recurrentBackward", st);
+            kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
+        }
+        afterLaunch("recurrentBackward");
+    };
+    if (bt == 4) launch(recurrentBackward<4>, 4);
+    else if (bt == 2) launch(recurrentBackward<2>, 2);
+    else launch(recurrentBackward<1>, 1);
+
+    // dx
+    {
+        const size_t smem = sizeof(float) * kGradRows * (C + 1);
+        RXMET_CUDA(cudaFuncSetAttribute(inputGrad, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        {
+            KernelTimer timer__("inputGrad", st);
+            inputGrad<<<static_cast<int>((rows + kGradRows - 1) / kGradRows), 256, smem, st>>>(dp, static_cast<int>(rows), C, W, I, mk.x, call.dx);
+        }
+        afterLaunch("inputGrad");
+    }
+    // dW, dR
+    auto weightGrad = [&](const float *A, int M, const float *G, const uint8_t *mask, float *out) {
+        const int tilesM = (M + kTile - 1) / kTile, tilesN = (C + kTile - 1) / kTile;
+        const int splits = splitsFor(static_cast<int>(rows), tilesM * tilesN);
+        const int chunk = (static_cast<int>(rows) + splits - 1) / splits;
+        float *partial = ws.take<float>(static_cast<size_t>(splits) * M * C);
+        {
+            KernelTimer timer__("gemmTN", st);
+            gemmTN<<<dim3(tilesN, tilesM, splits), 256, 0, st>>>(A, G, static_cast<int>(rows), M, C, chunk, partial);
+        }
+        afterLaunch("gemmTN");
+        {
+            KernelTimer timer__("reduceSplits", st);
+            reduceSplits<<<gridFor(static_cast<size_t>(M) * C, 256), 256, 0, st>>>(partial, splits, static_cast<size_t>(M) * C, mask, out);
+        }
+        afterLaunch("reduceSplits");
+    };
+    weightGrad(x, I, dp, mk.W, call.dW);
+    weightGrad(call.h, H, dq, mk.R, call.dR);
+    // bias gradients
+    {
+        float *partial = ws.take<float>(2 * static_cast<size_t>(kBiasSplits) * C);
+        const int chunk = (static_cast<int>(rows) + kBiasSplits - 1) / kBiasSplits;
+        {
+            KernelTimer timer__("columnSums", st);
+            columnSums<<<dim3((C + 127) / 128, 2, kBiasSplits), 128, 0, st>>>(dp, dq, static_cast<int>(rows), C, chunk, partial);
+        }
+        afterLaunch("columnSums");
+        {
+            KernelTimer timer__("reduceSplits", st);
+            reduceSplits<<<gridFor(C, 128), 128, 0, st>>>(partial, kBiasSplits, C, mk.bw, call.dbw);
+        }
+        afterLaunch("reduceSplits");
+        {
+            KernelTimer timer__("reduceSplits", st);
+            reduceSplits<<<gridFor(C, 128), 128, 0, st>>>(partial + static_cast<size_t>(kBiasSplits) * C, kBiasSplits, C, mk.br, call.dbr);
+        }
+        afterLaunch("reduceSplits");
+    }
+}
+
+}  // namespace gru
+}  // namespace rxmet

@@ -1,0 +1,129 @@
+// Device-side integer primitives of the QuantGRU integer carrier.  Bit-level
+// behaviour follows operators/quant-gru/include/quantize_ops_helper.h of the
+// reference (cited per function); the code is organised for the GPU: 32-bit
+// fast paths where the operands provably fit, tables in shared memory.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "gru_params.h"
+
+namespace rxmet {
+namespace gru {
+
+// round_half_even(x / 2^n) on the magnitude, sign restored afterwards; n <= 0
+// shifts left (quantize_ops_helper.h:201-224).
+__device__ __forceinline__ int64_t rshiftRound(int64_t x, int n) {
+    if (n <= 0) return x << (-n);
+    const bool neg = x < 0;
+    const uint64_t a = neg ? static_cast<uint64_t>(-x) : static_cast<uint64_t>(x);
+    const uint64_t q = a >> n;
+    const uint64_t r = a & ((1ull << n) - 1ull);
+    const uint64_t half = 1ull << (n - 1);
+    const uint64_t up = (r > half) || (r == half && (q & 1ull));
+    const int64_t res = static_cast<int64_t>(q + up);
+    return neg ? -res : res;
+}
+
+// quantize_ops_helper.h:242-248
+__device__ __forceinline__ int64_t applyRescale(int64_t x, Rescale r) {
+    return rshiftRound(x * static_cast<int64_t>(r.mult), r.shift);
+}
+
+// quantize_ops_helper.h:267-278 ; keep = 1 when the value was inside the grid.
+__device__ __forceinline__ int32_t clampCode(int32_t v, int32_t lo, int32_t hi, uint8_t &keep) {
+    keep = (v < lo || v > hi) ? 0 : 1;
+    return max(lo, min(v, hi));
+}
+
+// Float -> code: divide, round half even, add the zero point afterwards,
+// saturate (quantize_ops_helper.h:133-140,280-292,357-365).  The rounded
+// quotient is saturated to +-2^31 before the integer add; that cannot change
+// the clamped result because |zp| < 2^31 and the grid is at most 32 bit.
+__device__ __forceinline__ int32_t quantizeValue(float v, float scale, int32_t zp, int32_t lo, int32_t hi,
+                                                 uint8_t &keep) {
+    float r = rintf(v / scale);
+    r = fminf(fmaxf(r, -4294967296.0f), 4294967296.0f);
+    const int64_t code = static_cast<int64_t>(r) + zp;
+    keep = (code < lo || code > hi) ? 0 : 1;
+    return static_cast<int32_t>(code < lo ? lo : (code > hi ? hi : code));
+}
+
+// 16-segment table: first segment whose threshold exceeds q_x, else the last
+// (quantize_ops_helper.h:503-532).
+__device__ __forceinline__ int32_t lutEval(int32_t qx, const Lut &lut) {
+    int seg = kSegments - 1;
+#pragma unroll
+    for (int i = kSegments - 2; i >= 0; --i) seg = (qx < lut.threshold[i]) ? i : seg;
+    const int64_t bx = static_cast<int64_t>(lut.q_b[seg]) * static_cast<int64_t>(qx - lut.zp_x);
+    const int n = lut.n_bx[seg];
+    const int32_t term = (n >= 0) ? static_cast<int32_t>(rshiftRound(bx, n)) : static_cast<int32_t>(bx << (-n));
+    return term + lut.term_c[seg];
+}
+
+struct GateMasks {
+    uint8_t in[3];   // update, reset, new : gate-input clamp
+    uint8_t out[3];  // update, reset, new : gate-output clamp
+    uint8_t h;       // hidden-state clamp
+};
+
+struct GateCodes {
+    int32_t z, r, n, h;
+};
+
+// One (batch, hidden) element of a GRU step on the integer grids
+// (quantize_ops_helper.h:683-1023).  ih* / hh* are the linear-stage codes of
+// the three gates, hOld the previous hidden code.
+__device__ __forceinline__ GateCodes gruCell(int32_t ihz, int32_t ihr, int32_t ihn, int32_t hhz, int32_t hhr,
+                                             int32_t hhn, int32_t hOld, const GateExec &g, GateMasks &m) {
+    const int32_t zpIh = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], zpHh = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
+    GateCodes c;
+    {   // update gate
+        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihz) - zpIh, g.ih_to_update));
+        const int32_t b = static_cast<int32_t>(applyRescale(static_cast<int64_t>(hhz) - zpHh, g.hh_to_update));
+        const int32_t pre = clampCode(a + b + g.zp[RXMET_GRU_UPDATE_GATE_INPUT], g.qlo[RXMET_GRU_UPDATE_GATE_INPUT],
+                                      g.qhi[RXMET_GRU_UPDATE_GATE_INPUT], m.in[0]);
+        c.z = clampCode(lutEval(pre, g.lut_update), g.qlo[RXMET_GRU_UPDATE_GATE_OUTPUT],
+                        g.qhi[RXMET_GRU_UPDATE_GATE_OUTPUT], m.out[0]);
+    }
+    {   // reset gate
+        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihr) - zpIh, g.ih_to_reset));
+        const int32_t b = static_cast<int32_t>(applyRescale(static_cast<int64_t>(hhr) - zpHh, g.hh_to_reset));
+        const int32_t pre = clampCode(a + b + g.zp[RXMET_GRU_RESET_GATE_INPUT], g.qlo[RXMET_GRU_RESET_GATE_INPUT],
+                                      g.qhi[RXMET_GRU_RESET_GATE_INPUT], m.in[1]);
+        c.r = clampCode(lutEval(pre, g.lut_reset), g.qlo[RXMET_GRU_RESET_GATE_OUTPUT],
+                        g.qhi[RXMET_GRU_RESET_GATE_OUTPUT], m.out[1]);
+    }
+    {   // candidate: the reset product goes straight to the gate-input grid
+        const int64_t prod = (static_cast<int64_t>(c.r) - g.zp[RXMET_GRU_RESET_GATE_OUTPUT]) *
+                             (static_cast<int64_t>(hhn) - zpHh);
+        const int32_t rh = static_cast<int32_t>(applyRescale(prod, g.rh_to_new));
+        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihn) - zpIh, g.ih_to_new));
+        const int32_t pre = clampCode(a + rh + g.zp[RXMET_GRU_NEW_GATE_INPUT], g.qlo[RXMET_GRU_NEW_GATE_INPUT],
+                                      g.qhi[RXMET_GRU_NEW_GATE_INPUT], m.in[2]);
+        c.n = clampCode(lutEval(pre, g.lut_new), g.qlo[RXMET_GRU_NEW_GATE_OUTPUT], g.qhi[RXMET_GRU_NEW_GATE_OUTPUT],
+                        m.out[2]);
+    }
+    {   // h' = z*h + (1-z)*n on the h grid, one rounding for the sum
+        const int32_t zpH = g.zp[RXMET_GRU_H];
+        const int32_t nAligned =
+            static_cast<int32_t>(applyRescale(static_cast<int64_t>(c.n) - g.zp[RXMET_GRU_NEW_GATE_OUTPUT], g.new_to_h)) + zpH;
+        const int64_t oldPart = (static_cast<int64_t>(c.z) - g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]) *
+                                (static_cast<int64_t>(hOld) - zpH);
+        const int64_t newPart = (static_cast<int64_t>(g.quant_one) - c.z) * (static_cast<int64_t>(nAligned) - zpH);
+        const int32_t hNew = static_cast<int32_t>(applyRescale(oldPart + newPart, g.update_old_to_h)) + zpH;
+        c.h = clampCode(hNew, g.qlo[RXMET_GRU_H], g.qhi[RXMET_GRU_H], m.h);
+    }
+    return c;
+}
+
+// Accumulate a[k] * w[k] exactly.  int8 x int8 packs four products per dp4a.
+template <class AccT>
+__device__ __forceinline__ void macCodes(AccT &acc, int32_t w, int32_t a) {
+    acc += static_cast<AccT>(w) * static_cast<AccT>(a);
+}
+
+}  // namespace gru
+}  // namespace rxmet

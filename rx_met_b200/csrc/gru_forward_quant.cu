@@ -1,0 +1,542 @@
+// Quantized GRU forward on the integer carrier.
+//
+// Data flow (one direction, one call):
+//   1. quantizeTensor       : float master weights / biases / x / h0 -> integer codes in the
+//                             narrowest storage class, optional int32 copy and clamp mask.
+//   2. channelPrep          : per output channel, zero-point compensation sum_k W[k,c]*zp and
+//                             the bias term already moved to the accumulator grid.
+//   3. inputLinear          : ih[n,c] for all T*B rows at once (the recurrence does not need it
+//                             step by step), stored as 16-bit codes when the grid allows.
+//   4. recurrentForward     : ONE launch for all T steps.  Sequences are independent, so each
+//                             CTA owns a small batch tile and keeps the whole recurrent weight
+//                             matrix resident in shared memory for the entire sequence; no
+//                             grid-wide barrier exists.  Each step is a tile GEMM (dp4a for
+//                             8-bit grids), the hh-linear epilogue, the integer gates and the
+//                             dequantized outputs, fused.
+//
+// Reference: operators/quant-gru/src/gru_forward_gpu_quant.cu (per-step GEMM + pointwise
+// launches) and src/gru_forward_cpu_quant.cc (CPU integer core).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <type_traits>
+#include <vector>
+
+#include "common.h"
+#include "gru_device.cuh"
+#include "gru_forward_quant.h"
+
+namespace rxmet {
+namespace gru {
+namespace {
+
+// ---- exact dot products ---------------------------------------------------
+
+// Generic: one code per element, 64-bit accumulation (never overflows).
+template <class WT, class AT>
+struct Dot {
+    using Acc = int64_t;
+    using WWord = WT;
+    using AWord = AT;
+    static constexpr int kPack = 1;
+    static __device__ __forceinline__ void mac(Acc &acc, WWord w, AWord a) {
+        acc += static_cast<int64_t>(w) * static_cast<int64_t>(a);
+    }
+};
+// 8-bit x 8-bit: four codes per 32-bit word, dp4a, 32-bit accumulation.  Exact for K < 2^16.
+template <>
+struct Dot<int8_t, int8_t> {
+    using Acc = int32_t;
+    using WWord = int32_t;
+    using AWord = int32_t;
+    static constexpr int kPack = 4;
+    static __device__ __forceinline__ void mac(Acc &acc, WWord w, AWord a) { acc = __dp4a(w, a, acc); }
+};
+
+__host__ __device__ inline int padTo(int v, int m) { return (v + m - 1) / m * m; }
+
+// ---- 1. quantize ----------------------------------------------------------
+
+// dst layout: row-major [rowsPadded, cols] when pack == 1; [rowsPadded/pack, cols, pack] when the
+// tensor is a packed weight (pack consecutive rows of one column share a word).  For activations
+// (transposedPack == false) rows are samples and cols is the padded feature count.
+template <class CodeT>
+__global__ void quantizeTensor(const float *__restrict__ src, int rows, int cols, int rowsPadded, int colsPadded,
+                               const float *__restrict__ channelScale, float scalarScale, int32_t zp, int32_t lo,
+                               int32_t hi, int weightPack, CodeT *__restrict__ codes, int32_t *__restrict__ codes32,
+                               uint8_t *__restrict__ mask) {
+    const size_t total = static_cast<size_t>(rowsPadded) * colsPadded;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / colsPadded), c = static_cast<int>(i % colsPadded);
+        int32_t q = 0;
+        if (r < rows && c < cols) {
+            const size_t s = static_cast<size_t>(r) * cols + c;
+            uint8_t keep;
+            q = quantizeValue(src[s], channelScale ? channelScale[c] : scalarScale, zp, lo, hi, keep);
+            if (codes32) codes32[s] = q;
+            if (mask) mask[s] = keep;
+        }
+        const size_t d = weightPack > 1
+                             ? (static_cast<size_t>(r / weightPack) * colsPadded + c) * weightPack + (r % weightPack)
+                             : i;
+        codes[d] = static_cast<CodeT>(q);
+    }
+}
+
+// Fills a code tensor with a constant (initial state = zero point).
+template <class CodeT>
+__global__ void fillCodes(CodeT *dst, size_t n, int32_t value) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        dst[i] = static_cast<CodeT>(value);
+}
+
+// int32 codes handed in by the caller -> storage class, padded rows.
+template <class CodeT>
+__global__ void narrowCodes(const int32_t *__restrict__ src, int rows, int cols, int colsPadded,
+                            CodeT *__restrict__ dst) {
+    const size_t total = static_cast<size_t>(rows) * colsPadded;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / colsPadded), c = static_cast<int>(i % colsPadded);
+        dst[i] = c < cols ? static_cast<CodeT>(src[static_cast<size_t>(r) * cols + c]) : CodeT(0);
+    }
+}
+
+// ---- 2. per-channel preparation --------------------------------------------
+
+// comp[c] = zpIn * sum_k W[k,c]; biasAcc[c] = rescale(bias[c]) on the accumulator grid
+// (reference: gru_forward_cpu_quant.cc:76-111,133-134).
+template <class WT, class AT>
+__global__ void channelPrep(const typename Dot<WT, AT>::WWord *__restrict__ w, int kWords, int channels, int32_t zpIn,
+                            const int32_t *__restrict__ biasCodes, const Rescale *__restrict__ biasRescale,
+                            int64_t *__restrict__ comp, int64_t *__restrict__ biasAcc) {
+    using D = Dot<WT, AT>;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    int64_t sum = 0;
+    for (int kk = 0; kk < kWords; ++kk) {
+        const typename D::WWord word = w[static_cast<size_t>(kk) * channels + c];
+        if constexpr (D::kPack == 4) {
+            sum += static_cast<int8_t>(word & 0xff) + static_cast<int8_t>((word >> 8) & 0xff) +
+                   static_cast<int8_t>((word >> 16) & 0xff) + static_cast<int8_t>((word >> 24) & 0xff);
+        } else {
+            sum += static_cast<int64_t>(word);
+        }
+    }
+    comp[c] = sum * zpIn;
+    biasAcc[c] = applyRescale(static_cast<int64_t>(biasCodes[c]), biasRescale[c]);
+}
+
+// Epilogue shared by both linear stages (gru_forward_gpu_quant.cu:163-178).
+__device__ __forceinline__ int32_t linearEpilogue(int64_t acc, int64_t comp, int64_t biasAcc, Rescale r, int32_t zpOut,
+                                                  int32_t lo, int32_t hi, uint8_t &keep) {
+    const int64_t res = applyRescale(acc - comp + biasAcc, r) + zpOut;
+    return clampCode(static_cast<int32_t>(res), lo, hi, keep);
+}
+
+// ---- 3. input projection for all steps -------------------------------------
+
+constexpr int kLinearRows = 8;
+
+template <class WT, class AT, class LT>
+__global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, int rows, int kWords, int channels,
+                            const typename Dot<WT, AT>::WWord *__restrict__ w, const int64_t *__restrict__ comp,
+                            const int64_t *__restrict__ biasAcc, const Rescale *__restrict__ rescale, int32_t zpOut,
+                            int32_t lo, int32_t hi, LT *__restrict__ out, uint8_t *__restrict__ mask) {
+    using D = Dot<WT, AT>;
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    auto *xs = reinterpret_cast<typename D::AWord *>(smemRaw);  // [kLinearRows][kWords]
+    const int row0 = blockIdx.x * kLinearRows;
+    const int nRows = min(kLinearRows, rows - row0);
+    for (int i = threadIdx.x; i < kLinearRows * kWords; i += blockDim.x) {
+        const int r = i / kWords;
+        xs[i] = r < nRows ? x[static_cast<size_t>(row0 + r) * kWords + (i % kWords)] : typename D::AWord(0);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        typename D::Acc acc[kLinearRows];
+#pragma unroll
+        for (int r = 0; r < kLinearRows; ++r) acc[r] = 0;
+        for (int kk = 0; kk < kWords; ++kk) {
+            const typename D::WWord word = w[static_cast<size_t>(kk) * channels + c];
+#pragma unroll
+            for (int r = 0; r < kLinearRows; ++r) D::mac(acc[r], word, xs[r * kWords + kk]);
+        }
+        const int64_t cmp = comp[c], bias = biasAcc[c];
+        const Rescale rs = rescale[c];
+#pragma unroll
+        for (int r = 0; r < kLinearRows; ++r) {
+            if (r < nRows) {
+                uint8_t keep;
+                const int32_t q = linearEpilogue(acc[r], cmp, bias, rs, zpOut, lo, hi, keep);
+                const size_t o = static_cast<size_t>(row0 + r) * channels + c;
+                out[o] = static_cast<LT>(q);
+                if (mask) mask[o] = keep;
+            }
+        }
+    }
+}
+
+// ---- 4. the recurrence: one launch for all steps ----------------------------
+
+struct RecurrentArgs {
+    int T, B, H;
+    int kWords;           // padded H / pack
+    int weightsInSmem;    // 1: R is staged into shared memory once; 0: read through L2
+    const void *R;        // [kWords][3H] words
+    const void *ih;       // LT [T][B][3H]
+    const void *h0;       // AT [B][kWords*pack] initial codes
+    const int64_t *comp;  // [3H]
+    const int64_t *biasAcc;
+    const Rescale *rescale;
+    float *h;             // [T+1][B][H] dequantized (row 0 written here too)
+    float *v;             // [T][B][4H] dequantized
+    int32_t *hq;          // optional [T+1][B][H]
+    int32_t *vq;          // optional [T][B][4H]
+    uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;  // optional
+};
+
+template <class WT, class AT, class LT, int BT>
+__global__ void __launch_bounds__(768)
+recurrentForward(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec gateParam) {
+    using D = Dot<WT, AT>;
+    using WWord = typename D::WWord;
+    using AWord = typename D::AWord;
+    const int H = a.H, C = 3 * a.H, kWords = a.kWords;
+    const int kPadded = kWords * D::kPack;
+
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    size_t off = 0;
+    auto carve = [&](size_t bytes) {
+        unsigned char *p = smemRaw + off;
+        off = (off + bytes + 15) & ~static_cast<size_t>(15);
+        return p;
+    };
+    GateExec &g = *reinterpret_cast<GateExec *>(carve(sizeof(GateExec)));
+    int64_t *compS = reinterpret_cast<int64_t *>(carve(sizeof(int64_t) * C));
+    int64_t *biasS = reinterpret_cast<int64_t *>(carve(sizeof(int64_t) * C));
+    Rescale *rescaleS = reinterpret_cast<Rescale *>(carve(sizeof(Rescale) * C));
+    int32_t *hhS = reinterpret_cast<int32_t *>(carve(sizeof(int32_t) * BT * C));
+    AT *hS = reinterpret_cast<AT *>(carve(sizeof(AT) * BT * kPadded));
+    WWord *RS = reinterpret_cast<WWord *>(carve(a.weightsInSmem ? sizeof(WWord) * kWords * C : 0));
+
+    const int b0 = blockIdx.x * BT;
+    const int nb = min(BT, a.B - b0);
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+
+    // one-time staging
+    for (int i = tid; i < static_cast<int>(sizeof(GateExec) / 4); i += nthreads)
+        reinterpret_cast<int32_t *>(&g)[i] = reinterpret_cast<const int32_t *>(&gateParam)[i];
+    for (int c = tid; c < C; c += nthreads) {
+        compS[c] = a.comp[c];
+        biasS[c] = a.biasAcc[c];
+        rescaleS[c] = a.rescale[c];
+    }
+    const WWord *Rsrc = static_cast<const WWord *>(a.R);
+    if (a.weightsInSmem) {
+        for (int i = tid; i < kWords * C; i += nthreads) RS[i] = Rsrc[i];
+        Rsrc = RS;
+    }
+    const AT *h0 = static_cast<const AT *>(a.h0);
+    for (int i = tid; i < BT * kPadded; i += nthreads) {
+        const int b = i / kPadded;
+        hS[i] = b < nb ? h0[static_cast<size_t>(b0 + b) * kPadded + (i % kPadded)] : AT(0);
+    }
+    __syncthreads();
+
+    const float scaleH = g.eff[RXMET_GRU_H];
+    const int32_t zpH = g.zp[RXMET_GRU_H];
+    // h[0]: the (quantized) initial state, dequantized like every other step
+    for (int i = tid; i < nb * H; i += nthreads) {
+        const int b = i / H, j = i % H;
+        const int32_t q = hS[b * kPadded + j];
+        const size_t o = static_cast<size_t>(b0 + b) * H + j;
+        a.h[o] = static_cast<float>(q - zpH) * scaleH;
+        if (a.hq) a.hq[o] = q;
+    }
+
+    const LT *ih = static_cast<const LT *>(a.ih);
+    const AWord *hWords = reinterpret_cast<const AWord *>(hS);
+    const int32_t zpOut = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
+    const int32_t loOut = g.qlo[RXMET_GRU_WEIGHT_HH_LINEAR], hiOut = g.qhi[RXMET_GRU_WEIGHT_HH_LINEAR];
+
+    for (int t = 0; t < a.T; ++t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;  // first (t, b) row of this tile
+
+        // ---- hh linear: this tile's rows times all 3H columns
+        for (int c = tid; c < C; c += nthreads) {
+            typename D::Acc acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0;
+            for (int kk = 0; kk < kWords; ++kk) {
+                const WWord word = Rsrc[static_cast<size_t>(kk) * C + c];
+#pragma unroll
+                for (int b = 0; b < BT; ++b) D::mac(acc[b], word, hWords[b * kWords + kk]);
+            }
+            const int64_t cmp = compS[c], bias = biasS[c];
+            const Rescale rs = rescaleS[c];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                uint8_t keep;
+                hhS[b * C + c] = linearEpilogue(acc[b], cmp, bias, rs, zpOut, loOut, hiOut, keep);
+                if (a.maskHh && b < nb) a.maskHh[(rowBase + b) * C + c] = keep;
+            }
+        }
+        __syncthreads();
+
+        // ---- gates, state update, outputs
+        for (int i = tid; i < nb * H; i += nthreads) {
+            const int b = i / H, j = i % H;
+            const size_t row = rowBase + b;
+            const LT *ihRow = ih + row * C;
+            const int32_t *hhRow = hhS + b * C;
+            GateMasks m;
+            const int32_t hOld = hS[b * kPadded + j];
+            const GateCodes q = gruCell(ihRow[j], ihRow[H + j], ihRow[2 * H + j], hhRow[j], hhRow[H + j],
+                                        hhRow[2 * H + j], hOld, g, m);
+            hS[b * kPadded + j] = static_cast<AT>(q.h);
+
+            const size_t ho = (row + a.B) * H + j;  // h[t+1]
+            a.h[ho] = static_cast<float>(q.h - zpH) * scaleH;
+            float *vRow = a.v + row * 4 * H;
+            vRow[j] = static_cast<float>(q.z - g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]) * g.eff[RXMET_GRU_UPDATE_GATE_OUTPUT];
+            vRow[H + j] = static_cast<float>(q.r - g.zp[RXMET_GRU_RESET_GATE_OUTPUT]) * g.eff[RXMET_GRU_RESET_GATE_OUTPUT];
+            vRow[2 * H + j] = static_cast<float>(q.n - g.zp[RXMET_GRU_NEW_GATE_OUTPUT]) * g.eff[RXMET_GRU_NEW_GATE_OUTPUT];
+            vRow[3 * H + j] = static_cast<float>(hhRow[2 * H + j] - zpOut) * g.eff[RXMET_GRU_WEIGHT_HH_LINEAR];
+            if (a.hq) a.hq[ho] = q.h;
+            if (a.vq) {
+                int32_t *vq = a.vq + row * 4 * H;
+                vq[j] = q.z; vq[H + j] = q.r; vq[2 * H + j] = q.n; vq[3 * H + j] = hhRow[2 * H + j];
+            }
+            if (a.maskGateIn) {
+                uint8_t *mi = a.maskGateIn + row * C, *mo = a.maskGateOut + row * C;
+                mi[j] = m.in[0]; mi[H + j] = m.in[1]; mi[2 * H + j] = m.in[2];
+                mo[j] = m.out[0]; mo[H + j] = m.out[1]; mo[2 * H + j] = m.out[2];
+                a.maskH[row * H + j] = m.h;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+size_t recurrentSmemBytes(int H, int kWords, int pack, size_t wordBytes, size_t actBytes, int BT, bool weights) {
+    const int C = 3 * H;
+    auto up = [](size_t v) { return (v + 15) & ~static_cast<size_t>(15); };
+    size_t s = up(sizeof(GateExec)) + up(sizeof(int64_t) * C) * 2 + up(sizeof(Rescale) * C) +
+               up(sizeof(int32_t) * BT * C) + up(actBytes * BT * kWords * pack);
+    if (weights) s += up(wordBytes * kWords * C);
+    return s;
+}
+
+int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
+
+template <class CodeT>
+void launchQuantize(cudaStream_t st, const float *src, int rows, int cols, int rowsPadded, int colsPadded,
+                    const float *channelScale, float scalarScale, int32_t zp, int32_t lo, int32_t hi, int weightPack,
+                    CodeT *codes, int32_t *codes32, uint8_t *mask) {
+    const size_t total = static_cast<size_t>(rowsPadded) * colsPadded;
+    {
+        KernelTimer timer__("quantizeTensor", st);
+        quantizeTensor<CodeT><<<gridFor(total, 256), 256, 0, st>>>(src, rows, cols, rowsPadded, colsPadded, channelScale,
+                                                                    scalarScale, zp, lo, hi, weightPack, codes, codes32, mask);
+    }
+    afterLaunch("quantizeTensor");
+}
+
+// Device copy of the per-channel block: 4 float arrays then 4 Rescale arrays.
+struct ChannelDevice {
+    const float *effW, *effR, *effBw, *effBr;
+    const Rescale *gemmX, *biasX, *gemmH, *biasH;
+};
+
+ChannelDevice uploadChannels(const Exec &e, Workspace &ws, cudaStream_t st) {
+    const size_t C = 3 * static_cast<size_t>(e.hidden);
+    auto *block = ws.take<int32_t>(12 * C);
+    std::vector<int32_t> host(12 * C);
+    auto putF = [&](size_t slot, const std::vector<float> &v) { std::memcpy(&host[slot * C], v.data(), C * 4); };
+    auto putR = [&](size_t slot, const std::vector<Rescale> &v) { std::memcpy(&host[slot * C], v.data(), C * 8); };
+    putF(0, e.chan.eff_W); putF(1, e.chan.eff_R); putF(2, e.chan.eff_bw); putF(3, e.chan.eff_br);
+    putR(4, e.chan.gemm_x); putR(6, e.chan.bias_x); putR(8, e.chan.gemm_h); putR(10, e.chan.bias_h);
+    // The source is pageable host memory: the runtime stages it before returning, so the
+    // temporary may die at the end of this function.
+    RXMET_CUDA(cudaMemcpyAsync(block, host.data(), host.size() * 4, cudaMemcpyHostToDevice, st));
+    ChannelDevice d;
+    d.effW = reinterpret_cast<const float *>(block);
+    d.effR = d.effW + C; d.effBw = d.effW + 2 * C; d.effBr = d.effW + 3 * C;
+    d.gemmX = reinterpret_cast<const Rescale *>(block + 4 * C);
+    d.biasX = d.gemmX + C; d.gemmH = d.gemmX + 2 * C; d.biasH = d.gemmX + 3 * C;
+    return d;
+}
+
+template <class WT, class AT, class LT>
+void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaStream_t st) {
+    using D = Dot<WT, AT>;
+    using WWord = typename D::WWord;
+    using AWord = typename D::AWord;
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 3 * H;
+    const GateExec &g = e.gate;
+    const size_t rows = static_cast<size_t>(T) * B;
+    const int iWords = padTo(I, D::kPack) / D::kPack, hWords = padTo(H, D::kPack) / D::kPack;
+    const int iPad = iWords * D::kPack, hPad = hWords * D::kPack;
+    const bool training = call.isTraining != 0;
+    const rxmet_gru_masks none{};
+    const rxmet_gru_masks &mk = (training && call.masks) ? *call.masks : none;
+
+    const ChannelDevice ch = uploadChannels(e, ws, st);
+    auto *wCodes = ws.take<WWord>(static_cast<size_t>(iWords) * C);
+    auto *rCodes = ws.take<WWord>(static_cast<size_t>(hWords) * C);
+    auto *bwCodes = ws.take<int32_t>(C);
+    auto *brCodes = ws.take<int32_t>(C);
+    auto *xCodes = ws.take<AT>(rows * iPad);
+    auto *h0Codes = ws.take<AT>(static_cast<size_t>(B) * hPad);
+    auto *ihCodes = ws.take<LT>(rows * C);
+    auto *comp = ws.take<int64_t>(4 * static_cast<size_t>(C));
+    int64_t *compX = comp, *biasX = comp + C, *compH = comp + 2 * C, *biasH = comp + 3 * C;
+
+    // 1. codes
+    launchQuantize<WT>(st, call.W, I, C, iPad, C, ch.effW, 0.f, 0, g.qlo[RXMET_GRU_W], g.qhi[RXMET_GRU_W], D::kPack,
+                       reinterpret_cast<WT *>(wCodes), call.W_q, mk.W);
+    launchQuantize<WT>(st, call.R, H, C, hPad, C, ch.effR, 0.f, 0, g.qlo[RXMET_GRU_R], g.qhi[RXMET_GRU_R], D::kPack,
+                       reinterpret_cast<WT *>(rCodes), call.R_q, mk.R);
+    launchQuantize<int32_t>(st, call.bw, 1, C, 1, C, ch.effBw, 0.f, 0, g.qlo[RXMET_GRU_BW], g.qhi[RXMET_GRU_BW], 1,
+                            bwCodes, call.bw_q, mk.bw);
+    launchQuantize<int32_t>(st, call.br, 1, C, 1, C, ch.effBr, 0.f, 0, g.qlo[RXMET_GRU_BR], g.qhi[RXMET_GRU_BR], 1,
+                            brCodes, call.br_q, mk.br);
+    if (call.x_codes_in) {
+        {
+            KernelTimer timer__("narrowCodes", st);
+            narrowCodes<AT><<<gridFor(rows * iPad, 256), 256, 0, st>>>(call.x_codes_in, static_cast<int>(rows), I, iPad, xCodes);
+        }
+        afterLaunch("narrowCodes");
+    } else {
+        launchQuantize<AT>(st, call.x, static_cast<int>(rows), I, static_cast<int>(rows), iPad, nullptr,
+                           g.eff[RXMET_GRU_X], g.zp[RXMET_GRU_X], g.qlo[RXMET_GRU_X], g.qhi[RXMET_GRU_X], 1, xCodes,
+                           call.x_q, mk.x);
+    }
+    if (call.h0_codes_in) {
+        {
+            KernelTimer timer__("narrowCodes", st);
+            narrowCodes<AT><<<gridFor(static_cast<size_t>(B) * hPad, 256), 256, 0, st>>>(call.h0_codes_in, B, H, hPad, h0Codes);
+        }
+        afterLaunch("narrowCodes");
+    } else if (call.h0) {
+        launchQuantize<AT>(st, call.h0, B, H, B, hPad, nullptr, g.eff[RXMET_GRU_H], g.zp[RXMET_GRU_H],
+                           g.qlo[RXMET_GRU_H], g.qhi[RXMET_GRU_H], 1, h0Codes, nullptr, mk.h0);
+    } else {
+        // padding columns hold the zero point too; they meet zero weights, so they do not matter
+        {
+            KernelTimer timer__("fillCodes", st);
+            fillCodes<AT><<<gridFor(static_cast<size_t>(B) * hPad, 256), 256, 0, st>>>(h0Codes, static_cast<size_t>(B) * hPad,
+                                                                                      g.zp[RXMET_GRU_H]);
+        }
+        afterLaunch("fillCodes");
+    }
+
+    // 2. per-channel terms
+    {
+        KernelTimer timer__("channelPrep", st);
+        channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(wCodes, iWords, C, g.zp[RXMET_GRU_X], bwCodes, ch.biasX, compX, biasX);
+    }
+    afterLaunch("channelPrep");
+    {
+        KernelTimer timer__("channelPrep", st);
+        channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(rCodes, hWords, C, g.zp[RXMET_GRU_H], brCodes, ch.biasH, compH, biasH);
+    }
+    afterLaunch("channelPrep");
+
+    // 3. input projection, all steps
+    {
+        const int block = std::min(padTo(C, 32), 512);
+        const size_t smem = sizeof(AWord) * kLinearRows * iWords;
+        const int grid = static_cast<int>((rows + kLinearRows - 1) / kLinearRows);
+        {
+            KernelTimer timer__("inputLinear", st);
+            inputLinear<WT, AT, LT><<<grid, block, smem, st>>>(
+                reinterpret_cast<const AWord *>(xCodes), static_cast<int>(rows), iWords, C, wCodes, compX, biasX, ch.gemmX,
+                g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR], g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR],
+                ihCodes, mk.weight_ih_linear);
+        }
+        afterLaunch("inputLinear");
+    }
+
+    // 4. recurrence
+    RecurrentArgs a{};
+    a.T = T; a.B = B; a.H = H; a.kWords = hWords;
+    a.R = rCodes; a.ih = ihCodes; a.h0 = h0Codes;
+    a.comp = compH; a.biasAcc = biasH; a.rescale = ch.gemmH;
+    a.h = call.h; a.v = call.v; a.hq = call.h_q; a.vq = call.v_q;
+    a.maskHh = mk.weight_hh_linear; a.maskGateIn = mk.gate_input; a.maskGateOut = mk.gate_output; a.maskH = mk.h;
+    if (mk.gate_input || mk.gate_output || mk.h)
+        RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
+
+    int device = 0, smemMax = 0, sms = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    // Batch tile: as small as keeps every SM busy; a larger tile only amortises weight reads.
+    const int bt = (B >= 4 * 2 * sms) ? 4 : ((B >= 2 * 2 * sms) ? 2 : 1);
+    const int block = std::min(padTo(C, 32), 768);
+    auto launch = [&](auto kernel, int BT) {
+        size_t smem = recurrentSmemBytes(H, hWords, D::kPack, sizeof(WWord), sizeof(AT), BT, true);
+        a.weightsInSmem = smem <= static_cast<size_t>(smemMax) ? 1 : 0;
+        if (!a.weightsInSmem) smem = recurrentSmemBytes(H, hWords, D::kPack, sizeof(WWord), sizeof(AT), BT, false);
+        if (smem > static_cast<size_t>(smemMax))
+            fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
+        RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        {
+            KernelTimer timer__("recurrentForward", st);
+            kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a, g);
+        }
+        afterLaunch("recurrentForward");
+    };
+    if (bt == 4) launch(recurrentForward<WT, AT, LT, 4>, 4);
+    else if (bt == 2) launch(recurrentForward<WT, AT, LT, 2>, 2);
+    else launch(recurrentForward<WT, AT, LT, 1>, 1);
+}
+
+template <class WT, class AT, class LT>
+void sizeTyped(WorkspaceSizer &ws, int T, int B, int I, int H) {
+    using D = Dot<WT, AT>;
+    const size_t C = 3 * static_cast<size_t>(H), rows = static_cast<size_t>(T) * B;
+    const int iWords = padTo(I, D::kPack) / D::kPack, hWords = padTo(H, D::kPack) / D::kPack;
+    ws.take<int32_t>(12 * C);
+    ws.take<typename D::WWord>(iWords * C);
+    ws.take<typename D::WWord>(hWords * C);
+    ws.take<int32_t>(C);
+    ws.take<int32_t>(C);
+    ws.take<AT>(rows * iWords * D::kPack);
+    ws.take<AT>(static_cast<size_t>(B) * hWords * D::kPack);
+    ws.take<LT>(rows * C);
+    ws.take<int64_t>(4 * C);
+}
+
+}  // namespace
+
+size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
+    // The widest storage classes bound every configuration.
+    WorkspaceSizer ws;
+    sizeTyped<int32_t, int32_t, int32_t>(ws, T, B, I, H);
+    return ws.used() + 4096;
+}
+
+void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes,
+                  cudaStream_t st) {
+    Workspace ws(workspace, workspaceBytes);
+    const CodeClass w = e.weightClass, a = e.actClass, l = e.linearClass;
+    if (l == CodeClass::I32 || w == CodeClass::I32 || a == CodeClass::I32) {
+        runTyped<int32_t, int32_t, int32_t>(call, e, ws, st);
+    } else if (w == CodeClass::I8 && a == CodeClass::I8) {
+        runTyped<int8_t, int8_t, int16_t>(call, e, ws, st);
+    } else if (w == CodeClass::I8) {
+        runTyped<int8_t, int16_t, int16_t>(call, e, ws, st);
+    } else {
+        runTyped<int16_t, int16_t, int16_t>(call, e, ws, st);
+    }
+}
+
+}  // namespace gru
+}  // namespace rxmet

@@ -1,0 +1,36 @@
+// Host entry of the quantized GRU forward (integer carrier).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "gru_params.h"
+#include "rxmet_b200.h"
+
+namespace rxmet {
+namespace gru {
+
+// All pointers are device pointers; optional ones may be null.
+struct ForwardQuantCall {
+    int isTraining = 0;
+    int T = 0, B = 0, I = 0, H = 0;
+    const float *W = nullptr, *R = nullptr, *bw = nullptr, *br = nullptr;
+    const float *x = nullptr;               // [T,B,I] float input, or
+    const int32_t *x_codes_in = nullptr;    // [T,B,I] codes already on the x grid
+    const float *h0 = nullptr;              // [B,H] float initial state, or
+    const int32_t *h0_codes_in = nullptr;   // [B,H] codes already on the h grid (else zero point)
+    float *h = nullptr;                     // [T+1,B,H] dequantized
+    float *v = nullptr;                     // [T,B,4H] dequantized
+    int32_t *W_q = nullptr, *R_q = nullptr, *bw_q = nullptr, *br_q = nullptr, *x_q = nullptr;
+    int32_t *h_q = nullptr, *v_q = nullptr;
+    const rxmet_gru_masks *masks = nullptr;
+};
+
+size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H);
+void forwardQuant(const ForwardQuantCall &call, const Exec &exec, void *workspace, size_t workspaceBytes,
+                  cudaStream_t stream);
+
+}  // namespace gru
+}  // namespace rxmet

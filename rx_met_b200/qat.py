@@ -1,0 +1,137 @@
+"""Preallocated QuantGRU calibration + QAT step over the C ABI (one direction, one layer).
+
+``gru_interface_binding`` mirrors the reference's call-by-call interface and allocates its
+outputs on every call, as the reference does.  A training loop that runs the same shapes every
+step does not need that: this class allocates every buffer once (weights and their gradients as
+views of two flat tensors, so that the data-parallel all-reduce and the SGD update are one
+operation each) and then only launches kernels.  Batches shard over ranks; the only exchanges
+are the calibration min/max all-reduce and the gradient all-reduce.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _cabi as cabi
+from .gru_interface_binding import GRUQuantParams, OperatorQuantConfig
+
+
+def _p(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class GruQatStep:
+    def __init__(self, T: int, B: int, I: int, H: int, device: torch.device,
+                 config: Optional[OperatorQuantConfig] = None, process_group=None, seed: int = 0):
+        self.lib = cabi.load_library()
+        self.T, self.B, self.I, self.H = T, B, I, H
+        self.device = torch.device(device)
+        self.group = process_group
+        self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
+        self.config = config or OperatorQuantConfig()
+        C3 = 3 * H
+        f32 = dict(dtype=torch.float32, device=self.device)
+        # master weights (gate order z,r,n; W [I,3H], R [H,3H]) and their gradients, flat
+        sizes = [I * C3, H * C3, C3, C3]
+        self.flat_w = torch.empty(sum(sizes), **f32)
+        self.flat_g = torch.zeros(sum(sizes), **f32)
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        k = 1.0 / (H ** 0.5)
+        self.flat_w.copy_((torch.rand(sum(sizes), generator=gen) * 2 - 1) * k)  # same on every rank
+        offs = [0]
+        for s in sizes:
+            offs.append(offs[-1] + s)
+        view = lambda flat, i, shape: flat[offs[i]:offs[i + 1]].view(shape)  # noqa: E731
+        self.W, self.R = view(self.flat_w, 0, (I, C3)), view(self.flat_w, 1, (H, C3))
+        self.bw, self.br = view(self.flat_w, 2, (C3,)), view(self.flat_w, 3, (C3,))
+        self.dW, self.dR = view(self.flat_g, 0, (I, C3)), view(self.flat_g, 1, (H, C3))
+        self.dbw, self.dbr = view(self.flat_g, 2, (C3,)), view(self.flat_g, 3, (C3,))
+        # activations, caches, masks
+        i32 = dict(dtype=torch.int32, device=self.device)
+        u8 = dict(dtype=torch.uint8, device=self.device)
+        self.h = torch.empty((T + 1, B, H), **f32)
+        self.v = torch.empty((T, B, 4 * H), **f32)
+        self.W_q, self.R_q = torch.empty((I, C3), **i32), torch.empty((H, C3), **i32)
+        self.bw_q, self.br_q = torch.empty((C3,), **i32), torch.empty((C3,), **i32)
+        self.x_q = torch.empty((T, B, I), **i32)
+        shapes = {"x": (T, B, I), "W": (I, C3), "R": (H, C3), "bw": (C3,), "br": (C3,),
+                  "weight_ih_linear": (T, B, C3), "weight_hh_linear": (T, B, C3), "gate_input": (T, B, C3),
+                  "gate_output": (T, B, C3), "h": (T, B, H)}
+        self.masks = {k_: torch.empty(s, **u8) for k_, s in shapes.items()}
+        self.mask_struct = cabi.Masks()
+        for k_, t in self.masks.items():
+            setattr(self.mask_struct, k_, t.data_ptr())
+        self.dh_new = torch.zeros((T + 1, B, H), **f32)
+        self.dx = torch.empty((T, B, I), **f32)
+        self.dh0 = torch.empty((B, H), **f32)
+        nbytes = max(self.lib.rxmet_gru_workspace_bytes(op, T, B, I, H) for op in (0, 1, 2))
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.stats = torch.empty(self.lib.rxmet_gru_stats_floats(H), **f32)
+        self.params: Optional[GRUQuantParams] = None
+        self._c_params = None
+        self._keep = None
+
+    # ---- calibration -----------------------------------------------------
+    def calibrate(self, batches) -> GRUQuantParams:
+        """min/max calibration over an iterable of [T,B,I] device tensors.  With a process group
+        the per-batch statistics are all-reduced (MIN / MAX), so every rank derives the same
+        encodings as one process would on the concatenated batch."""
+        from .gru_interface_binding import GRUQuantizationRanges, calculate_gru_quantitative_parameters
+        ranges = GRUQuantizationRanges(self.H)
+        c_ranges, keep = ranges._to_c()
+        half = self.stats.numel() // 2
+        for x in batches:
+            cabi.check(self.lib.rxmet_gru_forward_calibrate_stats(
+                self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+                _p(self.h), _p(self.v), _p(self.stats), _p(self.ws), C.c_size_t(self.ws.numel()), self._stream()),
+                "forward_calibrate_stats")
+            if self.group is not None:
+                torch.distributed.all_reduce(self.stats[:half], op=torch.distributed.ReduceOp.MIN, group=self.group)
+                torch.distributed.all_reduce(self.stats[half:], op=torch.distributed.ReduceOp.MAX, group=self.group)
+            host = self.stats.cpu().contiguous()
+            cabi.check(self.lib.rxmet_gru_ranges_fold_stats(
+                C.byref(c_ranges), C.cast(host.data_ptr(), C.POINTER(C.c_float))), "ranges_fold_stats")
+        ranges._from_c(c_ranges, keep)
+        self.set_params(calculate_gru_quantitative_parameters(ranges, self.config))
+        return self.params
+
+    def set_params(self, params: GRUQuantParams) -> None:
+        self.params = params
+        self._c_params, self._keep = params._to_c()
+
+    # ---- one training step -------------------------------------------------
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Quantized training forward; returns the output sequence h[1:] (a view)."""
+        cabi.check(self.lib.rxmet_gru_forward_quant(
+            1, self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+            C.byref(self._c_params), _p(self.h), _p(self.v), _p(self.W_q), _p(self.R_q), _p(self.bw_q),
+            _p(self.br_q), _p(self.x_q), None, None, C.byref(self.mask_struct), _p(self.ws),
+            C.c_size_t(self.ws.numel()), self._stream()), "forward_quant")
+        return self.h[1:]
+
+    def backward(self) -> None:
+        """BPTT from self.dh_new ([T+1,B,H], row 0 unused) into the flat gradient buffer."""
+        cabi.check(self.lib.rxmet_gru_backward_quant(
+            self.T, self.B, self.I, self.H, _p(self.W_q), _p(self.R_q), _p(self.bw_q), _p(self.br_q), _p(self.x_q),
+            _p(self.dh_new), _p(self.h), _p(self.v), C.byref(self._c_params), C.byref(self.mask_struct),
+            _p(self.dx), _p(self.dW), _p(self.dR), _p(self.dbw), _p(self.dbr), _p(self.dh0), _p(self.ws),
+            C.c_size_t(self.ws.numel()), self._stream()), "backward_quant")
+
+    def step(self, x: torch.Tensor, target: torch.Tensor, lr: float) -> torch.Tensor:
+        """forward, MSE loss gradient, backward, gradient all-reduce, SGD update.  Returns the loss
+        (a device scalar, not synchronised)."""
+        out = self.forward(x)
+        diff = out - target
+        loss = diff.square().mean()
+        torch.mul(diff, 2.0 / diff.numel(), out=self.dh_new[1:])
+        self.backward()
+        if self.group is not None:
+            torch.distributed.all_reduce(self.flat_g, group=self.group)
+            self.flat_g.div_(self.world)
+        self.flat_w.add_(self.flat_g, alpha=-lr)
+        return loss

@@ -212,8 +212,10 @@ def forward_calibrate_minmax(prefix, W, R, bw, br, x, h0, ranges: RangesBox, cfg
     return h, v
 
 
-def forward_quant(prefix, W, R, bw, br, x, h0, params: ParamsBox, training=True):
-    """Returns a dict with h, v (float) and the codes; the restatement also returns masks."""
+def forward_quant(prefix, W, R, bw, br, x, h0, params: ParamsBox, training=True, want_float=True):
+    """Returns a dict with h, v (float) and the codes; the restatement also returns masks.
+    want_float=False skips the dequantized outputs (the compiled reference needs a second pass
+    over the sequence to produce them)."""
     T, B, I = x.shape
     H = R.shape[0]
     out = {"h": np.empty((T + 1, B, H), np.float32), "v": np.empty((T, B, 4 * H), np.float32),
@@ -223,8 +225,10 @@ def forward_quant(prefix, W, R, bw, br, x, h0, params: ParamsBox, training=True)
     if prefix == "ref":
         rc = lib.ref_gru_forward_quant(T, B, I, H, _fp(W), _fp(R), _fp(bw), _fp(br), _fp(x), _fp(h0),
                                        C.byref(params.c), _ip(out["x_q"]), _ip(out["h_q"]), _ip(out["v_q"]),
-                                       _fp(out["h"]), _fp(out["v"]))
+                                       _fp(out["h"]) if want_float else None, _fp(out["v"]) if want_float else None)
         assert rc == 0, lib.ref_last_error()
+        if not want_float:
+            return out
         wq = {k: np.empty(s, np.int32) for k, s in
               (("W_q", (I, 3 * H)), ("R_q", (H, 3 * H)), ("bw_q", (3 * H,)), ("br_q", (3 * H,)))}
         rc = lib.ref_gru_quantize_weights(I, H, _fp(W), _fp(R), _fp(bw), _fp(br), C.byref(params.c),

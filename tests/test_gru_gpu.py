@@ -1,0 +1,296 @@
+"""GPU parity tests: the CUDA library, called through its C ABI, against the CPU restatement
+and the golden fixtures.  Integer codes, clamp masks and dequantized outputs must be bit-exact;
+float paths (calibration forward, backward) must agree within 1e-5 relative."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from rx_met_b200 import _cabi as cabi
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+GOLDEN = sorted((ROOT / "tests" / "golden").glob("gru_*.npz"))
+REL = 1e-5  # tolerance for float results, relative to the largest magnitude of the tensor
+
+
+@pytest.fixture(scope="module")
+def gl():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    import gpu_lib
+    return gpu_lib
+
+
+def close(a, b, rel=REL, what=""):
+    scale = max(float(np.abs(b).max()), 1e-30)
+    err = float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max())
+    assert err <= rel * scale, f"{what}: max abs err {err:.3e} vs scale {scale:.3e}"
+
+
+def calibrated(shape, seed, cfg, with_h0, x_scale=1.0):
+    T, B, I, H = shape
+    W, R, bw, br, x, h0 = ol.gru_problem(seed, T, B, I, H, x_scale=x_scale, with_h0=with_h0)
+    rg = ol.RangesBox(H)
+    ol.forward_calibrate_minmax("orc", W, R, bw, br, x, h0, rg)
+    return (W, R, bw, br, x, h0), ol.params_from_ranges("orc", rg, cfg)
+
+
+def assert_forward_equal(got, want, training=True):
+    for k in ("W_q", "R_q", "bw_q", "br_q", "x_q", "h_q", "v_q"):
+        assert np.array_equal(got[k], want[k]), f"codes {k}: {(got[k] != want[k]).sum()} of {got[k].size} differ"
+    for k in ("h", "v"):
+        assert np.array_equal(got[k], want[k]), f"dequantized {k} differs"
+    if training:
+        for k, m in want["masks"].arr.items():
+            assert np.array_equal(got["masks"][k], m), f"mask {k}: {(got['masks'][k] != m).sum()} differ"
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.stem)
+def test_forward_quant_matches_golden(gl, path):
+    g = np.load(path)
+    seed, T, B, I, H, bits, sym, pot, gran, with_h0 = (int(v) for v in g["meta"])
+    cfg = ol.make_config(bits=bits, symmetric=bool(sym), use_pot2=bool(pot), granularity=gran)
+    params = ol.ParamsBox(H, cfg).load_dict({k[len("param_"):]: g[k] for k in g.files if k.startswith("param_")})
+    h0 = g["h0"] if with_h0 else None
+    rc, got = gl.forward_quant(g["W"], g["R"], g["bw"], g["br"], g["x"], h0, params)
+    assert rc == 0, got
+    for k in ("W_q", "R_q", "bw_q", "br_q", "x_q", "h_q", "v_q", "h", "v"):
+        assert np.array_equal(got[k], g[f"fwd_{k}"]), k
+
+
+CONFIGS = {
+    "w8a8": dict(bits=8, symmetric=False),
+    "w8a8_sym": dict(bits=8, symmetric=True),
+    "w8a8_pot2": dict(bits=8, symmetric=False, use_pot2=True),
+    "a16": dict(bits=8, symmetric=False, overrides={n: (16, False, False) for n in (
+        "x", "h", "weight_ih_linear", "weight_hh_linear", "update_gate_input", "reset_gate_input",
+        "new_gate_input", "new_gate_output", "mul_reset_hidden", "mul_old_contribution", "mul_new_contribution")}),
+    "w16a16": dict(bits=16, symmetric=False),
+    "w4": dict(bits=8, symmetric=False, granularity=cabi.PER_GATE,
+               overrides={"W": (4, False, True), "R": (4, False, True)}),
+    "unsigned_x": dict(bits=8, symmetric=False, overrides={"x": (8, True, False)}),
+    "b24": dict(bits=24, symmetric=False),
+}
+SHAPES = [(3, 1, 1, 1), (5, 2, 3, 4), (7, 3, 31, 33), (6, 5, 40, 64), (4, 37, 20, 128), (3, 2, 9, 160)]
+
+
+@pytest.mark.parametrize("cfg_name", list(CONFIGS))
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_forward_quant_matches_restatement(gl, cfg_name, shape):
+    cfg = ol.make_config(**CONFIGS[cfg_name])
+    with_h0 = (shape[0] + shape[1]) % 2 == 0
+    prob, params = calibrated(shape, seed=sum(shape), cfg=cfg, with_h0=with_h0, x_scale=1.5)
+    want = ol.forward_quant("orc", *prob, params, training=True)
+    rc, got = gl.forward_quant(*prob, params, training=True)
+    assert rc == 0, got
+    assert_forward_equal(got, want)
+    rc, inf = gl.forward_quant(*prob, params, training=False)
+    assert rc == 0, inf
+    for k in ("h_q", "v_q", "h", "v"):
+        assert np.array_equal(inf[k], want[k]), k
+    # integer in / integer out chaining reproduces the same state codes
+    h0_q = want["h_q"][0] if with_h0 else None
+    assert np.array_equal(gl.forward_int_io(*prob[:4], want["x_q"], h0_q, params), want["h_q"])
+
+
+def test_forward_quant_saturating_inputs(gl):
+    """Inputs far outside the calibrated range exercise every clamp mask."""
+    cfg = ol.make_config(bits=8, symmetric=False)
+    prob, params = calibrated((6, 4, 12, 32), seed=77, cfg=cfg, with_h0=True)
+    W, R, bw, br, x, h0 = prob
+    x = (x * 6.0).astype(np.float32)
+    h0 = (h0 * 8.0).astype(np.float32)
+    want = ol.forward_quant("orc", W, R, bw, br, x, h0, params)
+    assert (want["masks"].arr["x"] == 0).any() and (want["masks"].arr["h0"] == 0).any()
+    rc, got = gl.forward_quant(W, R, bw, br, x, h0, params)
+    assert rc == 0, got
+    assert_forward_equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(5, 2, 3, 4), (7, 3, 31, 33), (9, 6, 40, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_calibration_forward(gl, shape):
+    T, B, I, H = shape
+    W, R, bw, br, x, h0 = ol.gru_problem(3, T, B, I, H, with_h0=True)
+    want_r, got_r = ol.RangesBox(H), ol.RangesBox(H)
+    h_w, v_w = ol.forward_calibrate_minmax("orc", W, R, bw, br, x, h0, want_r)
+    h_g, v_g = gl.forward_float(W, R, bw, br, x, h0, ranges=got_r)
+    close(h_g, h_w, what="h")
+    close(v_g, v_w, what="v")
+    w, g = want_r.as_dict(), got_r.as_dict()
+    for k in ("min_W", "max_W", "min_R", "max_R", "min_bw", "max_bw", "min_br", "max_br"):
+        assert np.array_equal(g[k], w[k]), k  # no arithmetic involved: exact
+    assert g["min"][cabi.X] == w["min"][cabi.X] and g["max"][cabi.X] == w["max"][cabi.X]
+    for op in cabi.SCALAR_OPS:
+        for kind in ("min", "max"):
+            assert abs(g[kind][op] - w[kind][op]) <= 1e-5 * max(1.0, abs(w[kind][op])), (kind, cabi.OP_NAMES[op])
+    # a second batch accumulates into the same ranges, and the float forward alone agrees too
+    x2 = (x * 1.7).astype(np.float32)
+    ol.forward_calibrate_minmax("orc", W, R, bw, br, x2, None, want_r)
+    gl.forward_float(W, R, bw, br, x2, None, ranges=got_r)
+    assert got_r.as_dict()["max"][cabi.X] == want_r.as_dict()["max"][cabi.X]
+    h_f, v_f = gl.forward_float(W, R, bw, br, x, h0)
+    assert np.array_equal(h_f, h_g) and np.array_equal(v_f, v_g)
+
+
+def test_calibration_ignores_non_finite_values(gl):
+    T, B, I, H = 4, 2, 5, 8
+    W, R, bw, br, x, _ = ol.gru_problem(8, T, B, I, H)
+    x[1, 0, 2] = np.inf
+    x[2, 1, 0] = np.nan
+    want_r, got_r = ol.RangesBox(H), ol.RangesBox(H)
+    ol.forward_calibrate_minmax("orc", W, R, bw, br, x, None, want_r)
+    gl.forward_float(W, R, bw, br, x, None, ranges=got_r)
+    w, g = want_r.as_dict(), got_r.as_dict()
+    assert g["min"][cabi.X] == w["min"][cabi.X] and g["max"][cabi.X] == w["max"][cabi.X]
+    assert np.isfinite(g["max"]).all()
+
+
+@pytest.mark.parametrize("cfg_name", ["w8a8", "a16", "w8a8_pot2"])
+@pytest.mark.parametrize("shape", [(5, 2, 3, 4), (7, 3, 31, 33), (8, 9, 40, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_backward_quant(gl, cfg_name, shape):
+    T, B, I, H = shape
+    cfg = ol.make_config(**CONFIGS[cfg_name])
+    prob, params = calibrated(shape, seed=5 + T, cfg=cfg, with_h0=True)
+    W, R, bw, br, x, h0 = prob
+    x = (x * 2.5).astype(np.float32)  # make some clamps fire
+    f = ol.forward_quant("orc", W, R, bw, br, x, h0, params)
+    rng = np.random.default_rng(T)
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = rng.standard_normal((T, B, H)).astype(np.float32)
+    dh_new[-1] += rng.standard_normal((B, H)).astype(np.float32)
+    want = ol.backward_quant(f, dh_new, f["h"], f["v"], params, f["masks"])
+    got = gl.backward_quant(f, dh_new, f["h"], f["v"], params, f["masks"].arr)
+    for k in want:
+        close(got[k], want[k], what=k)
+    # masked-out positions are exactly zero
+    for k, m in (("dx", "x"), ("dW", "W"), ("dR", "R"), ("dbw", "bw"), ("dbr", "br"), ("dh0", "h0")):
+        assert not np.any(got[k][f["masks"].arr[m] == 0]), k
+    # no masks at all = every mask set
+    ones = {k: np.ones_like(v) for k, v in f["masks"].arr.items()}
+    a = gl.backward_quant(f, dh_new, f["h"], f["v"], params, ones)
+    b = gl.backward_quant(f, dh_new, f["h"], f["v"], params, None)
+    for k in a:
+        assert np.array_equal(a[k], b[k]), k
+
+
+def test_backward_float(gl):
+    T, B, I, H = 6, 5, 12, 48
+    W, R, bw, br, x, h0 = ol.gru_problem(31, T, B, I, H, with_h0=True)
+    h, v = ol.forward_fp(W, R, bw, br, x, h0)
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = np.random.default_rng(2).standard_normal((T, B, H)).astype(np.float32)
+    want = ol.backward_fp(W, R, bw, br, x, dh_new, h, v)
+    got = gl.backward_fp(W, R, bw, br, x, dh_new, h, v)
+    for k in want:
+        close(got[k], want[k], what=k)
+
+
+def test_full_size_properties(gl):
+    """QAT-step sized problem (T=100, B=256, I=40, H=128): too slow to check element by element
+    on the CPU in a unit test, so it is checked through size-independent properties."""
+    shape = (100, 256, 40, 128)
+    T, B, I, H = shape
+    cfg = ol.make_config(bits=8, symmetric=False)
+    small, params = calibrated((20, 8, I, H), seed=1, cfg=cfg, with_h0=False)
+    W, R, bw, br = small[:4]
+    x = np.random.default_rng(4).standard_normal((T, B, I)).astype(np.float32)
+    rc, full = gl.forward_quant(W, R, bw, br, x, None, params)
+    assert rc == 0, full
+    # (a) sequences are independent: any batch slice run alone gives the same codes
+    rc, part = gl.forward_quant(W, R, bw, br, x[:, 100:117], None, params)
+    assert rc == 0, part
+    assert np.array_equal(part["h_q"], full["h_q"][:, 100:117]) and np.array_equal(part["v_q"], full["v_q"][:, 100:117])
+    for k in ("weight_hh_linear", "gate_input", "gate_output", "h", "x", "weight_ih_linear"):
+        assert np.array_equal(part["masks"][k], full["masks"][k][:, 100:117]), k
+    # (b) the first sequences agree with the CPU restatement element by element
+    want = ol.forward_quant("orc", W, R, bw, br, np.ascontiguousarray(x[:, :6]), None, params)
+    assert np.array_equal(full["h_q"][:, :6], want["h_q"]) and np.array_equal(full["v_q"][:, :6], want["v_q"])
+    # (c) codes stay on their grids and masks are 0/1
+    assert full["h_q"].min() >= -128 and full["h_q"].max() <= 127
+    assert full["v_q"][..., :2 * H].min() >= 0 and full["v_q"][..., :2 * H].max() <= 255
+    for k, m in full["masks"].items():
+        assert m.max() <= 1, k
+    # (d) repeatable run to run, forward and backward
+    rc, again = gl.forward_quant(W, R, bw, br, x, None, params)
+    assert np.array_equal(again["h_q"], full["h_q"]) and np.array_equal(again["v"], full["v"])
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = np.random.default_rng(6).standard_normal((T, B, H)).astype(np.float32)
+    g1 = gl.backward_quant(full, dh_new, full["h"], full["v"], params, full["masks"])
+    g2 = gl.backward_quant(full, dh_new, full["h"], full["v"], params, full["masks"])
+    for k in g1:
+        assert np.array_equal(g1[k], g2[k]), k
+    # (e) the backward is linear in the incoming gradient, and zero in gives zero out
+    g3 = gl.backward_quant(full, (2.0 * dh_new).astype(np.float32), full["h"], full["v"], params, full["masks"])
+    for k in g1:
+        close(g3[k], 2.0 * g1[k], what=k)
+    g0 = gl.backward_quant(full, np.zeros_like(dh_new), full["h"], full["v"], params, full["masks"])
+    assert all(not np.any(v) for v in g0.values())
+    # (f) per-sequence gradients: a batch slice of dx equals the slice run alone
+    sl = slice(100, 117)
+    sub = {k: np.ascontiguousarray(full[k][:, sl]) if full[k].ndim == 3 else full[k]
+           for k in ("W_q", "R_q", "bw_q", "br_q", "x_q")}
+    sub_masks = {k: (np.ascontiguousarray(m[:, sl]) if m.ndim == 3 else m) for k, m in full["masks"].items()}
+    gs = gl.backward_quant(sub, np.ascontiguousarray(dh_new[:, sl]), np.ascontiguousarray(full["h"][:, sl]),
+                           np.ascontiguousarray(full["v"][:, sl]), params, sub_masks)
+    assert np.array_equal(gs["dx"], g1["dx"][:, sl])
+
+
+def test_errors_are_reported_not_fatal(gl):
+    cfg = ol.make_config(bits=8, symmetric=False)
+    prob, params = calibrated((4, 2, 3, 8), seed=2, cfg=cfg, with_h0=False)
+    rc, msg = gl.forward_quant(*prob, params, workspace_bytes=64)
+    assert rc == -3 and "workspace" in msg
+    wrong = ol.ParamsBox(16, cfg)
+    rc, msg = gl.forward_quant(*prob, wrong)
+    assert rc == -1 and "hidden" in msg
+    rc, ok = gl.forward_quant(*prob, params)  # the context is still usable
+    assert rc == 0
+
+
+def test_python_module_mirrors_reference_binding(gl):
+    """The drop-in module returns the reference's 18-tuple and 6-tuple and agrees with the C ABI."""
+    import torch
+    from rx_met_b200 import gru_interface_binding as ops
+    T, B, I, H = 6, 4, 10, 24
+    W, R, bw, br, x, h0 = ol.gru_problem(13, T, B, I, H, with_h0=True)
+    t = {k: torch.from_numpy(v).cuda() for k, v in dict(W=W, R=R, bw=bw, br=br, x=x, h0=h0).items()}
+    cfg = ops.OperatorQuantConfig()
+    for name in cabi.OP_NAMES:
+        if name not in ("W", "R", "bw", "br"):
+            setattr(cfg, f"{name}_symmetric_", False)
+    ranges = ops.GRUQuantizationRanges(H)
+    h_fp, v_fp = ops.forward_calibrate(False, T, B, I, H, t["W"], t["R"], t["bw"], t["br"], t["x"], t["h0"],
+                                       "minmax", cfg, quant_ranges=ranges)
+    assert ranges.max_x_ == float(x.max()) and len(ranges.min_W_) == 3 * H
+    qp = ops.calculate_gru_quantitative_parameters(ranges, cfg)
+    assert qp.hidden_ == H and len(qp.scale_W_) == 3 * H and qp.scale_x_ > 0
+    out_i = ops.forward_quant_int_storage(True, T, B, I, H, t["W"], t["R"], t["bw"], t["br"], t["x"], t["h0"], qp)
+    out_f = ops.forward_quant_float_storage(True, T, B, I, H, t["W"], t["R"], t["bw"], t["br"], t["x"], t["h0"], qp)
+    assert len(out_i) == 18 and len(out_f) == 18
+    assert out_i[2].dtype == torch.int32 and out_f[2].dtype == torch.float32 and out_i[7].dtype == torch.uint8
+    for a, b in zip(out_i, out_f):
+        assert torch.equal(a.float(), b.float())
+    inf = ops.forward_quant_int_storage(False, T, B, I, H, t["W"], t["R"], t["bw"], t["br"], t["x"], t["h0"], qp)
+    assert torch.equal(inf[0], out_i[0]) and all(m.numel() == 0 for m in inf[7:])
+    h, v = out_i[0], out_i[1]
+    dh_new = torch.zeros((T + 1, B, H), device="cuda")
+    dh_new[1:] = torch.randn((T, B, H), generator=torch.Generator().manual_seed(0)).cuda()
+    grads_i = ops.backward_quant_int_storage(T, B, I, H, *out_i[2:7], dh_new, h, v, qp, *out_i[7:])
+    grads_f = ops.backward_quant_float_storage(T, B, I, H, *out_f[2:7], dh_new, h, v, qp, *out_f[7:])
+    assert len(grads_i) == 6
+    for a, b in zip(grads_i, grads_f):
+        assert torch.equal(a, b)
+    assert tuple(grads_i[0].shape) == (T, B, I) and tuple(grads_i[1].shape) == (I, 3 * H)
+    # scale the module reports = scale the kernels dequantize with
+    eff = ops.decode_effective_scale(qp.scale_h_, False)
+    codes = torch.round(h / eff) + qp.zp_h_
+    assert torch.equal((codes - qp.zp_h_) * eff, h)
+    with pytest.raises(RuntimeError):
+        ops.forward_quant_int_storage(True, T, B, I, H, t["W"].cpu(), t["R"], t["bw"], t["br"], t["x"], t["h0"], qp)
+    out_q, hn_q = ops.forward_quantized_int_io(T, B, I, H, t["W"], t["R"], t["bw"], t["br"], out_i[6], None, qp)
+    assert out_q.dtype == torch.int32 and tuple(out_q.shape) == (T, B, H) and tuple(hn_q.shape) == (1, B, H)
