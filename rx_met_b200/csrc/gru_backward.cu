@@ -7,7 +7,7 @@
 //                       mask applied and then dh += R dq.
 //   gemmTN + reduce   : dW = x^T dp and dR = h^T dq as split-K tile GEMMs whose partial sums are
 //                       added in a fixed order, so gradients are reproducible run to run.
-//   inputGrad         : dx = dp W^T with the input clamp mask.
+//   gemmNT            : dx = dp W^T with the input clamp mask.
 //   columnSums        : bias gradients as fixed-order column sums (the reference uses float
 //                       atomics here, gru_backward_gpu_quant.cu:258-264).
 //
@@ -17,6 +17,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.h"
 #include "gru_backward.h"
@@ -136,6 +137,168 @@ __global__ void __launch_bounds__(768) recurrentBackward(const __grid_constant__
     }
 }
 
+// ---- quantized weights in registers -------------------------------------------
+//
+// For weight grids of at most 8 bits the codes are exact in bf16, so R[k][c] = code * scale[c]
+// can live in registers as packed bf16 code pairs with the per-channel scale folded into dq.
+// Thread (k, p) owns row k of gate p: H codes = CW packed words, resident for the whole sequence;
+// a step's dh += R dq then reads shared memory only for the broadcast of dq (128-bit loads).
+// All per-step operands (v, h, dh_new, 13 mask bytes) are fetched one step ahead.
+
+// RB[(p*CW + jj)*H + k] = bf16x2(code[k][p*H + 2jj], code[k][p*H + 2jj + 1])
+__global__ void packRecurrentBf16(const int32_t *__restrict__ Rq, int H, int CW, uint32_t *__restrict__ RB) {
+    const int total = 3 * CW * H;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % H, jj = (i / H) % CW, p = i / (H * CW);
+        const int j0 = 2 * jj, j1 = 2 * jj + 1;
+        const float c0 = j0 < H ? static_cast<float>(Rq[static_cast<size_t>(k) * 3 * H + p * H + j0]) : 0.0f;
+        const float c1 = j1 < H ? static_cast<float>(Rq[static_cast<size_t>(k) * 3 * H + p * H + j1]) : 0.0f;
+        // |code| <= 256 has at most 9 significant bits with a trailing zero beyond 8: exact in bf16
+        RB[i] = (__float_as_uint(c0) >> 16) | (__float_as_uint(c1) & 0xffff0000u);
+    }
+}
+
+struct BackwardQArgs {
+    int T, B, H;
+    const uint32_t *RB;      // packed codes, see packRecurrentBf16
+    const float *scaleR;     // [3H] effective scale per column
+    const float *h, *v, *dhNew;
+    float *dp, *dq, *dh0;
+    const uint8_t *mIh, *mHh, *mGateIn, *mGateOut, *mH, *mH0;
+};
+
+struct StepOperands {
+    float z, r, g, qg, hOld, dhNew;
+    uint32_t keepBits;  // bit i = keep flag: 0..2 gate_out(z,r,n) 3..5 gate_in 6..8 hh 9..11 ih 12 h
+};
+
+template <int CW, int BT>
+__global__ void __launch_bounds__(384) recurrentBackwardQ(const __grid_constant__ BackwardQArgs a) {
+    const int H = a.H, C = 3 * a.H;
+    constexpr int HP = 2 * CW;           // padded hidden size
+    extern __shared__ __align__(16) float smemB[];
+    float *dqS = smemB;                  // [BT][3][HP]  dq scaled by the column scale, gate-major
+    float *partS = dqS + BT * 3 * HP;    // [3][BT][H]
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    const int k = tid % H, p = tid / H;  // blockDim == 3H
+
+    uint32_t rw[CW];
+#pragma unroll
+    for (int jj = 0; jj < CW; ++jj) rw[jj] = a.RB[static_cast<size_t>(p * CW + jj) * H + k];
+    for (int i = tid; i < BT * 3 * HP; i += nthreads) dqS[i] = 0.0f;
+    for (int i = tid; i < 3 * BT * H; i += nthreads) partS[i] = 0.0f;
+
+    constexpr int kSlots = (BT + 2) / 3;  // ceil(BT*H / 3H) gate elements per thread
+    const int elems = nb * H;
+    float dhBase[kSlots];
+    float scale[kSlots][3];
+    StepOperands cur[kSlots], nxt[kSlots];
+#pragma unroll
+    for (int s2 = 0; s2 < kSlots; ++s2) {
+        dhBase[s2] = 0.0f;
+        const int e = tid + s2 * nthreads;
+        const int j = e % H;
+        scale[s2][0] = a.scaleR[j]; scale[s2][1] = a.scaleR[H + j]; scale[s2][2] = a.scaleR[2 * H + j];
+    }
+    auto bit = [](const uint8_t *m, size_t i, int pos) -> uint32_t { return (m ? (m[i] ? 1u : 0u) : 1u) << pos; };
+    auto fetch = [&](int t, StepOperands (&dst)[kSlots]) {
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t row = static_cast<size_t>(t) * a.B + b0 + b;
+                const size_t hi = row * H + j, gi = row * C + j;
+                const float *vRow = a.v + row * 4 * H;
+                StepOperands o;
+                o.z = vRow[j]; o.r = vRow[H + j]; o.g = vRow[2 * H + j]; o.qg = vRow[3 * H + j];
+                o.hOld = a.h[hi];
+                o.dhNew = a.dhNew[hi + static_cast<size_t>(a.B) * H];
+                o.keepBits = bit(a.mGateOut, gi, 0) | bit(a.mGateOut, gi + H, 1) | bit(a.mGateOut, gi + 2 * H, 2) |
+                             bit(a.mGateIn, gi, 3) | bit(a.mGateIn, gi + H, 4) | bit(a.mGateIn, gi + 2 * H, 5) |
+                             bit(a.mHh, gi, 6) | bit(a.mHh, gi + H, 7) | bit(a.mHh, gi + 2 * H, 8) |
+                             bit(a.mIh, gi, 9) | bit(a.mIh, gi + H, 10) | bit(a.mIh, gi + 2 * H, 11) |
+                             bit(a.mH, hi, 12);
+                dst[s2] = o;
+            }
+        }
+    };
+    fetch(a.T - 1, cur);
+    __syncthreads();
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        if (t > 0) fetch(t - 1, nxt);
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        // ---- pointwise derivative with masks (gru_backward_gpu_quant.cu:110-240)
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t gi = (rowBase + b) * C + j;
+                const StepOperands o = cur[s2];
+                auto keep = [&](int pos) { return static_cast<float>((o.keepBits >> pos) & 1u); };
+                const float carried = dhBase[s2] + partS[(0 * BT + b) * H + j] + partS[(1 * BT + b) * H + j] +
+                                      partS[(2 * BT + b) * H + j];
+                const float dhTotal = (o.dhNew + carried) * keep(12);
+                dhBase[s2] = o.z * dhTotal;
+                const float dg = (1.0f - o.z) * dhTotal;
+                const float dz = (o.hOld - o.g) * dhTotal;
+                const float dpG = (1.0f - o.g * o.g) * dg * keep(2) * keep(5);
+                const float dqG = dpG * o.r;
+                const float dr = dpG * o.qg;
+                const float dpR = (o.r * (1.0f - o.r)) * dr;
+                const float dpZ = (o.z * (1.0f - o.z)) * dz;
+                const float kz = keep(0) * keep(3), kr = keep(1) * keep(4);
+                const float pz = dpZ * kz * keep(9), pr = dpR * kr * keep(10), pg = dpG * keep(11);
+                const float qz = dpZ * kz * keep(6), qr = dpR * kr * keep(7), qn = dqG * keep(8);
+                a.dp[gi] = pz; a.dp[gi + H] = pr; a.dp[gi + 2 * H] = pg;
+                a.dq[gi] = qz; a.dq[gi + H] = qr; a.dq[gi + 2 * H] = qn;
+                float *dqRow = dqS + b * 3 * HP;
+                dqRow[j] = qz * scale[s2][0]; dqRow[HP + j] = qr * scale[s2][1]; dqRow[2 * HP + j] = qn * scale[s2][2];
+            }
+        }
+        __syncthreads();
+        // ---- part p of dh[b,k] = sum_j R[k][pH + j] dq'[b][pH + j]
+        {
+            float acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+            const float4 *dq4 = reinterpret_cast<const float4 *>(dqS + p * HP);
+#pragma unroll
+            for (int j4 = 0; j4 < CW / 2; ++j4) {
+                const float w0 = __uint_as_float(rw[2 * j4] << 16), w1 = __uint_as_float(rw[2 * j4] & 0xffff0000u);
+                const float w2 = __uint_as_float(rw[2 * j4 + 1] << 16), w3 = __uint_as_float(rw[2 * j4 + 1] & 0xffff0000u);
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    const float4 d = dq4[b * (3 * HP / 4) + j4];
+                    acc[b] = fmaf(w0, d.x, acc[b]);
+                    acc[b] = fmaf(w1, d.y, acc[b]);
+                    acc[b] = fmaf(w2, d.z, acc[b]);
+                    acc[b] = fmaf(w3, d.w, acc[b]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b) partS[(p * BT + b) * H + k] = acc[b];
+        }
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) cur[s2] = nxt[s2];
+        __syncthreads();
+    }
+#pragma unroll
+    for (int s2 = 0; s2 < kSlots; ++s2) {
+        const int e = tid + s2 * nthreads;
+        if (e < elems) {
+            const int b = e / H, j = e % H;
+            const size_t o = static_cast<size_t>(b0 + b) * H + j;
+            const float carried = dhBase[s2] + partS[(0 * BT + b) * H + j] + partS[(1 * BT + b) * H + j] +
+                                  partS[(2 * BT + b) * H + j];
+            a.dh0[o] = carried * keepOf(a.mH0, o);
+        }
+    }
+}
+
 __global__ void transposeMatrix(const float *__restrict__ in, int rows, int cols, float *__restrict__ out) {
     __shared__ float tile[32][33];
     const int x = blockIdx.x * 32 + threadIdx.x, y0 = blockIdx.y * 32;
@@ -199,27 +362,47 @@ __global__ void reduceSplits(const float *__restrict__ partial, int splits, size
     }
 }
 
-// dx[n][i] = mask * sum_c dp[n][c] * W[i][c]
-constexpr int kGradRows = 16;
-__global__ void inputGrad(const float *__restrict__ dp, int rows, int C, const float *__restrict__ W, int I,
-                          const uint8_t *__restrict__ mask, float *__restrict__ dx) {
-    extern __shared__ float smemB[];
-    float *dps = smemB;  // [kGradRows][C + 1]
-    const int row0 = blockIdx.x * kGradRows, nRows = min(kGradRows, rows - row0);
-    for (int i = threadIdx.x; i < kGradRows * C; i += blockDim.x) {
-        const int r = i / C, c = i % C;
-        dps[r * (C + 1) + c] = r < nRows ? dp[static_cast<size_t>(row0 + r) * C + c] : 0.0f;
+// out[m][n] = mask * sum_k A[m][k] * B[n][k]   (both operands K-contiguous).  Used for
+// dx = dp W^T: M = T*B rows, N = I, K = 3H.  64x64 tile, 32-deep K steps, 4x4 outputs per thread;
+// tiles are stored K-major in shared memory so that the inner product reads are conflict free.
+constexpr int kNtDepth = 32;
+__global__ void __launch_bounds__(256) gemmNT(const float *__restrict__ A, const float *__restrict__ Bm, int M, int N,
+                                              int K, const uint8_t *__restrict__ mask, float *__restrict__ out) {
+    __shared__ float As[kNtDepth][kTile + 1];
+    __shared__ float Bs[kNtDepth][kTile + 1];
+    const int m0 = blockIdx.x * kTile, n0 = blockIdx.y * kTile;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += kNtDepth) {
+        for (int i = threadIdx.x; i < kTile * kNtDepth; i += 256) {
+            const int r = i / kNtDepth, kk = i % kNtDepth;
+            const int k = k0 + kk;
+            As[kk][r] = (m0 + r < M && k < K) ? A[static_cast<size_t>(m0 + r) * K + k] : 0.0f;
+            Bs[kk][r] = (n0 + r < N && k < K) ? Bm[static_cast<size_t>(n0 + r) * K + k] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kNtDepth; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[kk][ty * 4 + i]; bv[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    for (int o = threadIdx.x; o < nRows * I; o += blockDim.x) {
-        const int r = o / I, i = o % I;
-        const float *w = W + static_cast<size_t>(i) * C;
-        const float *d = dps + r * (C + 1);
-        float acc = 0.0f;
-        for (int c = 0; c < C; ++c) acc = fmaf(d[c], w[c], acc);
-        const size_t out = static_cast<size_t>(row0 + r) * I + i;
-        dx[out] = acc * keepOf(mask, out);
-    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) {
+                const size_t o = static_cast<size_t>(m) * N + n;
+                out[o] = acc[i][j] * keepOf(mask, o);
+            }
+        }
 }
 
 // partial[s][c] = sum over the s-th row chunk of g[n][c]; blockIdx.y selects dp or dq.
@@ -251,6 +434,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(rows * C);          // dp
     ws.take<float>(rows * C);          // dq
     ws.take<float>(C * H);             // R transposed
+    ws.take<uint32_t>(3 * 64 * static_cast<size_t>(H));  // packed recurrent codes
     ws.take<float>(static_cast<size_t>(I) * C);  // W real-valued
     ws.take<float>(static_cast<size_t>(H) * C);  // R real-valued
     ws.take<float>(rows * I);          // x real-valued
@@ -274,6 +458,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     const rxmet_gru_masks &mk = call.masks ? *call.masks : none;
 
     const float *W = call.W, *R = call.R, *x = call.x;
+    const float *chanScaleR = nullptr;
     if (call.W_q) {  // QAT path: rebuild the real-valued operands from the saved codes
         RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
         const Exec &e = *call.exec;
@@ -300,55 +485,83 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         }
         afterLaunch("dequantCodes");
         W = Wf; R = Rf; x = xf;
+        chanScaleR = chan + C;
     }
 
-    {
-        KernelTimer timer__("transposeMatrix", st);
-        transposeMatrix<<<dim3((C + 31) / 32, (H + 31) / 32), dim3(32, 8), 0, st>>>(R, H, C, RT);
-    }
-    afterLaunch("transposeMatrix");
-
-    BackwardArgs a{};
-    a.T = T; a.B = B; a.H = H;
-    a.RT = RT; a.h = call.h; a.v = call.v; a.dhNew = call.dh_new; a.dp = dp; a.dq = dq; a.dh0 = call.dh0;
-    a.mIh = mk.weight_ih_linear; a.mHh = mk.weight_hh_linear; a.mGateIn = mk.gate_input;
-    a.mGateOut = mk.gate_output; a.mH = mk.h; a.mH0 = mk.h0;
     int device = 0, smemMax = 0, sms = 0;
     RXMET_CUDA(cudaGetDevice(&device));
     RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
     RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    const int block = std::min(std::max((C + 31) / 32 * 32, 128), 768);
-    a.parts = std::max(1, std::min(block / std::max(H, 1), 8));
-    const int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
-    auto launch = [&](auto kernel, int BT) {
-        const size_t base = sizeof(float) * (static_cast<size_t>(BT) * H + static_cast<size_t>(BT) * C +
-                                             static_cast<size_t>(a.parts) * BT * H);
-        const size_t full = base + sizeof(float) * static_cast<size_t>(C) * H;
-        a.weightsInSmem = full <= static_cast<size_t>(smemMax) ? 1 : 0;
-        const size_t smem = a.weightsInSmem ? full : base;
-        if (smem > static_cast<size_t>(smemMax))
-            fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
-        RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+    if (const char *env = std::getenv("RXMET_GRU_BWD_BT")) bt = std::atoi(env);
+    if (bt != 1 && bt != 2 && bt != 4) bt = 2;
+
+    const bool registerPath = call.W_q != nullptr && call.exec->weightClass == CodeClass::I8 && H <= 128 &&
+                              std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
+    if (registerPath) {
+        const int CW = H <= 32 ? 16 : (H <= 64 ? 32 : 64);
+        uint32_t *RB = ws.take<uint32_t>(3 * static_cast<size_t>(CW) * H);
+        {
+            KernelTimer timer__("packRecurrentBf16", st);
+            packRecurrentBf16<<<gridFor(3 * static_cast<size_t>(CW) * H, 256), 256, 0, st>>>(call.R_q, H, CW, RB);
+        }
+        afterLaunch("packRecurrentBf16");
+        BackwardQArgs q{};
+        q.T = T; q.B = B; q.H = H; q.RB = RB; q.scaleR = chanScaleR;
+        q.h = call.h; q.v = call.v; q.dhNew = call.dh_new; q.dp = dp; q.dq = dq; q.dh0 = call.dh0;
+        q.mIh = mk.weight_ih_linear; q.mHh = mk.weight_hh_linear; q.mGateIn = mk.gate_input;
+        q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
+        const size_t smem = sizeof(float) * (static_cast<size_t>(bt) * 3 * 2 * CW + 3 * static_cast<size_t>(bt) * H);
+        const int grid = (B + bt - 1) / bt;
         {
             KernelTimer timer__("recurrentBackward", st);
-            kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
+#define RXMET_BWD_CASE(CWV, BTV) \
+    if (CW == CWV && bt == BTV) recurrentBackwardQ<CWV, BTV><<<grid, 3 * H, smem, st>>>(q);
+            RXMET_BWD_CASE(16, 1) RXMET_BWD_CASE(16, 2) RXMET_BWD_CASE(16, 4)
+            RXMET_BWD_CASE(32, 1) RXMET_BWD_CASE(32, 2) RXMET_BWD_CASE(32, 4)
+            RXMET_BWD_CASE(64, 1) RXMET_BWD_CASE(64, 2) RXMET_BWD_CASE(64, 4)
+#undef RXMET_BWD_CASE
         }
+        afterLaunch("recurrentBackwardQ");
+    } else {
+        {
+            KernelTimer timer__("transposeMatrix", st);
+            transposeMatrix<<<dim3((C + 31) / 32, (H + 31) / 32), dim3(32, 8), 0, st>>>(R, H, C, RT);
+        }
+        afterLaunch("transposeMatrix");
+
+        BackwardArgs a{};
+        a.T = T; a.B = B; a.H = H;
+        a.RT = RT; a.h = call.h; a.v = call.v; a.dhNew = call.dh_new; a.dp = dp; a.dq = dq; a.dh0 = call.dh0;
+        a.mIh = mk.weight_ih_linear; a.mHh = mk.weight_hh_linear; a.mGateIn = mk.gate_input;
+        a.mGateOut = mk.gate_output; a.mH = mk.h; a.mH0 = mk.h0;
+        const int block = std::min(std::max((C + 31) / 32 * 32, 128), 768);
+        a.parts = std::max(1, std::min(block / std::max(H, 1), 8));
+        auto launch = [&](auto kernel, int BT) {
+            const size_t base = sizeof(float) * (static_cast<size_t>(BT) * H + static_cast<size_t>(BT) * C +
+                                                 static_cast<size_t>(a.parts) * BT * H);
+            const size_t full = base + sizeof(float) * static_cast<size_t>(C) * H;
+            a.weightsInSmem = full <= static_cast<size_t>(smemMax) ? 1 : 0;
+            const size_t smem = a.weightsInSmem ? full : base;
+            if (smem > static_cast<size_t>(smemMax))
+                fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
+            RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            KernelTimer timer__("recurrentBackward", st);
+            kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
+        };
+        if (bt == 4) launch(recurrentBackward<4>, 4);
+        else if (bt == 2) launch(recurrentBackward<2>, 2);
+        else launch(recurrentBackward<1>, 1);
         afterLaunch("recurrentBackward");
-    };
-    if (bt == 4) launch(recurrentBackward<4>, 4);
-    else if (bt == 2) launch(recurrentBackward<2>, 2);
-    else launch(recurrentBackward<1>, 1);
+    }
 
     // dx
     {
-        const size_t smem = sizeof(float) * kGradRows * (C + 1);
-        RXMET_CUDA(cudaFuncSetAttribute(inputGrad, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        {
-            KernelTimer timer__("inputGrad", st);
-            inputGrad<<<static_cast<int>((rows + kGradRows - 1) / kGradRows), 256, smem, st>>>(dp, static_cast<int>(rows), C, W, I, mk.x, call.dx);
-        }
-        afterLaunch("inputGrad");
+        KernelTimer timer__("gemmNT", st);
+        gemmNT<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
+            dp, W, static_cast<int>(rows), I, C, mk.x, call.dx);
     }
+    afterLaunch("gemmNT");
     // dW, dR
     auto weightGrad = [&](const float *A, int M, const float *G, const uint8_t *mask, float *out) {
         const int tilesM = (M + kTile - 1) / kTile, tilesN = (C + kTile - 1) / kTile;

@@ -32,6 +32,28 @@ __device__ __forceinline__ int64_t applyRescale(int64_t x, Rescale r) {
     return rshiftRound(x * static_cast<int64_t>(r.mult), r.shift);
 }
 
+// 32-bit variant for operands whose product with the multiplier provably fits 31 bits
+// (|x| < 2^15 and mult < 2^16).  Same rounding rule.
+__device__ __forceinline__ int32_t rshiftRound32(int32_t x, int n) {
+    if (n <= 0) return x << (-n);
+    if (n > 31) return 0;  // |x| < 2^31 <= half : rounds to zero
+    const bool neg = x < 0;
+    const uint32_t a = neg ? static_cast<uint32_t>(-x) : static_cast<uint32_t>(x);
+    const uint32_t q = a >> n;
+    const uint32_t r = a & ((1u << n) - 1u);
+    const uint32_t half = 1u << (n - 1);
+    const uint32_t up = (r > half) || (r == half && (q & 1u));
+    const int32_t res = static_cast<int32_t>(q + up);
+    return neg ? -res : res;
+}
+
+// Rescale of a small operand (a grid difference): 32-bit when Narrow, else 64-bit.
+template <bool Narrow>
+__device__ __forceinline__ int32_t rescaleSmall(int32_t x, Rescale r) {
+    if constexpr (Narrow) return rshiftRound32(x * r.mult, r.shift);
+    else return static_cast<int32_t>(rshiftRound(static_cast<int64_t>(x) * r.mult, r.shift));
+}
+
 // quantize_ops_helper.h:267-278 ; keep = 1 when the value was inside the grid.
 __device__ __forceinline__ int32_t clampCode(int32_t v, int32_t lo, int32_t hi, uint8_t &keep) {
     keep = (v < lo || v > hi) ? 0 : 1;
@@ -53,13 +75,19 @@ __device__ __forceinline__ int32_t quantizeValue(float v, float scale, int32_t z
 
 // 16-segment table: first segment whose threshold exceeds q_x, else the last
 // (quantize_ops_helper.h:503-532).
+template <bool Narrow = false>
 __device__ __forceinline__ int32_t lutEval(int32_t qx, const Lut &lut) {
     int seg = kSegments - 1;
 #pragma unroll
     for (int i = kSegments - 2; i >= 0; --i) seg = (qx < lut.threshold[i]) ? i : seg;
-    const int64_t bx = static_cast<int64_t>(lut.q_b[seg]) * static_cast<int64_t>(qx - lut.zp_x);
     const int n = lut.n_bx[seg];
-    const int32_t term = (n >= 0) ? static_cast<int32_t>(rshiftRound(bx, n)) : static_cast<int32_t>(bx << (-n));
+    int32_t term;
+    if constexpr (Narrow) {
+        term = rshiftRound32(lut.q_b[seg] * (qx - lut.zp_x), n);
+    } else {
+        const int64_t bx = static_cast<int64_t>(lut.q_b[seg]) * static_cast<int64_t>(qx - lut.zp_x);
+        term = (n >= 0) ? static_cast<int32_t>(rshiftRound(bx, n)) : static_cast<int32_t>(bx << (-n));
+    }
     return term + lut.term_c[seg];
 }
 
@@ -75,41 +103,44 @@ struct GateCodes {
 
 // One (batch, hidden) element of a GRU step on the integer grids
 // (quantize_ops_helper.h:683-1023).  ih* / hh* are the linear-stage codes of
-// the three gates, hOld the previous hidden code.
+// the three gates, hOld the previous hidden code.  Narrow = true computes the
+// grid-to-grid rescales and the table products in 32 bit; the host enables it
+// only when every such operand is below 2^15 in magnitude and every table
+// slope times its operand is below 2^31 (true for all grids of 8 bit or less).
+template <bool Narrow = false>
 __device__ __forceinline__ GateCodes gruCell(int32_t ihz, int32_t ihr, int32_t ihn, int32_t hhz, int32_t hhr,
                                              int32_t hhn, int32_t hOld, const GateExec &g, GateMasks &m) {
     const int32_t zpIh = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], zpHh = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
     GateCodes c;
     {   // update gate
-        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihz) - zpIh, g.ih_to_update));
-        const int32_t b = static_cast<int32_t>(applyRescale(static_cast<int64_t>(hhz) - zpHh, g.hh_to_update));
+        const int32_t a = rescaleSmall<Narrow>(ihz - zpIh, g.ih_to_update);
+        const int32_t b = rescaleSmall<Narrow>(hhz - zpHh, g.hh_to_update);
         const int32_t pre = clampCode(a + b + g.zp[RXMET_GRU_UPDATE_GATE_INPUT], g.qlo[RXMET_GRU_UPDATE_GATE_INPUT],
                                       g.qhi[RXMET_GRU_UPDATE_GATE_INPUT], m.in[0]);
-        c.z = clampCode(lutEval(pre, g.lut_update), g.qlo[RXMET_GRU_UPDATE_GATE_OUTPUT],
+        c.z = clampCode(lutEval<Narrow>(pre, g.lut_update), g.qlo[RXMET_GRU_UPDATE_GATE_OUTPUT],
                         g.qhi[RXMET_GRU_UPDATE_GATE_OUTPUT], m.out[0]);
     }
     {   // reset gate
-        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihr) - zpIh, g.ih_to_reset));
-        const int32_t b = static_cast<int32_t>(applyRescale(static_cast<int64_t>(hhr) - zpHh, g.hh_to_reset));
+        const int32_t a = rescaleSmall<Narrow>(ihr - zpIh, g.ih_to_reset);
+        const int32_t b = rescaleSmall<Narrow>(hhr - zpHh, g.hh_to_reset);
         const int32_t pre = clampCode(a + b + g.zp[RXMET_GRU_RESET_GATE_INPUT], g.qlo[RXMET_GRU_RESET_GATE_INPUT],
                                       g.qhi[RXMET_GRU_RESET_GATE_INPUT], m.in[1]);
-        c.r = clampCode(lutEval(pre, g.lut_reset), g.qlo[RXMET_GRU_RESET_GATE_OUTPUT],
+        c.r = clampCode(lutEval<Narrow>(pre, g.lut_reset), g.qlo[RXMET_GRU_RESET_GATE_OUTPUT],
                         g.qhi[RXMET_GRU_RESET_GATE_OUTPUT], m.out[1]);
     }
     {   // candidate: the reset product goes straight to the gate-input grid
         const int64_t prod = (static_cast<int64_t>(c.r) - g.zp[RXMET_GRU_RESET_GATE_OUTPUT]) *
                              (static_cast<int64_t>(hhn) - zpHh);
         const int32_t rh = static_cast<int32_t>(applyRescale(prod, g.rh_to_new));
-        const int32_t a = static_cast<int32_t>(applyRescale(static_cast<int64_t>(ihn) - zpIh, g.ih_to_new));
+        const int32_t a = rescaleSmall<Narrow>(ihn - zpIh, g.ih_to_new);
         const int32_t pre = clampCode(a + rh + g.zp[RXMET_GRU_NEW_GATE_INPUT], g.qlo[RXMET_GRU_NEW_GATE_INPUT],
                                       g.qhi[RXMET_GRU_NEW_GATE_INPUT], m.in[2]);
-        c.n = clampCode(lutEval(pre, g.lut_new), g.qlo[RXMET_GRU_NEW_GATE_OUTPUT], g.qhi[RXMET_GRU_NEW_GATE_OUTPUT],
+        c.n = clampCode(lutEval<Narrow>(pre, g.lut_new), g.qlo[RXMET_GRU_NEW_GATE_OUTPUT], g.qhi[RXMET_GRU_NEW_GATE_OUTPUT],
                         m.out[2]);
     }
     {   // h' = z*h + (1-z)*n on the h grid, one rounding for the sum
         const int32_t zpH = g.zp[RXMET_GRU_H];
-        const int32_t nAligned =
-            static_cast<int32_t>(applyRescale(static_cast<int64_t>(c.n) - g.zp[RXMET_GRU_NEW_GATE_OUTPUT], g.new_to_h)) + zpH;
+        const int32_t nAligned = rescaleSmall<Narrow>(c.n - g.zp[RXMET_GRU_NEW_GATE_OUTPUT], g.new_to_h) + zpH;
         const int64_t oldPart = (static_cast<int64_t>(c.z) - g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]) *
                                 (static_cast<int64_t>(hOld) - zpH);
         const int64_t newPart = (static_cast<int64_t>(g.quant_one) - c.z) * (static_cast<int64_t>(nAligned) - zpH);

@@ -20,6 +20,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 #include <vector>
@@ -323,6 +324,150 @@ recurrentForward(const __grid_constant__ RecurrentArgs a, const __grid_constant_
     }
 }
 
+// ---- 4b. the recurrence for 8-bit grids: weights in registers ----------------
+//
+// Thread c owns column c of R for the whole sequence as KW packed words (four int8 codes each),
+// so a step's GEMM touches shared memory only for the broadcast reads of h (128-bit loads).  The
+// ih codes of step t+1 are fetched while step t computes, which takes the L2/HBM latency off the
+// serial chain.  Requires 3H <= blockDim and H <= 4*KW.
+template <int KW, int BT, bool Narrow>
+__global__ void __launch_bounds__(KW * 12)
+recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec gateParam) {
+    const int H = a.H, C = 3 * a.H;
+    constexpr int kPadded = KW * 4;
+    __shared__ GateExec g;
+    __shared__ __align__(16) int8_t hS[BT * kPadded];
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    int32_t *hhS = reinterpret_cast<int32_t *>(smemRaw);  // [BT][C]
+
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    for (int i = tid; i < static_cast<int>(sizeof(GateExec) / 4); i += nthreads)
+        reinterpret_cast<int32_t *>(&g)[i] = reinterpret_cast<const int32_t *>(&gateParam)[i];
+
+    // this thread's column of R, zero point compensation and bias term
+    const bool hasColumn = tid < C;
+    int32_t rw[KW];
+    int64_t cmp = 0, bias = 0;
+    Rescale rs{1, 0};
+    {
+        const int32_t *Rg = static_cast<const int32_t *>(a.R);
+#pragma unroll
+        for (int kk = 0; kk < KW; ++kk) rw[kk] = (hasColumn && kk < a.kWords) ? Rg[static_cast<size_t>(kk) * C + tid] : 0;
+        if (hasColumn) { cmp = a.comp[tid]; bias = a.biasAcc[tid]; rs = a.rescale[tid]; }
+    }
+    const int8_t *h0 = static_cast<const int8_t *>(a.h0);
+    const int srcPadded = a.kWords * 4;
+    for (int i = tid; i < BT * kPadded; i += nthreads) {
+        const int b = i / kPadded, k = i % kPadded;
+        hS[i] = (b < nb && k < srcPadded) ? h0[static_cast<size_t>(b0 + b) * srcPadded + k] : int8_t(0);
+    }
+    __syncthreads();
+
+    const float scaleH = g.eff[RXMET_GRU_H];
+    const int32_t zpH = g.zp[RXMET_GRU_H];
+    for (int i = tid; i < nb * H; i += nthreads) {
+        const int b = i / H, j = i % H;
+        const int32_t q = hS[b * kPadded + j];
+        const size_t o = static_cast<size_t>(b0 + b) * H + j;
+        a.h[o] = static_cast<float>(q - zpH) * scaleH;
+        if (a.hq) a.hq[o] = q;
+    }
+
+    const int16_t *ih = static_cast<const int16_t *>(a.ih);
+    const int32_t zpOut = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
+    const int32_t loOut = g.qlo[RXMET_GRU_WEIGHT_HH_LINEAR], hiOut = g.qhi[RXMET_GRU_WEIGHT_HH_LINEAR];
+    const float sZ = g.eff[RXMET_GRU_UPDATE_GATE_OUTPUT], sR = g.eff[RXMET_GRU_RESET_GATE_OUTPUT];
+    const float sN = g.eff[RXMET_GRU_NEW_GATE_OUTPUT], sHh = g.eff[RXMET_GRU_WEIGHT_HH_LINEAR];
+    const int32_t zZ = g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT], zR = g.zp[RXMET_GRU_RESET_GATE_OUTPUT];
+    const int32_t zN = g.zp[RXMET_GRU_NEW_GATE_OUTPUT];
+
+    // gate phase: element e = tid + s*nthreads of this tile (at most kSlots per thread)
+    constexpr int kSlots = 2;
+    const int elems = nb * H;
+    int16_t ihCur[kSlots][3], ihNext[kSlots][3];
+    auto fetch = [&](int t, int16_t (&dst)[kSlots][3]) {
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int16_t *row = ih + (static_cast<size_t>(t) * a.B + b0 + e / H) * C + (e % H);
+                dst[s2][0] = row[0]; dst[s2][1] = row[H]; dst[s2][2] = row[2 * H];
+            }
+        }
+    };
+    fetch(0, ihCur);
+
+    const int4 *hS4 = reinterpret_cast<const int4 *>(hS);
+    for (int t = 0; t < a.T; ++t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        if (t + 1 < a.T) fetch(t + 1, ihNext);
+
+        if (hasColumn) {
+            int32_t acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0;
+#pragma unroll
+            for (int k4 = 0; k4 < KW / 4; ++k4) {
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    const int4 hv = hS4[b * (KW / 4) + k4];
+                    acc[b] = __dp4a(rw[4 * k4 + 0], hv.x, acc[b]);
+                    acc[b] = __dp4a(rw[4 * k4 + 1], hv.y, acc[b]);
+                    acc[b] = __dp4a(rw[4 * k4 + 2], hv.z, acc[b]);
+                    acc[b] = __dp4a(rw[4 * k4 + 3], hv.w, acc[b]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                uint8_t keep;
+                hhS[b * C + tid] = linearEpilogue(acc[b], cmp, bias, rs, zpOut, loOut, hiOut, keep);
+                if (a.maskHh && b < nb) a.maskHh[(rowBase + b) * C + tid] = keep;
+            }
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t row = rowBase + b;
+                const int32_t *hhRow = hhS + b * C;
+                GateMasks m;
+                const int32_t hOld = hS[b * kPadded + j];
+                const int32_t hhn = hhRow[2 * H + j];
+                const GateCodes q = gruCell<Narrow>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j],
+                                                    hhn, hOld, g, m);
+                hS[b * kPadded + j] = static_cast<int8_t>(q.h);
+                const size_t ho = (row + a.B) * H + j;
+                a.h[ho] = static_cast<float>(q.h - zpH) * scaleH;
+                float *vRow = a.v + row * 4 * H;
+                vRow[j] = static_cast<float>(q.z - zZ) * sZ;
+                vRow[H + j] = static_cast<float>(q.r - zR) * sR;
+                vRow[2 * H + j] = static_cast<float>(q.n - zN) * sN;
+                vRow[3 * H + j] = static_cast<float>(hhn - zpOut) * sHh;
+                if (a.hq) a.hq[ho] = q.h;
+                if (a.vq) {
+                    int32_t *vq = a.vq + row * 4 * H;
+                    vq[j] = q.z; vq[H + j] = q.r; vq[2 * H + j] = q.n; vq[3 * H + j] = hhn;
+                }
+                if (a.maskGateIn) {
+                    uint8_t *mi = a.maskGateIn + row * C, *mo = a.maskGateOut + row * C;
+                    mi[j] = m.in[0]; mi[H + j] = m.in[1]; mi[2 * H + j] = m.in[2];
+                    mo[j] = m.out[0]; mo[H + j] = m.out[1]; mo[2 * H + j] = m.out[2];
+                    a.maskH[row * H + j] = m.h;
+                }
+            }
+        }
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2)
+#pragma unroll
+            for (int q3 = 0; q3 < 3; ++q3) ihCur[s2][q3] = ihNext[s2][q3];
+        __syncthreads();
+    }
+}
+
 size_t recurrentSmemBytes(int H, int kWords, int pack, size_t wordBytes, size_t actBytes, int BT, bool weights) {
     const int C = 3 * H;
     auto up = [](size_t v) { return (v + 15) & ~static_cast<size_t>(15); };
@@ -370,6 +515,27 @@ ChannelDevice uploadChannels(const Exec &e, Workspace &ws, cudaStream_t st) {
     d.gemmX = reinterpret_cast<const Rescale *>(block + 4 * C);
     d.biasX = d.gemmX + C; d.gemmH = d.gemmX + 2 * C; d.biasH = d.gemmX + 3 * C;
     return d;
+}
+
+// 32-bit gate arithmetic is exact when every grid difference that gets rescaled is below 2^13
+// in magnitude (multipliers are below 2^16) and every table slope times its operand is below
+// 2^31: linear, gate-input and gate-output grids of at most 12 bits with zero points on the grid.
+bool narrowGateMath(const GateExec &g) {
+    const int ops[] = {RXMET_GRU_WEIGHT_IH_LINEAR, RXMET_GRU_WEIGHT_HH_LINEAR, RXMET_GRU_UPDATE_GATE_INPUT,
+                       RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT, RXMET_GRU_UPDATE_GATE_OUTPUT,
+                       RXMET_GRU_RESET_GATE_OUTPUT, RXMET_GRU_NEW_GATE_OUTPUT};
+    for (int op : ops) {
+        const int64_t span = static_cast<int64_t>(g.qhi[op]) - g.qlo[op];
+        if (span >= (1 << 12) || g.zp[op] < g.qlo[op] || g.zp[op] > g.qhi[op]) return false;
+    }
+    const Rescale rs[] = {g.ih_to_update, g.hh_to_update, g.ih_to_reset, g.hh_to_reset, g.ih_to_new, g.new_to_h};
+    for (const Rescale &r : rs)
+        if (r.mult < 0 || r.mult >= (1 << 16) || r.shift < 0) return false;
+    const Lut *luts[] = {&g.lut_update, &g.lut_reset, &g.lut_new};
+    for (const Lut *l : luts)
+        for (int s2 = 0; s2 < kSegments; ++s2)
+            if (l->q_b[s2] >= (1 << 13) || l->q_b[s2] <= -(1 << 13) || l->n_bx[s2] < 0) return false;
+    return true;
 }
 
 template <class WT, class AT, class LT>
@@ -493,6 +659,36 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
         }
         afterLaunch("recurrentForward");
     };
+    if constexpr (std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value && std::is_same<LT, int16_t>::value) {
+        // register-resident variant: one thread per column, at most two gate elements per thread
+        const int blockI8 = padTo(C, 32);
+        int btI8 = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+        if (const char *env = std::getenv("RXMET_GRU_FWD_BT")) btI8 = std::atoi(env);
+        const bool fits = blockI8 <= 768 && hWords <= 64 && btI8 * H <= 2 * blockI8;
+        if (fits && (btI8 == 1 || btI8 == 2 || btI8 == 4)) {
+            const bool narrow = narrowGateMath(g);
+            auto launchI8 = [&](auto kernel) {
+                const size_t smem = sizeof(int32_t) * btI8 * C;
+                kernel<<<(B + btI8 - 1) / btI8, blockI8, smem, st>>>(a, g);
+            };
+            KernelTimer timer__("recurrentForward", st);
+#define RXMET_I8_CASE(KW, BT)                                                              \
+    if (hWords <= KW && btI8 == BT) {                                                       \
+        if (narrow) launchI8(recurrentForwardI8<KW, BT, true>);                             \
+        else launchI8(recurrentForwardI8<KW, BT, false>);                                   \
+        goto launchedI8;                                                                    \
+    }
+            RXMET_I8_CASE(16, 1) RXMET_I8_CASE(16, 2) RXMET_I8_CASE(16, 4)
+            RXMET_I8_CASE(32, 1) RXMET_I8_CASE(32, 2) RXMET_I8_CASE(32, 4)
+            RXMET_I8_CASE(64, 1) RXMET_I8_CASE(64, 2) RXMET_I8_CASE(64, 4)
+#undef RXMET_I8_CASE
+        launchedI8:;
+        }
+        if (fits && (btI8 == 1 || btI8 == 2 || btI8 == 4)) {
+            afterLaunch("recurrentForwardI8");
+            return;
+        }
+    }
     if (bt == 4) launch(recurrentForward<WT, AT, LT, 4>, 4);
     else if (bt == 2) launch(recurrentForward<WT, AT, LT, 2>, 2);
     else launch(recurrentForward<WT, AT, LT, 1>, 1);
