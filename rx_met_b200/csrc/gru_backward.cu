@@ -351,6 +351,189 @@ __global__ void __launch_bounds__(256) gemmTN(const float *__restrict__ A, const
         }
 }
 
+// ---- weight and bias gradients on tensor cores --------------------------------
+//
+// dW = x^T dp and dR = h^T dq contract over the T*B rows.  With activation grids of at most 8
+// bits the left operand is an integer of magnitude <= 255 times one scale: exact in bf16.  The
+// right operand (fp32 gradients) is split into three bf16 terms that carry all 24 significand
+// bits, so every product is exact and only the fp32 accumulation rounds, as in an fp32 GEMM.
+// A row of ones appended to the left operand yields the column sums, i.e. the bias gradients,
+// from the same pass over dp / dq.  Split-K partials are reduced in a fixed order afterwards.
+//
+// Tile: all M rows (MT m16-tiles) x 64 columns per CTA, 8 warps = 8 n8-tiles, K chunks of 32
+// staged in shared memory as [k][m] / [k][n] and read with transposing ldmatrix.
+constexpr int kWgChunk = 32, kWgCols = 64;
+
+struct WeightGradProblem {
+    const int32_t *aCodes;  // [K][M] integer codes (x path), or
+    const float *aFloat;    // [K][M] dequantized values (h path)
+    float aInvScale;        // 1/scale for the float path
+    int32_t aZero;          // zero point for the code path
+    int M;                  // real rows (multiple of 4); row M is the ones row
+    const float *B;         // [K][N] gradients, N a multiple of 4
+    float *partial;         // [splits][M+1][N]
+};
+
+__device__ __forceinline__ uint32_t packBf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16Lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16Hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Loads of the next K chunk are issued into registers before the tensor work of the current
+// chunk, so the HBM latency overlaps the MMAs; one shared-memory buffer, two barriers per chunk.
+template <int MT>
+__global__ void __launch_bounds__(256, 2) weightGradMma(const WeightGradProblem p, int K, int N, int chunkK) {
+    constexpr int MP = MT * 16 + 8;       // padded row length (bf16 elements) of the A tile
+    constexpr int NP = kWgCols + 8;
+    constexpr int AV = (MT + 1) / 2;      // 4-element A vectors per thread and chunk (upper bound)
+    __shared__ __align__(16) uint16_t As[kWgChunk][MP];
+    __shared__ __align__(16) uint16_t Bs[3][kWgChunk][NP];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * kWgCols;
+    const int kBegin = blockIdx.y * chunkK, kEnd = min(K, kBegin + chunkK);
+    const int M = p.M, M4 = M / 4;
+
+    // constant part of the A tile: the ones column at m == M, zeros beyond
+    for (int i = tid; i < kWgChunk * (MT * 16 - M); i += 256) {
+        const int kk = i / (MT * 16 - M), m = M + i % (MT * 16 - M);
+        As[kk][m] = (m == M) ? 0x3f80 : 0;
+    }
+
+    // per-thread slots of the chunk loads (fixed across chunks)
+    int aRow[AV], aCol[AV];
+#pragma unroll
+    for (int v = 0; v < AV; ++v) {
+        const int idx = tid + v * 256;
+        aRow[v] = idx < kWgChunk * M4 ? idx / M4 : -1;
+        aCol[v] = idx < kWgChunk * M4 ? (idx % M4) * 4 : 0;
+    }
+    const int bRow0 = tid / 16, bCol = (tid % 16) * 4;  // two B vectors per thread: rows bRow0, bRow0+16
+    const bool bColOk = n0 + bCol < N;
+
+    float4 aReg[AV], bReg[2];
+    auto loadChunk = [&](int k0) {
+#pragma unroll
+        for (int v = 0; v < AV; ++v) {
+            aReg[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int k = k0 + aRow[v];
+            if (aRow[v] >= 0 && k < kEnd) {
+                if (p.aCodes) {
+                    const int4 q = *reinterpret_cast<const int4 *>(p.aCodes + static_cast<size_t>(k) * M + aCol[v]);
+                    aReg[v] = make_float4(static_cast<float>(q.x - p.aZero), static_cast<float>(q.y - p.aZero),
+                                          static_cast<float>(q.z - p.aZero), static_cast<float>(q.w - p.aZero));
+                } else {
+                    aReg[v] = *reinterpret_cast<const float4 *>(p.aFloat + static_cast<size_t>(k) * M + aCol[v]);
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+            const int k = k0 + bRow0 + v * 16;
+            bReg[v] = (bColOk && k < kEnd) ? *reinterpret_cast<const float4 *>(p.B + static_cast<size_t>(k) * N + n0 + bCol)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto storeChunk = [&]() {
+#pragma unroll
+        for (int v = 0; v < AV; ++v) {
+            if (aRow[v] >= 0) {
+                float4 a = aReg[v];
+                if (!p.aCodes) {  // recover the integer code difference from the dequantized value
+                    a.x = rintf(a.x * p.aInvScale); a.y = rintf(a.y * p.aInvScale);
+                    a.z = rintf(a.z * p.aInvScale); a.w = rintf(a.w * p.aInvScale);
+                }
+                *reinterpret_cast<uint2 *>(&As[aRow[v]][aCol[v]]) = make_uint2(packBf16(a.x, a.y), packBf16(a.z, a.w));
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+            const float4 b = bReg[v];
+            const uint32_t h0 = packBf16(b.x, b.y), h1 = packBf16(b.z, b.w);
+            const float rx = b.x - bf16Lo(h0), ry = b.y - bf16Hi(h0), rz = b.z - bf16Lo(h1), rw = b.w - bf16Hi(h1);
+            const uint32_t m0 = packBf16(rx, ry), m1 = packBf16(rz, rw);
+            const uint32_t l0 = packBf16(rx - bf16Lo(m0), ry - bf16Hi(m0)), l1 = packBf16(rz - bf16Lo(m1), rw - bf16Hi(m1));
+            const int row = bRow0 + v * 16;
+            *reinterpret_cast<uint2 *>(&Bs[0][row][bCol]) = make_uint2(h0, h1);
+            *reinterpret_cast<uint2 *>(&Bs[1][row][bCol]) = make_uint2(m0, m1);
+            *reinterpret_cast<uint2 *>(&Bs[2][row][bCol]) = make_uint2(l0, l1);
+        }
+    };
+
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+    loadChunk(kBegin);
+    storeChunk();
+    __syncthreads();
+    for (int k0 = kBegin; k0 < kEnd; k0 += kWgChunk) {
+        const bool more = k0 + kWgChunk < kEnd;
+        if (more) loadChunk(k0 + kWgChunk);
+#pragma unroll
+        for (int ks = 0; ks < kWgChunk; ks += 16) {
+            uint32_t b[3][2];
+#pragma unroll
+            for (int sp = 0; sp < 3; ++sp) {
+                const uint32_t addr = static_cast<uint32_t>(
+                    __cvta_generic_to_shared(&Bs[sp][ks + (lane & 7) + ((lane >> 3) & 1) * 8][warp * 8]));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                             : "=r"(b[sp][0]), "=r"(b[sp][1]) : "r"(addr));
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t a[4];
+                const int id = lane >> 3, r = lane & 7;
+                const uint32_t addr = static_cast<uint32_t>(
+                    __cvta_generic_to_shared(&As[ks + (id >> 1) * 8 + r][mt * 16 + (id & 1) * 8]));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) {
+                    asm volatile(
+                        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                        "{%0,%1,%2,%3};"
+                        : "+f"(acc[mt][0]), "+f"(acc[mt][1]), "+f"(acc[mt][2]), "+f"(acc[mt][3])
+                        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[sp][0]), "r"(b[sp][1]));
+                }
+            }
+        }
+        __syncthreads();
+        if (more) storeChunk();
+        __syncthreads();
+    }
+    float *out = p.partial + static_cast<size_t>(blockIdx.y) * (M + 1) * N;
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = mt * 16 + g + half * 8;
+            const int n = n0 + warp * 8 + 2 * t4;
+            if (m <= M && n < N)
+                *reinterpret_cast<float2 *>(out + static_cast<size_t>(m) * N + n) =
+                    make_float2(acc[mt][half * 2], acc[mt][half * 2 + 1]);
+        }
+    }
+}
+
+// weight[m][n] = scale * mask * sum_s partial[s][m][n] (m < M); bias[n] = biasMask * sum_s partial[s][M][n]
+__global__ void reduceWeightGrad(const float *__restrict__ partial, int splits, int M, int N, float scale,
+                                 const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
+                                 float *__restrict__ weight, float *__restrict__ bias) {
+    const size_t total = static_cast<size_t>(M + 1) * N;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float s = 0.0f;
+        for (int sp = 0; sp < splits; ++sp) s += partial[static_cast<size_t>(sp) * total + i];
+        const size_t m = i / N, n = i % N;
+        if (m < static_cast<size_t>(M)) weight[i] = s * scale * keepOf(weightMask, i);
+        else bias[n] = s * keepOf(biasMask, n);
+    }
+}
+
 // out[i] = mask[i] * sum_s partial[s][i], s ascending.
 __global__ void reduceSplits(const float *__restrict__ partial, int splits, size_t n, const uint8_t *__restrict__ mask,
                              float *__restrict__ out) {
@@ -444,6 +627,10 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(splitW * I * C);
     ws.take<float>(splitR * H * C);
     ws.take<float>(2 * kBiasSplits * C);
+    // tensor-core path: at most ceil(rows/256) splits of (I+1) and (H+1) rows
+    const size_t splitT = std::min<size_t>((rows + 255) / 256, 2 * 148 + 8);
+    ws.take<float>(splitT * (I + 1) * C);
+    ws.take<float>(splitT * (H + 1) * C);
     return ws.used() + 4096;
 }
 
@@ -562,7 +749,52 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             dp, W, static_cast<int>(rows), I, C, mk.x, call.dx);
     }
     afterLaunch("gemmNT");
-    // dW, dR
+    // dW, dR, dbw, dbr
+    const bool tensorGrads = call.W_q != nullptr && call.exec->actClass == CodeClass::I8 && I + 1 <= 144 &&
+                             H + 1 <= 144 && I % 4 == 0 && H % 4 == 0 &&
+                             std::getenv("RXMET_GRU_GRAD_SIMT") == nullptr;
+    if (tensorGrads) {
+        const Exec &e = *call.exec;
+        const int K = static_cast<int>(rows);
+        const int nTiles = (C + kWgCols - 1) / kWgCols;
+        int splits = std::max(1, std::min((2 * sms + 2 * nTiles - 1) / (2 * nTiles), (K + 255) / 256));
+        const int chunkK = ((K + splits - 1) / splits + kWgChunk - 1) / kWgChunk * kWgChunk;
+        splits = (K + chunkK - 1) / chunkK;
+        WeightGradProblem px{}, ph{};
+        px.aCodes = call.x_q; px.aZero = e.gate.zp[RXMET_GRU_X]; px.M = I; px.B = dp;
+        px.partial = ws.take<float>(static_cast<size_t>(splits) * (I + 1) * C);
+        ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
+        ph.partial = ws.take<float>(static_cast<size_t>(splits) * (H + 1) * C);
+        auto launchWg = [&](const WeightGradProblem &prob) {
+            const int mt = (prob.M + 1 + 15) / 16;
+            const dim3 grid(nTiles, splits);
+            KernelTimer timer__("weightGradMma", st);
+            switch (mt) {
+#define RXMET_WG_CASE(MTV) case MTV: weightGradMma<MTV><<<grid, 256, 0, st>>>(prob, K, C, chunkK); break;
+                RXMET_WG_CASE(1) RXMET_WG_CASE(2) RXMET_WG_CASE(3) RXMET_WG_CASE(4) RXMET_WG_CASE(5)
+                RXMET_WG_CASE(6) RXMET_WG_CASE(7) RXMET_WG_CASE(8) RXMET_WG_CASE(9)
+#undef RXMET_WG_CASE
+                default: fail(RXMET_ERR_UNSUPPORTED, "weight gradient tile count %d", mt);
+            }
+        };
+        launchWg(px);
+        afterLaunch("weightGradMma");
+        launchWg(ph);
+        afterLaunch("weightGradMma");
+        {
+            KernelTimer timer__("reduceWeightGrad", st);
+            reduceWeightGrad<<<gridFor(static_cast<size_t>(I + 1) * C, 256), 256, 0, st>>>(
+                px.partial, splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw);
+        }
+        afterLaunch("reduceWeightGrad");
+        {
+            KernelTimer timer__("reduceWeightGrad", st);
+            reduceWeightGrad<<<gridFor(static_cast<size_t>(H + 1) * C, 256), 256, 0, st>>>(
+                ph.partial, splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr);
+        }
+        afterLaunch("reduceWeightGrad");
+        return;
+    }
     auto weightGrad = [&](const float *A, int M, const float *G, const uint8_t *mask, float *out) {
         const int tilesM = (M + kTile - 1) / kTile, tilesN = (C + kTile - 1) / kTile;
         const int splits = splitsFor(static_cast<int>(rows), tilesM * tilesN);

@@ -17,14 +17,12 @@ namespace gru {
 // shifts left (quantize_ops_helper.h:201-224).
 __device__ __forceinline__ int64_t rshiftRound(int64_t x, int n) {
     if (n <= 0) return x << (-n);
-    const bool neg = x < 0;
-    const uint64_t a = neg ? static_cast<uint64_t>(-x) : static_cast<uint64_t>(x);
-    const uint64_t q = a >> n;
-    const uint64_t r = a & ((1ull << n) - 1ull);
+    // floor quotient + non-negative remainder: round-half-even is symmetric, so this equals the
+    // reference's round-the-magnitude-then-negate formulation for every x
+    const int64_t q = x >> n;
+    const uint64_t r = static_cast<uint64_t>(x) & ((1ull << n) - 1ull);
     const uint64_t half = 1ull << (n - 1);
-    const uint64_t up = (r > half) || (r == half && (q & 1ull));
-    const int64_t res = static_cast<int64_t>(q + up);
-    return neg ? -res : res;
+    return q + static_cast<int64_t>((r > half) || (r == half && (q & 1)));
 }
 
 // quantize_ops_helper.h:242-248
@@ -36,15 +34,16 @@ __device__ __forceinline__ int64_t applyRescale(int64_t x, Rescale r) {
 // (|x| < 2^15 and mult < 2^16).  Same rounding rule.
 __device__ __forceinline__ int32_t rshiftRound32(int32_t x, int n) {
     if (n <= 0) return x << (-n);
-    if (n > 31) return 0;  // |x| < 2^31 <= half : rounds to zero
-    const bool neg = x < 0;
-    const uint32_t a = neg ? static_cast<uint32_t>(-x) : static_cast<uint32_t>(x);
-    const uint32_t q = a >> n;
-    const uint32_t r = a & ((1u << n) - 1u);
+    if (n > 31) return 0;  // |x| < 2^30 < half : rounds to zero
+    const int32_t q = x >> n;
+    const uint32_t r = static_cast<uint32_t>(x) & ((1u << n) - 1u);
     const uint32_t half = 1u << (n - 1);
-    const uint32_t up = (r > half) || (r == half && (q & 1u));
-    const int32_t res = static_cast<int32_t>(q + up);
-    return neg ? -res : res;
+    return q + static_cast<int32_t>((r > half) || (r == half && (q & 1)));
+}
+
+// 32-bit operand times 16-bit multiplier in one widening multiply, then the 64-bit rounding shift.
+__device__ __forceinline__ int32_t rescaleWide(int32_t x, Rescale r) {
+    return static_cast<int32_t>(rshiftRound(static_cast<int64_t>(x) * static_cast<int64_t>(r.mult), r.shift));
 }
 
 // Rescale of a small operand (a grid difference): 32-bit when Narrow, else 64-bit.
@@ -146,6 +145,55 @@ __device__ __forceinline__ GateCodes gruCell(int32_t ihz, int32_t ihr, int32_t i
         const int64_t newPart = (static_cast<int64_t>(g.quant_one) - c.z) * (static_cast<int64_t>(nAligned) - zpH);
         const int32_t hNew = static_cast<int32_t>(applyRescale(oldPart + newPart, g.update_old_to_h)) + zpH;
         c.h = clampCode(hNew, g.qlo[RXMET_GRU_H], g.qhi[RXMET_GRU_H], m.h);
+    }
+    return c;
+}
+
+// Direct activation tables: entry [q - lo] = (output code << 1) | keep, for every gate-input code.
+struct DirectTables {
+    const int32_t *update, *reset, *fresh;
+};
+
+// The same cell for small grids (the host checks: linear, gate-input and gate-output grids of at
+// most 10 bits, zero points on their grids, non-negative shifts): 32-bit rescales, widening
+// multiplies for the two products, activations read from direct tables.  az/ar/an are the ih
+// contributions ALREADY rescaled to the three gate-input grids (the input projection does that
+// once for all steps, since it does not depend on the state).
+__device__ __forceinline__ GateCodes gruCellFast(int32_t az, int32_t ar, int32_t an, int32_t hhz, int32_t hhr,
+                                                 int32_t hhn, int32_t hOld, const GateExec &g, const DirectTables &tab,
+                                                 GateMasks &m) {
+    const int32_t zpHh = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
+    GateCodes c;
+    {
+        const int32_t b = rshiftRound32((hhz - zpHh) * g.hh_to_update.mult, g.hh_to_update.shift);
+        const int32_t lo = g.qlo[RXMET_GRU_UPDATE_GATE_INPUT];
+        const int32_t pre = clampCode(az + b + g.zp[RXMET_GRU_UPDATE_GATE_INPUT], lo, g.qhi[RXMET_GRU_UPDATE_GATE_INPUT], m.in[0]);
+        const int32_t e = tab.update[pre - lo];
+        c.z = e >> 1;
+        m.out[0] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t b = rshiftRound32((hhr - zpHh) * g.hh_to_reset.mult, g.hh_to_reset.shift);
+        const int32_t lo = g.qlo[RXMET_GRU_RESET_GATE_INPUT];
+        const int32_t pre = clampCode(ar + b + g.zp[RXMET_GRU_RESET_GATE_INPUT], lo, g.qhi[RXMET_GRU_RESET_GATE_INPUT], m.in[1]);
+        const int32_t e = tab.reset[pre - lo];
+        c.r = e >> 1;
+        m.out[1] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t prod = (c.r - g.zp[RXMET_GRU_RESET_GATE_OUTPUT]) * (hhn - zpHh);
+        const int32_t rh = rescaleWide(prod, g.rh_to_new);
+        const int32_t lo = g.qlo[RXMET_GRU_NEW_GATE_INPUT];
+        const int32_t pre = clampCode(an + rh + g.zp[RXMET_GRU_NEW_GATE_INPUT], lo, g.qhi[RXMET_GRU_NEW_GATE_INPUT], m.in[2]);
+        const int32_t e = tab.fresh[pre - lo];
+        c.n = e >> 1;
+        m.out[2] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t zpH = g.zp[RXMET_GRU_H];
+        const int32_t nAligned = rshiftRound32((c.n - g.zp[RXMET_GRU_NEW_GATE_OUTPUT]) * g.new_to_h.mult, g.new_to_h.shift) + zpH;
+        const int32_t sum = (c.z - g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]) * (hOld - zpH) + (g.quant_one - c.z) * (nAligned - zpH);
+        c.h = clampCode(rescaleWide(sum, g.update_old_to_h) + zpH, g.qlo[RXMET_GRU_H], g.qhi[RXMET_GRU_H], m.h);
     }
     return c;
 }

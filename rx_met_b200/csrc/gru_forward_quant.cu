@@ -143,11 +143,21 @@ __device__ __forceinline__ int32_t linearEpilogue(int64_t acc, int64_t comp, int
 
 constexpr int kLinearRows = 8;
 
+// When `pre.enabled`, the stored value is not the ih code itself but its contribution to the gate
+// input, rescale(code - zp) with the rescale of the gate the column belongs to: that term does not
+// depend on the recurrent state, so it is computed here once instead of in every step.
+struct PreRescale {
+    int enabled;
+    int hidden;
+    Rescale toGate[3];
+};
+
 template <class WT, class AT, class LT>
 __global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, int rows, int kWords, int channels,
                             const typename Dot<WT, AT>::WWord *__restrict__ w, const int64_t *__restrict__ comp,
                             const int64_t *__restrict__ biasAcc, const Rescale *__restrict__ rescale, int32_t zpOut,
-                            int32_t lo, int32_t hi, LT *__restrict__ out, uint8_t *__restrict__ mask) {
+                            int32_t lo, int32_t hi, LT *__restrict__ out, uint8_t *__restrict__ mask,
+                            const PreRescale pre) {
     using D = Dot<WT, AT>;
     extern __shared__ __align__(16) unsigned char smemRaw[];
     auto *xs = reinterpret_cast<typename D::AWord *>(smemRaw);  // [kLinearRows][kWords]
@@ -173,8 +183,9 @@ __global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, i
         for (int r = 0; r < kLinearRows; ++r) {
             if (r < nRows) {
                 uint8_t keep;
-                const int32_t q = linearEpilogue(acc[r], cmp, bias, rs, zpOut, lo, hi, keep);
+                int32_t q = linearEpilogue(acc[r], cmp, bias, rs, zpOut, lo, hi, keep);
                 const size_t o = static_cast<size_t>(row0 + r) * channels + c;
+                if (pre.enabled) q = rescaleWide(q - zpOut, pre.toGate[c / pre.hidden]);
                 out[o] = static_cast<LT>(q);
                 if (mask) mask[o] = keep;
             }
@@ -330,7 +341,9 @@ recurrentForward(const __grid_constant__ RecurrentArgs a, const __grid_constant_
 // so a step's GEMM touches shared memory only for the broadcast reads of h (128-bit loads).  The
 // ih codes of step t+1 are fetched while step t computes, which takes the L2/HBM latency off the
 // serial chain.  Requires 3H <= blockDim and H <= 4*KW.
-template <int KW, int BT, bool Narrow>
+// Mode 0: 64-bit gate arithmetic; 1: 32-bit where provably exact; 2: additionally direct
+// activation tables in shared memory and ih contributions pre-rescaled by the input projection.
+template <int KW, int BT, int Mode>
 __global__ void __launch_bounds__(KW * 12)
 recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec gateParam) {
     const int H = a.H, C = 3 * a.H;
@@ -339,11 +352,33 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
     __shared__ __align__(16) int8_t hS[BT * kPadded];
     extern __shared__ __align__(16) unsigned char smemRaw[];
     int32_t *hhS = reinterpret_cast<int32_t *>(smemRaw);  // [BT][C]
+    int32_t *tabS = hhS + BT * C;                          // Mode 2: three direct tables
 
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
     for (int i = tid; i < static_cast<int>(sizeof(GateExec) / 4); i += nthreads)
         reinterpret_cast<int32_t *>(&g)[i] = reinterpret_cast<const int32_t *>(&gateParam)[i];
+    DirectTables tab{};
+    if constexpr (Mode == 2) {
+        const int inOp[3] = {RXMET_GRU_UPDATE_GATE_INPUT, RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT};
+        const int outOp[3] = {RXMET_GRU_UPDATE_GATE_OUTPUT, RXMET_GRU_RESET_GATE_OUTPUT, RXMET_GRU_NEW_GATE_OUTPUT};
+        const Lut *luts[3] = {&gateParam.lut_update, &gateParam.lut_reset, &gateParam.lut_new};
+        int32_t *base = tabS;
+        const int32_t *ptrs[3];
+#pragma unroll
+        for (int l = 0; l < 3; ++l) {
+            const int32_t lo = gateParam.qlo[inOp[l]], span = gateParam.qhi[inOp[l]] - lo + 1;
+            for (int i = tid; i < span; i += nthreads) {
+                uint8_t keep;
+                const int32_t code = clampCode(lutEval<true>(lo + i, *luts[l]), gateParam.qlo[outOp[l]],
+                                               gateParam.qhi[outOp[l]], keep);
+                base[i] = code * 2 + keep;
+            }
+            ptrs[l] = base;
+            base += span;
+        }
+        tab.update = ptrs[0]; tab.reset = ptrs[1]; tab.fresh = ptrs[2];
+    }
 
     // this thread's column of R, zero point compensation and bias term
     const bool hasColumn = tid < C;
@@ -437,8 +472,11 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
                 GateMasks m;
                 const int32_t hOld = hS[b * kPadded + j];
                 const int32_t hhn = hhRow[2 * H + j];
-                const GateCodes q = gruCell<Narrow>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j],
-                                                    hhn, hOld, g, m);
+                GateCodes q;
+                if constexpr (Mode == 2)
+                    q = gruCellFast(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, g, tab, m);
+                else
+                    q = gruCell<Mode == 1>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, g, m);
                 hS[b * kPadded + j] = static_cast<int8_t>(q.h);
                 const size_t ho = (row + a.B) * H + j;
                 a.h[ho] = static_cast<float>(q.h - zpH) * scaleH;
@@ -538,6 +576,26 @@ bool narrowGateMath(const GateExec &g) {
     return true;
 }
 
+// Mode 2 of the 8-bit recurrence: small grids everywhere, so that the direct tables stay small, the
+// pre-rescaled ih terms fit 16 bits and all 32-bit products are exact.
+bool fastGateMath(const GateExec &g) {
+    if (!narrowGateMath(g)) return false;
+    const int ops[] = {RXMET_GRU_WEIGHT_IH_LINEAR, RXMET_GRU_WEIGHT_HH_LINEAR, RXMET_GRU_UPDATE_GATE_INPUT,
+                       RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT, RXMET_GRU_UPDATE_GATE_OUTPUT,
+                       RXMET_GRU_RESET_GATE_OUTPUT, RXMET_GRU_NEW_GATE_OUTPUT, RXMET_GRU_H};
+    for (int op : ops) {
+        const int64_t span = static_cast<int64_t>(g.qhi[op]) - g.qlo[op];
+        if (span >= (1 << 10) || g.zp[op] < g.qlo[op] || g.zp[op] > g.qhi[op]) return false;
+    }
+    if (g.quant_one <= -(1 << 15) || g.quant_one >= (1 << 15)) return false;
+    const int64_t spanIh = static_cast<int64_t>(g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR]) - g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR];
+    for (const Rescale &r : {g.ih_to_update, g.ih_to_reset, g.ih_to_new})
+        if (r.shift < 0 || ((spanIh * r.mult) >> r.shift) > 30000) return false;
+    for (const Rescale &r : {g.rh_to_new, g.update_old_to_h})
+        if (r.mult < 0 || r.mult >= (1 << 16) || r.shift < 0) return false;
+    return true;
+}
+
 template <class WT, class AT, class LT>
 void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaStream_t st) {
     using D = Dot<WT, AT>;
@@ -614,6 +672,28 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     }
     afterLaunch("channelPrep");
 
+    // Which recurrence runs decides what the input projection stores.
+    int device = 0, smemMax = 0, sms = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    constexpr bool kI8 = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value &&
+                         std::is_same<LT, int16_t>::value;
+    const int blockI8 = padTo(C, 32);
+    int btI8 = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+    if (const char *env = std::getenv("RXMET_GRU_FWD_BT")) btI8 = std::atoi(env);
+    const bool registerPath = kI8 && blockI8 <= 768 && hWords <= 64 && btI8 * H <= 2 * blockI8 &&
+                              (btI8 == 1 || btI8 == 2 || btI8 == 4) && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr;
+    int mode = 0;
+    if (registerPath) {
+        mode = fastGateMath(g) ? 2 : (narrowGateMath(g) ? 1 : 0);
+        if (const char *env = std::getenv("RXMET_GRU_FWD_MODE")) mode = std::min(mode, std::atoi(env));
+    }
+    PreRescale pre{};
+    pre.enabled = mode == 2 ? 1 : 0;
+    pre.hidden = H;
+    pre.toGate[0] = g.ih_to_update; pre.toGate[1] = g.ih_to_reset; pre.toGate[2] = g.ih_to_new;
+
     // 3. input projection, all steps
     {
         const int block = std::min(padTo(C, 32), 512);
@@ -624,7 +704,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
             inputLinear<WT, AT, LT><<<grid, block, smem, st>>>(
                 reinterpret_cast<const AWord *>(xCodes), static_cast<int>(rows), iWords, C, wCodes, compX, biasX, ch.gemmX,
                 g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR], g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR],
-                ihCodes, mk.weight_ih_linear);
+                ihCodes, mk.weight_ih_linear, pre);
         }
         afterLaunch("inputLinear");
     }
@@ -639,10 +719,6 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     if (mk.gate_input || mk.gate_output || mk.h)
         RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
 
-    int device = 0, smemMax = 0, sms = 0;
-    RXMET_CUDA(cudaGetDevice(&device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     // Batch tile: as small as keeps every SM busy; a larger tile only amortises weight reads.
     const int bt = (B >= 4 * 2 * sms) ? 4 : ((B >= 2 * 2 * sms) ? 2 : 1);
     const int block = std::min(padTo(C, 32), 768);
@@ -659,32 +735,30 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
         }
         afterLaunch("recurrentForward");
     };
-    if constexpr (std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value && std::is_same<LT, int16_t>::value) {
-        // register-resident variant: one thread per column, at most two gate elements per thread
-        const int blockI8 = padTo(C, 32);
-        int btI8 = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
-        if (const char *env = std::getenv("RXMET_GRU_FWD_BT")) btI8 = std::atoi(env);
-        const bool fits = blockI8 <= 768 && hWords <= 64 && btI8 * H <= 2 * blockI8;
-        if (fits && (btI8 == 1 || btI8 == 2 || btI8 == 4)) {
-            const bool narrow = narrowGateMath(g);
-            auto launchI8 = [&](auto kernel) {
-                const size_t smem = sizeof(int32_t) * btI8 * C;
-                kernel<<<(B + btI8 - 1) / btI8, blockI8, smem, st>>>(a, g);
-            };
-            KernelTimer timer__("recurrentForward", st);
-#define RXMET_I8_CASE(KW, BT)                                                              \
-    if (hWords <= KW && btI8 == BT) {                                                       \
-        if (narrow) launchI8(recurrentForwardI8<KW, BT, true>);                             \
-        else launchI8(recurrentForwardI8<KW, BT, false>);                                   \
-        goto launchedI8;                                                                    \
+    if constexpr (kI8) {
+        if (registerPath) {
+            // register-resident variant: one thread per column, at most two gate elements per thread
+            size_t smem = sizeof(int32_t) * btI8 * C;
+            if (mode == 2) {
+                for (int op : {RXMET_GRU_UPDATE_GATE_INPUT, RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT})
+                    smem += sizeof(int32_t) * (g.qhi[op] - g.qlo[op] + 1);
+            }
+            auto launchI8 = [&](auto kernel) { kernel<<<(B + btI8 - 1) / btI8, blockI8, smem, st>>>(a, g); };
+            {
+                KernelTimer timer__("recurrentForward", st);
+                bool done = false;
+#define RXMET_I8_CASE(KW, BT)                                                 \
+    if (!done && hWords <= KW && btI8 == BT) {                                 \
+        if (mode == 2) launchI8(recurrentForwardI8<KW, BT, 2>);                \
+        else if (mode == 1) launchI8(recurrentForwardI8<KW, BT, 1>);           \
+        else launchI8(recurrentForwardI8<KW, BT, 0>);                          \
+        done = true;                                                           \
     }
-            RXMET_I8_CASE(16, 1) RXMET_I8_CASE(16, 2) RXMET_I8_CASE(16, 4)
-            RXMET_I8_CASE(32, 1) RXMET_I8_CASE(32, 2) RXMET_I8_CASE(32, 4)
-            RXMET_I8_CASE(64, 1) RXMET_I8_CASE(64, 2) RXMET_I8_CASE(64, 4)
+                RXMET_I8_CASE(16, 1) RXMET_I8_CASE(16, 2) RXMET_I8_CASE(16, 4)
+                RXMET_I8_CASE(32, 1) RXMET_I8_CASE(32, 2) RXMET_I8_CASE(32, 4)
+                RXMET_I8_CASE(64, 1) RXMET_I8_CASE(64, 2) RXMET_I8_CASE(64, 4)
 #undef RXMET_I8_CASE
-        launchedI8:;
-        }
-        if (fits && (btI8 == 1 || btI8 == 2 || btI8 == 4)) {
+            }
             afterLaunch("recurrentForwardI8");
             return;
         }
