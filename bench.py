@@ -255,7 +255,7 @@ def run_ours(args):
     lib.rxmet_set_kernel_timing(1)
     k_steps = min(args.steps, 10)
     timed(resident, k_steps, 1)
-    names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "packRecurrentBf16", "weightGradMma", "reduceWeightGrad", "fillCodes",
+    names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "packRecurrentBf16", "weightGradMma", "reduceWeightGrad", "fillCodes", "packStepMasks",
              "reduceSplits", "columnSums", "channelPrep", "dequantCodes", "transposeMatrix"]
     per_kernel = {}
     for n in names:

@@ -28,6 +28,9 @@ namespace {
 
 __device__ __forceinline__ float keepOf(const uint8_t *m, size_t i) { return m ? static_cast<float>(m[i]) : 1.0f; }
 
+// Pulls the line holding *p into L2 without occupying a register or blocking the warp.
+__device__ __forceinline__ void prefetchL2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // out[i] = (codes[i] - zp) * scale, scale per column when channelScale is set
 // (gru_interface_binding.cc:842-856).
 __global__ void dequantCodes(const int32_t *__restrict__ q, size_t n, int cols, const float *__restrict__ channelScale,
@@ -137,6 +140,15 @@ __global__ void __launch_bounds__(768) recurrentBackward(const __grid_constant__
     }
 }
 
+// bf16 helpers: exact conversions of small integers, round-to-nearest splits of fp32 values
+__device__ __forceinline__ uint32_t packBf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16Lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16Hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
 // ---- quantized weights in registers -------------------------------------------
 //
 // For weight grids of at most 8 bits the codes are exact in bf16, so R[k][c] = code * scale[c]
@@ -158,6 +170,25 @@ __global__ void packRecurrentBf16(const int32_t *__restrict__ Rq, int H, int CW,
     }
 }
 
+// One 16-bit word per (t, b, j) with the 13 keep flags the pointwise derivative of hidden unit j
+// needs: bits 0..2 gate_output (z,r,n), 3..5 gate_input, 6..8 weight_hh_linear, 9..11
+// weight_ih_linear, 12 h.  Packing them once, outside the serial time loop, replaces 13 byte loads
+// per element and step on the critical path by one.
+__global__ void packStepMasks(const uint8_t *__restrict__ mIh, const uint8_t *__restrict__ mHh,
+                              const uint8_t *__restrict__ mGateIn, const uint8_t *__restrict__ mGateOut,
+                              const uint8_t *__restrict__ mH, size_t rows, int H, uint16_t *__restrict__ out) {
+    const size_t total = rows * H;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / H, j = i % H, gi = row * 3 * H + j;
+        auto bit = [](const uint8_t *m, size_t at, int pos) -> uint32_t { return (m ? (m[at] ? 1u : 0u) : 1u) << pos; };
+        out[i] = static_cast<uint16_t>(
+            bit(mGateOut, gi, 0) | bit(mGateOut, gi + H, 1) | bit(mGateOut, gi + 2 * H, 2) | bit(mGateIn, gi, 3) |
+            bit(mGateIn, gi + H, 4) | bit(mGateIn, gi + 2 * H, 5) | bit(mHh, gi, 6) | bit(mHh, gi + H, 7) |
+            bit(mHh, gi + 2 * H, 8) | bit(mIh, gi, 9) | bit(mIh, gi + H, 10) | bit(mIh, gi + 2 * H, 11) | bit(mH, i, 12));
+    }
+}
+
 struct BackwardQArgs {
     int T, B, H;
     const uint32_t *RB;      // packed codes, see packRecurrentBf16
@@ -165,6 +196,7 @@ struct BackwardQArgs {
     const float *h, *v, *dhNew;
     float *dp, *dq, *dh0;
     const uint8_t *mIh, *mHh, *mGateIn, *mGateOut, *mH, *mH0;
+    const uint16_t *stepBits;  // packed keep flags, see packStepMasks; null = nothing was clamped
 };
 
 struct StepOperands {
@@ -201,7 +233,6 @@ __global__ void __launch_bounds__(384) recurrentBackwardQ(const __grid_constant_
         const int j = e % H;
         scale[s2][0] = a.scaleR[j]; scale[s2][1] = a.scaleR[H + j]; scale[s2][2] = a.scaleR[2 * H + j];
     }
-    auto bit = [](const uint8_t *m, size_t i, int pos) -> uint32_t { return (m ? (m[i] ? 1u : 0u) : 1u) << pos; };
     auto fetch = [&](int t, StepOperands (&dst)[kSlots]) {
 #pragma unroll
         for (int s2 = 0; s2 < kSlots; ++s2) {
@@ -209,17 +240,13 @@ __global__ void __launch_bounds__(384) recurrentBackwardQ(const __grid_constant_
             if (e < elems) {
                 const int b = e / H, j = e % H;
                 const size_t row = static_cast<size_t>(t) * a.B + b0 + b;
-                const size_t hi = row * H + j, gi = row * C + j;
+                const size_t hi = row * H + j;
                 const float *vRow = a.v + row * 4 * H;
                 StepOperands o;
                 o.z = vRow[j]; o.r = vRow[H + j]; o.g = vRow[2 * H + j]; o.qg = vRow[3 * H + j];
                 o.hOld = a.h[hi];
                 o.dhNew = a.dhNew[hi + static_cast<size_t>(a.B) * H];
-                o.keepBits = bit(a.mGateOut, gi, 0) | bit(a.mGateOut, gi + H, 1) | bit(a.mGateOut, gi + 2 * H, 2) |
-                             bit(a.mGateIn, gi, 3) | bit(a.mGateIn, gi + H, 4) | bit(a.mGateIn, gi + 2 * H, 5) |
-                             bit(a.mHh, gi, 6) | bit(a.mHh, gi + H, 7) | bit(a.mHh, gi + 2 * H, 8) |
-                             bit(a.mIh, gi, 9) | bit(a.mIh, gi + H, 10) | bit(a.mIh, gi + 2 * H, 11) |
-                             bit(a.mH, hi, 12);
+                o.keepBits = a.stepBits ? a.stepBits[hi] : 0x1fffu;
                 dst[s2] = o;
             }
         }
@@ -299,6 +326,185 @@ __global__ void __launch_bounds__(384) recurrentBackwardQ(const __grid_constant_
     }
 }
 
+// ---- dh += R dq on tensor cores -------------------------------------------------
+//
+// Same data flow as recurrentBackwardQ, but the per-step product runs as mma.sync m16n8k16:
+// M = hidden rows k, N = batch tile (padded to 8), K = the 3H columns.  Warp w owns two m16 tiles
+// (rows 32*(w/3) .. +31) and the K range of gate w%3; its A fragments (exact bf16 weight codes)
+// stay in registers for the whole sequence.  dq, scaled per column, is split into three bf16
+// terms in shared memory so that the products are exact and only the fp32 accumulation rounds.
+template <int HT, int BT>  // H = 32*HT, blockDim = 96*HT
+__global__ void __launch_bounds__(96 * HT) recurrentBackwardMma(const __grid_constant__ BackwardQArgs a,
+                                                                const int32_t *__restrict__ Rq) {
+    constexpr int H = 32 * HT, C = 3 * H, KS = 2 * HT;  // k16 steps per warp
+    constexpr int CP = C + 8;                           // padded row of the bf16 dq tiles
+    __shared__ __align__(16) uint16_t dqB[3][8][CP];    // [split][batch row][column]
+    __shared__ float partS[3][BT][H];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int grp = warp % 3, mpair = warp / 3;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+
+    // A fragments: rows mpair*32 + {0,16} + g (+8), columns grp*H + ks*16 + 2*t4 (+8)
+    uint32_t afrag[2][KS][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int row = mpair * 32 + mt * 16 + g + (q & 1) * 8;
+                const int col = grp * H + ks * 16 + 2 * t4 + (q >> 1) * 8;
+                const int2 w = *reinterpret_cast<const int2 *>(Rq + static_cast<size_t>(row) * C + col);
+                afrag[mt][ks][q] = (__float_as_uint(static_cast<float>(w.x)) >> 16) |
+                                   (__float_as_uint(static_cast<float>(w.y)) & 0xffff0000u);
+            }
+    for (int i = tid; i < 3 * 8 * CP; i += nthreads) (&dqB[0][0][0])[i] = 0;
+    for (int i = tid; i < 3 * BT * H; i += nthreads) (&partS[0][0][0])[i] = 0.0f;
+
+    constexpr int kSlots = (BT + 2) / 3;
+    const int elems = nb * H;
+    float dhBase[kSlots];
+    float scale[kSlots][3];
+    StepOperands cur[kSlots], nxt[kSlots];
+#pragma unroll
+    for (int s2 = 0; s2 < kSlots; ++s2) {
+        dhBase[s2] = 0.0f;
+        const int j = (tid + s2 * nthreads) % H;
+        scale[s2][0] = a.scaleR[j]; scale[s2][1] = a.scaleR[H + j]; scale[s2][2] = a.scaleR[2 * H + j];
+    }
+    auto fetch = [&](int t, StepOperands (&dst)[kSlots]) {
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t row = static_cast<size_t>(t) * a.B + b0 + b;
+                const size_t hi = row * H + j;
+                const float *vRow = a.v + row * 4 * H;
+                StepOperands o;
+                o.z = vRow[j]; o.r = vRow[H + j]; o.g = vRow[2 * H + j]; o.qg = vRow[3 * H + j];
+                o.hOld = a.h[hi];
+                o.dhNew = a.dhNew[hi + static_cast<size_t>(a.B) * H];
+                o.keepBits = a.stepBits ? a.stepBits[hi] : 0x1fffu;
+                dst[s2] = o;
+            }
+        }
+    };
+    // Operands of a step several iterations ahead are pulled into L2, so that the register
+    // prefetch of the next step is an L2 hit instead of an HBM round trip on the serial chain.
+    constexpr int kAhead = 4;
+    auto warmL2 = [&](int t) {
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t row = static_cast<size_t>(t) * a.B + b0 + b;
+                const size_t hi = row * H + j;
+                const float *vRow = a.v + row * 4 * H;
+                prefetchL2(vRow + j); prefetchL2(vRow + H + j); prefetchL2(vRow + 2 * H + j); prefetchL2(vRow + 3 * H + j);
+                prefetchL2(a.h + hi);
+                prefetchL2(a.dhNew + hi + static_cast<size_t>(a.B) * H);
+                if (a.stepBits) prefetchL2(a.stepBits + hi);
+            }
+        }
+    };
+    auto splitStore = [&](int b, int c, float v) {
+        const float hi = bf16Lo(packBf16(v, 0.0f));
+        const float r1 = v - hi;
+        const float mid = bf16Lo(packBf16(r1, 0.0f));
+        const float lo = r1 - mid;
+        dqB[0][b][c] = static_cast<uint16_t>(__float_as_uint(hi) >> 16);
+        dqB[1][b][c] = static_cast<uint16_t>(__float_as_uint(mid) >> 16);
+        dqB[2][b][c] = static_cast<uint16_t>(packBf16(lo, 0.0f) & 0xffffu);
+    };
+    for (int t = a.T - 2; t >= 0 && t >= a.T - 1 - kAhead; --t) warmL2(t);
+    fetch(a.T - 1, cur);
+    __syncthreads();
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        if (t > 0) fetch(t - 1, nxt);
+        if (t - 1 - kAhead >= 0) warmL2(t - 1 - kAhead);
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            const int e = tid + s2 * nthreads;
+            if (e < elems) {
+                const int b = e / H, j = e % H;
+                const size_t gi = (rowBase + b) * C + j;
+                const StepOperands o = cur[s2];
+                auto keep = [&](int pos) { return static_cast<float>((o.keepBits >> pos) & 1u); };
+                const float carried = dhBase[s2] + partS[0][b][j] + partS[1][b][j] + partS[2][b][j];
+                const float dhTotal = (o.dhNew + carried) * keep(12);
+                dhBase[s2] = o.z * dhTotal;
+                const float dg = (1.0f - o.z) * dhTotal;
+                const float dz = (o.hOld - o.g) * dhTotal;
+                const float dpG = (1.0f - o.g * o.g) * dg * keep(2) * keep(5);
+                const float dqG = dpG * o.r;
+                const float dr = dpG * o.qg;
+                const float dpR = (o.r * (1.0f - o.r)) * dr;
+                const float dpZ = (o.z * (1.0f - o.z)) * dz;
+                const float kz = keep(0) * keep(3), kr = keep(1) * keep(4);
+                const float pz = dpZ * kz * keep(9), pr = dpR * kr * keep(10), pg = dpG * keep(11);
+                const float qz = dpZ * kz * keep(6), qr = dpR * kr * keep(7), qn = dqG * keep(8);
+                a.dp[gi] = pz; a.dp[gi + H] = pr; a.dp[gi + 2 * H] = pg;
+                a.dq[gi] = qz; a.dq[gi + H] = qr; a.dq[gi + 2 * H] = qn;
+                splitStore(b, j, qz * scale[s2][0]);
+                splitStore(b, H + j, qr * scale[s2][1]);
+                splitStore(b, 2 * H + j, qn * scale[s2][2]);
+            }
+        }
+        __syncthreads();
+        {
+            float acc[2][3][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) acc[mt][sp][0] = acc[mt][sp][1] = acc[mt][sp][2] = acc[mt][sp][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int c0 = grp * H + ks * 16 + 2 * t4;
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) {
+                    const uint32_t bf0 = *reinterpret_cast<const uint32_t *>(&dqB[sp][g][c0]);
+                    const uint32_t bf1 = *reinterpret_cast<const uint32_t *>(&dqB[sp][g][c0 + 8]);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        asm volatile(
+                            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                            "{%0,%1,%2,%3};"
+                            : "+f"(acc[mt][sp][0]), "+f"(acc[mt][sp][1]), "+f"(acc[mt][sp][2]), "+f"(acc[mt][sp][3])
+                            : "r"(afrag[mt][ks][0]), "r"(afrag[mt][ks][1]), "r"(afrag[mt][ks][2]), "r"(afrag[mt][ks][3]),
+                              "r"(bf0), "r"(bf1));
+                    }
+                }
+            }
+            // D fragment: (row g, cols 2*t4, 2*t4+1) and (row g+8, same cols); columns are batch rows
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int n = 2 * t4 + (q & 1);
+                    const int k = mpair * 32 + mt * 16 + g + (q >> 1) * 8;
+                    if (n < BT) partS[grp][n][k] = (acc[mt][2][q] + acc[mt][1][q]) + acc[mt][0][q];
+                }
+        }
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) cur[s2] = nxt[s2];
+        __syncthreads();
+    }
+#pragma unroll
+    for (int s2 = 0; s2 < kSlots; ++s2) {
+        const int e = tid + s2 * nthreads;
+        if (e < elems) {
+            const int b = e / H, j = e % H;
+            const size_t o = static_cast<size_t>(b0 + b) * H + j;
+            a.dh0[o] = (dhBase[s2] + partS[0][b][j] + partS[1][b][j] + partS[2][b][j]) * keepOf(a.mH0, o);
+        }
+    }
+}
+
 __global__ void transposeMatrix(const float *__restrict__ in, int rows, int cols, float *__restrict__ out) {
     __shared__ float tile[32][33];
     const int x = blockIdx.x * 32 + threadIdx.x, y0 = blockIdx.y * 32;
@@ -374,13 +580,6 @@ struct WeightGradProblem {
     float *partial;         // [splits][M+1][N]
 };
 
-__device__ __forceinline__ uint32_t packBf16(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-__device__ __forceinline__ float bf16Lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf16Hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 // Loads of the next K chunk are issued into registers before the tensor work of the current
 // chunk, so the HBM latency overlaps the MMAs; one shared-memory buffer, two barriers per chunk.
@@ -618,6 +817,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(rows * C);          // dq
     ws.take<float>(C * H);             // R transposed
     ws.take<uint32_t>(3 * 64 * static_cast<size_t>(H));  // packed recurrent codes
+    ws.take<uint16_t>(rows * H);                         // packed per-step keep flags
     ws.take<float>(static_cast<size_t>(I) * C);  // W real-valued
     ws.take<float>(static_cast<size_t>(H) * C);  // R real-valued
     ws.take<float>(rows * I);          // x real-valued
@@ -694,13 +894,33 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         }
         afterLaunch("packRecurrentBf16");
         BackwardQArgs q{};
+        if (mk.weight_ih_linear || mk.weight_hh_linear || mk.gate_input || mk.gate_output || mk.h) {
+            uint16_t *bits = ws.take<uint16_t>(rows * H);
+            {
+                KernelTimer timer__("packStepMasks", st);
+                packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear,
+                                                                      mk.gate_input, mk.gate_output, mk.h, rows, H, bits);
+            }
+            afterLaunch("packStepMasks");
+            q.stepBits = bits;
+        }
         q.T = T; q.B = B; q.H = H; q.RB = RB; q.scaleR = chanScaleR;
         q.h = call.h; q.v = call.v; q.dhNew = call.dh_new; q.dp = dp; q.dq = dq; q.dh0 = call.dh0;
         q.mIh = mk.weight_ih_linear; q.mHh = mk.weight_hh_linear; q.mGateIn = mk.gate_input;
         q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
         const size_t smem = sizeof(float) * (static_cast<size_t>(bt) * 3 * 2 * CW + 3 * static_cast<size_t>(bt) * H);
         const int grid = (B + bt - 1) / bt;
-        {
+        const bool mmaPath = H % 32 == 0 && std::getenv("RXMET_GRU_BWD_SIMT") == nullptr;
+        if (mmaPath) {
+            KernelTimer timer__("recurrentBackward", st);
+#define RXMET_BWD_CASE(HTV, BTV) \
+    if (H == 32 * HTV && bt == BTV) recurrentBackwardMma<HTV, BTV><<<grid, 96 * HTV, 0, st>>>(q, call.R_q);
+            RXMET_BWD_CASE(1, 1) RXMET_BWD_CASE(1, 2) RXMET_BWD_CASE(1, 4)
+            RXMET_BWD_CASE(2, 1) RXMET_BWD_CASE(2, 2) RXMET_BWD_CASE(2, 4)
+            RXMET_BWD_CASE(3, 1) RXMET_BWD_CASE(3, 2) RXMET_BWD_CASE(3, 4)
+            RXMET_BWD_CASE(4, 1) RXMET_BWD_CASE(4, 2) RXMET_BWD_CASE(4, 4)
+#undef RXMET_BWD_CASE
+        } else {
             KernelTimer timer__("recurrentBackward", st);
 #define RXMET_BWD_CASE(CWV, BTV) \
     if (CW == CWV && bt == BTV) recurrentBackwardQ<CWV, BTV><<<grid, 3 * H, smem, st>>>(q);
