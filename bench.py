@@ -44,6 +44,11 @@ def _algo_bytes_per_st(I, H):
     return 4 * I + 4 * H + S
 
 
+# DRAM traffic per launch of the recurrent kernels at this workload, from the ncu captures
+# summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, one launch).
+NCU_TRAFFIC_BYTES = {"recurrentForward": 19.80e6 + 42.90e6, "recurrentBackward": 85.42e6 + 40.81e6}
+
+
 def _peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -70,7 +75,7 @@ class ClockSampler:
         os.close(fd)
         self.proc = subprocess.Popen(
             ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-             "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+             "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
     def stop(self):
         if self.proc is None:
@@ -270,7 +275,7 @@ def run_ours(args):
     algo = _algo_bytes_per_st(I, H) * T * B
     achieved = algo / (top_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES.get(top),
                 "kernel_ms": top_ms, "algorithmic_bytes": algo,
                 "kernel_ms_per_step": {n: v[0] / k_steps for n, v in per_kernel.items()}}
 
