@@ -309,6 +309,38 @@ RXMET_API int rxmet_gru_backward_fp(int T, int B, int I, int H,
                                     void *workspace_dev, size_t workspace_bytes,
                                     void *stream);
 
+/* ------------------------------------------------------------------------ */
+/* Allocation-free variant                                                    */
+/* ------------------------------------------------------------------------ */
+
+/* Size of the scratch array built into the library image (bytes). */
+#define RXMET_STATIC_SCRATCH_BYTES (8u << 20)
+RXMET_API size_t rxmet_static_scratch_bytes(void);
+
+/* Float GRU forward that needs no workspace and allocates nothing, neither on
+ * the device nor on the host: same arguments and results as
+ * rxmet_gru_forward_fp minus the workspace pair.  It has no counterpart in the
+ * reference (whose wrappers allocate their outputs and temporaries on every
+ * call); it exists for callers that must not allocate while they run, such as
+ * a runtime plugin's enqueue callback, a fixed-deadline audio or control loop,
+ * or a process whose memory pool is frozen after start-up.
+ *   - The scratch (W x + bw for all T*B rows) lives in a fixed 8 MiB array
+ *     inside the library image; every GPU that loads the library holds it
+ *     until the process exits.  Calls with T*B*3H*4 > 8 MiB are rejected with
+ *     RXMET_ERR_WORKSPACE and leave the outputs untouched.
+ *   - The first call on each device looks up the device address of that array
+ *     (a host-side query, no allocation).  Make that first call during
+ *     start-up, outside any stream capture; later calls only launch kernels.
+ *   - All calls on one device share the array.  Nothing in it has to be
+ *     cleared between calls, but two calls whose kernels can overlap on the
+ *     GPU (different streams, or threads racing on one stream) would overwrite
+ *     each other's projection: serialise them. */
+RXMET_API int rxmet_gru_forward_fp_static(int T, int B, int I, int H,
+                                          const float *W_dev, const float *R_dev,
+                                          const float *bw_dev, const float *br_dev,
+                                          const float *x_dev, const float *h0_dev,
+                                          float *h_dev, float *v_dev, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
