@@ -314,7 +314,9 @@ def run_ours(args):
 
     if rank == 0:
         cpu = None
+        secondary = None
         if world == 1:
+            secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak)}
             v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
             cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
         line = {
@@ -329,11 +331,48 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
                     "final_loss": losses[-1] if losses else None},
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "clocks": clocks, "secondary": secondary,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def aimet_kernel_bandwidth(lib, torch, device, peak_gbs):
+    """HBM-bound AIMET native kernels on a 1 GiB float32 tensor (larger than L2): GB/s of
+    algorithmic traffic (QDQ 8 B/element, min/max and histogram 4 B/element) from CUDA events."""
+    n = 1 << 28
+    x = torch.randn(n, device=device)
+    y = torch.empty_like(x)
+    lib.rxmet_aimet_minmax_workspace_bytes.restype = C.c_size_t
+    ws = torch.empty(lib.rxmet_aimet_minmax_workspace_bytes(), dtype=torch.uint8, device=device)
+    mm = torch.empty(2, device=device)
+    hist = torch.empty(lib.rxmet_aimet_pdf_size(), dtype=torch.int32, device=device)
+    st = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    calls = {
+        "qdq": (8, lambda: lib.rxmet_aimet_qdq(p(x), C.c_uint64(n), 0, C.c_double(-4.0), C.c_double(3.96875),
+                                                C.c_double(0.03125), 0, C.c_uint64(0), p(y), st)),
+        "minmax": (4, lambda: lib.rxmet_aimet_minmax(p(x), C.c_uint64(n), C.c_uint64(n), 0, p(mm), p(mm[1:]), p(ws),
+                                                      C.c_size_t(ws.numel()), st)),
+        "histogram": (4, lambda: lib.rxmet_aimet_histogram(p(x), C.c_uint64(n), 0, C.c_double(0.01), -768, p(hist), st)),
+    }
+    out = {}
+    for name, (bytes_per, fn) in calls.items():
+        for _ in range(3):
+            assert fn() == 0, lib.rxmet_last_error()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        gbs = bytes_per * n * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
+        out[name] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peak_gbs, "bytes_per_element": bytes_per}
+    out["elements"] = n
+    return out
 
 
 def main():

@@ -310,6 +310,72 @@ RXMET_API int rxmet_gru_backward_fp(int T, int B, int I, int H,
                                     void *stream);
 
 /* ------------------------------------------------------------------------ */
+/* AIMET native kernels: quantize-dequantize, min/max, PDF histogram          */
+/* ------------------------------------------------------------------------ */
+
+/* dtype: 0 = float32, 1 = float64.  Tensors are dense device arrays.  The
+ * arithmetic is the reference's CPU definition, which its tests hold equal to
+ * torch fake-quantize bit for bit (tests/integration/
+ * test_native_qdq_alignment.py:78-131): clamp in the real domain, multiply by
+ * the ROUNDED reciprocal of delta, round half to even, multiply by delta; NaN
+ * passes through, infinities saturate. */
+
+/* out = QDQ(in) with one encoding.  Replaces quantizeDequantizeGpu
+ * (native/common/src/trim_functions.cu:47-58,118-127; value function
+ * native/common/src/quantize_dequantize.hpp:36-46).  stochastic != 0 rounds
+ * floor(x + u), u uniform in [0,1) from a counter-based generator keyed by
+ * seed (statistically, not bitwise, comparable with the reference's curand). */
+RXMET_API int rxmet_aimet_qdq(const void *in_dev, uint64_t count, int dtype, double enc_min,
+                              double enc_max, double delta, int stochastic, uint64_t seed,
+                              void *out_dev, void *stream);
+
+/* Per-channel QDQ, channel = (i / elements_per_channel) % num_channels; the
+ * encoding arrays are device arrays of the tensor's dtype.  Replaces
+ * quantizeDequantizePerChannelGpu (trim_functions.cu:75-86). */
+RXMET_API int rxmet_aimet_qdq_per_channel(const void *in_dev, int num_channels, int64_t num_elements,
+                                          int64_t elements_per_channel, int dtype,
+                                          const void *min_dev, const void *max_dev,
+                                          const void *delta_dev, void *out_dev, void *stream);
+
+/* Broadcast QDQ: strides (host arrays, num_dims <= 8) of the broadcast-aligned
+ * tensor and encoding shapes, encoding stride 0 along broadcast dimensions.
+ * Replaces quantizeDequantizeBroadcastGpu (trim_functions.cu:90-116). */
+RXMET_API int rxmet_aimet_qdq_broadcast(const void *in_dev, void *out_dev, int64_t num_elements,
+                                        int num_dims, const int64_t *input_strides,
+                                        const int64_t *encoding_strides, int dtype,
+                                        const void *min_dev, const void *max_dev,
+                                        const void *delta_dev, void *stream);
+
+/* Quantize to the integer index grid (values stay in the tensor's dtype):
+ * round_half_away(clamp(x)/delta - offset) - (shift_to_signed ? 2^(bw-1) : 0).
+ * Replaces quantizeToFxpGpu (trim_functions.cu:60-73, trim_functions.cuh:
+ * 122-149); division is IEEE here, as on the reference's CPU path. */
+RXMET_API int rxmet_aimet_quantize_to_fxp(const void *in_dev, uint64_t count, int dtype,
+                                          double enc_min, double enc_max, double delta,
+                                          double offset, int bitwidth, int shift_to_signed,
+                                          void *out_dev, void *stream);
+
+/* Min and max of each consecutive block of block_size elements (count /
+ * block_size results, device arrays of the tensor's dtype); block_size ==
+ * count gives the whole-tensor pair.  NaN never wins, infinities do.
+ * Replaces GetMinMax_gpu (native/common/src/math_functions.cu:81-169).  The
+ * whole-tensor form needs rxmet_aimet_minmax_workspace_bytes() of scratch. */
+RXMET_API size_t rxmet_aimet_minmax_workspace_bytes(void);
+RXMET_API int rxmet_aimet_minmax(const void *data_dev, uint64_t count, uint64_t block_size, int dtype,
+                                 void *min_out_dev, void *max_out_dev, void *workspace_dev,
+                                 size_t workspace_bytes, void *stream);
+
+/* PDF histogram with rxmet_aimet_pdf_size() (= 1536) buckets: bucket of x is
+ * floor(x * (1/bucket_size)) - pdf_offset, values outside are dropped;
+ * histogram_dev (uint32) is overwritten.  Replaces GetHistogram_gpu
+ * (math_functions.cu:232-268) with the bucket rule of the reference's CPU
+ * path (native/common/src/math_functions.cpp:395-412), which is what its
+ * encoding analyzers are specified against. */
+RXMET_API int rxmet_aimet_pdf_size(void);
+RXMET_API int rxmet_aimet_histogram(const void *data_dev, uint64_t count, int dtype, double bucket_size,
+                                    int pdf_offset, uint32_t *histogram_dev, void *stream);
+
+/* ------------------------------------------------------------------------ */
 /* Allocation-free variant                                                    */
 /* ------------------------------------------------------------------------ */
 

@@ -1,0 +1,145 @@
+"""CPU tests of the AIMET native restatement: against the reference's own CPU sources (where the
+compiled checker is present) and against the known-answer cases of the reference's
+tests/integration/test_native_qdq_alignment.py."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+ROOT = Path(__file__).resolve().parent.parent
+AIMET_REF = ROOT / "oracle" / "_ref" / "libaimet_ref.so"
+
+
+def fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def ref():
+    return C.CDLL(str(AIMET_REF)) if AIMET_REF.exists() else None
+
+
+def grid(bits, scale, offset=None):
+    """Encoding of a `bits`-wide grid: symmetric signed when offset is None."""
+    steps = 2 ** bits - 1
+    if offset is None:
+        offset = -(2 ** (bits - 1))
+    return dict(min=scale * offset, max=scale * (offset + steps), delta=scale, offset=offset, bw=bits)
+
+
+def orc_qdq(x, enc):
+    out = np.empty_like(x)
+    ol.oracle().orc_aimet_qdq_f32(fp(x), C.c_uint64(x.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                                  C.c_double(enc["delta"]), fp(out))
+    return out
+
+
+def expected_qdq(x, enc):
+    """The contract of the reference's alignment test: clamp, multiply by the float32-rounded
+    reciprocal, round half to even, multiply back; all in float32."""
+    lo, hi, d = np.float32(enc["min"]), np.float32(enc["max"]), np.float32(enc["delta"])
+    inv = np.float32(1.0) / d
+    y = np.rint(np.clip(x, lo, hi) * inv).astype(np.float32) * d
+    return np.where(np.isnan(x), x, y).astype(np.float32)
+
+
+def test_ties_to_even_reciprocal_nan_and_infinity():
+    codes = np.array([-7.5, -3.5, -2.5, -1.5, -.5, .5, 1.5, 2.5, 3.5, 7.5], np.float32)
+    for bits, scale in ((8, 2.0 ** -7), (16, 2.0 ** -15), (32, 2.0 ** -21)):
+        for offset in (None, -13):
+            enc = grid(bits, scale, offset)
+            x = (codes * np.float32(scale)).astype(np.float32)
+            got = orc_qdq(x, enc)
+            assert np.array_equal(got, expected_qdq(x, enc))
+            if offset is None:  # half codes land on the even neighbour
+                assert np.array_equal(got / np.float32(scale), np.array([-8, -4, -2, -2, -0., 0, 2, 2, 4, 8], np.float32))
+    codes = np.arange(-63, 64, dtype=np.float32) + .5
+    for scale in (1. / 32767, .013007, .027019):
+        x = codes * np.float32(scale)
+        enc = grid(16, scale)
+        assert np.array_equal(orc_qdq(x, enc), expected_qdq(x, enc))
+    for bits, scale in ((8, 2.0 ** -7), (16, 2.0 ** -15), (32, 2.0 ** -21)):
+        enc = grid(bits, scale)
+        x = np.array([np.nan, -np.inf, -scale, 0, scale, np.inf], np.float32)
+        got = orc_qdq(x, enc)
+        want = np.array([np.nan, enc["min"], -scale, 0, scale, enc["max"]], np.float32)
+        assert np.array_equal(got, want, equal_nan=True)
+    small = np.array([-257, -65, -7, -3, -1, 0, 1, 3, 7, 65, 257], np.float32) * np.float32(2.0 ** -21)
+    assert np.array_equal(orc_qdq(small, grid(32, 2.0 ** -21)), small)
+
+
+@pytest.mark.skipif(ref() is None, reason="compiled reference not present on this machine")
+def test_restatement_matches_compiled_reference():
+    r, o = ref(), ol.oracle()
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(20011) * 3).astype(np.float32)
+    x[::97] = np.nan
+    x[5::211] = np.inf
+    x[7::311] = -np.inf
+    for bits, scale, offset in ((8, 0.0231, None), (8, 0.017, -31), (16, 1.0 / 32767, None), (4, 0.3, -3)):
+        enc = grid(bits, scale, offset)
+        a, b = np.empty_like(x), np.empty_like(x)
+        assert r.ref_aimet_qdq_f32(fp(x), C.c_uint64(x.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                                   C.c_double(enc["delta"]), fp(a)) == 0
+        o.orc_aimet_qdq_f32(fp(x), C.c_uint64(x.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                            C.c_double(enc["delta"]), fp(b))
+        assert np.array_equal(a, b, equal_nan=True)
+        finite = np.nan_to_num(x, nan=0.0, posinf=100.0, neginf=-100.0)
+        for signed in (0, 1):
+            assert r.ref_aimet_to_fxp_f32(fp(finite), C.c_uint64(x.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                                          C.c_double(enc["delta"]), C.c_double(enc["offset"]), bits, signed, fp(a)) == 0
+            o.orc_aimet_to_fxp_f32(fp(finite), C.c_uint64(x.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                                   C.c_double(enc["delta"]), C.c_double(enc["offset"]), bits, signed, fp(b))
+            assert np.array_equal(a, b)
+    # double precision
+    xd = x.astype(np.float64)
+    ad, bd = np.empty_like(xd), np.empty_like(xd)
+    enc = grid(16, 0.00731)
+    dp = lambda t: t.ctypes.data_as(C.POINTER(C.c_double))  # noqa: E731
+    assert r.ref_aimet_qdq_f64(dp(xd), C.c_uint64(xd.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                               C.c_double(enc["delta"]), dp(ad)) == 0
+    o.orc_aimet_qdq_f64(dp(xd), C.c_uint64(xd.size), C.c_double(enc["min"]), C.c_double(enc["max"]),
+                        C.c_double(enc["delta"]), dp(bd))
+    assert np.array_equal(ad, bd, equal_nan=True)
+    # per channel and broadcast
+    t = (rng.standard_normal((6, 5, 7)) * 2).astype(np.float32)
+    ch = 6
+    mn = np.linspace(-3, -1, ch).astype(np.float32)
+    dl = np.linspace(0.01, 0.03, ch).astype(np.float32)
+    mx = (mn + dl * 255).astype(np.float32)
+    off = np.zeros(ch, np.float32)
+    a, b = np.empty_like(t), np.empty_like(t)
+    assert r.ref_aimet_qdq_per_channel_f32(fp(t), ch, t.size, 35, fp(a), fp(mn), fp(mx), fp(dl), fp(off)) == 0
+    o.orc_aimet_qdq_per_channel_f32(fp(t), ch, C.c_int64(t.size), C.c_int64(35), fp(b), fp(mn), fp(mx), fp(dl))
+    assert np.array_equal(a, b)
+    shape = (C.c_int64 * 3)(6, 5, 7)
+    enc_shape = (C.c_int64 * 3)(6, 1, 1)
+    d3 = lambda v: (C.c_double * ch)(*[float(q) for q in v])  # noqa: E731
+    assert r.ref_aimet_qdq_broadcast_f32(fp(t), fp(a), ch, d3(mn), d3(mx), d3(dl), 3, shape, enc_shape) == 0
+    in_str = (C.c_int64 * 3)(35, 7, 1)
+    enc_str = (C.c_int64 * 3)(1, 0, 0)
+    o.orc_aimet_qdq_broadcast_f32(fp(t), fp(b), C.c_int64(t.size), 3, in_str, enc_str, fp(mn), fp(mx), fp(dl))
+    assert np.array_equal(a, b)
+    # min/max, whole tensor and per block; NaN never wins, infinities do
+    y = (rng.standard_normal(4096) * 5).astype(np.float32)
+    y[17] = np.nan
+    y[300] = np.inf
+    for block in (4096, 256, 7):
+        n = y.size // block
+        amin, amax, bmin, bmax = (np.empty(n, np.float32) for _ in range(4))
+        assert r.ref_aimet_minmax_f32(fp(y), C.c_uint64(y.size), C.c_uint64(block), fp(amin), fp(amax)) == 0
+        o.orc_aimet_minmax_f32(fp(y), C.c_uint64(y.size), C.c_uint64(block), fp(bmin), fp(bmax))
+        assert np.array_equal(amin, bmin) and np.array_equal(amax, bmax)
+    # histogram
+    pdf = r.ref_aimet_pdf_size()
+    assert pdf == 1536
+    z = (rng.standard_normal(50000) * 2).astype(np.float32)
+    z[11] = np.nan
+    for bucket, offset in ((0.01, -768), (0.0037, -100), (0.5, 0)):
+        ha, hb = np.zeros(pdf, np.uint32), np.zeros(pdf, np.uint32)
+        u32 = lambda t: t.ctypes.data_as(C.POINTER(C.c_uint32))  # noqa: E731
+        assert r.ref_aimet_histogram_f32(fp(z), C.c_uint64(z.size), u32(ha), C.c_double(bucket), offset, 1) == 0
+        o.orc_aimet_histogram_f32(fp(z), C.c_uint64(z.size), u32(hb), C.c_double(bucket), offset)
+        assert np.array_equal(ha, hb) and ha.sum() > 0
