@@ -1,0 +1,384 @@
+// LSTM backward through time on real values, with the optional clamp masks of the QAT path.
+//
+// Launch plan (the reference runs T x (pointwise kernel + cuBLAS GEMM) and three cuBLAS GEMMs,
+// operators/quant-lstm/src/lstm/backward_float_cuda.cu:50-104,189-330):
+//   dequantWeights x2  : QAT only - q-carrier weight codes x per-channel scale -> real weights
+//   recurrentBackward  : ONE launch for all T steps; a CTA owns BT batch rows, walks t = T-1..0,
+//                        keeps dc in registers and dh in shared memory, writes the masked gate
+//                        gradients of both linear branches, and propagates dh through weight_hh
+//                        (rows resident in shared memory as far as they fit, the rest from L2)
+//   gemmRowsTN + reduce: dW_ih = G_ih^T x, dW_hh = G_hh^T h_prev as split-K tile GEMMs over the T*B
+//                        rows with fixed-order reduction (bit-reproducible), masks applied there
+//   gemmNN             : dx = G_ih W_ih with the input clamp mask
+//   columnSums + reduce: bias gradients
+// Saved q-carrier tensors are dequantized while they are loaded: real = (value - zp) * scale.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.h"
+#include "lstm_kernels.h"
+
+namespace rxmet {
+namespace lstm {
+namespace {
+
+__device__ __forceinline__ float keepOf(const uint8_t *mask, size_t i) { return (mask == nullptr || mask[i] == 0) ? 1.0f : 0.0f; }
+__device__ __forceinline__ float realOf(float v, Dequant d) { return (v - d.zeroPoint) * d.scale; }
+
+__global__ void dequantWeights(const float *__restrict__ codes, const float *__restrict__ channelScale, int rows, int cols,
+                               float *__restrict__ out) {
+    const size_t n = static_cast<size_t>(rows) * cols;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[i] = codes[i] * channelScale[i / cols];
+}
+
+struct RecurrentArgs {
+    int T, B, H, smemRows;
+    const float *weightHh;  // real [4H][H]
+    const float *c0;
+    const float *gateOutputs, *cellStates, *cellTanh;
+    const float *gradOutput, *gradFinalHidden, *gradFinalCell;
+    Dequant dqC, dqGate[4], dqTanh;
+    rxmet_lstm_backward_masks mk;
+    float *gIh, *gHh;  // [T][B][4H]
+    float *dh0, *dc0;  // [B][H] (masks applied)
+};
+
+template <int BT>
+__global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__ RecurrentArgs a) {
+    const int H = a.H, C = 4 * a.H;
+    extern __shared__ float smemF[];
+    float *gS = smemF;             // [BT][C] gradient entering the hh branch
+    float *partS = gS + BT * C;    // [4][BT][H] partial sums of dh
+    float *wS = partS + 4 * BT * H;  // [smemRows][H] rows of weight_hh
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    for (int i = tid; i < a.smemRows * H; i += nthreads) wS[i] = a.weightHh[i];
+    for (int i = tid; i < 4 * BT * H; i += nthreads) partS[i] = 0.0f;
+    for (int i = tid; i < BT * C; i += nthreads) gS[i] = 0.0f;
+
+    const int elems = nb * H;
+    const bool hasElem = tid < elems;
+    const int eb = hasElem ? tid / H : 0, ej = hasElem ? tid % H : 0;
+    const size_t stateIdx = static_cast<size_t>(b0 + eb) * H + ej;
+    float dhCarry = hasElem ? a.gradFinalHidden[stateIdx] : 0.0f;
+    float dc = hasElem ? a.gradFinalCell[stateIdx] : 0.0f;
+    // phase A ownership: quarter q of the channels, hidden column j
+    const bool hasColumn = tid < C;
+    const int q = tid / H, cj = tid % H;
+    __syncthreads();
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        if (hasElem) {
+            const size_t row = rowBase + eb, so = row * H + ej, go = row * C + ej;
+            const float ig = realOf(a.gateOutputs[go], a.dqGate[0]), fg = realOf(a.gateOutputs[go + H], a.dqGate[1]);
+            const float cg = realOf(a.gateOutputs[go + 2 * H], a.dqGate[2]), og = realOf(a.gateOutputs[go + 3 * H], a.dqGate[3]);
+            const float ct = realOf(a.cellTanh[so], a.dqTanh);
+            float cPrev = 0.0f;
+            if (t > 0) cPrev = realOf(a.cellStates[so - static_cast<size_t>(a.B) * H], a.dqC);
+            else if (a.c0) cPrev = realOf(a.c0[stateIdx], a.dqC);
+            const float incoming = dhCarry + partS[(0 * BT + eb) * H + ej] + partS[(1 * BT + eb) * H + ej] +
+                                   partS[(2 * BT + eb) * H + ej] + partS[(3 * BT + eb) * H + ej];
+            const float dh = (incoming + a.gradOutput[so]) * keepOf(a.mk.hidden_outputs, so);
+            const float gOut = dh * ct;
+            const float gTanh = dh * og * keepOf(a.mk.cell_tanh_outputs, so);
+            const float dcAll = dc + gTanh * (1.0f - ct * ct);
+            const float mdc = dcAll * keepOf(a.mk.cell_states, so);
+            const float go4[4] = {mdc * cg * keepOf(a.mk.gate_outputs, go), mdc * cPrev * keepOf(a.mk.gate_outputs, go + H),
+                                  mdc * ig * keepOf(a.mk.gate_outputs, go + 2 * H), gOut * keepOf(a.mk.gate_outputs, go + 3 * H)};
+            const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
+                                  go4[3] * og * (1.0f - og)};
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const size_t o = go + static_cast<size_t>(g) * H;
+                const float grad = gi4[g] * keepOf(a.mk.gate_inputs, o);
+                const float hh = grad * keepOf(a.mk.weight_hh_linear, o);
+                a.gIh[o] = grad * keepOf(a.mk.weight_ih_linear, o);
+                a.gHh[o] = hh;
+                gS[eb * C + g * H + ej] = hh;
+            }
+            dc = mdc * fg;
+            dhCarry = 0.0f;
+        }
+        __syncthreads();
+        if (hasColumn) {
+            float acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+            const int cBegin = q * H, cEnd = cBegin + H;
+            for (int c = cBegin; c < cEnd; ++c) {
+                const float w = c < a.smemRows ? wS[c * H + cj] : a.weightHh[static_cast<size_t>(c) * H + cj];
+#pragma unroll
+                for (int b = 0; b < BT; ++b) acc[b] = fmaf(gS[b * C + c], w, acc[b]);
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b) partS[(q * BT + b) * H + cj] = acc[b];
+        }
+        __syncthreads();
+    }
+    if (hasElem) {
+        const float dh0 = dhCarry + partS[(0 * BT + eb) * H + ej] + partS[(1 * BT + eb) * H + ej] +
+                          partS[(2 * BT + eb) * H + ej] + partS[(3 * BT + eb) * H + ej];
+        a.dh0[stateIdx] = dh0 * keepOf(a.mk.initial_hidden, stateIdx);
+        a.dc0[stateIdx] = dc * keepOf(a.mk.initial_cell, stateIdx);
+    }
+}
+
+// Rows of a [rows, cols] operand that switches source after `split` rows (h_prev = [h0 ; hidden[0..T-2]]).
+struct RowSource {
+    const float *first;  // rows [0, split) ; null = zeros
+    const float *rest;   // rows [split, ...) start here
+    int split;
+    Dequant dq;
+    __device__ __forceinline__ float at(int row, int col, int cols) const {
+        if (row < split) return first ? realOf(first[static_cast<size_t>(row) * cols + col], dq) : 0.0f;
+        return realOf(rest[static_cast<size_t>(row - split) * cols + col], dq);
+    }
+};
+
+constexpr int kTile = 64, kDepth = 16;
+
+// partial[s][m][n] = sum over the s-th chunk of rows k of G[k][m] * X[k][n].
+__global__ void __launch_bounds__(256) gemmRowsTN(const float *__restrict__ G, const RowSource X, int K, int M, int N,
+                                                  int chunk, float *__restrict__ partial) {
+    __shared__ float As[kDepth][kTile + 4];
+    __shared__ float Bs[kDepth][kTile + 4];
+    const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+    const int kBegin = blockIdx.z * chunk, kEnd = min(K, kBegin + chunk);
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4] = {};
+    for (int k0 = kBegin; k0 < kEnd; k0 += kDepth) {
+        for (int i = threadIdx.x; i < kDepth * kTile; i += 256) {
+            const int kk = i / kTile, c = i % kTile, k = k0 + kk;
+            As[kk][c] = (k < kEnd && m0 + c < M) ? G[static_cast<size_t>(k) * M + m0 + c] : 0.0f;
+            Bs[kk][c] = (k < kEnd && n0 + c < N) ? X.at(k, n0 + c, N) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kDepth; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[kk][ty * 4 + i]; bv[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float *out = partial + static_cast<size_t>(blockIdx.z) * M * N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) out[static_cast<size_t>(m) * N + n] = acc[i][j];
+        }
+}
+
+// out[i] = keep[i] * sum_s partial[s][i], s ascending.
+__global__ void reduceSplits(const float *__restrict__ partial, int splits, size_t n, const uint8_t *__restrict__ mask,
+                             float *__restrict__ out) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float s = 0.0f;
+        for (int p = 0; p < splits; ++p) s += partial[static_cast<size_t>(p) * n + i];
+        out[i] = s * keepOf(mask, i);
+    }
+}
+
+// out[m][n] = keep * sum_k A[m][k] * W[k][n]   (dx = G_ih W_ih: M = T*B, K = 4H, N = I).
+__global__ void __launch_bounds__(256) gemmNN(const float *__restrict__ A, const float *__restrict__ W, int M, int N, int K,
+                                              const uint8_t *__restrict__ mask, float *__restrict__ out) {
+    __shared__ float As[kDepth][kTile + 1];
+    __shared__ float Ws[kDepth][kTile + 4];
+    const int m0 = blockIdx.x * kTile, n0 = blockIdx.y * kTile;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += kDepth) {
+        for (int i = threadIdx.x; i < kTile * kDepth; i += 256) {
+            const int r = i / kDepth, kk = i % kDepth;
+            As[kk][r] = (m0 + r < M && k0 + kk < K) ? A[static_cast<size_t>(m0 + r) * K + k0 + kk] : 0.0f;
+            const int wk = i / kTile, wc = i % kTile;
+            Ws[wk][wc] = (k0 + wk < K && n0 + wc < N) ? W[static_cast<size_t>(k0 + wk) * N + n0 + wc] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kDepth; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[kk][ty * 4 + i]; bv[i] = Ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) {
+                const size_t o = static_cast<size_t>(m) * N + n;
+                out[o] = acc[i][j] * keepOf(mask, o);
+            }
+        }
+}
+
+// partial[which][s][c] = sum over the s-th chunk of rows of g[n][c]; blockIdx.y selects G_ih or G_hh.
+__global__ void columnSums(const float *__restrict__ gIh, const float *__restrict__ gHh, int rows, int C, int chunk,
+                           float *__restrict__ partial) {
+    const float *g = blockIdx.y == 0 ? gIh : gHh;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int n0 = blockIdx.z * chunk, n1 = min(rows, n0 + chunk);
+    float s = 0.0f;
+    for (int n = n0; n < n1; ++n) s += g[static_cast<size_t>(n) * C + c];
+    partial[(static_cast<size_t>(blockIdx.y) * gridDim.z + blockIdx.z) * C + c] = s;
+}
+
+int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
+
+int splitsFor(int K, int tiles) {
+    const int want = std::max(1, (2 * 148 + tiles - 1) / tiles);
+    return std::max(1, std::min(want, (K + 255) / 256));
+}
+int tilesOf(int M, int N) { return ((M + kTile - 1) / kTile) * ((N + kTile - 1) / kTile); }
+
+constexpr int kBiasSplits = 64;
+
+}  // namespace
+
+size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
+    const size_t rows = static_cast<size_t>(T) * B, C = 4 * static_cast<size_t>(H);
+    WorkspaceSizer ws;
+    ws.take<float>(rows * C);  // G_ih
+    ws.take<float>(rows * C);  // G_hh
+    ws.take<float>(C * I);     // real weight_ih (QAT)
+    ws.take<float>(C * H);     // real weight_hh (QAT)
+    ws.take<float>(static_cast<size_t>(splitsFor(static_cast<int>(rows), tilesOf(static_cast<int>(C), I))) * C * I);
+    ws.take<float>(static_cast<size_t>(splitsFor(static_cast<int>(rows), tilesOf(static_cast<int>(C), H))) * C * H);
+    ws.take<float>(2 * kBiasSplits * C);
+    ws.take<float>(2 * C);     // per-channel weight scales (QAT)
+    return ws.used() + 1024;
+}
+
+void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
+    if (C > 512) fail(RXMET_ERR_UNSUPPORTED, "hidden sizes up to 128 are built (got %d)", H);
+    const size_t rows = static_cast<size_t>(T) * B;
+    Workspace ws(workspace, workspaceBytes);
+    float *gIh = ws.take<float>(rows * C);
+    float *gHh = ws.take<float>(rows * C);
+    float *wIhReal = ws.take<float>(static_cast<size_t>(C) * I);
+    float *wHhReal = ws.take<float>(static_cast<size_t>(C) * H);
+    const int splitIh = splitsFor(static_cast<int>(rows), tilesOf(C, I));
+    const int splitHh = splitsFor(static_cast<int>(rows), tilesOf(C, H));
+    float *partIh = ws.take<float>(static_cast<size_t>(splitIh) * C * I);
+    float *partHh = ws.take<float>(static_cast<size_t>(splitHh) * C * H);
+    float *partBias = ws.take<float>(2 * kBiasSplits * static_cast<size_t>(C));
+    float *channelScales = ws.take<float>(2 * static_cast<size_t>(C));
+
+    const float *wIh = call.weightIh, *wHh = call.weightHh;
+    if (call.quantized) {
+        RXMET_REQUIRE(call.weightIhScale && call.weightHhScale, "per-channel weight scales missing");
+        RXMET_CUDA(cudaMemcpyAsync(channelScales, call.weightIhScale, sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        RXMET_CUDA(cudaMemcpyAsync(channelScales + C, call.weightHhScale, sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        {
+            KernelTimer timer__("lstmDequantWeights", st);
+            dequantWeights<<<gridFor(static_cast<size_t>(C) * I, 256), 256, 0, st>>>(call.weightIh, channelScales, C, I, wIhReal);
+        }
+        afterLaunch("lstmDequantWeights");
+        {
+            KernelTimer timer__("lstmDequantWeights", st);
+            dequantWeights<<<gridFor(static_cast<size_t>(C) * H, 256), 256, 0, st>>>(call.weightHh, channelScales + C, C, H, wHhReal);
+        }
+        afterLaunch("lstmDequantWeights");
+        wIh = wIhReal;
+        wHh = wHhReal;
+    }
+    const rxmet_lstm_backward_masks none{};
+    const rxmet_lstm_backward_masks &mk = call.masks ? *call.masks : none;
+    {
+        RecurrentArgs a{};
+        a.T = T; a.B = B; a.H = H;
+        a.weightHh = wHh; a.c0 = call.c0;
+        a.gateOutputs = call.gateOutputs; a.cellStates = call.cellStates; a.cellTanh = call.cellTanhOutputs;
+        a.gradOutput = call.gradOutput; a.gradFinalHidden = call.gradFinalHidden; a.gradFinalCell = call.gradFinalCell;
+        a.dqC = call.dqC; a.dqTanh = call.dqTanh;
+        for (int g = 0; g < 4; ++g) a.dqGate[g] = call.dqGate[g];
+        a.mk = mk; a.gIh = gIh; a.gHh = gHh; a.dh0 = call.grads.initial_hidden; a.dc0 = call.grads.initial_cell;
+        int device = 0, smemMax = 0, sms = 0;
+        RXMET_CUDA(cudaGetDevice(&device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
+        const int block = (C + 31) / 32 * 32;
+        auto launch = [&](auto kernel, int BT) {
+            const size_t base = sizeof(float) * (static_cast<size_t>(BT) * C + 4 * static_cast<size_t>(BT) * H);
+            const size_t room = static_cast<size_t>(smemMax) > base + 1024 ? static_cast<size_t>(smemMax) - base - 1024 : 0;
+            a.smemRows = static_cast<int>(std::min<size_t>(C, room / (sizeof(float) * H)));
+            const size_t smem = base + sizeof(float) * static_cast<size_t>(a.smemRows) * H;
+            RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            {
+                KernelTimer timer__("lstmRecurrentBackward", st);
+                kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
+            }
+            afterLaunch("lstmRecurrentBackward");
+        };
+        if (bt == 4) launch(recurrentBackward<4>, 4);
+        else if (bt == 2) launch(recurrentBackward<2>, 2);
+        else launch(recurrentBackward<1>, 1);
+    }
+    {
+        KernelTimer timer__("lstmGemmNN", st);
+        gemmNN<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
+            gIh, wIh, static_cast<int>(rows), I, C, static_cast<const uint8_t *>(mk.input), call.grads.input);
+    }
+    afterLaunch("lstmGemmNN");
+    auto weightGrad = [&](const float *G, RowSource X, int N, int splits, float *partial, const uint8_t *mask, float *out) {
+        const int chunk = ((static_cast<int>(rows) + splits - 1) / splits + kDepth - 1) / kDepth * kDepth;
+        {
+            KernelTimer timer__("lstmGemmRowsTN", st);
+            gemmRowsTN<<<dim3((N + kTile - 1) / kTile, (C + kTile - 1) / kTile, splits), 256, 0, st>>>(
+                G, X, static_cast<int>(rows), C, N, chunk, partial);
+        }
+        afterLaunch("lstmGemmRowsTN");
+        {
+            KernelTimer timer__("lstmReduceSplits", st);
+            reduceSplits<<<gridFor(static_cast<size_t>(C) * N, 256), 256, 0, st>>>(partial, splits, static_cast<size_t>(C) * N, mask, out);
+        }
+        afterLaunch("lstmReduceSplits");
+    };
+    weightGrad(gIh, RowSource{call.x, call.x, 0, call.dqX}, I, splitIh, partIh, static_cast<const uint8_t *>(mk.weight_ih),
+               call.grads.weight_ih);
+    weightGrad(gHh, RowSource{call.h0, call.hiddenOutputs, B, call.dqH}, H, splitHh, partHh,
+               static_cast<const uint8_t *>(mk.weight_hh), call.grads.weight_hh);
+    if (call.grads.bias_ih || call.grads.bias_hh) {
+        const int chunk = (static_cast<int>(rows) + kBiasSplits - 1) / kBiasSplits;
+        {
+            KernelTimer timer__("lstmColumnSums", st);
+            columnSums<<<dim3((C + 127) / 128, 2, kBiasSplits), 128, 0, st>>>(gIh, gHh, static_cast<int>(rows), C, chunk, partBias);
+        }
+        afterLaunch("lstmColumnSums");
+        float *dst[2] = {call.grads.bias_ih, call.grads.bias_hh};
+        const uint8_t *msk[2] = {static_cast<const uint8_t *>(mk.bias_ih), static_cast<const uint8_t *>(mk.bias_hh)};
+        for (int k = 0; k < 2; ++k) {
+            if (!dst[k]) continue;
+            {
+                KernelTimer timer__("lstmReduceSplits", st);
+                reduceSplits<<<gridFor(C, 128), 128, 0, st>>>(partBias + static_cast<size_t>(k) * kBiasSplits * C, kBiasSplits, C, msk[k], dst[k]);
+            }
+            afterLaunch("lstmReduceSplits");
+        }
+    }
+}
+
+}  // namespace lstm
+}  // namespace rxmet

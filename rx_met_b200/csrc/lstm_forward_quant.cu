@@ -1,0 +1,514 @@
+// Quantized LSTM forward on 8-bit grids (the reference's FP32 q-carrier semantics, computed on
+// integer codes).
+//
+// Launch plan for one call (the reference runs T x (cuBLAS GEMM + pointwise kernel),
+// operators/quant-lstm/src/lstm/forward_quantized_fp_cuda.cu:690-880,1050-1230):
+//   quantizeCodes  x3  : x, h0, c0 -> signed-byte codes (+ optional q-carrier masters and clamp masks)
+//   prepChannels       : weight_ih / weight_hh -> packed byte codes laid out for register residency,
+//                        row sums for the zero-point correction, rescaled bias terms
+//   inputLinearQ       : all T*B rows of the input projection with dp4a; leaves the gate-input
+//                        contribution of the ih branch already rescaled to each gate's grid
+//   recurrentQ         : ONE launch for all T steps.  A CTA owns BT batch rows for the whole
+//                        sequence; thread c keeps row c of weight_hh in registers, the hidden codes
+//                        live in shared memory, the cell state in registers, activations are table
+//                        lookups, and the ih contribution of step t+1 is fetched during step t.
+//
+// Float semantics that decide codes are kept literally: rescale = rint((v * M) * 2^-shift) in
+// float with the product rounded once, cell update = rint(pf * rf + pi * ri) without contraction.
+// Integer accumulators are required to stay below 2^24, where the reference's float accumulation is
+// exact and therefore order independent.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.h"
+#include "lstm_kernels.h"
+
+namespace rxmet {
+namespace lstm {
+namespace {
+
+__device__ __forceinline__ float rescaleF(float v, DevRescale r) {
+    return rintf(__fmul_rn(__fmul_rn(v, r.mult), r.pow2));
+}
+
+// value -> clamp(rint(value / scale) + zp): division and rounding in double as the reference does
+// (operators/quant-lstm/include/quantization/float_carrier_ops.h:49-59).
+__device__ __forceinline__ int32_t quantizeCode(float v, float scale, int32_t zp, int32_t lo, int32_t hi, uint8_t &clamped) {
+    const double t = rint(static_cast<double>(v) / static_cast<double>(scale)) + static_cast<double>(zp);
+    clamped = (t < static_cast<double>(lo)) || (t > static_cast<double>(hi));
+    return t <= static_cast<double>(lo) ? lo : (t >= static_cast<double>(hi) ? hi : static_cast<int32_t>(t));
+}
+
+// Activation tensors: [rows][cols] floats -> [rows][colsPadded] signed bytes (code - shift, zero
+// padded), optional q-carrier copy, optional clamp mask, optional centred float copy (code - zp).
+__global__ void quantizeCodes(const float *__restrict__ src, int rows, int cols, int colsPadded, float scale, int32_t zp,
+                              int32_t lo, int32_t hi, int32_t shift, int8_t *__restrict__ codes,
+                              float *__restrict__ carrier, uint8_t *__restrict__ mask, float *__restrict__ centred) {
+    const size_t total = static_cast<size_t>(rows) * colsPadded;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / colsPadded), c = static_cast<int>(i % colsPadded);
+        if (c >= cols) {
+            if (codes) codes[i] = 0;
+            continue;
+        }
+        const size_t o = static_cast<size_t>(r) * cols + c;
+        uint8_t m = 0;
+        const int32_t q = src ? quantizeCode(src[o], scale, zp, lo, hi, m) : min(max(zp, lo), hi);
+        if (codes) codes[i] = static_cast<int8_t>(q - shift);
+        if (carrier) carrier[o] = static_cast<float>(q);
+        if (mask) mask[o] = m;
+        if (centred) centred[o] = static_cast<float>(q - zp);
+    }
+}
+
+struct PrepArgs {
+    int H, I, kWordsIh, kWordsHh;
+    const float *wIh, *wHh, *bIh, *bHh;  // float masters
+    const float *channel;                // kChannelFields x 4H
+    int32_t wLo, wHi, bLo, bHi;
+    int32_t xCorrection, hCorrection;    // (shift - zero point) of the x and h codes
+    uint32_t *wIhWords, *wHhWords;       // [kWords][4H]
+    int32_t *ihAddend, *hhAddend;        // correction * row sum + rescaled bias
+    float *mWIh, *mWHh, *mBIh, *mBHh;    // optional q-carrier masters
+    uint8_t *kWIh, *kWHh, *kBIh, *kBHh;  // optional clamp masks
+};
+
+// One thread per output channel: quantizes its weight rows and bias entries.
+__global__ void prepChannels(const PrepArgs a) {
+    const int C = 4 * a.H;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    auto field = [&](int f) { return a.channel[static_cast<size_t>(f) * C + c]; };
+    for (int side = 0; side < 2; ++side) {
+        const int K = side ? a.H : a.I, kWords = side ? a.kWordsHh : a.kWordsIh;
+        const float *w = (side ? a.wHh : a.wIh) + static_cast<size_t>(c) * K;
+        const float scale = field(side ? kWHhScale : kWIhScale);
+        uint32_t *words = side ? a.wHhWords : a.wIhWords;
+        float *master = side ? a.mWHh : a.mWIh;
+        uint8_t *keep = side ? a.kWHh : a.kWIh;
+        int32_t sum = 0;
+        for (int kw = 0; kw < kWords; ++kw) {
+            uint32_t word = 0;
+            for (int i = 0; i < 4; ++i) {
+                const int k = kw * 4 + i;
+                int32_t q = 0;
+                if (k < K) {
+                    uint8_t m;
+                    q = quantizeCode(w[k], scale, 0, a.wLo, a.wHi, m);
+                    if (master) master[static_cast<size_t>(c) * K + k] = static_cast<float>(q);
+                    if (keep) keep[static_cast<size_t>(c) * K + k] = m;
+                }
+                sum += q;
+                word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+            }
+            words[static_cast<size_t>(kw) * C + c] = word;
+        }
+        int32_t addend = (side ? a.hCorrection : a.xCorrection) * sum;
+        const float *b = side ? a.bHh : a.bIh;
+        if (b) {
+            uint8_t m;
+            const int32_t q = quantizeCode(b[c], field(side ? kBHhScale : kBIhScale), 0, a.bLo, a.bHi, m);
+            const DevRescale r{field(side ? kHhBiasMult : kIhBiasMult), field(side ? kHhBiasPow2 : kIhBiasPow2)};
+            addend += static_cast<int32_t>(rescaleF(static_cast<float>(q), r));
+            float *bm = side ? a.mBHh : a.mBIh;
+            uint8_t *bk = side ? a.kBHh : a.kBIh;
+            if (bm) bm[c] = static_cast<float>(q);
+            if (bk) bk[c] = m;
+        }
+        (side ? a.hhAddend : a.ihAddend)[c] = addend;
+    }
+}
+
+// accumulator -> centred linear code (code - zero point) and its clamp flag.
+__device__ __forceinline__ float linearCentred(int32_t total, DevRescale out, float cLo, float cHi, uint8_t &clamped) {
+    const float r = rescaleF(static_cast<float>(total), out);
+    clamped = (r < cLo) || (r > cHi);
+    return fminf(fmaxf(r, cLo), cHi);
+}
+
+constexpr int kIhRows = 8;
+
+struct InputLinearArgs {
+    int rows, H, kWords;
+    const int8_t *x;         // [rows][kWords*4]
+    const uint32_t *words;   // [kWords][4H]
+    const int32_t *addend;   // [4H]
+    const float *channel;
+    ScalarExec s;
+    float *lhs;              // [rows][4H] ih contribution on each gate's input grid
+    float *linear;           // optional checkpoint [rows][4H]
+    uint8_t *linearClamped;  // optional
+};
+
+template <int KW>
+__global__ void __launch_bounds__(512) inputLinearQ(const __grid_constant__ InputLinearArgs a) {
+    __shared__ __align__(16) int8_t xs[kIhRows][KW * 4];
+    const int C = 4 * a.H, c = threadIdx.x;
+    const int row0 = blockIdx.x * kIhRows, nRows = min(kIhRows, a.rows - row0);
+    const int padded = a.kWords * 4;
+    for (int i = threadIdx.x; i < kIhRows * KW * 4; i += blockDim.x) {
+        const int r = i / (KW * 4), k = i % (KW * 4);
+        xs[r][k] = (r < nRows && k < padded) ? a.x[static_cast<size_t>(row0 + r) * padded + k] : int8_t(0);
+    }
+    __syncthreads();
+    if (c >= C) return;
+    uint32_t w[KW];
+#pragma unroll
+    for (int kk = 0; kk < KW; ++kk) w[kk] = kk < a.kWords ? a.words[static_cast<size_t>(kk) * C + c] : 0u;
+    const int32_t addend = a.addend[c];
+    const DevRescale out{a.channel[static_cast<size_t>(kIhOutMult) * C + c], a.channel[static_cast<size_t>(kIhOutPow2) * C + c]};
+    const int op = RXMET_LSTM_WEIGHT_IH_LINEAR, g = c / a.H;
+    const float cLo = static_cast<float>(a.s.lo[op] - a.s.zp[op]), cHi = static_cast<float>(a.s.hi[op] - a.s.zp[op]);
+    const DevRescale toGate = a.s.ihToGate[g];
+    for (int r = 0; r < nRows; ++r) {
+        int32_t acc = 0;
+        const int32_t *xr = reinterpret_cast<const int32_t *>(xs[r]);
+#pragma unroll
+        for (int kk = 0; kk < KW; ++kk) acc = __dp4a(static_cast<int32_t>(w[kk]), xr[kk], acc);
+        uint8_t m;
+        const float cen = linearCentred(acc + addend, out, cLo, cHi, m);
+        const size_t o = static_cast<size_t>(row0 + r) * C + c;
+        a.lhs[o] = rescaleF(cen, toGate);
+        if (a.linear) a.linear[o] = cen + static_cast<float>(a.s.zp[op]);
+        if (a.linearClamped) a.linearClamped[o] = m;
+    }
+}
+
+struct RecurrentArgs {
+    int T, B, H, kWords;
+    const uint32_t *words;   // [kWords][4H] weight_hh codes
+    const int32_t *addend;   // [4H]
+    const float *channel;
+    const int32_t *tables;   // kTables x kTableSize
+    const float *lhs;        // [T][B][4H]
+    const int8_t *h0;        // [B][kWords*4] codes - hShift
+    const float *c0;         // [B][H] centred cell codes
+    ScalarExec s;
+    float *output;           // [T][B][H] dequantized
+    float *finalHidden, *finalCell;
+    rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearQ)
+};
+
+__device__ __forceinline__ float scaleCell(float product, float ratio, double mantissa, int exponent, int usesFp) {
+    if (usesFp) return static_cast<float>(ldexp(static_cast<double>(product) * mantissa, exponent));
+    return __fmul_rn(product, ratio);
+}
+
+template <int KW, int BT>
+__global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ RecurrentArgs a) {
+    const int H = a.H, C = 4 * a.H;
+    constexpr int kPadded = KW * 4;
+    __shared__ __align__(16) int8_t hS[BT][kPadded];
+    __shared__ int32_t tabS[kTables * kTableSize];
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    float *rhsS = reinterpret_cast<float *>(smemRaw);  // [BT][C]
+
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    const ScalarExec &s = a.s;
+    for (int i = tid; i < kTables * kTableSize; i += nthreads) tabS[i] = a.tables[i];
+
+    // phase A ownership: row c of weight_hh
+    const bool hasChannel = tid < C;
+    uint32_t rw[KW];
+    int32_t addend = 0;
+    DevRescale outR{1.0f, 1.0f}, toGate{1.0f, 1.0f};
+#pragma unroll
+    for (int kk = 0; kk < KW; ++kk) rw[kk] = (hasChannel && kk < a.kWords) ? a.words[static_cast<size_t>(kk) * C + tid] : 0u;
+    if (hasChannel) {
+        addend = a.addend[tid];
+        outR = {a.channel[static_cast<size_t>(kHhOutMult) * C + tid], a.channel[static_cast<size_t>(kHhOutPow2) * C + tid]};
+        toGate = s.hhToGate[tid / H];
+    }
+    const int srcPadded = a.kWords * 4;
+    for (int i = tid; i < BT * kPadded; i += nthreads) {
+        const int b = i / kPadded, k = i % kPadded;
+        hS[b][k] = (b < nb && k < srcPadded) ? a.h0[static_cast<size_t>(b0 + b) * srcPadded + k] : int8_t(0);
+    }
+
+    // phase B ownership: element (b, j) with its cell state in a register
+    const int elems = nb * H;
+    const bool hasElem = tid < elems;
+    const int eb = hasElem ? tid / H : 0, ej = hasElem ? tid % H : 0;
+    float cellCen = hasElem ? a.c0[static_cast<size_t>(b0 + eb) * H + ej] : 0.0f;
+    float hiddenCen = 0.0f;
+
+    const int opHh = RXMET_LSTM_WEIGHT_HH_LINEAR;
+    const float hhLo = static_cast<float>(s.lo[opHh] - s.zp[opHh]), hhHi = static_cast<float>(s.hi[opHh] - s.zp[opHh]);
+    const float zHh = static_cast<float>(s.zp[opHh]);
+    float giLo[4], giHi[4];
+    int32_t giBase[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int op = RXMET_LSTM_INPUT_GATE_INPUT + g;
+        giLo[g] = static_cast<float>(s.lo[op] - s.zp[op]);
+        giHi[g] = static_cast<float>(s.hi[op] - s.zp[op]);
+        giBase[g] = s.zp[op] - s.lo[op];
+    }
+    const int opC = RXMET_LSTM_CELL_STATE, opO = RXMET_LSTM_OUTPUT;
+    const float cLo = static_cast<float>(s.lo[opC] - s.zp[opC]), cHi = static_cast<float>(s.hi[opC] - s.zp[opC]);
+    const float oLo = static_cast<float>(s.lo[opO] - s.zp[opO]), oHi = static_cast<float>(s.hi[opO] - s.zp[opO]);
+    const int32_t cBase = s.zp[opC] - s.lo[opC];
+    const int32_t hStore = s.zp[opO] - s.hShift;  // centred hidden code -> stored byte
+    const float scaleH = s.scale[opO];
+
+    float lhsCur[4] = {0, 0, 0, 0}, lhsNext[4] = {0, 0, 0, 0};
+    auto fetch = [&](int t, float (&dst)[4]) {
+        if (hasElem) {
+            const float *row = a.lhs + (static_cast<size_t>(t) * a.B + b0 + eb) * C + ej;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) dst[g] = row[g * H];
+        }
+    };
+    fetch(0, lhsCur);
+    __syncthreads();
+
+    const int4 *hS4 = reinterpret_cast<const int4 *>(&hS[0][0]);
+    for (int t = 0; t < a.T; ++t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        if (t + 1 < a.T) fetch(t + 1, lhsNext);
+
+        if (hasChannel) {
+            int32_t acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0;
+#pragma unroll
+            for (int k4 = 0; k4 < KW / 4; ++k4) {
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    const int4 hv = hS4[b * (KW / 4) + k4];
+                    acc[b] = __dp4a(static_cast<int32_t>(rw[4 * k4 + 0]), hv.x, acc[b]);
+                    acc[b] = __dp4a(static_cast<int32_t>(rw[4 * k4 + 1]), hv.y, acc[b]);
+                    acc[b] = __dp4a(static_cast<int32_t>(rw[4 * k4 + 2]), hv.z, acc[b]);
+                    acc[b] = __dp4a(static_cast<int32_t>(rw[4 * k4 + 3]), hv.w, acc[b]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                uint8_t m;
+                const float cen = linearCentred(acc[b] + addend, outR, hhLo, hhHi, m);
+                rhsS[b * C + tid] = rescaleF(cen, toGate);
+                if (b < nb) {
+                    const size_t o = (rowBase + b) * C + tid;
+                    if (a.ck.weight_hh_linear) a.ck.weight_hh_linear[o] = cen + zHh;
+                    if (a.ck.weight_hh_linear_clamped) a.ck.weight_hh_linear_clamped[o] = m;
+                }
+            }
+        }
+        __syncthreads();
+
+        if (hasElem) {
+            const size_t row = rowBase + eb;
+            float outCen[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const float sum = lhsCur[g] + rhsS[eb * C + g * H + ej];
+                const float cen = fminf(fmaxf(sum, giLo[g]), giHi[g]);
+                const int32_t e = tabS[g * kTableSize + static_cast<int32_t>(cen) + giBase[g]];
+                outCen[g] = static_cast<float>(e >> 1);
+                const size_t o = row * C + g * H + ej;
+                if (a.ck.gate_inputs) a.ck.gate_inputs[o] = cen + static_cast<float>(s.zp[RXMET_LSTM_INPUT_GATE_INPUT + g]);
+                if (a.ck.gate_inputs_clamped) a.ck.gate_inputs_clamped[o] = (sum < giLo[g]) || (sum > giHi[g]);
+                if (a.ck.gate_outputs) a.ck.gate_outputs[o] = outCen[g] + static_cast<float>(s.zp[RXMET_LSTM_INPUT_GATE_OUTPUT + g]);
+                if (a.ck.gate_outputs_clamped) a.ck.gate_outputs_clamped[o] = static_cast<uint8_t>(e & 1);
+            }
+            const float pf = __fmul_rn(outCen[1], cellCen), pi = __fmul_rn(outCen[0], outCen[2]);
+            const float sf = scaleCell(pf, s.forgetRatio, s.forgetMantissa, s.forgetExponent, s.forgetUsesFp);
+            const float si = scaleCell(pi, s.inputRatio, s.inputMantissa, s.inputExponent, s.inputUsesFp);
+            const float rounded = rintf(__fadd_rn(sf, si));
+            cellCen = fminf(fmaxf(rounded, cLo), cHi);
+            const int32_t te = tabS[4 * kTableSize + static_cast<int32_t>(cellCen) + cBase];
+            const float tanhCen = static_cast<float>(te >> 1);
+            const float raw = __fmul_rn(outCen[3], tanhCen);
+            const float hr = rescaleF(raw, s.productToOutput);
+            hiddenCen = fminf(fmaxf(hr, oLo), oHi);
+            hS[eb][ej] = static_cast<int8_t>(static_cast<int32_t>(hiddenCen) + hStore);
+            const size_t so = row * H + ej;
+            a.output[so] = __fmul_rn(hiddenCen, scaleH);
+            if (a.ck.cell_states) a.ck.cell_states[so] = cellCen + static_cast<float>(s.zp[opC]);
+            if (a.ck.cell_states_clamped) a.ck.cell_states_clamped[so] = (rounded < cLo) || (rounded > cHi);
+            if (a.ck.cell_tanh_outputs) a.ck.cell_tanh_outputs[so] = tanhCen + static_cast<float>(s.zp[RXMET_LSTM_CELL_TANH_OUTPUT]);
+            if (a.ck.cell_tanh_outputs_clamped) a.ck.cell_tanh_outputs_clamped[so] = static_cast<uint8_t>(te & 1);
+            if (a.ck.hidden_outputs) a.ck.hidden_outputs[so] = hiddenCen + static_cast<float>(s.zp[opO]);
+            if (a.ck.hidden_outputs_clamped) a.ck.hidden_outputs_clamped[so] = (hr < oLo) || (hr > oHi);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) lhsCur[g] = lhsNext[g];
+        __syncthreads();
+    }
+    if (hasElem) {
+        const size_t o = static_cast<size_t>(b0 + eb) * H + ej;
+        if (a.T == 0) hiddenCen = static_cast<float>(static_cast<int32_t>(hS[eb][ej]) - hStore);
+        a.finalHidden[o] = __fmul_rn(hiddenCen, scaleH);
+        a.finalCell[o] = __fmul_rn(cellCen, s.scale[opC]);
+    }
+}
+
+int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
+
+int wordsFor(int k) { return (k + 3) / 4; }
+// register-resident word counts the kernels are instantiated for
+int roundWords(int kWords) { return kWords <= 8 ? 8 : (kWords <= 16 ? 16 : 32); }
+
+struct Plan {
+    int kWordsIh, kWordsHh, kwIh, kwHh;
+    size_t rows;
+};
+
+Plan planFor(int T, int B, int I, int H) {
+    Plan p;
+    p.kWordsIh = wordsFor(I);
+    p.kWordsHh = wordsFor(H);
+    p.kwIh = roundWords(p.kWordsIh);
+    p.kwHh = roundWords(p.kWordsHh);
+    p.rows = static_cast<size_t>(T) * B;
+    return p;
+}
+
+template <class W>
+void layout(W &ws, int T, int B, int I, int H, int8_t **x, int8_t **h0, float **c0, uint32_t **wIh, uint32_t **wHh,
+            int32_t **addIh, int32_t **addHh, float **channel, int32_t **tables, float **lhs) {
+    const Plan p = planFor(T, B, I, H);
+    const size_t C = 4 * static_cast<size_t>(H);
+    auto set = [](auto **dst, auto *v) { if (dst) *dst = v; };
+    set(x, ws.template take<int8_t>(p.rows * p.kWordsIh * 4));
+    set(h0, ws.template take<int8_t>(static_cast<size_t>(B) * p.kWordsHh * 4));
+    set(c0, ws.template take<float>(static_cast<size_t>(B) * H));
+    set(wIh, ws.template take<uint32_t>(p.kWordsIh * C));
+    set(wHh, ws.template take<uint32_t>(p.kWordsHh * C));
+    set(addIh, ws.template take<int32_t>(C));
+    set(addHh, ws.template take<int32_t>(C));
+    set(channel, ws.template take<float>(kChannelFields * C));
+    set(tables, ws.template take<int32_t>(kTables * kTableSize));
+    set(lhs, ws.template take<float>(p.rows * C));
+}
+
+struct SizerAdapter {
+    WorkspaceSizer ws;
+    template <class T>
+    T *take(size_t n) {
+        ws.take<T>(n);
+        return nullptr;
+    }
+};
+
+}  // namespace
+
+size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
+    SizerAdapter s;
+    layout(s, T, B, I, H, static_cast<int8_t **>(nullptr), static_cast<int8_t **>(nullptr), static_cast<float **>(nullptr),
+           static_cast<uint32_t **>(nullptr), static_cast<uint32_t **>(nullptr), static_cast<int32_t **>(nullptr),
+           static_cast<int32_t **>(nullptr), static_cast<float **>(nullptr), static_cast<int32_t **>(nullptr),
+           static_cast<float **>(nullptr));
+    return s.ws.used() + 1024;
+}
+
+void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
+    const ScalarExec &s = e.scalar;
+    for (int op = 0; op < kOps; ++op)
+        if (s.hi[op] - s.lo[op] > 255)
+            fail(RXMET_ERR_UNSUPPORTED, "this build runs grids of at most 8 bits (point %d is wider)", op);
+    if (!e.exactAccumulators)
+        fail(RXMET_ERR_UNSUPPORTED, "an integer accumulator of this configuration may reach 2^24, where the float carrier stops being order independent");
+    if (H > 128 || I > 128) fail(RXMET_ERR_UNSUPPORTED, "hidden and input sizes up to 128 are built (got H=%d, I=%d)", H, I);
+    const Plan p = planFor(T, B, I, H);
+    Workspace ws(workspace, workspaceBytes);
+    int8_t *xq, *h0q;
+    float *c0c, *channel, *lhs;
+    uint32_t *wIh, *wHh;
+    int32_t *addIh, *addHh, *tables;
+    layout(ws, T, B, I, H, &xq, &h0q, &c0c, &wIh, &wHh, &addIh, &addHh, &channel, &tables, &lhs);
+    RXMET_CUDA(cudaMemcpyAsync(channel, e.channel.data(), e.channel.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+    RXMET_CUDA(cudaMemcpyAsync(tables, e.tables.data(), e.tables.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+
+    const rxmet_lstm_masters none{};
+    const rxmet_lstm_masters &m = call.masters ? *call.masters : none;
+    auto quantize = [&](const float *src, int rows, int cols, int colsPadded, int op, int shift, int8_t *codes,
+                        float *carrier, uint8_t *mask, float *centred) {
+        const size_t total = static_cast<size_t>(rows) * colsPadded;
+        {
+            KernelTimer timer__("lstmQuantizeCodes", st);
+            quantizeCodes<<<gridFor(total, 256), 256, 0, st>>>(src, rows, cols, colsPadded, s.scale[op], s.zp[op], s.lo[op],
+                                                             s.hi[op], shift, codes, carrier, mask, centred);
+        }
+        afterLaunch("lstmQuantizeCodes");
+    };
+    quantize(call.x, static_cast<int>(p.rows), I, p.kWordsIh * 4, RXMET_LSTM_INPUT, s.xShift, xq, m.input, m.input_clamped, nullptr);
+    quantize(call.h0, B, H, p.kWordsHh * 4, RXMET_LSTM_OUTPUT, s.hShift, h0q, m.initial_hidden, m.initial_hidden_clamped, nullptr);
+    quantize(call.c0, B, H, H, RXMET_LSTM_CELL_STATE, 0, nullptr, m.initial_cell, m.initial_cell_clamped, c0c);
+    if (!call.h0) {
+        if (m.initial_hidden_clamped) RXMET_CUDA(cudaMemsetAsync(m.initial_hidden_clamped, 0, static_cast<size_t>(B) * H, st));
+        if (m.initial_cell_clamped) RXMET_CUDA(cudaMemsetAsync(m.initial_cell_clamped, 0, static_cast<size_t>(B) * H, st));
+    }
+
+    PrepArgs pa{};
+    pa.H = H; pa.I = I; pa.kWordsIh = p.kWordsIh; pa.kWordsHh = p.kWordsHh;
+    pa.wIh = call.weightIh; pa.wHh = call.weightHh; pa.bIh = call.biasIh; pa.bHh = call.biasHh;
+    pa.channel = channel;
+    pa.wLo = s.lo[RXMET_LSTM_WEIGHT_IH]; pa.wHi = s.hi[RXMET_LSTM_WEIGHT_IH];
+    pa.bLo = s.lo[RXMET_LSTM_BIAS_IH]; pa.bHi = s.hi[RXMET_LSTM_BIAS_IH];
+    pa.xCorrection = s.xShift - s.zp[RXMET_LSTM_INPUT];
+    pa.hCorrection = s.hShift - s.zp[RXMET_LSTM_OUTPUT];
+    pa.wIhWords = wIh; pa.wHhWords = wHh; pa.ihAddend = addIh; pa.hhAddend = addHh;
+    pa.mWIh = m.weight_ih; pa.mWHh = m.weight_hh; pa.mBIh = m.bias_ih; pa.mBHh = m.bias_hh;
+    pa.kWIh = m.weight_ih_clamped; pa.kWHh = m.weight_hh_clamped; pa.kBIh = m.bias_ih_clamped; pa.kBHh = m.bias_hh_clamped;
+    {
+        KernelTimer timer__("lstmPrepChannels", st);
+        prepChannels<<<(C + 63) / 64, 64, 0, st>>>(pa);
+    }
+    afterLaunch("lstmPrepChannels");
+
+    const rxmet_lstm_trace noTrace{};
+    const rxmet_lstm_trace &ck = call.checkpoints ? *call.checkpoints : noTrace;
+    const int block = (C + 31) / 32 * 32;
+    {
+        InputLinearArgs a{};
+        a.rows = static_cast<int>(p.rows); a.H = H; a.kWords = p.kWordsIh;
+        a.x = xq; a.words = wIh; a.addend = addIh; a.channel = channel; a.s = s; a.lhs = lhs;
+        a.linear = ck.weight_ih_linear; a.linearClamped = ck.weight_ih_linear_clamped;
+        const int grid = static_cast<int>((p.rows + kIhRows - 1) / kIhRows);
+        {
+            KernelTimer timer__("lstmInputLinearQ", st);
+            if (p.kwIh == 8) inputLinearQ<8><<<grid, block, 0, st>>>(a);
+            else if (p.kwIh == 16) inputLinearQ<16><<<grid, block, 0, st>>>(a);
+            else inputLinearQ<32><<<grid, block, 0, st>>>(a);
+        }
+        afterLaunch("lstmInputLinearQ");
+    }
+    {
+        RecurrentArgs a{};
+        a.T = T; a.B = B; a.H = H; a.kWords = p.kWordsHh;
+        a.words = wHh; a.addend = addHh; a.channel = channel; a.tables = tables; a.lhs = lhs; a.h0 = h0q; a.c0 = c0c;
+        a.s = s; a.output = call.output; a.finalHidden = call.finalHidden; a.finalCell = call.finalCell; a.ck = ck;
+        int device = 0, sms = 0;
+        RXMET_CUDA(cudaGetDevice(&device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        // BT*H elements must not exceed the 4H threads of a CTA
+        const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
+        auto launch = [&](auto kernel, int BT) {
+            const size_t smem = sizeof(float) * static_cast<size_t>(BT) * C;
+            {
+                KernelTimer timer__("lstmRecurrentQ", st);
+                kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
+            }
+            afterLaunch("lstmRecurrentQ");
+        };
+#define RXMET_LSTM_DISPATCH(KW)                          \
+    do {                                                  \
+        if (bt == 4) launch(recurrentQ<KW, 4>, 4);        \
+        else if (bt == 2) launch(recurrentQ<KW, 2>, 2);   \
+        else launch(recurrentQ<KW, 1>, 1);                \
+    } while (0)
+        if (p.kwHh == 8) RXMET_LSTM_DISPATCH(8);
+        else if (p.kwHh == 16) RXMET_LSTM_DISPATCH(16);
+        else RXMET_LSTM_DISPATCH(32);
+#undef RXMET_LSTM_DISPATCH
+    }
+}
+
+}  // namespace lstm
+}  // namespace rxmet

@@ -1,0 +1,55 @@
+// Launchers of the QuantLSTM kernels (declarations shared by the C ABI layer).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "lstm_params.h"
+
+namespace rxmet {
+namespace lstm {
+
+struct ForwardFloatCall {
+    int T, B, I, H;
+    const float *weightIh, *weightHh, *biasIh, *biasHh, *x, *h0, *c0;
+    float *output, *finalHidden, *finalCell;
+    const rxmet_lstm_trace *trace;  // optional
+    float *stats;                   // optional packed min/max statistics (device)
+};
+size_t forwardFloatWorkspaceBytes(int T, int B, int I, int H);
+void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
+
+struct ForwardQuantCall {
+    int T, B, I, H;
+    const float *weightIh, *weightHh, *biasIh, *biasHh, *x, *h0, *c0;
+    float *output, *finalHidden, *finalCell;
+    const rxmet_lstm_trace *checkpoints;  // optional
+    const rxmet_lstm_masters *masters;    // optional
+};
+size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H);
+void forwardQuant(const ForwardQuantCall &call, const Exec &exec, void *workspace, size_t workspaceBytes,
+                  cudaStream_t stream);
+
+// How a saved tensor is turned into real values while it is loaded: real = (value - zeroPoint) * scale.
+// The float backward uses {1, 0}; the QAT backward passes the grid of each saved q-carrier tensor.
+struct Dequant {
+    float scale = 1.0f;
+    float zeroPoint = 0.0f;
+};
+
+struct BackwardCall {
+    int T, B, I, H;
+    const float *weightIh, *weightHh, *x, *h0, *c0;
+    const float *gateOutputs, *cellStates, *cellTanhOutputs, *hiddenOutputs;
+    const float *gradOutput, *gradFinalHidden, *gradFinalCell;
+    const rxmet_lstm_backward_masks *masks;  // optional
+    rxmet_lstm_gradients grads;
+    // QAT: grids of the saved tensors and per-channel weight scales (host, 4H each); null = float
+    bool quantized = false;
+    Dequant dqX, dqH, dqC, dqGate[4], dqTanh;
+    const float *weightIhScale = nullptr, *weightHhScale = nullptr;
+};
+size_t backwardWorkspaceBytes(int T, int B, int I, int H);
+void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
+
+}  // namespace lstm
+}  // namespace rxmet

@@ -235,3 +235,70 @@ def test_backward_masks_zero_the_gradient_paths():
     wm = (rng.random((16, 3)) < 0.3).astype(np.uint8)
     part = ll.backward_float("orc", p, tr, *g, masks={"weight_ih": wm})
     np.testing.assert_array_equal(part["weight_ih"], np.where(wm, 0, base["weight_ih"]))
+
+
+# ---- host-side logic of the shipped library (no GPU needed) -------------------
+
+def product():
+    from rx_met_b200 import _quant_lstm
+    return _quant_lstm
+
+
+@pytest.mark.parametrize("cfg_kw", CONFIGS)
+@pytest.mark.parametrize("bias", [True, False])
+def test_library_host_logic_matches_checker(cfg_kw, bias):
+    m = product()
+    lib = m._library()
+    cfg = L.default_config(**cfg_kw)
+    T, B, I, H = 6, 3, 5, 8
+    p = ll.problem(T, B, I, H, seed=41, bias=bias)
+    ranges, want = ll.calibrate("orc", cfg, p, np.stack([p["x"]]))
+    got = L.ParamsBox(H)
+    assert lib.rxmet_lstm_params_from_ranges(C.byref(cfg), C.byref(ranges.struct), I, H, int(bias), *got.scale_ptrs(),
+                                             C.byref(got.struct)) == 0, lib.rxmet_last_error()
+    got.bind()
+    for op in range(L.NUM_OPS):
+        if op not in L.PARAMETER_OPS:
+            assert got.struct.scale[op] == want.struct.scale[op] and got.struct.zero_point[op] == want.struct.zero_point[op]
+    for k in range(4 if bias else 2):
+        np.testing.assert_array_equal(got.channel_scales[k], want.channel_scales[k])
+    ex = L.ExecutionBox(H)
+    assert lib.rxmet_lstm_derive_execution(C.byref(got.struct), 0, C.byref(ex.struct)) == 0
+    ref = ll.derive("orc", want)
+    assert ex.flat(bias) == ref.flat(bias)
+    assert ex.struct.exact_accumulation == ref.struct.exact_accumulation
+    # bundle JSON round trip and audit
+    text = m._params_to_bundle(got)
+    back = m._bundle_to_params(text)
+    assert m._params_to_bundle(back) == text
+    audit = m.audit_quant_params_bundle(text)
+    assert audit["bundle_json"] == text and audit["bias_enabled"] == bias
+    if ex.struct.exact_accumulation == 0:
+        assert lib.rxmet_lstm_derive_execution(C.byref(got.struct), 1, C.byref(ex.struct)) == -1
+        assert b"require_exact_accumulation" in lib.rxmet_last_error()
+
+
+def test_library_default_config_and_config_json():
+    m = product()
+    cfg = L.QuantConfig()
+    assert m._library().rxmet_lstm_default_config(C.byref(cfg)) == 0
+    want = L.default_config(symmetric_activations=True)
+    assert bytes(cfg) == bytes(want)
+    text = m._config_to_json(cfg)
+    assert m.validate_resolved_quant_config(text) == text
+    merged = json.loads(m.resolve_quant_config(text, json.dumps({"scale_mode": "pot2", "operators": {"cell_state": {"bitwidth": 16}}})))
+    assert merged["scale_mode"] == "pot2" and merged["operators"]["cell_state"]["bitwidth"] == 16
+    with pytest.raises(ValueError):
+        m.resolve_quant_config(text, json.dumps({"operators": {"nonsense": {}}}))
+    assert m._shortest_float(0.0078125) == "0.0078125" and m._shortest_float(1.1920929e-07) == "1.1920929e-07"
+    # the stats layout the fold consumes
+    lib = m._library()
+    H = 4
+    n = lib.rxmet_lstm_stats_floats(H)
+    assert n == 2 * (18 + 3 + 16 * H)
+    stats = np.concatenate([np.full(n // 2, 3.4028235e38, np.float32), np.full(n // 2, -3.4028235e38, np.float32)])
+    stats[L.INPUT], stats[n // 2 + L.INPUT] = -2.0, 5.0
+    box = L.RangesBox(H)
+    assert lib.rxmet_lstm_ranges_fold_stats(C.byref(box.struct), stats.ctypes.data_as(C.POINTER(C.c_float)), H, 1) == 0
+    assert (box.struct.minimum[L.INPUT], box.struct.maximum[L.INPUT]) == (-2.0, 5.0)
+    assert box.struct.minimum[L.OUTPUT] == np.inf  # untouched slots stay empty
