@@ -193,6 +193,12 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
     lib = cabi.load_library()
+    if args.profile_only and args.workload == "lstm":
+        # small LSTM training loop for captures under a profiler; prints no bench line
+        lstm_secondary(lib, torch, device, torch.empty(1, dtype=torch.uint8, device=device), profile_steps=args.steps,
+                       T_override=args.lstm_T)
+        print(json.dumps({"profile_only": True, "workload": "lstm"}), flush=True)
+        return
     T, B, I, H = (WORKLOAD[k] for k in "TBIH")
     cfg = ops.OperatorQuantConfig()
     for name in cabi.OP_NAMES:
@@ -316,7 +322,8 @@ def run_ours(args):
         cpu = None
         secondary = None
         if world == 1:
-            secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak)}
+            secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak),
+                         "lstm_w8a8": lstm_secondary(lib, torch, device, flush)}
             v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
             cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
         line = {
@@ -375,12 +382,112 @@ def aimet_kernel_bandwidth(lib, torch, device, peak_gbs):
     return out
 
 
+def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
+    """QuantLSTM at the same shape as the headline GRU workload (T=100, B=256, I=40, H=128, all
+    points 8 bit symmetric, per-channel weights): seq-timesteps/s of the quantized inference
+    forward, the training forward (7 checkpoints + masks saved) and the QAT backward, the
+    per-kernel milliseconds, and the reference's CPU quantized forward on the host cores."""
+    import numpy as np
+    import lstm_lib as ll
+    from rx_met_b200 import _cabi_lstm as L
+    from rx_met_b200 import _quant_lstm as m
+    T, B, I, H = (WORKLOAD[k] for k in "TBIH")
+    T = T_override or T
+    p = ll.problem(T, 16, I, H, seed=5, wscale=0.15)
+    cfg = L.default_config(symmetric_activations=True)
+    _, box = ll.calibrate("orc", cfg, p, np.stack([p["x"]]))
+    bundle = m._params_to_bundle(box)
+    gen = torch.Generator(device="cpu").manual_seed(99)
+    x = torch.randn((T, B, I), generator=gen).to(device)
+    h0 = (torch.randn((1, B, H), generator=gen) * 0.5).to(device)
+    c0 = (torch.randn((1, B, H), generator=gen) * 0.5).to(device)
+    w = [torch.from_numpy(p[k]).to(device) for k in ("w_ih", "w_hh", "b_ih", "b_hh")]
+    g = [torch.randn(s, generator=gen).to(device) for s in [(T, B, H), (B, H), (B, H)]]
+    saved = {}
+
+    def infer():
+        m.lstm_forward_quantized(x, *w, h0, c0, False, bundle)
+
+    def train_fwd():
+        saved["out"] = m.lstm_forward_quantized(x, *w, h0, c0, False, bundle, "pedantic", False, True)
+
+    def qat_bwd():
+        ck = saved["out"][3]
+        order = ("input", "weight_ih", "weight_hh", "bias_ih", "bias_hh", "h_0", "c_0")
+        m.lstm_backward_qat([ck["quantized_master"][n] for n in order], False, bundle,
+                            [ck["values"][n] for n in ("gate_outputs", "cell_states", "cell_tanh_outputs", "hidden_outputs")],
+                            *g, [ck["master_clamp_masks"][n] for n in order], [ck["clamp_masks"][n] for n in L.TRACE_VALUES])
+
+    def time_it(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / reps
+
+    if profile_steps:
+        for _ in range(profile_steps):
+            train_fwd(); qat_bwd()
+        torch.cuda.synchronize()
+        return None
+    out = {"workload": {"T": T, "B": B, "I": I, "H": H, "quant": "W8 per-channel symmetric, A8 symmetric, float-carrier semantics"}}
+    ms_inf, ms_fwd = time_it(infer), time_it(train_fwd)
+    ms_bwd = time_it(qat_bwd)
+    st = T * B
+    out["inference_forward"] = {"ms": ms_inf, "seq_timesteps_per_s": st / (ms_inf * 1e-3)}
+    out["training_forward"] = {"ms": ms_fwd, "seq_timesteps_per_s": st / (ms_fwd * 1e-3)}
+    out["qat_backward"] = {"ms": ms_bwd, "seq_timesteps_per_s": st / (ms_bwd * 1e-3)}
+    out["qat_forward_backward"] = {"ms": ms_fwd + ms_bwd, "seq_timesteps_per_s": st / ((ms_fwd + ms_bwd) * 1e-3)}
+    lib.rxmet_reset_kernel_timing()
+    lib.rxmet_set_kernel_timing(1)
+    for _ in range(3):
+        train_fwd(); qat_bwd()
+    torch.cuda.synchronize()
+    per = {}
+    for n in ["lstmQuantizeCodes", "lstmPrepChannels", "lstmInputLinearQ", "lstmRecurrentQ", "lstmDequantWeights",
+              "lstmPackStepMasks", "lstmRecurrentBackward", "lstmGemmNN", "lstmGemmRowsTN", "lstmReduceSplits",
+              "lstmColumnSums", "weightGradMma", "lstmReduceWeightGradT"]:
+        ms, cnt = C.c_double(), C.c_longlong()
+        lib.rxmet_get_kernel_timing(n.encode(), C.byref(ms), C.byref(cnt))
+        if cnt.value:
+            per[n] = ms.value / 3
+    lib.rxmet_set_kernel_timing(0)
+    out["kernel_ms_per_step"] = per
+    # the reference's CPU quantized forward (its only CPU path) on all host cores, bounded sample
+    prefix = "ref" if ll.have_ref() else "orc"
+    q = ll.quantize_masters("orc", p, box)
+    cores = os.cpu_count() or 1
+
+    def shard(_):
+        ll.forward_quantized(prefix, box, T, 16, q)
+
+    t0 = time.perf_counter(); shard(0); one = time.perf_counter() - t0
+    n_shards = cores * max(1, int(4.0 / max(one, 1e-3)))
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=cores) as pool:
+        list(pool.map(shard, range(n_shards)))
+    dt = time.perf_counter() - t0
+    out["cpu_baseline"] = {"value": n_shards * 16 * T / dt, "unit": UNIT, "cores": cores,
+                           "kind": "reference" if prefix == "ref" else "port",
+                           "sample": f"{n_shards} shards of 16 sequences x T={T}, q-carrier forward only, {dt:.1f} s"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["gru", "lstm"], default="gru",
+                    help="with --profile-only: which training loop to run (the bench line is always the GRU QAT step)")
+    ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only the device-resident leg (for captures under a profiler); prints no bench line")
     args = ap.parse_args()

@@ -265,7 +265,22 @@ def _parse_scale(text) -> np.float32:
     return v
 
 
+_BUNDLE_CACHE: dict = {}
+
+
 def _bundle_to_params(bundle_json: str) -> L.ParamsBox:
+    """Parsed parameters of a bundle; cached on the text, because a module passes the same bundle on
+    every call (treat the returned box as read-only)."""
+    box = _BUNDLE_CACHE.get(bundle_json)
+    if box is None:
+        box = _parse_bundle(bundle_json)
+        if len(_BUNDLE_CACHE) > 64:
+            _BUNDLE_CACHE.clear()
+        _BUNDLE_CACHE[bundle_json] = box
+    return box
+
+
+def _parse_bundle(bundle_json: str) -> L.ParamsBox:
     try:
         root = json.loads(bundle_json)
     except json.JSONDecodeError as e:
@@ -380,8 +395,14 @@ def _config_from_json(text: str) -> L.QuantConfig:
 
 
 def _execution(box: L.ParamsBox, require_exact: bool) -> L.ExecutionBox:
+    cached = getattr(box, "_execution", {}).get(bool(require_exact))
+    if cached is not None:
+        return cached
     ex = L.ExecutionBox(box.H)
     _check(_library().rxmet_lstm_derive_execution(C.byref(box.struct), int(require_exact), C.byref(ex.struct)), ValueError)
+    if not hasattr(box, "_execution"):
+        box._execution = {}
+    box._execution[bool(require_exact)] = ex
     return ex
 
 

@@ -21,6 +21,7 @@
 
 #include "common.h"
 #include "gru_backward.h"
+#include "weight_grad_mma.h"
 
 namespace rxmet {
 namespace gru {
@@ -570,16 +571,7 @@ __global__ void __launch_bounds__(256) gemmTN(const float *__restrict__ A, const
 // staged in shared memory as [k][m] / [k][n] and read with transposing ldmatrix.
 constexpr int kWgChunk = 32, kWgCols = 64;
 
-struct WeightGradProblem {
-    const int32_t *aCodes;  // [K][M] integer codes (x path), or
-    const float *aFloat;    // [K][M] dequantized values (h path)
-    float aInvScale;        // 1/scale for the float path
-    int32_t aZero;          // zero point for the code path
-    int M;                  // real rows (multiple of 4); row M is the ones row
-    const float *B;         // [K][N] gradients, N a multiple of 4
-    float *partial;         // [splits][M+1][N]
-};
-
+using WeightGradProblem = wgrad::Problem;
 
 // Loads of the next K chunk are issued into registers before the tensor work of the current
 // chunk, so the HBM latency overlaps the MMAs; one shared-memory buffer, two barriers per chunk.
@@ -641,8 +633,8 @@ __global__ void __launch_bounds__(256, 2) weightGradMma(const WeightGradProblem 
             if (aRow[v] >= 0) {
                 float4 a = aReg[v];
                 if (!p.aCodes) {  // recover the integer code difference from the dequantized value
-                    a.x = rintf(a.x * p.aInvScale); a.y = rintf(a.y * p.aInvScale);
-                    a.z = rintf(a.z * p.aInvScale); a.w = rintf(a.w * p.aInvScale);
+                    a.x = rintf(a.x * p.aInvScale) - p.aFloatZero; a.y = rintf(a.y * p.aInvScale) - p.aFloatZero;
+                    a.z = rintf(a.z * p.aInvScale) - p.aFloatZero; a.w = rintf(a.w * p.aInvScale) - p.aFloatZero;
                 }
                 *reinterpret_cast<uint2 *>(&As[aRow[v]][aCol[v]]) = make_uint2(packBf16(a.x, a.y), packBf16(a.z, a.w));
             }
@@ -809,6 +801,34 @@ int splitsFor(int K, int tiles) {
 constexpr int kBiasSplits = 64;
 
 }  // namespace
+
+}  // namespace gru
+
+namespace wgrad {
+
+int plan(int K, int N, int sms, int *chunkK) {
+    const int nTiles = (N + gru::kWgCols - 1) / gru::kWgCols;
+    int splits = std::max(1, std::min((2 * sms + 2 * nTiles - 1) / (2 * nTiles), (K + 255) / 256));
+    *chunkK = ((K + splits - 1) / splits + gru::kWgChunk - 1) / gru::kWgChunk * gru::kWgChunk;
+    return (K + *chunkK - 1) / *chunkK;
+}
+
+void launch(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+    const int mt = (prob.M + 1 + 15) / 16;
+    const dim3 grid((N + gru::kWgCols - 1) / gru::kWgCols, splits);
+    KernelTimer timer__("weightGradMma", st);
+    switch (mt) {
+#define RXMET_WG_CASE(MTV) case MTV: gru::weightGradMma<MTV><<<grid, 256, 0, st>>>(prob, K, N, chunkK); break;
+        RXMET_WG_CASE(1) RXMET_WG_CASE(2) RXMET_WG_CASE(3) RXMET_WG_CASE(4) RXMET_WG_CASE(5)
+        RXMET_WG_CASE(6) RXMET_WG_CASE(7) RXMET_WG_CASE(8) RXMET_WG_CASE(9)
+#undef RXMET_WG_CASE
+        default: fail(RXMET_ERR_UNSUPPORTED, "weight gradient tile count %d", mt);
+    }
+}
+
+}  // namespace wgrad
+
+namespace gru {
 
 size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     const size_t rows = static_cast<size_t>(T) * B, C = 3 * static_cast<size_t>(H);
@@ -985,18 +1005,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         px.partial = ws.take<float>(static_cast<size_t>(splits) * (I + 1) * C);
         ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
         ph.partial = ws.take<float>(static_cast<size_t>(splits) * (H + 1) * C);
-        auto launchWg = [&](const WeightGradProblem &prob) {
-            const int mt = (prob.M + 1 + 15) / 16;
-            const dim3 grid(nTiles, splits);
-            KernelTimer timer__("weightGradMma", st);
-            switch (mt) {
-#define RXMET_WG_CASE(MTV) case MTV: weightGradMma<MTV><<<grid, 256, 0, st>>>(prob, K, C, chunkK); break;
-                RXMET_WG_CASE(1) RXMET_WG_CASE(2) RXMET_WG_CASE(3) RXMET_WG_CASE(4) RXMET_WG_CASE(5)
-                RXMET_WG_CASE(6) RXMET_WG_CASE(7) RXMET_WG_CASE(8) RXMET_WG_CASE(9)
-#undef RXMET_WG_CASE
-                default: fail(RXMET_ERR_UNSUPPORTED, "weight gradient tile count %d", mt);
-            }
-        };
+        auto launchWg = [&](const WeightGradProblem &prob) { wgrad::launch(prob, K, C, chunkK, splits, st); };
         launchWg(px);
         afterLaunch("weightGradMma");
         launchWg(ph);

@@ -6,7 +6,7 @@
 //   recurrentBackward  : ONE launch for all T steps; a CTA owns BT batch rows, walks t = T-1..0,
 //                        keeps dc in registers and dh in shared memory, writes the masked gate
 //                        gradients of both linear branches, and propagates dh through weight_hh
-//                        (rows resident in shared memory as far as they fit, the rest from L2)
+//                        (rows resident in shared memory as far as they fit, the rest in registers)
 //   gemmRowsTN + reduce: dW_ih = G_ih^T x, dW_hh = G_hh^T h_prev as split-K tile GEMMs over the T*B
 //                        rows with fixed-order reduction (bit-reproducible), masks applied there
 //   gemmNN             : dx = G_ih W_ih with the input clamp mask
@@ -19,6 +19,7 @@
 
 #include "common.h"
 #include "lstm_kernels.h"
+#include "weight_grad_mma.h"
 
 namespace rxmet {
 namespace lstm {
@@ -35,8 +36,29 @@ __global__ void dequantWeights(const float *__restrict__ codes, const float *__r
         out[i] = codes[i] * channelScale[i / cols];
 }
 
+// One word of keep/drop flags per (t, b, j): bit 0 hidden, 1 tanh(cell), 2 cell, 3-6 gate outputs,
+// 7-10 gate inputs, 11-14 ih linear, 15-18 hh linear (a set bit = clamped = no gradient).  Packing them
+// once in a bandwidth-bound pass takes 19 byte loads per element off every step of the recurrence.
+__global__ void packStepMasks(const rxmet_lstm_backward_masks mk, size_t rows, int H, uint32_t *__restrict__ out) {
+    const size_t n = rows * H;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / H, j = i % H, go = row * 4 * H + j;
+        auto bit = [](const uint8_t *m, size_t idx) -> uint32_t { return (m != nullptr && m[idx] != 0) ? 1u : 0u; };
+        uint32_t w = bit(mk.hidden_outputs, i) | (bit(mk.cell_tanh_outputs, i) << 1) | (bit(mk.cell_states, i) << 2);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const size_t o = go + static_cast<size_t>(g) * H;
+            w |= (bit(mk.gate_outputs, o) << (3 + g)) | (bit(mk.gate_inputs, o) << (7 + g)) |
+                 (bit(mk.weight_ih_linear, o) << (11 + g)) | (bit(mk.weight_hh_linear, o) << (15 + g));
+        }
+        out[i] = w;
+    }
+}
+
 struct RecurrentArgs {
-    int T, B, H, smemRows;
+    int T, B, H, smemRows;  // smemRows: leading rows of each gate block held in shared memory
+    const uint32_t *stepMasks;  // packed flags [T][B][H] or null
     const float *weightHh;  // real [4H][H]
     const float *c0;
     const float *gateOutputs, *cellStates, *cellTanh;
@@ -47,16 +69,24 @@ struct RecurrentArgs {
     float *dh0, *dc0;  // [B][H] (masks applied)
 };
 
+// Rows of weight_hh that do not fit shared memory are kept in registers: thread (q, j) owns column j
+// of the rows of gate q, the first smemRows of them in shared memory and up to kRegRows after that
+// in registers, so that a step never goes to L2 for weights.
+constexpr int kRegRows = 32;
+
 template <int BT>
 __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__ RecurrentArgs a) {
-    const int H = a.H, C = 4 * a.H;
-    extern __shared__ float smemF[];
-    float *gS = smemF;             // [BT][C] gradient entering the hh branch
-    float *partS = gS + BT * C;    // [4][BT][H] partial sums of dh
-    float *wS = partS + 4 * BT * H;  // [smemRows][H] rows of weight_hh
+    const int H = a.H, C = 4 * a.H, S = a.smemRows, R = H - S;
+    extern __shared__ __align__(16) float smemF[];
+    float *gS = smemF;               // [BT][C] gradient entering the hh branch
+    float *partS = gS + BT * C;      // [4][BT][H] partial sums of dh
+    float *wS = partS + 4 * BT * H;  // [4][S][H] leading rows of each gate block of weight_hh
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
-    for (int i = tid; i < a.smemRows * H; i += nthreads) wS[i] = a.weightHh[i];
+    for (int i = tid; i < 4 * S * H; i += nthreads) {
+        const int g = i / (S * H), r = (i / H) % S, j = i % H;
+        wS[i] = a.weightHh[(static_cast<size_t>(g) * H + r) * H + j];
+    }
     for (int i = tid; i < 4 * BT * H; i += nthreads) partS[i] = 0.0f;
     for (int i = tid; i < BT * C; i += nthreads) gS[i] = 0.0f;
 
@@ -66,54 +96,112 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
     const size_t stateIdx = static_cast<size_t>(b0 + eb) * H + ej;
     float dhCarry = hasElem ? a.gradFinalHidden[stateIdx] : 0.0f;
     float dc = hasElem ? a.gradFinalCell[stateIdx] : 0.0f;
-    // phase A ownership: quarter q of the channels, hidden column j
+    // phase A ownership: gate block q of the channels, hidden column j
     const bool hasColumn = tid < C;
-    const int q = tid / H, cj = tid % H;
+    const int q = hasColumn ? tid / H : 0, cj = tid % H;
+    float wr[kRegRows];
+#pragma unroll
+    for (int r = 0; r < kRegRows; ++r)
+        wr[r] = (hasColumn && r < R) ? a.weightHh[(static_cast<size_t>(q) * H + S + r) * H + cj] : 0.0f;
+    const bool vec = (H % 4 == 0) && (S % 4 == 0);
     __syncthreads();
+
+    // inputs of one step for this thread's element, fetched one step ahead of their use
+    struct StepIn {
+        float gate[4], ct, cPrev, gradOut;
+        uint32_t bits;
+    };
+    auto fetch = [&](int t, StepIn &in) {
+        if (!hasElem) return;
+        const size_t row = static_cast<size_t>(t) * a.B + b0 + eb, so = row * H + ej, go = row * C + ej;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) in.gate[g] = a.gateOutputs[go + static_cast<size_t>(g) * H];
+        in.ct = a.cellTanh[so];
+        in.cPrev = t > 0 ? a.cellStates[so - static_cast<size_t>(a.B) * H] : (a.c0 ? a.c0[stateIdx] : a.dqC.zeroPoint);
+        in.gradOut = a.gradOutput[so];
+        in.bits = a.stepMasks ? a.stepMasks[so] : 0u;
+    };
+    StepIn cur{}, nxt{};
+    fetch(a.T - 1, cur);
 
     for (int t = a.T - 1; t >= 0; --t) {
         const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        if (t > 0) fetch(t - 1, nxt);
         if (hasElem) {
-            const size_t row = rowBase + eb, so = row * H + ej, go = row * C + ej;
-            const float ig = realOf(a.gateOutputs[go], a.dqGate[0]), fg = realOf(a.gateOutputs[go + H], a.dqGate[1]);
-            const float cg = realOf(a.gateOutputs[go + 2 * H], a.dqGate[2]), og = realOf(a.gateOutputs[go + 3 * H], a.dqGate[3]);
-            const float ct = realOf(a.cellTanh[so], a.dqTanh);
-            float cPrev = 0.0f;
-            if (t > 0) cPrev = realOf(a.cellStates[so - static_cast<size_t>(a.B) * H], a.dqC);
-            else if (a.c0) cPrev = realOf(a.c0[stateIdx], a.dqC);
+            const size_t row = rowBase + eb, go = row * C + ej;
+            auto keepBit = [&](int b) { return (cur.bits >> b) & 1u ? 0.0f : 1.0f; };
+            const float ig = realOf(cur.gate[0], a.dqGate[0]), fg = realOf(cur.gate[1], a.dqGate[1]);
+            const float cg = realOf(cur.gate[2], a.dqGate[2]), og = realOf(cur.gate[3], a.dqGate[3]);
+            const float ct = realOf(cur.ct, a.dqTanh);
+            const float cPrev = realOf(cur.cPrev, a.dqC);
             const float incoming = dhCarry + partS[(0 * BT + eb) * H + ej] + partS[(1 * BT + eb) * H + ej] +
                                    partS[(2 * BT + eb) * H + ej] + partS[(3 * BT + eb) * H + ej];
-            const float dh = (incoming + a.gradOutput[so]) * keepOf(a.mk.hidden_outputs, so);
+            const float dh = (incoming + cur.gradOut) * keepBit(0);
             const float gOut = dh * ct;
-            const float gTanh = dh * og * keepOf(a.mk.cell_tanh_outputs, so);
+            const float gTanh = dh * og * keepBit(1);
             const float dcAll = dc + gTanh * (1.0f - ct * ct);
-            const float mdc = dcAll * keepOf(a.mk.cell_states, so);
-            const float go4[4] = {mdc * cg * keepOf(a.mk.gate_outputs, go), mdc * cPrev * keepOf(a.mk.gate_outputs, go + H),
-                                  mdc * ig * keepOf(a.mk.gate_outputs, go + 2 * H), gOut * keepOf(a.mk.gate_outputs, go + 3 * H)};
+            const float mdc = dcAll * keepBit(2);
+            const float go4[4] = {mdc * cg * keepBit(3), mdc * cPrev * keepBit(4), mdc * ig * keepBit(5), gOut * keepBit(6)};
             const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
                                   go4[3] * og * (1.0f - og)};
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const size_t o = go + static_cast<size_t>(g) * H;
-                const float grad = gi4[g] * keepOf(a.mk.gate_inputs, o);
-                const float hh = grad * keepOf(a.mk.weight_hh_linear, o);
-                a.gIh[o] = grad * keepOf(a.mk.weight_ih_linear, o);
+                const float grad = gi4[g] * keepBit(7 + g);
+                const float hh = grad * keepBit(15 + g);
+                a.gIh[o] = grad * keepBit(11 + g);
                 a.gHh[o] = hh;
                 gS[eb * C + g * H + ej] = hh;
             }
             dc = mdc * fg;
             dhCarry = 0.0f;
         }
+        cur = nxt;
         __syncthreads();
         if (hasColumn) {
             float acc[BT];
 #pragma unroll
             for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
-            const int cBegin = q * H, cEnd = cBegin + H;
-            for (int c = cBegin; c < cEnd; ++c) {
-                const float w = c < a.smemRows ? wS[c * H + cj] : a.weightHh[static_cast<size_t>(c) * H + cj];
+            const float *wq = wS + static_cast<size_t>(q) * S * H + cj;
+            const float *gq = gS + q * H;
+            if (vec) {
+                for (int r = 0; r < S; r += 4) {
+                    const float w0 = wq[r * H], w1 = wq[(r + 1) * H], w2 = wq[(r + 2) * H], w3 = wq[(r + 3) * H];
 #pragma unroll
-                for (int b = 0; b < BT; ++b) acc[b] = fmaf(gS[b * C + c], w, acc[b]);
+                    for (int b = 0; b < BT; ++b) {
+                        const float4 gv = *reinterpret_cast<const float4 *>(gq + b * C + r);
+                        acc[b] = fmaf(gv.x, w0, acc[b]);
+                        acc[b] = fmaf(gv.y, w1, acc[b]);
+                        acc[b] = fmaf(gv.z, w2, acc[b]);
+                        acc[b] = fmaf(gv.w, w3, acc[b]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kRegRows; r += 4) {
+                    if (r < R) {
+#pragma unroll
+                        for (int b = 0; b < BT; ++b) {
+                            const float4 gv = *reinterpret_cast<const float4 *>(gq + b * C + S + r);
+                            acc[b] = fmaf(gv.x, wr[r], acc[b]);
+                            acc[b] = fmaf(gv.y, wr[r + 1], acc[b]);
+                            acc[b] = fmaf(gv.z, wr[r + 2], acc[b]);
+                            acc[b] = fmaf(gv.w, wr[r + 3], acc[b]);
+                        }
+                    }
+                }
+            } else {
+                for (int r = 0; r < S; ++r) {
+                    const float w = wq[r * H];
+#pragma unroll
+                    for (int b = 0; b < BT; ++b) acc[b] = fmaf(gq[b * C + r], w, acc[b]);
+                }
+#pragma unroll
+                for (int r = 0; r < kRegRows; ++r) {
+                    if (r < R) {
+#pragma unroll
+                        for (int b = 0; b < BT; ++b) acc[b] = fmaf(gq[b * C + S + r], wr[r], acc[b]);
+                    }
+                }
             }
 #pragma unroll
             for (int b = 0; b < BT; ++b) partS[(q * BT + b) * H + cj] = acc[b];
@@ -231,6 +319,35 @@ __global__ void __launch_bounds__(256) gemmNN(const float *__restrict__ A, const
         }
 }
 
+// weight[c][m] = scale * keep * sum_s partial[s][m][c] (m < M); bias[c] = keep * sum_s partial[s][M][c]:
+// reduces the split-K partials of the tensor-core GEMM and writes the transposed [4H][M] layout.
+__global__ void reduceWeightGradT(const float *__restrict__ partial, int splits, int M, int C, float scale,
+                                  const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
+                                  float *__restrict__ weight, float *__restrict__ bias) {
+    __shared__ float tile[32][33];
+    const size_t slab = static_cast<size_t>(M + 1) * C;
+    const int c0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        const int m = m0 + dy, c = c0 + threadIdx.x;
+        float s = 0.0f;
+        if (m <= M && c < C)
+            for (int sp = 0; sp < splits; ++sp) s += partial[static_cast<size_t>(sp) * slab + static_cast<size_t>(m) * C + c];
+        tile[dy][threadIdx.x] = s;
+    }
+    __syncthreads();
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        const int c = c0 + dy, m = m0 + threadIdx.x;
+        if (c >= C) continue;
+        const float s = tile[threadIdx.x][dy];
+        if (m < M) {
+            const size_t o = static_cast<size_t>(c) * M + m;
+            weight[o] = s * scale * keepOf(weightMask, o);
+        } else if (m == M && bias) {
+            bias[c] = s * keepOf(biasMask, c);
+        }
+    }
+}
+
 // partial[which][s][c] = sum over the s-th chunk of rows of g[n][c]; blockIdx.y selects G_ih or G_hh.
 __global__ void columnSums(const float *__restrict__ gIh, const float *__restrict__ gHh, int rows, int C, int chunk,
                            float *__restrict__ partial) {
@@ -252,6 +369,7 @@ int splitsFor(int K, int tiles) {
 int tilesOf(int M, int N) { return ((M + kTile - 1) / kTile) * ((N + kTile - 1) / kTile); }
 
 constexpr int kBiasSplits = 64;
+constexpr int kMaxTensorSplits = 8;
 
 }  // namespace
 
@@ -266,6 +384,10 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(static_cast<size_t>(splitsFor(static_cast<int>(rows), tilesOf(static_cast<int>(C), H))) * C * H);
     ws.take<float>(2 * kBiasSplits * C);
     ws.take<float>(2 * C);     // per-channel weight scales (QAT)
+    ws.take<float>(rows * H);  // h_prev codes for the tensor-core weight gradient (QAT)
+    ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (I + 1) * C);
+    ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (H + 1) * C);
+    ws.take<uint32_t>(rows * H);  // packed per-step clamp flags
     return ws.used() + 1024;
 }
 
@@ -284,6 +406,10 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     float *partHh = ws.take<float>(static_cast<size_t>(splitHh) * C * H);
     float *partBias = ws.take<float>(2 * kBiasSplits * static_cast<size_t>(C));
     float *channelScales = ws.take<float>(2 * static_cast<size_t>(C));
+    float *hPrev = ws.take<float>(rows * H);
+    float *tensorIh = ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (I + 1) * C);
+    float *tensorHh = ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (H + 1) * C);
+    uint32_t *stepMasks = ws.take<uint32_t>(rows * H);
 
     const float *wIh = call.weightIh, *wHh = call.weightHh;
     if (call.quantized) {
@@ -305,9 +431,19 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     }
     const rxmet_lstm_backward_masks none{};
     const rxmet_lstm_backward_masks &mk = call.masks ? *call.masks : none;
+    const bool anyStepMask = mk.hidden_outputs || mk.cell_tanh_outputs || mk.cell_states || mk.gate_outputs ||
+                             mk.gate_inputs || mk.weight_ih_linear || mk.weight_hh_linear;
+    if (anyStepMask) {
+        {
+            KernelTimer timer__("lstmPackStepMasks", st);
+            packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk, rows, H, stepMasks);
+        }
+        afterLaunch("lstmPackStepMasks");
+    }
     {
         RecurrentArgs a{};
         a.T = T; a.B = B; a.H = H;
+        a.stepMasks = anyStepMask ? stepMasks : nullptr;
         a.weightHh = wHh; a.c0 = call.c0;
         a.gateOutputs = call.gateOutputs; a.cellStates = call.cellStates; a.cellTanh = call.cellTanhOutputs;
         a.gradOutput = call.gradOutput; a.gradFinalHidden = call.gradFinalHidden; a.gradFinalCell = call.gradFinalCell;
@@ -323,8 +459,13 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         auto launch = [&](auto kernel, int BT) {
             const size_t base = sizeof(float) * (static_cast<size_t>(BT) * C + 4 * static_cast<size_t>(BT) * H);
             const size_t room = static_cast<size_t>(smemMax) > base + 1024 ? static_cast<size_t>(smemMax) - base - 1024 : 0;
-            a.smemRows = static_cast<int>(std::min<size_t>(C, room / (sizeof(float) * H)));
-            const size_t smem = base + sizeof(float) * static_cast<size_t>(a.smemRows) * H;
+            // rows per gate block in shared memory; the remaining rows of a block live in registers
+            int perGate = static_cast<int>(std::min<size_t>(H, room / (sizeof(float) * 4 * H)));
+            if (perGate < H) perGate = perGate / 4 * 4;
+            if (H - perGate > kRegRows)
+                fail(RXMET_ERR_UNSUPPORTED, "hidden size %d leaves %d weight rows per gate outside shared memory and registers", H, H - perGate);
+            a.smemRows = perGate;
+            const size_t smem = base + sizeof(float) * 4 * static_cast<size_t>(perGate) * H;
             RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             {
                 KernelTimer timer__("lstmRecurrentBackward", st);
@@ -342,6 +483,46 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             gIh, wIh, static_cast<int>(rows), I, C, static_cast<const uint8_t *>(mk.input), call.grads.input);
     }
     afterLaunch("lstmGemmNN");
+    // QAT on 8-bit activation grids: x and h_prev are integer codes, which the tensor-core GEMM
+    // multiplies exactly; its ones row also yields the bias gradients.
+    if (call.quantized && call.codesFitTensorPath && I % 4 == 0 && H % 4 == 0 && I <= 140 && H <= 140) {
+        const size_t stateBytes = sizeof(float) * static_cast<size_t>(B) * H;
+        if (call.h0) RXMET_CUDA(cudaMemcpyAsync(hPrev, call.h0, stateBytes, cudaMemcpyDeviceToDevice, st));
+        else RXMET_CUDA(cudaMemsetAsync(hPrev, 0, stateBytes, st));
+        if (T > 1)
+            RXMET_CUDA(cudaMemcpyAsync(hPrev + static_cast<size_t>(B) * H, call.hiddenOutputs, stateBytes * (T - 1),
+                                       cudaMemcpyDeviceToDevice, st));
+        int device = 0, sms = 0, chunkK = 0;
+        RXMET_CUDA(cudaGetDevice(&device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        int splits = wgrad::plan(static_cast<int>(rows), C, sms, &chunkK);
+        if (splits > kMaxTensorSplits) {
+            splits = kMaxTensorSplits;
+            chunkK = ((static_cast<int>(rows) + splits - 1) / splits + 31) / 32 * 32;
+            splits = (static_cast<int>(rows) + chunkK - 1) / chunkK;
+        }
+        wgrad::Problem px{}, ph{};
+        px.aFloat = call.x; px.aFloatZero = call.dqX.zeroPoint; px.M = I; px.B = gIh; px.partial = tensorIh;
+        ph.aFloat = hPrev; ph.aFloatZero = call.h0 ? call.dqH.zeroPoint : 0.0f; ph.M = H; ph.B = gHh; ph.partial = tensorHh;
+        if (!call.h0 && call.dqH.zeroPoint != 0.0f) {
+            // a missing h0 means real zeros, i.e. the zero-point code: fill instead of zeroing
+            fail(RXMET_ERR_INVALID_ARGUMENT, "the QAT backward needs the quantized initial hidden state");
+        }
+        wgrad::launch(px, static_cast<int>(rows), C, chunkK, splits, st);
+        afterLaunch("weightGradMma");
+        wgrad::launch(ph, static_cast<int>(rows), C, chunkK, splits, st);
+        afterLaunch("weightGradMma");
+        auto reduce = [&](const float *partial, int M, float scale, const uint8_t *wm, const uint8_t *bm, float *w, float *b) {
+            {
+                KernelTimer timer__("lstmReduceWeightGradT", st);
+                reduceWeightGradT<<<dim3((C + 31) / 32, (M + 1 + 31) / 32), dim3(32, 8), 0, st>>>(partial, splits, M, C, scale, wm, bm, w, b);
+            }
+            afterLaunch("lstmReduceWeightGradT");
+        };
+        reduce(tensorIh, I, call.dqX.scale, mk.weight_ih, mk.bias_ih, call.grads.weight_ih, call.grads.bias_ih);
+        reduce(tensorHh, H, call.dqH.scale, mk.weight_hh, mk.bias_hh, call.grads.weight_hh, call.grads.bias_hh);
+        return;
+    }
     auto weightGrad = [&](const float *G, RowSource X, int N, int splits, float *partial, const uint8_t *mask, float *out) {
         const int chunk = ((static_cast<int>(rows) + splits - 1) / splits + kDepth - 1) / kDepth * kDepth;
         {

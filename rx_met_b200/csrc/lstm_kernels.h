@@ -47,6 +47,7 @@ struct BackwardCall {
     bool quantized = false;
     Dequant dqX, dqH, dqC, dqGate[4], dqTanh;
     const float *weightIhScale = nullptr, *weightHhScale = nullptr;
+    bool codesFitTensorPath = false;  // x and hidden grids span at most 256 codes around their zero points
 };
 size_t backwardWorkspaceBytes(int T, int B, int I, int H);
 void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
