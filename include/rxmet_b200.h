@@ -173,7 +173,7 @@ RXMET_API int rxmet_gru_decode_effective_scale(float scale, int use_pot2, float 
 
 /* Bytes of device scratch the entry point named by `op` needs for these
  * sizes.  op: 0 forward_fp / forward_calibrate, 1 forward_quant,
- * 2 backward_quant / backward_fp. */
+ * 2 backward_quant / backward_fp, 3 forward_calibrate with histograms. */
 RXMET_API size_t rxmet_gru_workspace_bytes(int op, int T, int B, int I, int H);
 
 /* Float GRU forward.  Replaces forward_fp -> gru::ForwardPass<float>::Run
@@ -217,6 +217,73 @@ RXMET_API int rxmet_gru_forward_calibrate_stats(int T, int B, int I, int H,
                                                 void *stream);
 /* Folds packed statistics (host copy of stats_dev) into *ranges. */
 RXMET_API int rxmet_gru_ranges_fold_stats(rxmet_gru_ranges *ranges, const float *stats_host);
+
+/* ---- histogram calibration (SQNR / percentile) ---------------------------- */
+
+/* One histogram collector (HistogramCollector + Histogram,
+ * operators/quant-gru/include/histogram_collector.h:44-164,166-420): float counts
+ * over [min_val, max_val], the observed extremes and the growth limits.  counts
+ * is a host array of num_bins floats owned by the caller. */
+typedef struct rxmet_histogram {
+    float *counts;
+    int32_t num_bins;
+    float min_val, max_val;
+    float observed_min, observed_max;
+    int64_t total_count;
+    int32_t range_limit_set;
+    float range_limit_min, range_limit_max;
+} rxmet_histogram;
+
+/* Empties a collector (HistogramCollector::reset, histogram_collector.h:283-288).
+ * counts and num_bins must be set. */
+RXMET_API int rxmet_histogram_reset(rxmet_histogram *hist);
+/* Adds host data (HistogramCollector::collect, histogram_collector.h:185-247):
+ * first batch fixes the range, later batches extend it and redistribute the
+ * existing counts (AIMET merge_stats rule). */
+RXMET_API int rxmet_histogram_collect_host(rxmet_histogram *hist, const float *data_host, uint64_t count);
+/* Same for a device tensor of `rows` rows of `cols` contiguous floats, rows
+ * `row_stride` floats apart: min/max and the binning run on the device, the merge
+ * on the host.  Synchronises the stream.  Workspace: rxmet_histogram_workspace_bytes. */
+RXMET_API size_t rxmet_histogram_workspace_bytes(int num_bins);
+RXMET_API int rxmet_histogram_collect_dev(rxmet_histogram *hist, const float *data_dev, uint64_t rows, uint64_t cols,
+                                          uint64_t row_stride, void *workspace_dev, size_t workspace_bytes,
+                                          void *stream);
+/* Merges another collector's histogram (HistogramCollector::merge, :248-282). */
+RXMET_API int rxmet_histogram_merge(rxmet_histogram *hist, const rxmet_histogram *other);
+/* Continuous scale and covered range from a histogram
+ * (calibrateContinuousScaleFromHistogram, operators/quant-gru/include/
+ * pot_sqnr_calibrator.h:340-358: SQNR search :118-338 or percentile :19-107). */
+RXMET_API int rxmet_histogram_calibrate(const rxmet_histogram *hist, int bits, int is_unsigned, int symmetric,
+                                        int use_percentile, float percentile, float *scale, float *range_min,
+                                        float *range_max);
+
+/* All collectors of one GRU direction (GRUHistogramCollectors,
+ * histogram_collector.h:609-720): one per activation point (the W, R, bw, br
+ * entries of `point` are the per-tensor collectors), 3*hidden per-channel
+ * collectors and three per-gate collectors for each of W, R, bw, br. */
+typedef struct rxmet_gru_histograms {
+    int32_t hidden;
+    int32_t num_bins;
+    rxmet_histogram point[RXMET_GRU_NUM_OPS];
+    rxmet_histogram *channel[4]; /* host arrays of 3*hidden collectors: W, R, bw, br */
+    rxmet_histogram gate[4][3];
+} rxmet_gru_histograms;
+
+/* Float forward that feeds every collector (forwardWithCalibrationGPU with
+ * calib_method sqnr / percentile, operators/quant-gru/src/gru_interface.cc:936-1024;
+ * what is observed: src/gru_forward_cpu.cc:118-151).  Workspace:
+ * rxmet_gru_workspace_bytes(3, ...).  Synchronises the stream. */
+RXMET_API int rxmet_gru_forward_calibrate_hist(int T, int B, int I, int H, const float *W_dev, const float *R_dev,
+                                               const float *bw_dev, const float *br_dev, const float *x_dev,
+                                               const float *h0_dev, float *h_dev, float *v_dev,
+                                               const rxmet_gru_quant_config *config, rxmet_gru_histograms *hists,
+                                               void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* Histograms -> encodings (calculateGRUQuantitativeParametersFromHistograms,
+ * operators/quant-gru/src/gru_host.cc:254-335).  The four scale arrays of *params
+ * must point to 3*hidden floats each. */
+RXMET_API int rxmet_gru_params_from_histograms(const rxmet_gru_histograms *hists, const rxmet_gru_quant_config *config,
+                                               int use_percentile, float percentile, rxmet_gru_quant_params *params);
 
 /* The 11 clamp masks of a training forward (1 = kept, 0 = clamped;
  * operators/quant-gru/include/quantize_ops_helper.h:272-276), in the order

@@ -18,6 +18,8 @@
 #include "gru_host.h"          // reference: calculateGRUQuantitativeParameters, forwardWithCalibrationCPU, ...
 #include "gru_quant_cpu.h"     // reference: cpu::ForwardPassQuantCPU
 #include "scale_encoding.h"    // reference: toFixedScale, encodeMShift
+#include "histogram_collector.h"   // reference: HistogramCollector, GRUHistogramCollectors
+#include "pot_sqnr_calibrator.h"   // reference: calibrateContinuousScaleFromHistogram
 #include "rxmet_b200.h"
 
 namespace {
@@ -165,6 +167,82 @@ void fromRefParams(const GRUQuantParams &r, rxmet_gru_quant_params *p) {
     }
 }
 
+// Collector <-> flat struct.  The growth limits of a reference collector are private; with the
+// reference's infinite growth limit they never constrain anything, so a collector rebuilt from its
+// histogram alone behaves identically.
+HistogramCollector toRefCollector(const rxmet_histogram &s) {
+    HistogramCollector c(s.num_bins);
+    if (s.num_bins > 0 && s.total_count > 0) {
+        Histogram &h = c.histogram();
+        h.counts.assign(s.counts, s.counts + s.num_bins);
+        h.min_val = s.min_val;
+        h.max_val = s.max_val;
+        h.observed_min = s.observed_min;
+        h.observed_max = s.observed_max;
+        h.num_bins = s.num_bins;
+        h.total_count = s.total_count;
+    }
+    return c;
+}
+
+void fromRefCollector(const HistogramCollector &c, rxmet_histogram *s) {
+    const Histogram &h = c.histogram();
+    if (!c.is_valid()) return;
+    std::copy(h.counts.begin(), h.counts.end(), s->counts);
+    s->min_val = h.min_val;
+    s->max_val = h.max_val;
+    s->observed_min = h.observed_min;
+    s->observed_max = h.observed_max;
+    s->total_count = h.total_count;
+}
+
+HistogramCollector *pointCollector(GRUHistogramCollectors &g, int op) {
+    switch (op) {
+        case RXMET_GRU_X: return &g.x_hist;
+        case RXMET_GRU_H: return &g.h_hist;
+        case RXMET_GRU_W: return &g.W_tensor_hist;
+        case RXMET_GRU_R: return &g.R_tensor_hist;
+        case RXMET_GRU_BW: return &g.bw_tensor_hist;
+        case RXMET_GRU_BR: return &g.br_tensor_hist;
+        case RXMET_GRU_WEIGHT_IH_LINEAR: return &g.Wx_hist;
+        case RXMET_GRU_WEIGHT_HH_LINEAR: return &g.Rh_hist;
+        case RXMET_GRU_UPDATE_GATE_INPUT: return &g.update_gate_input_hist;
+        case RXMET_GRU_UPDATE_GATE_OUTPUT: return &g.update_gate_output_hist;
+        case RXMET_GRU_RESET_GATE_INPUT: return &g.reset_gate_input_hist;
+        case RXMET_GRU_RESET_GATE_OUTPUT: return &g.reset_gate_output_hist;
+        case RXMET_GRU_NEW_GATE_INPUT: return &g.new_gate_input_hist;
+        case RXMET_GRU_NEW_GATE_OUTPUT: return &g.new_gate_output_hist;
+        case RXMET_GRU_MUL_RESET_HIDDEN: return &g.mul_reset_hidden_hist;
+        case RXMET_GRU_MUL_OLD_CONTRIBUTION: return &g.mul_old_contribution_hist;
+        default: return &g.mul_new_contribution_hist;
+    }
+}
+
+std::vector<HistogramCollector> *channelCollectors(GRUHistogramCollectors &g, int slot) {
+    return slot == 0 ? &g.W_hist : (slot == 1 ? &g.R_hist : (slot == 2 ? &g.bw_hist : &g.br_hist));
+}
+std::array<HistogramCollector, 3> *gateCollectors(GRUHistogramCollectors &g, int slot) {
+    return slot == 0 ? &g.W_gate_hist : (slot == 1 ? &g.R_gate_hist : (slot == 2 ? &g.bw_gate_hist : &g.br_gate_hist));
+}
+
+GRUHistogramCollectors toRefHists(const rxmet_gru_histograms &s) {
+    GRUHistogramCollectors g(s.hidden, s.num_bins);
+    for (int op = 0; op < RXMET_GRU_NUM_OPS; ++op) *pointCollector(g, op) = toRefCollector(s.point[op]);
+    for (int slot = 0; slot < 4; ++slot) {
+        for (int c = 0; c < 3 * s.hidden; ++c) (*channelCollectors(g, slot))[c] = toRefCollector(s.channel[slot][c]);
+        for (int k = 0; k < 3; ++k) (*gateCollectors(g, slot))[k] = toRefCollector(s.gate[slot][k]);
+    }
+    return g;
+}
+
+void fromRefHists(GRUHistogramCollectors &g, rxmet_gru_histograms *s) {
+    for (int op = 0; op < RXMET_GRU_NUM_OPS; ++op) fromRefCollector(*pointCollector(g, op), &s->point[op]);
+    for (int slot = 0; slot < 4; ++slot) {
+        for (int c = 0; c < 3 * s->hidden; ++c) fromRefCollector((*channelCollectors(g, slot))[c], &s->channel[slot][c]);
+        for (int k = 0; k < 3; ++k) fromRefCollector((*gateCollectors(g, slot))[k], &s->gate[slot][k]);
+    }
+}
+
 template <class F>
 int guarded(F &&f) {
     try {
@@ -259,6 +337,60 @@ int ref_gru_forward_calibrate_minmax(int T, int B, int I, int H,
         forwardWithCalibrationCPU(T, B, I, H, W, R, bw, br, x, h0, CalibrationMethod::MINMAX, &r, nullptr,
                                   toRefConfig(*cfg), h, v);
         fromRefRanges(r, ranges);
+    });
+}
+
+// ---- histogram calibration ------------------------------------------------------
+
+int ref_histogram_collect_host(rxmet_histogram *hist, const float *data, uint64_t count) {
+    return guarded([&] {
+        HistogramCollector c = toRefCollector(*hist);
+        c.collect(data, count);
+        fromRefCollector(c, hist);
+    });
+}
+
+int ref_histogram_merge(rxmet_histogram *hist, const rxmet_histogram *other) {
+    return guarded([&] {
+        HistogramCollector c = toRefCollector(*hist);
+        c.merge(toRefCollector(*other).histogram());
+        fromRefCollector(c, hist);
+    });
+}
+
+int ref_histogram_calibrate(const rxmet_histogram *hist, int bits, int is_unsigned, int symmetric, int use_percentile,
+                            float percentile, float *scale, float *range_min, float *range_max) {
+    return guarded([&] {
+        const HistogramCollector c = toRefCollector(*hist);
+        const ContinuousScaleResult r = calibrateContinuousScaleFromHistogram(
+            c.histogram(), QuantBitWidth(static_cast<int8_t>(bits), is_unsigned != 0), symmetric != 0, use_percentile != 0,
+            percentile);
+        *scale = r.scale;
+        *range_min = r.min;
+        *range_max = r.max;
+    });
+}
+
+// Float forward + histogram observation: forwardWithCalibrationCPU with SQNR (the collectors are
+// fed the same way for PERCENTILE).
+int ref_gru_forward_calibrate_hist(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
+                                   const float *br, const float *x, const float *h0, const rxmet_gru_quant_config *cfg,
+                                   rxmet_gru_histograms *hists, float *h, float *v) {
+    return guarded([&] {
+        GRUHistogramCollectors g = toRefHists(*hists);
+        forwardWithCalibrationCPU(T, B, I, H, W, R, bw, br, x, h0, CalibrationMethod::SQNR, nullptr, &g,
+                                  toRefConfig(*cfg), h, v);
+        fromRefHists(g, hists);
+    });
+}
+
+int ref_gru_params_from_histograms(const rxmet_gru_histograms *hists, const rxmet_gru_quant_config *cfg,
+                                   int use_percentile, float percentile, rxmet_gru_quant_params *out) {
+    return guarded([&] {
+        GRUHistogramCollectors g = toRefHists(*hists);
+        const GRUQuantParams p = calculateGRUQuantitativeParametersFromHistograms(g, toRefConfig(*cfg), use_percentile != 0,
+                                                                                 percentile);
+        fromRefParams(p, out);
     });
 }
 

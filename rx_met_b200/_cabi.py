@@ -86,6 +86,64 @@ class Masks(C.Structure):
 
 MASK_NAMES = tuple(n for n, _ in Masks._fields_)
 
+
+class Histogram(C.Structure):
+    """``rxmet_histogram``: one collector; ``counts`` points at host floats."""
+    _fields_ = [("counts", _f32p), ("num_bins", C.c_int32), ("min_val", C.c_float), ("max_val", C.c_float),
+                ("observed_min", C.c_float), ("observed_max", C.c_float), ("total_count", C.c_int64),
+                ("range_limit_set", C.c_int32), ("range_limit_min", C.c_float), ("range_limit_max", C.c_float)]
+
+
+class GruHistograms(C.Structure):
+    """``rxmet_gru_histograms``."""
+    _fields_ = [("hidden", C.c_int32), ("num_bins", C.c_int32), ("point", Histogram * NUM_OPS),
+                ("channel", C.POINTER(Histogram) * 4), ("gate", (Histogram * 3) * 4)]
+
+
+class HistogramSet:
+    """All collectors of one GRU direction with the storage their count pointers refer to:
+    17 point collectors, 4 x 3 gate collectors and 4 x 3*hidden channel collectors."""
+
+    def __init__(self, hidden: int, num_bins: int = 2048):
+        import numpy as np
+        self.hidden, self.num_bins = int(hidden), int(num_bins)
+        total = NUM_OPS + 12 + 12 * self.hidden
+        self.counts = np.zeros((total, self.num_bins), np.float32)
+        self.channels = [(Histogram * (3 * self.hidden))() for _ in range(4)]
+        self.c = GruHistograms()
+        self.c.hidden, self.c.num_bins = self.hidden, self.num_bins
+        row = 0
+        for h in self.all():
+            h.counts = self.counts[row].ctypes.data_as(_f32p)
+            h.num_bins = self.num_bins
+            row += 1
+        for k in range(4):
+            self.c.channel[k] = C.cast(self.channels[k], C.POINTER(Histogram))
+        self.reset()
+
+    def all(self):
+        for op in range(NUM_OPS):
+            yield self.c.point[op]
+        for k in range(4):
+            for g in range(3):
+                yield self.c.gate[k][g]
+        for k in range(4):
+            for ch in range(3 * self.hidden):
+                yield self.channels[k][ch]
+
+    def reset(self):
+        self.counts[:] = 0
+        fmax = 3.4028234663852886e38
+        for h in self.all():
+            h.min_val, h.max_val = fmax, -fmax
+            h.observed_min, h.observed_max = fmax, -fmax
+            h.total_count = 0
+            h.range_limit_set = 0
+            h.range_limit_min = h.range_limit_max = 0.0
+
+    def is_valid(self) -> bool:
+        return self.hidden > 0 and self.c.point[X].total_count > 0
+
 LIB_NAME = "librxmet_b200.so"
 
 

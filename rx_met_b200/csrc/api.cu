@@ -211,6 +211,7 @@ size_t rxmet_gru_workspace_bytes(int op, int T, int B, int I, int H) {
         case 0: return gru::forwardFloatWorkspaceBytes(T, B, I, H);
         case 1: return gru::forwardQuantWorkspaceBytes(T, B, I, H);
         case 2: return gru::backwardWorkspaceBytes(T, B, I, H);
+        case 3: return gru::histCalibrationWorkspaceBytes(T, B, I, H, 8192);
         default: return 0;
     }
 }

@@ -171,6 +171,7 @@ struct FloatRecurrentArgs {
     float *h;         // [T+1][B][H]
     float *v;         // [T][B][4H]
     float *mins, *maxs;  // packed statistics or null
+    float *trRh, *trPre, *trMul;  // optional [T][B][3H] traces
 };
 
 template <int BT>
@@ -214,7 +215,10 @@ __global__ void __launch_bounds__(768) recurrentFloat(const __grid_constant__ Fl
             for (int b = 0; b < BT; ++b) {
                 const float val = acc[b] + bias;
                 rhS[b * C + c] = val;
-                if (b < nb) st[1].see(val);
+                if (b < nb) {
+                    st[1].see(val);
+                    if (a.trRh) a.trRh[(rowBase + b) * C + c] = val;
+                }
             }
         }
         __syncthreads();
@@ -239,6 +243,11 @@ __global__ void __launch_bounds__(768) recurrentFloat(const __grid_constant__ Fl
             a.h[(row + a.B) * H + j] = hNew;
             float *vRow = a.v + row * 4 * H;
             vRow[j] = z; vRow[H + j] = r; vRow[2 * H + j] = n; vRow[3 * H + j] = rec;
+            if (a.trPre) {
+                float *pre = a.trPre + row * C, *mul = a.trMul + row * C;
+                pre[j] = zPre; pre[H + j] = rPre; pre[2 * H + j] = nPre;
+                mul[j] = rm; mul[H + j] = newC; mul[2 * H + j] = oldC;
+            }
             st[0].see(hNew); st[2].see(zPre); st[3].see(rPre); st[4].see(nPre);
             st[5].see(z); st[6].see(r); st[7].see(n); st[8].see(rm); st[9].see(newC); st[10].see(oldC);
         }
@@ -272,6 +281,7 @@ void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspac
     const size_t rows = static_cast<size_t>(T) * B;
     Workspace ws(workspace, workspaceBytes);
     float *wx = ws.take<float>(rows * C);
+    if (call.traceWx) wx = call.traceWx;
     float *mins = nullptr, *maxs = nullptr;
     const size_t half = statsFloats(H) / 2;
     if (call.stats) {
@@ -313,6 +323,8 @@ void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspac
     a.T = T; a.B = B; a.H = H;
     a.R = call.R; a.br = call.br; a.wx = wx; a.h0 = call.h0; a.h = call.h; a.v = call.v;
     a.mins = mins; a.maxs = maxs;
+    a.trRh = call.traceRh; a.trPre = call.tracePre; a.trMul = call.traceMul;
+    RXMET_REQUIRE((call.tracePre == nullptr) == (call.traceMul == nullptr), "pre-activation and product traces go together");
     int device = 0, smemMax = 0, sms = 0;
     RXMET_CUDA(cudaGetDevice(&device));
     RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));

@@ -19,11 +19,16 @@ struct ForwardFloatCall {
     const float *W = nullptr, *R = nullptr, *bw = nullptr, *br = nullptr, *x = nullptr, *h0 = nullptr;
     float *h = nullptr, *v = nullptr;
     float *stats = nullptr;
+    // optional per-step tensors for the histogram calibration, each [T,B,3H]:
+    // W x + bw; R h + br; (z, r, n) pre-activations; (r*(Rh)_n, (1-z)*n, z*h_old)
+    float *traceWx = nullptr, *traceRh = nullptr, *tracePre = nullptr, *traceMul = nullptr;
 };
 
 size_t statsFloats(int H);
 size_t forwardFloatWorkspaceBytes(int T, int B, int I, int H);
 void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
+// Scratch of the histogram calibration forward (float forward + four [T,B,3H] traces + bin counters).
+size_t histCalibrationWorkspaceBytes(int T, int B, int I, int H, int bins);
 
 }  // namespace gru
 }  // namespace rxmet

@@ -4,6 +4,7 @@
 // kernels produce; this file is therefore compiled without FMA contraction and
 // without fast-math.  Citations are <file under operators/quant-gru/>:<line>.
 #include "gru_params.h"
+#include "gru_histogram.h"
 
 #include <algorithm>
 #include <array>
@@ -164,8 +165,7 @@ struct Encoding {
 };
 
 // include/gru_calibration_helpers.h:16-27 -> include/scale_encoding.h:207-320
-Encoding encodeRange(float lo, float hi, Width w, bool symmetric, const rxmet_gru_quant_config &cfg) {
-    const Continuous c = continuousFromRange(lo, hi, w, symmetric);
+Encoding encodeContinuous(const Continuous &c, Width w, bool symmetric, const rxmet_gru_quant_config &cfg) {
     const float qlo = static_cast<float>(w.lo());
     if (cfg.use_pot2) {
         const auto [po2, n] = scaleToPowerOfTwo(c.scale, cfg.pot_scale_method, c.lo, c.hi, cfg.pot_scale_tolerance);
@@ -181,6 +181,10 @@ Encoding encodeRange(float lo, float hi, Width w, bool symmetric, const rxmet_gr
     const float effective = static_cast<float>(ms.mult) * std::ldexp(1.0f, -ms.shift);
     const int32_t zp = symmetric ? 0 : static_cast<int32_t>(std::rint(qlo - c.lo / effective));
     return {c.scale, zp};
+}
+
+Encoding encodeRange(float lo, float hi, Width w, bool symmetric, const rxmet_gru_quant_config &cfg) {
+    return encodeContinuous(continuousFromRange(lo, hi, w, symmetric), w, symmetric, cfg);
 }
 
 // Calls f(begin, end) for each scale group of a 3*hidden channel array.
@@ -254,6 +258,72 @@ void paramsFromRanges(const rxmet_gru_ranges &r, const rxmet_gru_quant_config &c
     };
     biases(out->scale_bw, cfg.bw_granularity, RXMET_GRU_BW, r.min_bw, r.max_bw);
     biases(out->scale_br, cfg.br_granularity, RXMET_GRU_BR, r.min_br, r.max_br);
+}
+
+// src/gru_host.cc:254-335
+void paramsFromHistograms(const rxmet_gru_histograms &hs, const rxmet_gru_quant_config &cfg, bool usePercentile,
+                          float percentile, rxmet_gru_quant_params *out) {
+    RXMET_REQUIRE(out != nullptr && hs.hidden > 0, "params_from_histograms: bad arguments");
+    RXMET_REQUIRE(cfg.symmetric[RXMET_GRU_W] && cfg.symmetric[RXMET_GRU_R] && cfg.symmetric[RXMET_GRU_BW] &&
+                      cfg.symmetric[RXMET_GRU_BR],
+                  "W/R/bw/br must remain symmetric (zp=0)");
+    RXMET_REQUIRE(out->scale_W && out->scale_R && out->scale_bw && out->scale_br,
+                  "params_from_histograms: per-channel scale arrays are not set");
+    out->hidden = hs.hidden;
+    out->config = cfg;
+    std::fill(std::begin(out->scale), std::end(out->scale), 0.0f);
+    std::fill(std::begin(out->zero_point), std::end(out->zero_point), 0);
+    auto fromHistogram = [&](const rxmet_histogram &h, int op, const char *name) {
+        if (!(h.num_bins > 0 && h.total_count > 0)) fail(RXMET_ERR_INVALID_ARGUMENT, "%s is invalid.", name);
+        const Width w = widthOf(cfg, op);
+        const hist::Continuous c = hist::calibrate(h, w.lo(), w.hi(), w.isUnsigned, cfg.symmetric[op] != 0, usePercentile, percentile);
+        return encodeContinuous(Continuous{c.scale, c.lo, c.hi}, w, cfg.symmetric[op] != 0, cfg);
+    };
+    static const char *kNames[kOps] = {"scale_x", "scale_h", "W", "R", "bw", "br", "scale_weight_ih_linear",
+                                       "scale_weight_hh_linear", "scale_update_gate_input", "scale_update_gate_output",
+                                       "scale_reset_gate_input", "scale_reset_gate_output", "scale_new_gate_input",
+                                       "scale_new_gate_output", "scale_mul_reset_hidden", "scale_mul_old_contribution",
+                                       "scale_mul_new_contribution"};
+    for (int op = 0; op < kOps; ++op) {
+        if (op == RXMET_GRU_W || op == RXMET_GRU_R || op == RXMET_GRU_BW || op == RXMET_GRU_BR) continue;
+        const Encoding e = fromHistogram(hs.point[op], op, kNames[op]);
+        out->scale[op] = e.scale;
+        out->zero_point[op] = e.zeroPoint;
+    }
+    auto weights = [&](float *dst, int granularity, int op, int slot) {
+        const int hidden = hs.hidden, channels = 3 * hidden;
+        if (granularity == RXMET_PER_TENSOR) {
+            std::fill(dst, dst + channels, fromHistogram(hs.point[op], op, kNames[op]).scale);
+        } else if (granularity == RXMET_PER_GATE) {
+            for (int g = 0; g < 3; ++g)
+                std::fill(dst + g * hidden, dst + (g + 1) * hidden, fromHistogram(hs.gate[slot][g], op, kNames[op]).scale);
+        } else {
+            RXMET_REQUIRE(hs.channel[slot] != nullptr, "per-channel collectors are not set");
+            for (int c = 0; c < channels; ++c) dst[c] = fromHistogram(hs.channel[slot][c], op, kNames[op]).scale;
+        }
+    };
+    weights(out->scale_W, cfg.W_granularity, RXMET_GRU_W, 0);
+    weights(out->scale_R, cfg.R_granularity, RXMET_GRU_R, 1);
+    // biases: twice the observed extent of each group (include/gru_calibration_helpers.h:33-62)
+    auto biases = [&](float *dst, int granularity, int op, int slot) {
+        RXMET_REQUIRE(hs.channel[slot] != nullptr, "per-channel collectors are not set");
+        const Width w = widthOf(cfg, op);
+        forEachGroup(hs.hidden, granularity, [&](int begin, int end) {
+            double extent = 0.0;
+            for (int c = begin; c < end; ++c) {
+                const float lo = hs.channel[slot][c].observed_min, hi = hs.channel[slot][c].observed_max;
+                RXMET_REQUIRE(std::isfinite(lo) && std::isfinite(hi) && lo <= hi, "Bias calibration requires finite observations");
+                extent = std::max(extent, std::max(std::abs(static_cast<double>(lo)), std::abs(static_cast<double>(hi))));
+            }
+            double scale = std::max(2.0 * extent, 0.01) / w.hi();
+            if (cfg.use_pot2) scale = std::exp2(std::ceil(std::log2(scale)));
+            if (!std::isfinite(scale) || scale > std::numeric_limits<float>::max())
+                fail(RXMET_ERR_INVALID_ARGUMENT, "Bias headroom scale exceeds float32 range");
+            std::fill(dst + begin, dst + end, static_cast<float>(scale));
+        });
+    };
+    biases(out->scale_bw, cfg.bw_granularity, RXMET_GRU_BW, 2);
+    biases(out->scale_br, cfg.br_granularity, RXMET_GRU_BR, 3);
 }
 
 namespace {

@@ -70,6 +70,11 @@ struct Exec {
 void paramsFromRanges(const rxmet_gru_ranges &ranges, const rxmet_gru_quant_config &cfg,
                       rxmet_gru_quant_params *out);
 
+// Encodings from histogram collectors, SQNR search or percentile clipping
+// (reference: operators/quant-gru/src/gru_host.cc:254-335).
+void paramsFromHistograms(const rxmet_gru_histograms &hists, const rxmet_gru_quant_config &cfg, bool usePercentile,
+                          float percentile, rxmet_gru_quant_params *out);
+
 // The three tables in the public segment layout
 // (reference: operators/quant-gru/src/quantize_lut.cc:17-48).
 void buildLuts(const rxmet_gru_quant_params &params, rxmet_lut_segment out[3][16]);

@@ -157,20 +157,24 @@ class GRUQuantizationRanges:
 
 
 class GRUHistogramCollectors:
-    """Histogram (SQNR / percentile) calibration state.  Not available in this build: only
-    min/max calibration is implemented; the object exists so that callers can construct it."""
+    """Histogram (SQNR / percentile) calibration state of one direction: one 2048-bin collector per
+    activation point, per-tensor / per-gate / per-channel collectors for W, R, bw, br
+    (operators/quant-gru/include/histogram_collector.h:609-720).  The counts live in host memory;
+    ``forward_calibrate`` fills them from device-side binning."""
 
     def __init__(self, hidden: int = 0, num_bins: int = 2048):
         self._hidden, self._num_bins = int(hidden), int(num_bins)
+        self._set = cabi.HistogramSet(self._hidden, self._num_bins) if self._hidden > 0 else None
 
     def reset(self, hidden: int = -1, num_bins: int = -1) -> None:
         if hidden > 0:
             self._hidden = int(hidden)
         if num_bins > 0:
             self._num_bins = int(num_bins)
+        self._set = cabi.HistogramSet(self._hidden, self._num_bins) if self._hidden > 0 else None
 
     def is_valid(self) -> bool:
-        return False
+        return self._set is not None and self._set.is_valid()
 
     def hidden(self) -> int:
         return self._hidden
@@ -178,8 +182,15 @@ class GRUHistogramCollectors:
     def num_bins(self) -> int:
         return self._num_bins
 
+    def histogram(self, name: str):
+        """(counts, min, max, total) of the collector of an activation point, by its config name."""
+        h = self._set.c.point[cabi.OP_NAMES.index(name)]
+        row = cabi.OP_NAMES.index(name)
+        return self._set.counts[row].copy(), h.min_val, h.max_val, int(h.total_count)
+
     def print(self) -> None:
-        print(f"GRUHistogramCollectors: hidden={self._hidden} num_bins={self._num_bins} is_valid=false")
+        print(f"GRUHistogramCollectors: hidden={self._hidden} num_bins={self._num_bins} "
+              f"is_valid={'true' if self.is_valid() else 'false'}")
 
 
 class GRUQuantParams:
@@ -247,8 +258,22 @@ def calculate_gru_quantitative_parameters(quant_ranges: GRUQuantizationRanges,
 
 def calculate_gru_quantitative_parameters_from_histograms(hist_collectors, bitwidth_config=None,
                                                           use_percentile=False, percentile_value=99.99):
-    raise RuntimeError("histogram (SQNR / percentile) calibration is not implemented in this build; "
-                       "use calib_method='minmax'")
+    """Encodings from histogram collectors: SQNR search, or percentile clipping when
+    ``use_percentile`` (gru_interface_binding.cc, calculate_gru_quantitative_parameters_from_histograms)."""
+    if hist_collectors is None or hist_collectors._set is None:
+        raise RuntimeError("hist_collectors is invalid.")
+    cfg = (bitwidth_config or OperatorQuantConfig())._to_c()
+    n = 3 * hist_collectors.hidden()
+    out = cabi.QuantParams()
+    keep = [(C.c_float * n)() for _ in range(4)]
+    for name, arr in zip(_CHANNEL_NAMES, keep):
+        setattr(out, f"scale_{name}", C.cast(arr, C.POINTER(C.c_float)))
+    lib = cabi.load_library()
+    rc = lib.rxmet_gru_params_from_histograms(C.byref(hist_collectors._set.c), C.byref(cfg), int(bool(use_percentile)),
+                                              C.c_float(percentile_value), C.byref(out))
+    if rc != 0:
+        raise RuntimeError(lib.rxmet_last_error().decode())
+    return GRUQuantParams._from_c(out, keep)
 
 
 # --------------------------------------------------------------------------
@@ -315,14 +340,31 @@ def forward_fp(is_training, time_steps, batch_size, input_size, hidden_size, W, 
 
 def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, h0,
                       calib_method, bitwidth_config, quant_ranges=None, hist_collectors=None):
-    """Float forward that updates ``quant_ranges`` in place (calib_method 'minmax')."""
+    """Float forward that updates ``quant_ranges`` (calib_method 'minmax') or ``hist_collectors``
+    ('sqnr' / 'percentile') in place."""
     T, B, I, H = int(time_steps), int(batch_size), int(input_size), int(hidden_size)
     method = str(calib_method).lower()
     if method == "none":
         return forward_fp(is_training, T, B, I, H, W, R, bw, br, x, h0)
+    if method in ("sqnr", "percentile"):
+        if hist_collectors is None:
+            raise ValueError("Histogram calibration requires hist_collectors")
+        lib = cabi.load_library()
+        W, R, bw, br, x, h0v = _common_inputs(T, B, I, H, W, R, bw, br, x, h0)
+        if hist_collectors.hidden() != H or hist_collectors._set is None:
+            hist_collectors.reset(H)
+        dev = x.device
+        h = torch.empty((T + 1, B, H), dtype=torch.float32, device=dev)
+        v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=dev)
+        cfg = (bitwidth_config or OperatorQuantConfig())._to_c()
+        ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(3, T, B, I, H))
+        with torch.cuda.device(dev):
+            cabi.check(lib.rxmet_gru_forward_calibrate_hist(
+                T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v), _ptr(h), _ptr(v), C.byref(cfg),
+                C.byref(hist_collectors._set.c), _ptr(ws), C.c_size_t(ws.numel()), _stream(dev)), "forward_calibrate")
+        return h, v
     if method != "minmax":
-        raise RuntimeError("histogram (SQNR / percentile) calibration is not implemented in this build; "
-                           "use calib_method='minmax'")
+        raise ValueError(f"unknown calib_method {calib_method!r}")
     if quant_ranges is None:
         raise ValueError("MINMAX requires quant_ranges")
     lib = cabi.load_library()
