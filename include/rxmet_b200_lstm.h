@@ -215,7 +215,7 @@ RXMET_API int rxmet_lstm_derive_execution(const rxmet_lstm_quant_params *params,
 /* ---- device entry points --------------------------------------------------- */
 
 /* Workspace bytes of: op 0 float / calibration forward, 1 quantized forward,
- * 2 backward (lstmQuantizedFpCudaWorkspaceBreakdown, forward_quantized_fp_cuda.h:133-135;
+ * 2 backward, 3 histogram calibration forward (lstmQuantizedFpCudaWorkspaceBreakdown, forward_quantized_fp_cuda.h:133-135;
  * cudaBackwardWorkspaceElementCount, backward_float_cuda.h:45-46). */
 RXMET_API size_t rxmet_lstm_workspace_bytes(int op, int T, int B, int I, int H);
 
@@ -247,6 +247,66 @@ RXMET_API int rxmet_lstm_forward_calibrate_stats(int T, int B, int I, int H, con
 /* Merges host copies of packed statistics into `ranges`
  * (LstmCalibrationCollector::merge, calibration.cc:233-276). */
 RXMET_API int rxmet_lstm_ranges_fold_stats(rxmet_lstm_ranges *ranges, const float *stats_host, int H, int bias_enabled);
+
+/* ---- histogram calibration (SQNR / percentile) ------------------------------ */
+
+/* One collector (quantization::Histogram / HistogramCollector, operators/quant-lstm/
+ * include/quantization/histogram.h:9-37): double counts over [minimum, maximum].
+ * counts is a host array of num_bins doubles owned by the caller; an empty
+ * collector has total_count 0. */
+typedef struct rxmet_lstm_histogram {
+    double *counts;
+    int32_t num_bins;
+    float minimum, maximum;
+    uint64_t total_count;
+} rxmet_lstm_histogram;
+
+/* Collectors of a calibration session (LstmCalibrationCollector::histograms_,
+ * operators/quant-lstm/include/lstm/calibration.h:113-114): one per activation
+ * point; for the four parameter points the collectors of the configured
+ * granularity are used: point[op] (per tensor), gate[slot] (per gate) or
+ * channel[slot][4H] (per channel), slot = op - RXMET_LSTM_WEIGHT_IH. */
+typedef struct rxmet_lstm_histograms {
+    int32_t hidden_size;
+    int32_t num_bins;
+    rxmet_lstm_histogram point[RXMET_LSTM_NUM_OPS];
+    rxmet_lstm_histogram gate[4][4];
+    rxmet_lstm_histogram *channel[4];
+} rxmet_lstm_histograms;
+
+/* Adds host data to a collector (HistogramCollector::collect,
+ * operators/quant-lstm/src/quantization/histogram.cc:129-161): the batch is binned
+ * over its own finite range and merged by re-binning bin centres (:163-183). */
+RXMET_API int rxmet_lstm_histogram_collect_host(rxmet_lstm_histogram *hist, const float *data_host, uint64_t count);
+RXMET_API int rxmet_lstm_histogram_merge(rxmet_lstm_histogram *hist, const rxmet_lstm_histogram *other);
+/* Range chosen from a collector (calibrateHistogramRange, histogram.cc:186-254):
+ * method 0 = SQNR search, 1 = percentile. */
+RXMET_API int rxmet_lstm_histogram_range(const rxmet_lstm_histogram *hist, int bitwidth, int is_unsigned,
+                                         int is_symmetric, int method, float percentile, float *range_min,
+                                         float *range_max);
+
+/* Float forward of one calibration batch that feeds ranges AND histograms
+ * (lstmForwardCalibrateCuda with a histogram-collecting session,
+ * operators/quant-lstm/include/lstm/calibration_cuda.h:10-16; collection order
+ * operators/quant-lstm/src/lstm/calibration.cc:128-232,233-276).  Min/max and the
+ * binning run on the device, merges on the host; synchronises the stream.
+ * Workspace: rxmet_lstm_workspace_bytes(3, ...). */
+RXMET_API int rxmet_lstm_forward_calibrate_hist(int T, int B, int I, int H, const float *weight_ih,
+                                                const float *weight_hh, const float *bias_ih, const float *bias_hh,
+                                                const float *x, const float *h0, const float *c0, float *output,
+                                                float *final_hidden, float *final_cell,
+                                                const rxmet_lstm_quant_config *config, rxmet_lstm_ranges *ranges,
+                                                rxmet_lstm_histograms *hists, void *workspace, size_t workspace_bytes,
+                                                void *stream);
+
+/* Ranges + histograms -> parameters (LstmCalibrationSession::finalize with
+ * method sqnr / percentile, calibration.cc:312-346): every non-bias group takes
+ * the range calibrateHistogramRange selects, biases keep their observed range. */
+RXMET_API int rxmet_lstm_params_from_histograms(const rxmet_lstm_quant_config *config, const rxmet_lstm_ranges *ranges,
+                                                const rxmet_lstm_histograms *hists, int method, float percentile,
+                                                int input_size, int hidden_size, int bias_enabled,
+                                                float *weight_ih_scale, float *weight_hh_scale, float *bias_ih_scale,
+                                                float *bias_hh_scale, rxmet_lstm_quant_params *params);
 
 /* Quantized forward on the FP32 q-carrier (lstmForwardQuantizedFpCuda,
  * forward_quantized_fp_cuda.h:137-169; binding lstm_forward_quantized,

@@ -18,6 +18,7 @@
 #include "lstm/quant_config.h"
 #include "lstm/quant_params.h"
 #include "quantization/float_carrier_ops.h"
+#include "quantization/histogram.h"
 #include "quantization/real_activation.h"
 #include "quantization/scale_encoding.h"
 #include "rxmet_b200_lstm.h"
@@ -91,9 +92,122 @@ rxmet_lstm_cell_scale flat(const ql::Q31Scale &s) {
     return {s.multiplier, s.fp_mantissa, s.fp_exponent, s.uses_fp_scale ? 1 : 0};
 }
 
+qq::HistogramCollector toCollector(const rxmet_lstm_histogram &s) {
+    qq::HistogramCollector c(static_cast<std::size_t>(s.num_bins));
+    if (s.total_count != 0) {
+        qq::Histogram h;
+        h.minimum = s.minimum;
+        h.maximum = s.maximum;
+        h.counts.assign(s.counts, s.counts + s.num_bins);
+        h.total_count = s.total_count;
+        c.merge(h);  // an empty collector takes the histogram over unchanged
+    }
+    return c;
+}
+
+void fromHistogram(const qq::Histogram &h, rxmet_lstm_histogram *s) {
+    if (h.empty()) return;
+    std::copy(h.counts.begin(), h.counts.end(), s->counts);
+    s->minimum = h.minimum;
+    s->maximum = h.maximum;
+    s->total_count = h.total_count;
+}
+
 }  // namespace
 
 extern "C" {
+
+int ref_lstm_histogram_collect_host(rxmet_lstm_histogram *hist, const float *data, uint64_t count) {
+    return guarded([&] {
+        qq::HistogramCollector c = toCollector(*hist);
+        c.collect(data, count);
+        fromHistogram(c.histogram(), hist);
+    });
+}
+
+int ref_lstm_histogram_merge(rxmet_lstm_histogram *hist, const rxmet_lstm_histogram *other) {
+    return guarded([&] {
+        qq::HistogramCollector c = toCollector(*hist);
+        c.merge(toCollector(*other).histogram());
+        fromHistogram(c.histogram(), hist);
+    });
+}
+
+int ref_lstm_histogram_range(const rxmet_lstm_histogram *hist, int bits, int is_unsigned, int is_symmetric, int method,
+                             float percentile, float *lo, float *hi) {
+    return guarded([&] {
+        const qq::HistogramCollector c = toCollector(*hist);
+        qq::HistogramCalibrationOptions options;
+        options.percentile = percentile;
+        const qq::QuantizationType type{static_cast<std::uint8_t>(bits), is_unsigned != 0, is_symmetric != 0};
+        const auto r = qq::calibrateHistogramRange(c.histogram(), type,
+                                                   method == 1 ? qq::HistogramCalibrationMethod::Percentile
+                                                               : qq::HistogramCalibrationMethod::Sqnr,
+                                                   options);
+        *lo = r.first;
+        *hi = r.second;
+    });
+}
+
+// Calibration session with method 1 = sqnr or 2 = percentile over `batches` equally shaped batches;
+// returns the session's histogram collectors and the parameters it finalizes.
+int ref_lstm_calibrate_hist(const rxmet_lstm_quant_config *config, int method, float percentile, int batches, int T,
+                            int B, int I, int H, const float *w_ih, const float *w_hh, const float *b_ih,
+                            const float *b_hh, const float *x_all, const float *h0, const float *c0,
+                            rxmet_lstm_histograms *hists, float *w_ih_scale, float *w_hh_scale, float *b_ih_scale,
+                            float *b_hh_scale, rxmet_lstm_quant_params *params) {
+    return guarded([&] {
+        const auto cfg = toConfig(*config);
+        const bool bias = b_ih != nullptr;
+        qq::HistogramCalibrationOptions options;
+        options.percentile = percentile;
+        ql::LstmCalibrationSession session(cfg, I, H, bias,
+                                           method == 2 ? ql::CalibrationMethod::Percentile : ql::CalibrationMethod::Sqnr,
+                                           options, static_cast<std::size_t>(hists->num_bins));
+        const std::size_t per_batch = static_cast<std::size_t>(T) * B * I;
+        for (int n = 0; n < batches; ++n)
+            session.collect({T, B, I, H}, {w_ih, w_hh, b_ih, b_hh}, x_all + n * per_batch, h0, c0);
+        const auto &fin = session.finalize(false);
+        const auto &all = session.collector().histograms();
+        for (int i = 0; i < RXMET_LSTM_NUM_OPS; ++i) {
+            const auto id = static_cast<ql::QuantOperator>(i);
+            const auto &groups = all[i];
+            if (groups.empty()) continue;
+            if (!ql::isParameterOperator(id)) {
+                fromHistogram(groups[0].histogram(), &hists->point[i]);
+                continue;
+            }
+            const int slot = i - RXMET_LSTM_WEIGHT_IH;
+            const auto gran = cfg.operators[i].granularity;
+            for (std::size_t g = 0; g < groups.size(); ++g) {
+                rxmet_lstm_histogram *dst = gran == ql::QuantGranularity::PerTensor ? &hists->point[i]
+                                            : (gran == ql::QuantGranularity::PerGate ? &hists->gate[slot][g] : &hists->channel[slot][g]);
+                fromHistogram(groups[g].histogram(), dst);
+            }
+        }
+        std::memset(params, 0, sizeof(*params));
+        params->config = *config;
+        params->input_size = I;
+        params->hidden_size = H;
+        params->bias_enabled = bias;
+        float *dst[4] = {w_ih_scale, w_hh_scale, b_ih_scale, b_hh_scale};
+        for (int i = 0; i < RXMET_LSTM_NUM_OPS; ++i) {
+            const auto id = static_cast<ql::QuantOperator>(i);
+            const auto &values = fin.quant_params.operators[i].values;
+            if (values.empty()) continue;
+            if (ql::isParameterOperator(id)) {
+                for (int ch = 0; ch < 4 * H; ++ch) dst[i - RXMET_LSTM_WEIGHT_IH][ch] = values[ch].scale;
+            } else {
+                params->scale[i] = values[0].scale;
+                params->zero_point[i] = values[0].zero_point;
+            }
+        }
+        params->weight_ih_scale = w_ih_scale;
+        params->weight_hh_scale = w_hh_scale;
+        params->bias_ih_scale = bias ? b_ih_scale : nullptr;
+        params->bias_hh_scale = bias ? b_hh_scale : nullptr;
+    });
+}
 
 const char *ref_lstm_last_error() { return g_error.c_str(); }
 

@@ -153,6 +153,49 @@ class ExecutionBox:
         return out
 
 
+class Histogram(C.Structure):
+    """``rxmet_lstm_histogram``; ``counts`` points at host doubles."""
+    _fields_ = [("counts", C.POINTER(C.c_double)), ("num_bins", C.c_int32), ("minimum", C.c_float),
+                ("maximum", C.c_float), ("total_count", C.c_uint64)]
+
+
+class Histograms(C.Structure):
+    """``rxmet_lstm_histograms``."""
+    _fields_ = [("hidden_size", C.c_int32), ("num_bins", C.c_int32), ("point", Histogram * NUM_OPS),
+                ("gate", (Histogram * 4) * 4), ("channel", C.POINTER(Histogram) * 4)]
+
+
+class HistogramSet:
+    """All collectors of a calibration session with their storage: 18 point collectors, 4 x 4 gate
+    collectors and 4 x 4H channel collectors."""
+
+    def __init__(self, hidden: int, num_bins: int = 2048):
+        self.hidden, self.num_bins = int(hidden), int(num_bins)
+        total = NUM_OPS + 16 + 16 * self.hidden
+        self.counts = np.zeros((total, self.num_bins), np.float64)
+        self.channels = [(Histogram * (4 * self.hidden))() for _ in range(4)]
+        self.struct = Histograms()
+        self.struct.hidden_size, self.struct.num_bins = self.hidden, self.num_bins
+        for row, h in enumerate(self.all()):
+            h.counts = self.counts[row].ctypes.data_as(C.POINTER(C.c_double))
+            h.num_bins = self.num_bins
+        for k in range(4):
+            self.struct.channel[k] = C.cast(self.channels[k], C.POINTER(Histogram))
+
+    def all(self):
+        for op in range(NUM_OPS):
+            yield self.struct.point[op]
+        for k in range(4):
+            for g in range(4):
+                yield self.struct.gate[k][g]
+        for k in range(4):
+            for ch in range(4 * self.hidden):
+                yield self.channels[k][ch]
+
+    def states(self):
+        return [(h.minimum, h.maximum, int(h.total_count)) for h in self.all()]
+
+
 def default_config(scale_mode=SCALE_AFFINE, bits=8, symmetric_activations=False,
                    parameter_granularity=PER_CHANNEL) -> QuantConfig:
     """8-bit grid: symmetric signed parameters, unsigned sigmoid outputs, other activations signed."""

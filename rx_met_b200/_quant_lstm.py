@@ -520,25 +520,26 @@ def lstm_backward_qat(master_values, batch_first, bundle_json, checkpoint_values
 # --------------------------------------------------------------------------
 
 class CalibrationSession:
-    """Min/max calibration over any number of batches (CalibrationSessionBinding,
-    lstm_interface_binding.cc:791-882).  The statistics of a batch are reduced on the device by
-    the calibration forward and folded on the host; ``finalize`` turns them into a parameter bundle."""
+    """Calibration over any number of batches, method "minmax", "sqnr" or "percentile"
+    (CalibrationSessionBinding, lstm_interface_binding.cc:791-882).  The statistics of a batch are
+    reduced (and, for the histogram methods, binned) on the device by the calibration forward and
+    merged on the host; ``finalize`` turns them into a parameter bundle."""
 
     def __init__(self, resolved_config_json: str, input_size: int, hidden_size: int, bias_enabled: bool,
                  method: str = "minmax", percentile: float = 99.99):
         if method not in ("minmax", "sqnr", "percentile"):
             raise ValueError("calibration_method must be minmax, sqnr or percentile")
-        if method != "minmax":
-            raise RuntimeError(f"calibration method {method!r} is not built; only minmax is")
         if not (0.0 < percentile <= 100.0):
             raise RuntimeError("percentile must be in (0, 100]")
         self._config = _config_from_json(resolved_config_json)
         self._I, self._H, self._bias = int(input_size), int(hidden_size), bool(bias_enabled)
         self._method = method
+        self._percentile = float(percentile)
         self.reset()
 
     def reset(self):
         self._ranges = L.RangesBox(self._H)
+        self._hists = L.HistogramSet(self._H) if self._method != "minmax" else None
         self._batches = 0
         self._state = "empty"
         self._final = None
@@ -561,11 +562,23 @@ class CalibrationSession:
         if (p.b_ih is not None) != self._bias:
             raise RuntimeError("calibration bias setting does not match the session")
         lib = _library()
-        stats = torch.empty(lib.rxmet_lstm_stats_floats(p.H), dtype=torch.float32, device=p.device)
-        out, hn, cn = _run_float(p, None, stats)
-        host = stats.cpu().numpy()
-        _check(lib.rxmet_lstm_ranges_fold_stats(C.byref(self._ranges.struct), host.ctypes.data_as(C.POINTER(C.c_float)),
-                                                p.H, int(self._bias)), RuntimeError)
+        if self._hists is not None:
+            T, B, I, H = p.dims()
+            out, hn, cn = p.empty(T, B, H), p.empty(1, B, H), p.empty(1, B, H)
+            ws, n = _workspace(3, T, B, I, H, p.device)
+            with torch.cuda.device(p.device):
+                rc = lib.rxmet_lstm_forward_calibrate_hist(
+                    T, B, I, H, _ptr(p.w_ih), _ptr(p.w_hh), _ptr(p.b_ih), _ptr(p.b_hh), _ptr(p.x), _ptr(p.h0), _ptr(p.c0),
+                    _ptr(out), _ptr(hn), _ptr(cn), C.byref(self._config), C.byref(self._ranges.struct),
+                    C.byref(self._hists.struct), _ptr(ws), C.c_size_t(n), _stream())
+            _check(rc, RuntimeError)
+        else:
+            stats = torch.empty(lib.rxmet_lstm_stats_floats(p.H), dtype=torch.float32, device=p.device)
+            out, hn, cn = _run_float(p, None, stats)
+            host = stats.cpu().numpy()
+            _check(lib.rxmet_lstm_ranges_fold_stats(C.byref(self._ranges.struct),
+                                                    host.ctypes.data_as(C.POINTER(C.c_float)), p.H, int(self._bias)),
+                   RuntimeError)
         self._batches += 1
         self._state = "dirty"
         return (out.transpose(0, 1) if batch_first else out), hn, cn
@@ -575,9 +588,15 @@ class CalibrationSession:
             raise RuntimeError("an empty calibration session cannot be finalized")
         if self._final is None:
             box = L.ParamsBox(self._H)
-            _check(_library().rxmet_lstm_params_from_ranges(
-                C.byref(self._config), C.byref(self._ranges.struct), self._I, self._H, int(self._bias),
-                *box.scale_ptrs(), C.byref(box.struct)), ValueError)
+            if self._hists is None:
+                _check(_library().rxmet_lstm_params_from_ranges(
+                    C.byref(self._config), C.byref(self._ranges.struct), self._I, self._H, int(self._bias),
+                    *box.scale_ptrs(), C.byref(box.struct)), ValueError)
+            else:
+                _check(_library().rxmet_lstm_params_from_histograms(
+                    C.byref(self._config), C.byref(self._ranges.struct), C.byref(self._hists.struct),
+                    0 if self._method == "sqnr" else 1, C.c_float(self._percentile), self._I, self._H, int(self._bias),
+                    *box.scale_ptrs(), C.byref(box.struct)), ValueError)
             box.bind()
             ex = _execution(box, require_exact_accumulation)
             r = self._ranges.struct

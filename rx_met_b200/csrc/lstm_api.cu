@@ -88,6 +88,7 @@ size_t rxmet_lstm_workspace_bytes(int op, int T, int B, int I, int H) {
         case 0: return lstm::forwardFloatWorkspaceBytes(T, B, I, H);
         case 1: return lstm::forwardQuantWorkspaceBytes(T, B, I, H);
         case 2: return lstm::backwardWorkspaceBytes(T, B, I, H);
+        case 3: return lstm::histCalibrationWorkspaceBytes(T, B, I, H);
         default: return 0;
     }
 }

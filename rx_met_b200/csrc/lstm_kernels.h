@@ -18,6 +18,15 @@ struct ForwardFloatCall {
 size_t forwardFloatWorkspaceBytes(int T, int B, int I, int H);
 void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
 
+// Histogram calibration: float forward of one batch that updates ranges and histogram collectors.
+size_t histCalibrationWorkspaceBytes(int T, int B, int I, int H);
+void forwardCalibrateHist(const ForwardFloatCall &call, const rxmet_lstm_quant_config &config, rxmet_lstm_ranges *ranges,
+                          rxmet_lstm_histograms *hists, void *workspace, size_t workspaceBytes, cudaStream_t stream);
+void paramsFromHistograms(const rxmet_lstm_quant_config &config, const rxmet_lstm_ranges &observed,
+                          const rxmet_lstm_histograms &hists, int method, float percentile, int inputSize, int hidden,
+                          bool bias, float *wIhScale, float *wHhScale, float *bIhScale, float *bHhScale,
+                          rxmet_lstm_quant_params *out);
+
 struct ForwardQuantCall {
     int T, B, I, H;
     const float *weightIh, *weightHh, *biasIh, *biasHh, *x, *h0, *c0;

@@ -340,11 +340,17 @@ DevRescale device(const rxmet_lstm_rescale &r) {
 
 }  // namespace
 
-Grid gridOf(const rxmet_lstm_quant_config &cfg, int op) {
-    const int bits = cfg.bitwidth[op];
-    if (cfg.is_unsigned[op]) return {0, static_cast<int32_t>((uint64_t{1} << bits) - 1u)};
+Grid gridOfBits(int bits, bool isUnsigned) {
+    if (isUnsigned) return {0, static_cast<int32_t>((uint64_t{1} << bits) - 1u)};
     const int32_t hi = static_cast<int32_t>((uint64_t{1} << (bits - 1)) - 1u);
     return {-hi - 1, hi};
+}
+
+Grid gridOf(const rxmet_lstm_quant_config &cfg, int op) { return gridOfBits(cfg.bitwidth[op], cfg.is_unsigned[op] != 0); }
+
+MinMaxParam minMaxParam(float lo, float hi, int bits, bool isUnsigned, bool symmetric) {
+    const Calibrated c = fromMinMax(lo, hi, isUnsigned, symmetric, gridOfBits(bits, isUnsigned));
+    return {c.scale, c.zeroPoint};
 }
 
 void defaultConfig(rxmet_lstm_quant_config *cfg) {

@@ -28,6 +28,15 @@ void paramsFromRanges(const rxmet_lstm_quant_config &cfg, const rxmet_lstm_range
 // provably exact in float; throws when requireExact is set and it is not.
 void deriveExecution(const rxmet_lstm_quant_params &params, bool requireExact, rxmet_lstm_execution *out);
 void foldStats(rxmet_lstm_ranges *ranges, const float *stats, int hidden, bool bias);
+
+// Scale and zero point that cover [lo, hi] on a grid (calibrateMinMax of the reference, no
+// power-of-two snapping); used by the histogram range search to score candidate ranges.
+struct MinMaxParam {
+    float scale;
+    int32_t zeroPoint;
+};
+MinMaxParam minMaxParam(float lo, float hi, int bits, bool isUnsigned, bool symmetric);
+Grid gridOfBits(int bits, bool isUnsigned);
 size_t statsFloats(int hidden);
 
 // A rescale in the form the kernels apply it: rint(v * mult * pow2), both factors floats.

@@ -199,3 +199,14 @@ def stage(params: L.ParamsBox, which: int, rows: int, a, b=None, c=None, out_sha
     a, b, c = cont(a), cont(b), cont(c)
     _call("orc", "stage", C.byref(params.struct), which, C.c_longlong(rows), _fp(a), _fp(b), _fp(c), _fp(out), _up(mask))
     return out, mask
+
+
+def calibrate_hist(cfg, p, batches_x: np.ndarray, method: str, percentile: float, bins: int = 2048):
+    """Reference calibration session with a histogram method.  Returns (HistogramSet, ParamsBox)."""
+    T, B, I, H = p["T"], p["B"], p["I"], p["H"]
+    hs, box = L.HistogramSet(H, bins), L.ParamsBox(H)
+    _call("ref", "calibrate_hist", C.byref(cfg), 1 if method == "sqnr" else 2, C.c_float(percentile), batches_x.shape[0],
+          T, B, I, H, _fp(p["w_ih"]), _fp(p["w_hh"]), _fp(p["b_ih"]), _fp(p["b_hh"]), _fp(np.ascontiguousarray(batches_x)),
+          _fp(p["h0"]), _fp(p["c0"]), C.byref(hs.struct), *box.scale_ptrs(), C.byref(box.struct))
+    box.bind()
+    return hs, box

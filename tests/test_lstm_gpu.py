@@ -225,3 +225,41 @@ def test_errors_are_reported_not_faulted():
     wbox, wbundle = calibrated_bundle(wide, p)
     with pytest.raises(RuntimeError, match="8 bits"):
         m.lstm_forward_quantized(*torch_args(p), False, wbundle)
+
+
+@pytest.mark.skipif(not ll.have_ref(), reason="compiled reference not available")
+@pytest.mark.parametrize("method", ["sqnr", "percentile"])
+@pytest.mark.parametrize("state", [True, False])
+def test_histogram_calibration_session_matches_reference(method, state):
+    T, B, I, H = 12, 8, 10, 16
+    cfg = L.default_config()
+    p = ll.problem(T, B, I, H, seed=51, state=state)
+    xs = np.stack([p["x"], ll.problem(T, B, I, H, seed=52)["x"] * 1.5])
+    want_h, want_p = ll.calibrate_hist(cfg, p, xs, method, 99.9)
+    m = mod()
+    session = m.CalibrationSession(m._config_to_json(cfg), I, H, True, method, 99.9)
+    for x in xs:
+        session.collect(dev(x), dev(p["w_ih"]), dev(p["w_hh"]), dev(p["b_ih"]), dev(p["b_hh"]), state3(p["h0"]), state3(p["c0"]))
+    got_h = session._hists
+    for (glo, ghi, gn), (wlo, whi, wn) in zip(got_h.states(), want_h.states()):
+        assert gn == wn
+        if wn:
+            span = max(whi - wlo, 1e-6)
+            assert abs(glo - wlo) <= 1e-5 * span + 1e-7 and abs(ghi - whi) <= 1e-5 * span + 1e-7
+    for op in range(L.NUM_OPS):
+        total = want_h.struct.point[op].total_count
+        if total:
+            moved = np.abs(got_h.counts[op] - want_h.counts[op]).sum()
+            assert moved <= 0.02 * total, (L.OP_NAMES[op], moved, total)
+    # x and the parameters involve no arithmetic: exact
+    np.testing.assert_array_equal(got_h.counts[L.INPUT], want_h.counts[L.INPUT])
+    np.testing.assert_array_equal(got_h.counts[L.NUM_OPS:], want_h.counts[L.NUM_OPS:])
+    final = session.finalize()
+    got_p = m._bundle_to_params(final["bundle_json"])
+    for k in range(4):
+        np.testing.assert_array_equal(got_p.channel_scales[k], want_p.channel_scales[k])
+    for op in range(L.NUM_OPS):
+        if op not in L.PARAMETER_OPS:
+            close([got_p.struct.scale[op]], [want_p.struct.scale[op]], 0.03, L.OP_NAMES[op])
+    out = m.lstm_forward_quantized(*torch_args(p), False, final["bundle_json"])
+    assert torch.isfinite(out[0]).all()
