@@ -193,6 +193,11 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
     lib = cabi.load_library()
+    if args.profile_only and args.workload == "aimet":
+        # the AIMET native kernels on a 256 MiB tensor (larger than L2) for captures under a profiler
+        out = aimet_kernel_bandwidth(lib, torch, device, _peaks()[0], elements=1 << 26, reps=2)
+        print(json.dumps({"profile_only": True, "workload": "aimet", "result": out}), flush=True)
+        return
     if args.profile_only and args.workload == "lstm":
         # small LSTM training loop for captures under a profiler; prints no bench line
         lstm_secondary(lib, torch, device, torch.empty(1, dtype=torch.uint8, device=device), profile_steps=args.steps,
@@ -345,10 +350,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def aimet_kernel_bandwidth(lib, torch, device, peak_gbs):
-    """HBM-bound AIMET native kernels on a 1 GiB float32 tensor (larger than L2): GB/s of
+def aimet_kernel_bandwidth(lib, torch, device, peak_gbs, elements=1 << 28, reps=10):
+    """HBM-bound AIMET native kernels on a float32 tensor larger than L2 (1 GiB by default): GB/s of
     algorithmic traffic (QDQ 8 B/element, min/max and histogram 4 B/element) from CUDA events."""
-    n = 1 << 28
+    n = elements
     x = torch.randn(n, device=device)
     y = torch.empty_like(x)
     lib.rxmet_aimet_minmax_workspace_bytes.restype = C.c_size_t
@@ -370,7 +375,6 @@ def aimet_kernel_bandwidth(lib, torch, device, peak_gbs):
             assert fn() == 0, lib.rxmet_last_error()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 10
         e0.record()
         for _ in range(reps):
             fn()
@@ -485,7 +489,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["gru", "lstm"], default="gru",
+    ap.add_argument("--workload", choices=["gru", "lstm", "aimet"], default="gru",
                     help="with --profile-only: which training loop to run (the bench line is always the GRU QAT step)")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
     ap.add_argument("--profile-only", action="store_true",
