@@ -442,6 +442,29 @@ RXMET_API int rxmet_aimet_pdf_size(void);
 RXMET_API int rxmet_aimet_histogram(const void *data_dev, uint64_t count, int dtype, double bucket_size,
                                     int pdf_offset, uint32_t *histogram_dev, void *stream);
 
+/* Encoding of a (min, max) range (TfEncoding, native/common/include/DlQuantization/
+ * Quantization.hpp:114-121). */
+typedef struct rxmet_aimet_encoding {
+    double min, max, delta, offset;
+    int32_t bw;
+} rxmet_aimet_encoding;
+
+/* Range -> encoding (getComputedEncodings, native/common/src/quantization_utils.cpp:59-117):
+ * zero kept on the grid, symmetric / strict-symmetric / unsigned-symmetric modes,
+ * delta clamped so that the dequantized range stays inside 0.99 of float32. */
+RXMET_API int rxmet_aimet_compute_encoding(int bw, double range_min, double range_max, int symmetric,
+                                           int strict_symmetric, int unsigned_symmetric,
+                                           rxmet_aimet_encoding *encoding);
+
+/* Min/max statistics -> encoding (MinMaxEncodingAnalyzer::computeEncoding,
+ * native/common/src/MinMaxEncodingAnalyzer.cpp:80-107): zero included, maximum
+ * nudged to at least minimum + 0.01 (0.01 in the analyzer's element type: dtype 0
+ * = float, 1 = double).  stats_min / stats_max are the running extremes that
+ * rxmet_aimet_minmax accumulates. */
+RXMET_API int rxmet_aimet_minmax_encoding(int bw, int dtype, double stats_min, double stats_max, int symmetric,
+                                          int strict_symmetric, int unsigned_symmetric,
+                                          rxmet_aimet_encoding *encoding);
+
 /* ------------------------------------------------------------------------ */
 /* Allocation-free variant                                                    */
 /* ------------------------------------------------------------------------ */

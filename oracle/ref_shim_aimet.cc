@@ -13,6 +13,8 @@
 #include "DlQuantization/Quantization.hpp"
 #include "math_functions.hpp"
 #include "trim_functions.hpp"
+#include "quantization_utils.hpp"
+#include "MinMaxEncodingAnalyzer.h"
 
 using namespace DlQuantization;
 
@@ -80,5 +82,28 @@ int ref_aimet_histogram_f32(const float *in, uint64_t n, uint32_t *hist, double 
     } catch (...) { return -1; }
 }
 int ref_aimet_pdf_size(void) { return PDF_SIZE; }
+
+// out: {min, max, delta, offset, bw}
+int ref_aimet_compute_encoding(int bw, double mn, double mx, int symmetric, int strict, int unsignedSymmetric, double *out) {
+    try {
+        const TfEncoding e = getComputedEncodings(static_cast<uint8_t>(bw), mn, mx, symmetric != 0, strict != 0, unsignedSymmetric != 0);
+        out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
+        return 0;
+    } catch (...) { return -1; }
+}
+
+// MinMaxEncodingAnalyzer<float> fed the given statistics through updateStats on two one-element tensors.
+int ref_aimet_minmax_encoding(int bw, float statsMin, float statsMax, int symmetric, int strict, int unsignedSymmetric,
+                              double *out) {
+    try {
+        MinMaxEncodingAnalyzer<float> analyzer(TensorDims{1});
+        const float values[2] = {statsMin, statsMax};
+        analyzer.updateStats(values, TensorDims{2}, COMP_MODE_CPU, nullptr, nullptr);
+        const Encodings all = analyzer.computeEncoding(static_cast<uint8_t>(bw), symmetric != 0, strict != 0, unsignedSymmetric != 0);
+        const TfEncoding &e = all[0];
+        out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
+        return 0;
+    } catch (...) { return -1; }
+}
 
 }  // extern "C"

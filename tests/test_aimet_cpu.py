@@ -143,3 +143,34 @@ def test_restatement_matches_compiled_reference():
         assert r.ref_aimet_histogram_f32(fp(z), C.c_uint64(z.size), u32(ha), C.c_double(bucket), offset, 1) == 0
         o.orc_aimet_histogram_f32(fp(z), C.c_uint64(z.size), u32(hb), C.c_double(bucket), offset)
         assert np.array_equal(ha, hb) and ha.sum() > 0
+
+
+class _Encoding(C.Structure):
+    _fields_ = [("min", C.c_double), ("max", C.c_double), ("delta", C.c_double), ("offset", C.c_double), ("bw", C.c_int32)]
+
+
+@pytest.mark.skipif(ref() is None, reason="compiled reference not available")
+def test_library_encodings_match_the_reference():
+    """Host logic of the shipped library (range -> encoding, min/max statistics -> encoding)."""
+    from rx_met_b200 import _cabi
+    lib, r = _cabi.load_library(), ref()
+    rng = np.random.default_rng(3)
+    ranges = [(-1.0, 1.0), (0.0, 6.0), (-3.5, 0.25), (0.0, 0.0), (-1e-9, 1e-9), (-1e38, 3e38), (0.2, 5.0), (-7.0, -2.0)]
+    ranges += [tuple(sorted(rng.standard_normal(2) * 10.0 ** rng.integers(-3, 4))) for _ in range(40)]
+    modes = [(0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)]
+    for lo, hi in ranges:
+        for bw in (2, 4, 8, 16, 31):
+            for sym, strict, uns in modes:
+                e = _Encoding()
+                out = (C.c_double * 5)()
+                assert lib.rxmet_aimet_compute_encoding(bw, C.c_double(lo), C.c_double(hi), sym, strict, uns, C.byref(e)) == 0
+                assert r.ref_aimet_compute_encoding(bw, C.c_double(lo), C.c_double(hi), sym, strict, uns, out) == 0
+                got = (e.min, e.max, e.delta, e.offset, float(e.bw))
+                assert all(a == b or (a != a and b != b) for a, b in zip(got, out)), (lo, hi, bw, sym, strict, uns, got, list(out))
+                lo32, hi32 = np.float32(lo), np.float32(hi)
+                assert lib.rxmet_aimet_minmax_encoding(bw, 0, C.c_double(lo32), C.c_double(hi32), sym, strict, uns, C.byref(e)) == 0
+                assert r.ref_aimet_minmax_encoding(bw, C.c_float(lo32), C.c_float(hi32), sym, strict, uns, out) == 0
+                got = (e.min, e.max, e.delta, e.offset, float(e.bw))
+                assert all(a == b or (a != a and b != b) for a, b in zip(got, out)), ("minmax", lo, hi, bw, sym, strict, uns)
+    e = _Encoding()
+    assert lib.rxmet_aimet_compute_encoding(0, C.c_double(0), C.c_double(1), 0, 0, 0, C.byref(e)) == -1
