@@ -487,7 +487,7 @@ def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
     torch.cuda.synchronize()
     per = {}
     for n in ["lstmQuantizeCodes", "lstmPrepChannels", "lstmInputLinearQ", "lstmRecurrentQ", "lstmDequantWeights",
-              "lstmPackStepMasks", "lstmRecurrentBackward", "lstmGemmNN", "lstmGemmRowsTN", "lstmReduceSplits",
+              "lstmPackStepMasks", "lstmRecurrentBackward", "lstmRecurrentBackwardMma", "lstmGemmNN", "lstmInputGradNarrow", "lstmGemmRowsTN", "lstmReduceSplits",
               "lstmColumnSums", "weightGradMma", "lstmReduceWeightGradT"]:
         ms, cnt = C.c_double(), C.c_longlong()
         lib.rxmet_get_kernel_timing(n.encode(), C.byref(ms), C.byref(cnt))

@@ -16,6 +16,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.h"
 #include "lstm_kernels.h"
@@ -58,6 +59,7 @@ __global__ void packStepMasks(const rxmet_lstm_backward_masks mk, size_t rows, i
 
 struct RecurrentArgs {
     int T, B, H, smemRows;  // smemRows: leading rows of each gate block held in shared memory
+    int smemStride;         // floats between consecutive columns of the transposed copy (odd multiple of 4)
     const uint32_t *stepMasks;  // packed flags [T][B][H] or null
     const float *weightHh;  // real [4H][H]
     const float *c0;
@@ -83,9 +85,12 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
     float *wS = partS + 4 * BT * H;  // [4][S][H] leading rows of each gate block of weight_hh
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    // transposed per thread: the S leading rows of column j of gate block g are contiguous (stride SP),
+    // so that phase A reads four of them with one 128-bit load
+    const int SP = a.smemStride;
     for (int i = tid; i < 4 * S * H; i += nthreads) {
         const int g = i / (S * H), r = (i / H) % S, j = i % H;
-        wS[i] = a.weightHh[(static_cast<size_t>(g) * H + r) * H + j];
+        wS[(static_cast<size_t>(g) * H + j) * SP + r] = a.weightHh[(static_cast<size_t>(g) * H + r) * H + j];
     }
     for (int i = tid; i < 4 * BT * H; i += nthreads) partS[i] = 0.0f;
     for (int i = tid; i < BT * C; i += nthreads) gS[i] = 0.0f;
@@ -103,7 +108,7 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
 #pragma unroll
     for (int r = 0; r < kRegRows; ++r)
         wr[r] = (hasColumn && r < R) ? a.weightHh[(static_cast<size_t>(q) * H + S + r) * H + cj] : 0.0f;
-    const bool vec = (H % 4 == 0) && (S % 4 == 0);
+    const bool vec = (H % 4 == 0) && (S % 4 == 0) && (SP % 4 == 0);
     __syncthreads();
 
     // inputs of one step for this thread's element, fetched one step ahead of their use
@@ -162,18 +167,19 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
             float acc[BT];
 #pragma unroll
             for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
-            const float *wq = wS + static_cast<size_t>(q) * S * H + cj;
+            const float *wq = wS + (static_cast<size_t>(q) * H + cj) * SP;
             const float *gq = gS + q * H;
             if (vec) {
+#pragma unroll 4
                 for (int r = 0; r < S; r += 4) {
-                    const float w0 = wq[r * H], w1 = wq[(r + 1) * H], w2 = wq[(r + 2) * H], w3 = wq[(r + 3) * H];
+                    const float4 wv = *reinterpret_cast<const float4 *>(wq + r);
 #pragma unroll
                     for (int b = 0; b < BT; ++b) {
                         const float4 gv = *reinterpret_cast<const float4 *>(gq + b * C + r);
-                        acc[b] = fmaf(gv.x, w0, acc[b]);
-                        acc[b] = fmaf(gv.y, w1, acc[b]);
-                        acc[b] = fmaf(gv.z, w2, acc[b]);
-                        acc[b] = fmaf(gv.w, w3, acc[b]);
+                        acc[b] = fmaf(gv.x, wv.x, acc[b]);
+                        acc[b] = fmaf(gv.y, wv.y, acc[b]);
+                        acc[b] = fmaf(gv.z, wv.z, acc[b]);
+                        acc[b] = fmaf(gv.w, wv.w, acc[b]);
                     }
                 }
 #pragma unroll
@@ -191,7 +197,7 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
                 }
             } else {
                 for (int r = 0; r < S; ++r) {
-                    const float w = wq[r * H];
+                    const float w = wq[r];
 #pragma unroll
                     for (int b = 0; b < BT; ++b) acc[b] = fmaf(gq[b * C + r], w, acc[b]);
                 }
@@ -211,6 +217,169 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
     if (hasElem) {
         const float dh0 = dhCarry + partS[(0 * BT + eb) * H + ej] + partS[(1 * BT + eb) * H + ej] +
                           partS[(2 * BT + eb) * H + ej] + partS[(3 * BT + eb) * H + ej];
+        a.dh0[stateIdx] = dh0 * keepOf(a.mk.initial_hidden, stateIdx);
+        a.dc0[stateIdx] = dc * keepOf(a.mk.initial_cell, stateIdx);
+    }
+}
+
+// ---- dh = G_hh W_hh on tensor cores (QAT with weight grids of at most 8 bits) ------------------
+//
+// Same data flow as recurrentBackward, but the per-step product runs as mma.sync m16n8k16 with
+// M = hidden column k, N = batch tile (padded to 8), K = the 4H channels.  Warp w owns two m16 tiles
+// (hidden columns 32*(w/4) .. +31) and the K range of gate w%4; its A fragments - the integer weight
+// codes, exact in bf16 - stay in registers for the whole sequence.  The gate gradient, multiplied by
+// the channel's weight scale, is split into three bf16 terms in shared memory so that every product
+// is exact and only the fp32 accumulation rounds.
+__device__ __forceinline__ uint32_t packBf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16Lo(uint32_t v) { return __uint_as_float(v << 16); }
+
+struct RecurrentMmaArgs {
+    RecurrentArgs base;
+    const float *weightCodes;   // q-carrier codes [4H][H]
+    const float *channelScale;  // [4H] scale of weight_hh per channel
+};
+
+template <int HT, int BT>  // H = 32*HT, blockDim = 128*HT
+__global__ void __launch_bounds__(128 * HT) recurrentBackwardMma(const __grid_constant__ RecurrentMmaArgs args) {
+    const RecurrentArgs &a = args.base;
+    constexpr int H = 32 * HT, C = 4 * H, KS = 2 * HT;  // k16 steps per warp
+    constexpr int CP = C + 8;                           // padded row of the bf16 gradient tiles
+    __shared__ __align__(16) uint16_t gB[3][8][CP];     // [split][batch row][channel]
+    __shared__ float partS[4][BT][H];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int grp = warp % 4, mpair = warp / 4;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+
+    // A fragments: element (m = hidden column, k = channel) = code[channel][hidden column]
+    uint32_t afrag[2][KS][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int row = mpair * 32 + mt * 16 + g8 + (q & 1) * 8;
+                const int col = grp * H + ks * 16 + 2 * t4 + (q >> 1) * 8;
+                const float w0 = args.weightCodes[static_cast<size_t>(col) * H + row];
+                const float w1 = args.weightCodes[static_cast<size_t>(col + 1) * H + row];
+                afrag[mt][ks][q] = (__float_as_uint(w0) >> 16) | (__float_as_uint(w1) & 0xffff0000u);
+            }
+    for (int i = tid; i < 3 * 8 * CP; i += nthreads) (&gB[0][0][0])[i] = 0;
+    for (int i = tid; i < 4 * BT * H; i += nthreads) (&partS[0][0][0])[i] = 0.0f;
+
+    const int elems = nb * H;
+    const bool hasElem = tid < elems;
+    const int eb = hasElem ? tid / H : 0, ej = hasElem ? tid % H : 0;
+    const size_t stateIdx = static_cast<size_t>(b0 + eb) * H + ej;
+    float dhCarry = hasElem ? a.gradFinalHidden[stateIdx] : 0.0f;
+    float dc = hasElem ? a.gradFinalCell[stateIdx] : 0.0f;
+    float scale[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) scale[g] = args.channelScale[g * H + ej];
+
+    struct StepIn {
+        float gate[4], ct, cPrev, gradOut;
+        uint32_t bits;
+    };
+    auto fetch = [&](int t, StepIn &in) {
+        if (!hasElem) return;
+        const size_t row = static_cast<size_t>(t) * a.B + b0 + eb, so = row * H + ej, go = row * C + ej;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) in.gate[g] = a.gateOutputs[go + static_cast<size_t>(g) * H];
+        in.ct = a.cellTanh[so];
+        in.cPrev = t > 0 ? a.cellStates[so - static_cast<size_t>(a.B) * H] : (a.c0 ? a.c0[stateIdx] : a.dqC.zeroPoint);
+        in.gradOut = a.gradOutput[so];
+        in.bits = a.stepMasks ? a.stepMasks[so] : 0u;
+    };
+    auto splitStore = [&](int b, int c, float v) {
+        const float hi = bf16Lo(packBf16(v, 0.0f));
+        const float r1 = v - hi;
+        const float mid = bf16Lo(packBf16(r1, 0.0f));
+        const float lo = r1 - mid;
+        gB[0][b][c] = static_cast<uint16_t>(__float_as_uint(hi) >> 16);
+        gB[1][b][c] = static_cast<uint16_t>(__float_as_uint(mid) >> 16);
+        gB[2][b][c] = static_cast<uint16_t>(packBf16(lo, 0.0f) & 0xffffu);
+    };
+    StepIn cur{}, nxt{};
+    fetch(a.T - 1, cur);
+    __syncthreads();
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
+        if (t > 0) fetch(t - 1, nxt);
+        if (hasElem) {
+            const size_t row = rowBase + eb, go = row * C + ej;
+            auto keepBit = [&](int b) { return (cur.bits >> b) & 1u ? 0.0f : 1.0f; };
+            const float ig = realOf(cur.gate[0], a.dqGate[0]), fg = realOf(cur.gate[1], a.dqGate[1]);
+            const float cg = realOf(cur.gate[2], a.dqGate[2]), og = realOf(cur.gate[3], a.dqGate[3]);
+            const float ct = realOf(cur.ct, a.dqTanh);
+            const float cPrev = realOf(cur.cPrev, a.dqC);
+            const float incoming = dhCarry + partS[0][eb][ej] + partS[1][eb][ej] + partS[2][eb][ej] + partS[3][eb][ej];
+            const float dh = (incoming + cur.gradOut) * keepBit(0);
+            const float gOut = dh * ct;
+            const float gTanh = dh * og * keepBit(1);
+            const float dcAll = dc + gTanh * (1.0f - ct * ct);
+            const float mdc = dcAll * keepBit(2);
+            const float go4[4] = {mdc * cg * keepBit(3), mdc * cPrev * keepBit(4), mdc * ig * keepBit(5), gOut * keepBit(6)};
+            const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
+                                  go4[3] * og * (1.0f - og)};
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const size_t o = go + static_cast<size_t>(g) * H;
+                const float grad = gi4[g] * keepBit(7 + g);
+                const float hh = grad * keepBit(15 + g);
+                a.gIh[o] = grad * keepBit(11 + g);
+                a.gHh[o] = hh;
+                splitStore(eb, g * H + ej, hh * scale[g]);
+            }
+            dc = mdc * fg;
+            dhCarry = 0.0f;
+        }
+        cur = nxt;
+        __syncthreads();
+        {
+            float acc[2][3][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) acc[mt][sp][0] = acc[mt][sp][1] = acc[mt][sp][2] = acc[mt][sp][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int c0 = grp * H + ks * 16 + 2 * t4;
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) {
+                    const uint32_t bf0 = *reinterpret_cast<const uint32_t *>(&gB[sp][g8][c0]);
+                    const uint32_t bf1 = *reinterpret_cast<const uint32_t *>(&gB[sp][g8][c0 + 8]);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        asm volatile(
+                            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                            "{%0,%1,%2,%3};"
+                            : "+f"(acc[mt][sp][0]), "+f"(acc[mt][sp][1]), "+f"(acc[mt][sp][2]), "+f"(acc[mt][sp][3])
+                            : "r"(afrag[mt][ks][0]), "r"(afrag[mt][ks][1]), "r"(afrag[mt][ks][2]), "r"(afrag[mt][ks][3]),
+                              "r"(bf0), "r"(bf1));
+                    }
+                }
+            }
+            // D fragment: rows g8 / g8+8 are hidden columns, columns 2*t4 / 2*t4+1 are batch rows
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int n = 2 * t4 + (q & 1);
+                    const int k = mpair * 32 + mt * 16 + g8 + (q >> 1) * 8;
+                    if (n < BT) partS[grp][n][k] = (acc[mt][2][q] + acc[mt][1][q]) + acc[mt][0][q];
+                }
+        }
+        __syncthreads();
+    }
+    if (hasElem) {
+        const float dh0 = dhCarry + partS[0][eb][ej] + partS[1][eb][ej] + partS[2][eb][ej] + partS[3][eb][ej];
         a.dh0[stateIdx] = dh0 * keepOf(a.mk.initial_hidden, stateIdx);
         a.dc0[stateIdx] = dc * keepOf(a.mk.initial_cell, stateIdx);
     }
@@ -348,6 +517,60 @@ __global__ void reduceWeightGradT(const float *__restrict__ partial, int splits,
     }
 }
 
+// dx = G_ih W_ih for a narrow N (= input size <= 128): a CTA owns 64 rows, thread (row, quarter) keeps
+// NO consecutive outputs in registers and walks K in chunks of 32 staged in shared memory (the G chunk
+// transposed so that neighbouring rows read neighbouring banks, the W chunk read as warp-wide
+// broadcasts).  The 64x64-tile kernel above wastes a third of its tile at N = 40.
+constexpr int kDxRows = 64, kDxChunk = 32;
+template <int NO>
+__global__ void __launch_bounds__(256) inputGradNarrow(const float *__restrict__ G, const float *__restrict__ W, int M, int N,
+                                                       int K, const uint8_t *__restrict__ mask, float *__restrict__ out) {
+    __shared__ float Gs[kDxChunk][kDxRows + 1];
+    __shared__ __align__(16) float Ws[kDxChunk][4 * NO];
+    const int tid = threadIdx.x, r = tid % kDxRows, p = tid / kDxRows;
+    const int row0 = blockIdx.x * kDxRows;
+    float acc[NO];
+#pragma unroll
+    for (int i = 0; i < NO; ++i) acc[i] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += kDxChunk) {
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+            const int lr = tid / 8 + v * 32, c4 = (tid % 8) * 4;
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row0 + lr < M && k0 + c4 < K) g = *reinterpret_cast<const float4 *>(G + static_cast<size_t>(row0 + lr) * K + k0 + c4);
+            Gs[c4][lr] = g.x; Gs[c4 + 1][lr] = g.y; Gs[c4 + 2][lr] = g.z; Gs[c4 + 3][lr] = g.w;
+        }
+        for (int i = tid; i < kDxChunk * 4 * NO; i += 256) {
+            const int kk = i / (4 * NO), n = i % (4 * NO);
+            Ws[kk][n] = (k0 + kk < K && n < N) ? W[static_cast<size_t>(k0 + kk) * N + n] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < kDxChunk; ++kk) {
+            const float g = Gs[kk][r];
+#pragma unroll
+            for (int i4 = 0; i4 < NO / 4; ++i4) {
+                const float4 w = *reinterpret_cast<const float4 *>(&Ws[kk][p * NO + i4 * 4]);
+                acc[i4 * 4 + 0] = fmaf(g, w.x, acc[i4 * 4 + 0]);
+                acc[i4 * 4 + 1] = fmaf(g, w.y, acc[i4 * 4 + 1]);
+                acc[i4 * 4 + 2] = fmaf(g, w.z, acc[i4 * 4 + 2]);
+                acc[i4 * 4 + 3] = fmaf(g, w.w, acc[i4 * 4 + 3]);
+            }
+        }
+        __syncthreads();
+    }
+    const int row = row0 + r;
+    if (row >= M) return;
+#pragma unroll
+    for (int i = 0; i < NO; ++i) {
+        const int n = p * NO + i;
+        if (n < N) {
+            const size_t o = static_cast<size_t>(row) * N + n;
+            out[o] = acc[i] * keepOf(mask, o);
+        }
+    }
+}
+
 // partial[which][s][c] = sum over the s-th chunk of rows of g[n][c]; blockIdx.y selects G_ih or G_hh.
 __global__ void columnSums(const float *__restrict__ gIh, const float *__restrict__ gHh, int rows, int C, int chunk,
                            float *__restrict__ partial) {
@@ -369,7 +592,7 @@ int splitsFor(int K, int tiles) {
 int tilesOf(int M, int N) { return ((M + kTile - 1) / kTile) * ((N + kTile - 1) / kTile); }
 
 constexpr int kBiasSplits = 64;
-constexpr int kMaxTensorSplits = 8;
+constexpr int kMaxTensorSplits = 40;
 
 }  // namespace
 
@@ -456,16 +679,47 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
         const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
         const int block = (C + 31) / 32 * 32;
+        const bool tensorPath = call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
+                                std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
+        if (tensorPath) {
+            RecurrentMmaArgs m{};
+            m.base = a;
+            m.weightCodes = call.weightHh;  // q-carrier codes as saved by the forward
+            m.channelScale = channelScales + C;
+            bool launched = false;
+#define RXMET_LSTM_MMA(HTV, BTV)                                                     \
+    if (!launched && H == 32 * HTV && bt == BTV) {                                    \
+        KernelTimer timer__("lstmRecurrentBackwardMma", st);                         \
+        recurrentBackwardMma<HTV, BTV><<<(B + BTV - 1) / BTV, 128 * HTV, 0, st>>>(m); \
+        launched = true;                                                              \
+    }
+            RXMET_LSTM_MMA(1, 1) RXMET_LSTM_MMA(1, 2) RXMET_LSTM_MMA(1, 4)
+            RXMET_LSTM_MMA(2, 1) RXMET_LSTM_MMA(2, 2) RXMET_LSTM_MMA(2, 4)
+            RXMET_LSTM_MMA(3, 1) RXMET_LSTM_MMA(3, 2) RXMET_LSTM_MMA(3, 4)
+            RXMET_LSTM_MMA(4, 1) RXMET_LSTM_MMA(4, 2) RXMET_LSTM_MMA(4, 4)
+#undef RXMET_LSTM_MMA
+            afterLaunch("lstmRecurrentBackwardMma");
+        }
         auto launch = [&](auto kernel, int BT) {
+            if (tensorPath) return;
             const size_t base = sizeof(float) * (static_cast<size_t>(BT) * C + 4 * static_cast<size_t>(BT) * H);
             const size_t room = static_cast<size_t>(smemMax) > base + 1024 ? static_cast<size_t>(smemMax) - base - 1024 : 0;
             // rows per gate block in shared memory; the remaining rows of a block live in registers
-            int perGate = static_cast<int>(std::min<size_t>(H, room / (sizeof(float) * 4 * H)));
-            if (perGate < H) perGate = perGate / 4 * 4;
+            // column stride of the transposed copy: a multiple of 4 floats whose quarter is odd keeps the
+            // 128-bit loads of eight neighbouring threads on distinct bank groups
+            auto strideFor = [](int rows) {
+                int sp = (rows + 3) / 4 * 4;
+                if ((sp / 4) % 2 == 0) sp += 4;
+                return sp;
+            };
+            int perGate = (H % 4 == 0) ? H : H / 4 * 4;
+            while (perGate > 0 && sizeof(float) * 4 * static_cast<size_t>(H) * strideFor(perGate) > room) perGate -= 4;
+            if (perGate < 0) perGate = 0;
             if (H - perGate > kRegRows)
                 fail(RXMET_ERR_UNSUPPORTED, "hidden size %d leaves %d weight rows per gate outside shared memory and registers", H, H - perGate);
             a.smemRows = perGate;
-            const size_t smem = base + sizeof(float) * 4 * static_cast<size_t>(perGate) * H;
+            a.smemStride = strideFor(std::max(perGate, 1));
+            const size_t smem = base + sizeof(float) * 4 * static_cast<size_t>(H) * a.smemStride;
             RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             {
                 KernelTimer timer__("lstmRecurrentBackward", st);
@@ -477,12 +731,28 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         else if (bt == 2) launch(recurrentBackward<2>, 2);
         else launch(recurrentBackward<1>, 1);
     }
-    {
-        KernelTimer timer__("lstmGemmNN", st);
-        gemmNN<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
-            gIh, wIh, static_cast<int>(rows), I, C, static_cast<const uint8_t *>(mk.input), call.grads.input);
+    if (I <= 128 && C % 4 == 0) {
+        const int perThread = (I + 3) / 4;  // outputs per thread, four threads share a row
+        const unsigned grid = static_cast<unsigned>((rows + kDxRows - 1) / kDxRows);
+        const uint8_t *inputMask = static_cast<const uint8_t *>(mk.input);
+        {
+            KernelTimer timer__("lstmInputGradNarrow", st);
+            if (perThread <= 4) inputGradNarrow<4><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+            else if (perThread <= 8) inputGradNarrow<8><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+            else if (perThread <= 12) inputGradNarrow<12><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+            else if (perThread <= 16) inputGradNarrow<16><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+            else if (perThread <= 24) inputGradNarrow<24><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+            else inputGradNarrow<32><<<grid, 256, 0, st>>>(gIh, wIh, static_cast<int>(rows), I, C, inputMask, call.grads.input);
+        }
+        afterLaunch("lstmInputGradNarrow");
+    } else {
+        {
+            KernelTimer timer__("lstmGemmNN", st);
+            gemmNN<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
+                gIh, wIh, static_cast<int>(rows), I, C, static_cast<const uint8_t *>(mk.input), call.grads.input);
+        }
+        afterLaunch("lstmGemmNN");
     }
-    afterLaunch("lstmGemmNN");
     // QAT on 8-bit activation grids: x and h_prev are integer codes, which the tensor-core GEMM
     // multiplies exactly; its ones row also yields the bias gradients.
     if (call.quantized && call.codesFitTensorPath && I % 4 == 0 && H % 4 == 0 && I <= 140 && H <= 140) {

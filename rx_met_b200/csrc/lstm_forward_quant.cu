@@ -76,50 +76,55 @@ struct PrepArgs {
     uint8_t *kWIh, *kWHh, *kBIh, *kBHh;  // optional clamp masks
 };
 
-// One thread per output channel: quantizes its weight rows and bias entries.
+// One warp per output channel and side (blockIdx.y: 0 = weight_ih, 1 = weight_hh): lanes quantize
+// consecutive words of the channel's weight row (coalesced), the row sum is reduced by shuffles, lane
+// 0 adds the rescaled bias term.
 __global__ void prepChannels(const PrepArgs a) {
     const int C = 4 * a.H;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (c >= C) return;
+    const int side = blockIdx.y;
     auto field = [&](int f) { return a.channel[static_cast<size_t>(f) * C + c]; };
-    for (int side = 0; side < 2; ++side) {
-        const int K = side ? a.H : a.I, kWords = side ? a.kWordsHh : a.kWordsIh;
-        const float *w = (side ? a.wHh : a.wIh) + static_cast<size_t>(c) * K;
-        const float scale = field(side ? kWHhScale : kWIhScale);
-        uint32_t *words = side ? a.wHhWords : a.wIhWords;
-        float *master = side ? a.mWHh : a.mWIh;
-        uint8_t *keep = side ? a.kWHh : a.kWIh;
-        int32_t sum = 0;
-        for (int kw = 0; kw < kWords; ++kw) {
-            uint32_t word = 0;
-            for (int i = 0; i < 4; ++i) {
-                const int k = kw * 4 + i;
-                int32_t q = 0;
-                if (k < K) {
-                    uint8_t m;
-                    q = quantizeCode(w[k], scale, 0, a.wLo, a.wHi, m);
-                    if (master) master[static_cast<size_t>(c) * K + k] = static_cast<float>(q);
-                    if (keep) keep[static_cast<size_t>(c) * K + k] = m;
-                }
-                sum += q;
-                word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+    const int K = side ? a.H : a.I, kWords = side ? a.kWordsHh : a.kWordsIh;
+    const float *w = (side ? a.wHh : a.wIh) + static_cast<size_t>(c) * K;
+    const float scale = field(side ? kWHhScale : kWIhScale);
+    uint32_t *words = side ? a.wHhWords : a.wIhWords;
+    float *master = side ? a.mWHh : a.mWIh;
+    uint8_t *keep = side ? a.kWHh : a.kWIh;
+    int32_t sum = 0;
+    for (int kw = lane; kw < kWords; kw += 32) {
+        uint32_t word = 0;
+        for (int i = 0; i < 4; ++i) {
+            const int k = kw * 4 + i;
+            int32_t q = 0;
+            if (k < K) {
+                uint8_t m;
+                q = quantizeCode(w[k], scale, 0, a.wLo, a.wHi, m);
+                if (master) master[static_cast<size_t>(c) * K + k] = static_cast<float>(q);
+                if (keep) keep[static_cast<size_t>(c) * K + k] = m;
             }
-            words[static_cast<size_t>(kw) * C + c] = word;
+            sum += q;
+            word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
         }
-        int32_t addend = (side ? a.hCorrection : a.xCorrection) * sum;
-        const float *b = side ? a.bHh : a.bIh;
-        if (b) {
-            uint8_t m;
-            const int32_t q = quantizeCode(b[c], field(side ? kBHhScale : kBIhScale), 0, a.bLo, a.bHi, m);
-            const DevRescale r{field(side ? kHhBiasMult : kIhBiasMult), field(side ? kHhBiasPow2 : kIhBiasPow2)};
-            addend += static_cast<int32_t>(rescaleF(static_cast<float>(q), r));
-            float *bm = side ? a.mBHh : a.mBIh;
-            uint8_t *bk = side ? a.kBHh : a.kBIh;
-            if (bm) bm[c] = static_cast<float>(q);
-            if (bk) bk[c] = m;
-        }
-        (side ? a.hhAddend : a.ihAddend)[c] = addend;
+        words[static_cast<size_t>(kw) * C + c] = word;
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane != 0) return;
+    int32_t addend = (side ? a.hCorrection : a.xCorrection) * sum;
+    const float *b = side ? a.bHh : a.bIh;
+    if (b) {
+        uint8_t m;
+        const int32_t q = quantizeCode(b[c], field(side ? kBHhScale : kBIhScale), 0, a.bLo, a.bHi, m);
+        const DevRescale r{field(side ? kHhBiasMult : kIhBiasMult), field(side ? kHhBiasPow2 : kIhBiasPow2)};
+        addend += static_cast<int32_t>(rescaleF(static_cast<float>(q), r));
+        float *bm = side ? a.mBHh : a.mBIh;
+        uint8_t *bk = side ? a.kBHh : a.kBIh;
+        if (bm) bm[c] = static_cast<float>(q);
+        if (bk) bk[c] = m;
+    }
+    (side ? a.hhAddend : a.ihAddend)[c] = addend;
 }
 
 // accumulator -> centred linear code (code - zero point) and its clamp flag.
@@ -458,7 +463,7 @@ void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, 
     pa.kWIh = m.weight_ih_clamped; pa.kWHh = m.weight_hh_clamped; pa.kBIh = m.bias_ih_clamped; pa.kBHh = m.bias_hh_clamped;
     {
         KernelTimer timer__("lstmPrepChannels", st);
-        prepChannels<<<(C + 63) / 64, 64, 0, st>>>(pa);
+        prepChannels<<<dim3((C + 7) / 8, 2), 256, 0, st>>>(pa);
     }
     afterLaunch("lstmPrepChannels");
 

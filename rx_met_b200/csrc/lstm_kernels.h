@@ -57,6 +57,7 @@ struct BackwardCall {
     Dequant dqX, dqH, dqC, dqGate[4], dqTanh;
     const float *weightIhScale = nullptr, *weightHhScale = nullptr;
     bool codesFitTensorPath = false;  // x and hidden grids span at most 256 codes around their zero points
+    bool weightCodesFitBf16 = false;  // weight_hh grid of at most 8 bits: codes are exact in bf16
 };
 size_t backwardWorkspaceBytes(int T, int B, int I, int H);
 void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);

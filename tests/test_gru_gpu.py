@@ -294,3 +294,23 @@ def test_python_module_mirrors_reference_binding(gl):
         ops.forward_quant_int_storage(True, T, B, I, H, t["W"].cpu(), t["R"], t["bw"], t["br"], t["x"], t["h0"], qp)
     out_q, hn_q = ops.forward_quantized_int_io(T, B, I, H, t["W"], t["R"], t["bw"], t["br"], out_i[6], None, qp)
     assert out_q.dtype == torch.int32 and tuple(out_q.shape) == (T, B, H) and tuple(hn_q.shape) == (1, B, H)
+
+
+@pytest.mark.parametrize("cfg_name", ["a16", "w8a8"])
+@pytest.mark.parametrize("shape", [(4, 3, 40, 256), (3, 2, 512, 256)], ids=lambda s: "x".join(map(str, s)))
+def test_kws_body_layer_shapes(gl, cfg_name, shape):
+    """Layer shapes of the stacked keyword-spotting body (hidden 256, input 40 or 512, W8 per channel,
+    A16 or A8): forward codes and masks bit-exact, QAT gradients within 1e-5."""
+    T, B, I, H = shape
+    cfg = ol.make_config(**CONFIGS[cfg_name])
+    prob, params = calibrated(shape, seed=9 + I, cfg=cfg, with_h0=True, x_scale=1.2)
+    want = ol.forward_quant("orc", *prob, params, training=True)
+    rc, got = gl.forward_quant(*prob, params, training=True)
+    assert rc == 0, got
+    assert_forward_equal(got, want)
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = np.random.default_rng(I).standard_normal((T, B, H)).astype(np.float32)
+    wb = ol.backward_quant(want, dh_new, want["h"], want["v"], params, want["masks"])
+    gb = gl.backward_quant(want, dh_new, want["h"], want["v"], params, want["masks"].arr)
+    for k in wb:
+        close(gb[k], wb[k], what=k)

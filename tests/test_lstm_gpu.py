@@ -130,25 +130,24 @@ def test_quantized_forward_is_bit_exact(cfg_kw, T, B, I, H, bias, state):
     assert torch.equal(out, out2) and torch.equal(hn, hn2) and torch.equal(cn, cn2) and empty == {}
 
 
-def test_quantized_forward_bench_shape_round_trip_and_qat_backward():
-    """BASELINE shape: bit-exact against the checker, and the QAT backward on the saved tensors."""
-    T, B, I, H = 20, 256, 40, 128
-    cfg = L.default_config(symmetric_activations=True)
-    p = ll.problem(T, B, I, H, seed=77, wscale=0.15)
-    box, bundle = calibrated_bundle(cfg, p)
+def qat_round_trip(T, B, I, H, seed, cfg, batch_first):
+    """Quantized training forward (bit-exact against the checker), then the QAT backward on the saved
+    tensors against the masked float backward of the checker on the dequantized tensors."""
+    p = ll.problem(T, B, I, H, seed=seed, wscale=0.15)
+    box, bundle = calibrated_bundle(cfg, p, scale_x=0.8)
     q, qmask = ll.quantize_masters("orc", p, box, with_masks=True)
     w_out, w_hn, w_cn, w_tr, w_mk = ll.forward_quantized_masked(box, T, B, q)
     m = mod()
     a = list(torch_args(p))
-    a[0] = a[0].transpose(0, 1).contiguous()
-    out, hn, cn, ck, _ = m.lstm_forward_quantized(*a, True, bundle, "pedantic", False, True)
+    if batch_first:
+        a[0] = a[0].transpose(0, 1).contiguous()
+    out, hn, cn, ck, _ = m.lstm_forward_quantized(*a, batch_first, bundle, "pedantic", False, True)
     for n in L.TRACE_VALUES:
         np.testing.assert_array_equal(ck["values"][n].cpu().numpy(), w_tr[n], err_msg=n)
         np.testing.assert_array_equal(ck["clamp_masks"][n].cpu().numpy(), w_mk[n], err_msg=n + " mask")
-    assert out.shape == (B, T, H)
-    # QAT backward: checker = masked float backward on the dequantized saved tensors
+    assert out.shape == ((B, T, H) if batch_first else (T, B, H))
     s = box.struct
-    deq = lambda v, op: ll.dequantize(v, [s.scale[op]], s.zero_point[op])
+    deq = lambda v, op: ll.dequantize(v, [s.scale[op]], s.zero_point[op])  # noqa: E731
     real = dict(p)
     real.update(x=deq(q["x"], L.INPUT), h0=deq(q["h0"], L.OUTPUT), c0=deq(q["c0"], L.CELL_STATE),
                 w_ih=ll.dequantize(q["w_ih"], box.channel_scales[0], 0, I), w_hh=ll.dequantize(q["w_hh"], box.channel_scales[1], 0, H))
@@ -165,11 +164,24 @@ def test_quantized_forward_bench_shape_round_trip_and_qat_backward():
     qm, qk = ck["quantized_master"], ck["master_clamp_masks"]
     order = ("input", "weight_ih", "weight_hh", "bias_ih", "bias_hh", "h_0", "c_0")
     values = [ck["values"][n] for n in ("gate_outputs", "cell_states", "cell_tanh_outputs", "hidden_outputs")]
-    got = m.lstm_backward_qat([qm[n] for n in order], True, bundle, values, dev(g[0]), dev(g[1]), dev(g[2]),
+    got = m.lstm_backward_qat([qm[n] for n in order], batch_first, bundle, values, dev(g[0]), dev(g[1]), dev(g[2]),
                               [qk[n] for n in order], [ck["clamp_masks"][n] for n in L.TRACE_VALUES])
-    close(got[0].transpose(0, 1).cpu().numpy(), want["input"], 2e-5, "input")
+    dx = got[0].transpose(0, 1) if batch_first else got[0]
+    close(dx.cpu().numpy(), want["input"], 2e-5, "input")
     for n, t in list(zip(L.MASTER_VALUES, got))[1:]:
         close(t.cpu().numpy().reshape(want[n].shape), want[n], 2e-5, n)
+
+
+def test_quantized_forward_bench_shape_round_trip_and_qat_backward():
+    """BASELINE shape (tensor-core backward, two batch rows per CTA)."""
+    qat_round_trip(20, 256, 40, 128, 77, L.default_config(symmetric_activations=True), batch_first=True)
+
+
+@pytest.mark.parametrize("T,B,I,H", [(6, 3, 8, 32), (5, 5, 12, 64), (4, 2, 40, 96), (5, 700, 16, 32), (6, 4, 9, 20)])
+def test_qat_backward_other_tile_shapes(T, B, I, H):
+    """Every hidden size the tensor-core backward is built for, one / two / four rows per CTA, an
+    asymmetric grid, and a hidden size that takes the SIMT kernel (H = 20)."""
+    qat_round_trip(T, B, I, H, 7 + H, L.default_config(), batch_first=False)
 
 
 def test_calibration_session_matches_checker():
