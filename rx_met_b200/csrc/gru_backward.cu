@@ -710,19 +710,33 @@ __global__ void __launch_bounds__(256, 2) weightGradMma(const WeightGradProblem 
     }
 }
 
-// weight[m][n] = scale * mask * sum_s partial[s][m][n] (m < M); bias[n] = biasMask * sum_s partial[s][M][n]
-__global__ void reduceWeightGrad(const float *__restrict__ partial, int splits, int M, int N, float scale,
-                                 const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
-                                 float *__restrict__ weight, float *__restrict__ bias) {
+// weight[m][n] = scale * mask * sum_s partial[s][m][n] (m < M); bias[n] = biasMask * sum_s partial[s][M][n].
+// A CTA owns 64 outputs; its four thread layers each sum every fourth split and layer 0 adds the
+// four sums in layer order, so the result does not depend on the launch.
+// A set status word (a bounded wait of the producing kernel gave up) turns the results into NaN.
+constexpr int kReduceLayers = 4, kReduceWidth = 64;
+__global__ void __launch_bounds__(kReduceWidth * kReduceLayers)
+reduceWeightGrad(const float *__restrict__ partial, int splits, int M, int N, float scale,
+                 const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
+                 const int *__restrict__ status, float *__restrict__ weight, float *__restrict__ bias) {
+    __shared__ float layer[kReduceLayers][kReduceWidth];
     const size_t total = static_cast<size_t>(M + 1) * N;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        float s = 0.0f;
-        for (int sp = 0; sp < splits; ++sp) s += partial[static_cast<size_t>(sp) * total + i];
-        const size_t m = i / N, n = i % N;
-        if (m < static_cast<size_t>(M)) weight[i] = s * scale * keepOf(weightMask, i);
-        else bias[n] = s * keepOf(biasMask, n);
+    const size_t i = static_cast<size_t>(blockIdx.x) * kReduceWidth + threadIdx.x;
+    float s = 0.0f;
+    if (i < total) {
+#pragma unroll 4
+        for (int sp = threadIdx.y; sp < splits; sp += kReduceLayers) s += partial[static_cast<size_t>(sp) * total + i];
     }
+    layer[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y != 0 || i >= total) return;
+    s = layer[0][threadIdx.x];
+#pragma unroll
+    for (int l = 1; l < kReduceLayers; ++l) s += layer[l][threadIdx.x];
+    if (status && *status) s = __int_as_float(0x7fc00000);
+    const size_t m = i / N, n = i % N;
+    if (m < static_cast<size_t>(M)) weight[i] = s * scale * keepOf(weightMask, i);
+    else bias[n] = s * keepOf(biasMask, n);
 }
 
 // out[i] = mask[i] * sum_s partial[s][i], s ascending.
@@ -806,16 +820,37 @@ constexpr int kBiasSplits = 64;
 
 namespace wgrad {
 
-int plan(int K, int N, int sms, int *chunkK) {
+constexpr int kMaxSms = 160;
+
+Plan plan(int K, int M, int N, int sms) {
+    Plan pl;
+    sms = std::min(sms, kMaxSms);
+    pl.tensorMemory = tensorMemoryPath(M, N);
+    if (pl.tensorMemory) {
+        pl.splits = planTensorMemory(K, N, sms, &pl.chunkK);
+        return pl;
+    }
     const int nTiles = (N + gru::kWgCols - 1) / gru::kWgCols;
-    int splits = std::max(1, std::min((2 * sms + 2 * nTiles - 1) / (2 * nTiles), (K + 255) / 256));
-    *chunkK = ((K + splits - 1) / splits + gru::kWgChunk - 1) / gru::kWgChunk * gru::kWgChunk;
-    return (K + *chunkK - 1) / *chunkK;
+    const int splits = std::max(1, std::min((2 * sms + 2 * nTiles - 1) / (2 * nTiles), (K + 255) / 256));
+    pl.chunkK = ((K + splits - 1) / splits + gru::kWgChunk - 1) / gru::kWgChunk * gru::kWgChunk;
+    pl.splits = (K + pl.chunkK - 1) / pl.chunkK;
+    return pl;
 }
 
-void launch(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+int splitBound(int K, int M, int N) {
+    // both kernels ask for about two CTAs per SM spread over the column tiles
+    (void)M;
+    return std::max(1, std::min((K + gru::kWgChunk - 1) / gru::kWgChunk, 2 * kMaxSms + 8));
+}
+
+void launch(const Problem &prob, int K, int N, const Plan &pl, cudaStream_t st) {
+    if (pl.tensorMemory) {
+        launchTensorMemory(prob, K, N, pl.chunkK, pl.splits, st);
+        return;
+    }
+    const int chunkK = pl.chunkK;
     const int mt = (prob.M + 1 + 15) / 16;
-    const dim3 grid((N + gru::kWgCols - 1) / gru::kWgCols, splits);
+    const dim3 grid((N + gru::kWgCols - 1) / gru::kWgCols, pl.splits);
     KernelTimer timer__("weightGradMma", st);
     switch (mt) {
 #define RXMET_WG_CASE(MTV) case MTV: gru::weightGradMma<MTV><<<grid, 256, 0, st>>>(prob, K, N, chunkK); break;
@@ -847,10 +882,10 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(splitW * I * C);
     ws.take<float>(splitR * H * C);
     ws.take<float>(2 * kBiasSplits * C);
-    // tensor-core path: at most ceil(rows/256) splits of (I+1) and (H+1) rows
-    const size_t splitT = std::min<size_t>((rows + 255) / 256, 2 * 148 + 8);
-    ws.take<float>(splitT * (I + 1) * C);
-    ws.take<float>(splitT * (H + 1) * C);
+    // tensor-core path: split-K partials of (I+1) and (H+1) rows and the status word
+    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C))) * (I + 1) * C);
+    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
+    ws.take<int>(1);
     return ws.used() + 4096;
 }
 
@@ -996,30 +1031,31 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     if (tensorGrads) {
         const Exec &e = *call.exec;
         const int K = static_cast<int>(rows);
-        const int nTiles = (C + kWgCols - 1) / kWgCols;
-        int splits = std::max(1, std::min((2 * sms + 2 * nTiles - 1) / (2 * nTiles), (K + 255) / 256));
-        const int chunkK = ((K + splits - 1) / splits + kWgChunk - 1) / kWgChunk * kWgChunk;
-        splits = (K + chunkK - 1) / chunkK;
+        const wgrad::Plan planX = wgrad::plan(K, I, C, sms), planH = wgrad::plan(K, H, C, sms);
         WeightGradProblem px{}, ph{};
         px.aCodes = call.x_q; px.aZero = e.gate.zp[RXMET_GRU_X]; px.M = I; px.B = dp;
-        px.partial = ws.take<float>(static_cast<size_t>(splits) * (I + 1) * C);
+        px.partial = ws.take<float>(static_cast<size_t>(planX.splits) * (I + 1) * C);
         ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
-        ph.partial = ws.take<float>(static_cast<size_t>(splits) * (H + 1) * C);
-        auto launchWg = [&](const WeightGradProblem &prob) { wgrad::launch(prob, K, C, chunkK, splits, st); };
-        launchWg(px);
-        afterLaunch("weightGradMma");
-        launchWg(ph);
-        afterLaunch("weightGradMma");
+        ph.partial = ws.take<float>(static_cast<size_t>(planH.splits) * (H + 1) * C);
+        int *status = ws.take<int>(1);
+        px.status = ph.status = status;
+        if (planX.tensorMemory || planH.tensorMemory) RXMET_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+        wgrad::launch(px, K, C, planX, st);
+        afterLaunch("weightGrad");
+        wgrad::launch(ph, K, C, planH, st);
+        afterLaunch("weightGrad");
         {
             KernelTimer timer__("reduceWeightGrad", st);
-            reduceWeightGrad<<<gridFor(static_cast<size_t>(I + 1) * C, 256), 256, 0, st>>>(
-                px.partial, splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw);
+            reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(I + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
+                px.partial, planX.splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, planX.tensorMemory ? status : nullptr,
+                call.dW, call.dbw);
         }
         afterLaunch("reduceWeightGrad");
         {
             KernelTimer timer__("reduceWeightGrad", st);
-            reduceWeightGrad<<<gridFor(static_cast<size_t>(H + 1) * C, 256), 256, 0, st>>>(
-                ph.partial, splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr);
+            reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(H + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
+                ph.partial, planH.splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, planH.tensorMemory ? status : nullptr,
+                call.dR, call.dbr);
         }
         afterLaunch("reduceWeightGrad");
         return;

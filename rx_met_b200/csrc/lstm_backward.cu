@@ -490,30 +490,36 @@ __global__ void __launch_bounds__(256) gemmNN(const float *__restrict__ A, const
 
 // weight[c][m] = scale * keep * sum_s partial[s][m][c] (m < M); bias[c] = keep * sum_s partial[s][M][c]:
 // reduces the split-K partials of the tensor-core GEMM and writes the transposed [4H][M] layout.
-__global__ void reduceWeightGradT(const float *__restrict__ partial, int splits, int M, int C, float scale,
-                                  const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
-                                  float *__restrict__ weight, float *__restrict__ bias) {
-    __shared__ float tile[32][33];
+// A CTA owns 32 channels x 8 rows; its four thread layers each sum every fourth split, and layer 0
+// adds the four sums in layer order, so the result does not depend on the launch.
+// A set status word (a bounded wait of the producing kernel gave up) turns the results into NaN.
+constexpr int kReduceLayers = 4, kReduceRows = 8;
+__global__ void __launch_bounds__(32 * kReduceRows * kReduceLayers)
+reduceWeightGradT(const float *__restrict__ partial, int splits, int M, int C, float scale,
+                  const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
+                  const int *__restrict__ status, float *__restrict__ weight, float *__restrict__ bias) {
+    __shared__ float layer[kReduceLayers][kReduceRows][32];
     const size_t slab = static_cast<size_t>(M + 1) * C;
-    const int c0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
-    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
-        const int m = m0 + dy, c = c0 + threadIdx.x;
-        float s = 0.0f;
-        if (m <= M && c < C)
-            for (int sp = 0; sp < splits; ++sp) s += partial[static_cast<size_t>(sp) * slab + static_cast<size_t>(m) * C + c];
-        tile[dy][threadIdx.x] = s;
+    const int c = blockIdx.x * 32 + threadIdx.x, m = blockIdx.y * kReduceRows + threadIdx.y;
+    const bool inside = m <= M && c < C;
+    float s = 0.0f;
+    if (inside) {
+        const float *src = partial + static_cast<size_t>(m) * C + c;
+#pragma unroll 4
+        for (int sp = threadIdx.z; sp < splits; sp += kReduceLayers) s += src[static_cast<size_t>(sp) * slab];
     }
+    layer[threadIdx.z][threadIdx.y][threadIdx.x] = s;
     __syncthreads();
-    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
-        const int c = c0 + dy, m = m0 + threadIdx.x;
-        if (c >= C) continue;
-        const float s = tile[threadIdx.x][dy];
-        if (m < M) {
-            const size_t o = static_cast<size_t>(c) * M + m;
-            weight[o] = s * scale * keepOf(weightMask, o);
-        } else if (m == M && bias) {
-            bias[c] = s * keepOf(biasMask, c);
-        }
+    if (threadIdx.z != 0 || !inside) return;
+    s = layer[0][threadIdx.y][threadIdx.x];
+#pragma unroll
+    for (int l = 1; l < kReduceLayers; ++l) s += layer[l][threadIdx.y][threadIdx.x];
+    if (status && *status) s = __int_as_float(0x7fc00000);
+    if (m < M) {
+        const size_t o = static_cast<size_t>(c) * M + m;
+        weight[o] = s * scale * keepOf(weightMask, o);
+    } else if (bias) {
+        bias[c] = s * keepOf(biasMask, c);
     }
 }
 
@@ -608,8 +614,9 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(2 * kBiasSplits * C);
     ws.take<float>(2 * C);     // per-channel weight scales (QAT)
     ws.take<float>(rows * H);  // h_prev codes for the tensor-core weight gradient (QAT)
-    ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (I + 1) * C);
-    ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (H + 1) * C);
+    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C))) * (I + 1) * C);
+    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
+    ws.take<int>(1);              // status word of the tensor-memory weight-gradient kernel
     ws.take<uint32_t>(rows * H);  // packed per-step clamp flags
     return ws.used() + 1024;
 }
@@ -630,8 +637,9 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     float *partBias = ws.take<float>(2 * kBiasSplits * static_cast<size_t>(C));
     float *channelScales = ws.take<float>(2 * static_cast<size_t>(C));
     float *hPrev = ws.take<float>(rows * H);
-    float *tensorIh = ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (I + 1) * C);
-    float *tensorHh = ws.take<float>(static_cast<size_t>(kMaxTensorSplits) * (H + 1) * C);
+    float *tensorIh = ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, C)) * (I + 1) * C);
+    float *tensorHh = ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, C)) * (H + 1) * C);
+    int *tensorStatus = ws.take<int>(1);
     uint32_t *stepMasks = ws.take<uint32_t>(rows * H);
 
     const float *wIh = call.weightIh, *wHh = call.weightHh;
@@ -762,15 +770,18 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         if (T > 1)
             RXMET_CUDA(cudaMemcpyAsync(hPrev + static_cast<size_t>(B) * H, call.hiddenOutputs, stateBytes * (T - 1),
                                        cudaMemcpyDeviceToDevice, st));
-        int device = 0, sms = 0, chunkK = 0;
+        int device = 0, sms = 0;
         RXMET_CUDA(cudaGetDevice(&device));
         RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-        int splits = wgrad::plan(static_cast<int>(rows), C, sms, &chunkK);
-        if (splits > kMaxTensorSplits) {
-            splits = kMaxTensorSplits;
-            chunkK = ((static_cast<int>(rows) + splits - 1) / splits + 31) / 32 * 32;
-            splits = (static_cast<int>(rows) + chunkK - 1) / chunkK;
-        }
+        auto planFor = [&](int M) {
+            wgrad::Plan pl = wgrad::plan(static_cast<int>(rows), M, C, sms);
+            if (!pl.tensorMemory && pl.splits > kMaxTensorSplits) {
+                pl.chunkK = ((static_cast<int>(rows) + kMaxTensorSplits - 1) / kMaxTensorSplits + 31) / 32 * 32;
+                pl.splits = (static_cast<int>(rows) + pl.chunkK - 1) / pl.chunkK;
+            }
+            return pl;
+        };
+        const wgrad::Plan planX = planFor(I), planH = planFor(H);
         wgrad::Problem px{}, ph{};
         px.aFloat = call.x; px.aFloatZero = call.dqX.zeroPoint; px.M = I; px.B = gIh; px.partial = tensorIh;
         ph.aFloat = hPrev; ph.aFloatZero = call.h0 ? call.dqH.zeroPoint : 0.0f; ph.M = H; ph.B = gHh; ph.partial = tensorHh;
@@ -778,19 +789,23 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             // a missing h0 means real zeros, i.e. the zero-point code: fill instead of zeroing
             fail(RXMET_ERR_INVALID_ARGUMENT, "the QAT backward needs the quantized initial hidden state");
         }
-        wgrad::launch(px, static_cast<int>(rows), C, chunkK, splits, st);
-        afterLaunch("weightGradMma");
-        wgrad::launch(ph, static_cast<int>(rows), C, chunkK, splits, st);
-        afterLaunch("weightGradMma");
-        auto reduce = [&](const float *partial, int M, float scale, const uint8_t *wm, const uint8_t *bm, float *w, float *b) {
+        px.status = ph.status = tensorStatus;
+        if (planX.tensorMemory || planH.tensorMemory) RXMET_CUDA(cudaMemsetAsync(tensorStatus, 0, sizeof(int), st));
+        wgrad::launch(px, static_cast<int>(rows), C, planX, st);
+        afterLaunch("weightGrad");
+        wgrad::launch(ph, static_cast<int>(rows), C, planH, st);
+        afterLaunch("weightGrad");
+        auto reduce = [&](const float *partial, const wgrad::Plan &pl, int M, float scale, const uint8_t *wm, const uint8_t *bm,
+                          float *w, float *b) {
             {
                 KernelTimer timer__("lstmReduceWeightGradT", st);
-                reduceWeightGradT<<<dim3((C + 31) / 32, (M + 1 + 31) / 32), dim3(32, 8), 0, st>>>(partial, splits, M, C, scale, wm, bm, w, b);
+                reduceWeightGradT<<<dim3((C + 31) / 32, (M + 1 + kReduceRows - 1) / kReduceRows), dim3(32, kReduceRows, kReduceLayers), 0, st>>>(
+                    partial, pl.splits, M, C, scale, wm, bm, pl.tensorMemory ? tensorStatus : nullptr, w, b);
             }
             afterLaunch("lstmReduceWeightGradT");
         };
-        reduce(tensorIh, I, call.dqX.scale, mk.weight_ih, mk.bias_ih, call.grads.weight_ih, call.grads.bias_ih);
-        reduce(tensorHh, H, call.dqH.scale, mk.weight_hh, mk.bias_hh, call.grads.weight_hh, call.grads.bias_hh);
+        reduce(tensorIh, planX, I, call.dqX.scale, mk.weight_ih, mk.bias_ih, call.grads.weight_ih, call.grads.bias_ih);
+        reduce(tensorHh, planH, H, call.dqH.scale, mk.weight_hh, mk.bias_hh, call.grads.weight_hh, call.grads.bias_hh);
         return;
     }
     auto weightGrad = [&](const float *G, RowSource X, int N, int splits, float *partial, const uint8_t *mask, float *out) {

@@ -1,7 +1,7 @@
 // Tensor-core weight-gradient GEMM shared by the GRU and LSTM backward passes.
 //
 // partial[s][m][n] = sum over the s-th chunk of the K rows of A[k][m] * B[k][n], for m < M, and
-// partial[s][M][n] = the column sums of B (a row of ones appended to A), i.e. the bias gradient.
+// partial[s][M][n] = the column sums of B over the same rows, i.e. the bias gradient.
 // A holds small integers (activation codes minus their zero point, magnitude at most 256), which
 // bf16 represents exactly; B (fp32 gradients) is split into three bf16 terms that together carry
 // all 24 significand bits, so every product is exact and only the fp32 accumulation rounds.
@@ -23,12 +23,27 @@ struct Problem {
     int M = 0;                        // real rows (multiple of 4, at most 143); row M is the ones row
     const float *B = nullptr;         // [K][N] gradients, N a multiple of 4
     float *partial = nullptr;         // [splits][M+1][N]
+    int *status = nullptr;            // device word, set to 1 when a bounded wait of the kernel gave up
 };
 
-// Number of K splits for a problem with N output columns on a device with `sms` SMs; chunkK
-// receives the rows per split (a multiple of the kernel's K tile).
-int plan(int K, int N, int sms, int *chunkK);
-void launch(const Problem &problem, int K, int N, int chunkK, int splits, cudaStream_t stream);
+// How a problem is cut: K splits of chunkK rows each (a multiple of the kernel's K tile), and
+// which kernel runs it.  The tcgen05 kernel (accumulators in tensor memory) takes problems with
+// at most 128 rows whose column count is a multiple of 128, 192 or 256; the others run on the
+// mma.sync kernel.  Setting RXMET_WGRAD_MMA_SYNC in the environment forces the latter.
+struct Plan {
+    int splits = 0;
+    int chunkK = 0;
+    bool tensorMemory = false;
+};
+Plan plan(int K, int M, int N, int sms);
+// Upper bound of plan(...).splits over every device, for sizing the partial buffers.
+int splitBound(int K, int M, int N);
+void launch(const Problem &problem, int K, int N, const Plan &plan, cudaStream_t stream);
+
+// The tcgen05 kernel (weight_grad_umma.cu).
+bool tensorMemoryPath(int M, int N);
+int planTensorMemory(int K, int N, int sms, int *chunkK);
+void launchTensorMemory(const Problem &problem, int K, int N, int chunkK, int splits, cudaStream_t stream);
 
 }  // namespace wgrad
 }  // namespace rxmet

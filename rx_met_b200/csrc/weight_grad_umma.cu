@@ -1,0 +1,418 @@
+// Weight-gradient GEMM on the fifth-generation tensor cores (tcgen05.mma, accumulators in
+// tensor memory).
+//
+//   partial[s][m][n] = sum over the K rows of split s of A[k][m] * B[k][n]      (m < M)
+//   partial[s][M][n] = sum over the same rows of B[k][n]                        (bias gradient)
+//
+// A holds small integers (activation codes minus their zero point), exact in bf16.  B (fp32
+// gradients) is split into three bf16 terms that together carry all 24 significand bits, and the
+// three products accumulate into the same fp32 accumulator, so every product is exact and only
+// the accumulation rounds, as in an fp32 GEMM.
+//
+// One CTA owns a 128 x NT accumulator tile (NT columns of tensor memory) over one K split.
+// Both operands arrive from HBM with the contraction index outermost ([k][m], [k][n]), which is
+// the "MN-major" operand form of the instruction: no transposition anywhere.  The producer
+// threads load fp32 / int32 rows, convert, and store 16-byte pieces straight into the
+// un-swizzled canonical operand layout (8 k-rows x 8 mn-elements per 128-byte core matrix);
+// one thread then issues the MMAs for the stage and commits them to an mbarrier.  Two operand
+// stages alternate, so the conversion of one 32-row chunk overlaps the tensor work of the
+// previous one.  One CTA per SM: the raw rows reach shared memory through a ring of cp.async
+// copies issued several chunks ahead, which keeps enough bytes in flight to cover the HBM
+// latency from a single CTA and halves the number of K splits (and partial tiles) against two
+// CTAs per SM.
+//
+// Every mbarrier wait is bounded: when a wait gives up the CTA records it in the status word and
+// carries on with the same control flow (the results are then wrong, and the reduction that
+// follows turns them into NaN), so the kernel always reaches the point where it gives its tensor
+// memory back.
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.h"
+#include "weight_grad_mma.h"
+
+namespace rxmet {
+namespace wgrad {
+namespace {
+
+constexpr int kStageRows = 32;          // K rows per stage: two MMA k-steps of 16
+constexpr int kTileM = 128;             // accumulator rows = tensor-memory lanes
+constexpr uint32_t kCore = 128;         // bytes of one core matrix: 8 k-rows of 16 bytes
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smemAddr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ uint32_t packBf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16Lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16Hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Shared-memory operand descriptor, no swizzle, MN-major: element (mn, k) lives at
+//   (mn / 8) * mnGroupStride + (k / 8) * kGroupStride + (k % 8) * 16 + (mn % 8) * 2   bytes.
+// Bits: start address >> 4 in [0,14), k-group stride >> 4 in [16,30) ("leading byte offset"),
+// mn-group stride >> 4 in [32,46) ("stride byte offset"), descriptor version 1 in [46,48).
+__device__ __forceinline__ uint64_t operandDescriptor(uint32_t addr, uint32_t kGroupStride, uint32_t mnGroupStride) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3fffu) | (static_cast<uint64_t>((kGroupStride >> 4) & 0x3fffu) << 16) |
+           (static_cast<uint64_t>((mnGroupStride >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator (bits [4,6) = 1), bf16 A and B
+// ([7,10) = [10,13) = 1), both MN-major (bits 15, 16), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t instructionDescriptor(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mmaBf16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n"
+        :
+        : "r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void commitTo(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Polls the barrier phase of the given parity; false when the limit ran out.
+__device__ __forceinline__ bool waitPhase(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct Converted {
+    uint4 hi, mid, lo;
+};
+
+// Eight fp32 values -> three bf16x8 vectors whose sum is the input exactly.
+__device__ __forceinline__ Converted splitThree(const float4 &u, const float4 &v) {
+    const float x[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+    uint32_t h[4], m[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        h[i] = packBf16(x[2 * i], x[2 * i + 1]);
+        const float r0 = x[2 * i] - bf16Lo(h[i]), r1 = x[2 * i + 1] - bf16Hi(h[i]);
+        m[i] = packBf16(r0, r1);
+        l[i] = packBf16(r0 - bf16Lo(m[i]), r1 - bf16Hi(m[i]));
+    }
+    Converted c;
+    c.hi = make_uint4(h[0], h[1], h[2], h[3]);
+    c.mid = make_uint4(m[0], m[1], m[2], m[3]);
+    c.lo = make_uint4(l[0], l[1], l[2], l[3]);
+    return c;
+}
+
+// 16-byte asynchronous copy global -> shared; `valid` false writes zeros instead.
+__device__ __forceinline__ void copyAsync16(void *dst, const void *src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smemAddr(dst)), "l"(src), "r"(valid ? 16u : 0u)
+                 : "memory");
+}
+
+// Depth of the ring of raw (unconverted) chunks, chosen so that ring + operand stages fill the
+// shared memory of an SM.
+template <int NT>
+struct Geometry {
+    static constexpr int kThreads = 2 * NT;                      // two thread halves, two k-groups of B each
+    static constexpr int kWarps = kThreads / 32;
+    static constexpr int kAPieces = (16 + kWarps - 1) / kWarps;  // A pieces (k-group x 32 rows of m) per warp
+    static constexpr int kSlots = 4 + 2 * kAPieces;              // 16-byte slots per thread and chunk
+    static constexpr uint32_t kAKStride = (kTileM / 8) * kCore;  // bytes between k-groups of the A tile
+    static constexpr uint32_t kBKStride = (NT / 8) * kCore;
+    static constexpr uint32_t kABytes = (kStageRows / 8) * kAKStride;
+    static constexpr uint32_t kBBytes = (kStageRows / 8) * kBKStride;
+    static constexpr uint32_t kStageBytes = kABytes + 3 * kBBytes;
+    static constexpr uint32_t kRawBytes = kSlots * 16 * kThreads;
+    static constexpr int kRing = NT <= 128 ? 4 : 2;
+    static_assert(2 * kStageBytes + kRing * kRawBytes <= 227 * 1024, "shared memory of one SM");
+    static constexpr size_t kSmem = 2 * kStageBytes + static_cast<size_t>(kRing) * kRawBytes;
+};
+
+// blockDim.x == 2 NT, one CTA per SM.  Warp w produces the B columns [32 (w % (NT/32)), + 32) of
+// the tile for two of the four k-groups of a chunk (which two: w / (NT/32)): lane -> k-row
+// (lane % 8) of a k-group and 8-column piece (lane / 8), so a warp's 16-byte operand stores cover
+// four whole core matrices (512 contiguous bytes) and its loads cover 8 rows x 128 contiguous bytes.  Each thread copies its own pieces of the next chunks into a
+// ring of raw buffers with cp.async, kRing chunks ahead; a warp later converts exactly the pieces
+// it copied, so the ring needs no CTA-wide barrier of its own.
+template <int NT>
+__global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int K, int N, int chunkK, int *status) {
+    using G = Geometry<NT>;
+    constexpr int NW = G::kWarps, CW = NT / 32, AT = G::kAPieces, R = G::kRing, TH = G::kThreads;
+    constexpr uint32_t kAKStride = G::kAKStride, kBKStride = G::kBKStride, kABytes = G::kABytes, kBBytes = G::kBBytes;
+    constexpr uint32_t kStageBytes = G::kStageBytes;
+    constexpr uint32_t kTmemCols = NT > 128 ? 256 : 128;
+    constexpr uint32_t kIdesc = instructionDescriptor(NT);
+
+    extern __shared__ __align__(128) uint8_t stages[];
+    __shared__ __align__(8) uint64_t bars[3];
+    __shared__ uint32_t tmemSlot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rk = lane & 7, cq = lane >> 3;
+    const int cw = warp % CW, half = warp / CW;  // column warp and k-group half of the B pieces
+    const int n0 = blockIdx.x * NT;
+    const int kBegin = blockIdx.y * chunkK, kEnd = min(K, kBegin + chunkK);
+    const int chunks = (kEnd - kBegin + kStageRows - 1) / kStageRows;
+    const int M = p.M, quads = (M + 31) / 32;
+    uint4 *raw = reinterpret_cast<uint4 *>(stages + 2 * kStageBytes);  // [R][kSlots][TH]
+
+    if (tid == 0) {
+        failed = 0;
+        for (int i = 0; i < 3; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smemAddr(&bars[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // rows of A beyond M stay zero for the whole kernel
+    for (uint32_t i = tid; i < 2 * kABytes / 16; i += TH) {
+        const uint32_t stage = i / (kABytes / 16), off = i % (kABytes / 16);
+        *reinterpret_cast<uint4 *>(stages + stage * kStageBytes + off * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemSlot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    const void *aBase = p.aCodes ? static_cast<const void *>(p.aCodes) : static_cast<const void *>(p.aFloat);
+    // Copies this warp's pieces of chunk `chunk` into ring entry `slot` and closes the group.  A
+    // piece is 8 k-rows x 128 bytes; one copy instruction of the warp covers four whole rows of
+    // it (lane -> row lane / 8, 16-byte part lane % 8), so every request is a full 128-byte line.
+    // Part p of row r is kept at position r * 8 + (p ^ r) of the piece, which makes both these
+    // writes and the converting reads (lane -> row lane % 8, parts 2 (lane / 8) and + 1) free of
+    // bank conflicts.
+    constexpr int kPieces = 2 + AT;
+    auto issueChunk = [&](int chunk, int slot) {
+        const int k0 = kBegin + chunk * kStageRows;
+        uint4 *dst = raw + (static_cast<size_t>(slot) * NW + warp) * kPieces * 64;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int wrow = 4 * i + (lane >> 3), part = lane & 7, pos = wrow * 8 + (part ^ wrow);
+#pragma unroll
+            for (int gi = 0; gi < 2; ++gi) {
+                const int k = k0 + 8 * (2 * half + gi) + wrow;
+                const bool ok = k < kEnd;
+                copyAsync16(dst + gi * 64 + pos, ok ? p.B + static_cast<size_t>(k) * N + n0 + 32 * cw + 4 * part : p.B, ok);
+            }
+#pragma unroll
+            for (int t = 0; t < AT; ++t) {
+                const int task = warp + t * NW, m = 32 * (task >> 2) + 4 * part;
+                const int k = k0 + 8 * (task & 3) + wrow;
+                const bool ok = task < 4 * quads && k < kEnd && m < M;
+                const size_t at = ok ? static_cast<size_t>(k) * M + m : 0;
+                copyAsync16(dst + (2 + t) * 64 + pos, static_cast<const uint32_t *>(aBase) + at, ok);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int r = 0; r < R; ++r) issueChunk(r, r);
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmemSlot;
+
+    float csum[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) csum[j] = 0.0f;
+
+    // converts ring entry `slot` into the operand stage
+    auto convertChunk = [&](int slot, uint8_t *stage) {
+        const uint4 *src = raw + (static_cast<size_t>(slot) * NW + warp) * kPieces * 64;
+        const int posU = rk * 8 + ((2 * cq) ^ rk), posV = rk * 8 + ((2 * cq + 1) ^ rk);
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+            const int g = 2 * half + gi;
+            const uint4 ru = src[gi * 64 + posU], rv = src[gi * 64 + posV];
+            const float4 u = make_float4(__uint_as_float(ru.x), __uint_as_float(ru.y), __uint_as_float(ru.z), __uint_as_float(ru.w));
+            const float4 v = make_float4(__uint_as_float(rv.x), __uint_as_float(rv.y), __uint_as_float(rv.z), __uint_as_float(rv.w));
+            csum[0] += u.x; csum[1] += u.y; csum[2] += u.z; csum[3] += u.w;
+            csum[4] += v.x; csum[5] += v.y; csum[6] += v.z; csum[7] += v.w;
+            const Converted c = splitThree(u, v);
+            uint8_t *dst = stage + kABytes + (4 * cw + cq) * kCore + rk * 16 + g * kBKStride;
+            *reinterpret_cast<uint4 *>(dst) = c.hi;
+            *reinterpret_cast<uint4 *>(dst + kBBytes) = c.mid;
+            *reinterpret_cast<uint4 *>(dst + 2 * kBBytes) = c.lo;
+        }
+#pragma unroll
+        for (int t = 0; t < AT; ++t) {
+            const int task = warp + t * NW, g = task & 3, quad = task >> 2;
+            if (task >= 4 * quads) continue;
+            const uint4 ru = src[(2 + t) * 64 + posU], rv = src[(2 + t) * 64 + posV];
+            float x[8];
+            // zero-filled pieces decode to some finite value: they only meet zero rows of B or
+            // accumulator rows that are never stored
+            if (p.aCodes) {
+                const uint32_t q[8] = {ru.x, ru.y, ru.z, ru.w, rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = static_cast<float>(static_cast<int32_t>(q[i]) - p.aZero);
+            } else {  // recover the integer code difference from the dequantized value
+                const uint32_t q[8] = {ru.x, ru.y, ru.z, ru.w, rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = rintf(__uint_as_float(q[i]) * p.aInvScale) - p.aFloatZero;
+            }
+            *reinterpret_cast<uint4 *>(stage + (4 * quad + cq) * kCore + rk * 16 + g * kAKStride) =
+                make_uint4(packBf16(x[0], x[1]), packBf16(x[2], x[3]), packBf16(x[4], x[5]), packBf16(x[6], x[7]));
+        }
+    };
+
+    for (int c = 0; c < chunks; ++c) {
+        const int s = c & 1, slot = c % R;
+        uint8_t *stage = stages + s * kStageBytes;
+        asm volatile("cp.async.wait_group %0;" ::"n"(R - 1) : "memory");
+        __syncwarp();  // the lanes of a warp convert what other lanes of it copied
+        // the MMAs that read this stage two chunks ago must have finished
+        if (c >= 2 && !waitPhase(smemAddr(&bars[s]), ((c >> 1) - 1) & 1)) failed = 1;
+        convertChunk(slot, stage);
+        __syncwarp();
+        issueChunk(c + R, slot);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t base = smemAddr(stage);
+#pragma unroll
+            for (int ks = 0; ks < kStageRows / 16; ++ks) {
+                const uint64_t descA = operandDescriptor(base + ks * 2 * kAKStride, kAKStride, kCore);
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp) {
+                    const uint64_t descB =
+                        operandDescriptor(base + kABytes + sp * kBBytes + ks * 2 * kBKStride, kBKStride, kCore);
+                    mmaBf16(tmem, descA, descB, kIdesc, (c > 0 || ks > 0 || sp > 0) ? 1u : 0u);
+                }
+            }
+            commitTo(smemAddr(&bars[s]));
+            if (c + 1 == chunks) commitTo(smemAddr(&bars[2]));
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (chunks > 0 && !waitPhase(smemAddr(&bars[2]), 0)) failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    float *out = p.partial + static_cast<size_t>(blockIdx.y) * (M + 1) * N;
+    // accumulator rows: warp w may read the tensor-memory lanes [32 (w % 4), 32 (w % 4) + 32)
+    {
+        const int q = warp & 3, sharing = (NW - q + 3) / 4;
+        if (32 * q < M && chunks > 0) {
+            const int m = 32 * q + lane;
+            for (int j = warp >> 2; j < CW; j += sharing) {
+                uint32_t r[32];
+                tmemLoad32(tmem + (static_cast<uint32_t>(32 * q) << 16) + 32 * j, r);
+                if (m < M) {
+                    float4 *dst = reinterpret_cast<float4 *>(out + static_cast<size_t>(m) * N + n0 + 32 * j);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                }
+            }
+        }
+    }
+    // column sums of B: fold the eight k-row lanes, fixed order
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float v = csum[j];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        csum[j] = v;
+    }
+    // ... then the two thread halves, through the (now idle) first operand stage
+    float *scratch = reinterpret_cast<float *>(stages);
+    if (half == 1 && rk == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) scratch[32 * cw + 8 * cq + j] = csum[j];
+    }
+    __syncthreads();
+    if (half == 0 && rk == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) csum[j] += scratch[32 * cw + 8 * cq + j];
+        float4 *dst = reinterpret_cast<float4 *>(out + static_cast<size_t>(M) * N + n0 + 32 * cw + 8 * cq);
+        dst[0] = make_float4(csum[0], csum[1], csum[2], csum[3]);
+        dst[1] = make_float4(csum[4], csum[5], csum[6], csum[7]);
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && failed && status) atomicExch(status, 1);
+}
+
+template <int NT>
+void launchTile(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+    constexpr size_t smem = Geometry<NT>::kSmem;
+    static bool configured = false;
+    if (!configured) {
+        RXMET_CUDA(cudaFuncSetAttribute(weightGradUmma<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured = true;
+    }
+    KernelTimer timer__("weightGradUmma", st);
+    weightGradUmma<NT><<<dim3(N / NT, splits), Geometry<NT>::kThreads, smem, st>>>(prob, K, N, chunkK, prob.status);
+}
+
+int tileColumns(int N) {
+    for (int nt : {256, 192, 128})
+        if (N % nt == 0) return nt;
+    return 0;
+}
+
+}  // namespace
+
+bool tensorMemoryPath(int M, int N) {
+    static const bool disabled = std::getenv("RXMET_WGRAD_MMA_SYNC") != nullptr;
+    return !disabled && M >= 4 && M <= kTileM && M % 4 == 0 && N % 4 == 0 && tileColumns(N) != 0;
+}
+
+int planTensorMemory(int K, int N, int sms, int *chunkK) {
+    const int tiles = N / tileColumns(N);
+    const int want = std::max(1, sms / tiles);  // one CTA per SM
+    *chunkK = ((K + want - 1) / want + kStageRows - 1) / kStageRows * kStageRows;
+    return (K + *chunkK - 1) / *chunkK;
+}
+
+void launchTensorMemory(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+    switch (tileColumns(N)) {
+        case 256: launchTile<256>(prob, K, N, chunkK, splits, st); break;
+        case 192: launchTile<192>(prob, K, N, chunkK, splits, st); break;
+        case 128: launchTile<128>(prob, K, N, chunkK, splits, st); break;
+        default: fail(RXMET_ERR_UNSUPPORTED, "no tensor-memory tile for %d columns", N);
+    }
+}
+
+}  // namespace wgrad
+}  // namespace rxmet
