@@ -148,14 +148,14 @@ struct Geometry {
     static constexpr int kThreads = 2 * NT;                      // two thread halves, two k-groups of B each
     static constexpr int kWarps = kThreads / 32;
     static constexpr int kAPieces = (16 + kWarps - 1) / kWarps;  // A pieces (k-group x 32 rows of m) per warp
-    static constexpr int kSlots = 4 + 2 * kAPieces;              // 16-byte slots per thread and chunk
     static constexpr uint32_t kAKStride = (kTileM / 8) * kCore;  // bytes between k-groups of the A tile
     static constexpr uint32_t kBKStride = (NT / 8) * kCore;
     static constexpr uint32_t kABytes = (kStageRows / 8) * kAKStride;
     static constexpr uint32_t kBBytes = (kStageRows / 8) * kBKStride;
     static constexpr uint32_t kStageBytes = kABytes + 3 * kBBytes;
-    static constexpr uint32_t kRawBytes = kSlots * 16 * kThreads;
-    static constexpr int kRing = NT <= 128 ? 4 : 2;
+    static constexpr uint32_t kRawPieces = 2 * kWarps + 16;      // 1 KB pieces of a raw chunk: B per warp, then A
+    static constexpr uint32_t kRawBytes = kRawPieces * 1024;
+    static constexpr int kRing = NT <= 128 ? 4 : (NT <= 192 ? 3 : 2);
     static_assert(2 * kStageBytes + kRing * kRawBytes <= 227 * 1024, "shared memory of one SM");
     static constexpr size_t kSmem = 2 * kStageBytes + static_cast<size_t>(kRing) * kRawBytes;
 };
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
     const int kBegin = blockIdx.y * chunkK, kEnd = min(K, kBegin + chunkK);
     const int chunks = (kEnd - kBegin + kStageRows - 1) / kStageRows;
     const int M = p.M, quads = (M + 31) / 32;
-    uint4 *raw = reinterpret_cast<uint4 *>(stages + 2 * kStageBytes);  // [R][kSlots][TH]
+    uint4 *raw = reinterpret_cast<uint4 *>(stages + 2 * kStageBytes);  // [R][kRawPieces][64]
 
     if (tid == 0) {
         failed = 0;
@@ -213,10 +213,10 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
     // Part p of row r is kept at position r * 8 + (p ^ r) of the piece, which makes both these
     // writes and the converting reads (lane -> row lane % 8, parts 2 (lane / 8) and + 1) free of
     // bank conflicts.
-    constexpr int kPieces = 2 + AT;
     auto issueChunk = [&](int chunk, int slot) {
         const int k0 = kBegin + chunk * kStageRows;
-        uint4 *dst = raw + (static_cast<size_t>(slot) * NW + warp) * kPieces * 64;
+        uint4 *dstB = raw + (static_cast<size_t>(slot) * G::kRawPieces + 2 * warp) * 64;
+        uint4 *dstA = raw + (static_cast<size_t>(slot) * G::kRawPieces + 2 * NW) * 64;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int wrow = 4 * i + (lane >> 3), part = lane & 7, pos = wrow * 8 + (part ^ wrow);
@@ -224,15 +224,16 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
             for (int gi = 0; gi < 2; ++gi) {
                 const int k = k0 + 8 * (2 * half + gi) + wrow;
                 const bool ok = k < kEnd;
-                copyAsync16(dst + gi * 64 + pos, ok ? p.B + static_cast<size_t>(k) * N + n0 + 32 * cw + 4 * part : p.B, ok);
+                copyAsync16(dstB + gi * 64 + pos, ok ? p.B + static_cast<size_t>(k) * N + n0 + 32 * cw + 4 * part : p.B, ok);
             }
 #pragma unroll
             for (int t = 0; t < AT; ++t) {
                 const int task = warp + t * NW, m = 32 * (task >> 2) + 4 * part;
                 const int k = k0 + 8 * (task & 3) + wrow;
+                if (task >= 16) continue;
                 const bool ok = task < 4 * quads && k < kEnd && m < M;
                 const size_t at = ok ? static_cast<size_t>(k) * M + m : 0;
-                copyAsync16(dst + (2 + t) * 64 + pos, static_cast<const uint32_t *>(aBase) + at, ok);
+                copyAsync16(dstA + task * 64 + pos, static_cast<const uint32_t *>(aBase) + at, ok);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -251,12 +252,13 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
 
     // converts ring entry `slot` into the operand stage
     auto convertChunk = [&](int slot, uint8_t *stage) {
-        const uint4 *src = raw + (static_cast<size_t>(slot) * NW + warp) * kPieces * 64;
+        const uint4 *srcB = raw + (static_cast<size_t>(slot) * G::kRawPieces + 2 * warp) * 64;
+        const uint4 *srcA = raw + (static_cast<size_t>(slot) * G::kRawPieces + 2 * NW) * 64;
         const int posU = rk * 8 + ((2 * cq) ^ rk), posV = rk * 8 + ((2 * cq + 1) ^ rk);
 #pragma unroll
         for (int gi = 0; gi < 2; ++gi) {
             const int g = 2 * half + gi;
-            const uint4 ru = src[gi * 64 + posU], rv = src[gi * 64 + posV];
+            const uint4 ru = srcB[gi * 64 + posU], rv = srcB[gi * 64 + posV];
             const float4 u = make_float4(__uint_as_float(ru.x), __uint_as_float(ru.y), __uint_as_float(ru.z), __uint_as_float(ru.w));
             const float4 v = make_float4(__uint_as_float(rv.x), __uint_as_float(rv.y), __uint_as_float(rv.z), __uint_as_float(rv.w));
             csum[0] += u.x; csum[1] += u.y; csum[2] += u.z; csum[3] += u.w;
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
         for (int t = 0; t < AT; ++t) {
             const int task = warp + t * NW, g = task & 3, quad = task >> 2;
             if (task >= 4 * quads) continue;
-            const uint4 ru = src[(2 + t) * 64 + posU], rv = src[(2 + t) * 64 + posV];
+            const uint4 ru = srcA[task * 64 + posU], rv = srcA[task * 64 + posV];
             float x[8];
             // zero-filled pieces decode to some finite value: they only meet zero rows of B or
             // accumulator rows that are never stored
@@ -327,17 +329,25 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
     {
         const int q = warp & 3, sharing = (NW - q + 3) / 4;
         if (32 * q < M && chunks > 0) {
-            const int m = 32 * q + lane;
+            float4 *tile = reinterpret_cast<float4 *>(stages + warp * 4096);  // the operand stages are idle now
             for (int j = warp >> 2; j < CW; j += sharing) {
                 uint32_t r[32];
                 tmemLoad32(tmem + (static_cast<uint32_t>(32 * q) << 16) + 32 * j, r);
-                if (m < M) {
-                    float4 *dst = reinterpret_cast<float4 *>(out + static_cast<size_t>(m) * N + n0 + 32 * j);
+                // lane = accumulator row here; turn the 32 x 32 block through shared memory so that a
+                // store instruction of the warp writes four whole 128-byte row segments
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                for (int i = 0; i < 8; ++i)
+                    tile[lane * 8 + (i ^ (lane & 7))] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                    __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                __syncwarp();
+#pragma unroll
+                for (int pass = 0; pass < 8; ++pass) {
+                    const int row = 4 * pass + (lane >> 3), i = lane & 7;
+                    const float4 v = tile[row * 8 + (i ^ (row & 7))];
+                    if (32 * q + row < M)
+                        *reinterpret_cast<float4 *>(out + static_cast<size_t>(32 * q + row) * N + n0 + 32 * j + 4 * i) = v;
                 }
+                __syncwarp();
             }
         }
     }
@@ -351,7 +361,7 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
         csum[j] = v;
     }
     // ... then the two thread halves, through the (now idle) first operand stage
-    float *scratch = reinterpret_cast<float *>(stages);
+    float *scratch = reinterpret_cast<float *>(stages + NW * 4096);  // behind the warps' epilogue tiles
     if (half == 1 && rk == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) scratch[32 * cw + 8 * cq + j] = csum[j];
