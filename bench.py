@@ -271,7 +271,7 @@ def run_ours(args):
     lib.rxmet_set_kernel_timing(1)
     k_steps = min(args.steps, 10)
     timed(resident, k_steps, 1)
-    names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "packRecurrentBf16", "weightGradMma", "weightGradUmma", "reduceWeightGrad", "fillCodes", "packStepMasks",
+    names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "inputGradUmma", "packRecurrentBf16", "weightGradMma", "weightGradUmma", "reduceWeightGrad", "fillCodes", "packStepMasks",
              "reduceSplits", "columnSums", "channelPrep", "dequantCodes", "transposeMatrix"]
     per_kernel = {}
     for n in names:
@@ -487,7 +487,7 @@ def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
     torch.cuda.synchronize()
     per = {}
     for n in ["lstmQuantizeCodes", "lstmPrepChannels", "lstmInputLinearQ", "lstmRecurrentQ", "lstmDequantWeights",
-              "lstmPackStepMasks", "lstmRecurrentBackward", "lstmRecurrentBackwardMma", "lstmGemmNN", "lstmInputGradNarrow", "lstmGemmRowsTN", "lstmReduceSplits",
+              "lstmPackStepMasks", "lstmRecurrentBackward", "lstmRecurrentBackwardMma", "lstmGemmNN", "lstmInputGradNarrow", "inputGradUmma", "lstmGemmRowsTN", "lstmReduceSplits",
               "lstmColumnSums", "weightGradMma", "weightGradUmma", "lstmReduceWeightGradT"]:
         ms, cnt = C.c_double(), C.c_longlong()
         lib.rxmet_get_kernel_timing(n.encode(), C.byref(ms), C.byref(cnt))

@@ -21,6 +21,7 @@
 
 #include "common.h"
 #include "gru_backward.h"
+#include "input_grad_umma.h"
 #include "weight_grad_mma.h"
 
 namespace rxmet {
@@ -885,7 +886,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     // tensor-core path: split-K partials of (I+1) and (H+1) rows and the status word
     ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C))) * (I + 1) * C);
     ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
-    ws.take<int>(1);
+    ws.take<int>(64);
     return ws.used() + 4096;
 }
 
@@ -900,7 +901,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     const rxmet_gru_masks &mk = call.masks ? *call.masks : none;
 
     const float *W = call.W, *R = call.R, *x = call.x;
-    const float *chanScaleR = nullptr;
+    const float *chanScaleR = nullptr, *chanScaleW = nullptr;
     if (call.W_q) {  // QAT path: rebuild the real-valued operands from the saved codes
         RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
         const Exec &e = *call.exec;
@@ -928,6 +929,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         afterLaunch("dequantCodes");
         W = Wf; R = Rf; x = xf;
         chanScaleR = chan + C;
+        chanScaleW = chan;
     }
 
     int device = 0, smemMax = 0, sms = 0;
@@ -1018,7 +1020,17 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     }
 
     // dx
-    {
+    int *status = ws.take<int>(1);  // set by a tcgen05 kernel whose bounded wait gave up
+    if (call.W_q) RXMET_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+    if (call.W_q != nullptr && call.exec->weightClass == CodeClass::I8 && igrad::eligible(C, I) &&
+        std::getenv("RXMET_GRU_GRAD_SIMT") == nullptr) {
+        // QAT: gradients times the integer weight codes on the tensor cores, scales folded into the gradients
+        igrad::Problem pg{};
+        pg.G = dp; pg.kScale = chanScaleW; pg.codesNK = call.W_q; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
+        pg.mask = mk.x; pg.maskKeeps = 1; pg.out = call.dx; pg.status = status;
+        igrad::launch(pg, sms, st);
+        afterLaunch("inputGradUmma");
+    } else {
         KernelTimer timer__("gemmNT", st);
         gemmNT<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
             dp, W, static_cast<int>(rows), I, C, mk.x, call.dx);
@@ -1037,9 +1049,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         px.partial = ws.take<float>(static_cast<size_t>(planX.splits) * (I + 1) * C);
         ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
         ph.partial = ws.take<float>(static_cast<size_t>(planH.splits) * (H + 1) * C);
-        int *status = ws.take<int>(1);
         px.status = ph.status = status;
-        if (planX.tensorMemory || planH.tensorMemory) RXMET_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
         wgrad::launch(px, K, C, planX, st);
         afterLaunch("weightGrad");
         wgrad::launch(ph, K, C, planH, st);
@@ -1047,14 +1057,14 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         {
             KernelTimer timer__("reduceWeightGrad", st);
             reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(I + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
-                px.partial, planX.splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, planX.tensorMemory ? status : nullptr,
+                px.partial, planX.splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, status,
                 call.dW, call.dbw);
         }
         afterLaunch("reduceWeightGrad");
         {
             KernelTimer timer__("reduceWeightGrad", st);
             reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(H + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
-                ph.partial, planH.splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, planH.tensorMemory ? status : nullptr,
+                ph.partial, planH.splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, status,
                 call.dR, call.dbr);
         }
         afterLaunch("reduceWeightGrad");

@@ -19,6 +19,7 @@
 #include <cstdlib>
 
 #include "common.h"
+#include "input_grad_umma.h"
 #include "lstm_kernels.h"
 #include "weight_grad_mma.h"
 
@@ -739,7 +740,18 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         else if (bt == 2) launch(recurrentBackward<2>, 2);
         else launch(recurrentBackward<1>, 1);
     }
-    if (I <= 128 && C % 4 == 0) {
+    if (call.quantized) RXMET_CUDA(cudaMemsetAsync(tensorStatus, 0, sizeof(int), st));
+    if (call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I)) {
+        // QAT: gradients times the integer weight codes on the tensor cores, scales folded into the gradients
+        int device = 0, sms = 0;
+        RXMET_CUDA(cudaGetDevice(&device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        igrad::Problem pg{};
+        pg.G = gIh; pg.kScale = channelScales; pg.codesKN = call.weightIh; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
+        pg.mask = static_cast<const uint8_t *>(mk.input); pg.maskKeeps = 0; pg.out = call.grads.input; pg.status = tensorStatus;
+        igrad::launch(pg, sms, st);
+        afterLaunch("inputGradUmma");
+    } else if (I <= 128 && C % 4 == 0) {
         const int perThread = (I + 3) / 4;  // outputs per thread, four threads share a row
         const unsigned grid = static_cast<unsigned>((rows + kDxRows - 1) / kDxRows);
         const uint8_t *inputMask = static_cast<const uint8_t *>(mk.input);
@@ -790,7 +802,6 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             fail(RXMET_ERR_INVALID_ARGUMENT, "the QAT backward needs the quantized initial hidden state");
         }
         px.status = ph.status = tensorStatus;
-        if (planX.tensorMemory || planH.tensorMemory) RXMET_CUDA(cudaMemsetAsync(tensorStatus, 0, sizeof(int), st));
         wgrad::launch(px, static_cast<int>(rows), C, planX, st);
         afterLaunch("weightGrad");
         wgrad::launch(ph, static_cast<int>(rows), C, planH, st);
@@ -800,7 +811,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             {
                 KernelTimer timer__("lstmReduceWeightGradT", st);
                 reduceWeightGradT<<<dim3((C + 31) / 32, (M + 1 + kReduceRows - 1) / kReduceRows), dim3(32, kReduceRows, kReduceLayers), 0, st>>>(
-                    partial, pl.splits, M, C, scale, wm, bm, pl.tensorMemory ? tensorStatus : nullptr, w, b);
+                    partial, pl.splits, M, C, scale, wm, bm, tensorStatus, w, b);
             }
             afterLaunch("lstmReduceWeightGradT");
         };

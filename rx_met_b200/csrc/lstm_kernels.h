@@ -58,6 +58,7 @@ struct BackwardCall {
     const float *weightIhScale = nullptr, *weightHhScale = nullptr;
     bool codesFitTensorPath = false;  // x and hidden grids span at most 256 codes around their zero points
     bool weightCodesFitBf16 = false;  // weight_hh grid of at most 8 bits: codes are exact in bf16
+    bool weightIhCodesFitBf16 = false;  // the same for weight_ih
 };
 size_t backwardWorkspaceBytes(int T, int B, int I, int H);
 void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t stream);
