@@ -25,6 +25,14 @@ __device__ __forceinline__ int64_t rshiftRound(int64_t x, int n) {
     return q + static_cast<int64_t>((r > half) || (r == half && (q & 1)));
 }
 
+// The same rounding shift for 1 <= n <= 62 as one add and one shift:
+// floor((x + 2^(n-1) - 1 + odd(floor(x / 2^n))) / 2^n); roundAdd = 2^(n-1) - 1 is a constant of
+// the caller (per channel).  A remainder above half carries, one equal to half carries only into
+// an odd quotient, a smaller one never does.
+__device__ __forceinline__ int64_t rshiftRoundConst(int64_t x, int n, int64_t roundAdd) {
+    return (x + roundAdd + ((x >> n) & 1)) >> n;
+}
+
 // quantize_ops_helper.h:242-248
 __device__ __forceinline__ int64_t applyRescale(int64_t x, Rescale r) {
     return rshiftRound(x * static_cast<int64_t>(r.mult), r.shift);

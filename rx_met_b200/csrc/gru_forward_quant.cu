@@ -179,17 +179,138 @@ __global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, i
         }
         const int64_t cmp = comp[c], bias = biasAcc[c];
         const Rescale rs = rescale[c];
+        const Rescale gateRs = pre.enabled ? pre.toGate[c / pre.hidden] : Rescale{1, 0};
+        // Channel constants of the two rounding shifts.  With 32-bit accumulators, shifts in
+        // [1, 40] and multipliers below 2^24 (every practical parameter set; no 64-bit overflow) the epilogue is one widening multiply, one
+        // 64-bit add and one shift per rescale; anything else takes the general functions.
+        const int64_t offset = bias - cmp;
+        const bool quick = sizeof(typename D::Acc) == 4 && rs.shift >= 1 && rs.shift <= 40 && offset > -(1ll << 30) &&
+                           offset < (1ll << 30) && rs.mult > 0 && rs.mult < (1 << 24) && zpOut > -(1 << 20) && zpOut < (1 << 20) &&
+                           (!pre.enabled || (gateRs.shift >= 1 && gateRs.shift <= 40 && gateRs.mult > 0 && gateRs.mult < (1 << 24)));
+        // (acc + offset) * mult = acc * mult + offset * mult: the constant rides in the widening
+        // multiply-add; the output zero point rides in the rounding constant (it is a multiple of
+        // 2^shift there, so it does not disturb the remainder)
+        const int64_t mulAddOut = quick ? offset * rs.mult : 0;
+        const int64_t roundOut = quick ? (1ll << (rs.shift - 1)) - 1 + (static_cast<int64_t>(zpOut) << rs.shift) : 0;
+        const int64_t mulAddGate = (quick && pre.enabled) ? -static_cast<int64_t>(zpOut) * gateRs.mult : 0;
+        const int64_t roundGate = (quick && pre.enabled) ? (1ll << (gateRs.shift - 1)) - 1 : 0;
 #pragma unroll
         for (int r = 0; r < kLinearRows; ++r) {
             if (r < nRows) {
                 uint8_t keep;
-                int32_t q = linearEpilogue(acc[r], cmp, bias, rs, zpOut, lo, hi, keep);
+                int32_t q;
+                if (quick) {
+                    const int64_t prod = static_cast<int64_t>(static_cast<int32_t>(acc[r])) * rs.mult + mulAddOut;
+                    q = clampCode(static_cast<int32_t>(rshiftRoundConst(prod, rs.shift, roundOut)), lo, hi, keep);
+                    if (pre.enabled)
+                        q = static_cast<int32_t>(
+                            rshiftRoundConst(static_cast<int64_t>(q) * gateRs.mult + mulAddGate, gateRs.shift, roundGate));
+                } else {
+                    q = linearEpilogue(acc[r], cmp, bias, rs, zpOut, lo, hi, keep);
+                    if (pre.enabled) q = rescaleWide(q - zpOut, gateRs);
+                }
                 const size_t o = static_cast<size_t>(row0 + r) * channels + c;
-                if (pre.enabled) q = rescaleWide(q - zpOut, pre.toGate[c / pre.hidden]);
                 out[o] = static_cast<LT>(q);
                 if (mask) mask[o] = keep;
             }
         }
+    }
+}
+
+// 8-bit grids: thread = channel with its weight words in registers; a CTA walks blocks of
+// kI8Rows rows, staging the next block's codes (padded to four-word groups, read back as
+// 16-byte broadcasts) while it computes the current one.  Channels whose parameters allow it
+// (32-bit accumulator plus offset, multipliers that shrink, shifts in [1, 31]) round with
+// 32-bit funnel-shift arithmetic; the others take the general 64-bit functions.  Requires
+// blockDim.x >= kI8Rows * KW4 * 4 and blockDim.x >= channels.
+constexpr int kI8Rows = 16;
+
+// round_half_even(p / 2^n) for 1 <= n <= 31 when the quotient fits 32 bits: floor quotient by
+// funnel shift, remainder r < 2^n, and (r + odd(q)) > half is exactly "above half, or half into
+// an odd quotient".
+__device__ __forceinline__ int32_t rshiftRoundNarrow(int64_t p, int n, uint32_t remMask, uint32_t half) {
+    const uint32_t lo = static_cast<uint32_t>(p), hi = static_cast<uint32_t>(static_cast<uint64_t>(p) >> 32);
+    const int32_t q = static_cast<int32_t>(__funnelshift_r(lo, hi, n));
+    const uint32_t r = lo & remMask;
+    return q + static_cast<int32_t>((r + static_cast<uint32_t>(q & 1)) > half);
+}
+
+template <int KW4>
+__global__ void __launch_bounds__(512)
+inputLinearI8(const int32_t *__restrict__ x, int rows, int kWords, int channels, const int32_t *__restrict__ w,
+              const int64_t *__restrict__ comp, const int64_t *__restrict__ biasAcc, const Rescale *__restrict__ rescale,
+              int32_t zpOut, int32_t lo, int32_t hi, int16_t *__restrict__ out, uint8_t *__restrict__ mask,
+              const PreRescale pre) {
+    constexpr int kRowWords = KW4 * 4;
+    __shared__ __align__(16) int32_t xs[2][kI8Rows][kRowWords];
+    const int tid = threadIdx.x, c = tid;
+    const bool live = c < channels;
+    int32_t wreg[kRowWords];
+#pragma unroll
+    for (int kk = 0; kk < kRowWords; ++kk) wreg[kk] = (live && kk < kWords) ? w[static_cast<size_t>(kk) * channels + c] : 0;
+
+    const int64_t offset = live ? biasAcc[c] - comp[c] : 0;
+    const Rescale rs = live ? rescale[c] : Rescale{1, 1};
+    const Rescale gateRs = (pre.enabled && live) ? pre.toGate[c / pre.hidden] : Rescale{1, 1};
+    // |acc| < 2^30 for every input size the 32-bit accumulator admits, so acc + offset fits 32 bits;
+    // mult <= 2^shift keeps the quotient inside 32 bits
+    const bool narrowOut = rs.shift >= 1 && rs.shift <= 31 && offset > -(1ll << 30) && offset < (1ll << 30) && rs.mult > 0 &&
+                           static_cast<int64_t>(rs.mult) <= (1ll << rs.shift);
+    const bool narrowGate = gateRs.shift >= 1 && gateRs.shift <= 31 && gateRs.mult > 0 &&
+                            static_cast<int64_t>(gateRs.mult) <= (1ll << min(gateRs.shift + 9, 31)) && lo >= -(1 << 20) &&
+                            hi <= (1 << 20) && zpOut >= -(1 << 20) && zpOut <= (1 << 20);
+    const int64_t mulAddOut = offset * rs.mult;
+    const uint32_t maskOut = (1u << (rs.shift & 31)) - 1u, halfOut = 1u << ((rs.shift - 1) & 31);
+    const int64_t mulAddGate = -static_cast<int64_t>(zpOut) * gateRs.mult;
+    const uint32_t maskGate = (1u << (gateRs.shift & 31)) - 1u, halfGate = 1u << ((gateRs.shift - 1) & 31);
+
+    const int blocks = (rows + kI8Rows - 1) / kI8Rows;
+    const int sRow = tid / kRowWords, sWord = tid % kRowWords;  // the word of a block this thread stages
+    const bool stager = tid < kI8Rows * kRowWords;
+    auto fetch = [&](int blk) -> int32_t {
+        const int row = blk * kI8Rows + sRow;
+        return (stager && blk < blocks && row < rows && sWord < kWords) ? x[static_cast<size_t>(row) * kWords + sWord] : 0;
+    };
+    int buf = 0;
+    if (stager) xs[0][sRow][sWord] = fetch(blockIdx.x);
+    __syncthreads();
+    for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const int32_t pending = fetch(blk + gridDim.x);
+        const int row0 = blk * kI8Rows, nRows = min(kI8Rows, rows - row0);
+        if (live) {
+            int16_t *outPtr = out + static_cast<size_t>(row0) * channels + c;
+            uint8_t *maskPtr = mask ? mask + static_cast<size_t>(row0) * channels + c : nullptr;
+            for (int r = 0; r < nRows; ++r) {
+                int32_t acc = 0;
+#pragma unroll
+                for (int g4 = 0; g4 < KW4; ++g4) {
+                    const int4 xv = *reinterpret_cast<const int4 *>(&xs[buf][r][4 * g4]);
+                    acc = __dp4a(wreg[4 * g4], xv.x, acc);
+                    acc = __dp4a(wreg[4 * g4 + 1], xv.y, acc);
+                    acc = __dp4a(wreg[4 * g4 + 2], xv.z, acc);
+                    acc = __dp4a(wreg[4 * g4 + 3], xv.w, acc);
+                }
+                const int64_t prod = static_cast<int64_t>(acc) * rs.mult + mulAddOut;
+                const int32_t res = (narrowOut ? rshiftRoundNarrow(prod, rs.shift, maskOut, halfOut)
+                                               : static_cast<int32_t>(rshiftRound(prod, rs.shift))) + zpOut;
+                uint8_t keep;
+                int32_t q = clampCode(res, lo, hi, keep);
+                if (pre.enabled) {
+                    const int64_t prodGate = static_cast<int64_t>(q) * gateRs.mult + mulAddGate;
+                    q = narrowGate ? rshiftRoundNarrow(prodGate, gateRs.shift, maskGate, halfGate)
+                                   : static_cast<int32_t>(rshiftRound(prodGate, gateRs.shift));
+                }
+                *outPtr = static_cast<int16_t>(q);
+                outPtr += channels;
+                if (maskPtr) {
+                    *maskPtr = keep;
+                    maskPtr += channels;
+                }
+            }
+        }
+        if (stager) xs[buf ^ 1][sRow][sWord] = pending;
+        __syncthreads();
+        buf ^= 1;
     }
 }
 
@@ -697,9 +818,33 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     // 3. input projection, all steps
     {
         const int block = std::min(padTo(C, 32), 512);
-        const size_t smem = sizeof(AWord) * kLinearRows * iWords;
-        const int grid = static_cast<int>((rows + kLinearRows - 1) / kLinearRows);
-        {
+        const int kw4 = (iWords + 3) / 4;
+        bool specialised = false;
+        if constexpr (kI8) {
+            if (C <= 512 && kw4 <= 4 && block >= kI8Rows * kw4 * 4 && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr) {
+                specialised = true;
+                const int blocks = static_cast<int>((rows + kI8Rows - 1) / kI8Rows);
+                const int32_t zp = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], qlo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR],
+                              qhi = g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR];
+                KernelTimer timer__("inputLinear", st);
+#define RXMET_IL_CASE(N)                                                                                                   \
+    case N: {                                                                                                              \
+        int perSm = 1;                                                                                                     \
+        RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, inputLinearI8<N>, block, 0));                     \
+        const int grid = std::max(1, std::min(blocks, sms * std::max(1, perSm)));                                          \
+        inputLinearI8<N><<<grid, block, 0, st>>>(reinterpret_cast<const int32_t *>(xCodes), static_cast<int>(rows), iWords, C, \
+                                                 reinterpret_cast<const int32_t *>(wCodes), compX, biasX, ch.gemmX, zp, qlo, qhi, \
+                                                 reinterpret_cast<int16_t *>(ihCodes), mk.weight_ih_linear, pre);            \
+    } break;
+                switch (kw4) {
+                    RXMET_IL_CASE(1) RXMET_IL_CASE(2) RXMET_IL_CASE(3) RXMET_IL_CASE(4)
+                }
+#undef RXMET_IL_CASE
+            }
+        }
+        if (!specialised) {
+            const size_t smem = sizeof(AWord) * kLinearRows * iWords;
+            const int grid = static_cast<int>((rows + kLinearRows - 1) / kLinearRows);
             KernelTimer timer__("inputLinear", st);
             inputLinear<WT, AT, LT><<<grid, block, smem, st>>>(
                 reinterpret_cast<const AWord *>(xCodes), static_cast<int>(rows), iWords, C, wCodes, compX, biasX, ch.gemmX,
