@@ -191,6 +191,33 @@ __global__ void packStepMasks(const uint8_t *__restrict__ mIh, const uint8_t *__
     }
 }
 
+// The same packing, four hidden units per thread (H a multiple of 4, flag bytes 0 or 1, as every
+// forward of this library writes them): 32-bit loads of four flag bytes, two byte permutes spread
+// them over the 16-bit lanes of two words, and a multiply-add moves each pair into its bit position.
+__global__ void packStepMasks4(const uint8_t *__restrict__ mIh, const uint8_t *__restrict__ mHh,
+                               const uint8_t *__restrict__ mGateIn, const uint8_t *__restrict__ mGateOut,
+                               const uint8_t *__restrict__ mH, size_t quads, int H, uint2 *__restrict__ out) {
+    for (size_t q = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; q < quads;
+         q += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t i = q * 4, row = i / H, j = i % H, gi = row * 3 * H + j;
+        uint32_t lanes01 = 0, lanes23 = 0;
+        auto add = [&](const uint8_t *m, size_t at, int pos) {
+            const uint32_t w = m ? *reinterpret_cast<const uint32_t *>(m + at) : 0x01010101u;
+            lanes01 += __byte_perm(w, 0u, 0x4140) * (1u << pos);
+            lanes23 += __byte_perm(w, 0u, 0x4342) * (1u << pos);
+        };
+#pragma unroll
+        for (int g = 0; g < 3; ++g) {
+            add(mGateOut, gi + static_cast<size_t>(g) * H, g);
+            add(mGateIn, gi + static_cast<size_t>(g) * H, 3 + g);
+            add(mHh, gi + static_cast<size_t>(g) * H, 6 + g);
+            add(mIh, gi + static_cast<size_t>(g) * H, 9 + g);
+        }
+        add(mH, i, 12);
+        out[q] = make_uint2(lanes01, lanes23);
+    }
+}
+
 struct BackwardQArgs {
     int T, B, H;
     const uint32_t *RB;      // packed codes, see packRecurrentBf16
@@ -955,8 +982,15 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             uint16_t *bits = ws.take<uint16_t>(rows * H);
             {
                 KernelTimer timer__("packStepMasks", st);
-                packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear,
-                                                                      mk.gate_input, mk.gate_output, mk.h, rows, H, bits);
+                auto aligned4 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0; };
+                if (H % 4 == 0 && aligned4(mk.weight_ih_linear) && aligned4(mk.weight_hh_linear) && aligned4(mk.gate_input) &&
+                    aligned4(mk.gate_output) && aligned4(mk.h))
+                    packStepMasks4<<<gridFor(rows * H / 4, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear, mk.gate_input,
+                                                                              mk.gate_output, mk.h, rows * H / 4, H,
+                                                                              reinterpret_cast<uint2 *>(bits));
+                else
+                    packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear,
+                                                                          mk.gate_input, mk.gate_output, mk.h, rows, H, bits);
             }
             afterLaunch("packStepMasks");
             q.stepBits = bits;

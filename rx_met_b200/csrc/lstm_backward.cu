@@ -58,6 +58,36 @@ __global__ void packStepMasks(const rxmet_lstm_backward_masks mk, size_t rows, i
     }
 }
 
+// The same packing, four hidden units per thread (H a multiple of 4, flag bytes 0 or 1, as every
+// forward of this library writes them): 32-bit loads of four flag bytes, byte permutes spread them
+// over the 16-bit lanes of two words and a multiply-add moves each pair into its bit position.
+// Bits 0..14 are gathered in one pair of words, bits 15..18 in a second pair.
+__global__ void packStepMasks4(const rxmet_lstm_backward_masks mk, size_t quads, int H, uint4 *__restrict__ out) {
+    for (size_t q = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; q < quads;
+         q += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t i = q * 4, row = i / H, j = i % H, go = row * 4 * H + j;
+        uint32_t low01 = 0, low23 = 0, high01 = 0, high23 = 0;
+        auto add = [](const void *m, size_t at, int pos, uint32_t &a01, uint32_t &a23) {
+            const uint32_t w = m ? *reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(m) + at) : 0u;
+            a01 += __byte_perm(w, 0u, 0x4140) * (1u << pos);
+            a23 += __byte_perm(w, 0u, 0x4342) * (1u << pos);
+        };
+        add(mk.hidden_outputs, i, 0, low01, low23);
+        add(mk.cell_tanh_outputs, i, 1, low01, low23);
+        add(mk.cell_states, i, 2, low01, low23);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const size_t o = go + static_cast<size_t>(g) * H;
+            add(mk.gate_outputs, o, 3 + g, low01, low23);
+            add(mk.gate_inputs, o, 7 + g, low01, low23);
+            add(mk.weight_ih_linear, o, 11 + g, low01, low23);
+            add(mk.weight_hh_linear, o, g, high01, high23);
+        }
+        out[q] = make_uint4((low01 & 0xffffu) | ((high01 & 0xffffu) << 15), (low01 >> 16) | ((high01 >> 16) << 15),
+                            (low23 & 0xffffu) | ((high23 & 0xffffu) << 15), (low23 >> 16) | ((high23 >> 16) << 15));
+    }
+}
+
 struct RecurrentArgs {
     int T, B, H, smemRows;  // smemRows: leading rows of each gate block held in shared memory
     int smemStride;         // floats between consecutive columns of the transposed copy (odd multiple of 4)
@@ -668,7 +698,13 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     if (anyStepMask) {
         {
             KernelTimer timer__("lstmPackStepMasks", st);
-            packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk, rows, H, stepMasks);
+            auto aligned4 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0; };
+            if (H % 4 == 0 && aligned4(mk.hidden_outputs) && aligned4(mk.cell_tanh_outputs) && aligned4(mk.cell_states) &&
+                aligned4(mk.gate_outputs) && aligned4(mk.gate_inputs) && aligned4(mk.weight_ih_linear) &&
+                aligned4(mk.weight_hh_linear))
+                packStepMasks4<<<gridFor(rows * H / 4, 256), 256, 0, st>>>(mk, rows * H / 4, H, reinterpret_cast<uint4 *>(stepMasks));
+            else
+                packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk, rows, H, stepMasks);
         }
         afterLaunch("lstmPackStepMasks");
     }
