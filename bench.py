@@ -272,7 +272,7 @@ def run_ours(args):
     k_steps = min(args.steps, 10)
     timed(resident, k_steps, 1)
     names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "inputGradUmma", "packRecurrentBf16", "weightGradMma", "weightGradUmma", "reduceWeightGrad", "fillCodes", "packStepMasks",
-             "reduceSplits", "columnSums", "channelPrep", "dequantCodes", "transposeMatrix"]
+             "reduceSplits", "columnSums", "channelPrep", "prepareWeights", "dequantCodes", "transposeMatrix"]
     per_kernel = {}
     for n in names:
         ms, cnt = C.c_double(), C.c_longlong()

@@ -927,10 +927,27 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     const rxmet_gru_masks none{};
     const rxmet_gru_masks &mk = call.masks ? *call.masks : none;
 
+    int device = 0, smemMax = 0, sms = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+    if (const char *env = std::getenv("RXMET_GRU_BWD_BT")) bt = std::atoi(env);
+    if (bt != 1 && bt != 2 && bt != 4) bt = 2;
+
+    // Which kernels take the saved integer codes directly (QAT on 8-bit grids).
+    const bool qat = call.W_q != nullptr;
+    if (qat) RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
+    const bool simtGrads = std::getenv("RXMET_GRU_GRAD_SIMT") != nullptr;
+    const bool registerPath = qat && call.exec->weightClass == CodeClass::I8 && H <= 128 &&
+                              std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
+    const bool tensorInputGrad = qat && call.exec->weightClass == CodeClass::I8 && igrad::eligible(C, I) && !simtGrads;
+    const bool tensorGrads = qat && call.exec->actClass == CodeClass::I8 && I + 1 <= 144 && H + 1 <= 144 && I % 4 == 0 &&
+                             H % 4 == 0 && !simtGrads;
+
     const float *W = call.W, *R = call.R, *x = call.x;
     const float *chanScaleR = nullptr, *chanScaleW = nullptr;
-    if (call.W_q) {  // QAT path: rebuild the real-valued operands from the saved codes
-        RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
+    if (qat) {  // rebuild the real-valued operands that the remaining float kernels read
         const Exec &e = *call.exec;
         float *Wf = ws.take<float>(static_cast<size_t>(I) * C);
         float *Rf = ws.take<float>(static_cast<size_t>(H) * C);
@@ -938,17 +955,17 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         float *chan = ws.take<float>(2 * static_cast<size_t>(C));
         RXMET_CUDA(cudaMemcpyAsync(chan, e.chan.eff_W.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
         RXMET_CUDA(cudaMemcpyAsync(chan + C, e.chan.eff_R.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
-        {
+        if (!tensorInputGrad) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(I) * C, 256), 256, 0, st>>>(call.W_q, static_cast<size_t>(I) * C, C, chan, 0.f, 0, Wf);
         }
         afterLaunch("dequantCodes");
-        {
+        if (!registerPath) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(H) * C, 256), 256, 0, st>>>(call.R_q, static_cast<size_t>(H) * C, C, chan + C, 0.f, 0, Rf);
         }
         afterLaunch("dequantCodes");
-        {
+        if (!tensorGrads) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(rows * I, 256), 256, 0, st>>>(call.x_q, rows * I, I, nullptr, e.gate.eff[RXMET_GRU_X],
                                                                 e.gate.zp[RXMET_GRU_X], xf);
@@ -959,16 +976,6 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         chanScaleW = chan;
     }
 
-    int device = 0, smemMax = 0, sms = 0;
-    RXMET_CUDA(cudaGetDevice(&device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
-    if (const char *env = std::getenv("RXMET_GRU_BWD_BT")) bt = std::atoi(env);
-    if (bt != 1 && bt != 2 && bt != 4) bt = 2;
-
-    const bool registerPath = call.W_q != nullptr && call.exec->weightClass == CodeClass::I8 && H <= 128 &&
-                              std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
     if (registerPath) {
         const int CW = H <= 32 ? 16 : (H <= 64 ? 32 : 64);
         uint32_t *RB = ws.take<uint32_t>(3 * static_cast<size_t>(CW) * H);
@@ -1056,8 +1063,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     // dx
     int *status = ws.take<int>(1);  // set by a tcgen05 kernel whose bounded wait gave up
     if (call.W_q) RXMET_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
-    if (call.W_q != nullptr && call.exec->weightClass == CodeClass::I8 && igrad::eligible(C, I) &&
-        std::getenv("RXMET_GRU_GRAD_SIMT") == nullptr) {
+    if (tensorInputGrad) {
         // QAT: gradients times the integer weight codes on the tensor cores, scales folded into the gradients
         igrad::Problem pg{};
         pg.G = dp; pg.kScale = chanScaleW; pg.codesNK = call.W_q; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
@@ -1071,9 +1077,6 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     }
     afterLaunch("gemmNT");
     // dW, dR, dbw, dbr
-    const bool tensorGrads = call.W_q != nullptr && call.exec->actClass == CodeClass::I8 && I + 1 <= 144 &&
-                             H + 1 <= 144 && I % 4 == 0 && H % 4 == 0 &&
-                             std::getenv("RXMET_GRU_GRAD_SIMT") == nullptr;
     if (tensorGrads) {
         const Exec &e = *call.exec;
         const int K = static_cast<int>(rows);

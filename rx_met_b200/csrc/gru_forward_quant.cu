@@ -132,6 +132,87 @@ __global__ void channelPrep(const typename Dot<WT, AT>::WWord *__restrict__ w, i
     biasAcc[c] = applyRescale(static_cast<int64_t>(biasCodes[c]), biasRescale[c]);
 }
 
+// 8-bit weights: everything that depends on the parameters alone, in one launch.  A CTA owns 32
+// channels; its thread layers share the rows of W and R (four rows = one packed word),
+// quantize them, store the packed words (and the optional 32-bit codes and clamp flags) and
+// sum the codes; layer 0 then adds the layers' sums, quantizes the two biases and writes the
+// zero-point correction and the bias on the accumulator grid.  Same arithmetic as
+// quantizeTensor + channelPrep above.  kPrepLayers thread layers keep the chain of dependent
+// loads per thread short: this launch sits on the critical path of every step.
+struct WeightPrepArgs {
+    const float *W, *R, *bw, *br;
+    int I, H, C, iWords, hWords;
+    const float *effW, *effR, *effBw, *effBr;
+    int32_t loW, hiW, loR, hiR, loBw, hiBw, loBr, hiBr;
+    int32_t *wCodes, *rCodes, *bwCodes, *brCodes;  // packed words / bias codes
+    int32_t *W_q, *R_q, *bw_q, *br_q;              // optional 32-bit copies of the codes
+    uint8_t *mW, *mR, *mBw, *mBr;                  // optional clamp flags
+    int32_t zpX, zpH;
+    const Rescale *biasRescaleX, *biasRescaleH;
+    int64_t *compX, *biasX, *compH, *biasH;
+};
+
+constexpr int kPrepLayers = 32;
+__global__ void __launch_bounds__(32 * kPrepLayers) prepareWeightsI8(const WeightPrepArgs a) {
+    __shared__ int32_t sums[2][kPrepLayers][32];
+    const int cl = threadIdx.x & 31, layer = threadIdx.x >> 5, c = blockIdx.x * 32 + cl;
+    const bool live = c < a.C;
+    auto pass = [&](const float *__restrict__ src, int rowsK, int words, float scale, int32_t lo, int32_t hi,
+                    int32_t *__restrict__ codes, int32_t *__restrict__ codes32, uint8_t *__restrict__ mask) {
+        int32_t sum = 0;
+        for (int kk = layer; kk < words; kk += kPrepLayers) {
+            float v[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) v[b] = 4 * kk + b < rowsK ? src[static_cast<size_t>(4 * kk + b) * a.C + c] : 0.0f;
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int k = 4 * kk + b;
+                int32_t q = 0;
+                if (k < rowsK) {
+                    const size_t at = static_cast<size_t>(k) * a.C + c;
+                    uint8_t keep;
+                    q = quantizeValue(v[b], scale, 0, lo, hi, keep);
+                    if (codes32) codes32[at] = q;
+                    if (mask) mask[at] = keep;
+                }
+                sum += q;
+                word |= static_cast<uint32_t>(q & 0xff) << (8 * b);
+            }
+            codes[static_cast<size_t>(kk) * a.C + c] = static_cast<int32_t>(word);
+        }
+        return sum;
+    };
+    int32_t sumW = 0, sumR = 0;
+    if (live) {
+        sumW = pass(a.W, a.I, a.iWords, a.effW[c], a.loW, a.hiW, a.wCodes, a.W_q, a.mW);
+        sumR = pass(a.R, a.H, a.hWords, a.effR[c], a.loR, a.hiR, a.rCodes, a.R_q, a.mR);
+    }
+    sums[0][layer][cl] = sumW;
+    sums[1][layer][cl] = sumR;
+    __syncthreads();
+    if (layer != 0 || !live) return;
+    int64_t totalW = 0, totalR = 0;
+#pragma unroll
+    for (int l = 0; l < kPrepLayers; ++l) {
+        totalW += sums[0][l][cl];
+        totalR += sums[1][l][cl];
+    }
+    uint8_t keep;
+    const int32_t qBw = quantizeValue(a.bw[c], a.effBw[c], 0, a.loBw, a.hiBw, keep);
+    a.bwCodes[c] = qBw;
+    if (a.bw_q) a.bw_q[c] = qBw;
+    if (a.mBw) a.mBw[c] = keep;
+    const int32_t qBr = quantizeValue(a.br[c], a.effBr[c], 0, a.loBr, a.hiBr, keep);
+    a.brCodes[c] = qBr;
+    if (a.br_q) a.br_q[c] = qBr;
+    if (a.mBr) a.mBr[c] = keep;
+    a.compX[c] = totalW * a.zpX;
+    a.biasX[c] = applyRescale(static_cast<int64_t>(qBw), a.biasRescaleX[c]);
+    a.compH[c] = totalR * a.zpH;
+    a.biasH[c] = applyRescale(static_cast<int64_t>(qBr), a.biasRescaleH[c]);
+}
+
 // Epilogue shared by both linear stages (gru_forward_gpu_quant.cu:163-178).
 __device__ __forceinline__ int32_t linearEpilogue(int64_t acc, int64_t comp, int64_t biasAcc, Rescale r, int32_t zpOut,
                                                   int32_t lo, int32_t hi, uint8_t &keep) {
@@ -742,15 +823,38 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     auto *comp = ws.take<int64_t>(4 * static_cast<size_t>(C));
     int64_t *compX = comp, *biasX = comp + C, *compH = comp + 2 * C, *biasH = comp + 3 * C;
 
-    // 1. codes
-    launchQuantize<WT>(st, call.W, I, C, iPad, C, ch.effW, 0.f, 0, g.qlo[RXMET_GRU_W], g.qhi[RXMET_GRU_W], D::kPack,
-                       reinterpret_cast<WT *>(wCodes), call.W_q, mk.W);
-    launchQuantize<WT>(st, call.R, H, C, hPad, C, ch.effR, 0.f, 0, g.qlo[RXMET_GRU_R], g.qhi[RXMET_GRU_R], D::kPack,
-                       reinterpret_cast<WT *>(rCodes), call.R_q, mk.R);
-    launchQuantize<int32_t>(st, call.bw, 1, C, 1, C, ch.effBw, 0.f, 0, g.qlo[RXMET_GRU_BW], g.qhi[RXMET_GRU_BW], 1,
-                            bwCodes, call.bw_q, mk.bw);
-    launchQuantize<int32_t>(st, call.br, 1, C, 1, C, ch.effBr, 0.f, 0, g.qlo[RXMET_GRU_BR], g.qhi[RXMET_GRU_BR], 1,
-                            brCodes, call.br_q, mk.br);
+    // 1. codes (8-bit weights: together with the per-channel terms of step 2)
+    constexpr bool kPackedWeights = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value;
+    const bool fusedPrep = kPackedWeights && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr;
+    if (fusedPrep) {
+        WeightPrepArgs p{};
+        p.W = call.W; p.R = call.R; p.bw = call.bw; p.br = call.br;
+        p.I = I; p.H = H; p.C = C; p.iWords = iWords; p.hWords = hWords;
+        p.effW = ch.effW; p.effR = ch.effR; p.effBw = ch.effBw; p.effBr = ch.effBr;
+        p.loW = g.qlo[RXMET_GRU_W]; p.hiW = g.qhi[RXMET_GRU_W]; p.loR = g.qlo[RXMET_GRU_R]; p.hiR = g.qhi[RXMET_GRU_R];
+        p.loBw = g.qlo[RXMET_GRU_BW]; p.hiBw = g.qhi[RXMET_GRU_BW]; p.loBr = g.qlo[RXMET_GRU_BR]; p.hiBr = g.qhi[RXMET_GRU_BR];
+        p.wCodes = reinterpret_cast<int32_t *>(wCodes); p.rCodes = reinterpret_cast<int32_t *>(rCodes);
+        p.bwCodes = bwCodes; p.brCodes = brCodes;
+        p.W_q = call.W_q; p.R_q = call.R_q; p.bw_q = call.bw_q; p.br_q = call.br_q;
+        p.mW = mk.W; p.mR = mk.R; p.mBw = mk.bw; p.mBr = mk.br;
+        p.zpX = g.zp[RXMET_GRU_X]; p.zpH = g.zp[RXMET_GRU_H];
+        p.biasRescaleX = ch.biasX; p.biasRescaleH = ch.biasH;
+        p.compX = compX; p.biasX = biasX; p.compH = compH; p.biasH = biasH;
+        {
+            KernelTimer timer__("prepareWeights", st);
+            prepareWeightsI8<<<(C + 31) / 32, 32 * kPrepLayers, 0, st>>>(p);
+        }
+        afterLaunch("prepareWeights");
+    } else {
+        launchQuantize<WT>(st, call.W, I, C, iPad, C, ch.effW, 0.f, 0, g.qlo[RXMET_GRU_W], g.qhi[RXMET_GRU_W], D::kPack,
+                           reinterpret_cast<WT *>(wCodes), call.W_q, mk.W);
+        launchQuantize<WT>(st, call.R, H, C, hPad, C, ch.effR, 0.f, 0, g.qlo[RXMET_GRU_R], g.qhi[RXMET_GRU_R], D::kPack,
+                           reinterpret_cast<WT *>(rCodes), call.R_q, mk.R);
+        launchQuantize<int32_t>(st, call.bw, 1, C, 1, C, ch.effBw, 0.f, 0, g.qlo[RXMET_GRU_BW], g.qhi[RXMET_GRU_BW], 1,
+                                bwCodes, call.bw_q, mk.bw);
+        launchQuantize<int32_t>(st, call.br, 1, C, 1, C, ch.effBr, 0.f, 0, g.qlo[RXMET_GRU_BR], g.qhi[RXMET_GRU_BR], 1,
+                                brCodes, call.br_q, mk.br);
+    }
     if (call.x_codes_in) {
         {
             KernelTimer timer__("narrowCodes", st);
@@ -782,16 +886,18 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     }
 
     // 2. per-channel terms
-    {
-        KernelTimer timer__("channelPrep", st);
-        channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(wCodes, iWords, C, g.zp[RXMET_GRU_X], bwCodes, ch.biasX, compX, biasX);
+    if (!fusedPrep) {
+        {
+            KernelTimer timer__("channelPrep", st);
+            channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(wCodes, iWords, C, g.zp[RXMET_GRU_X], bwCodes, ch.biasX, compX, biasX);
+        }
+        afterLaunch("channelPrep");
+        {
+            KernelTimer timer__("channelPrep", st);
+            channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(rCodes, hWords, C, g.zp[RXMET_GRU_H], brCodes, ch.biasH, compH, biasH);
+        }
+        afterLaunch("channelPrep");
     }
-    afterLaunch("channelPrep");
-    {
-        KernelTimer timer__("channelPrep", st);
-        channelPrep<WT, AT><<<(C + 127) / 128, 128, 0, st>>>(rCodes, hWords, C, g.zp[RXMET_GRU_H], brCodes, ch.biasH, compH, biasH);
-    }
-    afterLaunch("channelPrep");
 
     // Which recurrence runs decides what the input projection stores.
     int device = 0, smemMax = 0, sms = 0;

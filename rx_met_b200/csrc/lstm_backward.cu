@@ -673,17 +673,22 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     int *tensorStatus = ws.take<int>(1);
     uint32_t *stepMasks = ws.take<uint32_t>(rows * H);
 
+    // Which kernels multiply by the saved integer weight codes directly (QAT on 8-bit grids); the
+    // others read real-valued weights rebuilt here.
+    const bool tensorPath = call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
+                            std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
+    const bool tensorInputGrad = call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I);
     const float *wIh = call.weightIh, *wHh = call.weightHh;
     if (call.quantized) {
         RXMET_REQUIRE(call.weightIhScale && call.weightHhScale, "per-channel weight scales missing");
         RXMET_CUDA(cudaMemcpyAsync(channelScales, call.weightIhScale, sizeof(float) * C, cudaMemcpyHostToDevice, st));
         RXMET_CUDA(cudaMemcpyAsync(channelScales + C, call.weightHhScale, sizeof(float) * C, cudaMemcpyHostToDevice, st));
-        {
+        if (!tensorInputGrad) {
             KernelTimer timer__("lstmDequantWeights", st);
             dequantWeights<<<gridFor(static_cast<size_t>(C) * I, 256), 256, 0, st>>>(call.weightIh, channelScales, C, I, wIhReal);
         }
         afterLaunch("lstmDequantWeights");
-        {
+        if (!tensorPath) {
             KernelTimer timer__("lstmDequantWeights", st);
             dequantWeights<<<gridFor(static_cast<size_t>(C) * H, 256), 256, 0, st>>>(call.weightHh, channelScales + C, C, H, wHhReal);
         }
@@ -724,8 +729,6 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
         const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
         const int block = (C + 31) / 32 * 32;
-        const bool tensorPath = call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
-                                std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
         if (tensorPath) {
             RecurrentMmaArgs m{};
             m.base = a;
@@ -777,7 +780,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         else launch(recurrentBackward<1>, 1);
     }
     if (call.quantized) RXMET_CUDA(cudaMemsetAsync(tensorStatus, 0, sizeof(int), st));
-    if (call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I)) {
+    if (tensorInputGrad) {
         // QAT: gradients times the integer weight codes on the tensor cores, scales folded into the gradients
         int device = 0, sms = 0;
         RXMET_CUDA(cudaGetDevice(&device));
