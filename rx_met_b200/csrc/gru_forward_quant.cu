@@ -877,7 +877,10 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                            g.qlo[RXMET_GRU_H], g.qhi[RXMET_GRU_H], 1, h0Codes, nullptr, mk.h0);
     } else {
         // padding columns hold the zero point too; they meet zero weights, so they do not matter
-        {
+        if constexpr (sizeof(AT) == 1) {
+            // one-byte codes: a memset node instead of a kernel
+            RXMET_CUDA(cudaMemsetAsync(h0Codes, g.zp[RXMET_GRU_H] & 0xff, static_cast<size_t>(B) * hPad, st));
+        } else {
             KernelTimer timer__("fillCodes", st);
             fillCodes<AT><<<gridFor(static_cast<size_t>(B) * hPad, 256), 256, 0, st>>>(h0Codes, static_cast<size_t>(B) * hPad,
                                                                                       g.zp[RXMET_GRU_H]);
