@@ -471,7 +471,8 @@ def lstm_forward_quantized(input, weight_ih, weight_hh, bias_ih=None, bias_hh=No
         mv = [torch.empty_like(p.x), torch.empty_like(p.w_ih), torch.empty_like(p.w_hh),
               p.empty(4 * H) if p.b_ih is not None else p.empty(0), p.empty(4 * H) if p.b_ih is not None else p.empty(0),
               p.empty(1, B, H), p.empty(1, B, H)]
-        mm = [torch.zeros(v.shape, dtype=torch.bool, device=p.device) for v in mv]
+        # every flag is written by the library (0 or 1), so the buffers need no zero-fill
+        mm = [torch.empty(v.shape, dtype=torch.bool, device=p.device) for v in mv]
         ms = L.Masters()
         for n, v, m in zip(L.MASTER_VALUES, mv, mm):
             setattr(ms, n, v.data_ptr() if v.numel() else None)

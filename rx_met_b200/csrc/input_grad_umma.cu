@@ -100,8 +100,9 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
     for (int r = 0; r < kRing; ++r) issueChunk(r, r);
 
     // the weight operand: column n, channels [8 j, 8 j + 8) -> one 16-byte row of a core matrix
+    // (consecutive threads walk the contiguous index of whichever code layout was given)
     for (int item = tid; item < NP * (K / 8); item += kThreads) {
-        const int n = item / (K / 8), k8 = item % (K / 8);
+        const int n = p.codesNK ? item / (K / 8) : item % NP, k8 = p.codesNK ? item % (K / 8) : item / NP;
         float c[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
