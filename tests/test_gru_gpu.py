@@ -178,6 +178,25 @@ def test_backward_quant(gl, cfg_name, shape):
         assert np.array_equal(a[k], b[k]), k
 
 
+def test_backward_quant_row_ranges_of_several_tiles(gl):
+    """Enough rows (T*B = 20480) that every CTA of the tcgen05 input-gradient kernel walks two 128-row
+    tiles and the split-K weight-gradient kernel runs many chunks per split."""
+    shape = (80, 256, 40, 128)
+    T, B, I, H = shape
+    cfg = ol.make_config(**CONFIGS["w8a8"])
+    prob, params = calibrated(shape, seed=91, cfg=cfg, with_h0=True)
+    W, R, bw, br, x, h0 = prob
+    x = (x * 2.5).astype(np.float32)
+    f = ol.forward_quant("orc", W, R, bw, br, x, h0, params)
+    rng = np.random.default_rng(17)
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = rng.standard_normal((T, B, H)).astype(np.float32)
+    want = ol.backward_quant(f, dh_new, f["h"], f["v"], params, f["masks"])
+    got = gl.backward_quant(f, dh_new, f["h"], f["v"], params, f["masks"].arr)
+    for k in want:
+        close(got[k], want[k], what=k)
+
+
 def test_backward_float(gl):
     T, B, I, H = 6, 5, 12, 48
     W, R, bw, br, x, h0 = ol.gru_problem(31, T, B, I, H, with_h0=True)

@@ -177,6 +177,11 @@ def test_quantized_forward_bench_shape_round_trip_and_qat_backward():
     qat_round_trip(20, 256, 40, 128, 77, L.default_config(symmetric_activations=True), batch_first=True)
 
 
+def test_qat_backward_row_ranges_of_several_tiles():
+    """T*B = 20480 rows: every CTA of the tcgen05 input-gradient kernel walks two 128-row tiles."""
+    qat_round_trip(80, 256, 40, 128, 78, L.default_config(symmetric_activations=True), batch_first=False)
+
+
 @pytest.mark.parametrize("T,B,I,H", [(6, 3, 8, 32), (5, 5, 12, 64), (4, 2, 40, 96), (5, 700, 16, 32), (6, 4, 9, 20)])
 def test_qat_backward_other_tile_shapes(T, B, I, H):
     """Every hidden size the tensor-core backward is built for, one / two / four rows per CTA, an
