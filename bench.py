@@ -233,11 +233,13 @@ def run_ours(args):
         timed.launches0 = lib.rxmet_kernel_launch_count()
         start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        host0 = time.perf_counter()
         for i in range(steps):
             start[i].record()
             fn(i)
             stop[i].record()
             flush.zero_()
+        timed.host_ms = (time.perf_counter() - host0) * 1e3 / steps  # host time to enqueue one step
         barrier()
         timed.launches = lib.rxmet_kernel_launch_count() - timed.launches0
         ms = sum(s.elapsed_time(e) for s, e in zip(start, stop))
@@ -255,6 +257,7 @@ def run_ours(args):
         sampler.start()
     total_ms = timed(resident, args.steps, args.warmup)
     launches = timed.launches
+    resident_host_ms = timed.host_ms
     clocks = sampler.stop() if rank == 0 else None
     st_per_step = T * B * world
     value = st_per_step * args.steps / (total_ms * 1e-3)
@@ -351,6 +354,7 @@ def run_ours(args):
     for ev in consumed:
         ev.record()
     e2e_ms = timed(e2e, e2e_steps, min(args.warmup, 3))
+    e2e_host_ms = timed.host_ms
     e2e_value = st_per_step * e2e_steps / (e2e_ms * 1e-3)
     torch.cuda.synchronize()
     losses.append(float(loss_host[(e2e_steps - 1) % 2]))
@@ -374,7 +378,9 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
-                    "final_loss": losses[-1] if losses else None},
+                    "final_loss": losses[-1] if losses else None, "ms_per_step": e2e_ms / e2e_steps,
+                    "host_enqueue_ms_per_step": e2e_host_ms},
+            "host_enqueue_ms_per_step": resident_host_ms,
             "gpu_launches": int(launches), "clocks": clocks, "secondary": secondary,
         }
         print(json.dumps(line), flush=True)

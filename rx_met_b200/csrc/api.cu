@@ -44,6 +44,35 @@ TimingState &timing() {
 
 bool kernelTimingEnabled() { return timing().enabled; }
 
+const DeviceInfo &currentDevice() {
+    constexpr int kMaxDevices = 64;
+    static DeviceInfo table[kMaxDevices];
+    static std::atomic<bool> known[kMaxDevices];
+    int device = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) fail(RXMET_ERR_UNSUPPORTED, "device ordinal %d", device);
+    if (!known[device].load(std::memory_order_acquire)) {
+        DeviceInfo info;
+        info.device = device;
+        RXMET_CUDA(cudaDeviceGetAttribute(&info.smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        RXMET_CUDA(cudaDeviceGetAttribute(&info.sms, cudaDevAttrMultiProcessorCount, device));
+        table[device] = info;  // racing threads write the same values
+        known[device].store(true, std::memory_order_release);
+    }
+    return table[device];
+}
+
+void ensureDynamicSmem(const void *kernel, size_t bytes) {
+    static std::mutex guard;
+    static std::map<std::pair<int, const void *>, size_t> granted;
+    const int device = currentDevice().device;
+    std::lock_guard<std::mutex> lock(guard);
+    size_t &have = granted[{device, kernel}];
+    if (bytes <= have) return;
+    RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    have = bytes;
+}
+
 void kernelTimingBegin(const char *, cudaStream_t stream, cudaEvent_t *start, cudaEvent_t *stop) {
     if (cudaEventCreate(start) != cudaSuccess || cudaEventCreate(stop) != cudaSuccess) {
         *start = *stop = nullptr;

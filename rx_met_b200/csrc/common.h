@@ -91,6 +91,16 @@ class KernelTimer {
     cudaEvent_t start_ = nullptr, stop_ = nullptr;
 };
 
+// Properties of the current device, queried once per device and process (the attribute queries
+// cost microseconds each, and the hot entry points run once per training step).
+struct DeviceInfo {
+    int device = 0, sms = 0, smemMax = 0;
+};
+const DeviceInfo &currentDevice();
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when `bytes` exceeds what the kernel
+// was last given.
+void ensureDynamicSmem(const void *kernel, size_t bytes);
+
 inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Carves aligned sub-buffers out of a caller-provided device workspace.

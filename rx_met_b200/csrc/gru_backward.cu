@@ -21,6 +21,7 @@
 
 #include "common.h"
 #include "gru_backward.h"
+#include "gru_forward_quant.h"
 #include "input_grad_umma.h"
 #include "weight_grad_mma.h"
 
@@ -927,10 +928,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     const rxmet_gru_masks none{};
     const rxmet_gru_masks &mk = call.masks ? *call.masks : none;
 
-    int device = 0, smemMax = 0, sms = 0;
-    RXMET_CUDA(cudaGetDevice(&device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int smemMax = currentDevice().smemMax, sms = currentDevice().sms;
     int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
     if (const char *env = std::getenv("RXMET_GRU_BWD_BT")) bt = std::atoi(env);
     if (bt != 1 && bt != 2 && bt != 4) bt = 2;
@@ -953,8 +951,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         float *Rf = ws.take<float>(static_cast<size_t>(H) * C);
         float *xf = ws.take<float>(rows * I);
         float *chan = ws.take<float>(2 * static_cast<size_t>(C));
-        RXMET_CUDA(cudaMemcpyAsync(chan, e.chan.eff_W.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
-        RXMET_CUDA(cudaMemcpyAsync(chan + C, e.chan.eff_R.data(), sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        // effective scales of W then R: the first two arrays of the page-locked per-channel block
+        RXMET_CUDA(cudaMemcpyAsync(chan, pinnedChannelBlock(e), 2 * sizeof(float) * C, cudaMemcpyHostToDevice, st));
         if (!tensorInputGrad) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(I) * C, 256), 256, 0, st>>>(call.W_q, static_cast<size_t>(I) * C, C, chan, 0.f, 0, Wf);
@@ -1050,7 +1048,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             const size_t smem = a.weightsInSmem ? full : base;
             if (smem > static_cast<size_t>(smemMax))
                 fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
-            RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
             KernelTimer timer__("recurrentBackward", st);
             kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
         };

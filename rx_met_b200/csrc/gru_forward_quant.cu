@@ -31,6 +31,21 @@
 
 namespace rxmet {
 namespace gru {
+
+const int32_t *pinnedChannelBlock(const Exec &e) {
+    std::call_once(e.pinnedOnce, [&] {
+        const size_t C = 3 * static_cast<size_t>(e.hidden);
+        int32_t *host = nullptr;
+        RXMET_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&host), 12 * C * sizeof(int32_t), cudaHostAllocDefault));
+        e.pinnedChannels = std::shared_ptr<int32_t>(host, [](int32_t *ptr) { cudaFreeHost(ptr); });
+        auto putF = [&](size_t slot, const std::vector<float> &v) { std::memcpy(host + slot * C, v.data(), C * 4); };
+        auto putR = [&](size_t slot, const std::vector<Rescale> &v) { std::memcpy(host + slot * C, v.data(), C * 8); };
+        putF(0, e.chan.eff_W); putF(1, e.chan.eff_R); putF(2, e.chan.eff_bw); putF(3, e.chan.eff_br);
+        putR(4, e.chan.gemm_x); putR(6, e.chan.bias_x); putR(8, e.chan.gemm_h); putR(10, e.chan.bias_h);
+    });
+    return e.pinnedChannels.get();
+}
+
 namespace {
 
 // ---- exact dot products ---------------------------------------------------
@@ -741,14 +756,7 @@ struct ChannelDevice {
 ChannelDevice uploadChannels(const Exec &e, Workspace &ws, cudaStream_t st) {
     const size_t C = 3 * static_cast<size_t>(e.hidden);
     auto *block = ws.take<int32_t>(12 * C);
-    std::vector<int32_t> host(12 * C);
-    auto putF = [&](size_t slot, const std::vector<float> &v) { std::memcpy(&host[slot * C], v.data(), C * 4); };
-    auto putR = [&](size_t slot, const std::vector<Rescale> &v) { std::memcpy(&host[slot * C], v.data(), C * 8); };
-    putF(0, e.chan.eff_W); putF(1, e.chan.eff_R); putF(2, e.chan.eff_bw); putF(3, e.chan.eff_br);
-    putR(4, e.chan.gemm_x); putR(6, e.chan.bias_x); putR(8, e.chan.gemm_h); putR(10, e.chan.bias_h);
-    // The source is pageable host memory: the runtime stages it before returning, so the
-    // temporary may die at the end of this function.
-    RXMET_CUDA(cudaMemcpyAsync(block, host.data(), host.size() * 4, cudaMemcpyHostToDevice, st));
+    RXMET_CUDA(cudaMemcpyAsync(block, pinnedChannelBlock(e), 12 * C * sizeof(int32_t), cudaMemcpyHostToDevice, st));
     ChannelDevice d;
     d.effW = reinterpret_cast<const float *>(block);
     d.effR = d.effW + C; d.effBw = d.effW + 2 * C; d.effBr = d.effW + 3 * C;
@@ -903,10 +911,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     }
 
     // Which recurrence runs decides what the input projection stores.
-    int device = 0, smemMax = 0, sms = 0;
-    RXMET_CUDA(cudaGetDevice(&device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int smemMax = currentDevice().smemMax, sms = currentDevice().sms;
     constexpr bool kI8 = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value &&
                          std::is_same<LT, int16_t>::value;
     const int blockI8 = padTo(C, 32);
@@ -938,8 +943,9 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                 KernelTimer timer__("inputLinear", st);
 #define RXMET_IL_CASE(N)                                                                                                   \
     case N: {                                                                                                              \
-        int perSm = 1;                                                                                                     \
-        RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, inputLinearI8<N>, block, 0));                     \
+        static int perSmFor[17] = {};  /* resident CTAs per SM by block size / 32, asked once */                          \
+        int &perSm = perSmFor[block / 32];                                                                                 \
+        if (perSm == 0) RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, inputLinearI8<N>, block, 0));     \
         const int grid = std::max(1, std::min(blocks, sms * std::max(1, perSm)));                                          \
         inputLinearI8<N><<<grid, block, 0, st>>>(reinterpret_cast<const int32_t *>(xCodes), static_cast<int>(rows), iWords, C, \
                                                  reinterpret_cast<const int32_t *>(wCodes), compX, biasX, ch.gemmX, zp, qlo, qhi, \
@@ -982,7 +988,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
         if (!a.weightsInSmem) smem = recurrentSmemBytes(H, hWords, D::kPack, sizeof(WWord), sizeof(AT), BT, false);
         if (smem > static_cast<size_t>(smemMax))
             fail(RXMET_ERR_UNSUPPORTED, "hidden size %d needs %zu bytes of shared memory per CTA", H, smem);
-        RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
         {
             KernelTimer timer__("recurrentForward", st);
             kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a, g);

@@ -6,6 +6,7 @@
 
 #include <cstdint>
 #include <memory>
+#include <mutex>
 #include <vector>
 
 #include "rxmet_b200.h"
@@ -64,6 +65,11 @@ struct Exec {
     CodeClass weightClass = CodeClass::I8;  // W and R codes
     CodeClass actClass = CodeClass::I8;     // x and h codes
     CodeClass linearClass = CodeClass::I16; // ih / hh linear codes
+    // Page-locked host copy of the per-channel block (four float arrays, four Rescale arrays) in
+    // the layout the kernels read, filled on first use: uploads from it are plain asynchronous
+    // copies, while pageable sources make the runtime stage every call.
+    mutable std::once_flag pinnedOnce;
+    mutable std::shared_ptr<int32_t> pinnedChannels;
 };
 
 // Encodings from ranges (reference: operators/quant-gru/src/gru_host.cc:13-125).

@@ -723,10 +723,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         a.dqC = call.dqC; a.dqTanh = call.dqTanh;
         for (int g = 0; g < 4; ++g) a.dqGate[g] = call.dqGate[g];
         a.mk = mk; a.gIh = gIh; a.gHh = gHh; a.dh0 = call.grads.initial_hidden; a.dc0 = call.grads.initial_cell;
-        int device = 0, smemMax = 0, sms = 0;
-        RXMET_CUDA(cudaGetDevice(&device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        const int smemMax = currentDevice().smemMax, sms = currentDevice().sms;
         const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
         const int block = (C + 31) / 32 * 32;
         if (tensorPath) {
@@ -768,7 +765,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             a.smemRows = perGate;
             a.smemStride = strideFor(std::max(perGate, 1));
             const size_t smem = base + sizeof(float) * 4 * static_cast<size_t>(H) * a.smemStride;
-            RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
             {
                 KernelTimer timer__("lstmRecurrentBackward", st);
                 kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a);
@@ -782,9 +779,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     if (call.quantized) RXMET_CUDA(cudaMemsetAsync(tensorStatus, 0, sizeof(int), st));
     if (tensorInputGrad) {
         // QAT: gradients times the integer weight codes on the tensor cores, scales folded into the gradients
-        int device = 0, sms = 0;
-        RXMET_CUDA(cudaGetDevice(&device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        const int sms = currentDevice().sms;
         igrad::Problem pg{};
         pg.G = gIh; pg.kScale = channelScales; pg.codesKN = call.weightIh; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
         pg.mask = static_cast<const uint8_t *>(mk.input); pg.maskKeeps = 0; pg.out = call.grads.input; pg.status = tensorStatus;
@@ -821,9 +816,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         if (T > 1)
             RXMET_CUDA(cudaMemcpyAsync(hPrev + static_cast<size_t>(B) * H, call.hiddenOutputs, stateBytes * (T - 1),
                                        cudaMemcpyDeviceToDevice, st));
-        int device = 0, sms = 0;
-        RXMET_CUDA(cudaGetDevice(&device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        const int sms = currentDevice().sms;
         auto planFor = [&](int M) {
             wgrad::Plan pl = wgrad::plan(static_cast<int>(rows), M, C, sms);
             if (!pl.tensorMemory && pl.splits > kMaxTensorSplits) {

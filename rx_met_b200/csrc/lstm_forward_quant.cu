@@ -489,9 +489,7 @@ void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, 
         a.T = T; a.B = B; a.H = H; a.kWords = p.kWordsHh;
         a.words = wHh; a.addend = addHh; a.channel = channel; a.tables = tables; a.lhs = lhs; a.h0 = h0q; a.c0 = c0c;
         a.s = s; a.output = call.output; a.finalHidden = call.finalHidden; a.finalCell = call.finalCell; a.ck = ck;
-        int device = 0, sms = 0;
-        RXMET_CUDA(cudaGetDevice(&device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        const int sms = currentDevice().sms;
         // BT*H elements must not exceed the 4H threads of a CTA
         const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
         auto launch = [&](auto kernel, int BT) {

@@ -60,6 +60,12 @@ class OperatorQuantConfig:
         self.pot_scale_method_ = cabi.POT_COVER_RANGE
         self.pot_scale_tolerance_ = 0.02
 
+    def __setattr__(self, key, value):
+        # a change counter lets holders of a converted copy (GRUQuantParams) notice assignments
+        object.__setattr__(self, key, value)
+        if not key.startswith("_"):
+            object.__setattr__(self, "_version", getattr(self, "_version", 0) + 1)
+
     # the reference exposes the same field under two spellings
     @property
     def usePO2_(self):
@@ -206,7 +212,25 @@ class GRUQuantParams:
             setattr(self, f"scale_{name}_", [])
         self.bitwidth_config_ = OperatorQuantConfig()
 
+    def __setattr__(self, key, value):
+        object.__setattr__(self, key, value)
+        if not key.startswith("_"):
+            object.__setattr__(self, "_c_copy", None)
+
     def _to_c(self):
+        """The C struct and the arrays its pointers refer to.  The conversion is kept until an
+        attribute of this object or of its bit-width configuration is assigned (as with the
+        reference's bound classes, editing a returned list in place changes nothing)."""
+        cfg = self.bitwidth_config_
+        stamp = (id(cfg), getattr(cfg, "_version", 0))
+        cached = getattr(self, "_c_copy", None)
+        if cached is not None and cached[0] == stamp:
+            return cached[1], cached[2]
+        c, keep = self._build_c()
+        object.__setattr__(self, "_c_copy", (stamp, c, keep))
+        return c, keep
+
+    def _build_c(self):
         if self.hidden_ <= 0:
             raise ValueError("GRUQuantParams hidden size must be > 0")
         n = 3 * self.hidden_
@@ -391,25 +415,42 @@ _MASK_SHAPES = lambda T, B, I, H: {  # noqa: E731
     "gate_output": (T, B, 3 * H), "h": (T, B, H)}
 
 
+def _carve(device, dtype, shapes):
+    """Tensors of the given shapes as views of ONE allocation (each starts on a 16-byte boundary):
+    a forward call returns 16 small tensors, and one allocator round trip per tensor is host time
+    on the critical path of a training step."""
+    item = torch.empty((), dtype=dtype).element_size()
+    per = 16 // item
+    counts = [1 if not shape else int(torch.Size(shape).numel()) for shape in shapes]
+    offsets, total = [], 0
+    for n in counts:
+        offsets.append(total)
+        total += (n + per - 1) // per * per
+    pool = torch.empty((max(total, 1),), dtype=dtype, device=device)
+    return [pool[o:o + n].view(shape) for o, n, shape in zip(offsets, counts, shapes)]
+
+
 def _forward_quant(is_training, T, B, I, H, W, R, bw, br, x, h0, quant_params, code_dtype):
     lib = cabi.load_library()
     W, R, bw, br, x, h0v = _common_inputs(T, B, I, H, W, R, bw, br, x, h0)
     dev = x.device
     params, keep = quant_params._to_c()
-    i32 = dict(dtype=torch.int32, device=dev)
     h = torch.empty((T + 1, B, H), dtype=torch.float32, device=dev)
     v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=dev)
-    codes = {"W_q": torch.empty((I, 3 * H), **i32), "R_q": torch.empty((H, 3 * H), **i32),
-             "bw_q": torch.empty((3 * H,), **i32), "br_q": torch.empty((3 * H,), **i32),
-             "x_q": torch.empty((T, B, I), **i32)}
-    masks = {}
+    code_shapes = {"W_q": (I, 3 * H), "R_q": (H, 3 * H), "bw_q": (3 * H,), "br_q": (3 * H,), "x_q": (T, B, I)}
+    codes = dict(zip(code_shapes, _carve(dev, torch.int32, list(code_shapes.values()))))
     mask_struct = cabi.Masks()
-    for name, shape in _MASK_SHAPES(T, B, I, H).items():
-        if is_training and not (name == "h0" and h0v is None):
-            masks[name] = torch.empty(shape, dtype=torch.uint8, device=dev)
+    shapes = _MASK_SHAPES(T, B, I, H)
+    wanted = [name for name in shapes if is_training and not (name == "h0" and h0v is None)]
+    masks = dict(zip(wanted, _carve(dev, torch.uint8, [shapes[name] for name in wanted]))) if wanted else {}
+    empty = None
+    for name in shapes:
+        if name in masks:
             setattr(mask_struct, name, masks[name].data_ptr())
         else:
-            masks[name] = torch.empty((0,), dtype=torch.uint8, device=dev)
+            if empty is None:
+                empty = torch.empty((0,), dtype=torch.uint8, device=dev)
+            masks[name] = empty
     ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(1, T, B, I, H))
     with torch.cuda.device(dev):
         cabi.check(lib.rxmet_gru_forward_quant(
@@ -488,9 +529,8 @@ def _backward_quant(T, B, I, H, W_q, R_q, bw_q, br_q, x_q, dh_new, h, v, quant_p
             m = m.contiguous()
             live.append(m)
             setattr(mask_struct, name, m.data_ptr())
-    f32 = dict(dtype=torch.float32, device=dev)
-    dx = torch.empty((T, B, I), **f32); dW = torch.empty((I, 3 * H), **f32); dR = torch.empty((H, 3 * H), **f32)
-    dbw = torch.empty((3 * H,), **f32); dbr = torch.empty((3 * H,), **f32); dh0 = torch.empty((B, H), **f32)
+    dx, dW, dR, dbw, dbr, dh0 = _carve(dev, torch.float32,
+                                       [(T, B, I), (I, 3 * H), (H, 3 * H), (3 * H,), (3 * H,), (B, H)])
     ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(2, T, B, I, H))
     with torch.cuda.device(dev):
         cabi.check(lib.rxmet_gru_backward_quant(
@@ -534,9 +574,8 @@ def backward_fp(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x
     h = _check_f32(h, "h", (T + 1, B, H))
     v = _check_f32(v, "v", (T, B, 4 * H))
     dev = x.device
-    f32 = dict(dtype=torch.float32, device=dev)
-    dx = torch.empty((T, B, I), **f32); dW = torch.empty((I, 3 * H), **f32); dR = torch.empty((H, 3 * H), **f32)
-    dbw = torch.empty((3 * H,), **f32); dbr = torch.empty((3 * H,), **f32); dh0 = torch.empty((B, H), **f32)
+    dx, dW, dR, dbw, dbr, dh0 = _carve(dev, torch.float32,
+                                       [(T, B, I), (I, 3 * H), (H, 3 * H), (3 * H,), (3 * H,), (B, H)])
     ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(2, T, B, I, H))
     with torch.cuda.device(dev):
         cabi.check(lib.rxmet_gru_backward_fp(

@@ -118,3 +118,31 @@ def test_histogram_argument_checks():
     assert lib.rxmet_histogram_calibrate(C.byref(a), 8, 0, 1, 0, C.c_float(0), C.byref(out, 0), C.byref(out, 4), C.byref(out, 8)) == -1
     assert b"invalid" in lib.rxmet_last_error()
     assert lib.rxmet_histogram_workspace_bytes(2048) > 8192
+
+
+def test_quant_params_conversion_is_kept_until_an_attribute_is_assigned():
+    """The binding converts GRUQuantParams to the C struct once and keeps it; assigning any attribute of
+    the parameters or of their bit-width configuration makes the next call convert again."""
+    import rx_met_b200.gru_interface_binding as binding
+
+    p = binding.GRUQuantParams()
+    p.hidden_ = 2
+    for name in ("W", "R", "bw", "br"):
+        setattr(p, f"scale_{name}_", [0.5] * 6)
+    p.scale_x_ = 0.25
+    c1, keep1 = p._to_c()
+    c2, _ = p._to_c()
+    assert c1 is c2 and c1.scale[cabi.X] == 0.25 and keep1[0][5] == 0.5
+    p.scale_x_ = 0.125
+    c3, _ = p._to_c()
+    assert c3 is not c1 and c3.scale[cabi.X] == 0.125
+    p.bitwidth_config_.x_ = 16
+    c4, _ = p._to_c()
+    assert c4 is not c3 and c4.config.bits[cabi.X] == 16
+    p.scale_W_ = [0.75] * 6
+    c5, keep5 = p._to_c()
+    assert c5 is not c4 and keep5[0][0] == 0.75
+    cfg = binding.OperatorQuantConfig()
+    cfg.h_ = 12
+    p.bitwidth_config_ = cfg
+    assert p._to_c()[0].config.bits[cabi.H] == 12
