@@ -465,6 +465,51 @@ RXMET_API int rxmet_aimet_minmax_encoding(int bw, int dtype, double stats_min, d
                                           int strict_symmetric, int unsigned_symmetric,
                                           rxmet_aimet_encoding *encoding);
 
+/* Running histogram statistics of the histogram analyzers (struct PDF,
+ * native/common/src/math_functions.hpp): left bucket edges and the running
+ * average of the per-batch probabilities, rxmet_aimet_pdf_size() doubles each,
+ * in host memory owned by the caller. */
+typedef struct rxmet_aimet_pdf {
+    double *x_left;
+    double *pdf;
+    int32_t initialized; /* the first batch that is not all zero fixes the range */
+    int32_t iterations;  /* batches averaged so far */
+    int32_t updated;     /* a batch was offered (all-zero batches count) */
+} rxmet_aimet_pdf;
+
+RXMET_API int rxmet_aimet_pdf_reset(rxmet_aimet_pdf *pdf);
+/* UpdatePdf (native/common/src/math_functions.cpp:272-316) in three steps, so that the counting
+ * can run wherever the data lives:
+ *   plan   - from the batch extremes: on the first non-zero batch the range (InitializePdf,
+ *            :226-269: tripled around its centre); returns the bucket size and offset for the
+ *            counting, or *skip = 1 for an all-zero batch before any range exists;
+ *   count  - rxmet_aimet_histogram on the device (or any exact counter);
+ *   commit - pdf = (pdf * iterations + histogram / count) / (iterations + 1). */
+RXMET_API int rxmet_aimet_pdf_plan(rxmet_aimet_pdf *pdf, float batch_min, float batch_max, int signed_values,
+                                   double *bucket_size, int *pdf_offset, int *skip);
+RXMET_API int rxmet_aimet_pdf_commit(rxmet_aimet_pdf *pdf, const uint32_t *histogram, uint64_t count);
+/* All three steps on a host tensor (the reference's CPU mode). */
+RXMET_API int rxmet_aimet_pdf_update_host(rxmet_aimet_pdf *pdf, const float *data, uint64_t count, int signed_values);
+/* All three steps on a device float tensor: rxmet_aimet_minmax when no range exists yet,
+ * rxmet_aimet_histogram, one synchronisation of the stream per step that returns to the host.
+ * workspace: rxmet_aimet_pdf_workspace_bytes() device bytes. */
+RXMET_API size_t rxmet_aimet_pdf_workspace_bytes(void);
+RXMET_API int rxmet_aimet_pdf_update(rxmet_aimet_pdf *pdf, const float *data_dev, uint64_t count, int signed_values,
+                                     void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* TfEnhancedEncodingAnalyzer<float>::computeEncoding (native/common/src/
+ * TfEnhancedEncodingAnalyzer.cpp:86-411): grid search over (delta, offset) candidates - 17 x 21
+ * clamped to the observed range plus the observed range itself, or 101 deltas on the symmetric
+ * grid - for the least quantization cost + 3 x saturation cost of the bucket centres. */
+RXMET_API int rxmet_aimet_tf_enhanced_encoding(const rxmet_aimet_pdf *pdf, int bw, int symmetric, int strict_symmetric,
+                                               int unsigned_symmetric, rxmet_aimet_encoding *encoding);
+/* PercentileEncodingAnalyzer<float>::computeEncoding (native/common/src/
+ * PercentileEncodingAnalyzer.cpp:86-203): range between the (100 - p) and p percentiles of the
+ * collected distribution (never beyond the observed maximum), zero included, then
+ * rxmet_aimet_compute_encoding. */
+RXMET_API int rxmet_aimet_percentile_encoding(const rxmet_aimet_pdf *pdf, int bw, int symmetric, int strict_symmetric,
+                                              int unsigned_symmetric, float percentile, rxmet_aimet_encoding *encoding);
+
 /* ------------------------------------------------------------------------ */
 /* Allocation-free variant                                                    */
 /* ------------------------------------------------------------------------ */

@@ -15,6 +15,8 @@
 #include "trim_functions.hpp"
 #include "quantization_utils.hpp"
 #include "MinMaxEncodingAnalyzer.h"
+#include "PercentileEncodingAnalyzer.h"
+#include "TfEnhancedEncodingAnalyzer.h"
 
 using namespace DlQuantization;
 
@@ -103,6 +105,38 @@ int ref_aimet_minmax_encoding(int bw, float statsMin, float statsMax, int symmet
         const TfEncoding &e = all[0];
         out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
         return 0;
+    } catch (...) { return -1; }
+}
+
+// Histogram analyzers: the batches (concatenated in `data`, `sizes[i]` values each) go through
+// updateStats in CPU mode, then computeEncoding.  kind 0 = TF-enhanced, 1 = percentile.
+// out: {min, max, delta, offset, bw}; pdfOut (optional): xLeft[PDF_SIZE] then pdf[PDF_SIZE].
+int ref_aimet_histogram_encoding(int kind, const float *data, const uint64_t *sizes, int batches, int bw, int symmetric,
+                                 int strict, int unsignedSymmetric, float percentile, double *out, double *pdfOut) {
+    try {
+        TfEncoding e{};
+        std::vector<std::tuple<double, double>> hist;
+        if (kind == 0) {
+            TfEnhancedEncodingAnalyzer<float> analyzer;
+            for (int b = 0; b < batches; ++b) { analyzer.updateStats(data, sizes[b], COMP_MODE_CPU); data += sizes[b]; }
+            e = analyzer.computeEncoding(static_cast<uint8_t>(bw), symmetric != 0, strict != 0, unsignedSymmetric != 0);
+            hist = analyzer.getStatsHistogram();
+        } else {
+            PercentileEncodingAnalyzer<float> analyzer;
+            analyzer.setPercentileValue(percentile);
+            for (int b = 0; b < batches; ++b) { analyzer.updateStats(data, sizes[b], COMP_MODE_CPU); data += sizes[b]; }
+            e = analyzer.computeEncoding(static_cast<uint8_t>(bw), symmetric != 0, strict != 0, unsignedSymmetric != 0);
+            hist = analyzer.getStatsHistogram();
+        }
+        out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
+        if (pdfOut) {
+            for (size_t i = 0; i < hist.size() && i < static_cast<size_t>(PDF_SIZE); ++i) {
+                pdfOut[i] = std::get<0>(hist[i]);
+                pdfOut[PDF_SIZE + i] = std::get<1>(hist[i]);
+            }
+            if (hist.empty()) for (int i = 0; i < 2 * PDF_SIZE; ++i) pdfOut[i] = 0.0;
+        }
+        return static_cast<int>(hist.size());
     } catch (...) { return -1; }
 }
 

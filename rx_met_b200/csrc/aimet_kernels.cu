@@ -14,6 +14,8 @@
 #include <cmath>
 #include <cstdint>
 
+#include <vector>
+
 #include "common.h"
 #include "rxmet_b200.h"
 
@@ -461,6 +463,43 @@ int rxmet_aimet_histogram(const void *data_dev, uint64_t count, int dtype, doubl
                 static_cast<const T *>(data_dev), count, static_cast<T>(1 / bucket_size), pdf_offset, histogram_dev);
         });
         afterLaunch("pdfHistogram");
+    });
+}
+
+size_t rxmet_aimet_pdf_workspace_bytes(void) {
+    return rxmet_aimet_minmax_workspace_bytes() + 256 + sizeof(uint32_t) * kPdfSize + 256;
+}
+
+int rxmet_aimet_pdf_update(rxmet_aimet_pdf *pdf, const float *data_dev, uint64_t count, int signed_values,
+                           void *workspace_dev, size_t workspace_bytes, void *stream) {
+    return guarded([&] {
+        RXMET_REQUIRE(pdf != nullptr && data_dev != nullptr && count > 0, "pdf update: null pdf or empty tensor");
+        RXMET_REQUIRE(workspace_dev != nullptr && workspace_bytes >= rxmet_aimet_pdf_workspace_bytes(),
+                      "pdf update: workspace too small");
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        char *base = static_cast<char *>(workspace_dev);
+        float *extremes = reinterpret_cast<float *>(base);
+        uint32_t *histogram = reinterpret_cast<uint32_t *>(base + 256);
+        void *scratch = base + 256 + alignUp(sizeof(uint32_t) * kPdfSize, 256);
+        auto check = [](int rc) {
+            if (rc != 0) fail(rc, "%s", std::string(rxmet_last_error()).c_str());
+        };
+        float host[2] = {1.0f, 1.0f};  // only the first batches need the extremes: they fix the range
+        if (!pdf->initialized) {
+            check(rxmet_aimet_minmax(data_dev, count, count, 0, extremes, extremes + 1, scratch,
+                                     rxmet_aimet_minmax_workspace_bytes(), stream));
+            RXMET_CUDA(cudaMemcpyAsync(host, extremes, sizeof(host), cudaMemcpyDeviceToHost, st));
+            RXMET_CUDA(cudaStreamSynchronize(st));
+        }
+        double bucket = 0;
+        int offset = 0, skip = 0;
+        check(rxmet_aimet_pdf_plan(pdf, host[0], host[1], signed_values, &bucket, &offset, &skip));
+        if (skip) return;
+        check(rxmet_aimet_histogram(data_dev, count, 0, bucket, offset, histogram, stream));
+        std::vector<uint32_t> counts(kPdfSize);
+        RXMET_CUDA(cudaMemcpyAsync(counts.data(), histogram, sizeof(uint32_t) * kPdfSize, cudaMemcpyDeviceToHost, st));
+        RXMET_CUDA(cudaStreamSynchronize(st));
+        check(rxmet_aimet_pdf_commit(pdf, counts.data(), count));
     });
 }
 

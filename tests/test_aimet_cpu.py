@@ -174,3 +174,80 @@ def test_library_encodings_match_the_reference():
                 assert all(a == b or (a != a and b != b) for a, b in zip(got, out)), ("minmax", lo, hi, bw, sym, strict, uns)
     e = _Encoding()
     assert lib.rxmet_aimet_compute_encoding(0, C.c_double(0), C.c_double(1), 0, 0, 0, C.byref(e)) == -1
+
+
+class _Pdf(C.Structure):
+    _fields_ = [("x_left", C.POINTER(C.c_double)), ("pdf", C.POINTER(C.c_double)), ("initialized", C.c_int32),
+                ("iterations", C.c_int32), ("updated", C.c_int32)]
+
+
+def _new_pdf(lib):
+    n = lib.rxmet_aimet_pdf_size()
+    x_left, pdf = np.zeros(n, np.float64), np.zeros(n, np.float64)
+    s = _Pdf(x_left.ctypes.data_as(C.POINTER(C.c_double)), pdf.ctypes.data_as(C.POINTER(C.c_double)), 0, 0, 0)
+    assert lib.rxmet_aimet_pdf_reset(C.byref(s)) == 0
+    return s, x_left, pdf
+
+
+def _histogram_cases():
+    rng = np.random.default_rng(11)
+    cases = {
+        "normal": [rng.standard_normal(4000).astype(np.float32) for _ in range(3)],
+        "positive": [np.abs(rng.standard_normal(3000)).astype(np.float32) * 4 for _ in range(2)],
+        "heavy_tail": [(rng.standard_t(2, 5000) * 0.3).astype(np.float32)],
+        "shifted": [(rng.standard_normal(2500) * 0.2 + 5).astype(np.float32), (rng.standard_normal(2500) * 0.2 + 4).astype(np.float32)],
+        "zero_then_data": [np.zeros(100, np.float32), rng.standard_normal(1000).astype(np.float32)],
+        "constant": [np.full(64, 2.5, np.float32)],
+        "outliers_later": [rng.standard_normal(2000).astype(np.float32), (rng.standard_normal(2000) * 30).astype(np.float32)],
+        "only_zero": [np.zeros(50, np.float32)],
+    }
+    return cases
+
+
+@pytest.mark.skipif(ref() is None, reason="compiled reference not available")
+def test_histogram_analyzers_match_the_reference():
+    """Running PDF statistics, TF-enhanced and percentile encodings of the shipped library against the
+    reference's TfEnhancedEncodingAnalyzer<float> / PercentileEncodingAnalyzer<float> driven in CPU mode."""
+    from rx_met_b200 import _cabi
+    lib, r = _cabi.load_library(), ref()
+    n = lib.rxmet_aimet_pdf_size()
+    lib.rxmet_aimet_pdf_update_host.argtypes = [C.POINTER(_Pdf), C.POINTER(C.c_float), C.c_uint64, C.c_int]
+    modes = [(0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)]
+    for name, batches in _histogram_cases().items():
+        s, x_left, pdf = _new_pdf(lib)
+        for b in batches:
+            assert lib.rxmet_aimet_pdf_update_host(C.byref(s), fp(b), b.size, 1) == 0, name
+        data = np.concatenate(batches)
+        sizes = (C.c_uint64 * len(batches))(*[b.size for b in batches])
+        want_pdf = np.zeros(2 * n, np.float64)
+        for bw in (4, 8, 16):
+            for sym, strict, uns in modes:
+                for kind, percentile in ((0, 0.0), (1, 99.9), (1, 100.0), (1, 90.0)):
+                    out = (C.c_double * 5)()
+                    bins = r.ref_aimet_histogram_encoding(kind, fp(data), sizes, len(batches), bw, sym, strict, uns,
+                                                          C.c_float(percentile), out,
+                                                          want_pdf.ctypes.data_as(C.POINTER(C.c_double)))
+                    assert bins >= 0
+                    e = _Encoding()
+                    if kind == 0:
+                        rc = lib.rxmet_aimet_tf_enhanced_encoding(C.byref(s), bw, sym, strict, uns, C.byref(e))
+                    else:
+                        rc = lib.rxmet_aimet_percentile_encoding(C.byref(s), bw, sym, strict, uns, C.c_float(percentile), C.byref(e))
+                    assert rc == 0
+                    got = (e.min, e.max, e.delta, e.offset, float(e.bw))
+                    assert all(a == b for a, b in zip(got, out)), (name, bw, sym, strict, uns, kind, percentile, got, list(out))
+        if bins:
+            np.testing.assert_array_equal(x_left, want_pdf[:n], err_msg=name)
+            np.testing.assert_array_equal(pdf, want_pdf[n:], err_msg=name)
+        else:
+            assert not s.initialized, name
+
+
+def test_histogram_analyzers_before_any_batch():
+    from rx_met_b200 import _cabi
+    lib = _cabi.load_library()
+    s, _, _ = _new_pdf(lib)
+    e = _Encoding()
+    assert lib.rxmet_aimet_tf_enhanced_encoding(C.byref(s), 8, 0, 0, 0, C.byref(e)) == 0
+    assert (e.min, e.max, e.delta, e.offset, e.bw) == (0.0, 0.0, 0.0, 0.0, 0)  # the failure marker
+    assert lib.rxmet_aimet_percentile_encoding(None, 8, 0, 0, 0, C.c_float(99.0), C.byref(e)) == -1

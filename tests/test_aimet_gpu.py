@@ -162,3 +162,46 @@ def test_minmax_and_histogram(env):
     offset = int(np.floor(finite.min() / bucket))
     assert lib.rxmet_aimet_histogram(ptr(src), C.c_uint64(z.size), 0, C.c_double(bucket), offset, ptr(hist), stream(torch)) == 0
     assert int(hist.sum().item()) == finite.size
+
+
+def test_histogram_analyzers_on_device_batches(env):
+    """The running PDF statistics fed from device tensors (min/max and bucket counting on the GPU) and the
+    TF-enhanced / percentile encodings derived from them, against the reference's analyzers driven on the
+    same batches in CPU mode: identical bucket edges, probabilities and encodings."""
+    from test_aimet_cpu import AIMET_REF, _Encoding, _histogram_cases, _new_pdf, _Pdf
+    torch, lib = env
+    if not AIMET_REF.exists():
+        pytest.fail("the compiled reference checker (oracle/_ref/libaimet_ref.so) must travel with the tests")
+    r = C.CDLL(str(AIMET_REF))
+    lib.rxmet_aimet_pdf_workspace_bytes.restype = C.c_size_t
+    lib.rxmet_aimet_pdf_update.argtypes = [C.POINTER(_Pdf), C.c_void_p, C.c_uint64, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    n = lib.rxmet_aimet_pdf_size()
+    ws = torch.empty(lib.rxmet_aimet_pdf_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    rng = np.random.default_rng(5)
+    cases = _histogram_cases()
+    cases["large"] = [(rng.standard_normal(1 << 20) * (1 + i)).astype(np.float32) for i in range(3)]
+    for name, batches in cases.items():
+        s, x_left, pdf = _new_pdf(lib)
+        for b in batches:
+            src = dev(torch, b)
+            rc = lib.rxmet_aimet_pdf_update(C.byref(s), ptr(src), b.size, 1, ptr(ws), ws.numel(), stream(torch))
+            assert rc == 0, lib.rxmet_last_error()
+        data = np.concatenate(batches)
+        sizes = (C.c_uint64 * len(batches))(*[b.size for b in batches])
+        want_pdf = np.zeros(2 * n, np.float64)
+        for bw, sym, strict, uns, kind, percentile in ((8, 0, 0, 0, 0, 0.0), (8, 1, 0, 0, 0, 0.0), (4, 1, 1, 0, 0, 0.0),
+                                                       (8, 0, 0, 0, 1, 99.9), (16, 1, 0, 1, 1, 99.0)):
+            out = (C.c_double * 5)()
+            bins = r.ref_aimet_histogram_encoding(kind, fp(data), sizes, len(batches), bw, sym, strict, uns,
+                                                  C.c_float(percentile), out, want_pdf.ctypes.data_as(C.POINTER(C.c_double)))
+            e = _Encoding()
+            if kind == 0:
+                rc = lib.rxmet_aimet_tf_enhanced_encoding(C.byref(s), bw, sym, strict, uns, C.byref(e))
+            else:
+                rc = lib.rxmet_aimet_percentile_encoding(C.byref(s), bw, sym, strict, uns, C.c_float(percentile), C.byref(e))
+            assert rc == 0
+            got = (e.min, e.max, e.delta, e.offset, float(e.bw))
+            assert all(a == b for a, b in zip(got, out)), (name, bw, sym, strict, uns, kind, got, list(out))
+        if bins:
+            np.testing.assert_array_equal(x_left, want_pdf[:n], err_msg=name)
+            np.testing.assert_array_equal(pdf, want_pdf[n:], err_msg=name)
