@@ -206,6 +206,112 @@ __device__ __forceinline__ GateCodes gruCellFast(int32_t az, int32_t ar, int32_t
     return c;
 }
 
+// round_half_even(p / 2^n) for 1 <= n <= 31 when the quotient fits 32 bits: floor quotient by
+// funnel shift, remainder r < 2^n, and (r + odd(q)) > half is exactly "above half, or half into
+// an odd quotient".
+__device__ __forceinline__ int32_t rshiftRoundNarrow(int64_t p, int n, uint32_t remMask, uint32_t half) {
+    const uint32_t lo = static_cast<uint32_t>(p), hi = static_cast<uint32_t>(static_cast<uint64_t>(p) >> 32);
+    const int32_t q = static_cast<int32_t>(__funnelshift_r(lo, hi, n));
+    const uint32_t r = lo & remMask;
+    return q + static_cast<int32_t>((r + static_cast<uint32_t>(q & 1)) > half);
+}
+
+// One rescale of the fast cell with its constants in registers.  Small operands (grid
+// differences times a 16-bit multiplier, product below 2^31): shift in [0, 31], branch free
+// (shift 0 has an empty remainder and a half nothing exceeds).  Products: `narrow` says that the
+// 64-bit product can be rounded with 32-bit pieces (multiplier at most 2^shift, shift in [1, 31]).
+struct PreparedRescale {
+    int32_t mult, shift;
+    uint32_t remMask, half;
+    bool narrow;
+};
+__device__ __forceinline__ PreparedRescale prepareRescale(Rescale r) {
+    PreparedRescale p;
+    p.mult = r.mult;
+    p.shift = r.shift;
+    const int n = r.shift & 31;
+    p.remMask = (1u << n) - 1u;
+    p.half = n ? (1u << (n - 1)) : 0x7fffffffu;
+    p.narrow = r.shift >= 1 && r.shift <= 31 && r.mult > 0 && static_cast<int64_t>(r.mult) <= (1ll << r.shift);
+    return p;
+}
+__device__ __forceinline__ int32_t rescaleSmallPrepared(int32_t x, const PreparedRescale &p) {
+    const int32_t v = x * p.mult, q = v >> p.shift;
+    const uint32_t r = static_cast<uint32_t>(v) & p.remMask;
+    return q + static_cast<int32_t>((r + static_cast<uint32_t>(q & 1)) > p.half);
+}
+__device__ __forceinline__ int32_t rescaleProductPrepared(int32_t x, const PreparedRescale &p) {
+    const int64_t prod = static_cast<int64_t>(x) * p.mult;
+    return p.narrow ? rshiftRoundNarrow(prod, p.shift, p.remMask, p.half) : static_cast<int32_t>(rshiftRound(prod, p.shift));
+}
+
+// Constants of gruCellFast gathered in registers once per thread (the cell otherwise re-reads
+// them from the shared copy of the parameters in every step).
+struct FastCell {
+    PreparedRescale hhToUpdate, hhToReset, rhToNew, newToH, updateOldToH;
+    int32_t zpHh, zpR, zpN, zpZ, zpH, quantOne;
+    int32_t zpIn[3], loIn[3], hiIn[3];
+    int32_t loH, hiH;
+};
+__device__ __forceinline__ FastCell prepareFastCell(const GateExec &g) {
+    FastCell f;
+    f.hhToUpdate = prepareRescale(g.hh_to_update);
+    f.hhToReset = prepareRescale(g.hh_to_reset);
+    f.rhToNew = prepareRescale(g.rh_to_new);
+    f.newToH = prepareRescale(g.new_to_h);
+    f.updateOldToH = prepareRescale(g.update_old_to_h);
+    f.zpHh = g.zp[RXMET_GRU_WEIGHT_HH_LINEAR];
+    f.zpR = g.zp[RXMET_GRU_RESET_GATE_OUTPUT];
+    f.zpN = g.zp[RXMET_GRU_NEW_GATE_OUTPUT];
+    f.zpZ = g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT];
+    f.zpH = g.zp[RXMET_GRU_H];
+    f.quantOne = g.quant_one;
+    const int ops[3] = {RXMET_GRU_UPDATE_GATE_INPUT, RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT};
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        f.zpIn[i] = g.zp[ops[i]];
+        f.loIn[i] = g.qlo[ops[i]];
+        f.hiIn[i] = g.qhi[ops[i]];
+    }
+    f.loH = g.qlo[RXMET_GRU_H];
+    f.hiH = g.qhi[RXMET_GRU_H];
+    return f;
+}
+
+// gruCellFast with prepared constants: the same arithmetic, value for value.
+__device__ __forceinline__ GateCodes gruCellPrepared(int32_t az, int32_t ar, int32_t an, int32_t hhz, int32_t hhr, int32_t hhn,
+                                                     int32_t hOld, const FastCell &f, const DirectTables &tab, GateMasks &m) {
+    GateCodes c;
+    {
+        const int32_t b = rescaleSmallPrepared(hhz - f.zpHh, f.hhToUpdate);
+        const int32_t pre = clampCode(az + b + f.zpIn[0], f.loIn[0], f.hiIn[0], m.in[0]);
+        const int32_t e = tab.update[pre - f.loIn[0]];
+        c.z = e >> 1;
+        m.out[0] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t b = rescaleSmallPrepared(hhr - f.zpHh, f.hhToReset);
+        const int32_t pre = clampCode(ar + b + f.zpIn[1], f.loIn[1], f.hiIn[1], m.in[1]);
+        const int32_t e = tab.reset[pre - f.loIn[1]];
+        c.r = e >> 1;
+        m.out[1] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t prod = (c.r - f.zpR) * (hhn - f.zpHh);
+        const int32_t rh = rescaleProductPrepared(prod, f.rhToNew);
+        const int32_t pre = clampCode(an + rh + f.zpIn[2], f.loIn[2], f.hiIn[2], m.in[2]);
+        const int32_t e = tab.fresh[pre - f.loIn[2]];
+        c.n = e >> 1;
+        m.out[2] = static_cast<uint8_t>(e & 1);
+    }
+    {
+        const int32_t nAligned = rescaleSmallPrepared(c.n - f.zpN, f.newToH) + f.zpH;
+        const int32_t sum = (c.z - f.zpZ) * (hOld - f.zpH) + (f.quantOne - c.z) * (nAligned - f.zpH);
+        c.h = clampCode(rescaleProductPrepared(sum, f.updateOldToH) + f.zpH, f.loH, f.hiH, m.h);
+    }
+    return c;
+}
+
 // Accumulate a[k] * w[k] exactly.  int8 x int8 packs four products per dp4a.
 template <class AccT>
 __device__ __forceinline__ void macCodes(AccT &acc, int32_t w, int32_t a) {

@@ -321,16 +321,6 @@ __global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, i
 // blockDim.x >= kI8Rows * KW4 * 4 and blockDim.x >= channels.
 constexpr int kI8Rows = 16;
 
-// round_half_even(p / 2^n) for 1 <= n <= 31 when the quotient fits 32 bits: floor quotient by
-// funnel shift, remainder r < 2^n, and (r + odd(q)) > half is exactly "above half, or half into
-// an odd quotient".
-__device__ __forceinline__ int32_t rshiftRoundNarrow(int64_t p, int n, uint32_t remMask, uint32_t half) {
-    const uint32_t lo = static_cast<uint32_t>(p), hi = static_cast<uint32_t>(static_cast<uint64_t>(p) >> 32);
-    const int32_t q = static_cast<int32_t>(__funnelshift_r(lo, hi, n));
-    const uint32_t r = lo & remMask;
-    return q + static_cast<int32_t>((r + static_cast<uint32_t>(q & 1)) > half);
-}
-
 template <int KW4>
 __global__ void __launch_bounds__(512)
 inputLinearI8(const int32_t *__restrict__ x, int rows, int kWords, int channels, const int32_t *__restrict__ w,
@@ -638,12 +628,39 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
     constexpr int kSlots = 2;
     const int elems = nb * H;
     int16_t ihCur[kSlots][3], ihNext[kSlots][3];
-    auto fetch = [&](int t, int16_t (&dst)[kSlots][3]) {
+
+    // hh epilogue of this thread's channel: with |acc + bias - comp| < 2^31, a multiplier that
+    // shrinks and a shift in [1, 31] the rounding rescale is one widening multiply-add and a
+    // 32-bit funnel shift (rshiftRoundNarrow); otherwise the general 64-bit functions.
+    const int64_t hhOffset = bias - cmp;
+    const bool hhNarrow = rs.shift >= 1 && rs.shift <= 31 && rs.mult > 0 && static_cast<int64_t>(rs.mult) <= (1ll << rs.shift) &&
+                          hhOffset > -(1ll << 30) && hhOffset < (1ll << 30);
+    const int64_t hhMulAdd = hhOffset * rs.mult;
+    const uint32_t hhRemMask = (1u << (rs.shift & 31)) - 1u, hhHalf = 1u << ((rs.shift - 1) & 31);
+
+    FastCell fast{};
+    if constexpr (Mode == 2) fast = prepareFastCell(g);
+
+    // per-element output offsets (fixed over the steps; a step adds its own base)
+    size_t offH[kSlots], offC[kSlots], offV[kSlots];
+    int elemB[kSlots], elemJ[kSlots];
+#pragma unroll
+    for (int s2 = 0; s2 < kSlots; ++s2) {
+        const int e = tid + s2 * nthreads;
+        elemB[s2] = e < elems ? e / H : 0;
+        elemJ[s2] = e < elems ? e % H : 0;
+        offH[s2] = static_cast<size_t>(b0 + elemB[s2]) * H + elemJ[s2];
+        offC[s2] = static_cast<size_t>(b0 + elemB[s2]) * C + elemJ[s2];
+        offV[s2] = static_cast<size_t>(b0 + elemB[s2]) * 4 * H + elemJ[s2];
+    }
+    const size_t stepH = static_cast<size_t>(a.B) * H, stepC = static_cast<size_t>(a.B) * C, stepV = 4 * stepH;
+    size_t baseH = 0, baseC = 0, baseV = 0;  // t * step
+    // the three ih terms of an element at the step whose base offset is given
+    auto fetch = [&](size_t stepBase, int16_t (&dst)[kSlots][3]) {
 #pragma unroll
         for (int s2 = 0; s2 < kSlots; ++s2) {
-            const int e = tid + s2 * nthreads;
-            if (e < elems) {
-                const int16_t *row = ih + (static_cast<size_t>(t) * a.B + b0 + e / H) * C + (e % H);
+            if (tid + s2 * nthreads < elems) {
+                const int16_t *row = ih + stepBase + offC[s2];
                 dst[s2][0] = row[0]; dst[s2][1] = row[H]; dst[s2][2] = row[2 * H];
             }
         }
@@ -651,9 +668,8 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
     fetch(0, ihCur);
 
     const int4 *hS4 = reinterpret_cast<const int4 *>(hS);
-    for (int t = 0; t < a.T; ++t) {
-        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
-        if (t + 1 < a.T) fetch(t + 1, ihNext);
+    for (int t = 0; t < a.T; ++t, baseH += stepH, baseC += stepC, baseV += stepV) {
+        if (t + 1 < a.T) fetch(baseC + stepC, ihNext);
 
         if (hasColumn) {
             int32_t acc[BT];
@@ -673,8 +689,15 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
 #pragma unroll
             for (int b = 0; b < BT; ++b) {
                 uint8_t keep;
-                hhS[b * C + tid] = linearEpilogue(acc[b], cmp, bias, rs, zpOut, loOut, hiOut, keep);
-                if (a.maskHh && b < nb) a.maskHh[(rowBase + b) * C + tid] = keep;
+                int32_t code;
+                if (hhNarrow) {
+                    const int64_t prod = static_cast<int64_t>(acc[b]) * rs.mult + hhMulAdd;
+                    code = clampCode(rshiftRoundNarrow(prod, rs.shift, hhRemMask, hhHalf) + zpOut, loOut, hiOut, keep);
+                } else {
+                    code = linearEpilogue(acc[b], cmp, bias, rs, zpOut, loOut, hiOut, keep);
+                }
+                hhS[b * C + tid] = code;
+                if (a.maskHh && b < nb) a.maskHh[baseC + static_cast<size_t>(b0 + b) * C + tid] = keep;
             }
         }
         __syncthreads();
@@ -683,35 +706,34 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
         for (int s2 = 0; s2 < kSlots; ++s2) {
             const int e = tid + s2 * nthreads;
             if (e < elems) {
-                const int b = e / H, j = e % H;
-                const size_t row = rowBase + b;
+                const int b = elemB[s2], j = elemJ[s2];
                 const int32_t *hhRow = hhS + b * C;
                 GateMasks m;
                 const int32_t hOld = hS[b * kPadded + j];
                 const int32_t hhn = hhRow[2 * H + j];
                 GateCodes q;
                 if constexpr (Mode == 2)
-                    q = gruCellFast(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, g, tab, m);
+                    q = gruCellPrepared(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, fast, tab, m);
                 else
                     q = gruCell<Mode == 1>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, g, m);
                 hS[b * kPadded + j] = static_cast<int8_t>(q.h);
-                const size_t ho = (row + a.B) * H + j;
+                const size_t ho = baseH + stepH + offH[s2];  // row t + 1 of h
                 a.h[ho] = static_cast<float>(q.h - zpH) * scaleH;
-                float *vRow = a.v + row * 4 * H;
-                vRow[j] = static_cast<float>(q.z - zZ) * sZ;
-                vRow[H + j] = static_cast<float>(q.r - zR) * sR;
-                vRow[2 * H + j] = static_cast<float>(q.n - zN) * sN;
-                vRow[3 * H + j] = static_cast<float>(hhn - zpOut) * sHh;
+                float *vRow = a.v + baseV + offV[s2];
+                vRow[0] = static_cast<float>(q.z - zZ) * sZ;
+                vRow[H] = static_cast<float>(q.r - zR) * sR;
+                vRow[2 * H] = static_cast<float>(q.n - zN) * sN;
+                vRow[3 * H] = static_cast<float>(hhn - zpOut) * sHh;
                 if (a.hq) a.hq[ho] = q.h;
                 if (a.vq) {
-                    int32_t *vq = a.vq + row * 4 * H;
-                    vq[j] = q.z; vq[H + j] = q.r; vq[2 * H + j] = q.n; vq[3 * H + j] = hhn;
+                    int32_t *vq = a.vq + baseV + offV[s2];
+                    vq[0] = q.z; vq[H] = q.r; vq[2 * H] = q.n; vq[3 * H] = hhn;
                 }
                 if (a.maskGateIn) {
-                    uint8_t *mi = a.maskGateIn + row * C, *mo = a.maskGateOut + row * C;
-                    mi[j] = m.in[0]; mi[H + j] = m.in[1]; mi[2 * H + j] = m.in[2];
-                    mo[j] = m.out[0]; mo[H + j] = m.out[1]; mo[2 * H + j] = m.out[2];
-                    a.maskH[row * H + j] = m.h;
+                    uint8_t *mi = a.maskGateIn + baseC + offC[s2], *mo = a.maskGateOut + baseC + offC[s2];
+                    mi[0] = m.in[0]; mi[H] = m.in[1]; mi[2 * H] = m.in[2];
+                    mo[0] = m.out[0]; mo[H] = m.out[1]; mo[2 * H] = m.out[2];
+                    a.maskH[baseH + offH[s2]] = m.h;
                 }
             }
         }
@@ -803,6 +825,9 @@ bool fastGateMath(const GateExec &g) {
         if (r.shift < 0 || ((spanIh * r.mult) >> r.shift) > 30000) return false;
     for (const Rescale &r : {g.rh_to_new, g.update_old_to_h})
         if (r.mult < 0 || r.mult >= (1 << 16) || r.shift < 0) return false;
+    // the prepared cell shifts 32-bit products by these amounts without a range branch
+    for (const Rescale &r : {g.hh_to_update, g.hh_to_reset, g.new_to_h})
+        if (r.shift > 31) return false;
     return true;
 }
 
