@@ -53,6 +53,13 @@ RXMET_API int rxmet_set_kernel_timing(int enabled);
 RXMET_API int rxmet_get_kernel_timing(const char *kernel_name, double *total_ms, long long *launches);
 RXMET_API int rxmet_reset_kernel_timing(void);
 
+/* Self-test of the bounded device-side wait that the tcgen05 kernels use: launches one CTA that
+ * polls an mbarrier nothing ever arrives on, with the kernels' own poll loop and limit.  The
+ * kernel gives up when the limit runs out, sets status_dev[0] to 1 and returns; the call waits
+ * for it and returns RXMET_ERR_DEVICE_TIMEOUT, the context stays usable.  status_dev: two ints of
+ * device memory (status, polls made); polls_out (optional, host) receives the number of polls. */
+RXMET_API int rxmet_selftest_bounded_wait(int *status_dev, unsigned int *polls_out, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* QuantGRU: configuration and encodings                                     */
 /* ------------------------------------------------------------------------ */

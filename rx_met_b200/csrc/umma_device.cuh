@@ -12,7 +12,7 @@ namespace umma {
 
 constexpr int kTileM = 128;             // accumulator rows = tensor-memory lanes
 constexpr uint32_t kCore = 128;         // bytes of one core matrix: 8 rows of 16 bytes
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20;  // about 0.13 s of polling; a legitimate wait lasts microseconds
 
 __device__ __forceinline__ uint32_t smemAddr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -61,8 +61,9 @@ __device__ __forceinline__ void commitTo(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// Polls the barrier phase of the given parity; false when the limit ran out.
-__device__ __forceinline__ bool waitPhase(uint32_t bar, uint32_t parity) {
+// Polls the barrier phase of the given parity; false when the limit ran out.  `polls`
+// (optional) receives the number of polls made.
+__device__ __forceinline__ bool waitPhase(uint32_t bar, uint32_t parity, uint32_t *polls = nullptr) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         uint32_t done;
         asm volatile(
@@ -74,8 +75,12 @@ __device__ __forceinline__ bool waitPhase(uint32_t bar, uint32_t parity) {
             : "=r"(done)
             : "r"(bar), "r"(parity)
             : "memory");
-        if (done) return true;
+        if (done) {
+            if (polls) *polls = i + 1;
+            return true;
+        }
     }
+    if (polls) *polls = kSpinLimit;
     return false;
 }
 

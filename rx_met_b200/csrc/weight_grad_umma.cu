@@ -326,4 +326,43 @@ void launchTensorMemory(const Problem &prob, int K, int N, int chunkK, int split
 }
 
 }  // namespace wgrad
+
+namespace {
+
+// One warp polls a barrier that nothing completes, with the poll loop of the tcgen05 kernels.
+__global__ void boundedWaitProbe(int *status, unsigned int *polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smemAddr(&bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    uint32_t made = 0;
+    const bool completed = umma::waitPhase(umma::smemAddr(&bar), 0, &made);
+    if (threadIdx.x == 0) {
+        *polls = made;
+        if (!completed) atomicExch(status, 1);
+    }
+}
+
+}  // namespace
 }  // namespace rxmet
+
+extern "C" int rxmet_selftest_bounded_wait(int *status_dev, unsigned int *polls_out, void *stream) {
+    using namespace rxmet;
+    return guarded([&] {
+        RXMET_REQUIRE(status_dev != nullptr, "status_dev must not be null");
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        unsigned int *pollsDev = reinterpret_cast<unsigned int *>(status_dev + 1);
+        RXMET_CUDA(cudaMemsetAsync(status_dev, 0, 2 * sizeof(int), st));
+        boundedWaitProbe<<<1, 32, 0, st>>>(status_dev, pollsDev);
+        afterLaunch("boundedWaitProbe");
+        int status = 0;
+        unsigned int polls = 0;
+        RXMET_CUDA(cudaMemcpyAsync(&status, status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+        RXMET_CUDA(cudaMemcpyAsync(&polls, pollsDev, sizeof(unsigned int), cudaMemcpyDeviceToHost, st));
+        RXMET_CUDA(cudaStreamSynchronize(st));
+        if (polls_out) *polls_out = polls;
+        if (status != 0) fail(RXMET_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out after %u polls", polls);
+    });
+}

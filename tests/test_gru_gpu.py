@@ -333,3 +333,19 @@ def test_kws_body_layer_shapes(gl, cfg_name, shape):
     gb = gl.backward_quant(want, dh_new, want["h"], want["v"], params, want["masks"].arr)
     for k in wb:
         close(gb[k], wb[k], what=k)
+
+
+def test_bounded_device_wait_gives_up_with_a_status(gl):
+    """The poll loop of the tcgen05 kernels on a barrier nothing completes: the kernel returns after its
+    limit, the status word is set, the call reports RXMET_ERR_DEVICE_TIMEOUT and the context keeps working."""
+    import torch
+    lib = cabi.load_library()
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    polls = C.c_uint(0)
+    rc = lib.rxmet_selftest_bounded_wait(C.c_void_p(status.data_ptr()), C.byref(polls),
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == -5, lib.rxmet_last_error()
+    assert b"ran out" in lib.rxmet_last_error()
+    assert status.cpu().tolist()[0] == 1 and polls.value == 1 << 20
+    # the context is still usable
+    assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
