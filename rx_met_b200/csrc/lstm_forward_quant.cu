@@ -260,10 +260,16 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
     const int32_t hStore = s.zp[opO] - s.hShift;  // centred hidden code -> stored byte
     const float scaleH = s.scale[opO];
 
+    // offsets of this thread's element and channel inside one step; a step adds its base
+    const size_t elemC = static_cast<size_t>(b0 + eb) * C + ej, elemH = static_cast<size_t>(b0 + eb) * H + ej;
+    const size_t chanC = static_cast<size_t>(b0) * C + tid;
+    const size_t stepC = static_cast<size_t>(a.B) * C, stepH = static_cast<size_t>(a.B) * H;
+    size_t baseC = 0, baseH = 0;  // t * step
+
     float lhsCur[4] = {0, 0, 0, 0}, lhsNext[4] = {0, 0, 0, 0};
-    auto fetch = [&](int t, float (&dst)[4]) {
+    auto fetch = [&](size_t stepBase, float (&dst)[4]) {
         if (hasElem) {
-            const float *row = a.lhs + (static_cast<size_t>(t) * a.B + b0 + eb) * C + ej;
+            const float *row = a.lhs + stepBase + elemC;
 #pragma unroll
             for (int g = 0; g < 4; ++g) dst[g] = row[g * H];
         }
@@ -272,9 +278,8 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
     __syncthreads();
 
     const int4 *hS4 = reinterpret_cast<const int4 *>(&hS[0][0]);
-    for (int t = 0; t < a.T; ++t) {
-        const size_t rowBase = static_cast<size_t>(t) * a.B + b0;
-        if (t + 1 < a.T) fetch(t + 1, lhsNext);
+    for (int t = 0; t < a.T; ++t, baseC += stepC, baseH += stepH) {
+        if (t + 1 < a.T) fetch(baseC + stepC, lhsNext);
 
         if (hasChannel) {
             int32_t acc[BT];
@@ -297,7 +302,7 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
                 const float cen = linearCentred(acc[b] + addend, outR, hhLo, hhHi, m);
                 rhsS[b * C + tid] = rescaleF(cen, toGate);
                 if (b < nb) {
-                    const size_t o = (rowBase + b) * C + tid;
+                    const size_t o = baseC + chanC + static_cast<size_t>(b) * C;
                     if (a.ck.weight_hh_linear) a.ck.weight_hh_linear[o] = cen + zHh;
                     if (a.ck.weight_hh_linear_clamped) a.ck.weight_hh_linear_clamped[o] = m;
                 }
@@ -306,7 +311,6 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
         __syncthreads();
 
         if (hasElem) {
-            const size_t row = rowBase + eb;
             float outCen[4];
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -314,10 +318,10 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
                 const float cen = fminf(fmaxf(sum, giLo[g]), giHi[g]);
                 const int32_t e = tabS[g * kTableSize + static_cast<int32_t>(cen) + giBase[g]];
                 outCen[g] = static_cast<float>(e >> 1);
-                const size_t o = row * C + g * H + ej;
-                if (a.ck.gate_inputs) a.ck.gate_inputs[o] = cen + static_cast<float>(s.zp[RXMET_LSTM_INPUT_GATE_INPUT + g]);
+                const size_t o = baseC + elemC + g * H;
+                if (a.ck.gate_inputs) a.ck.gate_inputs[o] = cen + s.zpF[RXMET_LSTM_INPUT_GATE_INPUT + g];
                 if (a.ck.gate_inputs_clamped) a.ck.gate_inputs_clamped[o] = (sum < giLo[g]) || (sum > giHi[g]);
-                if (a.ck.gate_outputs) a.ck.gate_outputs[o] = outCen[g] + static_cast<float>(s.zp[RXMET_LSTM_INPUT_GATE_OUTPUT + g]);
+                if (a.ck.gate_outputs) a.ck.gate_outputs[o] = outCen[g] + s.zpF[RXMET_LSTM_INPUT_GATE_OUTPUT + g];
                 if (a.ck.gate_outputs_clamped) a.ck.gate_outputs_clamped[o] = static_cast<uint8_t>(e & 1);
             }
             const float pf = __fmul_rn(outCen[1], cellCen), pi = __fmul_rn(outCen[0], outCen[2]);
@@ -331,13 +335,13 @@ __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ Re
             const float hr = rescaleF(raw, s.productToOutput);
             hiddenCen = fminf(fmaxf(hr, oLo), oHi);
             hS[eb][ej] = static_cast<int8_t>(static_cast<int32_t>(hiddenCen) + hStore);
-            const size_t so = row * H + ej;
+            const size_t so = baseH + elemH;
             a.output[so] = __fmul_rn(hiddenCen, scaleH);
-            if (a.ck.cell_states) a.ck.cell_states[so] = cellCen + static_cast<float>(s.zp[opC]);
+            if (a.ck.cell_states) a.ck.cell_states[so] = cellCen + s.zpF[opC];
             if (a.ck.cell_states_clamped) a.ck.cell_states_clamped[so] = (rounded < cLo) || (rounded > cHi);
-            if (a.ck.cell_tanh_outputs) a.ck.cell_tanh_outputs[so] = tanhCen + static_cast<float>(s.zp[RXMET_LSTM_CELL_TANH_OUTPUT]);
+            if (a.ck.cell_tanh_outputs) a.ck.cell_tanh_outputs[so] = tanhCen + s.zpF[RXMET_LSTM_CELL_TANH_OUTPUT];
             if (a.ck.cell_tanh_outputs_clamped) a.ck.cell_tanh_outputs_clamped[so] = static_cast<uint8_t>(te & 1);
-            if (a.ck.hidden_outputs) a.ck.hidden_outputs[so] = hiddenCen + static_cast<float>(s.zp[opO]);
+            if (a.ck.hidden_outputs) a.ck.hidden_outputs[so] = hiddenCen + s.zpF[opO];
             if (a.ck.hidden_outputs_clamped) a.ck.hidden_outputs_clamped[so] = (hr < oLo) || (hr > oHi);
         }
 #pragma unroll

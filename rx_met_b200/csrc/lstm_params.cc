@@ -484,6 +484,7 @@ std::shared_ptr<const Exec> deriveExec(const rxmet_lstm_quant_params &p, bool re
     for (int op = 0; op < kOps; ++op) {
         const Grid g = gridOf(p.config, op);
         s.zp[op] = isParameter(op) ? 0 : p.zero_point[op];
+        s.zpF[op] = static_cast<float>(s.zp[op]);
         s.lo[op] = g.lo;
         s.hi[op] = g.hi;
         s.scale[op] = isParameter(op) ? 0.0f : p.scale[op];

@@ -48,6 +48,7 @@ struct DevRescale {
 // Scalar parameters, passed to kernels by value.
 struct ScalarExec {
     int32_t zp[kOps];
+    float zpF[kOps];  // the same zero points as floats: kernels add them straight from the argument bank
     int32_t lo[kOps];
     int32_t hi[kOps];
     float scale[kOps];
