@@ -134,7 +134,7 @@ __device__ __forceinline__ float linearCentred(int32_t total, DevRescale out, fl
     return fminf(fmaxf(r, cLo), cHi);
 }
 
-constexpr int kIhRows = 8;
+constexpr int kIhRows = 16;
 
 struct InputLinearArgs {
     int rows, H, kWords;
@@ -148,37 +148,63 @@ struct InputLinearArgs {
     uint8_t *linearClamped;  // optional
 };
 
+// Persistent: a CTA keeps its threads' weight rows and channel constants in registers and walks
+// blocks of kIhRows rows; the codes of the next block are loaded while the current one computes
+// (each staging thread carries one 32-bit word) and read back as 16-byte broadcasts.
+// Requires blockDim.x >= kIhRows * KW (the words of one block) and blockDim.x >= 4H.
 template <int KW>
 __global__ void __launch_bounds__(512) inputLinearQ(const __grid_constant__ InputLinearArgs a) {
-    __shared__ __align__(16) int8_t xs[kIhRows][KW * 4];
-    const int C = 4 * a.H, c = threadIdx.x;
-    const int row0 = blockIdx.x * kIhRows, nRows = min(kIhRows, a.rows - row0);
-    const int padded = a.kWords * 4;
-    for (int i = threadIdx.x; i < kIhRows * KW * 4; i += blockDim.x) {
-        const int r = i / (KW * 4), k = i % (KW * 4);
-        xs[r][k] = (r < nRows && k < padded) ? a.x[static_cast<size_t>(row0 + r) * padded + k] : int8_t(0);
-    }
-    __syncthreads();
-    if (c >= C) return;
+    __shared__ __align__(16) int32_t xs[2][kIhRows][KW];
+    const int C = 4 * a.H, c = threadIdx.x, tid = threadIdx.x;
+    const bool live = c < C;
     uint32_t w[KW];
 #pragma unroll
-    for (int kk = 0; kk < KW; ++kk) w[kk] = kk < a.kWords ? a.words[static_cast<size_t>(kk) * C + c] : 0u;
-    const int32_t addend = a.addend[c];
-    const DevRescale out{a.channel[static_cast<size_t>(kIhOutMult) * C + c], a.channel[static_cast<size_t>(kIhOutPow2) * C + c]};
-    const int op = RXMET_LSTM_WEIGHT_IH_LINEAR, g = c / a.H;
+    for (int kk = 0; kk < KW; ++kk) w[kk] = (live && kk < a.kWords) ? a.words[static_cast<size_t>(kk) * C + c] : 0u;
+    const int32_t addend = live ? a.addend[c] : 0;
+    const DevRescale out = live ? DevRescale{a.channel[static_cast<size_t>(kIhOutMult) * C + c],
+                                             a.channel[static_cast<size_t>(kIhOutPow2) * C + c]}
+                                : DevRescale{1.0f, 1.0f};
+    const int op = RXMET_LSTM_WEIGHT_IH_LINEAR, g = live ? c / a.H : 0;
     const float cLo = static_cast<float>(a.s.lo[op] - a.s.zp[op]), cHi = static_cast<float>(a.s.hi[op] - a.s.zp[op]);
     const DevRescale toGate = a.s.ihToGate[g];
-    for (int r = 0; r < nRows; ++r) {
-        int32_t acc = 0;
-        const int32_t *xr = reinterpret_cast<const int32_t *>(xs[r]);
+    const float zp = a.s.zpF[op];
+
+    const int blocks = (a.rows + kIhRows - 1) / kIhRows;
+    const int sRow = tid / KW, sWord = tid % KW;  // the word of a block this thread stages
+    const bool stager = tid < kIhRows * KW;
+    const int32_t *xWords = reinterpret_cast<const int32_t *>(a.x);  // [rows][kWords]
+    auto fetch = [&](int blk) -> int32_t {
+        const int row = blk * kIhRows + sRow;
+        return (stager && blk < blocks && row < a.rows && sWord < a.kWords) ? xWords[static_cast<size_t>(row) * a.kWords + sWord] : 0;
+    };
+    int buf = 0;
+    if (stager) xs[0][sRow][sWord] = fetch(blockIdx.x);
+    __syncthreads();
+    for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const int32_t pending = fetch(blk + gridDim.x);
+        const int row0 = blk * kIhRows, nRows = min(kIhRows, a.rows - row0);
+        if (live) {
+            size_t o = static_cast<size_t>(row0) * C + c;
+            for (int r = 0; r < nRows; ++r, o += C) {
+                int32_t acc = 0;
 #pragma unroll
-        for (int kk = 0; kk < KW; ++kk) acc = __dp4a(static_cast<int32_t>(w[kk]), xr[kk], acc);
-        uint8_t m;
-        const float cen = linearCentred(acc + addend, out, cLo, cHi, m);
-        const size_t o = static_cast<size_t>(row0 + r) * C + c;
-        a.lhs[o] = rescaleF(cen, toGate);
-        if (a.linear) a.linear[o] = cen + static_cast<float>(a.s.zp[op]);
-        if (a.linearClamped) a.linearClamped[o] = m;
+                for (int k4 = 0; k4 < KW / 4; ++k4) {
+                    const int4 xv = *reinterpret_cast<const int4 *>(&xs[buf][r][4 * k4]);
+                    acc = __dp4a(static_cast<int32_t>(w[4 * k4 + 0]), xv.x, acc);
+                    acc = __dp4a(static_cast<int32_t>(w[4 * k4 + 1]), xv.y, acc);
+                    acc = __dp4a(static_cast<int32_t>(w[4 * k4 + 2]), xv.z, acc);
+                    acc = __dp4a(static_cast<int32_t>(w[4 * k4 + 3]), xv.w, acc);
+                }
+                uint8_t m;
+                const float cen = linearCentred(acc + addend, out, cLo, cHi, m);
+                a.lhs[o] = rescaleF(cen, toGate);
+                if (a.linear) a.linear[o] = cen + zp;
+                if (a.linearClamped) a.linearClamped[o] = m;
+            }
+        }
+        if (stager) xs[buf ^ 1][sRow][sWord] = pending;
+        __syncthreads();
+        buf ^= 1;
     }
 }
 
@@ -479,12 +505,21 @@ void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, 
         a.rows = static_cast<int>(p.rows); a.H = H; a.kWords = p.kWordsIh;
         a.x = xq; a.words = wIh; a.addend = addIh; a.channel = channel; a.s = s; a.lhs = lhs;
         a.linear = ck.weight_ih_linear; a.linearClamped = ck.weight_ih_linear_clamped;
-        const int grid = static_cast<int>((p.rows + kIhRows - 1) / kIhRows);
+        const int blocks = static_cast<int>((p.rows + kIhRows - 1) / kIhRows);
+        // the staging of a block needs kIhRows * KW threads
+        const int blockIh = std::max(block, kIhRows * p.kwIh);
+        auto launchIh = [&](auto kernel) {
+            static int perSmFor[17] = {};  // resident CTAs per SM by block size / 32, asked once per kernel
+            int &perSm = perSmFor[blockIh / 32];
+            if (perSm == 0) RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, blockIh, 0));
+            const int grid = std::max(1, std::min(blocks, currentDevice().sms * std::max(1, perSm)));
+            kernel<<<grid, blockIh, 0, st>>>(a);
+        };
         {
             KernelTimer timer__("lstmInputLinearQ", st);
-            if (p.kwIh == 8) inputLinearQ<8><<<grid, block, 0, st>>>(a);
-            else if (p.kwIh == 16) inputLinearQ<16><<<grid, block, 0, st>>>(a);
-            else inputLinearQ<32><<<grid, block, 0, st>>>(a);
+            if (p.kwIh == 8) launchIh(inputLinearQ<8>);
+            else if (p.kwIh == 16) launchIh(inputLinearQ<16>);
+            else launchIh(inputLinearQ<32>);
         }
         afterLaunch("lstmInputLinearQ");
     }
