@@ -743,13 +743,26 @@ __global__ void __launch_bounds__(256, 2) weightGradMma(const WeightGradProblem 
 // A CTA owns 64 outputs; its four thread layers each sum every fourth split and layer 0 adds the
 // four sums in layer order, so the result does not depend on the launch.
 // A set status word (a bounded wait of the producing kernel gave up) turns the results into NaN.
+// One launch reduces both problems of a step (blockIdx.y: 0 = input weights, 1 = recurrent weights).
 constexpr int kReduceLayers = 4, kReduceWidth = 64;
+struct ReduceJob {
+    const float *partial;
+    int splits, M;
+    float scale;
+    const uint8_t *weightMask, *biasMask;
+    float *weight, *bias;
+};
 __global__ void __launch_bounds__(kReduceWidth * kReduceLayers)
-reduceWeightGrad(const float *__restrict__ partial, int splits, int M, int N, float scale,
-                 const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
-                 const int *__restrict__ status, float *__restrict__ weight, float *__restrict__ bias) {
+reduceWeightGrad(const ReduceJob jobX, const ReduceJob jobH, int N, const int *__restrict__ status) {
     __shared__ float layer[kReduceLayers][kReduceWidth];
+    const ReduceJob &job = blockIdx.y == 0 ? jobX : jobH;
+    const float *__restrict__ partial = job.partial;
+    const int splits = job.splits, M = job.M;
+    const float scale = job.scale;
+    const uint8_t *__restrict__ weightMask = job.weightMask, *__restrict__ biasMask = job.biasMask;
+    float *__restrict__ weight = job.weight, *__restrict__ bias = job.bias;
     const size_t total = static_cast<size_t>(M + 1) * N;
+    if (static_cast<size_t>(blockIdx.x) * kReduceWidth >= total) return;  // the other problem is larger
     const size_t i = static_cast<size_t>(blockIdx.x) * kReduceWidth + threadIdx.x;
     float s = 0.0f;
     if (i < total) {
@@ -1090,17 +1103,12 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         wgrad::launch(ph, K, C, planH, st);
         afterLaunch("weightGrad");
         {
+            const ReduceJob jobX{px.partial, planX.splits, I, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw};
+            const ReduceJob jobH{ph.partial, planH.splits, H, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr};
+            const size_t largest = static_cast<size_t>(std::max(I, H) + 1) * C;
             KernelTimer timer__("reduceWeightGrad", st);
-            reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(I + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
-                px.partial, planX.splits, I, C, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, status,
-                call.dW, call.dbw);
-        }
-        afterLaunch("reduceWeightGrad");
-        {
-            KernelTimer timer__("reduceWeightGrad", st);
-            reduceWeightGrad<<<static_cast<unsigned>((static_cast<size_t>(H + 1) * C + kReduceWidth - 1) / kReduceWidth), dim3(kReduceWidth, kReduceLayers), 0, st>>>(
-                ph.partial, planH.splits, H, C, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, status,
-                call.dR, call.dbr);
+            reduceWeightGrad<<<dim3(static_cast<unsigned>((largest + kReduceWidth - 1) / kReduceWidth), 2),
+                               dim3(kReduceWidth, kReduceLayers), 0, st>>>(jobX, jobH, C, status);
         }
         afterLaunch("reduceWeightGrad");
         return;

@@ -524,12 +524,25 @@ __global__ void __launch_bounds__(256) gemmNN(const float *__restrict__ A, const
 // A CTA owns 32 channels x 8 rows; its four thread layers each sum every fourth split, and layer 0
 // adds the four sums in layer order, so the result does not depend on the launch.
 // A set status word (a bounded wait of the producing kernel gave up) turns the results into NaN.
+// One launch reduces both problems of a step (blockIdx.z: 0 = weight_ih, 1 = weight_hh).
 constexpr int kReduceLayers = 4, kReduceRows = 8;
+struct ReduceJob {
+    const float *partial;
+    int splits, M;
+    float scale;
+    const uint8_t *weightMask, *biasMask;
+    float *weight, *bias;
+};
 __global__ void __launch_bounds__(32 * kReduceRows * kReduceLayers)
-reduceWeightGradT(const float *__restrict__ partial, int splits, int M, int C, float scale,
-                  const uint8_t *__restrict__ weightMask, const uint8_t *__restrict__ biasMask,
-                  const int *__restrict__ status, float *__restrict__ weight, float *__restrict__ bias) {
+reduceWeightGradT(const ReduceJob jobIh, const ReduceJob jobHh, int C, const int *__restrict__ status) {
     __shared__ float layer[kReduceLayers][kReduceRows][32];
+    const ReduceJob &job = blockIdx.z == 0 ? jobIh : jobHh;
+    const float *__restrict__ partial = job.partial;
+    const int splits = job.splits, M = job.M;
+    const float scale = job.scale;
+    const uint8_t *__restrict__ weightMask = job.weightMask, *__restrict__ biasMask = job.biasMask;
+    float *__restrict__ weight = job.weight, *__restrict__ bias = job.bias;
+    if (static_cast<int>(blockIdx.y) * kReduceRows > M) return;  // the other problem has more rows
     const size_t slab = static_cast<size_t>(M + 1) * C;
     const int c = blockIdx.x * 32 + threadIdx.x, m = blockIdx.y * kReduceRows + threadIdx.y;
     const bool inside = m <= M && c < C;
@@ -838,17 +851,17 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         afterLaunch("weightGrad");
         wgrad::launch(ph, static_cast<int>(rows), C, planH, st);
         afterLaunch("weightGrad");
-        auto reduce = [&](const float *partial, const wgrad::Plan &pl, int M, float scale, const uint8_t *wm, const uint8_t *bm,
-                          float *w, float *b) {
-            {
-                KernelTimer timer__("lstmReduceWeightGradT", st);
-                reduceWeightGradT<<<dim3((C + 31) / 32, (M + 1 + kReduceRows - 1) / kReduceRows), dim3(32, kReduceRows, kReduceLayers), 0, st>>>(
-                    partial, pl.splits, M, C, scale, wm, bm, tensorStatus, w, b);
-            }
-            afterLaunch("lstmReduceWeightGradT");
-        };
-        reduce(tensorIh, planX, I, call.dqX.scale, mk.weight_ih, mk.bias_ih, call.grads.weight_ih, call.grads.bias_ih);
-        reduce(tensorHh, planH, H, call.dqH.scale, mk.weight_hh, mk.bias_hh, call.grads.weight_hh, call.grads.bias_hh);
+        {
+            const ReduceJob jobIh{tensorIh, planX.splits, I, call.dqX.scale, static_cast<const uint8_t *>(mk.weight_ih),
+                                  static_cast<const uint8_t *>(mk.bias_ih), call.grads.weight_ih, call.grads.bias_ih};
+            const ReduceJob jobHh{tensorHh, planH.splits, H, call.dqH.scale, static_cast<const uint8_t *>(mk.weight_hh),
+                                  static_cast<const uint8_t *>(mk.bias_hh), call.grads.weight_hh, call.grads.bias_hh};
+            const int rowBlocks = (std::max(I, H) + 1 + kReduceRows - 1) / kReduceRows;
+            KernelTimer timer__("lstmReduceWeightGradT", st);
+            reduceWeightGradT<<<dim3((C + 31) / 32, rowBlocks, 2), dim3(32, kReduceRows, kReduceLayers), 0, st>>>(jobIh, jobHh, C,
+                                                                                                                  tensorStatus);
+        }
+        afterLaunch("lstmReduceWeightGradT");
         return;
     }
     auto weightGrad = [&](const float *G, RowSource X, int N, int splits, float *partial, const uint8_t *mask, float *out) {
