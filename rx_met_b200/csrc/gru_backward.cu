@@ -887,7 +887,7 @@ int splitBound(int K, int M, int N) {
 
 void launch(const Problem &prob, int K, int N, const Plan &pl, cudaStream_t st) {
     if (pl.tensorMemory) {
-        launchTensorMemory(prob, K, N, pl.chunkK, pl.splits, st);
+        launchTensorMemory(prob, nullptr, K, N, pl.chunkK, pl.splits, st);
         return;
     }
     const int chunkK = pl.chunkK;
@@ -901,6 +901,17 @@ void launch(const Problem &prob, int K, int N, const Plan &pl, cudaStream_t st) 
 #undef RXMET_WG_CASE
         default: fail(RXMET_ERR_UNSUPPORTED, "weight gradient tile count %d", mt);
     }
+}
+
+void launchPair(const Problem &a, const Plan &planA, const Problem &b, const Plan &planB, int K, int N, cudaStream_t st) {
+    if (planA.tensorMemory && planB.tensorMemory && planA.splits == planB.splits && planA.chunkK == planB.chunkK &&
+        a.status == b.status) {
+        const bool aFirst = a.M >= b.M;
+        launchTensorMemory(aFirst ? a : b, aFirst ? &b : &a, K, N, planA.chunkK, planA.splits, st);
+        return;
+    }
+    launch(a, K, N, planA, st);
+    launch(b, K, N, planB, st);
 }
 
 }  // namespace wgrad
@@ -1098,9 +1109,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
         ph.partial = ws.take<float>(static_cast<size_t>(planH.splits) * (H + 1) * C);
         px.status = ph.status = status;
-        wgrad::launch(px, K, C, planX, st);
-        afterLaunch("weightGrad");
-        wgrad::launch(ph, K, C, planH, st);
+        wgrad::launchPair(px, planX, ph, planH, K, C, st);
         afterLaunch("weightGrad");
         {
             const ReduceJob jobX{px.partial, planX.splits, I, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw};

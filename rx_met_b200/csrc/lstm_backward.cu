@@ -847,9 +847,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             fail(RXMET_ERR_INVALID_ARGUMENT, "the QAT backward needs the quantized initial hidden state");
         }
         px.status = ph.status = tensorStatus;
-        wgrad::launch(px, static_cast<int>(rows), C, planX, st);
-        afterLaunch("weightGrad");
-        wgrad::launch(ph, static_cast<int>(rows), C, planH, st);
+        wgrad::launchPair(px, planX, ph, planH, static_cast<int>(rows), C, st);
         afterLaunch("weightGrad");
         {
             const ReduceJob jobIh{tensorIh, planX.splits, I, call.dqX.scale, static_cast<const uint8_t *>(mk.weight_ih),

@@ -39,11 +39,16 @@ Plan plan(int K, int M, int N, int sms);
 // Upper bound of plan(...).splits over every device, for sizing the partial buffers.
 int splitBound(int K, int M, int N);
 void launch(const Problem &problem, int K, int N, const Plan &plan, cudaStream_t stream);
+// Two problems over the same K rows and N columns (the input and the recurrent weights of a step).
+// When both take the tcgen05 kernel with the same split they share ONE launch, the larger problem's
+// CTAs scheduled first; otherwise two launches.
+void launchPair(const Problem &a, const Plan &planA, const Problem &b, const Plan &planB, int K, int N, cudaStream_t stream);
 
 // The tcgen05 kernel (weight_grad_umma.cu).
 bool tensorMemoryPath(int M, int N);
 int planTensorMemory(int K, int N, int sms, int *chunkK);
-void launchTensorMemory(const Problem &problem, int K, int N, int chunkK, int splits, cudaStream_t stream);
+void launchTensorMemory(const Problem &problem, const Problem *other, int K, int N, int chunkK, int splits,
+                        cudaStream_t stream);
 
 }  // namespace wgrad
 }  // namespace rxmet

@@ -66,7 +66,9 @@ struct Geometry {
 // ring of raw buffers with cp.async, kRing chunks ahead; a warp later converts exactly the pieces
 // it copied, so the ring needs no CTA-wide barrier of its own.
 template <int NT>
-__global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int K, int N, int chunkK, int *status) {
+__global__ void __launch_bounds__(2 * NT, 1)
+weightGradUmma(const Problem first, const Problem second, int K, int N, int chunkK, int *status) {
+    const Problem p = blockIdx.z == 0 ? first : second;  // gridDim.z problems share one launch
     using G = Geometry<NT>;
     constexpr int NW = G::kWarps, CW = NT / 32, AT = G::kAPieces, R = G::kRing, TH = G::kThreads;
     constexpr uint32_t kAKStride = G::kAKStride, kBKStride = G::kBKStride, kABytes = G::kABytes, kBBytes = G::kBBytes;
@@ -285,7 +287,7 @@ __global__ void __launch_bounds__(2 * NT, 1) weightGradUmma(const Problem p, int
 }
 
 template <int NT>
-void launchTile(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+void launchTile(const Problem &prob, const Problem *other, int K, int N, int chunkK, int splits, cudaStream_t st) {
     constexpr size_t smem = Geometry<NT>::kSmem;
     static bool configured = false;
     if (!configured) {
@@ -293,7 +295,8 @@ void launchTile(const Problem &prob, int K, int N, int chunkK, int splits, cudaS
         configured = true;
     }
     KernelTimer timer__("weightGradUmma", st);
-    weightGradUmma<NT><<<dim3(N / NT, splits), Geometry<NT>::kThreads, smem, st>>>(prob, K, N, chunkK, prob.status);
+    weightGradUmma<NT><<<dim3(N / NT, splits, other ? 2 : 1), Geometry<NT>::kThreads, smem, st>>>(
+        prob, other ? *other : prob, K, N, chunkK, prob.status);
 }
 
 int tileColumns(int N) {
@@ -316,11 +319,11 @@ int planTensorMemory(int K, int N, int sms, int *chunkK) {
     return (K + *chunkK - 1) / *chunkK;
 }
 
-void launchTensorMemory(const Problem &prob, int K, int N, int chunkK, int splits, cudaStream_t st) {
+void launchTensorMemory(const Problem &prob, const Problem *other, int K, int N, int chunkK, int splits, cudaStream_t st) {
     switch (tileColumns(N)) {
-        case 256: launchTile<256>(prob, K, N, chunkK, splits, st); break;
-        case 192: launchTile<192>(prob, K, N, chunkK, splits, st); break;
-        case 128: launchTile<128>(prob, K, N, chunkK, splits, st); break;
+        case 256: launchTile<256>(prob, other, K, N, chunkK, splits, st); break;
+        case 192: launchTile<192>(prob, other, K, N, chunkK, splits, st); break;
+        case 128: launchTile<128>(prob, other, K, N, chunkK, splits, st); break;
         default: fail(RXMET_ERR_UNSUPPORTED, "no tensor-memory tile for %d columns", N);
     }
 }
