@@ -180,6 +180,7 @@ def run_ours(args):
     from rx_met_b200 import _cabi as cabi
     from rx_met_b200 import gru_interface_binding as ops
     from rx_met_b200.qat import GruQatStep
+    from rx_met_b200.staging import stage_from_pinned_host
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -312,8 +313,13 @@ def run_ours(args):
         slot = i % 2
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[slot])
-            x_buf[slot].copy_(xs_host[i % n_sets], non_blocking=True)
-            y_buf[slot].copy_(ys_host[i % n_sets], non_blocking=True)
+            if args.e2e_copy == "kernel":
+                # the library's staging kernel: a few CTAs read the pinned buffers over PCIe
+                stage_from_pinned_host(x_buf[slot], xs_host[i % n_sets], ctas=4, stream=copy_stream)
+                stage_from_pinned_host(y_buf[slot], ys_host[i % n_sets], ctas=4, stream=copy_stream)
+            else:
+                x_buf[slot].copy_(xs_host[i % n_sets], non_blocking=True)
+                y_buf[slot].copy_(ys_host[i % n_sets], non_blocking=True)
             copied[slot].record(copy_stream)
 
     def e2e(i):
@@ -379,7 +385,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
                     "final_loss": losses[-1] if losses else None, "ms_per_step": e2e_ms / e2e_steps,
-                    "host_enqueue_ms_per_step": e2e_host_ms},
+                    "host_enqueue_ms_per_step": e2e_host_ms, "copy": args.e2e_copy},
             "host_enqueue_ms_per_step": resident_host_ms,
             "gpu_launches": int(launches), "clocks": clocks, "secondary": secondary,
         }
@@ -530,6 +536,9 @@ def main():
     ap.add_argument("--workload", choices=["gru", "lstm", "aimet"], default="gru",
                     help="with --profile-only: which training loop to run (the bench line is always the GRU QAT step)")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
+    ap.add_argument("--e2e-copy", choices=["kernel", "dma"], default="kernel",
+                    help="how the end-to-end leg moves a step's inputs from pinned host memory: the library's staging "
+                         "kernel (rxmet_stage_from_pinned_host) or copy-engine transfers")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only the device-resident leg (for captures under a profiler); prints no bench line")
     args = ap.parse_args()

@@ -53,6 +53,14 @@ RXMET_API int rxmet_set_kernel_timing(int enabled);
 RXMET_API int rxmet_get_kernel_timing(const char *kernel_name, double *total_ms, long long *launches);
 RXMET_API int rxmet_reset_kernel_timing(void);
 
+/* Host -> device staging by a kernel instead of the copy engine: `ctas` CTAs (default 16 when
+ * <= 0) read the page-locked, device-mapped host buffer over PCIe and write dst_dev with
+ * evict-first stores.  For input staging on a side stream next to a training step, where a
+ * copy-engine transfer of the same bytes slows the step's latency-bound kernels more.
+ * src_host must be page-locked (cudaHostAlloc / cudaHostRegister / torch pin_memory); both
+ * pointers 16-byte aligned. */
+RXMET_API int rxmet_stage_from_pinned_host(void *dst_dev, const void *src_host, size_t bytes, int ctas, void *stream);
+
 /* Self-test of the bounded device-side wait that the tcgen05 kernels use: launches one CTA that
  * polls an mbarrier nothing ever arrives on, with the kernels' own poll loop and limit.  The
  * kernel gives up when the limit runs out, sets status_dev[0] to 1 and returns; the call waits
