@@ -334,8 +334,9 @@ def run_ours(args):
         h, v = out[0], out[1]
         diff = h[1:] - y_dev
         loss = diff.square().mean()
-        dh_new = torch.zeros_like(h)
-        dh_new[1:] = diff * (2.0 / diff.numel())
+        dh_new = torch.empty_like(h)
+        dh_new[0].zero_()
+        torch.mul(diff, 2.0 / diff.numel(), out=dh_new[1:])
         dx, dW, dR, dbw, dbr, _ = ops.backward_quant_int_storage(T, B, I, H, *out[2:7], dh_new, h, v, qp, *out[7:])
         consumed[slot].record()
         grads = [dW, dR, dbw, dbr]

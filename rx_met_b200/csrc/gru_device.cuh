@@ -240,9 +240,14 @@ __device__ __forceinline__ int32_t rescaleSmallPrepared(int32_t x, const Prepare
     const uint32_t r = static_cast<uint32_t>(v) & p.remMask;
     return q + static_cast<int32_t>((r + static_cast<uint32_t>(q & 1)) > p.half);
 }
+// The general rounding shift behind a call: a call is never evaluated speculatively, so code that
+// picks between it and the 32-bit form per value pays for the 64-bit form only when it is taken.
+__device__ __noinline__ int32_t rshiftRoundCalled(int64_t x, int n) { return static_cast<int32_t>(rshiftRound(x, n)); }
+
 __device__ __forceinline__ int32_t rescaleProductPrepared(int32_t x, const PreparedRescale &p) {
     const int64_t prod = static_cast<int64_t>(x) * p.mult;
-    return p.narrow ? rshiftRoundNarrow(prod, p.shift, p.remMask, p.half) : static_cast<int32_t>(rshiftRound(prod, p.shift));
+    if (p.narrow) return rshiftRoundNarrow(prod, p.shift, p.remMask, p.half);
+    return rshiftRoundCalled(prod, p.shift);
 }
 
 // Constants of gruCellFast gathered in registers once per thread (the cell otherwise re-reads

@@ -350,6 +350,9 @@ inputLinearI8(const int32_t *__restrict__ x, int rows, int kWords, int channels,
     const int64_t mulAddGate = -static_cast<int64_t>(zpOut) * gateRs.mult;
     const uint32_t maskGate = (1u << (gateRs.shift & 31)) - 1u, halfGate = 1u << ((gateRs.shift - 1) & 31);
 
+    // does every live channel of this warp take the 32-bit rounding in both rescales?
+    const bool warpNarrow = __all_sync(0xffffffffu, !live || (narrowOut && (!pre.enabled || narrowGate)));
+
     const int blocks = (rows + kI8Rows - 1) / kI8Rows;
     const int sRow = tid / kRowWords, sWord = tid % kRowWords;  // the word of a block this thread stages
     const bool stager = tid < kI8Rows * kRowWords;
@@ -366,33 +369,43 @@ inputLinearI8(const int32_t *__restrict__ x, int rows, int kWords, int channels,
         if (live) {
             int16_t *outPtr = out + static_cast<size_t>(row0) * channels + c;
             uint8_t *maskPtr = mask ? mask + static_cast<size_t>(row0) * channels + c : nullptr;
-            for (int r = 0; r < nRows; ++r) {
-                int32_t acc = 0;
+            // Two copies of the row loop: when every channel of the warp qualifies, the loop holds the
+            // 32-bit rounding only (a per-value choice makes the compiler evaluate both forms).
+            auto rowsLoop = [&](auto narrowTag) {
+                constexpr bool kNarrow = decltype(narrowTag)::value;
+                for (int r = 0; r < nRows; ++r) {
+                    int32_t acc = 0;
 #pragma unroll
-                for (int g4 = 0; g4 < KW4; ++g4) {
-                    const int4 xv = *reinterpret_cast<const int4 *>(&xs[buf][r][4 * g4]);
-                    acc = __dp4a(wreg[4 * g4], xv.x, acc);
-                    acc = __dp4a(wreg[4 * g4 + 1], xv.y, acc);
-                    acc = __dp4a(wreg[4 * g4 + 2], xv.z, acc);
-                    acc = __dp4a(wreg[4 * g4 + 3], xv.w, acc);
+                    for (int g4 = 0; g4 < KW4; ++g4) {
+                        const int4 xv = *reinterpret_cast<const int4 *>(&xs[buf][r][4 * g4]);
+                        acc = __dp4a(wreg[4 * g4], xv.x, acc);
+                        acc = __dp4a(wreg[4 * g4 + 1], xv.y, acc);
+                        acc = __dp4a(wreg[4 * g4 + 2], xv.z, acc);
+                        acc = __dp4a(wreg[4 * g4 + 3], xv.w, acc);
+                    }
+                    const int64_t prod = static_cast<int64_t>(acc) * rs.mult + mulAddOut;
+                    int32_t res;
+                    if constexpr (kNarrow) res = rshiftRoundNarrow(prod, rs.shift, maskOut, halfOut) + zpOut;
+                    else res = (narrowOut ? rshiftRoundNarrow(prod, rs.shift, maskOut, halfOut)
+                                          : static_cast<int32_t>(rshiftRound(prod, rs.shift))) + zpOut;
+                    uint8_t keep;
+                    int32_t q = clampCode(res, lo, hi, keep);
+                    if (pre.enabled) {
+                        const int64_t prodGate = static_cast<int64_t>(q) * gateRs.mult + mulAddGate;
+                        if constexpr (kNarrow) q = rshiftRoundNarrow(prodGate, gateRs.shift, maskGate, halfGate);
+                        else q = narrowGate ? rshiftRoundNarrow(prodGate, gateRs.shift, maskGate, halfGate)
+                                            : static_cast<int32_t>(rshiftRound(prodGate, gateRs.shift));
+                    }
+                    *outPtr = static_cast<int16_t>(q);
+                    outPtr += channels;
+                    if (maskPtr) {
+                        *maskPtr = keep;
+                        maskPtr += channels;
+                    }
                 }
-                const int64_t prod = static_cast<int64_t>(acc) * rs.mult + mulAddOut;
-                const int32_t res = (narrowOut ? rshiftRoundNarrow(prod, rs.shift, maskOut, halfOut)
-                                               : static_cast<int32_t>(rshiftRound(prod, rs.shift))) + zpOut;
-                uint8_t keep;
-                int32_t q = clampCode(res, lo, hi, keep);
-                if (pre.enabled) {
-                    const int64_t prodGate = static_cast<int64_t>(q) * gateRs.mult + mulAddGate;
-                    q = narrowGate ? rshiftRoundNarrow(prodGate, gateRs.shift, maskGate, halfGate)
-                                   : static_cast<int32_t>(rshiftRound(prodGate, gateRs.shift));
-                }
-                *outPtr = static_cast<int16_t>(q);
-                outPtr += channels;
-                if (maskPtr) {
-                    *maskPtr = keep;
-                    maskPtr += channels;
-                }
-            }
+            };
+            if (warpNarrow) rowsLoop(std::true_type{});
+            else rowsLoop(std::false_type{});
         }
         if (stager) xs[buf ^ 1][sRow][sWord] = pending;
         __syncthreads();
@@ -694,7 +707,8 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
                     const int64_t prod = static_cast<int64_t>(acc[b]) * rs.mult + hhMulAdd;
                     code = clampCode(rshiftRoundNarrow(prod, rs.shift, hhRemMask, hhHalf) + zpOut, loOut, hiOut, keep);
                 } else {
-                    code = linearEpilogue(acc[b], cmp, bias, rs, zpOut, loOut, hiOut, keep);
+                    const int64_t prod = (static_cast<int64_t>(acc[b]) - cmp + bias) * static_cast<int64_t>(rs.mult);
+                    code = clampCode(rshiftRoundCalled(prod, rs.shift) + zpOut, loOut, hiOut, keep);
                 }
                 hhS[b * C + tid] = code;
                 if (a.maskHh && b < nb) a.maskHh[baseC + static_cast<size_t>(b0 + b) * C + tid] = keep;
