@@ -223,8 +223,13 @@ struct RecurrentArgs {
     rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearQ)
 };
 
+// The double-precision form (ratios that do not fit Q31) sits behind a call, so that the common
+// single multiply is not accompanied by a speculative evaluation of it.
+__device__ __noinline__ float scaleCellWide(float product, double mantissa, int exponent) {
+    return static_cast<float>(ldexp(static_cast<double>(product) * mantissa, exponent));
+}
 __device__ __forceinline__ float scaleCell(float product, float ratio, double mantissa, int exponent, int usesFp) {
-    if (usesFp) return static_cast<float>(ldexp(static_cast<double>(product) * mantissa, exponent));
+    if (usesFp) return scaleCellWide(product, mantissa, exponent);
     return __fmul_rn(product, ratio);
 }
 
