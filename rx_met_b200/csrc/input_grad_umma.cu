@@ -147,9 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
         }
         __syncwarp();
         issueChunk(g + kRing, slot);
-#ifndef RXMET_NO_PROXY_FENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -202,9 +202,7 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
         convertChunk(slot, stage);
         __syncwarp();
         issueChunk(c + R, slot);
-#ifndef RXMET_NO_PROXY_FENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
