@@ -165,11 +165,38 @@ struct WeightPrepArgs {
     int32_t zpX, zpH;
     const Rescale *biasRescaleX, *biasRescaleH;
     int64_t *compX, *biasX, *compH, *biasH;
+    // Optional second job of the same launch: the input tensor -> codes (blocks beyond the
+    // parameter blocks; same arithmetic as quantizeTensor with one scale).  xSrc null = none.
+    const float *xSrc;
+    int xRows, xCols, xColsPadded;
+    float xScale;
+    int32_t xLo, xHi;
+    int8_t *xCodes;
+    int32_t *xCodes32;
+    uint8_t *xMask;
+    int prepBlocks;
 };
 
 constexpr int kPrepLayers = 32;
 __global__ void __launch_bounds__(32 * kPrepLayers) prepareWeightsI8(const WeightPrepArgs a) {
     __shared__ int32_t sums[2][kPrepLayers][32];
+    if (static_cast<int>(blockIdx.x) >= a.prepBlocks) {  // the input tensor's blocks
+        const size_t total = static_cast<size_t>(a.xRows) * a.xColsPadded;
+        const size_t stride = static_cast<size_t>(gridDim.x - a.prepBlocks) * blockDim.x;
+        for (size_t i = static_cast<size_t>(blockIdx.x - a.prepBlocks) * blockDim.x + threadIdx.x; i < total; i += stride) {
+            const int r = static_cast<int>(i / a.xColsPadded), col = static_cast<int>(i % a.xColsPadded);
+            int32_t q = 0;
+            if (col < a.xCols) {
+                const size_t at = static_cast<size_t>(r) * a.xCols + col;
+                uint8_t keep;
+                q = quantizeValue(a.xSrc[at], a.xScale, a.zpX, a.xLo, a.xHi, keep);
+                if (a.xCodes32) a.xCodes32[at] = q;
+                if (a.xMask) a.xMask[at] = keep;
+            }
+            a.xCodes[i] = static_cast<int8_t>(q);
+        }
+        return;
+    }
     const int cl = threadIdx.x & 31, layer = threadIdx.x >> 5, c = blockIdx.x * 32 + cl;
     const bool live = c < a.C;
     auto pass = [&](const float *__restrict__ src, int rowsK, int words, float scale, int32_t lo, int32_t hi,
@@ -873,6 +900,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     // 1. codes (8-bit weights: together with the per-channel terms of step 2)
     constexpr bool kPackedWeights = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value;
     const bool fusedPrep = kPackedWeights && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr;
+    bool fusedInput = false;
     if (fusedPrep) {
         WeightPrepArgs p{};
         p.W = call.W; p.R = call.R; p.bw = call.bw; p.br = call.br;
@@ -887,9 +915,20 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
         p.zpX = g.zp[RXMET_GRU_X]; p.zpH = g.zp[RXMET_GRU_H];
         p.biasRescaleX = ch.biasX; p.biasRescaleH = ch.biasH;
         p.compX = compX; p.biasX = biasX; p.compH = compH; p.biasH = biasH;
+        p.prepBlocks = (C + 31) / 32;
+        int xBlocks = 0;
+        if constexpr (kPackedWeights) {
+            if (!call.x_codes_in) {  // the input tensor rides in the same launch
+                p.xSrc = call.x; p.xRows = static_cast<int>(rows); p.xCols = I; p.xColsPadded = iPad;
+                p.xScale = g.eff[RXMET_GRU_X]; p.xLo = g.qlo[RXMET_GRU_X]; p.xHi = g.qhi[RXMET_GRU_X];
+                p.xCodes = reinterpret_cast<int8_t *>(xCodes); p.xCodes32 = call.x_q; p.xMask = mk.x;
+                xBlocks = static_cast<int>(std::min<size_t>((rows * iPad + 32 * kPrepLayers - 1) / (32 * kPrepLayers), 4 * 148));
+                fusedInput = true;
+            }
+        }
         {
             KernelTimer timer__("prepareWeights", st);
-            prepareWeightsI8<<<(C + 31) / 32, 32 * kPrepLayers, 0, st>>>(p);
+            prepareWeightsI8<<<p.prepBlocks + xBlocks, 32 * kPrepLayers, 0, st>>>(p);
         }
         afterLaunch("prepareWeights");
     } else {
@@ -908,7 +947,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
             narrowCodes<AT><<<gridFor(rows * iPad, 256), 256, 0, st>>>(call.x_codes_in, static_cast<int>(rows), I, iPad, xCodes);
         }
         afterLaunch("narrowCodes");
-    } else {
+    } else if (!fusedInput) {
         launchQuantize<AT>(st, call.x, static_cast<int>(rows), I, static_cast<int>(rows), iPad, nullptr,
                            g.eff[RXMET_GRU_X], g.zp[RXMET_GRU_X], g.qlo[RXMET_GRU_X], g.qhi[RXMET_GRU_X], 1, xCodes,
                            call.x_q, mk.x);
