@@ -1000,8 +1000,12 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
 
     if (registerPath) {
         const int CW = H <= 32 ? 16 : (H <= 64 ? 32 : 64);
-        uint32_t *RB = ws.take<uint32_t>(3 * static_cast<size_t>(CW) * H);
-        {
+        // The tensor-core kernel takes its fragments from the integer codes themselves; only the
+        // register kernel reads the packed pairs.
+        const bool mmaPath = H % 32 == 0 && std::getenv("RXMET_GRU_BWD_SIMT") == nullptr;
+        uint32_t *RB = nullptr;
+        if (!mmaPath) {
+            RB = ws.take<uint32_t>(3 * static_cast<size_t>(CW) * H);
             KernelTimer timer__("packRecurrentBf16", st);
             packRecurrentBf16<<<gridFor(3 * static_cast<size_t>(CW) * H, 256), 256, 0, st>>>(call.R_q, H, CW, RB);
         }
@@ -1030,7 +1034,6 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
         const size_t smem = sizeof(float) * (static_cast<size_t>(bt) * 3 * 2 * CW + 3 * static_cast<size_t>(bt) * H);
         const int grid = (B + bt - 1) / bt;
-        const bool mmaPath = H % 32 == 0 && std::getenv("RXMET_GRU_BWD_SIMT") == nullptr;
         if (mmaPath) {
             KernelTimer timer__("recurrentBackward", st);
 #define RXMET_BWD_CASE(HTV, BTV) \
