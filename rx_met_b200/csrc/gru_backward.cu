@@ -980,19 +980,19 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         if (!tensorInputGrad) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(I) * C, 256), 256, 0, st>>>(call.W_q, static_cast<size_t>(I) * C, C, chan, 0.f, 0, Wf);
+            afterLaunch("dequantCodes");
         }
-        afterLaunch("dequantCodes");
         if (!registerPath) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(H) * C, 256), 256, 0, st>>>(call.R_q, static_cast<size_t>(H) * C, C, chan + C, 0.f, 0, Rf);
+            afterLaunch("dequantCodes");
         }
-        afterLaunch("dequantCodes");
         if (!tensorGrads) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(rows * I, 256), 256, 0, st>>>(call.x_q, rows * I, I, nullptr, e.gate.eff[RXMET_GRU_X],
                                                                 e.gate.zp[RXMET_GRU_X], xf);
+            afterLaunch("dequantCodes");
         }
-        afterLaunch("dequantCodes");
         W = Wf; R = Rf; x = xf;
         chanScaleR = chan + C;
         chanScaleW = chan;
@@ -1008,8 +1008,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             RB = ws.take<uint32_t>(3 * static_cast<size_t>(CW) * H);
             KernelTimer timer__("packRecurrentBf16", st);
             packRecurrentBf16<<<gridFor(3 * static_cast<size_t>(CW) * H, 256), 256, 0, st>>>(call.R_q, H, CW, RB);
+            afterLaunch("packRecurrentBf16");
         }
-        afterLaunch("packRecurrentBf16");
         BackwardQArgs q{};
         if (mk.weight_ih_linear || mk.weight_hh_linear || mk.gate_input || mk.gate_output || mk.h) {
             uint16_t *bits = ws.take<uint16_t>(rows * H);
@@ -1099,8 +1099,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         KernelTimer timer__("gemmNT", st);
         gemmNT<<<dim3(static_cast<unsigned>((rows + kTile - 1) / kTile), (I + kTile - 1) / kTile), 256, 0, st>>>(
             dp, W, static_cast<int>(rows), I, C, mk.x, call.dx);
+        afterLaunch("gemmNT");
     }
-    afterLaunch("gemmNT");
     // dW, dR, dbw, dbr
     if (tensorGrads) {
         const Exec &e = *call.exec;

@@ -970,8 +970,8 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
             KernelTimer timer__("fillCodes", st);
             fillCodes<AT><<<gridFor(static_cast<size_t>(B) * hPad, 256), 256, 0, st>>>(h0Codes, static_cast<size_t>(B) * hPad,
                                                                                       g.zp[RXMET_GRU_H]);
+            afterLaunch("fillCodes");
         }
-        afterLaunch("fillCodes");
     }
 
     // 2. per-channel terms

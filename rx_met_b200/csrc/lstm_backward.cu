@@ -699,13 +699,13 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         if (!tensorInputGrad) {
             KernelTimer timer__("lstmDequantWeights", st);
             dequantWeights<<<gridFor(static_cast<size_t>(C) * I, 256), 256, 0, st>>>(call.weightIh, channelScales, C, I, wIhReal);
+            afterLaunch("lstmDequantWeights");
         }
-        afterLaunch("lstmDequantWeights");
         if (!tensorPath) {
             KernelTimer timer__("lstmDequantWeights", st);
             dequantWeights<<<gridFor(static_cast<size_t>(C) * H, 256), 256, 0, st>>>(call.weightHh, channelScales + C, C, H, wHhReal);
+            afterLaunch("lstmDequantWeights");
         }
-        afterLaunch("lstmDequantWeights");
         wIh = wIhReal;
         wHh = wHhReal;
     }
