@@ -371,6 +371,7 @@ def run_ours(args):
         secondary = None
         if world == 1:
             secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak),
+                         "affine_qdq": affine_qdq_bandwidth(torch, device, peak),
                          "lstm_w8a8": lstm_secondary(lib, torch, device, flush)}
             v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
             cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
@@ -428,6 +429,44 @@ def aimet_kernel_bandwidth(lib, torch, device, peak_gbs, elements=1 << 28, reps=
         gbs = bytes_per * n * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
         out[name] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peak_gbs, "bytes_per_element": bytes_per}
     out["elements"] = n
+    return out
+
+
+def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10):
+    """Learned-grid quantize-dequantize (aimet_torch.v2 affine quantizers) on float32 tensors larger than L2:
+    GB/s of algorithmic traffic from CUDA events: forward 8 B/element (read x, write y), backward 12 B/element
+    (read x and the incoming gradient, write dx; the scale and offset sums ride along)."""
+    from rx_met_b200 import affine_qdq
+    shapes = {"per_tensor_256M": ((1 << 28,), ()), "rows_8192x16384": ((8192, 16384), (8192, 1)),
+              "columns_131072x1024": ((131072, 1024), (1024,))}
+    out = {}
+    for name, (shape, grid_shape) in shapes.items():
+        x = torch.randn(shape, device=device)
+        g = torch.randn(shape, device=device)
+        scale = torch.full(grid_shape, 0.02, device=device)
+        offset = torch.zeros(grid_shape, device=device)
+        n = x.numel()
+        calls = {
+            "forward": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=False)),
+            "forward_fast": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=True)),
+            "backward": (12, lambda: affine_qdq.backward(g, x, scale, offset, -128, 127, reciprocal=False,
+                                                         want_scale_grad=True, want_offset_grad=True)),
+        }
+        entry = {}
+        for kind, (bytes_per, fn) in calls.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            gbs = bytes_per * n * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            entry[kind] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peak_gbs, "bytes_per_element": bytes_per}
+        out[name] = entry
+        del x, g
     return out
 
 

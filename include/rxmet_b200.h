@@ -557,6 +557,30 @@ RXMET_API int rxmet_gru_forward_fp_static(int T, int B, int I, int H,
                                           const float *x_dev, const float *h0_dev,
                                           float *h_dev, float *v_dev, void *stream);
 
+/* ---- affine quantizers with a learned grid (aimet_torch.v2) ---------------------------------
+ * Fused quantize-dequantize and its backward, replacing the eager tensor expressions of
+ * src/aimet_torch/v2/quantization/affine/backends/torch_builtins.py (quantize_dequantize :199-285,
+ * QuantDequantFunc.forward :640-669 and .backward :675-691, and the torch.fake_quantize fast path
+ * :288-360 taken when the grid is not trained).
+ *
+ * The tensor is [outer][channels][inner], contiguous; scale_dev / offset_dev hold one float per
+ * channel (channels == 1: per tensor).  reciprocal == 0 is the divide form (rne(x / s) - o), the one
+ * the reference differentiates with respect to scale and offset; reciprocal == 1 is the fast path
+ * (rne(x * (1 / s)) + zp on integers, NaN kept).  y, keep and dx are bit-exact; dscale / doffset are
+ * float sums (fixed order, run-to-run reproducible).  Infinite inputs saturate to the nearer end of the
+ * grid in both forms.  |qmin|, |qmax| < 2^24. */
+RXMET_API int rxmet_affine_qdq_forward(const float *x_dev, uint64_t outer, uint64_t channels, uint64_t inner,
+                                       const float *scale_dev, const float *offset_dev, int qmin, int qmax,
+                                       int reciprocal, float *y_dev,
+                                       uint8_t *keep_dev /* optional: 1 where inside the grid */, void *stream);
+RXMET_API size_t rxmet_affine_qdq_backward_workspace_bytes(uint64_t outer, uint64_t channels, uint64_t inner);
+/* Any of dx_dev, dscale_dev [channels], doffset_dev [channels] may be null; the grid gradients exist in
+ * the divide form only and need the workspace. */
+RXMET_API int rxmet_affine_qdq_backward(const float *grad_dev, const float *x_dev, uint64_t outer, uint64_t channels,
+                                        uint64_t inner, const float *scale_dev, const float *offset_dev, int qmin,
+                                        int qmax, int reciprocal, float *dx_dev, float *dscale_dev, float *doffset_dev,
+                                        void *workspace_dev, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
