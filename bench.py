@@ -199,6 +199,12 @@ def run_ours(args):
         out = aimet_kernel_bandwidth(lib, torch, device, _peaks()[0], elements=1 << 26, reps=2)
         print(json.dumps({"profile_only": True, "workload": "aimet", "result": out}), flush=True)
         return
+    if args.profile_only and args.workload == "affine":
+        # the learned-grid quantize-dequantize on 256 MiB tensors (larger than L2) for captures under a profiler
+        out = affine_qdq_bandwidth(torch, device, _peaks()[0], reps=max(args.steps, 1) if args.affine_log2 > 26 else 2,
+                                   elements=1 << args.affine_log2)
+        print(json.dumps({"profile_only": True, "workload": "affine", "result": out}), flush=True)
+        return
     if args.profile_only and args.workload == "lstm":
         # small LSTM training loop for captures under a profiler; prints no bench line
         lstm_secondary(lib, torch, device, torch.empty(1, dtype=torch.uint8, device=device), profile_steps=args.steps,
@@ -250,14 +256,22 @@ def run_ours(args):
         return float(t.item())
 
     # --- device-resident leg
+    replays = None
+    if args.graph == "on":
+        # one captured graph per resident input set: a replay is one launch for the whole step
+        replays = [eng.capture_step(xs[k], ys[k], lr)[0] for k in range(n_sets)]
+
     def resident(i):
-        eng.step(xs[i % n_sets], ys[i % n_sets], lr)
+        if replays is not None:
+            replays[i % n_sets]()
+        else:
+            eng.step(xs[i % n_sets], ys[i % n_sets], lr)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     total_ms = timed(resident, args.steps, args.warmup)
-    launches = timed.launches
+    launches = timed.launches if replays is None else args.steps * eng.captured_launches
     resident_host_ms = timed.host_ms
     clocks = sampler.stop() if rank == 0 else None
     st_per_step = T * B * world
@@ -274,7 +288,7 @@ def run_ours(args):
     lib.rxmet_reset_kernel_timing()
     lib.rxmet_set_kernel_timing(1)
     k_steps = min(args.steps, 10)
-    timed(resident, k_steps, 1)
+    timed(lambda i: eng.step(xs[i % n_sets], ys[i % n_sets], lr), k_steps, 1)   # eager: events sit between launches
     names = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "inputGradUmma", "packRecurrentBf16", "weightGradMma", "weightGradUmma", "reduceWeightGrad", "fillCodes", "packStepMasks",
              "reduceSplits", "columnSums", "channelPrep", "prepareWeights", "dequantCodes", "transposeMatrix"]
     per_kernel = {}
@@ -382,7 +396,8 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": "gru_qat_step", **WORKLOAD, "global_batch": B * world, "parallelism": f"dp{world}",
                        "quant": "W8 symmetric per-channel, A8 asymmetric, integer carrier", "l2": "flushed between steps",
-                       "kernel_timing": "second pass of the same step with CUDA events around every kernel"},
+                       "kernel_timing": "second pass of the same step with CUDA events around every kernel",
+                       "launch": "cuda graph replay" if args.graph == "on" else "eager launches"},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
@@ -432,13 +447,13 @@ def aimet_kernel_bandwidth(lib, torch, device, peak_gbs, elements=1 << 28, reps=
     return out
 
 
-def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10):
+def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10, elements=1 << 28):
     """Learned-grid quantize-dequantize (aimet_torch.v2 affine quantizers) on float32 tensors larger than L2:
     GB/s of algorithmic traffic from CUDA events: forward 8 B/element (read x, write y), backward 12 B/element
     (read x and the incoming gradient, write dx; the scale and offset sums ride along)."""
     from rx_met_b200 import affine_qdq
-    shapes = {"per_tensor_256M": ((1 << 28,), ()), "rows_8192x16384": ((8192, 16384), (8192, 1)),
-              "columns_131072x1024": ((131072, 1024), (1024,))}
+    shapes = {"per_tensor": ((elements,), ()), "rows_of_16384": ((elements >> 14, 16384), (elements >> 14, 1)),
+              "columns_1024": ((elements >> 10, 1024), (1024,))}
     out = {}
     for name, (shape, grid_shape) in shapes.items():
         x = torch.randn(shape, device=device)
@@ -573,12 +588,16 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["gru", "lstm", "aimet"], default="gru",
+    ap.add_argument("--workload", choices=["gru", "lstm", "aimet", "affine"], default="gru",
                     help="with --profile-only: which training loop to run (the bench line is always the GRU QAT step)")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
     ap.add_argument("--e2e-copy", choices=["kernel", "dma"], default="kernel",
                     help="how the end-to-end leg moves a step's inputs from pinned host memory: the library's staging "
                          "kernel (rxmet_stage_from_pinned_host) or copy-engine transfers")
+    ap.add_argument("--affine-log2", type=int, default=26,
+                    help="log2 of the element count of the --profile-only affine tensors (26: a small case for captures)")
+    ap.add_argument("--graph", choices=["on", "off"], default="off",
+                    help="device-resident leg: replay the step as one captured CUDA graph per input set")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only the device-resident leg (for captures under a profiler); prints no bench line")
     args = ap.parse_args()

@@ -22,6 +22,8 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.h"
 #include "rxmet_b200.h"
@@ -31,8 +33,12 @@ namespace affine {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxResident = 2048 / kThreads;   // CTAs of kThreads threads an SM can hold
 constexpr int kSegment = 8192;     // elements of one row handled by one CTA pass (long rows)
 constexpr int kChunkRows = 32;     // rows of one CTA tile (short rows)
+constexpr int kBatchForward = 4;   // rows whose loads are in flight together (short rows)
+constexpr int kBatchBackward = 2;  // two tensors are read there
 constexpr int kLongRow = 256;      // rows at least this long take the row kernel
 
 struct Grid {
@@ -48,15 +54,17 @@ struct Element {
 };
 
 template <bool kReciprocal>
-__device__ __forceinline__ Element quantDequant(float x, float s, float inv, float o, int zp, const Grid &g) {
+__device__ __forceinline__ Element quantDequant(float x, float s, float inv, float o, float zp, const Grid &g) {
     Element e;
     if constexpr (kReciprocal) {
-        const float r = __fadd_rn(nearbyintf(__fmul_rn(x, inv)), static_cast<float>(zp));
-        const long long q = static_cast<long long>(r);   // saturates; NaN gives 0
+        // The reference converts r to int64 (saturating), clamps and subtracts zp as integers.  r is an integer
+        // or infinite, qmin / qmax / zp are exact floats, and both float(int64 difference) and the float
+        // subtraction round the same exact integer, so the float domain gives the same bits without 64-bit work.
+        const float r = __fadd_rn(nearbyintf(__fmul_rn(x, inv)), zp);
         const bool nan = x != x;
-        const bool keep = !nan && q >= g.qmin && q <= g.qmax;
-        const long long c = q < g.qmin ? g.qmin : (q > g.qmax ? g.qmax : q);
-        e.y = nan ? x : __fmul_rn(static_cast<float>(c - zp), s);
+        const bool keep = g.lo <= r && r <= g.hi;    // false for NaN
+        const float c = fminf(fmaxf(r, g.lo), g.hi);
+        e.y = nan ? x : __fmul_rn(__fsub_rn(c, zp), s);
         e.keep = keep ? 1.0f : 0.0f;
     } else {
         const float t = __fsub_rn(nearbyintf(__fdiv_rn(x, s)), o);
@@ -86,21 +94,16 @@ __device__ __forceinline__ float backwardOne(float x, float gr, float s, float o
     return __fmul_rn(gr, m);
 }
 
-__device__ __forceinline__ Sums blockSum(Sums v) {
-    __shared__ float part[2][kThreads / 32];
+// One partial per warp: no CTA-wide barrier between work items.
+__device__ __forceinline__ void writeWarpPartial(Sums acc, float *partial, uint64_t at) {
     for (int d = 16; d > 0; d >>= 1) {
-        v.scale += __shfl_down_sync(0xffffffffu, v.scale, d);
-        v.offset += __shfl_down_sync(0xffffffffu, v.offset, d);
+        acc.scale += __shfl_down_sync(0xffffffffu, acc.scale, d);
+        acc.offset += __shfl_down_sync(0xffffffffu, acc.offset, d);
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __syncthreads();   // the buffer may still be read from the previous call
-    if (lane == 0) { part[0][warp] = v.scale; part[1][warp] = v.offset; }
-    __syncthreads();
-    Sums out;
-    if (threadIdx.x == 0) {
-        for (int w = 0; w < kThreads / 32; ++w) { out.scale += part[0][w]; out.offset += part[1][w]; }
+    if ((threadIdx.x & 31) == 0) {
+        partial[2 * at] = acc.scale;
+        partial[2 * at + 1] = acc.offset;
     }
-    return out;
 }
 
 struct Pass {
@@ -117,19 +120,27 @@ struct Pass {
 template <bool kBackward, bool kReciprocal>
 __global__ void __launch_bounds__(kThreads) rowPass(Pass p, Grid g, uint64_t segments, int vector) {
     const uint64_t rows = p.outer * p.channels;
+    // A per-tensor grid has one channel, so a warp keeps its sums across all its work items and writes one
+    // partial at the end; otherwise every work item writes its own.
+    const bool perTensor = rows == 1;
+    Sums acc;
     for (uint64_t item = blockIdx.x; item < rows * segments; item += gridDim.x) {
         const uint64_t row = item / segments, seg = item - row * segments;
         const uint64_t c = row % p.channels;
         const float s = __ldg(g.scale + c), o = __ldg(g.offset + c);
         const float inv = __fdiv_rn(1.0f, s);
-        const int zp = -static_cast<int>(o);
+        const float zp = static_cast<float>(-static_cast<int>(o));   // zero point of the fast form: -int32(o)
         const uint64_t begin = row * p.inner + seg * kSegment;
         const int count = static_cast<int>(min(static_cast<uint64_t>(kSegment), p.inner - seg * kSegment));
-        Sums acc;
+        if (!perTensor) acc = Sums();
         if (vector) {
-            const float4 *x4 = reinterpret_cast<const float4 *>(p.x + begin);
-            const float4 *g4 = kBackward ? reinterpret_cast<const float4 *>(p.grad + begin) : nullptr;
-            float4 *o4 = p.out ? reinterpret_cast<float4 *>(p.out + begin) : nullptr;
+            // restrict: the loads of the next iterations may move above this iteration's store, so several
+            // 16-byte requests per thread are in flight
+            const float4 *__restrict__ x4 = reinterpret_cast<const float4 *>(p.x + begin);
+            const float4 *__restrict__ g4 = kBackward ? reinterpret_cast<const float4 *>(p.grad + begin) : nullptr;
+            float4 *__restrict__ o4 = p.out ? reinterpret_cast<float4 *>(p.out + begin) : nullptr;
+            uint32_t *__restrict__ k4 = p.keep ? reinterpret_cast<uint32_t *>(p.keep + begin) : nullptr;
+#pragma unroll(kBackward ? 2 : 1)
             for (int v = threadIdx.x; v < count / 4; v += kThreads) {
                 const float4 xv = __ldcs(x4 + v);
                 float in[4] = {xv.x, xv.y, xv.z, xv.w}, res[4];
@@ -149,7 +160,7 @@ __global__ void __launch_bounds__(kThreads) rowPass(Pass p, Grid g, uint64_t seg
                         res[k] = e.y;
                         bits |= (e.keep != 0.0f ? 1u : 0u) << (8 * k);
                     }
-                    if (p.keep) reinterpret_cast<uint32_t *>(p.keep + begin)[v] = bits;
+                    if (k4) k4[v] = bits;
                 }
                 if (o4) __stcs(o4 + v, make_float4(res[0], res[1], res[2], res[3]));
             }
@@ -170,48 +181,99 @@ __global__ void __launch_bounds__(kThreads) rowPass(Pass p, Grid g, uint64_t seg
             }
         }
         if constexpr (kBackward) {
-            if (p.wantSums) {
-                const Sums total = blockSum(acc);
-                if (threadIdx.x == 0) { p.partial[2 * item] = total.scale; p.partial[2 * item + 1] = total.offset; }
-            }
+            if (p.wantSums && !perTensor) writeWarpPartial(acc, p.partial, item * kWarps + (threadIdx.x >> 5));
         }
+    }
+    if constexpr (kBackward) {
+        if (p.wantSums && perTensor)
+            writeWarpPartial(acc, p.partial, static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5));
     }
 }
 
-// Short rows: the tensor is a matrix [outer][channels * inner]; a thread owns one column (one channel) and
-// walks down kChunkRows rows, so a warp reads 128 contiguous bytes per row and nothing is reduced across threads.
-template <bool kBackward, bool kReciprocal>
-__global__ void __launch_bounds__(kThreads) columnPass(Pass p, Grid g) {
+// Short rows: the tensor is a matrix [outer][channels * inner].  A thread owns kVec adjacent columns (their
+// channels, scales and sums stay in registers) and walks down kChunkRows rows, so a warp reads 128 * kVec
+// contiguous bytes per row and nothing is reduced across threads.  Narrow matrices fold several row chunks
+// into one CTA: colThreads threads across, 256 / colThreads chunks down.
+template <bool kBackward, bool kReciprocal, int kVec>
+__global__ void __launch_bounds__(kThreads) columnPass(Pass p, Grid g, int colThreads) {
     const uint64_t period = p.channels * p.inner;
-    const uint64_t col = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int tx = threadIdx.x % colThreads, ty = threadIdx.x / colThreads, down = kThreads / colThreads;
+    const uint64_t col = (static_cast<uint64_t>(blockIdx.x) * colThreads + tx) * kVec;
     if (col >= period) return;
-    const uint64_t c = col / p.inner;
-    const float s = __ldg(g.scale + c), o = __ldg(g.offset + c);
-    const float inv = __fdiv_rn(1.0f, s);
-    const int zp = -static_cast<int>(o);
-    for (uint64_t chunk = blockIdx.y; chunk * kChunkRows < p.outer; chunk += gridDim.y) {
+    float s[kVec], o[kVec], inv[kVec], zp[kVec];
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) {
+        const uint64_t c = (col + k) / p.inner;
+        s[k] = __ldg(g.scale + c);
+        o[k] = __ldg(g.offset + c);
+        inv[k] = __fdiv_rn(1.0f, s[k]);
+        zp[k] = static_cast<float>(-static_cast<int>(o[k]));
+    }
+    constexpr int kBatch = kBackward ? kBatchBackward : kBatchForward;
+    const float *__restrict__ xIn = p.x;
+    const float *__restrict__ gIn = p.grad;
+    float *__restrict__ out = p.out;
+    uint8_t *__restrict__ keepOut = p.keep;
+    const uint64_t chunks = (p.outer + kChunkRows - 1) / kChunkRows;
+    for (uint64_t chunk = static_cast<uint64_t>(blockIdx.y) * down + ty; chunk < chunks;
+         chunk += static_cast<uint64_t>(gridDim.y) * down) {
         const uint64_t first = chunk * kChunkRows, last = min(first + kChunkRows, p.outer);
-        Sums acc;
-#pragma unroll 4
-        for (uint64_t r = first; r < last; ++r) {
-            const uint64_t at = r * period + col;
-            const float xv = __ldcs(p.x + at);
-            float res;
-            if constexpr (kBackward) {
-                const float gr = __ldcs(p.grad + at);
-                if (kReciprocal) res = __fmul_rn(gr, quantDequant<true>(xv, s, inv, o, zp, g).keep);
-                else res = backwardOne(xv, gr, s, o, g, acc);
-            } else {
-                const Element e = quantDequant<kReciprocal>(xv, s, inv, o, zp, g);
-                res = e.y;
-                if (p.keep) p.keep[at] = e.keep != 0.0f;
+        Sums acc[kVec];
+        for (uint64_t r0 = first; r0 < last; r0 += kBatch) {
+            // all loads of a batch of rows are issued before the first result is needed
+            float in[kBatch][kVec], gr[kBatch][kVec];
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                if (r0 + b >= last) break;
+                const uint64_t at = (r0 + b) * period + col;
+                if constexpr (kVec == 4) {
+                    const float4 xv = __ldcs(reinterpret_cast<const float4 *>(xIn + at));
+                    in[b][0] = xv.x; in[b][1] = xv.y; in[b][2] = xv.z; in[b][3] = xv.w;
+                    if constexpr (kBackward) {
+                        const float4 gv = __ldcs(reinterpret_cast<const float4 *>(gIn + at));
+                        gr[b][0] = gv.x; gr[b][1] = gv.y; gr[b][2] = gv.z; gr[b][3] = gv.w;
+                    }
+                } else {
+                    in[b][0] = __ldcs(xIn + at);
+                    if constexpr (kBackward) gr[b][0] = __ldcs(gIn + at);
+                }
             }
-            if (p.out) __stcs(p.out + at, res);
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                if (r0 + b >= last) break;
+                const uint64_t at = (r0 + b) * period + col;
+                float res[kVec];
+                uint32_t bits = 0;
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) {
+                    if constexpr (kBackward) {
+                        if (kReciprocal) res[k] = __fmul_rn(gr[b][k], quantDequant<true>(in[b][k], s[k], inv[k], o[k], zp[k], g).keep);
+                        else res[k] = backwardOne(in[b][k], gr[b][k], s[k], o[k], g, acc[k]);
+                    } else {
+                        const Element e = quantDequant<kReciprocal>(in[b][k], s[k], inv[k], o[k], zp[k], g);
+                        res[k] = e.y;
+                        bits |= (e.keep != 0.0f ? 1u : 0u) << (8 * k);
+                    }
+                }
+                if constexpr (!kBackward) {
+                    if (keepOut) {
+                        if constexpr (kVec == 4) *reinterpret_cast<uint32_t *>(keepOut + at) = bits;
+                        else keepOut[at] = static_cast<uint8_t>(bits);
+                    }
+                }
+                if (out) {
+                    if constexpr (kVec == 4) __stcs(reinterpret_cast<float4 *>(out + at), make_float4(res[0], res[1], res[2], res[3]));
+                    else __stcs(out + at, res[0]);
+                }
+            }
         }
         if constexpr (kBackward) {
             if (p.wantSums) {
-                p.partial[2 * (chunk * period + col)] = acc.scale;
-                p.partial[2 * (chunk * period + col) + 1] = acc.offset;
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) {
+                    p.partial[2 * (chunk * period + col + k)] = acc[k].scale;
+                    p.partial[2 * (chunk * period + col + k) + 1] = acc[k].offset;
+                }
             }
         }
     }
@@ -254,7 +316,9 @@ Plan planFor(uint64_t outer, uint64_t channels, uint64_t inner) {
     plan.rows = channels == 1 || inner >= kLongRow;
     if (plan.rows) {
         plan.segments = (inner + kSegment - 1) / kSegment;
-        plan.items = outer * channels * plan.segments;
+        // one partial per warp and segment; per tensor one per warp of the grid (at most kMaxResident CTAs per SM)
+        plan.items = outer * channels == 1 ? static_cast<uint64_t>(currentDevice().sms) * kMaxResident * kWarps
+                                           : outer * channels * plan.segments * kWarps;
     } else {
         plan.chunks = (outer + kChunkRows - 1) / kChunkRows;
         plan.items = plan.chunks * channels * inner;
@@ -267,8 +331,24 @@ void checkGrid(int qmin, int qmax) {
     RXMET_REQUIRE(qmin > -(1 << 24) && qmax < (1 << 24), "affine qdq: the code range must be exact in float (|q| < 2^24)");
 }
 
+// CTAs of `kernel` one SM holds; asked once per kernel.
+template <class Kernel>
+int residentCtas(Kernel kernel) {
+    static std::mutex lock;
+    static std::unordered_map<const void *, int> known;
+    std::lock_guard<std::mutex> hold(lock);
+    int &n = known[reinterpret_cast<const void *>(kernel)];
+    if (n == 0) {
+        RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0));
+        n = std::max(n, 1);
+    }
+    return n;
+}
+
+// Returns the number of CTAs of the row pass (0 for the column pass).
 template <bool kBackward>
-void run(Pass p, Grid g, int reciprocal, const Plan &plan, cudaStream_t st) {
+int run(Pass p, Grid g, int reciprocal, const Plan &plan, cudaStream_t st) {
+    int rowGrid = 0;
     const DeviceInfo dev = currentDevice();
     if (plan.rows) {
         // per tensor the whole tensor is one row: `outer` and `channels` fold into it on the host
@@ -277,19 +357,43 @@ void run(Pass p, Grid g, int reciprocal, const Plan &plan, cudaStream_t st) {
                              (!p.out || (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                              (!p.keep || (reinterpret_cast<uintptr_t>(p.keep) & 3) == 0);
         const uint64_t items = p.outer * p.channels * plan.segments;
-        const int grid = static_cast<int>(std::min<uint64_t>(items, static_cast<uint64_t>(dev.sms) * 8));
-        if (reciprocal) rowPass<kBackward, true><<<grid, kThreads, 0, st>>>(p, g, plan.segments, aligned ? 1 : 0);
-        else rowPass<kBackward, false><<<grid, kThreads, 0, st>>>(p, g, plan.segments, aligned ? 1 : 0);
+        auto launch = [&](auto kernel) {
+            // exactly one wave of resident CTAs, so that every CTA walks the same number of work items
+            const int grid = static_cast<int>(std::min<uint64_t>(
+                items, static_cast<uint64_t>(dev.sms) * std::min(residentCtas(kernel), kMaxResident)));
+            kernel<<<grid, kThreads, 0, st>>>(p, g, plan.segments, aligned ? 1 : 0);
+            rowGrid = grid;
+        };
+        if (reciprocal) launch(rowPass<kBackward, true>);
+        else launch(rowPass<kBackward, false>);
         afterLaunch("affineRowPass");
     } else {
         const uint64_t period = p.channels * p.inner;
-        const unsigned gx = static_cast<unsigned>((period + kThreads - 1) / kThreads);
-        const uint64_t want = std::max<uint64_t>(1, static_cast<uint64_t>(dev.sms) * 8 / gx);
-        const unsigned gy = static_cast<unsigned>(std::min<uint64_t>(std::min<uint64_t>(plan.chunks, want), 65535));
-        if (reciprocal) columnPass<kBackward, true><<<dim3(gx, gy), kThreads, 0, st>>>(p, g);
-        else columnPass<kBackward, false><<<dim3(gx, gy), kThreads, 0, st>>>(p, g);
+        const bool vec4 = period % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
+                          (!p.grad || (reinterpret_cast<uintptr_t>(p.grad) & 15) == 0) &&
+                          (!p.out || (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                          (!p.keep || (reinterpret_cast<uintptr_t>(p.keep) & 3) == 0);
+        const uint64_t lanes = vec4 ? period / 4 : period;             // threads one row needs
+        int colThreads = 32;
+        while (colThreads < kThreads && static_cast<uint64_t>(colThreads) < lanes) colThreads *= 2;
+        const int down = kThreads / colThreads;                        // row chunks per CTA
+        const unsigned gx = static_cast<unsigned>((lanes + colThreads - 1) / colThreads);
+        const uint64_t blocksDown = (plan.chunks + down - 1) / down;
+        auto launch = [&](auto kernel) {
+            const uint64_t want = std::max<uint64_t>(1, static_cast<uint64_t>(dev.sms) * residentCtas(kernel) / gx);
+            const unsigned gy = static_cast<unsigned>(std::min<uint64_t>(std::min<uint64_t>(blocksDown, want), 65535));
+            kernel<<<dim3(gx, gy), kThreads, 0, st>>>(p, g, colThreads);
+        };
+        if (vec4) {
+            if (reciprocal) launch(columnPass<kBackward, true, 4>);
+            else launch(columnPass<kBackward, false, 4>);
+        } else {
+            if (reciprocal) launch(columnPass<kBackward, true, 1>);
+            else launch(columnPass<kBackward, false, 1>);
+        }
         afterLaunch("affineColumnPass");
     }
+    return rowGrid;
 }
 
 }  // namespace
@@ -346,11 +450,13 @@ int rxmet_affine_qdq_backward(const float *grad_dev, const float *x_dev, uint64_
         }
         const Grid g{scale_dev, offset_dev, static_cast<float>(qmin), static_cast<float>(qmax), qmin, qmax};
         cudaStream_t st = static_cast<cudaStream_t>(stream);
-        run<true>(p, g, reciprocal, plan, st);
+        const int rowGrid = run<true>(p, g, reciprocal, plan, st);
         if (sums) {
-            if (plan.rows)
-                finishSums<<<static_cast<unsigned>(p.channels), 128, 0, st>>>(p.partial, p.outer, p.channels * plan.segments,
-                                                                              plan.segments, dscale_dev, doffset_dev);
+            if (plan.rows && p.outer * p.channels == 1)
+                finishSums<<<1, 128, 0, st>>>(p.partial, 1, 0, static_cast<uint64_t>(rowGrid) * kWarps, dscale_dev, doffset_dev);
+            else if (plan.rows)
+                finishSums<<<static_cast<unsigned>(p.channels), 128, 0, st>>>(p.partial, p.outer, p.channels * plan.segments * kWarps,
+                                                                              plan.segments * kWarps, dscale_dev, doffset_dev);
             else
                 finishSums<<<static_cast<unsigned>(p.channels), 128, 0, st>>>(p.partial, plan.chunks, p.channels * p.inner,
                                                                               p.inner, dscale_dev, doffset_dev);

@@ -135,3 +135,50 @@ class GruQatStep:
             self.flat_g.div_(self.world)
         self.flat_w.add_(self.flat_g, alpha=-lr)
         return loss
+
+    # ---- the same step as one graph launch ----------------------------------
+    def capture_step(self, x: torch.Tensor, target: torch.Tensor, lr: float, warmup: int = 3):
+        """Captures `step` on fixed buffers into a CUDA graph and returns `(replay, loss)`: `replay()` launches
+        the whole step (about ten kernels, two small copies, the loss and the update) as one graph on the
+        current stream; `loss` is the device scalar it refreshes.  `x` and `target` are read at replay time, so
+        the caller fills them in place (for example with `staging.stage_from_pinned_host`) before each replay.
+        With a process group only the local part is captured; the gradient all-reduce and the update follow
+        the graph launch.  The quantization parameters in force at capture are baked in: capture again after
+        `set_params`.  `warmup` eager steps run first (they do train), so that every lazy initialisation of the
+        library has happened before the capture begins."""
+        if self._c_params is None:
+            raise RuntimeError("calibrate or set_params before capturing a step")
+        local = self.group is None
+
+        def body():
+            out = self.forward(x)
+            diff = out - target
+            loss_ = diff.square().mean()
+            torch.mul(diff, 2.0 / diff.numel(), out=self.dh_new[1:])
+            self.backward()
+            if local:
+                self.flat_w.add_(self.flat_g, alpha=-lr)
+            return loss_
+
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 1)):
+                self.step(x, target, lr)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        before = self.lib.rxmet_kernel_launch_count()
+        with torch.cuda.graph(graph, stream=side):
+            loss = body()
+        self.captured_launches = int(self.lib.rxmet_kernel_launch_count() - before)  # library kernels per replay
+
+        def replay():
+            graph.replay()
+            if not local:
+                torch.distributed.all_reduce(self.flat_g, group=self.group)
+                self.flat_g.div_(self.world)
+                self.flat_w.add_(self.flat_g, alpha=-lr)
+            return loss
+
+        self._graph = graph   # keeps the captured buffers alive with the object
+        return replay, loss

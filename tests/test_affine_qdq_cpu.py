@@ -24,8 +24,12 @@ def case_arrays(name):
 
 
 def same_bits(a, b):
+    """Equal bit for bit (signed zeros included); a NaN matches a NaN of any payload."""
     a, b = np.asarray(a, dtype=np.float32), np.asarray(b, dtype=np.float32)
-    return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    if a.shape != b.shape or not np.array_equal(np.isnan(a), np.isnan(b)):
+        return False
+    real = ~np.isnan(a)
+    return np.array_equal(a.view(np.uint32)[real], b.view(np.uint32)[real])
 
 
 @pytest.mark.parametrize("name", CASES)

@@ -349,3 +349,35 @@ def test_bounded_device_wait_gives_up_with_a_status(gl):
     assert status.cpu().tolist()[0] == 1 and polls.value == 1 << 20
     # the context is still usable
     assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
+
+
+def test_captured_step_replays_the_eager_step():
+    """A CUDA-graph replay of the QAT step leaves the same weights and loss as the eager step."""
+    import torch
+    from rx_met_b200.qat import GruQatStep
+    T, B, I, H = 12, 16, 8, 32
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    xs = [torch.randn((T, B, I), generator=gen).to(dev) for _ in range(3)]
+    ys = [torch.randn((T, B, H), generator=gen).to(dev) for _ in range(3)]
+
+    def run(graph):
+        eng = GruQatStep(T, B, I, H, dev, seed=11)
+        eng.calibrate(xs[:2])
+        x, y = xs[0].clone(), ys[0].clone()
+        losses = []
+        if graph:
+            replay, loss = eng.capture_step(x, y, 1e-2, warmup=2)
+            assert eng.captured_launches >= 6
+        else:
+            for _ in range(2):
+                eng.step(x, y, 1e-2)
+        for k in range(3):
+            x.copy_(xs[k]); y.copy_(ys[k])
+            losses.append(float(replay() if graph else eng.step(x, y, 1e-2)))
+        return eng.flat_w.clone(), losses
+
+    w_eager, l_eager = run(False)
+    w_graph, l_graph = run(True)
+    assert l_eager == l_graph
+    assert torch.equal(w_eager, w_graph)
