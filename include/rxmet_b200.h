@@ -475,7 +475,9 @@ RXMET_API int rxmet_aimet_compute_encoding(int bw, double range_min, double rang
  * native/common/src/MinMaxEncodingAnalyzer.cpp:80-107): zero included, maximum
  * nudged to at least minimum + 0.01 (0.01 in the analyzer's element type: dtype 0
  * = float, 1 = double).  stats_min / stats_max are the running extremes that
- * rxmet_aimet_minmax accumulates. */
+ * rxmet_aimet_minmax accumulates.  With dtype 1 and statistics that start at 0 / 0 this is
+ * also TfEncodingAnalyzer::computeEncoding (native/common/src/TfEncodingAnalyzer.cpp:88-108),
+ * whose updateStats is a running min / max in double. */
 RXMET_API int rxmet_aimet_minmax_encoding(int bw, int dtype, double stats_min, double stats_max, int symmetric,
                                           int strict_symmetric, int unsigned_symmetric,
                                           rxmet_aimet_encoding *encoding);

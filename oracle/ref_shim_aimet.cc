@@ -15,6 +15,7 @@
 #include "trim_functions.hpp"
 #include "quantization_utils.hpp"
 #include "MinMaxEncodingAnalyzer.h"
+#include "TfEncodingAnalyzer.h"
 #include "PercentileEncodingAnalyzer.h"
 #include "TfEnhancedEncodingAnalyzer.h"
 
@@ -103,6 +104,18 @@ int ref_aimet_minmax_encoding(int bw, float statsMin, float statsMax, int symmet
         analyzer.updateStats(values, TensorDims{2}, COMP_MODE_CPU, nullptr, nullptr);
         const Encodings all = analyzer.computeEncoding(static_cast<uint8_t>(bw), symmetric != 0, strict != 0, unsignedSymmetric != 0);
         const TfEncoding &e = all[0];
+        out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
+        return 0;
+    } catch (...) { return -1; }
+}
+
+// TfEncodingAnalyzer<float> (running min / max that start at zero): the batches go through updateStats in CPU mode.
+int ref_aimet_tf_encoding(const float *data, const uint64_t *sizes, int batches, int bw, int symmetric, int strict,
+                          int unsignedSymmetric, double *out) {
+    try {
+        TfEncodingAnalyzer<float> analyzer;
+        for (int b = 0; b < batches; ++b) { analyzer.updateStats(data, sizes[b], COMP_MODE_CPU); data += sizes[b]; }
+        const TfEncoding e = analyzer.computeEncoding(static_cast<uint8_t>(bw), symmetric != 0, strict != 0, unsignedSymmetric != 0);
         out[0] = e.min; out[1] = e.max; out[2] = e.delta; out[3] = e.offset; out[4] = e.bw;
         return 0;
     } catch (...) { return -1; }

@@ -251,3 +251,26 @@ def test_histogram_analyzers_before_any_batch():
     assert lib.rxmet_aimet_tf_enhanced_encoding(C.byref(s), 8, 0, 0, 0, C.byref(e)) == 0
     assert (e.min, e.max, e.delta, e.offset, e.bw) == (0.0, 0.0, 0.0, 0.0, 0)  # the failure marker
     assert lib.rxmet_aimet_percentile_encoding(None, 8, 0, 0, 0, C.c_float(99.0), C.byref(e)) == -1
+
+
+@pytest.mark.skipif(ref() is None, reason="compiled reference not available")
+def test_plain_tf_analyzer_is_the_minmax_encoding_of_the_running_range():
+    """TfEncodingAnalyzer<float> keeps a running min / max in double that starts at zero; its encoding is the
+    library's min/max encoding of that range, so the analyzer binds to rxmet_aimet_minmax (per batch) and
+    rxmet_aimet_minmax_encoding (double statistics)."""
+    from rx_met_b200 import _cabi
+    lib, r = _cabi.load_library(), ref()
+    modes = [(0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)]
+    for name, batches in _histogram_cases().items():
+        data = np.concatenate(batches)
+        sizes = (C.c_uint64 * len(batches))(*[b.size for b in batches])
+        lo = min(0.0, min(float(b.min()) for b in batches))
+        hi = max(0.0, max(float(b.max()) for b in batches))
+        for bw in (4, 8, 16):
+            for sym, strict, uns in modes:
+                out = (C.c_double * 5)()
+                assert r.ref_aimet_tf_encoding(fp(data), sizes, len(batches), bw, sym, strict, uns, out) == 0
+                e = _Encoding()
+                assert lib.rxmet_aimet_minmax_encoding(bw, 1, C.c_double(lo), C.c_double(hi), sym, strict, uns, C.byref(e)) == 0
+                got = (e.min, e.max, e.delta, e.offset, float(e.bw))
+                assert all(a == b for a, b in zip(got, out)), (name, bw, sym, strict, uns, got, list(out))
