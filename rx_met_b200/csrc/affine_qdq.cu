@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) rowPass(Pass p, Grid g, uint64_t seg
 // contiguous bytes per row and nothing is reduced across threads.  Narrow matrices fold several row chunks
 // into one CTA: colThreads threads across, 256 / colThreads chunks down.
 template <bool kBackward, bool kReciprocal, int kVec>
-__global__ void __launch_bounds__(kThreads) columnPass(Pass p, Grid g, int colThreads) {
+__global__ void __launch_bounds__(kThreads, 4) columnPass(Pass p, Grid g, int colThreads) {
     const uint64_t period = p.channels * p.inner;
     const int tx = threadIdx.x % colThreads, ty = threadIdx.x / colThreads, down = kThreads / colThreads;
     const uint64_t col = (static_cast<uint64_t>(blockIdx.x) * colThreads + tx) * kVec;
