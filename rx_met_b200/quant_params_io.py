@@ -268,6 +268,38 @@ def operators_from_dict(operators: Dict[str, Dict[str, Any]], config, params) ->
 
 
 # ---------------------------------------------------------------------------------------------
+# grids at the module boundary (integer-in / integer-out chaining of stacked layers)
+# ---------------------------------------------------------------------------------------------
+
+def io_quant_meta(config, params, use_pot2_scale: Optional[bool] = None) -> Dict[str, Dict[str, Any]]:
+    """Grids of the input, the output sequence and the hidden state of a module, with the scale the integer
+    kernels really use (after the power-of-two or 16-bit multiplier encoding), so that codes handed from one
+    layer to the next mean the same on both sides (``QuantGRU.get_io_quant_meta``, quant_gru.py:2378-2425)."""
+    if params is None:
+        raise RuntimeError("QuantGRU not calibrated")
+    pot2 = bool(getattr(config, "usePOT2_", False)) if use_pot2_scale is None else bool(use_pot2_scale)
+
+    def entry(stem: str) -> Dict[str, Any]:
+        symmetric = bool(getattr(config, stem + "symmetric_"))
+        unsigned = bool(getattr(config, stem + "unsigned_", False))
+        return {
+            "scale": float(gru_ops.decode_effective_scale(float(getattr(params, "scale_" + stem)), pot2)),
+            "zp": int(getattr(params, "zp_" + stem)),
+            "bitwidth": int(getattr(config, stem)),
+            "is_symmetric": symmetric and not unsigned,
+            "is_unsigned": unsigned,
+        }
+
+    return {"input": entry("x_"), "output": entry("h_"), "hidden": entry("h_")}
+
+
+def grids_match(producer: Dict[str, Any], consumer: Dict[str, Any]) -> bool:
+    """True when codes on `producer`'s grid (a layer's "output") can be fed to `consumer`'s (the next layer's
+    "input") as they are: same effective scale, zero point, width and signedness."""
+    return all(producer[key] == consumer[key] for key in ("scale", "zp", "bitwidth", "is_unsigned"))
+
+
+# ---------------------------------------------------------------------------------------------
 # operator JSON
 # ---------------------------------------------------------------------------------------------
 

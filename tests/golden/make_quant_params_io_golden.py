@@ -93,6 +93,7 @@ def main(reference_root):
                 "config": config_attrs(cfg), "params": params_attrs(module.quant_params),
                 "params_reverse": params_attrs(module.quant_params_reverse) if bidirectional else None}
 
+        case["io_quant_meta"] = module.get_io_quant_meta()
         with tempfile.TemporaryDirectory() as folder:
             path = os.path.join(folder, "params.json")
             module.export_quant_params(path)

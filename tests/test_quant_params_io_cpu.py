@@ -197,3 +197,34 @@ def test_encoding_exponent_and_code_ranges():
     assert qio.quant_range(8) == (-128, 127) and qio.quant_range(8, True) == (0, 255) and qio.quant_range(4) == (-8, 7)
     with pytest.raises(ValueError):
         qio.quant_range(33)
+
+
+def test_quantized_weights_section():
+    import torch
+    case = CASES[0]
+    cfg, params, _ = _inputs(case)
+    I, H = case["input_size"], case["hidden_size"]
+    W_q = torch.arange(I * 3 * H, dtype=torch.int32).reshape(I, 3 * H) - 30
+    R_q = torch.arange(H * 3 * H, dtype=torch.int32).reshape(H, 3 * H) - 50
+    bw_q, br_q = torch.arange(3 * H, dtype=torch.int32), -torch.arange(3 * H, dtype=torch.int32)
+    weights = qio.weight_codes_for_export(W_q, R_q, bw_q, br_q)
+    assert weights["W"] == W_q.tolist() and weights["R"] == R_q.tolist()
+    assert weights["bw"] == bw_q.tolist() and weights["br"] == br_q.tolist()
+    assert set(qio.weight_codes_for_export(W_q, R_q)) == {"W", "R"}
+    document = qio.quant_params_document(input_size=I, hidden_size=H, config=cfg, params=params, quantized_weights=weights)
+    assert list(document) == ["model_info", "operators", "quantized_weights"]
+    json.dumps(document)
+    with pytest.raises(RuntimeError):
+        qio.quant_params_document(input_size=I, hidden_size=H, config=cfg, params=None)
+
+
+@pytest.mark.parametrize("case", CASES, ids=IDS)
+def test_io_quant_meta_matches_the_reference(case):
+    cfg, params, _ = _inputs(case)
+    meta = qio.io_quant_meta(cfg, params)
+    assert meta == case["io_quant_meta"]
+    assert qio.grids_match(meta["output"], meta["hidden"])
+    other = dict(meta["input"], zp=meta["input"]["zp"] + 1)
+    assert not qio.grids_match(meta["input"], other)
+    with pytest.raises(RuntimeError):
+        qio.io_quant_meta(cfg, None)
