@@ -78,3 +78,21 @@ def reduce_to_grid(terms, grid_shape):
     axes = tuple(a for a, n in enumerate(padded) if n == 1 and terms.shape[a] != 1)
     out = terms.sum(axis=axes, keepdims=True) if axes else terms
     return out.reshape(grid_shape)
+
+
+def expand_blocks(grid_value, tensor_shape):
+    """A blockwise grid repeated to the tensor's shape: entry [i, j, ...] covers the block of extents
+    tensor_shape[d] / grid_shape[d] (torch_builtins.py:717-754 views the tensor the other way round)."""
+    full = np.asarray(grid_value, dtype=F)
+    for axis, (extent, blocks) in enumerate(zip(tensor_shape, full.shape)):
+        full = np.repeat(full, extent // blocks, axis=axis)
+    return full
+
+
+def reduce_to_blocks(terms, grid_shape):
+    """Sum of per-element terms over every block, accumulated in double."""
+    terms = np.asarray(terms, dtype=np.float64)
+    view = []
+    for extent, blocks in zip(terms.shape, grid_shape):
+        view += [blocks, extent // blocks]
+    return terms.reshape(view).sum(axis=tuple(range(1, 2 * len(grid_shape), 2)))

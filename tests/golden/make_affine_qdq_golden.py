@@ -116,6 +116,28 @@ def main(reference_root):
         out[f"{name}/x"], out[f"{name}/grad"], out[f"{name}/scale"], out[f"{name}/offset"] = x, grad, scale, offset
         out[f"{name}/range"] = np.array([qmin, qmax], dtype=np.int64)
 
+    # blockwise grids: the tensor is cut into blocks along the blocked dimensions, one grid entry per block
+    for name, shape, grid_shape, block_size, qmin, qmax in [
+            ("blocks_of_16", (8, 64), (8, 4), [1, 16], -8, 7),
+            ("blocks_conv_weight", (6, 32, 3, 3), (6, 2, 1, 1), [-1, 16, -1, -1], -128, 127)]:
+        scale = rng.uniform(0.01, 0.2, size=grid_shape).astype(np.float32)
+        offset = np.zeros(grid_shape, dtype=np.float32)
+        full = scale
+        for axis, (extent, blocks) in enumerate(zip(shape, grid_shape)):
+            full = np.repeat(full, extent // blocks, axis=axis)
+        x = make_input(rng, shape, full, np.zeros(shape, np.float32), qmin, qmax, with_nan=False)
+        grad = rng.standard_normal(shape).astype(np.float32)
+        xt = torch.tensor(x, requires_grad=True)
+        st, ot = torch.tensor(scale, requires_grad=True), torch.tensor(offset, requires_grad=True)
+        y = backend.quantize_dequantize(xt, st, ot, qmin, qmax, block_size=block_size)
+        y.backward(torch.tensor(grad))
+        out[f"{name}/y"] = y.detach().numpy()
+        out[f"{name}/keep"] = packed_keep(xt.grad.numpy(), grad)
+        out[f"{name}/dscale"], out[f"{name}/doffset"] = st.grad.numpy().copy(), ot.grad.numpy().copy()
+        out[f"{name}/x"], out[f"{name}/grad"], out[f"{name}/scale"], out[f"{name}/offset"] = x, grad, scale, offset
+        out[f"{name}/range"] = np.array([qmin, qmax], dtype=np.int64)
+        out[f"{name}/block_size"] = np.array(block_size, dtype=np.int64)
+
     # NaN inputs: the divide form propagates them; the fast form restores them after the kernel
     x = make_input(rng, (1030,), np.float32(0.05), np.float32(-3.0), -128, 127, with_nan=True)
     st, ot = torch.tensor(0.05), torch.tensor(-3.0)

@@ -12,14 +12,16 @@ oracle = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(oracle)
 
 GOLDEN = np.load(os.path.join(HERE, "golden", "affine_qdq.npz"))
-CASES = sorted({key.split("/")[0] for key in GOLDEN.files} - {"nan"})
+BLOCK_CASES = sorted(key.split("/")[0] for key in GOLDEN.files if key.endswith("/block_size"))
+CASES = sorted({key.split("/")[0] for key in GOLDEN.files} - {"nan"} - set(BLOCK_CASES))
 
 
 def case_arrays(name):
     g = {key.split("/", 1)[1]: GOLDEN[key] for key in GOLDEN.files if key.startswith(name + "/")}
     n = g["x"].size
     for flags in ("keep", "fast_keep"):
-        g[flags] = np.unpackbits(g[flags])[:n].astype(bool).reshape(g["x"].shape)
+        if flags in g:
+            g[flags] = np.unpackbits(g[flags])[:n].astype(bool).reshape(g["x"].shape)
     return g
 
 
@@ -83,3 +85,32 @@ def test_grid_layout():
     for bad in ((4, 6), (5,), (2, 1, 1), (1, 1, 1, 6)):
         with pytest.raises(RuntimeError):
             grid_layout((4, 5, 6), bad)
+
+
+@pytest.mark.parametrize("name", BLOCK_CASES)
+def test_oracle_blockwise_grids_match_the_reference(name):
+    g = case_arrays(name)
+    qmin, qmax = (int(v) for v in g["range"])
+    scale, offset = oracle.expand_blocks(g["scale"], g["x"].shape), oracle.expand_blocks(g["offset"], g["x"].shape)
+    y, keep = oracle.divide_form(g["x"], scale, offset, qmin, qmax)
+    assert same_bits(y, g["y"]) and np.array_equal(keep, g["keep"])
+    dx, scale_terms, offset_terms = oracle.divide_form_backward(g["grad"], g["x"], scale, offset, qmin, qmax)
+    assert same_bits(dx, g["grad"] * g["keep"])
+    size = oracle.reduce_to_blocks(np.abs(scale_terms), g["scale"].shape)
+    assert np.all(np.abs(oracle.reduce_to_blocks(scale_terms, g["scale"].shape) - g["dscale"]) <= 1e-5 * size + 1e-30)
+    assert np.allclose(oracle.reduce_to_blocks(offset_terms, g["offset"].shape), g["doffset"], rtol=1e-5, atol=1e-5)
+
+
+def test_blocked_shapes():
+    from rx_met_b200.affine_qdq import blocked_shapes, grid_layout
+    assert blocked_shapes((8, 64), (8, 4), (1, 16)) == ((8, 1, 4, 16), (8, 1, 4, 1))
+    assert blocked_shapes((8, 64), (8, 4), (-1, -1)) == ((8, 1, 4, 16), (8, 1, 4, 1))
+    assert grid_layout(*blocked_shapes((8, 64), (8, 4), (1, 16))) == (1, 32, 16)
+    assert grid_layout(*blocked_shapes((6, 32, 3, 3), (6, 2, 1, 1), (-1, 16, -1, -1))) == (1, 12, 144)
+    assert grid_layout(*blocked_shapes((5, 8, 64), (8, 4), (1, 16))) == (5, 32, 16)
+    assert grid_layout((4, 5, 6), (4, 5, 1)) == (1, 20, 6)
+    for bad in (((8, 64), (8, 4), (1, 8)), ((8, 64), (8, 4), (16,)), ((64,), (8, 4), (1, 16))):
+        with pytest.raises(RuntimeError):
+            blocked_shapes(*bad)
+    with pytest.raises(RuntimeError):   # blocks along the first of two dimensions: entries are not contiguous
+        grid_layout(*blocked_shapes((8, 64), (2, 64), (4, 1)))

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from test_affine_qdq_cpu import CASES, GOLDEN, case_arrays, oracle, same_bits
+from test_affine_qdq_cpu import BLOCK_CASES, CASES, GOLDEN, case_arrays, oracle, same_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -125,7 +125,9 @@ def test_refusals():
     x = torch.zeros(8, 8, device="cuda")
     s, o = torch.ones(8, 1, device="cuda"), torch.zeros(8, 1, device="cuda")
     with pytest.raises(RuntimeError):
-        affine_qdq.quantize_dequantize(x, s, o, -128, 127, block_size=[1, 4])
+        affine_qdq.quantize_dequantize(x, s, o, -128, 127, block_size=[1, 3])
+    with pytest.raises(RuntimeError):
+        affine_qdq.quantize_dequantize(x, s, o, -128, 127, zero_point_shift=0.5)
     with pytest.raises(RuntimeError):
         affine_qdq.quantize_dequantize(x.double(), s, o, -128, 127)
     with pytest.raises(RuntimeError):
@@ -137,3 +139,27 @@ def test_refusals():
     empty = torch.zeros(0, 8, device="cuda")
     y, _ = affine_qdq.forward(empty, torch.ones((), device="cuda"), torch.zeros((), device="cuda"), -128, 127, reciprocal=False)
     assert y.shape == empty.shape
+
+
+@pytest.mark.parametrize("name", BLOCK_CASES)
+def test_cuda_blockwise_grids_match_the_reference(name):
+    from rx_met_b200 import affine_qdq
+    g = case_arrays(name)
+    qmin, qmax = (int(v) for v in g["range"])
+    block_size = [int(v) for v in g["block_size"]]
+    x = dev(g["x"]).requires_grad_()
+    s, o = dev(g["scale"]).requires_grad_(), dev(g["offset"]).requires_grad_()
+    y = affine_qdq.quantize_dequantize(x, s, o, qmin, qmax, block_size=block_size)
+    y.backward(dev(g["grad"]))
+    assert same_bits(y.detach().cpu().numpy(), g["y"])
+    assert same_bits(x.grad.cpu().numpy(), g["grad"] * g["keep"])
+    scale_full = oracle.expand_blocks(g["scale"], g["x"].shape)
+    _, scale_terms, _ = oracle.divide_form_backward(g["grad"], g["x"], scale_full, np.zeros_like(scale_full), qmin, qmax)
+    size = oracle.reduce_to_blocks(np.abs(scale_terms), g["scale"].shape)
+    assert s.grad.shape == s.shape
+    assert np.all(np.abs(s.grad.cpu().numpy() - g["dscale"]) <= 1e-5 * size + 1e-30)
+    assert np.allclose(o.grad.cpu().numpy(), g["doffset"], rtol=1e-5, atol=1e-5)
+    # a blockwise grid that is not trained still takes the divide form
+    with torch.no_grad():
+        y2 = affine_qdq.quantize_dequantize(dev(g["x"]), s, o, qmin, qmax, block_size=block_size)
+    assert same_bits(y2.cpu().numpy(), g["y"])
