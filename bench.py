@@ -453,7 +453,8 @@ def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10, elements=1 << 28):
     (read x and the incoming gradient, write dx; the scale and offset sums ride along)."""
     from rx_met_b200 import affine_qdq
     shapes = {"per_tensor": ((elements,), ()), "rows_of_16384": ((elements >> 14, 16384), (elements >> 14, 1)),
-              "columns_1024": ((elements >> 10, 1024), (1024,))}
+              "columns_1024": ((elements >> 10, 1024), (1024,)),
+              "blocks_of_64": ((elements >> 12, 4096), (elements >> 12, 64))}   # blockwise weights: block_size [1, 64]
     out = {}
     for name, (shape, grid_shape) in shapes.items():
         x = torch.randn(shape, device=device)
@@ -461,11 +462,12 @@ def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10, elements=1 << 28):
         scale = torch.full(grid_shape, 0.02, device=device)
         offset = torch.zeros(grid_shape, device=device)
         n = x.numel()
+        blocks = [1, 64] if name.startswith("blocks") else None
         calls = {
-            "forward": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=False)),
-            "forward_fast": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=True)),
+            "forward": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=False, block_size=blocks)),
+            "forward_fast": (8, lambda: affine_qdq.forward(x, scale, offset, -128, 127, reciprocal=True, block_size=blocks)),
             "backward": (12, lambda: affine_qdq.backward(g, x, scale, offset, -128, 127, reciprocal=False,
-                                                         want_scale_grad=True, want_offset_grad=True)),
+                                                         want_scale_grad=True, want_offset_grad=True, block_size=blocks)),
         }
         entry = {}
         for kind, (bytes_per, fn) in calls.items():

@@ -112,6 +112,7 @@ struct Pass {
     float *out;             // y (forward) or dx (backward); may be null in a backward that only wants sums
     uint8_t *keep;          // forward, optional: 1 where the value was inside the grid
     float *partial;         // backward, optional: [items][2]
+    float *dscale, *doffset;   // backward, block pass only: the sums of a row are the final result
     uint64_t outer, channels, inner;
     int wantSums;
 };
@@ -279,6 +280,89 @@ __global__ void __launch_bounds__(kThreads, 4) columnPass(Pass p, Grid g, int co
     }
 }
 
+// Short rows that are whole grid entries (outer == 1: blockwise weights, per-channel grids of short rows): a
+// group of lanesPerRow lanes (a power of two up to 32) owns one row, so a warp reads 32 / lanesPerRow adjacent
+// rows = one contiguous stretch, and the sums of a row, reduced with shuffles inside the group, are the final
+// dscale / doffset of its entry: no workspace, no second launch.
+template <bool kBackward, bool kReciprocal>
+__global__ void __launch_bounds__(kThreads) blockPass(Pass p, Grid g, int lanesPerRow, int vector) {
+    const uint64_t rows = p.channels;   // outer == 1
+    const int lane = threadIdx.x & 31, sub = lane / lanesPerRow, sl = lane % lanesPerRow;
+    const int rowsPerWarp = 32 / lanesPerRow;
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kWarps;
+    const float *__restrict__ xIn = p.x;
+    const float *__restrict__ gIn = p.grad;
+    float *__restrict__ out = p.out;
+    uint8_t *__restrict__ keepOut = p.keep;
+    for (uint64_t base = (static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5)) * rowsPerWarp; base < rows;
+         base += warps * rowsPerWarp) {
+        const uint64_t row = base + sub;
+        const bool live = row < rows;
+        Sums acc;
+        if (live) {
+            const float s = __ldg(g.scale + row), o = __ldg(g.offset + row);
+            const float inv = __fdiv_rn(1.0f, s);
+            const float zp = static_cast<float>(-static_cast<int>(o));
+            const uint64_t begin = row * p.inner;
+            if (vector) {
+                for (uint64_t v = sl; v < p.inner / 4; v += lanesPerRow) {
+                    const uint64_t at = begin + 4 * v;
+                    const float4 xv = __ldcs(reinterpret_cast<const float4 *>(xIn + at));
+                    const float in[4] = {xv.x, xv.y, xv.z, xv.w};
+                    float res[4];
+                    if constexpr (kBackward) {
+                        const float4 gv = __ldcs(reinterpret_cast<const float4 *>(gIn + at));
+                        const float gr[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (kReciprocal) res[k] = __fmul_rn(gr[k], quantDequant<true>(in[k], s, inv, o, zp, g).keep);
+                            else res[k] = backwardOne(in[k], gr[k], s, o, g, acc);
+                        }
+                    } else {
+                        uint32_t bits = 0;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const Element e = quantDequant<kReciprocal>(in[k], s, inv, o, zp, g);
+                            res[k] = e.y;
+                            bits |= (e.keep != 0.0f ? 1u : 0u) << (8 * k);
+                        }
+                        if (keepOut) *reinterpret_cast<uint32_t *>(keepOut + at) = bits;
+                    }
+                    if (out) __stcs(reinterpret_cast<float4 *>(out + at), make_float4(res[0], res[1], res[2], res[3]));
+                }
+            } else {
+                for (uint64_t i = sl; i < p.inner; i += lanesPerRow) {
+                    const uint64_t at = begin + i;
+                    const float xv = __ldcs(xIn + at);
+                    float res;
+                    if constexpr (kBackward) {
+                        const float gr = __ldcs(gIn + at);
+                        if (kReciprocal) res = __fmul_rn(gr, quantDequant<true>(xv, s, inv, o, zp, g).keep);
+                        else res = backwardOne(xv, gr, s, o, g, acc);
+                    } else {
+                        const Element e = quantDequant<kReciprocal>(xv, s, inv, o, zp, g);
+                        res = e.y;
+                        if (keepOut) keepOut[at] = e.keep != 0.0f;
+                    }
+                    if (out) __stcs(out + at, res);
+                }
+            }
+        }
+        if constexpr (kBackward) {
+            if (p.wantSums) {
+                for (int d = lanesPerRow >> 1; d > 0; d >>= 1) {   // every lane takes part, dead rows add zeros
+                    acc.scale += __shfl_down_sync(0xffffffffu, acc.scale, d, lanesPerRow);
+                    acc.offset += __shfl_down_sync(0xffffffffu, acc.offset, d, lanesPerRow);
+                }
+                if (live && sl == 0) {
+                    if (p.dscale) p.dscale[row] = acc.scale;
+                    if (p.doffset) p.doffset[row] = acc.offset;
+                }
+            }
+        }
+    }
+}
+
 // dscale[c], doffset[c] = sum over a < groups, b < run of partial[a * groupStride + c * run + b], in that order
 // per thread and then over the threads of the CTA: the same order on every run.
 __global__ void __launch_bounds__(128) finishSums(const float *partial, uint64_t groups, uint64_t groupStride, uint64_t run,
@@ -306,6 +390,7 @@ __global__ void __launch_bounds__(128) finishSums(const float *partial, uint64_t
 
 struct Plan {
     bool rows;              // row kernel or column kernel
+    bool blocks;            // block kernel: short rows that are whole grid entries; nothing else is set then
     uint64_t segments;      // row kernel: segments per row
     uint64_t chunks;        // column kernel: row chunks
     uint64_t items;         // partial entries
@@ -314,7 +399,10 @@ struct Plan {
 Plan planFor(uint64_t outer, uint64_t channels, uint64_t inner) {
     Plan plan{};
     plan.rows = channels == 1 || inner >= kLongRow;
-    if (plan.rows) {
+    plan.blocks = !plan.rows && outer == 1;
+    if (plan.blocks) {
+        plan.items = 0;
+    } else if (plan.rows) {
         plan.segments = (inner + kSegment - 1) / kSegment;
         // one partial per warp and segment; per tensor one per warp of the grid (at most kMaxResident CTAs per SM)
         plan.items = outer * channels == 1 ? static_cast<uint64_t>(currentDevice().sms) * kMaxResident * kWarps
@@ -350,7 +438,25 @@ template <bool kBackward>
 int run(Pass p, Grid g, int reciprocal, const Plan &plan, cudaStream_t st) {
     int rowGrid = 0;
     const DeviceInfo dev = currentDevice();
-    if (plan.rows) {
+    if (plan.blocks) {
+        const bool vector = p.inner % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
+                            (!p.grad || (reinterpret_cast<uintptr_t>(p.grad) & 15) == 0) &&
+                            (!p.out || (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                            (!p.keep || (reinterpret_cast<uintptr_t>(p.keep) & 3) == 0);
+        const uint64_t lanes = vector ? p.inner / 4 : p.inner;
+        int lanesPerRow = 1;
+        while (lanesPerRow < 32 && static_cast<uint64_t>(lanesPerRow) < lanes) lanesPerRow *= 2;
+        const uint64_t warpsNeeded = (p.channels + 32 / lanesPerRow - 1) / (32 / lanesPerRow);
+        auto launch = [&](auto kernel) {
+            const uint64_t ctas = (warpsNeeded + kWarps - 1) / kWarps;
+            const int grid = static_cast<int>(std::min<uint64_t>(
+                ctas, static_cast<uint64_t>(dev.sms) * std::min(residentCtas(kernel), kMaxResident)));
+            kernel<<<grid, kThreads, 0, st>>>(p, g, lanesPerRow, vector ? 1 : 0);
+        };
+        if (reciprocal) launch(blockPass<kBackward, true>);
+        else launch(blockPass<kBackward, false>);
+        afterLaunch("affineBlockPass");
+    } else if (plan.rows) {
         // per tensor the whole tensor is one row: `outer` and `channels` fold into it on the host
         const bool aligned = p.inner % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
                              (!p.grad || (reinterpret_cast<uintptr_t>(p.grad) & 15) == 0) &&
@@ -442,7 +548,10 @@ int rxmet_affine_qdq_backward(const float *grad_dev, const float *x_dev, uint64_
         p.outer = outer; p.channels = channels; p.inner = inner;
         if (channels == 1) { p.inner = outer * inner; p.outer = 1; }
         const Plan plan = planFor(p.outer, p.channels, p.inner);
-        if (sums) {
+        if (sums && plan.blocks) {
+            p.dscale = dscale_dev; p.doffset = doffset_dev;
+            p.wantSums = 1;
+        } else if (sums) {
             RXMET_REQUIRE(workspace_dev && workspace_bytes >= plan.items * 2 * sizeof(float),
                           "affine qdq backward: workspace of %zu bytes needed", static_cast<size_t>(plan.items * 2 * sizeof(float)));
             p.partial = static_cast<float *>(workspace_dev);
@@ -451,7 +560,7 @@ int rxmet_affine_qdq_backward(const float *grad_dev, const float *x_dev, uint64_
         const Grid g{scale_dev, offset_dev, static_cast<float>(qmin), static_cast<float>(qmax), qmin, qmax};
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         const int rowGrid = run<true>(p, g, reciprocal, plan, st);
-        if (sums) {
+        if (sums && !plan.blocks) {
             if (plan.rows && p.outer * p.channels == 1)
                 finishSums<<<1, 128, 0, st>>>(p.partial, 1, 0, static_cast<uint64_t>(rowGrid) * kWarps, dscale_dev, doffset_dev);
             else if (plan.rows)

@@ -60,6 +60,9 @@ def test_cuda_nan_inputs():
     ((4096, 768), (768,), 0, 255),              # activations, grid along the last axis
     ((33, 40, 50), (40, 1), -32768, 32767),     # middle axis, short rows
     ((9, 16, 300), (16, 1), -128, 127),         # middle axis, long rows, several outer slices
+    ((2048, 64), (2048, 1), -128, 127),         # short rows that are whole grid entries: 16 lanes per row
+    ((300, 37), (300, 1), -8, 7),               # the same with rows that are not a multiple of four long
+    ((1000, 8), (1000, 1), -128, 127),          # two lanes per row
 ])
 def test_cuda_matches_the_restatement_on_larger_tensors(shape, grid_shape, qmin, qmax):
     rng = np.random.default_rng(abs(hash((shape, grid_shape))) % (1 << 31))
@@ -163,3 +166,32 @@ def test_cuda_blockwise_grids_match_the_reference(name):
     with torch.no_grad():
         y2 = affine_qdq.quantize_dequantize(dev(g["x"]), s, o, qmin, qmax, block_size=block_size)
     assert same_bits(y2.cpu().numpy(), g["y"])
+
+
+@pytest.mark.parametrize("shape,grid_shape,block_size", [
+    ((512, 1024), (512, 16), [1, 64]),
+    ((96, 384), (96, 3), [-1, 128]),
+    ((64, 48, 3, 3), (64, 3, 1, 1), [-1, 16, -1, -1]),
+])
+def test_cuda_blockwise_grids_match_the_restatement_on_larger_tensors(shape, grid_shape, block_size):
+    from rx_met_b200 import affine_qdq
+    rng = np.random.default_rng(sum(shape))
+    scale = rng.uniform(0.005, 0.1, size=grid_shape).astype(np.float32)
+    offset = np.zeros(grid_shape, dtype=np.float32)
+    full = oracle.expand_blocks(scale, shape)
+    x = (rng.standard_normal(shape) * 5.0 * full).astype(np.float32)
+    grad = rng.standard_normal(shape).astype(np.float32)
+    xt, st, ot, gt = dev(x), dev(scale), dev(offset), dev(grad)
+    y, keep = affine_qdq.forward(xt, st, ot, -8, 7, reciprocal=False, want_keep=True, block_size=block_size)
+    want_y, want_keep = oracle.divide_form(x, full, np.zeros_like(full), -8, 7)
+    assert same_bits(y.cpu().numpy(), want_y) and np.array_equal(keep.cpu().numpy(), want_keep)
+    assert 0.02 < 1.0 - want_keep.mean() < 0.6
+    dx, ds, do = affine_qdq.backward(gt, xt, st, ot, -8, 7, reciprocal=False, want_scale_grad=True, want_offset_grad=True,
+                                     block_size=block_size)
+    want_dx, scale_terms, offset_terms = oracle.divide_form_backward(grad, x, full, np.zeros_like(full), -8, 7)
+    assert same_bits(dx.cpu().numpy(), want_dx)
+    for got, terms in ((ds, scale_terms), (do, offset_terms)):
+        want = oracle.reduce_to_blocks(terms, grid_shape)
+        size = oracle.reduce_to_blocks(np.abs(terms), grid_shape)
+        assert got.shape == want.shape
+        assert np.all(np.abs(got.cpu().numpy() - want) <= 1e-5 * size + 1e-30)
