@@ -294,8 +294,74 @@ __global__ void __launch_bounds__(kThreads) blockPass(Pass p, Grid g, int lanesP
     const float *__restrict__ gIn = p.grad;
     float *__restrict__ out = p.out;
     uint8_t *__restrict__ keepOut = p.keep;
-    for (uint64_t base = (static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5)) * rowsPerWarp; base < rows;
-         base += warps * rowsPerWarp) {
+    const uint64_t warpId = static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    if (vector && p.inner / 4 <= static_cast<uint64_t>(lanesPerRow)) {
+        // At most one 16-byte piece per lane and row (rows of up to 128 elements): a warp takes two adjacent
+        // stretches of rows per turn and issues all their loads before the first result is needed.
+        const bool has = static_cast<uint64_t>(sl) < p.inner / 4;
+        for (uint64_t base = warpId * rowsPerWarp * 2; base < rows; base += warps * rowsPerWarp * 2) {
+            uint64_t row[2], at[2];
+            bool live[2];
+            float4 xv[2], gv[2];
+            float s[2], o[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                row[j] = base + static_cast<uint64_t>(j) * rowsPerWarp + sub;
+                live[j] = has && row[j] < rows;
+                at[j] = row[j] * p.inner + 4 * static_cast<uint64_t>(sl);
+                if (live[j]) {
+                    xv[j] = __ldcs(reinterpret_cast<const float4 *>(xIn + at[j]));
+                    if constexpr (kBackward) gv[j] = __ldcs(reinterpret_cast<const float4 *>(gIn + at[j]));
+                    s[j] = __ldg(g.scale + row[j]);
+                    o[j] = __ldg(g.offset + row[j]);
+                }
+            }
+            Sums acc[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (!live[j]) continue;
+                const float inv = __fdiv_rn(1.0f, s[j]);
+                const float zp = static_cast<float>(-static_cast<int>(o[j]));
+                const float in[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+                float res[4];
+                if constexpr (kBackward) {
+                    const float gr[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (kReciprocal) res[k] = __fmul_rn(gr[k], quantDequant<true>(in[k], s[j], inv, o[j], zp, g).keep);
+                        else res[k] = backwardOne(in[k], gr[k], s[j], o[j], g, acc[j]);
+                    }
+                } else {
+                    uint32_t bits = 0;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const Element e = quantDequant<kReciprocal>(in[k], s[j], inv, o[j], zp, g);
+                        res[k] = e.y;
+                        bits |= (e.keep != 0.0f ? 1u : 0u) << (8 * k);
+                    }
+                    if (keepOut) *reinterpret_cast<uint32_t *>(keepOut + at[j]) = bits;
+                }
+                if (out) __stcs(reinterpret_cast<float4 *>(out + at[j]), make_float4(res[0], res[1], res[2], res[3]));
+            }
+            if constexpr (kBackward) {
+                if (p.wantSums) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        for (int d = lanesPerRow >> 1; d > 0; d >>= 1) {
+                            acc[j].scale += __shfl_down_sync(0xffffffffu, acc[j].scale, d, lanesPerRow);
+                            acc[j].offset += __shfl_down_sync(0xffffffffu, acc[j].offset, d, lanesPerRow);
+                        }
+                        if (sl == 0 && row[j] < rows) {
+                            if (p.dscale) p.dscale[row[j]] = acc[j].scale;
+                            if (p.doffset) p.doffset[row[j]] = acc[j].offset;
+                        }
+                    }
+                }
+            }
+        }
+        return;
+    }
+    for (uint64_t base = warpId * rowsPerWarp; base < rows; base += warps * rowsPerWarp) {
         const uint64_t row = base + sub;
         const bool live = row < rows;
         Sums acc;
