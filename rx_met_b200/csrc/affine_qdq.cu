@@ -88,7 +88,7 @@ __device__ __forceinline__ float backwardOne(float x, float gr, float s, float o
     const bool keep = g.lo <= t && t <= g.hi;
     const float m = keep ? 1.0f : 0.0f;
     const float lo = __fadd_rn(o, g.lo), hi = __fadd_rn(o, g.hi);
-    const float qc = q != q ? q : fminf(fmaxf(q, lo), hi);
+    const float qc = fminf(fmaxf(q, lo), hi);   // a NaN input reaches the sum through xs * m below
     acc.scale = __fadd_rn(acc.scale, __fmul_rn(gr, __fsub_rn(qc, __fmul_rn(xs, m))));
     acc.offset = __fadd_rn(acc.offset, __fmul_rn(gr, keep ? 0.0f : s));
     return __fmul_rn(gr, m);

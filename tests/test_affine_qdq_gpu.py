@@ -195,3 +195,18 @@ def test_cuda_blockwise_grids_match_the_restatement_on_larger_tensors(shape, gri
         size = oracle.reduce_to_blocks(np.abs(terms), grid_shape)
         assert got.shape == want.shape
         assert np.all(np.abs(got.cpu().numpy() - want) <= 1e-5 * size + 1e-30)
+
+
+def test_backward_of_nan_inputs():
+    """A NaN input has no gradient of its own (it is outside the grid) and makes the scale gradient NaN, as in the
+    reference's expressions; the offset gradient stays finite."""
+    from rx_met_b200 import affine_qdq
+    x = GOLDEN["nan/x"]
+    grad = np.ones_like(x)
+    s, o = dev(np.float32(0.05).reshape(())), dev(np.float32(-3.0).reshape(()))
+    dx, ds, do = affine_qdq.backward(dev(grad), dev(x), s, o, -128, 127, reciprocal=False, want_scale_grad=True,
+                                     want_offset_grad=True)
+    want_dx, scale_terms, offset_terms = oracle.divide_form_backward(grad, x, np.float32(0.05), np.float32(-3.0), -128, 127)
+    assert same_bits(dx.cpu().numpy(), want_dx) and not dx.cpu().numpy()[np.isnan(x)].any()
+    assert np.isnan(scale_terms).sum() == 3 and np.isnan(ds.cpu().numpy()).all()
+    assert np.allclose(do.cpu().numpy().reshape(()), offset_terms.astype(np.float64).sum(), rtol=1e-5)
