@@ -583,6 +583,17 @@ RXMET_API int rxmet_affine_qdq_backward(const float *grad_dev, const float *x_de
                                         int qmax, int reciprocal, float *dx_dev, float *dscale_dev, float *doffset_dev,
                                         void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* ---- loss of the training step -------------------------------------------------------------
+ * Mean-squared-error loss between the output sequence and a target and its gradient with respect to the
+ * output, fused: grad = (out - target) * (2 / count) (bit-identical to the eager float32 expressions
+ * `diff = out - target; grad = diff * (2.0 / diff.numel())` of a training loop; this entry has no
+ * counterpart in the reference, whose loss lives in the caller's torch code), *loss_dev =
+ * sum (out - target)^2 / count (fixed summation order).  workspace: rxmet_mse_loss_workspace_bytes()
+ * device bytes. */
+RXMET_API size_t rxmet_mse_loss_workspace_bytes(void);
+RXMET_API int rxmet_mse_loss_grad(const float *out_dev, const float *target_dev, uint64_t count, float *grad_dev,
+                                  float *loss_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,12 @@ class GruQatStep:
         nbytes = max(self.lib.rxmet_gru_workspace_bytes(op, T, B, I, H) for op in (0, 1, 2))
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.stats = torch.empty(self.lib.rxmet_gru_stats_floats(H), **f32)
+        self.lib.rxmet_mse_loss_workspace_bytes.restype = C.c_size_t
+        self.lib.rxmet_mse_loss_grad.restype = C.c_int
+        self.lib.rxmet_mse_loss_grad.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                 C.c_size_t, C.c_void_p]
+        self.loss = torch.zeros((), **f32)
+        self.loss_ws = torch.empty(self.lib.rxmet_mse_loss_workspace_bytes(), dtype=torch.uint8, device=self.device)
         self.params: Optional[GRUQuantParams] = None
         self._c_params = None
         self._keep = None
@@ -122,13 +128,21 @@ class GruQatStep:
             _p(self.dx), _p(self.dW), _p(self.dR), _p(self.dbw), _p(self.dbr), _p(self.dh0), _p(self.ws),
             C.c_size_t(self.ws.numel()), self._stream()), "backward_quant")
 
+    def mse_loss(self, target: torch.Tensor) -> torch.Tensor:
+        """Mean-squared error of the output sequence against `target` ([T,B,H] float32, contiguous) and its gradient
+        into self.dh_new[1:], one fused pass.  Returns self.loss, the device scalar every call overwrites."""
+        if target.dtype != torch.float32 or not target.is_contiguous() or tuple(target.shape) != (self.T, self.B, self.H):
+            raise ValueError("target must be a contiguous float32 tensor of shape [T, B, H]")
+        out, grad = self.h[1:], self.dh_new[1:]
+        cabi.check(self.lib.rxmet_mse_loss_grad(_p(out), _p(target), out.numel(), _p(grad), _p(self.loss), _p(self.loss_ws),
+                                                self.loss_ws.numel(), self._stream()), "mse_loss_grad")
+        return self.loss
+
     def step(self, x: torch.Tensor, target: torch.Tensor, lr: float) -> torch.Tensor:
-        """forward, MSE loss gradient, backward, gradient all-reduce, SGD update.  Returns the loss
-        (a device scalar, not synchronised)."""
-        out = self.forward(x)
-        diff = out - target
-        loss = diff.square().mean()
-        torch.mul(diff, 2.0 / diff.numel(), out=self.dh_new[1:])
+        """forward, MSE loss and its gradient, backward, gradient all-reduce, SGD update.  Returns the loss
+        (self.loss: a device scalar, not synchronised, overwritten by the next step)."""
+        self.forward(x)
+        loss = self.mse_loss(target)
         self.backward()
         if self.group is not None:
             torch.distributed.all_reduce(self.flat_g, group=self.group)
@@ -151,10 +165,8 @@ class GruQatStep:
         local = self.group is None
 
         def body():
-            out = self.forward(x)
-            diff = out - target
-            loss_ = diff.square().mean()
-            torch.mul(diff, 2.0 / diff.numel(), out=self.dh_new[1:])
+            self.forward(x)
+            loss_ = self.mse_loss(target)
             self.backward()
             if local:
                 self.flat_w.add_(self.flat_g, alpha=-lr)

@@ -381,3 +381,24 @@ def test_captured_step_replays_the_eager_step():
     w_graph, l_graph = run(True)
     assert l_eager == l_graph
     assert torch.equal(w_eager, w_graph)
+
+
+def test_fused_mse_loss_and_gradient():
+    """The step's loss kernel: gradient bit-identical to the eager float32 expressions, loss within 1e-6 relative."""
+    import torch
+    from rx_met_b200.qat import GruQatStep
+    for T, B, I, H in ((12, 16, 8, 32), (5, 3, 4, 33)):   # the second shape is not a multiple of four long
+        eng = GruQatStep(T, B, I, H, torch.device("cuda"), seed=3)
+        gen = torch.Generator(device="cpu").manual_seed(7)
+        eng.h.copy_(torch.randn(eng.h.shape, generator=gen))
+        target = torch.randn((T, B, H), generator=gen).cuda()
+        loss = eng.mse_loss(target)
+        diff = eng.h[1:] - target
+        want_grad = torch.mul(diff, 2.0 / diff.numel())
+        assert torch.equal(eng.dh_new[1:], want_grad)
+        want_loss = diff.double().square().mean()
+        assert abs(float(loss) - float(want_loss)) <= 1e-6 * float(want_loss)
+        again = float(eng.mse_loss(target))
+        assert again == float(loss)
+        with pytest.raises(ValueError):
+            eng.mse_loss(target[:, :, :-1])
