@@ -58,7 +58,9 @@ def _peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """SM clock and throttle reasons of one GPU during the timed region: an in-process NVML poll every
+    millisecond (read-only queries), because the region lasts a few tens of milliseconds, less than an
+    nvidia-smi process needs to start.  nvidia-smi in loop mode is the fallback when NVML cannot be loaded."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -67,8 +69,44 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []      # (sm MHz, reason bits)
+        self.sm_max = None
+        self._stop = False
+
+    def _nvml_index(self):
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            entries = [e.strip() for e in visible.split(",") if e.strip()]
+            if self.gpu_index < len(entries) and entries[self.gpu_index].isdigit():
+                return int(entries[self.gpu_index])
+        return self.gpu_index
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._nvml_index())
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons",
+                              getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+
+            def poll():
+                while not self._stop:
+                    try:
+                        sm = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        bits = int(reasons(handle)) if reasons is not None else 0
+                        self.samples.append((sm, bits))
+                    except pynvml.NVMLError:
+                        pass
+                    time.sleep(0.001)
+
+            self._pynvml = pynvml
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         if shutil.which("nvidia-smi") is None:
             return
         fd, self.path = tempfile.mkstemp(suffix=".csv")
@@ -77,9 +115,30 @@ class ClockSampler:
             ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
              "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
+    @staticmethod
+    def _summary(sm, smax, reasons, source):
+        # samples under load = upper half of the observed SM clocks
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm), "source": source}
+
     def stop(self):
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            nv = self._pynvml
+            names = {"hw_slowdown": "HwSlowdown", "hw_thermal_slowdown": "HwThermalSlowdown",
+                     "sw_thermal_slowdown": "SwThermalSlowdown", "sw_power_cap": "SwPowerCap"}
+            reasons = set()
+            for _, bits in self.samples:
+                for name, suffix in names.items():
+                    mask = getattr(nv, "nvmlClocksEventReason" + suffix, getattr(nv, "nvmlClocksThrottleReason" + suffix, 0))
+                    if bits & mask:
+                        reasons.add(name)
+            return self._summary([sm for sm, _ in self.samples], self.sm_max, reasons, "nvml")
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": None}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -98,11 +157,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         os.unlink(self.path)
-        # samples under load = upper half of the observed SM clocks
-        sm_sorted = sorted(sm)
-        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
-        return {"sm_mhz": statistics.median(load) if load else None,
-                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+        return self._summary(sm, max(smax) if smax else None, reasons, "nvidia-smi")
 
 
 # --------------------------------------------------------------------------
