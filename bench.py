@@ -235,6 +235,7 @@ def run_ours(args):
     from rx_met_b200 import _cabi as cabi
     from rx_met_b200 import gru_interface_binding as ops
     from rx_met_b200.qat import GruQatStep
+    from rx_met_b200.losses import mse_loss_grad, workspace as loss_workspace
     from rx_met_b200.staging import stage_from_pinned_host
 
     rank = int(os.environ.get("RANK", "0"))
@@ -374,6 +375,8 @@ def run_ours(args):
     copied = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    loss_dev = [torch.zeros((), dtype=torch.float32, device=device) for _ in range(2)]
+    loss_ws = loss_workspace(device)
     loss_ready = [torch.cuda.Event() for _ in range(2)]
     losses = []
     state = {"primed": -1}
@@ -401,11 +404,9 @@ def run_ours(args):
         x_dev, y_dev = x_buf[slot], y_buf[slot]
         out = ops.forward_quant_int_storage(True, T, B, I, H, W, R, bw, br, x_dev, None, qp)
         h, v = out[0], out[1]
-        diff = h[1:] - y_dev
-        loss = diff.square().mean()
         dh_new = torch.empty_like(h)
         dh_new[0].zero_()
-        torch.mul(diff, 2.0 / diff.numel(), out=dh_new[1:])
+        loss, _ = mse_loss_grad(h[1:], y_dev, dh_new[1:], loss_dev[slot], loss_ws)   # loss and its gradient, one pass
         dx, dW, dR, dbw, dbr, _ = ops.backward_quant_int_storage(T, B, I, H, *out[2:7], dh_new, h, v, qp, *out[7:])
         consumed[slot].record()
         grads = [dW, dR, dbw, dbr]

@@ -402,3 +402,23 @@ def test_fused_mse_loss_and_gradient():
         assert again == float(loss)
         with pytest.raises(ValueError):
             eng.mse_loss(target[:, :, :-1])
+
+
+def test_mse_loss_helper():
+    import torch
+    from rx_met_b200 import losses
+    gen = torch.Generator(device="cpu").manual_seed(9)
+    h = torch.randn((7, 5, 24), generator=gen).cuda()
+    target = torch.randn((6, 5, 24), generator=gen).cuda()
+    grad_buffer = torch.zeros_like(h)
+    loss, grad = losses.mse_loss_grad(h[1:], target, grad_buffer[1:])
+    diff = h[1:] - target
+    assert grad.data_ptr() == grad_buffer[1:].data_ptr() and torch.equal(grad, torch.mul(diff, 2.0 / diff.numel()))
+    assert not grad_buffer[0].any()
+    assert abs(float(loss) - float(diff.double().square().mean())) <= 1e-6 * float(loss)
+    loss2, grad2 = losses.mse_loss_grad(h[1:], target)
+    assert torch.equal(grad2, grad) and float(loss2) == float(loss)
+    with pytest.raises(RuntimeError):
+        losses.mse_loss_grad(h[1:], target[:, :, :-1])
+    with pytest.raises(RuntimeError):
+        losses.mse_loss_grad(h[1:].cpu(), target.cpu())
