@@ -120,9 +120,10 @@ def forward(tensor, scale, offset, qmin: int, qmax: int, *, reciprocal: bool, wa
     outer, channels, inner = _layout(x, scale, block_size)
     y = torch.empty_like(x)
     keep = torch.empty(x.shape, dtype=torch.bool, device=x.device) if want_keep else None
-    cabi.check(_library().rxmet_affine_qdq_forward(_ptr(x), outer, channels, inner, _ptr(s), _ptr(o), int(qmin), int(qmax),
-                                                  int(reciprocal), _ptr(y), _ptr(keep), _stream(x.device)),
-               "affine_qdq.forward")
+    with torch.cuda.device(x.device):  # launch on the tensor's device, whatever device is current
+        cabi.check(_library().rxmet_affine_qdq_forward(_ptr(x), outer, channels, inner, _ptr(s), _ptr(o), int(qmin),
+                                                      int(qmax), int(reciprocal), _ptr(y), _ptr(keep), _stream(x.device)),
+                   "affine_qdq.forward")
     return y, keep
 
 
@@ -141,9 +142,10 @@ def backward(grad, tensor, scale, offset, qmin: int, qmax: int, *, reciprocal: b
     if ds is not None or do is not None:
         ws_bytes = lib.rxmet_affine_qdq_backward_workspace_bytes(outer, channels, inner)
         ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=x.device)
-    cabi.check(lib.rxmet_affine_qdq_backward(_ptr(g), _ptr(x), outer, channels, inner, _ptr(s), _ptr(o), int(qmin), int(qmax),
-                                             int(reciprocal), _ptr(dx), _ptr(ds), _ptr(do), _ptr(ws), ws_bytes,
-                                             _stream(x.device)), "affine_qdq.backward")
+    with torch.cuda.device(x.device):
+        cabi.check(lib.rxmet_affine_qdq_backward(_ptr(g), _ptr(x), outer, channels, inner, _ptr(s), _ptr(o), int(qmin),
+                                                 int(qmax), int(reciprocal), _ptr(dx), _ptr(ds), _ptr(do), _ptr(ws), ws_bytes,
+                                                 _stream(x.device)), "affine_qdq.backward")
     return (dx, ds.view(scale.shape) if ds is not None else None, do.view(offset.shape) if do is not None else None)
 
 

@@ -26,15 +26,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxDims = 8;
 
-int smCount() {
-    static int sms = 0;
-    if (sms == 0) {
-        int device = 0;
-        RXMET_CUDA(cudaGetDevice(&device));
-        RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    }
-    return sms;
-}
+int smCount() { return currentDevice().sms; }
 int gridFor(uint64_t work, int perSm = 8) {
     const uint64_t blocks = (work + kThreads - 1) / kThreads;
     return static_cast<int>(std::max<uint64_t>(1, std::min<uint64_t>(blocks, static_cast<uint64_t>(smCount()) * perSm)));

@@ -6,6 +6,7 @@
 #include <cfloat>
 #include <cstring>
 #include <map>
+#include <tuple>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -71,6 +72,19 @@ void ensureDynamicSmem(const void *kernel, size_t bytes) {
     if (bytes <= have) return;
     RXMET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
     have = bytes;
+}
+
+int residentPerSm(const void *kernel, int block, size_t smem) {
+    static std::mutex guard;
+    static std::map<std::tuple<int, const void *, int, size_t>, int> known;
+    const int device = currentDevice().device;
+    std::lock_guard<std::mutex> lock(guard);
+    int &n = known[{device, kernel, block, smem}];
+    if (n == 0) {
+        RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, smem));
+        n = std::max(n, 1);
+    }
+    return n;
 }
 
 void kernelTimingBegin(const char *, cudaStream_t stream, cudaEvent_t *start, cudaEvent_t *stop) {

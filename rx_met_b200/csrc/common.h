@@ -100,8 +100,17 @@ const DeviceInfo &currentDevice();
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when `bytes` exceeds what the kernel
 // was last given.
 void ensureDynamicSmem(const void *kernel, size_t bytes);
+// Resident CTAs per SM of `kernel` at this block size and dynamic shared memory, asked once per
+// device and configuration (at least 1).
+int residentPerSm(const void *kernel, int block, size_t smem);
 
 inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Whether a caller's pointer may be read or written with `bytes`-wide vector accesses (null counts
+// as aligned: an absent optional tensor is never touched).  The tensor-core paths issue 16-byte
+// asynchronous copies and vector stores on the caller's buffers; a base pointer that fails this
+// check sends the call to the kernels that use scalar accesses instead.
+inline bool alignedTo(const void *ptr, size_t bytes) { return (reinterpret_cast<uintptr_t>(ptr) & (bytes - 1)) == 0; }
 
 // Carves aligned sub-buffers out of a caller-provided device workspace.
 class Workspace {

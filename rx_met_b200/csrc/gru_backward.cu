@@ -963,9 +963,12 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     const bool simtGrads = std::getenv("RXMET_GRU_GRAD_SIMT") != nullptr;
     const bool registerPath = qat && call.exec->weightClass == CodeClass::I8 && H <= 128 &&
                               std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
-    const bool tensorInputGrad = qat && call.exec->weightClass == CodeClass::I8 && igrad::eligible(C, I) && !simtGrads;
+    // The tcgen05 kernels read the saved codes with 16-byte copies and store dx as float4 (x mask:
+    // 8-byte loads); callers' buffers that are not aligned that way take the scalar kernels.
+    const bool tensorInputGrad = qat && call.exec->weightClass == CodeClass::I8 && igrad::eligible(C, I) && !simtGrads &&
+                                 alignedTo(call.dx, 16) && alignedTo(mk.x, 8) && alignedTo(call.W_q, 16);
     const bool tensorGrads = qat && call.exec->actClass == CodeClass::I8 && I + 1 <= 144 && H + 1 <= 144 && I % 4 == 0 &&
-                             H % 4 == 0 && !simtGrads;
+                             H % 4 == 0 && !simtGrads && alignedTo(call.x_q, 16) && alignedTo(call.h, 16);
 
     const float *W = call.W, *R = call.R, *x = call.x;
     const float *chanScaleR = nullptr, *chanScaleW = nullptr;
@@ -976,7 +979,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         float *xf = ws.take<float>(rows * I);
         float *chan = ws.take<float>(2 * static_cast<size_t>(C));
         // effective scales of W then R: the first two arrays of the page-locked per-channel block
-        RXMET_CUDA(cudaMemcpyAsync(chan, pinnedChannelBlock(e), 2 * sizeof(float) * C, cudaMemcpyHostToDevice, st));
+        RXMET_CUDA(cudaMemcpyAsync(chan, pinnedChannelBlock(e, st), 2 * sizeof(float) * C, cudaMemcpyHostToDevice, st));
         if (!tensorInputGrad) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(static_cast<size_t>(I) * C, 256), 256, 0, st>>>(call.W_q, static_cast<size_t>(I) * C, C, chan, 0.f, 0, Wf);

@@ -22,6 +22,8 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
+#include <mutex>
 #include <type_traits>
 #include <vector>
 
@@ -32,7 +34,11 @@
 namespace rxmet {
 namespace gru {
 
-const int32_t *pinnedChannelBlock(const Exec &e) {
+// The block is page-locked host memory owned by the Exec, and the Exec lives in a small cache that
+// evicts old entries.  A copy recorded into a CUDA graph reads the block again at every replay, long
+// after the call returned, so a block handed out while the stream is being captured is kept for the
+// life of the process (one block per captured parameter set; a few tens of KB each).
+const int32_t *pinnedChannelBlock(const Exec &e, cudaStream_t st) {
     std::call_once(e.pinnedOnce, [&] {
         const size_t C = 3 * static_cast<size_t>(e.hidden);
         int32_t *host = nullptr;
@@ -43,6 +49,13 @@ const int32_t *pinnedChannelBlock(const Exec &e) {
         putF(0, e.chan.eff_W); putF(1, e.chan.eff_R); putF(2, e.chan.eff_bw); putF(3, e.chan.eff_br);
         putR(4, e.chan.gemm_x); putR(6, e.chan.bias_x); putR(8, e.chan.gemm_h); putR(10, e.chan.bias_h);
     });
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &capture) == cudaSuccess && capture != cudaStreamCaptureStatusNone) {
+        static std::mutex mutex;
+        static std::vector<std::shared_ptr<int32_t>> captured;
+        std::lock_guard<std::mutex> lock(mutex);
+        if (std::find(captured.begin(), captured.end(), e.pinnedChannels) == captured.end()) captured.push_back(e.pinnedChannels);
+    }
     return e.pinnedChannels.get();
 }
 
@@ -819,7 +832,7 @@ struct ChannelDevice {
 ChannelDevice uploadChannels(const Exec &e, Workspace &ws, cudaStream_t st) {
     const size_t C = 3 * static_cast<size_t>(e.hidden);
     auto *block = ws.take<int32_t>(12 * C);
-    RXMET_CUDA(cudaMemcpyAsync(block, pinnedChannelBlock(e), 12 * C * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    RXMET_CUDA(cudaMemcpyAsync(block, pinnedChannelBlock(e, st), 12 * C * sizeof(int32_t), cudaMemcpyHostToDevice, st));
     ChannelDevice d;
     d.effW = reinterpret_cast<const float *>(block);
     d.effR = d.effW + C; d.effBw = d.effW + 2 * C; d.effBr = d.effW + 3 * C;
@@ -1021,9 +1034,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                 KernelTimer timer__("inputLinear", st);
 #define RXMET_IL_CASE(N)                                                                                                   \
     case N: {                                                                                                              \
-        static int perSmFor[17] = {};  /* resident CTAs per SM by block size / 32, asked once */                          \
-        int &perSm = perSmFor[block / 32];                                                                                 \
-        if (perSm == 0) RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, inputLinearI8<N>, block, 0));     \
+        const int perSm = residentPerSm(reinterpret_cast<const void *>(inputLinearI8<N>), block, 0);                       \
         const int grid = std::max(1, std::min(blocks, sms * std::max(1, perSm)));                                          \
         inputLinearI8<N><<<grid, block, 0, st>>>(reinterpret_cast<const int32_t *>(xCodes), static_cast<int>(rows), iWords, C, \
                                                  reinterpret_cast<const int32_t *>(wCodes), compX, biasX, ch.gemmX, zp, qlo, qhi, \

@@ -31,7 +31,7 @@ struct ForwardQuantCall {
 // Page-locked host copy of the per-channel block of `exec`, 12 arrays of 3H 32-bit words: effective
 // scales of W, R, bw, br (floats), then the Rescale pairs gemm_x, bias_x, gemm_h, bias_h.  Built on
 // first use and owned by `exec`.
-const int32_t *pinnedChannelBlock(const Exec &exec);
+const int32_t *pinnedChannelBlock(const Exec &exec, cudaStream_t stream);
 
 size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H);
 void forwardQuant(const ForwardQuantCall &call, const Exec &exec, void *workspace, size_t workspaceBytes,

@@ -234,11 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
 template <int NP>
 void launchPadded(const Problem &prob, int sms, cudaStream_t st) {
     const size_t smem = sharedBytes(prob.K, NP);
-    static size_t configured = 0;
-    if (configured < smem) {
-        RXMET_CUDA(cudaFuncSetAttribute(inputGradUmma<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = smem;
-    }
+    ensureDynamicSmem(reinterpret_cast<const void *>(inputGradUmma<NP>), smem);  // per device
     const int groups = (prob.rows + 7) / 8;
     const int grid = std::max(1, std::min(sms, groups));
     const int rowsPerCta = (groups + grid - 1) / grid * 8;

@@ -690,7 +690,10 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     // others read real-valued weights rebuilt here.
     const bool tensorPath = call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
                             std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
-    const bool tensorInputGrad = call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I);
+    // 16-byte copies of the caller's weight codes, float4 stores of dx and 8-byte loads of the input mask
+    const bool tensorInputGrad = call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I) &&
+                                 alignedTo(call.grads.input, 16) && alignedTo(call.weightIh, 16) &&
+                                 (call.masks == nullptr || alignedTo(call.masks->input, 8));
     const float *wIh = call.weightIh, *wHh = call.weightHh;
     if (call.quantized) {
         RXMET_REQUIRE(call.weightIhScale && call.weightHhScale, "per-channel weight scales missing");
@@ -822,7 +825,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     }
     // QAT on 8-bit activation grids: x and h_prev are integer codes, which the tensor-core GEMM
     // multiplies exactly; its ones row also yields the bias gradients.
-    if (call.quantized && call.codesFitTensorPath && I % 4 == 0 && H % 4 == 0 && I <= 140 && H <= 140) {
+    if (call.quantized && call.codesFitTensorPath && I % 4 == 0 && H % 4 == 0 && I <= 140 && H <= 140 &&
+        alignedTo(call.x, 16)) {
         const size_t stateBytes = sizeof(float) * static_cast<size_t>(B) * H;
         if (call.h0) RXMET_CUDA(cudaMemcpyAsync(hPrev, call.h0, stateBytes, cudaMemcpyDeviceToDevice, st));
         else RXMET_CUDA(cudaMemsetAsync(hPrev, 0, stateBytes, st));

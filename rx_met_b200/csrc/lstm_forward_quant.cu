@@ -514,9 +514,7 @@ void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, 
         // the staging of a block needs kIhRows * KW threads
         const int blockIh = std::max(block, kIhRows * p.kwIh);
         auto launchIh = [&](auto kernel) {
-            static int perSmFor[17] = {};  // resident CTAs per SM by block size / 32, asked once per kernel
-            int &perSm = perSmFor[blockIh / 32];
-            if (perSm == 0) RXMET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, blockIh, 0));
+            const int perSm = residentPerSm(reinterpret_cast<const void *>(kernel), blockIh, 0);
             const int grid = std::max(1, std::min(blocks, currentDevice().sms * std::max(1, perSm)));
             kernel<<<grid, blockIh, 0, st>>>(a);
         };

@@ -287,11 +287,7 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
 template <int NT>
 void launchTile(const Problem &prob, const Problem *other, int K, int N, int chunkK, int splits, cudaStream_t st) {
     constexpr size_t smem = Geometry<NT>::kSmem;
-    static bool configured = false;
-    if (!configured) {
-        RXMET_CUDA(cudaFuncSetAttribute(weightGradUmma<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = true;
-    }
+    ensureDynamicSmem(reinterpret_cast<const void *>(weightGradUmma<NT>), smem);  // per device
     KernelTimer timer__("weightGradUmma", st);
     weightGradUmma<NT><<<dim3(N / NT, splits, other ? 2 : 1), Geometry<NT>::kThreads, smem, st>>>(
         prob, other ? *other : prob, K, N, chunkK, prob.status);

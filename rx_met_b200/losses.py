@@ -44,7 +44,9 @@ def mse_loss_grad(out: torch.Tensor, target: torch.Tensor, grad: Optional[torch.
     loss = torch.empty((), dtype=torch.float32, device=out.device) if loss is None else loss
     scratch = workspace(out.device) if scratch is None else scratch
     ptr = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
-    cabi.check(_library().rxmet_mse_loss_grad(ptr(out), ptr(target), out.numel(), ptr(grad), ptr(loss), ptr(scratch),
-                                              scratch.numel(), C.c_void_p(torch.cuda.current_stream(out.device).cuda_stream)),
-               "mse_loss_grad")
+    with torch.cuda.device(out.device):  # the launch goes to the tensors' device, whatever device is current
+        cabi.check(_library().rxmet_mse_loss_grad(ptr(out), ptr(target), out.numel(), ptr(grad), ptr(loss), ptr(scratch),
+                                                  scratch.numel(),
+                                                  C.c_void_p(torch.cuda.current_stream(out.device).cuda_stream)),
+                   "mse_loss_grad")
     return loss, grad

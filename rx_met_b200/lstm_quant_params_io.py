@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import json
 import math
-import re
 import struct
 import warnings
 from copy import deepcopy
@@ -84,26 +83,39 @@ def _one_or_all(values: List[Any]) -> Any:
     return values[0] if len(values) == 1 else values
 
 
+_DTYPE_ERROR = "Encoding dtype must be an INTn or UINTn string"
+_MAX_BITS = {"INT": 32, "UINT": 31}
+
+
 def parse_dtype(dtype: Any, *, symmetric: Optional[bool] = None) -> Tuple[int, bool]:
-    """"INT8" -> (8, False), "UINT4" -> (4, True); lstm_aimet.py:51-63."""
-    match = re.fullmatch(r"(U?INT)([1-9][0-9]*)", dtype) if isinstance(dtype, str) else None
-    if match is None:
-        raise ValueError("Encoding dtype must be an INTn or UINTn string")
-    bitwidth, unsigned = int(match.group(2)), match.group(1) == "UINT"
-    if not 1 <= bitwidth <= (31 if unsigned else 32):
+    """"INT8" -> (8, False), "UINT4" -> (4, True).  Same acceptance rules and messages as the reference's
+    parser (lstm_aimet.py:51-63): widths 1..32 signed, 1..31 unsigned, no leading zeros, and no signed symmetric
+    one-bit grid (its largest code would be 0)."""
+    if not isinstance(dtype, str):
+        raise ValueError(_DTYPE_ERROR)
+    for family in ("UINT", "INT"):
+        digits = dtype[len(family):]
+        if dtype.startswith(family) and digits.isascii() and digits.isdigit() and digits[0] != "0":
+            break
+    else:
+        raise ValueError(_DTYPE_ERROR)
+    bitwidth = int(digits)
+    if bitwidth < 1 or bitwidth > _MAX_BITS[family]:
         raise ValueError("Encoding bitwidth must be INT1..INT32 or UINT1..UINT31")
-    if not unsigned and bitwidth == 1 and symmetric is True:
+    if family == "INT" and bitwidth == 1 and symmetric is True:
         raise ValueError("signed symmetric INT1 has qmax=0 and is unsupported")
-    return bitwidth, unsigned
+    return bitwidth, family == "UINT"
 
 
 def encoding_exponent(scale: Any) -> Any:
-    """lstm_aimet.py:66-73."""
+    """n with scale ~ 2^-n for one scale or, element by element, for a non-empty list of them
+    (lstm_aimet.py:66-73); anything but a positive finite number is rejected."""
     if isinstance(scale, list):
-        if not scale:
+        if len(scale) == 0:
             raise ValueError("Encoding scale cannot be empty")
-        return [encoding_exponent(v) for v in scale]
-    if isinstance(scale, bool) or not isinstance(scale, (int, float)) or not math.isfinite(scale) or scale <= 0:
+        return list(map(encoding_exponent, scale))
+    is_number = isinstance(scale, (int, float)) and not isinstance(scale, bool)
+    if not (is_number and math.isfinite(scale) and scale > 0):
         raise ValueError("Encoding scale must be positive and finite")
     return int(round(-math.log2(scale)))
 

@@ -89,10 +89,11 @@ class GruQatStep:
         c_ranges, keep = ranges._to_c()
         half = self.stats.numel() // 2
         for x in batches:
-            cabi.check(self.lib.rxmet_gru_forward_calibrate_stats(
-                self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
-                _p(self.h), _p(self.v), _p(self.stats), _p(self.ws), C.c_size_t(self.ws.numel()), self._stream()),
-                "forward_calibrate_stats")
+            with torch.cuda.device(self.device):
+                cabi.check(self.lib.rxmet_gru_forward_calibrate_stats(
+                    self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+                    _p(self.h), _p(self.v), _p(self.stats), _p(self.ws), C.c_size_t(self.ws.numel()), self._stream()),
+                    "forward_calibrate_stats")
             if self.group is not None:
                 torch.distributed.all_reduce(self.stats[:half], op=torch.distributed.ReduceOp.MIN, group=self.group)
                 torch.distributed.all_reduce(self.stats[half:], op=torch.distributed.ReduceOp.MAX, group=self.group)
@@ -113,20 +114,22 @@ class GruQatStep:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Quantized training forward; returns the output sequence h[1:] (a view)."""
-        cabi.check(self.lib.rxmet_gru_forward_quant(
-            1, self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
-            C.byref(self._c_params), _p(self.h), _p(self.v), _p(self.W_q), _p(self.R_q), _p(self.bw_q),
-            _p(self.br_q), _p(self.x_q), None, None, C.byref(self.mask_struct), _p(self.ws),
-            C.c_size_t(self.ws.numel()), self._stream()), "forward_quant")
+        with torch.cuda.device(self.device):
+            cabi.check(self.lib.rxmet_gru_forward_quant(
+                1, self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+                C.byref(self._c_params), _p(self.h), _p(self.v), _p(self.W_q), _p(self.R_q), _p(self.bw_q),
+                _p(self.br_q), _p(self.x_q), None, None, C.byref(self.mask_struct), _p(self.ws),
+                C.c_size_t(self.ws.numel()), self._stream()), "forward_quant")
         return self.h[1:]
 
     def backward(self) -> None:
         """BPTT from self.dh_new ([T+1,B,H], row 0 unused) into the flat gradient buffer."""
-        cabi.check(self.lib.rxmet_gru_backward_quant(
-            self.T, self.B, self.I, self.H, _p(self.W_q), _p(self.R_q), _p(self.bw_q), _p(self.br_q), _p(self.x_q),
-            _p(self.dh_new), _p(self.h), _p(self.v), C.byref(self._c_params), C.byref(self.mask_struct),
-            _p(self.dx), _p(self.dW), _p(self.dR), _p(self.dbw), _p(self.dbr), _p(self.dh0), _p(self.ws),
-            C.c_size_t(self.ws.numel()), self._stream()), "backward_quant")
+        with torch.cuda.device(self.device):
+            cabi.check(self.lib.rxmet_gru_backward_quant(
+                self.T, self.B, self.I, self.H, _p(self.W_q), _p(self.R_q), _p(self.bw_q), _p(self.br_q), _p(self.x_q),
+                _p(self.dh_new), _p(self.h), _p(self.v), C.byref(self._c_params), C.byref(self.mask_struct),
+                _p(self.dx), _p(self.dW), _p(self.dR), _p(self.dbw), _p(self.dbr), _p(self.dh0), _p(self.ws),
+                C.c_size_t(self.ws.numel()), self._stream()), "backward_quant")
 
     def mse_loss(self, target: torch.Tensor) -> torch.Tensor:
         """Mean-squared error of the output sequence against `target` ([T,B,H] float32, contiguous) and its gradient
@@ -134,8 +137,9 @@ class GruQatStep:
         if target.dtype != torch.float32 or not target.is_contiguous() or tuple(target.shape) != (self.T, self.B, self.H):
             raise ValueError("target must be a contiguous float32 tensor of shape [T, B, H]")
         out, grad = self.h[1:], self.dh_new[1:]
-        cabi.check(self.lib.rxmet_mse_loss_grad(_p(out), _p(target), out.numel(), _p(grad), _p(self.loss), _p(self.loss_ws),
-                                                self.loss_ws.numel(), self._stream()), "mse_loss_grad")
+        with torch.cuda.device(self.device):
+            cabi.check(self.lib.rxmet_mse_loss_grad(_p(out), _p(target), out.numel(), _p(grad), _p(self.loss),
+                                                    _p(self.loss_ws), self.loss_ws.numel(), self._stream()), "mse_loss_grad")
         return self.loss
 
     def step(self, x: torch.Tensor, target: torch.Tensor, lr: float) -> torch.Tensor:

@@ -173,7 +173,7 @@ def qat_round_trip(T, B, I, H, seed, cfg, batch_first):
 
 
 def test_quantized_forward_bench_shape_round_trip_and_qat_backward():
-    """BASELINE shape (tensor-core backward, two batch rows per CTA)."""
+    """I=40, H=128, B=256: the shape of the QAT throughput measurement (tensor-core backward, two batch rows per CTA)."""
     qat_round_trip(20, 256, 40, 128, 77, L.default_config(symmetric_activations=True), batch_first=True)
 
 
