@@ -272,6 +272,42 @@ RXMET_API int rxmet_histogram_calibrate(const rxmet_histogram *hist, int bits, i
                                         int use_percentile, float percentile, float *scale, float *range_min,
                                         float *range_max);
 
+/* ---- data-parallel calibration --------------------------------------------- */
+
+/* A batch sharded over ranks must give the collectors what one process would see on the
+ * concatenated batch (the collectors' range growth and binning are defined per batch,
+ * operators/quant-gru/include/histogram_collector.h:185-292).  That takes two exchanges inside
+ * one calibration batch: the finite extremes (MIN / MAX) before anything is binned, so that every
+ * rank bins on the same range, and the bin counts (SUM) before they are committed.  The library
+ * calls the hook below for each exchange; the hook reduces `count` elements at `data_dev` across
+ * the ranks IN PLACE, ordered on `stream`, and returns 0 (NCCL all-reduce in the Python layer).
+ * world_size scales what every rank observes identically (element totals). */
+enum { RXMET_REDUCE_MIN_F32 = 0, RXMET_REDUCE_MAX_F32 = 1, RXMET_REDUCE_SUM_U32 = 2, RXMET_REDUCE_SUM_U64 = 3 };
+typedef int (*rxmet_reduce_fn)(int kind, void *data_dev, uint64_t count, void *stream, void *user);
+typedef struct rxmet_exchange {
+    rxmet_reduce_fn reduce;
+    void *user;
+    int32_t world_size;
+} rxmet_exchange;
+
+/* The same three steps for one collector with the data on the host (the exchange is the
+ * caller's): plan from the batch's global extremes, count this rank's elements into
+ * counts[num_bins] (added to what is there), commit the summed counts with the global element
+ * total.  plan + count + commit on one rank equals rxmet_histogram_collect_host. */
+typedef struct rxmet_histogram_plan {
+    int32_t mode; /* 0 first batch, 1 range unchanged, 2 range extended */
+    float lo, hi, inv_bin_width;
+    float new_min, new_max;
+    float data_min, data_max;
+    float limit_min, limit_max;
+} rxmet_histogram_plan;
+RXMET_API int rxmet_histogram_plan_batch(const rxmet_histogram *hist, float batch_min, float batch_max,
+                                         rxmet_histogram_plan *plan);
+RXMET_API int rxmet_histogram_count_host(const rxmet_histogram_plan *plan, int num_bins, const float *data_host,
+                                         uint64_t count, uint32_t *counts);
+RXMET_API int rxmet_histogram_commit_counts(rxmet_histogram *hist, const rxmet_histogram_plan *plan,
+                                            const uint32_t *counts, uint64_t total_elements);
+
 /* All collectors of one GRU direction (GRUHistogramCollectors,
  * histogram_collector.h:609-720): one per activation point (the W, R, bw, br
  * entries of `point` are the per-tensor collectors), 3*hidden per-channel
@@ -293,6 +329,16 @@ RXMET_API int rxmet_gru_forward_calibrate_hist(int T, int B, int I, int H, const
                                                const float *h0_dev, float *h_dev, float *v_dev,
                                                const rxmet_gru_quant_config *config, rxmet_gru_histograms *hists,
                                                void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* The same with the batch sharded over ranks (exchange != NULL): statistics and bin counts of
+ * the 13 activation points are reduced through the hook; weights and biases are identical on
+ * every rank and are observed locally. */
+RXMET_API int rxmet_gru_forward_calibrate_hist_dp(int T, int B, int I, int H, const float *W_dev, const float *R_dev,
+                                                  const float *bw_dev, const float *br_dev, const float *x_dev,
+                                                  const float *h0_dev, float *h_dev, float *v_dev,
+                                                  const rxmet_gru_quant_config *config, rxmet_gru_histograms *hists,
+                                                  void *workspace_dev, size_t workspace_bytes, void *stream,
+                                                  const rxmet_exchange *exchange);
 
 /* Histograms -> encodings (calculateGRUQuantitativeParametersFromHistograms,
  * operators/quant-gru/src/gru_host.cc:254-335).  The four scale arrays of *params

@@ -299,6 +299,29 @@ RXMET_API int rxmet_lstm_forward_calibrate_hist(int T, int B, int I, int H, cons
                                                 rxmet_lstm_histograms *hists, void *workspace, size_t workspace_bytes,
                                                 void *stream);
 
+/* The same with the batch sharded over ranks (see rxmet_exchange in rxmet_b200.h): the range
+ * statistics, the finite extremes and counts of every observed tensor and the bin counts are
+ * reduced through the hook, so that every rank merges the batch histogram one process would build
+ * on the concatenated batch (per-batch collection: histogram.cc:145-193).  exchange == NULL is
+ * rxmet_lstm_forward_calibrate_hist. */
+RXMET_API int rxmet_lstm_forward_calibrate_hist_dp(int T, int B, int I, int H, const float *weight_ih,
+                                                   const float *weight_hh, const float *bias_ih, const float *bias_hh,
+                                                   const float *x, const float *h0, const float *c0, float *output,
+                                                   float *final_hidden, float *final_cell,
+                                                   const rxmet_lstm_quant_config *config, rxmet_lstm_ranges *ranges,
+                                                   rxmet_lstm_histograms *hists, void *workspace, size_t workspace_bytes,
+                                                   void *stream, const rxmet_exchange *exchange);
+
+/* One collector, data on the host, exchange by the caller: the range a batch with the given
+ * global finite extremes is binned over, this rank's counts over it (added to counts[num_bins]
+ * and *finite), and the merge of the summed counts (HistogramCollector::collect split in three,
+ * histogram.cc:129-161). */
+RXMET_API int rxmet_lstm_histogram_batch_range(float batch_min, float batch_max, float *range_min, float *range_max);
+RXMET_API int rxmet_lstm_histogram_count_host(float range_min, float range_max, int num_bins, const float *data_host,
+                                              uint64_t count, uint64_t *counts, uint64_t *finite);
+RXMET_API int rxmet_lstm_histogram_merge_counts(rxmet_lstm_histogram *hist, const uint64_t *counts, float range_min,
+                                                float range_max, uint64_t finite);
+
 /* Ranges + histograms -> parameters (LstmCalibrationSession::finalize with
  * method sqnr / percentile, calibration.cc:312-346): every non-bias group takes
  * the range calibrateHistogramRange selects, biases keep their observed range. */

@@ -70,6 +70,7 @@ typedef struct {
     const rxmet_lstm_quant_params *p;
     rxmet_lstm_execution e;
     int32_t lo[RXMET_LSTM_NUM_OPS], hi[RXMET_LSTM_NUM_OPS];
+    int exact_sums; /* 1: the two linear stages add up exactly in integers and round to float once */
 } ctx_t;
 
 static int ctx_init(ctx_t *c, const rxmet_lstm_quant_params *p) {
@@ -109,8 +110,19 @@ static void stage_linear(const ctx_t *c, int hh, long rows, const float *q_in, c
         for (int ch = 0; ch < C; ++ch) {
             const float *w = q_w + (size_t)ch * K;
             float acc = 0.0f;
-            for (int k = 0; k < K; ++k) acc += center(w[k], 0) * center(v[k], zin);
-            if (q_b) acc += apply_rescale(center(q_b[ch], 0), b2a[ch]);
+            if (c->exact_sums) {
+                /* The same sum without the intermediate float roundings: what the reference's float
+                 * accumulation yields whenever every partial sum stays below 2^24 (its
+                 * exact_integer_range class), and the correctly rounded sum beyond that.  This is the
+                 * arithmetic of the CUDA library's linear stages. */
+                int64_t total = 0;
+                for (int k = 0; k < K; ++k) total += (int64_t)w[k] * ((int64_t)v[k] - zin);
+                if (q_b) total += (int64_t)apply_rescale(center(q_b[ch], 0), b2a[ch]);
+                acc = (float)total;
+            } else {
+                for (int k = 0; k < K; ++k) acc += center(w[k], 0) * center(v[k], zin);
+                if (q_b) acc += apply_rescale(center(q_b[ch], 0), b2a[ch]);
+            }
             uint8_t m;
             lin[r * C + ch] = clamp_carrier((double)apply_rescale(acc, a2o[ch]) + zout, c->lo[out_op], c->hi[out_op], &m);
             if (mask) mask[r * C + ch] = m;
@@ -283,13 +295,14 @@ int orc_lstm_stage(const rxmet_lstm_quant_params *p, int stage, long long rows, 
 
 /* ---- exported: whole q-carrier forward ---------------------------------------- */
 
-int orc_lstm_forward_quantized_masked(const rxmet_lstm_quant_params *p, int T, int B, const float *q_w_ih,
-                                      const float *q_w_hh, const float *q_b_ih, const float *q_b_hh, const float *q_x,
-                                      const float *q_h0, const float *q_c0, float *out, float *hn, float *cn,
-                                      const rxmet_lstm_trace *tr) {
+static int forward_quantized_masked(const rxmet_lstm_quant_params *p, int exact_sums, int T, int B, const float *q_w_ih,
+                                    const float *q_w_hh, const float *q_b_ih, const float *q_b_hh, const float *q_x,
+                                    const float *q_h0, const float *q_c0, float *out, float *hn, float *cn,
+                                    const rxmet_lstm_trace *tr) {
     /* forward_quantized_fp_cpu.cc:70-198 */
     ctx_t c;
     if (ctx_init(&c, p) != 0) return -1;
+    c.exact_sums = exact_sums;
     const int I = p->input_size, H = p->hidden_size, C = 4 * H;
     const size_t BH = (size_t)B * H, BC = (size_t)B * C;
     float *h = malloc(BH * sizeof(float)), *cell = malloc(BH * sizeof(float));
@@ -335,6 +348,21 @@ int orc_lstm_forward_quantized_masked(const rxmet_lstm_quant_params *p, int T, i
     free(h); free(cell); free(ih); free(hh); free(gi); free(go); free(ct); free(cnew); free(hnew);
     ctx_free(&c);
     return 0;
+}
+
+int orc_lstm_forward_quantized_masked(const rxmet_lstm_quant_params *p, int T, int B, const float *q_w_ih,
+                                      const float *q_w_hh, const float *q_b_ih, const float *q_b_hh, const float *q_x,
+                                      const float *q_h0, const float *q_c0, float *out, float *hn, float *cn,
+                                      const rxmet_lstm_trace *tr) {
+    return forward_quantized_masked(p, 0, T, B, q_w_ih, q_w_hh, q_b_ih, q_b_hh, q_x, q_h0, q_c0, out, hn, cn, tr);
+}
+
+/* The q-carrier forward with exactly accumulated linear stages (see stage_linear). */
+int orc_lstm_forward_quantized_exact_sums(const rxmet_lstm_quant_params *p, int T, int B, const float *q_w_ih,
+                                          const float *q_w_hh, const float *q_b_ih, const float *q_b_hh,
+                                          const float *q_x, const float *q_h0, const float *q_c0, float *out,
+                                          float *hn, float *cn, const rxmet_lstm_trace *tr) {
+    return forward_quantized_masked(p, 1, T, B, q_w_ih, q_w_hh, q_b_ih, q_b_hh, q_x, q_h0, q_c0, out, hn, cn, tr);
 }
 
 /* Same argument list as the reference shim's entry point. */

@@ -380,6 +380,41 @@ int ref_lstm_forward_quantized(const rxmet_lstm_quant_params *params, int exact,
     });
 }
 
+// The reference's exact integer forward (lstmForwardInt32CpuReference, operators/quant-lstm/src/lstm/
+// forward_int32_cpu.cc:73) on the same q-carrier inputs: codes cross the shim as floats (they are
+// integers below 2^24) and are converted to int32 here and back.
+int ref_lstm_forward_int32(const rxmet_lstm_quant_params *params, int T, int B, const float *q_w_ih, const float *q_w_hh,
+                           const float *q_b_ih, const float *q_b_hh, const float *q_x, const float *q_h0,
+                           const float *q_c0, float *out, float *hn, float *cn, float *ih_lin, float *hh_lin,
+                           float *gate_in, float *gate_out, float *cell, float *cell_tanh, float *hidden) {
+    return guarded([&] {
+        const auto cfg = toConfig(params->config);
+        const auto qp = toParams(*params, cfg);
+        const auto e = ql::deriveLstmExecutionParams(cfg, qp, params->input_size, false);
+        const std::size_t I = params->input_size, H = params->hidden_size, C = 4 * H;
+        auto ints = [](const float *src, std::size_t n) {
+            std::vector<std::int32_t> v(src ? n : 0);
+            for (std::size_t i = 0; i < v.size(); ++i) v[i] = static_cast<std::int32_t>(src[i]);
+            return v;
+        };
+        const auto wih = ints(q_w_ih, C * I), whh = ints(q_w_hh, C * H), bih = ints(q_b_ih, C), bhh = ints(q_b_hh, C);
+        const auto x = ints(q_x, static_cast<std::size_t>(T) * B * I), h0 = ints(q_h0, B * H), c0 = ints(q_c0, B * H);
+        std::vector<std::int32_t> o(static_cast<std::size_t>(T) * B * H), h(B * H), c(B * H);
+        ql::LstmInt32ReferenceTrace trace;
+        ql::lstmForwardInt32CpuReference({T, B, params->input_size, params->hidden_size},
+                                         {wih.data(), whh.data(), q_b_ih ? bih.data() : nullptr, q_b_hh ? bhh.data() : nullptr},
+                                         x.data(), q_h0 ? h0.data() : nullptr, q_c0 ? c0.data() : nullptr, cfg, qp, e, o.data(),
+                                         h.data(), c.data(), &trace);
+        auto put = [](float *dst, const std::vector<std::int32_t> &src) {
+            if (dst) for (std::size_t i = 0; i < src.size(); ++i) dst[i] = static_cast<float>(src[i]);
+        };
+        put(out, o); put(hn, h); put(cn, c);
+        put(ih_lin, trace.weight_ih_linear); put(hh_lin, trace.weight_hh_linear);
+        put(gate_in, trace.gate_inputs); put(gate_out, trace.gate_outputs);
+        put(cell, trace.cell_states); put(cell_tanh, trace.cell_tanh_outputs); put(hidden, trace.hidden_outputs);
+    });
+}
+
 // MinMax calibration session over `batches` equally shaped batches; returns the ranges it observed
 // and the parameters it finalizes.
 int ref_lstm_calibrate_minmax(const rxmet_lstm_quant_config *config, int batches, int T, int B, int I, int H,

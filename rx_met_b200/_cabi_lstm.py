@@ -207,3 +207,16 @@ def default_config(scale_mode=SCALE_AFFINE, bits=8, symmetric_activations=False,
         cfg.is_symmetric[op] = 1 if (op in PARAMETER_OPS or symmetric_activations) else 0
         cfg.granularity[op] = parameter_granularity if op in PARAMETER_OPS else PER_TENSOR
     return cfg
+
+
+def mixed_config(weight_bits=8, activation_bits=16, bias_bits=None, scale_mode=SCALE_AFFINE, symmetric_activations=False,
+                 parameter_granularity=PER_CHANNEL) -> QuantConfig:
+    """Mixed-precision grid: `weight_bits` for weight_ih / weight_hh (W4, W8), `activation_bits` for every
+    activation point (input, output, cell state, the two linear outputs, gate inputs and outputs, tanh(cell));
+    biases take `bias_bits` (default: the activation width)."""
+    cfg = default_config(scale_mode=scale_mode, bits=activation_bits, symmetric_activations=symmetric_activations,
+                         parameter_granularity=parameter_granularity)
+    cfg.bitwidth[WEIGHT_IH] = cfg.bitwidth[WEIGHT_HH] = weight_bits
+    cfg.bitwidth[BIAS_IH] = cfg.bitwidth[BIAS_HH] = activation_bits if bias_bits is None else bias_bits
+    return cfg
+

@@ -553,6 +553,20 @@ class CalibrationSession:
     def batch_count(self) -> int:
         return self._batches
 
+    # Data-parallel calibration (no counterpart in the reference's session): with `process_group` set, every
+    # rank passes its shard of each batch to collect(); extremes and bin counts are all-reduced inside the batch,
+    # so all ranks finalize the parameters one process would derive from the concatenated batches.
+    process_group = None
+
+    def _exchange_for(self, device):
+        if self.process_group is None:
+            return None
+        key = (id(self.process_group), str(device))
+        if getattr(self, "_exchange_key", None) != key:
+            from .data_parallel import make_exchange
+            self._exchange, self._exchange_key = make_exchange(self.process_group, device), key
+        return self._exchange
+
     def collect(self, input, weight_ih, weight_hh, bias_ih=None, bias_hh=None, initial_hidden=None,
                 initial_cell=None, batch_first=False):
         if self._state == "locked":
@@ -567,15 +581,22 @@ class CalibrationSession:
             T, B, I, H = p.dims()
             out, hn, cn = p.empty(T, B, H), p.empty(1, B, H), p.empty(1, B, H)
             ws, n = _workspace(3, T, B, I, H, p.device)
+            exchange = self._exchange_for(p.device)
             with torch.cuda.device(p.device):
-                rc = lib.rxmet_lstm_forward_calibrate_hist(
+                rc = lib.rxmet_lstm_forward_calibrate_hist_dp(
                     T, B, I, H, _ptr(p.w_ih), _ptr(p.w_hh), _ptr(p.b_ih), _ptr(p.b_hh), _ptr(p.x), _ptr(p.h0), _ptr(p.c0),
                     _ptr(out), _ptr(hn), _ptr(cn), C.byref(self._config), C.byref(self._ranges.struct),
-                    C.byref(self._hists.struct), _ptr(ws), C.c_size_t(n), _stream())
+                    C.byref(self._hists.struct), _ptr(ws), C.c_size_t(n), _stream(),
+                    C.byref(exchange) if exchange is not None else None)
             _check(rc, RuntimeError)
         else:
             stats = torch.empty(lib.rxmet_lstm_stats_floats(p.H), dtype=torch.float32, device=p.device)
             out, hn, cn = _run_float(p, None, stats)
+            if self.process_group is not None:  # every rank folds the extremes of the whole batch
+                import torch.distributed as dist
+                half = stats.numel() // 2
+                dist.all_reduce(stats[:half], op=dist.ReduceOp.MIN, group=self.process_group)
+                dist.all_reduce(stats[half:], op=dist.ReduceOp.MAX, group=self.process_group)
             host = stats.cpu().numpy()
             _check(lib.rxmet_lstm_ranges_fold_stats(C.byref(self._ranges.struct),
                                                     host.ctypes.data_as(C.POINTER(C.c_float)), p.H, int(self._bias)),

@@ -87,7 +87,7 @@ struct Pending {
 // Bins every job on the device and commits the counts on the host.  jobsDev / countsDev are
 // workspace regions for jobs.size() entries; synchronises the stream.
 void runJobs(std::vector<BinJob> &jobs, std::vector<Pending> &pending, int bins, BinJob *jobsDev, uint32_t *countsDev,
-             cudaStream_t st) {
+             cudaStream_t st, const rxmet_exchange *exchange = nullptr) {
     if (jobs.empty()) return;
     RXMET_REQUIRE(bins <= kMaxSharedBins, "histograms of up to %d bins are built (got %d)", kMaxSharedBins, bins);
     const size_t n = jobs.size();
@@ -101,6 +101,8 @@ void runJobs(std::vector<BinJob> &jobs, std::vector<Pending> &pending, int bins,
         rangeHistogram<<<dim3(gridFor(largest, 256 * 8), static_cast<unsigned>(n)), 256, bins * sizeof(uint32_t), st>>>(jobsDev, bins);
     }
     afterLaunch("rangeHistogram");
+    if (exchange && exchange->reduce(RXMET_REDUCE_SUM_U32, countsDev, n * bins, st, exchange->user) != 0)
+        fail(RXMET_ERR_INVALID_ARGUMENT, "the exchange hook reported a failure (bin counts)");
     std::vector<uint32_t> host(n * bins);
     RXMET_CUDA(cudaMemcpyAsync(host.data(), countsDev, host.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
     RXMET_CUDA(cudaStreamSynchronize(st));
@@ -146,7 +148,10 @@ void observeParameter(const std::vector<float> &values, int rows, int hidden, rx
 
 void forwardCalibrateHist(int T, int B, int I, int H, const float *W, const float *R, const float *bw, const float *br,
                           const float *x, const float *h0, float *h, float *v, const rxmet_gru_quant_config &cfg,
-                          rxmet_gru_histograms *hs, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+                          rxmet_gru_histograms *hs, void *workspace, size_t workspaceBytes, cudaStream_t st,
+                          const rxmet_exchange *exchange) {
+    const unsigned long long world = exchange ? static_cast<unsigned long long>(std::max(exchange->world_size, 1)) : 1ull;
+    if (exchange) RXMET_REQUIRE(exchange->reduce != nullptr, "exchange without a reduce function");
     RXMET_REQUIRE(hs->hidden == H, "histogram collectors were made for hidden=%d, call has H=%d", hs->hidden, H);
     const int bins = hs->num_bins;
     for (int op = 0; op < kOps; ++op) {
@@ -169,6 +174,12 @@ void forwardCalibrateHist(int T, int B, int I, int H, const float *W, const floa
     call.stats = stats;
     call.traceWx = wx; call.traceRh = rh; call.tracePre = pre; call.traceMul = mul;
     forwardFloat(call, fwdWs, fwdBytes, st);
+    if (exchange) {  // every rank bins on the extremes of the whole batch
+        const size_t halfDev = statsFloats(H) / 2;
+        if (exchange->reduce(RXMET_REDUCE_MIN_F32, stats, halfDev, st, exchange->user) != 0 ||
+            exchange->reduce(RXMET_REDUCE_MAX_F32, stats + halfDev, halfDev, st, exchange->user) != 0)
+            fail(RXMET_ERR_INVALID_ARGUMENT, "the exchange hook reported a failure (extremes)");
+    }
     std::vector<float> host(statsFloats(H));
     RXMET_CUDA(cudaMemcpyAsync(host.data(), stats, host.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
     const size_t wCount = static_cast<size_t>(I) * C, rCount = static_cast<size_t>(H) * C;
@@ -206,9 +217,9 @@ void forwardCalibrateHist(int T, int B, int I, int H, const float *W, const floa
         rxmet_histogram *target = &hs->point[s.op];
         const hist::Plan p = hist::plan(*target, lo, hi);
         jobs.push_back({s.data, static_cast<unsigned long long>(rows), s.cols, s.stride, p.lo, p.hi, p.invBinWidth, nullptr});
-        pending.push_back({target, p, static_cast<unsigned long long>(rows) * s.cols});
+        pending.push_back({target, p, world * static_cast<unsigned long long>(rows) * s.cols});
     }
-    hist::runJobs(jobs, pending, bins, jobsDev, countsDev, st);
+    hist::runJobs(jobs, pending, bins, jobsDev, countsDev, st, exchange);
 
     observeParameter(hW, I, H, hs->channel[0], &hs->point[RXMET_GRU_W], hs->gate[0], cfg.W_granularity, false);
     observeParameter(hR, H, H, hs->channel[1], &hs->point[RXMET_GRU_R], hs->gate[1], cfg.R_granularity, false);
@@ -304,7 +315,59 @@ int rxmet_gru_forward_calibrate_hist(int T, int B, int I, int H, const float *W,
         RXMET_REQUIRE(T > 0 && B > 0 && I > 0 && H > 0, "GRU dimensions must be positive");
         RXMET_REQUIRE(W && R && bw && br && x && h && v && config && hists, "null argument");
         gru::forwardCalibrateHist(T, B, I, H, W, R, bw, br, x, h0, h, v, *config, hists, workspace, workspace_bytes,
-                                  static_cast<cudaStream_t>(stream));
+                                  static_cast<cudaStream_t>(stream), nullptr);
+    });
+}
+
+int rxmet_gru_forward_calibrate_hist_dp(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
+                                        const float *br, const float *x, const float *h0, float *h, float *v,
+                                        const rxmet_gru_quant_config *config, rxmet_gru_histograms *hists, void *workspace,
+                                        size_t workspace_bytes, void *stream, const rxmet_exchange *exchange) {
+    return guarded([&] {
+        RXMET_REQUIRE(T > 0 && B > 0 && I > 0 && H > 0, "GRU dimensions must be positive");
+        RXMET_REQUIRE(W && R && bw && br && x && h && v && config && hists, "null argument");
+        gru::forwardCalibrateHist(T, B, I, H, W, R, bw, br, x, h0, h, v, *config, hists, workspace, workspace_bytes,
+                                  static_cast<cudaStream_t>(stream), exchange);
+    });
+}
+
+int rxmet_histogram_plan_batch(const rxmet_histogram *h, float batch_min, float batch_max, rxmet_histogram_plan *out) {
+    return guarded([&] {
+        hist::checkCollector(h);
+        RXMET_REQUIRE(out != nullptr, "plan must not be null");
+        const hist::Plan p = hist::plan(*h, batch_min, batch_max);
+        *out = rxmet_histogram_plan{static_cast<int32_t>(p.mode), p.lo, p.hi, p.invBinWidth, p.newMin, p.newMax,
+                                    p.dataMin, p.dataMax, p.limitMin, p.limitMax};
+    });
+}
+
+namespace {
+hist::Plan fromC(const rxmet_histogram_plan &c) {
+    hist::Plan p;
+    p.mode = static_cast<hist::Plan::Mode>(c.mode);
+    p.lo = c.lo; p.hi = c.hi; p.invBinWidth = c.inv_bin_width;
+    p.newMin = c.new_min; p.newMax = c.new_max;
+    p.dataMin = c.data_min; p.dataMax = c.data_max;
+    p.limitMin = c.limit_min; p.limitMax = c.limit_max;
+    return p;
+}
+}  // namespace
+
+int rxmet_histogram_count_host(const rxmet_histogram_plan *plan, int num_bins, const float *data, uint64_t count,
+                               uint32_t *counts) {
+    return guarded([&] {
+        RXMET_REQUIRE(plan && counts && num_bins > 0 && (data || count == 0), "bad arguments");
+        hist::binHost(data, 1, count, count, fromC(*plan), num_bins, counts);
+    });
+}
+
+int rxmet_histogram_commit_counts(rxmet_histogram *h, const rxmet_histogram_plan *plan, const uint32_t *counts,
+                                  uint64_t total_elements) {
+    return guarded([&] {
+        hist::checkCollector(h);
+        RXMET_REQUIRE(plan && counts, "bad arguments");
+        if (total_elements == 0) return;
+        hist::commit(h, fromC(*plan), counts, total_elements);
     });
 }
 

@@ -253,6 +253,105 @@ __global__ void __launch_bounds__(512) recurrentBackward(const __grid_constant__
     }
 }
 
+// ---- hidden sizes above 128 -------------------------------------------------------------------
+//
+// Thread (j, s) owns hidden unit j for RB batch rows of row group s: the pointwise derivative of its
+// elements, then dh[b][j] = sum_c G_hh[b][c] * weight_hh[c][j] with column j of weight_hh streamed
+// from L2 (coalesced over j) and the CTA's gate gradients read from shared memory as 16-byte
+// broadcasts; dh and dc never leave the thread's registers.
+template <int RB>
+__global__ void __launch_bounds__(512, 1) recurrentBackwardWide(const __grid_constant__ RecurrentArgs a, const int HP) {
+    const int H = a.H, C = 4 * a.H;
+    extern __shared__ __align__(16) float smemF[];
+    float *gS = smemF;  // [BT][C]
+    const int tid = threadIdx.x, j = tid % HP, sg = tid / HP;
+    const int BT = (blockDim.x / HP) * RB;
+    const bool active = j < H;
+    const int b0 = blockIdx.x * BT + sg * RB;
+    for (int i = tid; i < BT * C; i += blockDim.x) gS[i] = 0.0f;
+    float dhCarry[RB], dc[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        const bool valid = active && b0 + r < a.B;
+        const size_t stateIdx = static_cast<size_t>(b0 + r) * H + j;
+        dhCarry[r] = valid ? a.gradFinalHidden[stateIdx] : 0.0f;
+        dc[r] = valid ? a.gradFinalCell[stateIdx] : 0.0f;
+    }
+    __syncthreads();
+    for (int t = a.T - 1; t >= 0; --t) {
+        if (active) {
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const int b = b0 + r;
+                if (b >= a.B) continue;
+                const size_t row = static_cast<size_t>(t) * a.B + b, so = row * H + j, go = row * C + j;
+                const size_t stateIdx = static_cast<size_t>(b) * H + j;
+                const uint32_t bits = a.stepMasks ? a.stepMasks[so] : 0u;
+                auto keepBit = [&](int bit) { return (bits >> bit) & 1u ? 0.0f : 1.0f; };
+                const float ig = realOf(a.gateOutputs[go], a.dqGate[0]);
+                const float fg = realOf(a.gateOutputs[go + static_cast<size_t>(H)], a.dqGate[1]);
+                const float cg = realOf(a.gateOutputs[go + 2 * static_cast<size_t>(H)], a.dqGate[2]);
+                const float og = realOf(a.gateOutputs[go + 3 * static_cast<size_t>(H)], a.dqGate[3]);
+                const float ct = realOf(a.cellTanh[so], a.dqTanh);
+                const float cPrevCode = t > 0 ? a.cellStates[so - static_cast<size_t>(a.B) * H]
+                                              : (a.c0 ? a.c0[stateIdx] : a.dqC.zeroPoint);
+                const float cPrev = realOf(cPrevCode, a.dqC);
+                const float dh = (dhCarry[r] + a.gradOutput[so]) * keepBit(0);
+                const float gOut = dh * ct;
+                const float gTanh = dh * og * keepBit(1);
+                const float dcAll = dc[r] + gTanh * (1.0f - ct * ct);
+                const float mdc = dcAll * keepBit(2);
+                const float go4[4] = {mdc * cg * keepBit(3), mdc * cPrev * keepBit(4), mdc * ig * keepBit(5), gOut * keepBit(6)};
+                const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
+                                      go4[3] * og * (1.0f - og)};
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const size_t o = go + static_cast<size_t>(g) * H;
+                    const float grad = gi4[g] * keepBit(7 + g);
+                    const float hh = grad * keepBit(15 + g);
+                    a.gIh[o] = grad * keepBit(11 + g);
+                    a.gHh[o] = hh;
+                    gS[(sg * RB + r) * C + g * H + j] = hh;
+                }
+                dc[r] = mdc * fg;
+            }
+        }
+        __syncthreads();
+        if (active) {
+            float acc[RB];
+#pragma unroll
+            for (int r = 0; r < RB; ++r) acc[r] = 0.0f;
+            const float *wp = a.weightHh + j;
+            const float *gRows = gS + sg * RB * C;
+            for (int c = 0; c < C; c += 4) {  // C = 4H is a multiple of 4
+                float w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[i] = __ldg(wp + static_cast<size_t>(c + i) * H);
+#pragma unroll
+                for (int r = 0; r < RB; ++r) {
+                    const float4 gv = *reinterpret_cast<const float4 *>(gRows + r * C + c);
+                    acc[r] = fmaf(gv.x, w[0], acc[r]);
+                    acc[r] = fmaf(gv.y, w[1], acc[r]);
+                    acc[r] = fmaf(gv.z, w[2], acc[r]);
+                    acc[r] = fmaf(gv.w, w[3], acc[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RB; ++r) dhCarry[r] = acc[r];
+        }
+        __syncthreads();
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            if (b0 + r >= a.B) continue;
+            const size_t stateIdx = static_cast<size_t>(b0 + r) * H + j;
+            a.dh0[stateIdx] = dhCarry[r] * keepOf(a.mk.initial_hidden, stateIdx);
+            a.dc0[stateIdx] = dc[r] * keepOf(a.mk.initial_cell, stateIdx);
+        }
+    }
+}
+
 // ---- dh = G_hh W_hh on tensor cores (QAT with weight grids of at most 8 bits) ------------------
 //
 // Same data flow as recurrentBackward, but the per-step product runs as mma.sync m16n8k16 with
@@ -667,7 +766,8 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
 
 void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, cudaStream_t st) {
     const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
-    if (C > 512) fail(RXMET_ERR_UNSUPPORTED, "hidden sizes up to 128 are built (got %d)", H);
+    if (H > 512) fail(RXMET_ERR_UNSUPPORTED, "hidden sizes up to 512 are built (got %d)", H);
+    const bool wide = C > 512;
     const size_t rows = static_cast<size_t>(T) * B;
     Workspace ws(workspace, workspaceBytes);
     float *gIh = ws.take<float>(rows * C);
@@ -688,7 +788,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
 
     // Which kernels multiply by the saved integer weight codes directly (QAT on 8-bit grids); the
     // others read real-valued weights rebuilt here.
-    const bool tensorPath = call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
+    const bool tensorPath = !wide && call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
                             std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
     // 16-byte copies of the caller's weight codes, float4 stores of dx and 8-byte loads of the input mask
     const bool tensorInputGrad = call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I) &&
@@ -761,8 +861,28 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
 #undef RXMET_LSTM_MMA
             afterLaunch("lstmRecurrentBackwardMma");
         }
+        if (wide) {
+            const int HP = (H + 31) / 32 * 32;
+            const int groupsMax = std::max(1, 512 / HP);
+            const int want = std::max(1, (B + sms - 1) / sms);
+            int rb = 1;
+            while (rb < 8 && rb * groupsMax < want) rb *= 2;
+            const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));
+            const int btWide = groups * rb;
+            const size_t smem = sizeof(float) * static_cast<size_t>(btWide) * C;
+            auto launchWide = [&](auto kernel) {
+                ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+                KernelTimer timer__("lstmRecurrentBackwardWide", st);
+                kernel<<<(B + btWide - 1) / btWide, groups * HP, smem, st>>>(a, HP);
+            };
+            if (rb == 1) launchWide(recurrentBackwardWide<1>);
+            else if (rb == 2) launchWide(recurrentBackwardWide<2>);
+            else if (rb == 4) launchWide(recurrentBackwardWide<4>);
+            else launchWide(recurrentBackwardWide<8>);
+            afterLaunch("lstmRecurrentBackwardWide");
+        }
         auto launch = [&](auto kernel, int BT) {
-            if (tensorPath) return;
+            if (tensorPath || wide) return;
             const size_t base = sizeof(float) * (static_cast<size_t>(BT) * C + 4 * static_cast<size_t>(BT) * H);
             const size_t room = static_cast<size_t>(smemMax) > base + 1024 ? static_cast<size_t>(smemMax) - base - 1024 : 0;
             // rows per gate block in shared memory; the remaining rows of a block live in registers

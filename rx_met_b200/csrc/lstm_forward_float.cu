@@ -224,6 +224,157 @@ __global__ void __launch_bounds__(512) recurrentFloat(const __grid_constant__ Fl
     }
 }
 
+// ---- hidden sizes above 128 -------------------------------------------------------------------
+//
+// 4H no longer fits the one-thread-per-channel layout above.  Here thread (j, s) owns hidden unit j -
+// all four gates - for RB batch rows of row group s, so the pointwise part needs no exchange between
+// threads: per step one 16-byte load per k brings the four gate weights of (k, j) from L2 (weight_hh
+// interleaved to [k][j][gate] once per call), the hidden state of the CTA's rows is double buffered
+// in shared memory (one barrier per step), the cell state stays in registers.  The sums run in the
+// same order (bias first, k ascending, one fused multiply-add per term) as in recurrentFloat.
+__global__ void interleaveGates(const float *__restrict__ w, int H, float *__restrict__ out) {
+    const size_t n = static_cast<size_t>(4) * H * H;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int g = static_cast<int>(i % 4), j = static_cast<int>((i / 4) % H), k = static_cast<int>(i / (4 * static_cast<size_t>(H)));
+        out[i] = w[(static_cast<size_t>(g) * H + j) * H + k];
+    }
+}
+
+struct FloatWideArgs {
+    FloatRecurrentArgs base;  // wT is unused
+    const float4 *w4;         // [H][H] float4: gates (i, f, g, o) of (k, j)
+    int HP;
+};
+
+template <int RB>
+__global__ void __launch_bounds__(512, 1) recurrentFloatWide(const __grid_constant__ FloatWideArgs wa) {
+    const FloatRecurrentArgs &a = wa.base;
+    const int H = a.H, C = 4 * a.H, HP = wa.HP;
+    extern __shared__ __align__(16) float smemF[];
+    const int tid = threadIdx.x, j = tid % HP, sg = tid / HP;
+    const int BT = (blockDim.x / HP) * RB;
+    const int HS = (H + 3) / 4 * 4;                       // row stride of the state buffers
+    float *hS = smemF;                                    // [2][BT][HS]
+    float *scratch = smemF + 2 * BT * HS;                 // 2 * kRecurrentStats * 16
+    const bool active = j < H;
+    const int ctaRow0 = blockIdx.x * BT, b0 = ctaRow0 + sg * RB;
+    for (int i = tid; i < 2 * BT * HS; i += blockDim.x) hS[i] = 0.0f;
+    __syncthreads();
+    for (int i = tid; i < BT * H; i += blockDim.x) {
+        const int r = i / H, k = i % H, b = ctaRow0 + r;
+        if (b < a.B && a.h0) hS[r * HS + k] = a.h0[static_cast<size_t>(b) * H + k];
+    }
+    float cell[RB], hidden[RB];
+    // order: hh linear, 4 gate inputs, 4 gate outputs, cell, tanh(cell), hidden, f*c, i*g, o*tanh
+    MinMax st[kRecurrentStats];
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        const bool valid = active && b0 + r < a.B;
+        cell[r] = (valid && a.c0) ? a.c0[static_cast<size_t>(b0 + r) * H + j] : 0.0f;
+        hidden[r] = valid ? hS[(sg * RB + r) * HS + j] : 0.0f;
+        if (valid) {
+            st[11].see(hidden[r]);  // the initial states are observed too (zeros when absent)
+            st[9].see(cell[r]);
+        }
+    }
+    float bias[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) bias[g] = (active && a.bias) ? a.bias[g * H + j] : 0.0f;
+
+    for (int t = 0; t < a.T; ++t) {
+        const float *cur = hS + (t & 1) * BT * HS + sg * RB * HS;
+        float *nxt = hS + ((t + 1) & 1) * BT * HS + sg * RB * HS;
+        if (active) {
+            float acc[4][RB];
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+#pragma unroll
+                for (int r = 0; r < RB; ++r) acc[g][r] = bias[g];
+            const float4 *wp = wa.w4 + j;
+            int k = 0;
+            for (; k + 4 <= H; k += 4) {
+                float4 w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[i] = __ldg(wp + static_cast<size_t>(k + i) * H);
+#pragma unroll
+                for (int r = 0; r < RB; ++r) {
+                    const float4 hv = *reinterpret_cast<const float4 *>(cur + r * HS + k);
+                    const float hk[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[0][r] = fmaf(hk[i], w[i].x, acc[0][r]);
+                        acc[1][r] = fmaf(hk[i], w[i].y, acc[1][r]);
+                        acc[2][r] = fmaf(hk[i], w[i].z, acc[2][r]);
+                        acc[3][r] = fmaf(hk[i], w[i].w, acc[3][r]);
+                    }
+                }
+            }
+            for (; k < H; ++k) {
+                const float4 w = __ldg(wp + static_cast<size_t>(k) * H);
+#pragma unroll
+                for (int r = 0; r < RB; ++r) {
+                    const float hk = cur[r * HS + k];
+                    acc[0][r] = fmaf(hk, w.x, acc[0][r]);
+                    acc[1][r] = fmaf(hk, w.y, acc[1][r]);
+                    acc[2][r] = fmaf(hk, w.z, acc[2][r]);
+                    acc[3][r] = fmaf(hk, w.w, acc[3][r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const int b = b0 + r;
+                if (b >= a.B) continue;
+                const size_t row = static_cast<size_t>(t) * a.B + b;
+                const float *ih = a.ih + row * C + j;
+                float pre[4], act[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    st[0].see(acc[g][r]);
+                    if (a.tr.weight_hh_linear) a.tr.weight_hh_linear[row * C + g * H + j] = acc[g][r];
+                    pre[g] = ih[g * H] + acc[g][r];
+                    act[g] = g == 2 ? tanhf(pre[g]) : sigmoidStable(pre[g]);
+                    st[1 + g].see(pre[g]);
+                    st[5 + g].see(act[g]);
+                    if (a.tr.gate_inputs) a.tr.gate_inputs[row * C + g * H + j] = pre[g];
+                    if (a.tr.gate_outputs) a.tr.gate_outputs[row * C + g * H + j] = act[g];
+                }
+                const float keepOld = act[1] * cell[r], writeNew = act[0] * act[2];
+                cell[r] = keepOld + writeNew;
+                const float ct = tanhf(cell[r]);
+                hidden[r] = act[3] * ct;
+                st[9].see(cell[r]); st[10].see(ct); st[11].see(hidden[r]);
+                st[12].see(keepOld); st[13].see(writeNew); st[14].see(hidden[r]);
+                const size_t so = row * H + j;
+                a.output[so] = hidden[r];
+                if (a.tr.cell_states) a.tr.cell_states[so] = cell[r];
+                if (a.tr.cell_tanh_outputs) a.tr.cell_tanh_outputs[so] = ct;
+                if (a.tr.hidden_outputs) a.tr.hidden_outputs[so] = hidden[r];
+                nxt[r * HS + j] = hidden[r];
+            }
+        }
+        __syncthreads();
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            if (b0 + r >= a.B) continue;
+            const size_t o = static_cast<size_t>(b0 + r) * H + j;
+            a.finalHidden[o] = hidden[r];
+            a.finalCell[o] = cell[r];
+        }
+    }
+    if (a.mins) {
+        const int slots[kRecurrentStats] = {
+            RXMET_LSTM_WEIGHT_HH_LINEAR, RXMET_LSTM_INPUT_GATE_INPUT, RXMET_LSTM_FORGET_GATE_INPUT,
+            RXMET_LSTM_CELL_GATE_INPUT, RXMET_LSTM_OUTPUT_GATE_INPUT, RXMET_LSTM_INPUT_GATE_OUTPUT,
+            RXMET_LSTM_FORGET_GATE_OUTPUT, RXMET_LSTM_CELL_GATE_OUTPUT, RXMET_LSTM_OUTPUT_GATE_OUTPUT,
+            RXMET_LSTM_CELL_STATE, RXMET_LSTM_CELL_TANH_OUTPUT, RXMET_LSTM_OUTPUT, kOps + 0, kOps + 1, kOps + 2};
+        stats::commit<kRecurrentStats>(st, slots, a.mins, a.maxs, scratch);
+    }
+}
+
 int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
 
 }  // namespace
@@ -233,13 +384,14 @@ size_t forwardFloatWorkspaceBytes(int T, int B, int I, int H) {
     const size_t C = 4 * static_cast<size_t>(H);
     ws.take<float>(static_cast<size_t>(T) * B * C);  // ih linear
     ws.take<float>(static_cast<size_t>(I) * C);      // weight_ih transposed
-    ws.take<float>(static_cast<size_t>(H) * C);      // weight_hh transposed
+    ws.take<float>(static_cast<size_t>(H) * C);      // weight_hh transposed (H > 128: interleaved by gate)
     return ws.used() + 1024;
 }
 
 void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspaceBytes, cudaStream_t st) {
     const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
-    if (C > 512) fail(RXMET_ERR_UNSUPPORTED, "hidden sizes up to 128 are built (got %d)", H);
+    if (H > 512) fail(RXMET_ERR_UNSUPPORTED, "hidden sizes up to 512 are built (got %d)", H);
+    const bool wide = C > 512;
     const size_t rows = static_cast<size_t>(T) * B;
     Workspace ws(workspace, workspaceBytes);
     float *ih = ws.take<float>(rows * C);
@@ -281,7 +433,13 @@ void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspac
         afterLaunch("lstmTransposeWeights");
     };
     transpose(call.weightIh, C, I, wIhT);
-    transpose(call.weightHh, C, H, wHhT);
+    if (wide) {
+        KernelTimer timer__("lstmInterleaveGates", st);
+        interleaveGates<<<gridFor(static_cast<size_t>(C) * H, 256), 256, 0, st>>>(call.weightHh, H, wHhT);
+        afterLaunch("lstmInterleaveGates");
+    } else {
+        transpose(call.weightHh, C, H, wHhT);
+    }
     {
         const int block = std::min((C + 31) / 32 * 32, 512);
         const size_t smem = sizeof(float) * (kRowsPerBlock * I + 2 * 32);
@@ -298,10 +456,30 @@ void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspac
     a.wT = wHhT; a.bias = call.biasHh; a.ih = ih; a.h0 = call.h0; a.c0 = call.c0;
     a.output = call.output; a.finalHidden = call.finalHidden; a.finalCell = call.finalCell;
     a.tr = tr; a.mins = mins; a.maxs = maxs;
-    int device = 0, smemMax = 0, sms = 0;
-    RXMET_CUDA(cudaGetDevice(&device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&smemMax, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    RXMET_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int smemMax = currentDevice().smemMax, sms = currentDevice().sms;
+    if (wide) {
+        FloatWideArgs wa{};
+        wa.base = a;
+        wa.w4 = reinterpret_cast<const float4 *>(wHhT);
+        wa.HP = (H + 31) / 32 * 32;
+        const int groupsMax = std::max(1, 512 / wa.HP);
+        const int want = std::max(1, (B + sms - 1) / sms);
+        int rb = 1;
+        while (rb < 4 && rb * groupsMax < want) rb *= 2;
+        const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));
+        const int btWide = groups * rb, blockWide = groups * wa.HP;
+        const size_t smem = sizeof(float) * (2 * static_cast<size_t>(btWide) * ((H + 3) / 4 * 4) + 2 * kRecurrentStats * 16);
+        auto launchWide = [&](auto kernel) {
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("lstmRecurrentFloatWide", st);
+            kernel<<<(B + btWide - 1) / btWide, blockWide, smem, st>>>(wa);
+        };
+        if (rb == 1) launchWide(recurrentFloatWide<1>);
+        else if (rb == 2) launchWide(recurrentFloatWide<2>);
+        else launchWide(recurrentFloatWide<4>);
+        afterLaunch("lstmRecurrentFloatWide");
+        return;
+    }
     const int bt = (B >= 4 * sms) ? 4 : ((B > sms) ? 2 : 1);
     const int block = (C + 31) / 32 * 32;
     auto launch = [&](auto kernel, int BT) {

@@ -23,23 +23,16 @@
 #include <cstdint>
 
 #include "common.h"
+#include "lstm_device.cuh"
 #include "lstm_kernels.h"
 
 namespace rxmet {
 namespace lstm {
 namespace {
 
-__device__ __forceinline__ float rescaleF(float v, DevRescale r) {
-    return rintf(__fmul_rn(__fmul_rn(v, r.mult), r.pow2));
-}
-
-// value -> clamp(rint(value / scale) + zp): division and rounding in double as the reference does
-// (operators/quant-lstm/include/quantization/float_carrier_ops.h:49-59).
-__device__ __forceinline__ int32_t quantizeCode(float v, float scale, int32_t zp, int32_t lo, int32_t hi, uint8_t &clamped) {
-    const double t = rint(static_cast<double>(v) / static_cast<double>(scale)) + static_cast<double>(zp);
-    clamped = (t < static_cast<double>(lo)) || (t > static_cast<double>(hi));
-    return t <= static_cast<double>(lo) ? lo : (t >= static_cast<double>(hi) ? hi : static_cast<int32_t>(t));
-}
+using dev::quantizeCode;
+using dev::rescaleF;
+using dev::scaleCell;
 
 // Activation tensors: [rows][cols] floats -> [rows][colsPadded] signed bytes (code - shift, zero
 // padded), optional q-carrier copy, optional clamp mask, optional centred float copy (code - zp).
@@ -129,9 +122,7 @@ __global__ void prepChannels(const PrepArgs a) {
 
 // accumulator -> centred linear code (code - zero point) and its clamp flag.
 __device__ __forceinline__ float linearCentred(int32_t total, DevRescale out, float cLo, float cHi, uint8_t &clamped) {
-    const float r = rescaleF(static_cast<float>(total), out);
-    clamped = (r < cLo) || (r > cHi);
-    return fminf(fmaxf(r, cLo), cHi);
+    return dev::linearCentredF(static_cast<float>(total), out, cLo, cHi, clamped);
 }
 
 constexpr int kIhRows = 16;
@@ -222,16 +213,6 @@ struct RecurrentArgs {
     float *finalHidden, *finalCell;
     rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearQ)
 };
-
-// The double-precision form (ratios that do not fit Q31) sits behind a call, so that the common
-// single multiply is not accompanied by a speculative evaluation of it.
-__device__ __noinline__ float scaleCellWide(float product, double mantissa, int exponent) {
-    return static_cast<float>(ldexp(static_cast<double>(product) * mantissa, exponent));
-}
-__device__ __forceinline__ float scaleCell(float product, float ratio, double mantissa, int exponent, int usesFp) {
-    if (usesFp) return scaleCellWide(product, mantissa, exponent);
-    return __fmul_rn(product, ratio);
-}
 
 template <int KW, int BT>
 __global__ void __launch_bounds__(KW * 16) recurrentQ(const __grid_constant__ RecurrentArgs a) {
@@ -437,24 +418,38 @@ struct SizerAdapter {
 
 }  // namespace
 
+void quantizeCellCodes(const float *c0, int B, int H, const ScalarExec &s, float *centred, float *carrier, uint8_t *mask,
+                       cudaStream_t st) {
+    const int op = RXMET_LSTM_CELL_STATE;
+    const size_t total = static_cast<size_t>(B) * H;
+    {
+        KernelTimer timer__("lstmQuantizeCodes", st);
+        quantizeCodes<<<gridFor(total, 256), 256, 0, st>>>(c0, B, H, H, s.scale[op], s.zp[op], s.lo[op], s.hi[op], 0, nullptr,
+                                                         carrier, mask, centred);
+    }
+    afterLaunch("lstmQuantizeCodes");
+}
+
 size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
     SizerAdapter s;
     layout(s, T, B, I, H, static_cast<int8_t **>(nullptr), static_cast<int8_t **>(nullptr), static_cast<float **>(nullptr),
            static_cast<uint32_t **>(nullptr), static_cast<uint32_t **>(nullptr), static_cast<int32_t **>(nullptr),
            static_cast<int32_t **>(nullptr), static_cast<float **>(nullptr), static_cast<int32_t **>(nullptr),
            static_cast<float **>(nullptr));
-    return s.ws.used() + 1024;
+    return std::max(s.ws.used() + 1024, forwardQuantWideWorkspaceBytes(T, B, I, H));
 }
 
 void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes, cudaStream_t st) {
     const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
     const ScalarExec &s = e.scalar;
-    for (int op = 0; op < kOps; ++op)
-        if (s.hi[op] - s.lo[op] > 255)
-            fail(RXMET_ERR_UNSUPPORTED, "this build runs grids of at most 8 bits (point %d is wider)", op);
-    if (!e.exactAccumulators)
-        fail(RXMET_ERR_UNSUPPORTED, "an integer accumulator of this configuration may reach 2^24, where the float carrier stops being order independent");
-    if (H > 128 || I > 128) fail(RXMET_ERR_UNSUPPORTED, "hidden and input sizes up to 128 are built (got H=%d, I=%d)", H, I);
+    // The byte-code kernels below take grids of at most 8 bits whose accumulators stay below 2^24 and
+    // I, H <= 128 (weight rows live in registers); everything else goes to the wide kernels.
+    bool bytePath = e.exactAccumulators && H <= 128 && I <= 128 && !e.tables.empty();
+    for (int op = 0; op < kOps; ++op) bytePath = bytePath && (static_cast<int64_t>(s.hi[op]) - s.lo[op] <= 255);
+    if (!bytePath) {
+        forwardQuantWide(call, e, workspace, workspaceBytes, st);
+        return;
+    }
     const Plan p = planFor(T, B, I, H);
     Workspace ws(workspace, workspaceBytes);
     int8_t *xq, *h0q;

@@ -1,0 +1,608 @@
+// Quantized LSTM forward for activation grids of up to 16 bits, weight grids of up to 8 bits
+// (W4 / W8), hidden sizes up to 512 and input sizes up to 256: the configurations the byte-code
+// kernels of lstm_forward_quant.cu do not take.
+//
+// Semantics: the reference's FP32 q-carrier (operators/quant-lstm/src/lstm/forward_quantized_fp_cuda.cu:
+// 690-880, CPU statement src/lstm/forward_quantized_fp_cpu.cc:71-200).  Every float rounding of the
+// pointwise part is kept literally.  The two linear stages are accumulated EXACTLY in integers and
+// converted to float once; that equals the reference's float accumulation whenever every partial sum
+// stays below 2^24 (its "exact_integer_range" class) and is the correctly rounded value of the sum
+// otherwise, where the reference's own CPU (sequential float sums) and CUDA (cuBLAS) builds differ
+// from each other in the last place.
+//
+// Codes wider than a byte are stored as byte planes of u = code - grid minimum (0 .. 65535): a high
+// and a low plane, each packed four along K, so that the products stay on dp4a (signed weight bytes
+// times unsigned code bytes); sum = 256 * sum_hi + sum_lo + (grid minimum - zero point) * row sum.
+//
+// Launch plan for one call:
+//   quantizePlanes x2    : x, h0 -> byte planes (+ optional q-carrier masters and clamp masks)
+//   quantizeCodes        : c0 -> centred cell codes (lstm_forward_quant.cu)
+//   prepChannelsWide     : weights -> packed byte codes, 64-bit addends (zero-point correction + bias)
+//   inputLinearWide      : all T*B rows of the input projection, persistent CTAs, cp.async staging
+//   recurrentWide        : ONE launch for all T steps.  Thread (j, s) owns hidden unit j - all four
+//                          gates - for RB batch rows of row group s, so the gate math needs no
+//                          exchange between threads; weight_hh streams from L2 (it no longer fits one
+//                          SM at H = 512), the hidden codes of a CTA's rows live in shared memory
+//                          (double buffered, one barrier per step), the cell state in registers.
+//   Activations are table lookups (code -> code + clamp flag) built on the host with the libm calls the
+//   reference's CPU path makes; for these grids the five tables (up to 65,536 entries each) sit in
+//   device memory and are served by L2.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.h"
+#include "lstm_device.cuh"
+#include "lstm_kernels.h"
+
+namespace rxmet {
+namespace lstm {
+namespace {
+
+using dev::dotSignedUnsigned;
+using dev::linearCentredF;
+using dev::quantizeCode;
+using dev::rescaleF;
+using dev::scaleCell;
+
+// [rows][cols] floats -> [rows][PLANES][kWords] words of four unsigned bytes of (code - lo); columns
+// beyond `cols` are zero.  With PLANES = 2 plane 0 holds the high bytes.  src == null stands for real
+// zeros (the zero-point code).
+template <int PLANES>
+__global__ void quantizePlanes(const float *__restrict__ src, int rows, int cols, int kWords, float scale, int32_t zp,
+                               int32_t lo, int32_t hi, uint32_t *__restrict__ planes, float *__restrict__ carrier,
+                               uint8_t *__restrict__ mask) {
+    const size_t total = static_cast<size_t>(rows) * kWords;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / kWords;
+        const int kw = static_cast<int>(i % kWords);
+        uint32_t high = 0, low = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = kw * 4 + e;
+            if (k >= cols) continue;
+            const size_t o = r * cols + k;
+            uint8_t m = 0;
+            const int32_t q = src ? quantizeCode(src[o], scale, zp, lo, hi, m) : min(max(zp, lo), hi);
+            const uint32_t u = static_cast<uint32_t>(q - lo);
+            low |= (u & 0xffu) << (8 * e);
+            high |= ((u >> 8) & 0xffu) << (8 * e);
+            if (carrier) carrier[o] = static_cast<float>(q);
+            if (mask) mask[o] = m;
+        }
+        uint32_t *row = planes + r * PLANES * kWords;
+        if (PLANES == 2) {
+            row[kw] = high;
+            row[kWords + kw] = low;
+        } else {
+            row[kw] = low;
+        }
+    }
+}
+
+struct WidePrepArgs {
+    int H, I, kWordsIh, kWordsHh;
+    const float *wIh, *wHh, *bIh, *bHh;  // float masters
+    const float *channel;                // kChannelFields x 4H
+    int32_t wLo, wHi, bLo, bHi;
+    int64_t xCorrection, hCorrection;    // (grid minimum - zero point) of the x and h codes
+    uint32_t *wIhWords;                  // [kWordsIh][4H]
+    uint32_t *wHhWords;                  // [2 gate pairs][kWordsHh][H][2]
+    int64_t *ihAddend, *hhAddend;        // correction * row sum + rescaled bias
+    float *mWIh, *mWHh, *mBIh, *mBHh;    // optional q-carrier masters
+    uint8_t *kWIh, *kWHh, *kBIh, *kBHh;  // optional clamp masks
+};
+
+// One warp per output channel and side (blockIdx.y: 0 = weight_ih, 1 = weight_hh).
+__global__ void prepChannelsWide(const WidePrepArgs a) {
+    const int C = 4 * a.H;
+    const int lane = threadIdx.x & 31;
+    const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (c >= C) return;
+    const int side = blockIdx.y;
+    auto field = [&](int f) { return a.channel[static_cast<size_t>(f) * C + c]; };
+    const int K = side ? a.H : a.I, kWords = side ? a.kWordsHh : a.kWordsIh;
+    const float *w = (side ? a.wHh : a.wIh) + static_cast<size_t>(c) * K;
+    const float scale = field(side ? kWHhScale : kWIhScale);
+    float *master = side ? a.mWHh : a.mWIh;
+    uint8_t *keep = side ? a.kWHh : a.kWIh;
+    const int g = c / a.H, j = c % a.H;
+    int32_t sum = 0;
+    for (int kw = lane; kw < kWords; kw += 32) {
+        uint32_t word = 0;
+        for (int i = 0; i < 4; ++i) {
+            const int k = kw * 4 + i;
+            int32_t q = 0;
+            if (k < K) {
+                uint8_t m;
+                q = quantizeCode(w[k], scale, 0, a.wLo, a.wHi, m);
+                if (master) master[static_cast<size_t>(c) * K + k] = static_cast<float>(q);
+                if (keep) keep[static_cast<size_t>(c) * K + k] = m;
+            }
+            sum += q;
+            word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+        }
+        if (side) a.wHhWords[((static_cast<size_t>(g >> 1) * kWords + kw) * a.H + j) * 2 + (g & 1)] = word;
+        else a.wIhWords[static_cast<size_t>(kw) * C + c] = word;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane != 0) return;
+    int64_t addend = (side ? a.hCorrection : a.xCorrection) * static_cast<int64_t>(sum);
+    const float *b = side ? a.bHh : a.bIh;
+    if (b) {
+        uint8_t m;
+        const int32_t q = quantizeCode(b[c], field(side ? kBHhScale : kBIhScale), 0, a.bLo, a.bHi, m);
+        const DevRescale r{field(side ? kHhBiasMult : kIhBiasMult), field(side ? kHhBiasPow2 : kIhBiasPow2)};
+        addend += static_cast<int64_t>(rescaleF(static_cast<float>(q), r));
+        float *bm = side ? a.mBHh : a.mBIh;
+        uint8_t *bk = side ? a.kBHh : a.kBIh;
+        if (bm) bm[c] = static_cast<float>(q);
+        if (bk) bk[c] = m;
+    }
+    (side ? a.hhAddend : a.ihAddend)[c] = addend;
+}
+
+__device__ __forceinline__ void copyAsync16(void *dst, const void *src, bool valid) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(valid ? 16u : 0u) : "memory");
+}
+__device__ __forceinline__ void commitCopies() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void waitCopies() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 256 * high + low + addend as the float the reference's accumulator holds (rounded once).
+template <int PLANES>
+__device__ __forceinline__ float combine(const int32_t (&acc)[PLANES], int64_t addend) {
+    int64_t total = addend;
+    if (PLANES == 2) total += (static_cast<int64_t>(acc[0]) << 8) + acc[1];
+    else total += acc[0];
+    return __ll2float_rn(total);
+}
+
+constexpr int kWideRows = 16;
+constexpr int kWideThreads = 512;
+
+struct WideInputArgs {
+    int rows, H, kWords;
+    const uint32_t *x;       // [rows][PLANES][kWords]
+    const uint32_t *words;   // [kWords][4H]
+    const int64_t *addend;   // [4H]
+    const float *channel;
+    ScalarExec s;
+    float *lhs;              // [rows][4H] ih contribution on each gate's input grid
+    float *linear;           // optional checkpoint [rows][4H]
+    uint8_t *linearClamped;  // optional
+};
+
+// Persistent over blocks of kWideRows rows (blockIdx.x strides the blocks); blockIdx.y picks a slab
+// of blockDim.x output channels.  A thread keeps its channel's weight words (up to KW) in registers;
+// the code rows of the next block arrive by cp.async while the current block computes and are read
+// back as 16-byte broadcasts.
+template <int KW, int PLANES>
+__global__ void __launch_bounds__(kWideThreads) inputLinearWide(const __grid_constant__ WideInputArgs a) {
+    extern __shared__ __align__(16) uint32_t wideSmem[];  // [2][kWideRows][PLANES * kWords]
+    const int C = 4 * a.H, tid = threadIdx.x, c = blockIdx.y * blockDim.x + tid;
+    const bool live = c < C;
+    const int kWords = a.kWords, rowWords = PLANES * kWords, blockWords = kWideRows * rowWords;
+    uint32_t w[KW];
+#pragma unroll
+    for (int kk = 0; kk < KW; ++kk) w[kk] = (live && kk < kWords) ? a.words[static_cast<size_t>(kk) * C + c] : 0u;
+    const int64_t addend = live ? a.addend[c] : 0;
+    const DevRescale out = live ? DevRescale{a.channel[static_cast<size_t>(kIhOutMult) * C + c],
+                                             a.channel[static_cast<size_t>(kIhOutPow2) * C + c]}
+                                : DevRescale{1.0f, 1.0f};
+    const int op = RXMET_LSTM_WEIGHT_IH_LINEAR, g = live ? c / a.H : 0;
+    const float cLo = static_cast<float>(a.s.lo[op] - a.s.zp[op]), cHi = static_cast<float>(a.s.hi[op] - a.s.zp[op]);
+    const DevRescale toGate = a.s.ihToGate[g];
+    const float zp = a.s.zpF[op];
+
+    const int blocks = (a.rows + kWideRows - 1) / kWideRows;
+    const size_t limit = static_cast<size_t>(a.rows) * rowWords;
+    auto stage = [&](int blk, int buf) {
+        const size_t base = static_cast<size_t>(blk) * blockWords;
+        uint32_t *dst = wideSmem + buf * blockWords;
+        for (int i = tid * 4; i < blockWords; i += blockDim.x * 4) {
+            const bool valid = blk < blocks && base + i < limit;
+            copyAsync16(dst + i, a.x + (valid ? base + i : 0), valid);
+        }
+        commitCopies();
+    };
+    stage(blockIdx.x, 0);
+    int buf = 0;
+    for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x, buf ^= 1) {
+        stage(blk + gridDim.x, buf ^ 1);
+        waitCopies<1>();
+        __syncthreads();
+        const int row0 = blk * kWideRows, nRows = min(kWideRows, a.rows - row0);
+        if (live) {
+            size_t o = static_cast<size_t>(row0) * C + c;
+            const uint32_t *xr = wideSmem + buf * blockWords;
+            for (int r = 0; r < nRows; ++r, o += C, xr += rowWords) {
+                int32_t acc[PLANES];
+#pragma unroll
+                for (int p = 0; p < PLANES; ++p) acc[p] = 0;
+#pragma unroll
+                for (int k4 = 0; k4 < KW / 4; ++k4) {
+                    if (4 * k4 < kWords) {
+#pragma unroll
+                        for (int p = 0; p < PLANES; ++p) {
+                            const uint4 xv = *reinterpret_cast<const uint4 *>(xr + p * kWords + 4 * k4);
+                            acc[p] = dotSignedUnsigned(w[4 * k4 + 0], xv.x, acc[p]);
+                            acc[p] = dotSignedUnsigned(w[4 * k4 + 1], xv.y, acc[p]);
+                            acc[p] = dotSignedUnsigned(w[4 * k4 + 2], xv.z, acc[p]);
+                            acc[p] = dotSignedUnsigned(w[4 * k4 + 3], xv.w, acc[p]);
+                        }
+                    }
+                }
+                uint8_t m;
+                const float cen = linearCentredF(combine<PLANES>(acc, addend), out, cLo, cHi, m);
+                a.lhs[o] = rescaleF(cen, toGate);
+                if (a.linear) a.linear[o] = cen + zp;
+                if (a.linearClamped) a.linearClamped[o] = m;
+            }
+        }
+        __syncthreads();
+    }
+    waitCopies<0>();
+}
+
+struct WideRecurrentArgs {
+    int T, B, H, HP, kWords;
+    const uint2 *words;      // [2 gate pairs][kWords][H]: (x, y) = gates (2 * pair, 2 * pair + 1)
+    const int64_t *addend;   // [4H]
+    const float *channel;
+    const int32_t *tables;   // device: five tables back to back
+    int tableOffset[kTables];
+    const float *lhs;        // [T][B][4H]
+    const uint32_t *h0;      // [B][PLANES][kWords]
+    const float *c0;         // [B][H] centred cell codes
+    ScalarExec s;
+    float *output;           // [T][B][H] dequantized
+    float *finalHidden, *finalCell;
+    rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearWide)
+};
+
+template <int PLANES, int RB>
+__global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_constant__ WideRecurrentArgs a) {
+    extern __shared__ __align__(16) uint32_t wideSmem[];  // [2][BT][PLANES][kWords]
+    const int H = a.H, C = 4 * a.H, kWords = a.kWords;
+    const int tid = threadIdx.x, j = tid % a.HP, sg = tid / a.HP;
+    const int BT = (blockDim.x / a.HP) * RB;
+    const bool active = j < H;
+    const int rowWords = PLANES * kWords, bufWords = BT * rowWords;
+    const int ctaRow0 = blockIdx.x * BT, b0 = ctaRow0 + sg * RB;
+    const ScalarExec &s = a.s;
+
+    for (int i = tid; i < 2 * bufWords; i += blockDim.x) wideSmem[i] = 0u;
+    __syncthreads();
+    for (int i = tid; i < bufWords; i += blockDim.x) {
+        const int b = ctaRow0 + i / rowWords;
+        if (b < a.B) wideSmem[i] = a.h0[static_cast<size_t>(b) * rowWords + i % rowWords];
+    }
+
+    int64_t addend[4];
+    DevRescale outR[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int c = g * H + j;
+        addend[g] = active ? a.addend[c] : 0;
+        outR[g] = active ? DevRescale{a.channel[static_cast<size_t>(kHhOutMult) * C + c],
+                                      a.channel[static_cast<size_t>(kHhOutPow2) * C + c]}
+                         : DevRescale{1.0f, 1.0f};
+    }
+    float cellCen[RB], hiddenCen[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        cellCen[r] = (active && b0 + r < a.B) ? a.c0[static_cast<size_t>(b0 + r) * H + j] : 0.0f;
+        hiddenCen[r] = 0.0f;
+    }
+
+    const int opHh = RXMET_LSTM_WEIGHT_HH_LINEAR, opC = RXMET_LSTM_CELL_STATE, opO = RXMET_LSTM_OUTPUT;
+    const float hhLo = static_cast<float>(s.lo[opHh] - s.zp[opHh]), hhHi = static_cast<float>(s.hi[opHh] - s.zp[opHh]);
+    const float cLo = static_cast<float>(s.lo[opC] - s.zp[opC]), cHi = static_cast<float>(s.hi[opC] - s.zp[opC]);
+    const float oLo = static_cast<float>(s.lo[opO] - s.zp[opO]), oHi = static_cast<float>(s.hi[opO] - s.zp[opO]);
+    const int32_t cBase = s.zp[opC] - s.lo[opC], hBase = s.zp[opO] - s.lo[opO];
+    const float scaleH = s.scale[opO];
+    const size_t stepC = static_cast<size_t>(a.B) * C, stepH = static_cast<size_t>(a.B) * H;
+    __syncthreads();
+
+    for (int t = 0; t < a.T; ++t) {
+        const uint32_t *cur = wideSmem + (t & 1) * bufWords;
+        uint8_t *nxt = reinterpret_cast<uint8_t *>(wideSmem + ((t + 1) & 1) * bufWords);
+        const size_t baseC = t * stepC, baseH = t * stepH;
+        if (active) {
+            float rhs[4][RB];
+            // ---- hh linear stage, two gates at a time ----
+#pragma unroll
+            for (int pair = 0; pair < 2; ++pair) {
+                int32_t acc[2][RB][PLANES];
+#pragma unroll
+                for (int gg = 0; gg < 2; ++gg)
+#pragma unroll
+                    for (int r = 0; r < RB; ++r)
+#pragma unroll
+                        for (int p = 0; p < PLANES; ++p) acc[gg][r][p] = 0;
+                const uint2 *wp = a.words + static_cast<size_t>(pair) * kWords * H + j;
+                const uint4 *hRows = reinterpret_cast<const uint4 *>(cur + sg * RB * rowWords);
+#pragma unroll 2
+                for (int k4 = 0; k4 < kWords / 4; ++k4) {
+                    uint2 w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) w[i] = __ldg(wp + static_cast<size_t>(4 * k4 + i) * H);
+#pragma unroll
+                    for (int r = 0; r < RB; ++r)
+#pragma unroll
+                        for (int p = 0; p < PLANES; ++p) {
+                            const uint4 hv = hRows[(r * PLANES + p) * (kWords / 4) + k4];
+                            acc[0][r][p] = dotSignedUnsigned(w[0].x, hv.x, acc[0][r][p]);
+                            acc[1][r][p] = dotSignedUnsigned(w[0].y, hv.x, acc[1][r][p]);
+                            acc[0][r][p] = dotSignedUnsigned(w[1].x, hv.y, acc[0][r][p]);
+                            acc[1][r][p] = dotSignedUnsigned(w[1].y, hv.y, acc[1][r][p]);
+                            acc[0][r][p] = dotSignedUnsigned(w[2].x, hv.z, acc[0][r][p]);
+                            acc[1][r][p] = dotSignedUnsigned(w[2].y, hv.z, acc[1][r][p]);
+                            acc[0][r][p] = dotSignedUnsigned(w[3].x, hv.w, acc[0][r][p]);
+                            acc[1][r][p] = dotSignedUnsigned(w[3].y, hv.w, acc[1][r][p]);
+                        }
+                }
+#pragma unroll
+                for (int gg = 0; gg < 2; ++gg) {
+                    const int g = 2 * pair + gg;
+#pragma unroll
+                    for (int r = 0; r < RB; ++r) {
+                        uint8_t m;
+                        const float cen = linearCentredF(combine<PLANES>(acc[gg][r], addend[g]), outR[g], hhLo, hhHi, m);
+                        rhs[g][r] = rescaleF(cen, s.hhToGate[g]);
+                        if (b0 + r < a.B) {
+                            const size_t o = baseC + static_cast<size_t>(b0 + r) * C + g * H + j;
+                            if (a.ck.weight_hh_linear) a.ck.weight_hh_linear[o] = cen + s.zpF[opHh];
+                            if (a.ck.weight_hh_linear_clamped) a.ck.weight_hh_linear_clamped[o] = m;
+                        }
+                    }
+                }
+            }
+            // ---- gates, cell and hidden for this thread's (row, j) elements ----
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const int b = b0 + r;
+                if (b >= a.B) continue;
+                const size_t rowC = baseC + static_cast<size_t>(b) * C + j, so = baseH + static_cast<size_t>(b) * H + j;
+                float outCen[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int opIn = RXMET_LSTM_INPUT_GATE_INPUT + g;
+                    const float giLo = static_cast<float>(s.lo[opIn] - s.zp[opIn]), giHi = static_cast<float>(s.hi[opIn] - s.zp[opIn]);
+                    const float sum = a.lhs[rowC + g * H] + rhs[g][r];
+                    const float cen = fminf(fmaxf(sum, giLo), giHi);
+                    const int32_t e = __ldg(a.tables + a.tableOffset[g] + static_cast<int32_t>(cen) + (s.zp[opIn] - s.lo[opIn]));
+                    outCen[g] = static_cast<float>(e >> 1);
+                    const size_t o = rowC + g * H;
+                    if (a.ck.gate_inputs) a.ck.gate_inputs[o] = cen + s.zpF[opIn];
+                    if (a.ck.gate_inputs_clamped) a.ck.gate_inputs_clamped[o] = (sum < giLo) || (sum > giHi);
+                    if (a.ck.gate_outputs) a.ck.gate_outputs[o] = outCen[g] + s.zpF[RXMET_LSTM_INPUT_GATE_OUTPUT + g];
+                    if (a.ck.gate_outputs_clamped) a.ck.gate_outputs_clamped[o] = static_cast<uint8_t>(e & 1);
+                }
+                const float pf = __fmul_rn(outCen[1], cellCen[r]), pi = __fmul_rn(outCen[0], outCen[2]);
+                const float sf = scaleCell(pf, s.forgetRatio, s.forgetMantissa, s.forgetExponent, s.forgetUsesFp);
+                const float si = scaleCell(pi, s.inputRatio, s.inputMantissa, s.inputExponent, s.inputUsesFp);
+                const float rounded = rintf(__fadd_rn(sf, si));
+                cellCen[r] = fminf(fmaxf(rounded, cLo), cHi);
+                const int32_t te = __ldg(a.tables + a.tableOffset[4] + static_cast<int32_t>(cellCen[r]) + cBase);
+                const float tanhCen = static_cast<float>(te >> 1);
+                const float raw = __fmul_rn(outCen[3], tanhCen);
+                const float hr = rescaleF(raw, s.productToOutput);
+                hiddenCen[r] = fminf(fmaxf(hr, oLo), oHi);
+                const uint32_t u = static_cast<uint32_t>(static_cast<int32_t>(hiddenCen[r]) + hBase);
+                uint8_t *rowBytes = nxt + static_cast<size_t>(sg * RB + r) * rowWords * 4;
+                if (PLANES == 2) {
+                    rowBytes[j] = static_cast<uint8_t>(u >> 8);
+                    rowBytes[kWords * 4 + j] = static_cast<uint8_t>(u & 0xffu);
+                } else {
+                    rowBytes[j] = static_cast<uint8_t>(u);
+                }
+                a.output[so] = __fmul_rn(hiddenCen[r], scaleH);
+                if (a.ck.cell_states) a.ck.cell_states[so] = cellCen[r] + s.zpF[opC];
+                if (a.ck.cell_states_clamped) a.ck.cell_states_clamped[so] = (rounded < cLo) || (rounded > cHi);
+                if (a.ck.cell_tanh_outputs) a.ck.cell_tanh_outputs[so] = tanhCen + s.zpF[RXMET_LSTM_CELL_TANH_OUTPUT];
+                if (a.ck.cell_tanh_outputs_clamped) a.ck.cell_tanh_outputs_clamped[so] = static_cast<uint8_t>(te & 1);
+                if (a.ck.hidden_outputs) a.ck.hidden_outputs[so] = hiddenCen[r] + s.zpF[opO];
+                if (a.ck.hidden_outputs_clamped) a.ck.hidden_outputs_clamped[so] = (hr < oLo) || (hr > oHi);
+            }
+        }
+        __syncthreads();
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            if (b0 + r >= a.B) continue;
+            const size_t o = static_cast<size_t>(b0 + r) * H + j;
+            a.finalHidden[o] = __fmul_rn(hiddenCen[r], scaleH);
+            a.finalCell[o] = __fmul_rn(cellCen[r], s.scale[opC]);
+        }
+    }
+}
+
+int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
+
+// words per code row: K padded to a multiple of 16 bytes so that rows are read as 16-byte pieces
+int wordsFor(int k) { return (k + 15) / 16 * 4; }
+
+struct WideLayout {
+    uint32_t *x, *h0, *wIh, *wHh;
+    float *c0, *channel, *lhs;
+    int64_t *addIh, *addHh;
+};
+
+template <class W>
+WideLayout layoutWide(W &ws, int T, int B, int I, int H, int planes) {
+    const size_t rows = static_cast<size_t>(T) * B, C = 4 * static_cast<size_t>(H);
+    const size_t kIh = wordsFor(I), kHh = wordsFor(H);
+    WideLayout l{};
+    l.x = ws.template take<uint32_t>(rows * planes * kIh);
+    l.h0 = ws.template take<uint32_t>(static_cast<size_t>(B) * planes * kHh);
+    l.c0 = ws.template take<float>(static_cast<size_t>(B) * H);
+    l.wIh = ws.template take<uint32_t>(kIh * C);
+    l.wHh = ws.template take<uint32_t>(kHh * C);
+    l.addIh = ws.template take<int64_t>(C);
+    l.addHh = ws.template take<int64_t>(C);
+    l.channel = ws.template take<float>(kChannelFields * C);
+    l.lhs = ws.template take<float>(rows * C);
+    return l;
+}
+
+struct SizerAdapter {
+    WorkspaceSizer ws;
+    template <class T>
+    T *take(size_t n) {
+        ws.take<T>(n);
+        return nullptr;
+    }
+};
+
+}  // namespace
+
+bool forwardQuantWideTakes(const Exec &e, int I, int H, const char **why) {
+    const char *reason = nullptr;
+    if (!e.weightsFitBytes) reason = "weight grids wider than 8 bits are not built";
+    else if (e.activationPlanes == 0) reason = "input / output grids wider than 16 bits are not built";
+    else if (e.wide.entries.empty()) reason = "gate-input and cell-state grids wider than 16 bits are not built";
+    else if (H > 512) reason = "hidden sizes above 512 are not built";
+    else if (I > 256) reason = "input sizes above 256 are not built";
+    else {
+        for (int op : {RXMET_LSTM_WEIGHT_IH_LINEAR, RXMET_LSTM_WEIGHT_HH_LINEAR})
+            if (static_cast<int64_t>(e.scalar.hi[op]) - e.scalar.lo[op] >= (int64_t{1} << 24))
+                reason = "linear-output grids wider than 24 bits are not built";
+    }
+    if (why) *why = reason;
+    return reason == nullptr;
+}
+
+size_t forwardQuantWideWorkspaceBytes(int T, int B, int I, int H) {
+    SizerAdapter s;
+    layoutWide(s, T, B, I, H, 2);
+    return s.ws.used() + 1024;
+}
+
+void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 4 * H;
+    const ScalarExec &s = e.scalar;
+    const char *why = nullptr;
+    if (!forwardQuantWideTakes(e, I, H, &why)) fail(RXMET_ERR_UNSUPPORTED, "quantized LSTM forward: %s (I=%d, H=%d)", why, I, H);
+    const int planes = e.activationPlanes;
+    const int kIh = wordsFor(I), kHh = wordsFor(H);
+    const size_t rows = static_cast<size_t>(T) * B;
+    Workspace ws(workspace, workspaceBytes);
+    const WideLayout l = layoutWide(ws, T, B, I, H, planes);
+    const int32_t *tables = e.wideTablesOnDevice();
+    RXMET_CUDA(cudaMemcpyAsync(l.channel, e.channel.data(), e.channel.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+
+    const rxmet_lstm_masters none{};
+    const rxmet_lstm_masters &m = call.masters ? *call.masters : none;
+    auto quantize = [&](const float *src, size_t nRows, int cols, int kWords, int op, uint32_t *dst, float *carrier, uint8_t *mask) {
+        const size_t total = nRows * kWords;
+        {
+            KernelTimer timer__("lstmQuantizePlanes", st);
+            if (planes == 2)
+                quantizePlanes<2><<<gridFor(total, 256), 256, 0, st>>>(src, static_cast<int>(nRows), cols, kWords, s.scale[op], s.zp[op],
+                                                                      s.lo[op], s.hi[op], dst, carrier, mask);
+            else
+                quantizePlanes<1><<<gridFor(total, 256), 256, 0, st>>>(src, static_cast<int>(nRows), cols, kWords, s.scale[op], s.zp[op],
+                                                                      s.lo[op], s.hi[op], dst, carrier, mask);
+        }
+        afterLaunch("lstmQuantizePlanes");
+    };
+    quantize(call.x, rows, I, kIh, RXMET_LSTM_INPUT, l.x, m.input, m.input_clamped);
+    quantize(call.h0, static_cast<size_t>(B), H, kHh, RXMET_LSTM_OUTPUT, l.h0, m.initial_hidden, m.initial_hidden_clamped);
+    quantizeCellCodes(call.c0, B, H, s, l.c0, m.initial_cell, m.initial_cell_clamped, st);
+    if (!call.h0) {
+        if (m.initial_hidden_clamped) RXMET_CUDA(cudaMemsetAsync(m.initial_hidden_clamped, 0, static_cast<size_t>(B) * H, st));
+        if (m.initial_cell_clamped) RXMET_CUDA(cudaMemsetAsync(m.initial_cell_clamped, 0, static_cast<size_t>(B) * H, st));
+    }
+
+    WidePrepArgs pa{};
+    pa.H = H; pa.I = I; pa.kWordsIh = kIh; pa.kWordsHh = kHh;
+    pa.wIh = call.weightIh; pa.wHh = call.weightHh; pa.bIh = call.biasIh; pa.bHh = call.biasHh;
+    pa.channel = l.channel;
+    pa.wLo = s.lo[RXMET_LSTM_WEIGHT_IH]; pa.wHi = s.hi[RXMET_LSTM_WEIGHT_IH];
+    pa.bLo = s.lo[RXMET_LSTM_BIAS_IH]; pa.bHi = s.hi[RXMET_LSTM_BIAS_IH];
+    pa.xCorrection = static_cast<int64_t>(s.lo[RXMET_LSTM_INPUT]) - s.zp[RXMET_LSTM_INPUT];
+    pa.hCorrection = static_cast<int64_t>(s.lo[RXMET_LSTM_OUTPUT]) - s.zp[RXMET_LSTM_OUTPUT];
+    pa.wIhWords = l.wIh; pa.wHhWords = l.wHh; pa.ihAddend = l.addIh; pa.hhAddend = l.addHh;
+    pa.mWIh = m.weight_ih; pa.mWHh = m.weight_hh; pa.mBIh = m.bias_ih; pa.mBHh = m.bias_hh;
+    pa.kWIh = m.weight_ih_clamped; pa.kWHh = m.weight_hh_clamped; pa.kBIh = m.bias_ih_clamped; pa.kBHh = m.bias_hh_clamped;
+    {
+        KernelTimer timer__("lstmPrepChannelsWide", st);
+        prepChannelsWide<<<dim3((C + 7) / 8, 2), 256, 0, st>>>(pa);
+    }
+    afterLaunch("lstmPrepChannelsWide");
+
+    const rxmet_lstm_trace noTrace{};
+    const rxmet_lstm_trace &ck = call.checkpoints ? *call.checkpoints : noTrace;
+    const int sms = currentDevice().sms;
+    {
+        WideInputArgs a{};
+        a.rows = static_cast<int>(rows); a.H = H; a.kWords = kIh;
+        a.x = l.x; a.words = l.wIh; a.addend = l.addIh; a.channel = l.channel; a.s = s; a.lhs = l.lhs;
+        a.linear = ck.weight_ih_linear; a.linearClamped = ck.weight_ih_linear_clamped;
+        const int block = std::min(kWideThreads, (C + 31) / 32 * 32);
+        const int slabs = (C + block - 1) / block;
+        const int blocks = static_cast<int>((rows + kWideRows - 1) / kWideRows);
+        const size_t smem = sizeof(uint32_t) * 2 * kWideRows * planes * kIh;
+        auto launch = [&](auto kernel) {
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            const int perSm = residentPerSm(reinterpret_cast<const void *>(kernel), block, smem);
+            const int grid = std::max(1, std::min(blocks, std::max(1, sms * perSm / slabs)));
+            KernelTimer timer__("lstmInputLinearWide", st);
+            kernel<<<dim3(grid, slabs), block, smem, st>>>(a);
+        };
+#define RXMET_WIDE_IH(KW)                                     \
+    do {                                                       \
+        if (planes == 2) launch(inputLinearWide<KW, 2>);       \
+        else launch(inputLinearWide<KW, 1>);                   \
+    } while (0)
+        if (kIh <= 16) RXMET_WIDE_IH(16);
+        else if (kIh <= 32) RXMET_WIDE_IH(32);
+        else RXMET_WIDE_IH(64);
+#undef RXMET_WIDE_IH
+        afterLaunch("lstmInputLinearWide");
+    }
+    {
+        WideRecurrentArgs a{};
+        a.T = T; a.B = B; a.H = H; a.HP = (H + 31) / 32 * 32; a.kWords = kHh;
+        a.words = reinterpret_cast<const uint2 *>(l.wHh); a.addend = l.addHh; a.channel = l.channel; a.tables = tables;
+        for (int t = 0; t < kTables; ++t) a.tableOffset[t] = e.wide.offset[t];
+        a.lhs = l.lhs; a.h0 = l.h0; a.c0 = l.c0; a.s = s;
+        a.output = call.output; a.finalHidden = call.finalHidden; a.finalCell = call.finalCell; a.ck = ck;
+        // rows per CTA: enough CTAs to occupy the SMs first, then more rows per thread so that a weight
+        // word fetched from L2 serves several rows
+        const int groupsMax = std::max(1, kWideThreads / a.HP);
+        const int want = std::max(1, (B + sms - 1) / sms);
+        int rb = 1;
+        while (rb < 8 && rb * groupsMax < want) rb *= 2;
+        const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));
+        const int bt = groups * rb;
+        const int block = groups * a.HP;
+        const size_t smem = sizeof(uint32_t) * 2 * bt * planes * kHh;
+        auto launch = [&](auto kernel) {
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("lstmRecurrentWide", st);
+            kernel<<<(B + bt - 1) / bt, block, smem, st>>>(a);
+        };
+#define RXMET_WIDE_REC(RBV)                                   \
+    do {                                                       \
+        if (planes == 2) launch(recurrentWide<2, RBV>);        \
+        else launch(recurrentWide<1, RBV>);                    \
+    } while (0)
+        if (rb == 1) RXMET_WIDE_REC(1);
+        else if (rb == 2) RXMET_WIDE_REC(2);
+        else if (rb == 4) RXMET_WIDE_REC(4);
+        else RXMET_WIDE_REC(8);
+#undef RXMET_WIDE_REC
+        afterLaunch("lstmRecurrentWide");
+    }
+}
+
+}  // namespace lstm
+}  // namespace rxmet

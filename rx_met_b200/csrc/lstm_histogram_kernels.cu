@@ -36,9 +36,15 @@ struct Job {
     float lo, hi;  // filled in before the binning launch
 };
 
+// Finite extremes and finite count of every job; three separate arrays on the device, so that a
+// data-parallel run can reduce each of them across ranks in place (MIN, MAX, SUM).
 struct JobStats {
     float lo, hi;
     unsigned long long finite;
+};
+struct JobStatsDev {
+    float *lo, *hi;
+    unsigned long long *finite;
 };
 
 __device__ __forceinline__ void atomicMinFloat(float *addr, float v) {
@@ -50,12 +56,16 @@ __device__ __forceinline__ void atomicMaxFloat(float *addr, float v) {
     else atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
 }
 
-__global__ void initJobStats(JobStats *stats, int n) {
+__global__ void initJobStats(JobStatsDev stats, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) stats[i] = {FLT_MAX, -FLT_MAX, 0ull};
+    if (i < n) {
+        stats.lo[i] = FLT_MAX;
+        stats.hi[i] = -FLT_MAX;
+        stats.finite[i] = 0ull;
+    }
 }
 
-__global__ void jobMinMax(const Job *__restrict__ jobs, JobStats *stats) {
+__global__ void jobMinMax(const Job *__restrict__ jobs, JobStatsDev stats) {
     __shared__ float sLo[8], sHi[8];
     __shared__ unsigned long long sN[8];
     const Job job = jobs[blockIdx.y];
@@ -83,9 +93,9 @@ __global__ void jobMinMax(const Job *__restrict__ jobs, JobStats *stats) {
     if (threadIdx.x == 0) {
         for (int w = 1; w < (blockDim.x >> 5); ++w) { lo = fminf(lo, sLo[w]); hi = fmaxf(hi, sHi[w]); finite += sN[w]; }
         if (finite) {
-            atomicMinFloat(&stats[blockIdx.y].lo, lo);
-            atomicMaxFloat(&stats[blockIdx.y].hi, hi);
-            atomicAdd(&stats[blockIdx.y].finite, finite);
+            atomicMinFloat(&stats.lo[blockIdx.y], lo);
+            atomicMaxFloat(&stats.hi[blockIdx.y], hi);
+            atomicAdd(&stats.finite[blockIdx.y], finite);
         }
     }
 }
@@ -171,13 +181,27 @@ size_t histCalibrationWorkspaceBytes(int T, int B, int I, int H) {
     for (int k = 0; k < 4; ++k) ws.take<float>(rows * C);
     for (int k = 0; k < 3; ++k) ws.take<float>(rows * H);
     ws.take<Job>(kMaxJobs);
-    ws.take<JobStats>(kMaxJobs);
+    ws.take<float>(kMaxJobs);
+    ws.take<float>(kMaxJobs);
+    ws.take<unsigned long long>(kMaxJobs);
     ws.take<uint32_t>(static_cast<size_t>(kMaxJobs) * kMaxSharedBins);
     return ws.used() + 1024;
 }
 
 void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_config &cfg, rxmet_lstm_ranges *ranges,
-                          rxmet_lstm_histograms *hs, void *workspace, size_t workspaceBytes, cudaStream_t st) {
+                          rxmet_lstm_histograms *hs, void *workspace, size_t workspaceBytes, cudaStream_t st,
+                          const rxmet_exchange *exchange) {
+    // Data parallel (exchange set): every rank holds a shard of the batch.  The ranks reduce the range
+    // statistics and the finite extremes / counts of every observed tensor, bin on the common range and
+    // sum the bin counts, so that every rank merges the histogram one process would build on the
+    // concatenated batch (the per-batch collection of the reference: histogram.cc:145-193).
+    const unsigned long long world = exchange ? static_cast<unsigned long long>(std::max(exchange->world_size, 1)) : 1ull;
+    auto reduce = [&](int kind, void *data, uint64_t count) {
+        if (!exchange) return;
+        RXMET_REQUIRE(exchange->reduce != nullptr, "exchange without a reduce function");
+        if (exchange->reduce(kind, data, count, st, exchange->user) != 0)
+            fail(RXMET_ERR_INVALID_ARGUMENT, "the exchange hook reported a failure (kind %d)", kind);
+    };
     const int T = user.T, B = user.B, I = user.I, H = user.H, C = 4 * H;
     RXMET_REQUIRE(hs->hidden_size == H, "histogram collectors were made for hidden_size=%d, call has H=%d", hs->hidden_size, H);
     const int bins = hs->num_bins;
@@ -197,7 +221,10 @@ void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_c
     tr.cell_tanh_outputs = ws.take<float>(rows * H);
     tr.hidden_outputs = ws.take<float>(rows * H);
     Job *jobsDev = ws.take<Job>(kMaxJobs);
-    JobStats *statsDev = ws.take<JobStats>(kMaxJobs);
+    JobStatsDev statsDev{};
+    statsDev.lo = ws.take<float>(kMaxJobs);
+    statsDev.hi = ws.take<float>(kMaxJobs);
+    statsDev.finite = ws.take<unsigned long long>(kMaxJobs);
     uint32_t *countsDev = ws.take<uint32_t>(static_cast<size_t>(kMaxJobs) * bins);
 
     ForwardFloatCall call = user;
@@ -238,9 +265,20 @@ void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_c
         jobMinMax<<<dim3(gridFor(largest, 256 * 8), n), 256, 0, st>>>(jobsDev, statsDev);
     }
     afterLaunch("lstmJobMinMax");
+    {
+        const size_t half = statsFloats(H) / 2;
+        reduce(RXMET_REDUCE_MIN_F32, stats, half);
+        reduce(RXMET_REDUCE_MAX_F32, stats + half, half);
+        reduce(RXMET_REDUCE_MIN_F32, statsDev.lo, n);
+        reduce(RXMET_REDUCE_MAX_F32, statsDev.hi, n);
+        reduce(RXMET_REDUCE_SUM_U64, statsDev.finite, n);
+    }
     std::vector<JobStats> jobStats(n);
-    std::vector<float> hostStats(statsFloats(H));
-    RXMET_CUDA(cudaMemcpyAsync(jobStats.data(), statsDev, n * sizeof(JobStats), cudaMemcpyDeviceToHost, st));
+    std::vector<float> hostStats(statsFloats(H)), hostLo(n), hostHi(n);
+    std::vector<unsigned long long> hostFinite(n);
+    RXMET_CUDA(cudaMemcpyAsync(hostLo.data(), statsDev.lo, n * sizeof(float), cudaMemcpyDeviceToHost, st));
+    RXMET_CUDA(cudaMemcpyAsync(hostHi.data(), statsDev.hi, n * sizeof(float), cudaMemcpyDeviceToHost, st));
+    RXMET_CUDA(cudaMemcpyAsync(hostFinite.data(), statsDev.finite, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
     RXMET_CUDA(cudaMemcpyAsync(hostStats.data(), stats, hostStats.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
     // weights for the host-side parameter collectors
     std::vector<float> wIh(static_cast<size_t>(C) * I), wHh(static_cast<size_t>(C) * H), bIh(bias ? C : 0), bHh(bias ? C : 0);
@@ -251,6 +289,7 @@ void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_c
         RXMET_CUDA(cudaMemcpyAsync(bHh.data(), user.biasHh, C * sizeof(float), cudaMemcpyDeviceToHost, st));
     }
     RXMET_CUDA(cudaStreamSynchronize(st));
+    for (int j = 0; j < n; ++j) jobStats[j] = {hostLo[j], hostHi[j], hostFinite[j]};
 
     for (int j = 0; j < n; ++j) {
         const auto range = jobStats[j].finite ? hist::batchRange(jobStats[j].lo, jobStats[j].hi) : std::pair<float, float>{0.0f, 1.0f};
@@ -264,6 +303,7 @@ void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_c
         jobHistogram<<<dim3(gridFor(largest, 256 * 8), n), 256, bins * sizeof(uint32_t), st>>>(jobsDev, bins, countsDev);
     }
     afterLaunch("lstmJobHistogram");
+    reduce(RXMET_REDUCE_SUM_U32, countsDev, static_cast<uint64_t>(n) * bins);
     std::vector<uint32_t> counts(static_cast<size_t>(n) * bins);
     RXMET_CUDA(cudaMemcpyAsync(counts.data(), countsDev, counts.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
     RXMET_CUDA(cudaStreamSynchronize(st));
@@ -281,8 +321,9 @@ void forwardCalibrateHist(const ForwardFloatCall &user, const rxmet_lstm_quant_c
     auto zeros = [&](int op) {  // an absent initial state is observed as B*H zeros
         const auto range = hist::batchRange(0.0f, 0.0f);
         std::fill(asDouble.begin(), asDouble.end(), 0.0);
-        asDouble[hist::binIndex(0.0f, range.first, range.second, bins)] = static_cast<double>(static_cast<uint64_t>(B) * H);
-        hist::mergeBatch(batchOf(op), asDouble.data(), range.first, range.second, static_cast<uint64_t>(B) * H);
+        const uint64_t zerosSeen = world * static_cast<uint64_t>(B) * H;
+        asDouble[hist::binIndex(0.0f, range.first, range.second, bins)] = static_cast<double>(zerosSeen);
+        hist::mergeBatch(batchOf(op), asDouble.data(), range.first, range.second, zerosSeen);
     };
     for (int j = 0; j < n; ++j) {
         if (src[j].op == RXMET_LSTM_OUTPUT && src[j].data == tr.hidden_outputs && !user.h0) zeros(RXMET_LSTM_OUTPUT);
@@ -397,7 +438,62 @@ int rxmet_lstm_forward_calibrate_hist(int T, int B, int I, int H, const float *w
         call.weightIh = weight_ih; call.weightHh = weight_hh; call.biasIh = bias_ih; call.biasHh = bias_hh;
         call.x = x; call.h0 = h0; call.c0 = c0;
         call.output = output; call.finalHidden = final_hidden; call.finalCell = final_cell;
-        lstm::forwardCalibrateHist(call, *config, ranges, hists, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+        lstm::forwardCalibrateHist(call, *config, ranges, hists, workspace, workspace_bytes, static_cast<cudaStream_t>(stream),
+                                   nullptr);
+    });
+}
+
+int rxmet_lstm_forward_calibrate_hist_dp(int T, int B, int I, int H, const float *weight_ih, const float *weight_hh,
+                                         const float *bias_ih, const float *bias_hh, const float *x, const float *h0,
+                                         const float *c0, float *output, float *final_hidden, float *final_cell,
+                                         const rxmet_lstm_quant_config *config, rxmet_lstm_ranges *ranges,
+                                         rxmet_lstm_histograms *hists, void *workspace, size_t workspace_bytes, void *stream,
+                                         const rxmet_exchange *exchange) {
+    return guarded([&] {
+        RXMET_REQUIRE(T > 0 && B > 0 && I > 0 && H > 0, "LSTM dimensions must be positive");
+        RXMET_REQUIRE(weight_ih && weight_hh && x && output && final_hidden && final_cell && config && ranges && hists, "null argument");
+        RXMET_REQUIRE((bias_ih == nullptr) == (bias_hh == nullptr), "bias_ih and bias_hh are given together or not at all");
+        RXMET_REQUIRE((h0 == nullptr) == (c0 == nullptr), "h0 and c0 are given together or not at all");
+        lstm::ForwardFloatCall call{};
+        call.T = T; call.B = B; call.I = I; call.H = H;
+        call.weightIh = weight_ih; call.weightHh = weight_hh; call.biasIh = bias_ih; call.biasHh = bias_hh;
+        call.x = x; call.h0 = h0; call.c0 = c0;
+        call.output = output; call.finalHidden = final_hidden; call.finalCell = final_cell;
+        lstm::forwardCalibrateHist(call, *config, ranges, hists, workspace, workspace_bytes, static_cast<cudaStream_t>(stream),
+                                   exchange);
+    });
+}
+
+int rxmet_lstm_histogram_batch_range(float batch_min, float batch_max, float *range_min, float *range_max) {
+    return guarded([&] {
+        RXMET_REQUIRE(range_min && range_max, "output pointers must not be null");
+        const auto r = lstm::hist::batchRange(batch_min, batch_max);
+        *range_min = r.first;
+        *range_max = r.second;
+    });
+}
+
+int rxmet_lstm_histogram_count_host(float range_min, float range_max, int num_bins, const float *data, uint64_t count,
+                                    uint64_t *counts, uint64_t *finite) {
+    return guarded([&] {
+        RXMET_REQUIRE(num_bins >= 2 && counts && finite && (data || count == 0), "bad arguments");
+        for (uint64_t i = 0; i < count; ++i) {
+            if (!std::isfinite(data[i])) continue;
+            ++counts[lstm::hist::binIndex(data[i], range_min, range_max, num_bins)];
+            ++*finite;
+        }
+    });
+}
+
+int rxmet_lstm_histogram_merge_counts(rxmet_lstm_histogram *h, const uint64_t *counts, float range_min, float range_max,
+                                      uint64_t finite) {
+    return guarded([&] {
+        lstm::checkCollector(h);
+        RXMET_REQUIRE(counts != nullptr, "counts must not be null");
+        if (finite == 0) return;
+        std::vector<double> asDouble(h->num_bins);
+        for (int i = 0; i < h->num_bins; ++i) asDouble[i] = static_cast<double>(counts[i]);
+        lstm::hist::mergeBatch(h, asDouble.data(), range_min, range_max, finite);
     });
 }
 

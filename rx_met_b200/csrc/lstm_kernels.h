@@ -21,7 +21,8 @@ void forwardFloat(const ForwardFloatCall &call, void *workspace, size_t workspac
 // Histogram calibration: float forward of one batch that updates ranges and histogram collectors.
 size_t histCalibrationWorkspaceBytes(int T, int B, int I, int H);
 void forwardCalibrateHist(const ForwardFloatCall &call, const rxmet_lstm_quant_config &config, rxmet_lstm_ranges *ranges,
-                          rxmet_lstm_histograms *hists, void *workspace, size_t workspaceBytes, cudaStream_t stream);
+                          rxmet_lstm_histograms *hists, void *workspace, size_t workspaceBytes, cudaStream_t stream,
+                          const rxmet_exchange *exchange);
 void paramsFromHistograms(const rxmet_lstm_quant_config &config, const rxmet_lstm_ranges &observed,
                           const rxmet_lstm_histograms &hists, int method, float percentile, int inputSize, int hidden,
                           bool bias, float *wIhScale, float *wHhScale, float *bIhScale, float *bHhScale,
@@ -35,8 +36,19 @@ struct ForwardQuantCall {
     const rxmet_lstm_masters *masters;    // optional
 };
 size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H);
+// Picks the byte-code kernels (every grid <= 8 bits, accumulators below 2^24, I and H <= 128) or the
+// wide kernels below.
 void forwardQuant(const ForwardQuantCall &call, const Exec &exec, void *workspace, size_t workspaceBytes,
                   cudaStream_t stream);
+
+// Activation grids up to 16 bits, weight grids up to 8 bits, H <= 512, I <= 256 (lstm_forward_wide.cu).
+bool forwardQuantWideTakes(const Exec &exec, int I, int H, const char **why);
+size_t forwardQuantWideWorkspaceBytes(int T, int B, int I, int H);
+void forwardQuantWide(const ForwardQuantCall &call, const Exec &exec, void *workspace, size_t workspaceBytes,
+                      cudaStream_t stream);
+// c0 [B,H] (null = real zeros) -> centred cell codes, optional q-carrier copy and clamp mask.
+void quantizeCellCodes(const float *c0, int B, int H, const ScalarExec &scalar, float *centred, float *carrier,
+                       uint8_t *mask, cudaStream_t stream);
 
 // How a saved tensor is turned into real values while it is loaded: real = (value - zeroPoint) * scale.
 // The float backward uses {1, 0}; the QAT backward passes the grid of each saved q-carrier tensor.

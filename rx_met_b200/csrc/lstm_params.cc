@@ -323,7 +323,6 @@ float sigmoidReal(float v) {
 
 void buildTable(const rxmet_lstm_quant_params &p, int inOp, int outOp, bool isTanh, int32_t *table) {
     const Grid gi = gridOf(p.config, inOp), g = gridOf(p.config, outOp);
-    for (int i = 0; i < kTableSize; ++i) table[i] = 0;
     for (int64_t q = gi.lo; q <= gi.hi; ++q) {
         const float real = static_cast<float>((static_cast<double>(q) - p.zero_point[inOp]) * static_cast<double>(p.scale[inOp]));
         const float act = isTanh ? std::tanh(real) : sigmoidReal(real);
@@ -531,10 +530,43 @@ std::shared_ptr<const Exec> deriveExec(const rxmet_lstm_quant_params &p, bool re
         for (int t = 0; t < kTables; ++t)
             buildTable(p, tableIn[t], tableOut[t], t == 2 || t == 4, e->tables.data() + static_cast<size_t>(t) * kTableSize);
     }
+    bool wideFit = true;
+    for (int t = 0; t < kTables; ++t)
+        wideFit = wideFit && p.config.bitwidth[tableIn[t]] <= 16 && p.config.bitwidth[tableOut[t]] <= 24;
+    if (wideFit) {
+        size_t total = 0;
+        for (int t = 0; t < kTables; ++t) {
+            e->wide.offset[t] = static_cast<int>(total);
+            total += size_t{1} << p.config.bitwidth[tableIn[t]];
+        }
+        e->wide.entries.assign(total, 0);
+        for (int t = 0; t < kTables; ++t)
+            buildTable(p, tableIn[t], tableOut[t], t == 2 || t == 4, e->wide.entries.data() + e->wide.offset[t]);
+    }
+    e->weightsFitBytes = p.config.bitwidth[RXMET_LSTM_WEIGHT_IH] <= 8 && p.config.bitwidth[RXMET_LSTM_WEIGHT_HH] <= 8;
+    const int actBits = std::max(p.config.bitwidth[RXMET_LSTM_INPUT], p.config.bitwidth[RXMET_LSTM_OUTPUT]);
+    e->activationPlanes = actBits <= 8 ? 1 : (actBits <= 16 ? 2 : 0);
     std::lock_guard<std::mutex> lock(mutex);
     if (cache.size() > 64) cache.clear();
     cache[key] = e;
     return e;
+}
+
+const int32_t *Exec::wideTablesOnDevice() const {
+    int device = 0;
+    RXMET_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(deviceLock);
+    for (const auto &entry : deviceTables)
+        if (entry.first == device) return entry.second.get();
+    RXMET_REQUIRE(!wide.entries.empty(), "activation tables of this parameter set were not built");
+    int32_t *buffer = nullptr;
+    const size_t bytes = wide.entries.size() * sizeof(int32_t);
+    RXMET_CUDA(cudaMalloc(reinterpret_cast<void **>(&buffer), bytes));
+    std::shared_ptr<int32_t> owner(buffer, [](int32_t *ptr) { cudaFree(ptr); });
+    // synchronous on purpose: the entries are pageable host memory and the buffer is shared by every stream
+    RXMET_CUDA(cudaMemcpy(buffer, wide.entries.data(), bytes, cudaMemcpyHostToDevice));
+    deviceTables.emplace_back(device, owner);
+    return buffer;
 }
 
 }  // namespace lstm

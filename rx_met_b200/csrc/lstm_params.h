@@ -5,6 +5,8 @@
 
 #include <cstdint>
 #include <memory>
+#include <mutex>
+#include <utility>
 #include <vector>
 
 #include "rxmet_b200_lstm.h"
@@ -75,12 +77,27 @@ enum ChannelField {
 constexpr int kTableSize = 256;
 constexpr int kTables = 5;
 
+// Activation tables for grids of 9 to 16 bits (the five tables back to back, table t has
+// 2^bits(input grid of t) entries in the same entry format).  They are too large for shared memory and
+// live in device memory, uploaded once per parameter set and device.
+struct WideTables {
+    std::vector<int32_t> entries;
+    int offset[kTables] = {};
+};
+
 struct Exec {
     int hidden = 0;
     ScalarExec scalar{};
     std::vector<float> channel;            // kChannelFields * 4H
-    std::vector<int32_t> tables;           // kTables * kTableSize
+    std::vector<int32_t> tables;           // kTables * kTableSize; empty when a table input is wider than 8 bits
+    WideTables wide;                       // filled instead when every table input has at most 16 bits
     bool exactAccumulators = false;        // every integer accumulator stays below 2^24
+    bool weightsFitBytes = false;          // weight_ih and weight_hh grids of at most 8 bits
+    int activationPlanes = 1;              // byte planes that hold an input / hidden code: 1 (<= 8 bit) or 2 (<= 16 bit); 0 = wider
+    // Device copy of wide.entries on the current device (cudaMalloc on first use, freed with the Exec).
+    const int32_t *wideTablesOnDevice() const;
+    mutable std::mutex deviceLock;
+    mutable std::vector<std::pair<int, std::shared_ptr<int32_t>>> deviceTables;  // (device ordinal, buffer)
 };
 
 // Cached on the content of `params`: callers pass the same encodings on every step.

@@ -28,6 +28,30 @@ use_real_activation = False
 _FMAX = 3.4028234663852886e38
 
 
+# Data-parallel calibration (no counterpart in the reference's module): with a process group set here, every
+# rank passes its shard of each calibration batch to forward_calibrate(); min/max statistics and histogram bin
+# counts are all-reduced inside the batch, so all ranks end with the collectors one process would hold after
+# the concatenated batches.
+_calibration_group = None
+_exchange_cache = {}
+
+
+def set_calibration_process_group(group) -> None:
+    global _calibration_group
+    _calibration_group = group
+    _exchange_cache.clear()
+
+
+def _exchange_for(device):
+    if _calibration_group is None:
+        return None
+    key = str(device)
+    if key not in _exchange_cache:
+        from .data_parallel import make_exchange
+        _exchange_cache[key] = make_exchange(_calibration_group, device)
+    return _exchange_cache[key]
+
+
 def init_gru_cublas() -> None:
     """Kept for interface compatibility; the kernels do not use cuBLAS."""
     cabi.load_library()
@@ -382,10 +406,12 @@ def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_si
         v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=dev)
         cfg = (bitwidth_config or OperatorQuantConfig())._to_c()
         ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(3, T, B, I, H))
+        exchange = _exchange_for(dev)
         with torch.cuda.device(dev):
-            cabi.check(lib.rxmet_gru_forward_calibrate_hist(
+            cabi.check(lib.rxmet_gru_forward_calibrate_hist_dp(
                 T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v), _ptr(h), _ptr(v), C.byref(cfg),
-                C.byref(hist_collectors._set.c), _ptr(ws), C.c_size_t(ws.numel()), _stream(dev)), "forward_calibrate")
+                C.byref(hist_collectors._set.c), _ptr(ws), C.c_size_t(ws.numel()), _stream(dev),
+                C.byref(exchange) if exchange is not None else None), "forward_calibrate")
         return h, v
     if method != "minmax":
         raise ValueError(f"unknown calib_method {calib_method!r}")
@@ -401,10 +427,25 @@ def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_si
     ranges, keep = quant_ranges._to_c()
     nbytes = lib.rxmet_gru_workspace_bytes(0, T, B, I, H)
     ws = _workspace(dev, nbytes)
-    with torch.cuda.device(dev):
-        cabi.check(lib.rxmet_gru_forward_calibrate_minmax(
-            T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v), _ptr(h), _ptr(v),
-            C.byref(ranges), _ptr(ws), C.c_size_t(ws.numel()), _stream(dev)), "forward_calibrate")
+    if _calibration_group is not None:
+        # sharded batch: the packed extremes of this rank's shard are all-reduced before they are folded
+        import torch.distributed as dist
+        stats = torch.empty(lib.rxmet_gru_stats_floats(H), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            cabi.check(lib.rxmet_gru_forward_calibrate_stats(
+                T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v), _ptr(h), _ptr(v), _ptr(stats),
+                _ptr(ws), C.c_size_t(ws.numel()), _stream(dev)), "forward_calibrate")
+        half = stats.numel() // 2
+        dist.all_reduce(stats[:half], op=dist.ReduceOp.MIN, group=_calibration_group)
+        dist.all_reduce(stats[half:], op=dist.ReduceOp.MAX, group=_calibration_group)
+        host = stats.cpu().contiguous()
+        cabi.check(lib.rxmet_gru_ranges_fold_stats(C.byref(ranges), C.cast(host.data_ptr(), C.POINTER(C.c_float))),
+                   "ranges_fold_stats")
+    else:
+        with torch.cuda.device(dev):
+            cabi.check(lib.rxmet_gru_forward_calibrate_minmax(
+                T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v), _ptr(h), _ptr(v),
+                C.byref(ranges), _ptr(ws), C.c_size_t(ws.numel()), _stream(dev)), "forward_calibrate")
     quant_ranges._from_c(ranges, keep)
     return h, v
 

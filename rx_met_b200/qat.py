@@ -24,7 +24,11 @@ def _p(t: Optional[torch.Tensor]):
 
 class GruQatStep:
     def __init__(self, T: int, B: int, I: int, H: int, device: torch.device,
-                 config: Optional[OperatorQuantConfig] = None, process_group=None, seed: int = 0):
+                 config: Optional[OperatorQuantConfig] = None, process_group=None, seed: int = 0,
+                 weights: Optional[torch.Tensor] = None, grads: Optional[torch.Tensor] = None):
+        """`weights` / `grads`: optional flat float32 device tensors of `parameter_count(I, H)` elements that
+        this object uses as its master weights and gradient buffer (slices of a larger flat buffer, so that a
+        stack of layers all-reduces and updates in one operation); the caller initialises `weights`."""
         self.lib = cabi.load_library()
         self.T, self.B, self.I, self.H = T, B, I, H
         self.device = torch.device(device)
@@ -35,11 +39,16 @@ class GruQatStep:
         f32 = dict(dtype=torch.float32, device=self.device)
         # master weights (gate order z,r,n; W [I,3H], R [H,3H]) and their gradients, flat
         sizes = [I * C3, H * C3, C3, C3]
-        self.flat_w = torch.empty(sum(sizes), **f32)
-        self.flat_g = torch.zeros(sum(sizes), **f32)
-        gen = torch.Generator(device="cpu").manual_seed(seed)
-        k = 1.0 / (H ** 0.5)
-        self.flat_w.copy_((torch.rand(sum(sizes), generator=gen) * 2 - 1) * k)  # same on every rank
+        if weights is not None:
+            if weights.numel() != sum(sizes) or grads is None or grads.numel() != sum(sizes):
+                raise ValueError("weights and grads must both hold parameter_count(I, H) elements")
+            self.flat_w, self.flat_g = weights, grads
+        else:
+            self.flat_w = torch.empty(sum(sizes), **f32)
+            self.flat_g = torch.zeros(sum(sizes), **f32)
+            gen = torch.Generator(device="cpu").manual_seed(seed)
+            k = 1.0 / (H ** 0.5)
+            self.flat_w.copy_((torch.rand(sum(sizes), generator=gen) * 2 - 1) * k)  # same on every rank
         offs = [0]
         for s in sizes:
             offs.append(offs[-1] + s)
@@ -79,29 +88,47 @@ class GruQatStep:
         self._c_params = None
         self._keep = None
 
+    @staticmethod
+    def parameter_count(I: int, H: int) -> int:
+        """Elements of W [I,3H], R [H,3H], bw [3H] and br [3H] together."""
+        return (I + H + 2) * 3 * H
+
     # ---- calibration -----------------------------------------------------
     def calibrate(self, batches) -> GRUQuantParams:
         """min/max calibration over an iterable of [T,B,I] device tensors.  With a process group
         the per-batch statistics are all-reduced (MIN / MAX), so every rank derives the same
         encodings as one process would on the concatenated batch."""
-        from .gru_interface_binding import GRUQuantizationRanges, calculate_gru_quantitative_parameters
-        ranges = GRUQuantizationRanges(self.H)
-        c_ranges, keep = ranges._to_c()
-        half = self.stats.numel() // 2
+        self.begin_calibration()
         for x in batches:
-            with torch.cuda.device(self.device):
-                cabi.check(self.lib.rxmet_gru_forward_calibrate_stats(
-                    self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
-                    _p(self.h), _p(self.v), _p(self.stats), _p(self.ws), C.c_size_t(self.ws.numel()), self._stream()),
-                    "forward_calibrate_stats")
-            if self.group is not None:
-                torch.distributed.all_reduce(self.stats[:half], op=torch.distributed.ReduceOp.MIN, group=self.group)
-                torch.distributed.all_reduce(self.stats[half:], op=torch.distributed.ReduceOp.MAX, group=self.group)
-            host = self.stats.cpu().contiguous()
-            cabi.check(self.lib.rxmet_gru_ranges_fold_stats(
-                C.byref(c_ranges), C.cast(host.data_ptr(), C.POINTER(C.c_float))), "ranges_fold_stats")
-        ranges._from_c(c_ranges, keep)
-        self.set_params(calculate_gru_quantitative_parameters(ranges, self.config))
+            self.observe(x)
+        return self.finish_calibration()
+
+    def begin_calibration(self) -> None:
+        from .gru_interface_binding import GRUQuantizationRanges
+        self._ranges = GRUQuantizationRanges(self.H)
+        self._c_ranges, self._ranges_keep = self._ranges._to_c()
+
+    def observe(self, x: torch.Tensor) -> torch.Tensor:
+        """Float forward of one calibration batch that folds the ranges of all quantization points into the
+        running calibration; returns the float output sequence h[1:] (a view that the next call overwrites)."""
+        half = self.stats.numel() // 2
+        with torch.cuda.device(self.device):
+            cabi.check(self.lib.rxmet_gru_forward_calibrate_stats(
+                self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+                _p(self.h), _p(self.v), _p(self.stats), _p(self.ws), C.c_size_t(self.ws.numel()), self._stream()),
+                "forward_calibrate_stats")
+        if self.group is not None:
+            torch.distributed.all_reduce(self.stats[:half], op=torch.distributed.ReduceOp.MIN, group=self.group)
+            torch.distributed.all_reduce(self.stats[half:], op=torch.distributed.ReduceOp.MAX, group=self.group)
+        host = self.stats.cpu().contiguous()
+        cabi.check(self.lib.rxmet_gru_ranges_fold_stats(
+            C.byref(self._c_ranges), C.cast(host.data_ptr(), C.POINTER(C.c_float))), "ranges_fold_stats")
+        return self.h[1:]
+
+    def finish_calibration(self) -> GRUQuantParams:
+        from .gru_interface_binding import calculate_gru_quantitative_parameters
+        self._ranges._from_c(self._c_ranges, self._ranges_keep)
+        self.set_params(calculate_gru_quantitative_parameters(self._ranges, self.config))
         return self.params
 
     def set_params(self, params: GRUQuantParams) -> None:

@@ -174,8 +174,22 @@ def forward_quantized(prefix, params: L.ParamsBox, T, B, q, exact=False):
     return out, hn, cn, tr
 
 
-def forward_quantized_masked(params: L.ParamsBox, T, B, q):
-    """Oracle only: q-carrier forward that also returns the seven clamp masks."""
+def forward_int32(params: L.ParamsBox, T, B, q):
+    """The reference's exact integer forward (lstmForwardInt32CpuReference) on q-carrier inputs; codes come
+    back as floats.  Returns (out, hn, cn, trace)."""
+    H = params.H
+    out = np.zeros((T, B, H), np.float32)
+    hn, cn = np.zeros((B, H), np.float32), np.zeros((B, H), np.float32)
+    tr = {n: np.zeros((T, B, 4 * H if i < 4 else H), np.float32) for i, n in enumerate(L.TRACE_VALUES)}
+    _call("ref", "forward_int32", C.byref(params.struct), T, B, _fp(q["w_ih"]), _fp(q["w_hh"]), _fp(q["b_ih"]),
+          _fp(q["b_hh"]), _fp(q["x"]), _fp(q["h0"]), _fp(q["c0"]), _fp(out), _fp(hn), _fp(cn),
+          *[_fp(tr[n]) for n in L.TRACE_VALUES])
+    return out, hn, cn, tr
+
+
+def forward_quantized_masked(params: L.ParamsBox, T, B, q, exact_sums=False):
+    """Oracle only: q-carrier forward that also returns the seven clamp masks.  `exact_sums` accumulates the
+    two linear stages exactly (the CUDA library's arithmetic) instead of in sequential float additions."""
     H = params.H
     out = np.zeros((T, B, H), np.float32)
     hn, cn = np.zeros((B, H), np.float32), np.zeros((B, H), np.float32)
@@ -185,7 +199,8 @@ def forward_quantized_masked(params: L.ParamsBox, T, B, q):
     for n in L.TRACE_VALUES:
         setattr(t, n, tr[n].ctypes.data)
         setattr(t, n + "_clamped", mk[n].ctypes.data)
-    _call("orc", "forward_quantized_masked", C.byref(params.struct), T, B, _fp(q["w_ih"]), _fp(q["w_hh"]),
+    _call("orc", "forward_quantized_exact_sums" if exact_sums else "forward_quantized_masked", C.byref(params.struct), T, B,
+          _fp(q["w_ih"]), _fp(q["w_hh"]),
           _fp(q["b_ih"]), _fp(q["b_hh"]), _fp(q["x"]), _fp(q["h0"]), _fp(q["c0"]), _fp(out), _fp(hn), _fp(cn),
           C.byref(t))
     return out, hn, cn, tr, mk

@@ -238,7 +238,12 @@ def test_errors_are_reported_not_faulted():
     with pytest.raises(ValueError):
         m.lstm_forward_quantized(*torch_args(p), False, "{not json")
     wide = L.default_config()
-    wide.bitwidth[L.CELL_STATE] = 16
+    wide.bitwidth[L.CELL_STATE] = 20  # activation grids of up to 16 bits are built
+    wbox, wbundle = calibrated_bundle(wide, p)
+    with pytest.raises(RuntimeError, match="16 bits"):
+        m.lstm_forward_quantized(*torch_args(p), False, wbundle)
+    wide = L.default_config()
+    wide.bitwidth[L.WEIGHT_HH] = 12  # weight grids of up to 8 bits are built
     wbox, wbundle = calibrated_bundle(wide, p)
     with pytest.raises(RuntimeError, match="8 bits"):
         m.lstm_forward_quantized(*torch_args(p), False, wbundle)
