@@ -267,6 +267,16 @@ def run_ours(args):
                        T_override=args.lstm_T)
         print(json.dumps({"profile_only": True, "workload": "lstm"}), flush=True)
         return
+    if args.workload == "kws_body":
+        run_kws_body(args, torch, dist, lib, device, group, rank, world, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload in ("lstm_sweep", "lstm_bi"):
+        flush_ = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        fn = lstm_w4a16_sweep if args.workload == "lstm_sweep" else lstm_bidirectional_a16
+        print(json.dumps({"workload": args.workload, "result": fn(lib, torch, device, flush_, _peaks()[0], args)}), flush=True)
+        return
     T, B, I, H = (WORKLOAD[k] for k in "TBIH")
     cfg = ops.OperatorQuantConfig()
     for name in cabi.OP_NAMES:
@@ -442,7 +452,10 @@ def run_ours(args):
         if world == 1:
             secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak),
                          "affine_qdq": affine_qdq_bandwidth(torch, device, peak),
-                         "lstm_w8a8": lstm_secondary(lib, torch, device, flush)}
+                         "lstm_w8a8": lstm_secondary(lib, torch, device, flush),
+                         "lstm_bidirectional_w8a16": lstm_bidirectional_a16(lib, torch, device, flush, peak, args),
+                         "lstm_h512_w4a16_sweep": lstm_w4a16_sweep(lib, torch, device, flush, peak, args),
+                         "kws_body_qat": kws_body_secondary(torch, device, flush, peak)}
             v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
             cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
         line = {
@@ -543,6 +556,294 @@ def affine_qdq_bandwidth(torch, device, peak_gbs, reps=10, elements=1 << 28):
     return out
 
 
+
+# --------------------------------------------------------------------------
+# Roofline time of a recurrent workload: the slower of (GEMM flops / measured dense tensor peak) and
+# (module-boundary + saved-state bytes / measured HBM copy rate).  The int8 tensor peak is not measured on
+# this pool; the measured bf16 figure stands in for it (conservative for int8).
+# --------------------------------------------------------------------------
+
+def _tensor_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["bf16_tflops_sustained"]) * 1e12, "measured bf16 sustained"
+    return 1.4e15, "fallback bf16 sustained"
+
+
+def _roofline_frac(st_per_s, flops_per_st, bytes_per_st, hbm_gbs):
+    tc, tc_kind = _tensor_peak()
+    t_flops = flops_per_st / tc
+    t_bytes = bytes_per_st / (hbm_gbs * 1e9)
+    bound = "tensor" if t_flops >= t_bytes else "hbm"
+    roof_st_per_s = 1.0 / max(t_flops, t_bytes)
+    return {"bound": bound, "frac": st_per_s / roof_st_per_s, "roofline_st_per_s": roof_st_per_s,
+            "flops_per_st": flops_per_st, "bytes_per_st": bytes_per_st, "tensor_peak": tc_kind}
+
+
+def _event_ms(torch, fn, flush, reps, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / reps
+
+
+def _lstm_weights(torch, device, I, H, seed):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    k = 1.0 / (H ** 0.5)
+    u = lambda *s: ((torch.rand(s, generator=gen) * 2 - 1) * k).to(device)  # noqa: E731  PyTorch-default uniform init
+    return [u(4 * H, I), u(4 * H, H), u(4 * H), u(4 * H)]
+
+
+def _kernel_ms(lib, names, per=1):
+    out = {}
+    for n in names:
+        ms, cnt = C.c_double(), C.c_longlong()
+        lib.rxmet_get_kernel_timing(n.encode(), C.byref(ms), C.byref(cnt))
+        if cnt.value:
+            out[n] = ms.value / per
+    return out
+
+
+_LSTM_WIDE_KERNELS = ["lstmQuantizePlanes", "lstmQuantizeCodes", "lstmPrepChannelsWide", "lstmInputLinearWide", "lstmRecurrentWide",
+                      "lstmRecurrentFloatWide", "lstmRecurrentFloat", "lstmInputLinearFloat", "lstmJobMinMax", "lstmJobHistogram",
+                      "lstmRecurrentBackwardWide", "lstmRecurrentBackward", "lstmGemmNN", "lstmGemmRowsTN", "lstmReduceSplits",
+                      "lstmColumnSums", "lstmDequantWeights", "lstmPackStepMasks", "inputGradUmma", "weightGradUmma",
+                      "lstmReduceWeightGradT", "lstmInputGradNarrow"]
+
+
+def lstm_bidirectional_a16(lib, torch, device, flush, peak_gbs, args):
+    """Bidirectional QuantLSTM I=80, H=128, T=200, batch 128, W8 per-channel symmetric / A16 asymmetric:
+    histogram (SQNR) calibration of two seeded batches through the product's CalibrationSession, then the
+    quantized inference forward of both directions (two streams).  One seq-timestep = one batch element x one
+    time step of BOTH directions."""
+    from rx_met_b200 import _cabi_lstm as L
+    from rx_met_b200 import _quant_lstm as m
+    T, B, I, H = 200, 128, 80, 128
+    cfg = L.mixed_config(8, 16)
+    gen = torch.Generator(device="cpu").manual_seed(77)
+    batches = [torch.randn((T, B, I), generator=gen).to(device) for _ in range(2)]
+    x = torch.randn((T, B, I), generator=gen).to(device)
+    x_rev = x.flip(0).contiguous()
+    dirs = [_lstm_weights(torch, device, I, H, 100 + d) for d in range(2)]
+    sessions = [m.CalibrationSession(m._config_to_json(cfg), I, H, True, "sqnr") for _ in range(2)]
+    t0 = time.perf_counter()
+    for xb in batches:
+        for d, (s, w) in enumerate(zip(sessions, dirs)):
+            s.collect(xb if d == 0 else xb.flip(0).contiguous(), *w)
+    torch.cuda.synchronize()
+    calib_s = time.perf_counter() - t0
+    bundles = [s.finalize(False)["bundle_json"] for s in sessions]
+    side = torch.cuda.Stream(device)
+
+    def forward():
+        main = torch.cuda.current_stream(device)
+        side.wait_stream(main)
+        m.lstm_forward_quantized(x, *dirs[0], None, None, False, bundles[0])
+        with torch.cuda.stream(side):
+            m.lstm_forward_quantized(x_rev, *dirs[1], None, None, False, bundles[1])
+        main.wait_stream(side)
+
+    ms = _event_ms(torch, forward, flush, reps=5)
+    lib.rxmet_reset_kernel_timing(); lib.rxmet_set_kernel_timing(1)
+    m.lstm_forward_quantized(x, *dirs[0], None, None, False, bundles[0])
+    torch.cuda.synchronize()
+    kernels = _kernel_ms(lib, _LSTM_WIDE_KERNELS)
+    lib.rxmet_set_kernel_timing(0)
+    st = T * B
+    st_s = st / (ms * 1e-3)
+    return {"workload": {"T": T, "B": B, "I": I, "H": H, "directions": 2, "quant": "W8 per-channel symmetric, A16 asymmetric"},
+            "calibration": {"method": "sqnr histograms, 2048 bins", "batches": len(batches), "seconds": calib_s,
+                            "seq_timesteps_per_s": len(batches) * st / calib_s},
+            "quantized_forward": {"ms": ms, "seq_timesteps_per_s": st_s,
+                                  "roofline": _roofline_frac(st_s, 425984, 1344, peak_gbs)},
+            "kernel_ms_one_direction": kernels}
+
+
+def lstm_w4a16_sweep(lib, torch, device, flush, peak_gbs, args):
+    """QuantLSTM I=256, H=512, T=1000, W4 per-channel / A16, batch 1, 16, 256, 4096: quantized inference
+    forward at every batch size; QAT forward + backward at 1, 16 and 256 (at 4096 the seven float checkpoint
+    tensors and 14 masks the reference's training interface hands to the backward take more than one GPU's
+    memory: 4,096,000 rows x (4 x 2048 + 3 x 512) x 5 bytes = 199 GB)."""
+    from rx_met_b200 import _cabi_lstm as L
+    from rx_met_b200 import _quant_lstm as m
+    T, I, H = 1000, 256, 512
+    cfg = L.mixed_config(4, 16)
+    w = _lstm_weights(torch, device, I, H, 200)
+    gen = torch.Generator(device="cpu").manual_seed(78)
+    session = m.CalibrationSession(m._config_to_json(cfg), I, H, True, "minmax")
+    session.collect(torch.randn((50, 64, I), generator=gen).to(device), *w)
+    bundle = session.finalize(False)["bundle_json"]
+    out = {"workload": {"T": T, "I": I, "H": H, "quant": "W4 per-channel symmetric, A16 asymmetric"}, "batch": {}}
+    order = ("input", "weight_ih", "weight_hh", "bias_ih", "bias_hh", "h_0", "c_0")
+    for B in (1, 16, 256, 4096):
+        x = torch.randn((T, B, I), generator=gen).to(device)
+        reps = 3 if B <= 256 else 2
+        ms = _event_ms(torch, lambda: m.lstm_forward_quantized(x, *w, None, None, False, bundle), flush, reps, warmup=1)
+        st = T * B
+        entry = {"inference_forward": {"ms": ms, "seq_timesteps_per_s": st / (ms * 1e-3),
+                                       "roofline": _roofline_frac(st / (ms * 1e-3), 3145728, 3072, peak_gbs)}}
+        if B <= 256:
+            g = [torch.randn(s, generator=gen).to(device) for s in [(T, B, H), (B, H), (B, H)]]
+            saved = {}
+
+            def qat():
+                saved["o"] = m.lstm_forward_quantized(x, *w, None, None, False, bundle, "pedantic", False, True)
+                ck = saved["o"][3]
+                m.lstm_backward_qat([ck["quantized_master"][n] for n in order], False, bundle,
+                                    [ck["values"][n] for n in ("gate_outputs", "cell_states", "cell_tanh_outputs", "hidden_outputs")],
+                                    *g, [ck["master_clamp_masks"][n] for n in order], [ck["clamp_masks"][n] for n in L.TRACE_VALUES])
+
+            ms_q = _event_ms(torch, qat, flush, reps=2, warmup=1)
+            entry["qat_forward_backward"] = {"ms": ms_q, "seq_timesteps_per_s": st / (ms_q * 1e-3),
+                                             "roofline": _roofline_frac(st / (ms_q * 1e-3), 9437184, 23000, peak_gbs)}
+            if B == 256:
+                lib.rxmet_reset_kernel_timing(); lib.rxmet_set_kernel_timing(1)
+                qat()
+                torch.cuda.synchronize()
+                entry["kernel_ms_qat_step"] = _kernel_ms(lib, _LSTM_WIDE_KERNELS)
+                lib.rxmet_set_kernel_timing(0)
+            del saved, g
+        out["batch"][str(B)] = entry
+        del x
+        torch.cuda.empty_cache()
+    return out
+
+
+KWS = dict(T=100, B=128, I=40, H=256, layers=3, classes=12)
+
+
+def _kws_engine(torch, device, group, rank):
+    from rx_met_b200.stacked_qat import StackedGruQat, a16_config
+    T, B, I, H = KWS["T"], KWS["B"], KWS["I"], KWS["H"]
+    eng = StackedGruQat(T, B, I, H, KWS["layers"], KWS["classes"], device, a16_config(8, 16), process_group=group, seed=4321)
+    gen = torch.Generator(device="cpu").manual_seed(2000 + rank)
+    xs_host = [torch.randn((T, B, I), generator=gen).clamp_(-4, 4).pin_memory() for _ in range(4)]
+    ys_host = [torch.randint(0, KWS["classes"], (B,), generator=gen).pin_memory() for _ in range(4)]
+    xs = [t.to(device) for t in xs_host]
+    ys = [t.to(device) for t in ys_host]
+    eng.calibrate(xs[:2])
+    return eng, xs_host, ys_host, xs, ys
+
+
+_GRU_KERNELS = ["recurrentForward", "recurrentBackward", "inputLinear", "quantizeTensor", "gemmTN", "gemmNT", "inputGradUmma",
+                "packRecurrentBf16", "weightGradMma", "weightGradUmma", "reduceWeightGrad", "fillCodes", "packStepMasks",
+                "reduceSplits", "columnSums", "channelPrep", "prepareWeights", "dequantCodes", "transposeMatrix"]
+KWS_FLOPS_PER_ST, KWS_BYTES_PER_ST = 16883712, 57000
+
+
+def kws_body_secondary(torch, device, flush, peak_gbs):
+    """The stacked bidirectional QuantGRU QAT step (3 x bi-GRU H=256, 40 -> 512 -> 512, T=100, batch 128 per
+    GPU, W8 per-channel / A16, linear head + cross-entropy) on one GPU."""
+    from rx_met_b200 import _cabi as cabi
+    lib = cabi.load_library()
+    eng, _, _, xs, ys = _kws_engine(torch, device, None, 0)
+    state = {"i": 0}
+
+    def step():
+        eng.step(xs[state["i"] % 4], ys[state["i"] % 4], 1e-3)
+        state["i"] += 1
+
+    ms = _event_ms(torch, step, flush, reps=5)
+    lib.rxmet_reset_kernel_timing(); lib.rxmet_set_kernel_timing(1)
+    step()
+    torch.cuda.synchronize()
+    kernels = _kernel_ms(lib, _GRU_KERNELS)
+    lib.rxmet_set_kernel_timing(0)
+    st = KWS["T"] * KWS["B"]
+    return {"workload": {**KWS, "quant": "W8 per-channel symmetric, A16"}, "ms_per_step": ms, "seq_timesteps_per_s": st / (ms * 1e-3),
+            "roofline": _roofline_frac(st / (ms * 1e-3), KWS_FLOPS_PER_ST, KWS_BYTES_PER_ST, peak_gbs),
+            "kernel_ms_per_step": kernels, "gradient_floats": int(eng.flat_g.numel())}
+
+
+def run_kws_body(args, torch, dist, lib, device, group, rank, world, local_rank):
+    """Bench line of the stacked bidirectional QuantGRU QAT step, batch 128 per GPU (weak scaling)."""
+    eng, xs_host, ys_host, xs, ys = _kws_engine(torch, device, group, rank)
+    T, B = KWS["T"], KWS["B"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    lr = 1e-3
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+            flush.zero_()
+        barrier()
+        l0 = lib.rxmet_kernel_launch_count()
+        start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            start[i].record(); fn(i); stop[i].record()
+            flush.zero_()
+        barrier()
+        timed.launches = lib.rxmet_kernel_launch_count() - l0
+        t = torch.tensor([sum(s.elapsed_time(e) for s, e in zip(start, stop))], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(lambda i: eng.step(xs[i % 4], ys[i % 4], lr), args.steps, args.warmup)
+    launches = timed.launches
+    clocks = sampler.stop() if rank == 0 else None
+    st_per_step = T * B * world
+    value = st_per_step * args.steps / (total_ms * 1e-3)
+
+    # end to end: this step's inputs come from pinned host memory, the loss goes back to the host
+    x_buf, y_buf = torch.empty_like(xs[0]), torch.empty_like(ys[0])
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def e2e(i):
+        x_buf.copy_(xs_host[i % 4], non_blocking=True)
+        y_buf.copy_(ys_host[i % 4], non_blocking=True)
+        loss = eng.step(x_buf, y_buf, lr)
+        loss_host.copy_(loss.reshape(1), non_blocking=True)
+
+    e2e_steps = min(args.steps, 10)
+    e2e_ms = timed(e2e, e2e_steps, 3)
+    torch.cuda.synchronize()
+    if rank != 0:
+        return
+    peak, peak_kind = _peaks()
+    lib.rxmet_reset_kernel_timing(); lib.rxmet_set_kernel_timing(1)
+    eng.step(xs[0], ys[0], 0.0)
+    torch.cuda.synchronize()
+    kernels = _kernel_ms(lib, _GRU_KERNELS)
+    lib.rxmet_set_kernel_timing(0)
+    roof = _roofline_frac(value / world, KWS_FLOPS_PER_ST, KWS_BYTES_PER_ST, peak)
+    top = max(kernels, key=kernels.get)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weight codes x int16 activation codes / int64 accumulate fwd, fp32 bwd", "data": "synthetic",
+        "config": {"workload": "kws_body", **KWS, "global_batch": B * world, "parallelism": f"dp{world}",
+                   "quant": "W8 per-channel symmetric, A16, integer carrier", "l2": "flushed between steps"},
+        "roofline": {"bound": roof["bound"], "kernel": top, "achieved": value / world * (KWS_BYTES_PER_ST if roof["bound"] == "hbm" else KWS_FLOPS_PER_ST) / (1e9 if roof["bound"] == "hbm" else 1e12),
+                     "peak": peak if roof["bound"] == "hbm" else _tensor_peak()[0] / 1e12,
+                     "unit": "GB/s" if roof["bound"] == "hbm" else "TFLOP/s", "frac": roof["frac"],
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "scope": "whole step",
+                     "kernel_ms_per_step": kernels},
+        "cpu_baseline": None,
+        "e2e": {"value": st_per_step * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT, "steps": e2e_steps,
+                "h2d_bytes_per_step": (4 * T * B * KWS["I"] + 8 * B) * world, "d2h_bytes_per_step": 4 * world,
+                "final_loss": float(loss_host[0]), "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks, "gradient_allreduce_bytes": int(eng.flat_g.numel()) * 4,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
     """QuantLSTM at the same shape as the headline GRU workload (T=100, B=256, I=40, H=128, all
     points 8 bit symmetric, per-channel weights): seq-timesteps/s of the quantized inference
@@ -556,8 +857,12 @@ def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
     T = T_override or T
     p = ll.problem(T, 16, I, H, seed=5, wscale=0.15)
     cfg = L.default_config(symmetric_activations=True)
-    _, box = ll.calibrate("orc", cfg, p, np.stack([p["x"]]))
-    bundle = m._params_to_bundle(box)
+    to_dev = lambda a: torch.from_numpy(a).to(device)  # noqa: E731
+    session = m.CalibrationSession(m._config_to_json(cfg), I, H, True, "minmax")   # the product's calibration
+    session.collect(to_dev(p["x"]), to_dev(p["w_ih"]), to_dev(p["w_hh"]), to_dev(p["b_ih"]), to_dev(p["b_hh"]),
+                    to_dev(p["h0"])[None], to_dev(p["c0"])[None])
+    bundle = session.finalize(False)["bundle_json"]
+    box = m._bundle_to_params(bundle)
     gen = torch.Generator(device="cpu").manual_seed(99)
     x = torch.randn((T, B, I), generator=gen).to(device)
     h0 = (torch.randn((1, B, H), generator=gen) * 0.5).to(device)
@@ -646,8 +951,11 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["gru", "lstm", "aimet", "affine"], default="gru",
-                    help="with --profile-only: which training loop to run (the bench line is always the GRU QAT step)")
+    ap.add_argument("--workload", choices=["gru", "lstm", "aimet", "affine", "kws_body", "lstm_sweep", "lstm_bi"], default="gru",
+                    help="gru (default): the headline QAT step.  kws_body: the stacked bidirectional QuantGRU QAT step "
+                         "(its own bench line, any --gpus).  lstm_sweep / lstm_bi: print the QuantLSTM W4/A16 batch sweep or "
+                         "the bidirectional W8/A16 calibration + forward as a JSON object (1 GPU).  With --profile-only: "
+                         "which loop to run under a profiler")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
     ap.add_argument("--e2e-copy", choices=["kernel", "dma"], default="kernel",
                     help="how the end-to-end leg moves a step's inputs from pinned host memory: the library's staging "

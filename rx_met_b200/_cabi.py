@@ -94,6 +94,13 @@ class Histogram(C.Structure):
                 ("range_limit_set", C.c_int32), ("range_limit_min", C.c_float), ("range_limit_max", C.c_float)]
 
 
+class HistogramPlan(C.Structure):
+    """``rxmet_histogram_plan``: what a batch with given global extremes does to a collector."""
+    _fields_ = [("mode", C.c_int32), ("lo", C.c_float), ("hi", C.c_float), ("inv_bin_width", C.c_float),
+                ("new_min", C.c_float), ("new_max", C.c_float), ("data_min", C.c_float), ("data_max", C.c_float),
+                ("limit_min", C.c_float), ("limit_max", C.c_float)]
+
+
 class GruHistograms(C.Structure):
     """``rxmet_gru_histograms``."""
     _fields_ = [("hidden", C.c_int32), ("num_bins", C.c_int32), ("point", Histogram * NUM_OPS),
