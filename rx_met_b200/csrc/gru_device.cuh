@@ -13,6 +13,15 @@
 namespace rxmet {
 namespace gru {
 
+// Gate rescales the input projection may apply on top of its own output rescale: when enabled, what it
+// stores is rescale(code - zero point) with the rescale of the gate the column belongs to (the ih
+// contribution to the gate input, which does not depend on the recurrent state).
+struct PreRescale {
+    int enabled;
+    int hidden;
+    Rescale toGate[3];
+};
+
 // round_half_even(x / 2^n) on the magnitude, sign restored afterwards; n <= 0
 // shifts left (quantize_ops_helper.h:201-224).
 __device__ __forceinline__ int64_t rshiftRound(int64_t x, int n) {
@@ -242,7 +251,7 @@ __device__ __forceinline__ int32_t rescaleSmallPrepared(int32_t x, const Prepare
 }
 // The general rounding shift behind a call: a call is never evaluated speculatively, so code that
 // picks between it and the 32-bit form per value pays for the 64-bit form only when it is taken.
-__device__ __noinline__ int32_t rshiftRoundCalled(int64_t x, int n) { return static_cast<int32_t>(rshiftRound(x, n)); }
+static __device__ __noinline__ int32_t rshiftRoundCalled(int64_t x, int n) { return static_cast<int32_t>(rshiftRound(x, n)); }
 
 __device__ __forceinline__ int32_t rescaleProductPrepared(int32_t x, const PreparedRescale &p) {
     const int64_t prod = static_cast<int64_t>(x) * p.mult;

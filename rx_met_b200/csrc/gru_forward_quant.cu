@@ -30,6 +30,7 @@
 #include "common.h"
 #include "gru_device.cuh"
 #include "gru_forward_quant.h"
+#include "input_proj_umma.h"
 
 namespace rxmet {
 namespace gru {
@@ -282,12 +283,6 @@ constexpr int kLinearRows = 8;
 // When `pre.enabled`, the stored value is not the ih code itself but its contribution to the gate
 // input, rescale(code - zp) with the rescale of the gate the column belongs to: that term does not
 // depend on the recurrent state, so it is computed here once instead of in every step.
-struct PreRescale {
-    int enabled;
-    int hidden;
-    Rescale toGate[3];
-};
-
 template <class WT, class AT, class LT>
 __global__ void inputLinear(const typename Dot<WT, AT>::AWord *__restrict__ x, int rows, int kWords, int channels,
                             const typename Dot<WT, AT>::WWord *__restrict__ w, const int64_t *__restrict__ comp,
@@ -469,7 +464,8 @@ struct RecurrentArgs {
     float *v;             // [T][B][4H] dequantized
     int32_t *hq;          // optional [T+1][B][H]
     int32_t *vq;          // optional [T][B][4H]
-    uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;  // optional
+    uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;
+    const int *poison;    // optional device word: non-zero = the ih codes are not valid, write NaN
 };
 
 template <class WT, class AT, class LT, int BT>
@@ -616,6 +612,17 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
 
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    if (a.poison != nullptr && *reinterpret_cast<const volatile int *>(a.poison) != 0) {
+        // the producer of the ih codes gave up on a bounded wait: make that loud instead of computing on garbage
+        const float nan = __int_as_float(0x7fc00000);
+        for (int t = 0; t <= a.T; ++t)
+            for (int i = tid; i < nb * H; i += nthreads)
+                a.h[(static_cast<size_t>(t) * a.B + b0 + i / H) * H + i % H] = nan;
+        for (int t = 0; t < a.T; ++t)
+            for (int i = tid; i < nb * 4 * H; i += nthreads)
+                a.v[(static_cast<size_t>(t) * a.B + b0 + i / (4 * H)) * 4 * H + i % (4 * H)] = nan;
+        return;
+    }
     for (int i = tid; i < static_cast<int>(sizeof(GateExec) / 4); i += nthreads)
         reinterpret_cast<int32_t *>(&g)[i] = reinterpret_cast<const int32_t *>(&gateParam)[i];
     DirectTables tab{};
@@ -909,6 +916,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     auto *ihCodes = ws.take<LT>(rows * C);
     auto *comp = ws.take<int64_t>(4 * static_cast<size_t>(C));
     int64_t *compX = comp, *biasX = comp + C, *compH = comp + 2 * C, *biasH = comp + 3 * C;
+    int *projStatus = ws.take<int>(1);  // set by the tensor-core input projection when a bounded wait gave up
 
     // 1. codes (8-bit weights: together with the per-channel terms of step 2)
     constexpr bool kPackedWeights = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value;
@@ -1021,12 +1029,29 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     pre.toGate[0] = g.ih_to_update; pre.toGate[1] = g.ih_to_reset; pre.toGate[2] = g.ih_to_new;
 
     // 3. input projection, all steps
+    bool tensorProjection = false;
     {
         const int block = std::min(padTo(C, 32), 512);
         const int kw4 = (iWords + 3) / 4;
         bool specialised = false;
         if constexpr (kI8) {
-            if (C <= 512 && kw4 <= 4 && block >= kI8Rows * kw4 * 4 && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr) {
+            if (iproj::eligible(C, H, iWords, xCodes, ihCodes, mk.weight_ih_linear) && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr) {
+                // tcgen05 kind::i8 GEMM with the fused epilogue
+                specialised = true;
+                tensorProjection = true;
+                RXMET_CUDA(cudaMemsetAsync(projStatus, 0, sizeof(int), st));
+                iproj::Problem pj{};
+                pj.x = reinterpret_cast<const int32_t *>(xCodes); pj.rows = static_cast<int>(rows); pj.kWords = iWords;
+                pj.w = reinterpret_cast<const int32_t *>(wCodes); pj.C = C;
+                pj.comp = compX; pj.biasAcc = biasX; pj.rescale = ch.gemmX;
+                pj.zpOut = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR]; pj.lo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR];
+                pj.hi = g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR];
+                pj.pre = pre; pj.out = reinterpret_cast<int16_t *>(ihCodes); pj.mask = mk.weight_ih_linear; pj.status = projStatus;
+                iproj::launch(pj, sms, st);
+            }
+        }
+        if constexpr (kI8) {
+            if (!specialised && C <= 512 && kw4 <= 4 && block >= kI8Rows * kw4 * 4 && std::getenv("RXMET_GRU_FWD_GENERIC") == nullptr) {
                 specialised = true;
                 const int blocks = static_cast<int>((rows + kI8Rows - 1) / kI8Rows);
                 const int32_t zp = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR], qlo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR],
@@ -1065,6 +1090,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     a.comp = compH; a.biasAcc = biasH; a.rescale = ch.gemmH;
     a.h = call.h; a.v = call.v; a.hq = call.h_q; a.vq = call.v_q;
     a.maskHh = mk.weight_hh_linear; a.maskGateIn = mk.gate_input; a.maskGateOut = mk.gate_output; a.maskH = mk.h;
+    a.poison = tensorProjection ? projStatus : nullptr;
     if (mk.gate_input || mk.gate_output || mk.h)
         RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
 
@@ -1131,6 +1157,7 @@ void sizeTyped(WorkspaceSizer &ws, int T, int B, int I, int H) {
     ws.take<AT>(static_cast<size_t>(B) * hWords * D::kPack);
     ws.take<LT>(rows * C);
     ws.take<int64_t>(4 * C);
+    ws.take<int>(1);
 }
 
 }  // namespace
