@@ -16,6 +16,8 @@
 #include <string>
 
 #include "gru_interface.h"  // reference: quantGRUForwardInt, quantGRUForwardFP, quantGRUBackward, haste*
+#include "quantize_ops_helper.h"  // reference: dev::dequantificationFPInplace
+#include "scale_encoding.h"       // reference: toFixedScale
 #include "ref_shim_gru_convert.h"
 #include "rxmet_b200.h"
 
@@ -96,6 +98,19 @@ int refcuda_gru_backward_quant(int T, int B, int I, int H, const float *W_t, con
         } else {
             hasteGRUBackward(T, B, I, H, W_t, R_t, bw, br, x_t, dh_new, h, v, handle(), dx, dW, dR, dbw, dbr, dh);
         }
+    });
+}
+
+// What the reference's binding does to the saved float code caches before its backward
+// (gru_interface_binding.cc:842-866): weights and biases through dequantizeGRUWeights, the input codes
+// through dev::dequantificationFPInplace with the decoded x scale.  All five arrays are rewritten in place.
+int refcuda_gru_dequantize_saved(int I, int H, long long x_count, float *W_q, float *R_q, float *bw_q, float *br_q,
+                                 float *x_q, const rxmet_gru_quant_params *params) {
+    return guarded([&] {
+        const GRUQuantParams qp = refshim::toRefParams(*params);
+        dequantizeGRUWeights(W_q, R_q, bw_q, br_q, static_cast<size_t>(I), static_cast<size_t>(H), qp);
+        dev::dequantificationFPInplace(x_q, static_cast<size_t>(x_count), toFixedScale(qp.x_, qp.bitwidth_config_.usePOT2_),
+                                       qp.x_.zero_point);
     });
 }
 

@@ -356,6 +356,142 @@ __global__ void __launch_bounds__(384) recurrentBackwardQ(const __grid_constant_
     }
 }
 
+// ---- hidden sizes above 128: recurrent weight codes in shared memory ---------------------------
+//
+// For H > 128 the weight rows no longer fit the registers of recurrentBackwardQ / the fragments of the
+// tensor-core kernel, and as fp32 or bf16 they do not fit shared memory either (3H x H values; 393 KB as
+// bf16 at H = 256).  As 8-bit codes they do (196 KB at H = 256): word (c / 4, k) holds the codes
+// R[k][4 (c / 4) .. + 3], stored with bit 7 flipped so that a byte permute builds the float 2^23 + (code + 128)
+// directly and one subtraction yields the code (two full-rate instructions per weight, no integer-to-float
+// conversion).  The per-column scale is folded into dq as in the kernels above.  Thread (k, part) sums a
+// part of the 3H columns for hidden row k; the parts meet in shared memory.  Per-step operands are fetched
+// one step ahead.
+struct BackwardCodesArgs {
+    BackwardQArgs q;
+    const int32_t *Rq;  // [H][3H] integer codes as saved by the forward
+    int HP, parts;
+};
+
+template <int RB>
+__global__ void __launch_bounds__(512, 1) recurrentBackwardCodes(const __grid_constant__ BackwardCodesArgs ca) {
+    const BackwardQArgs &a = ca.q;
+    const int H = a.H, C = 3 * a.H, CW = C / 4, HP = ca.HP, P = ca.parts;
+    extern __shared__ __align__(16) unsigned char smemRawB[];
+    uint32_t *Rw = reinterpret_cast<uint32_t *>(smemRawB);             // [CW][H]
+    float *dqS = reinterpret_cast<float *>(Rw + static_cast<size_t>(CW) * H);  // [RB][C]
+    float *partS = dqS + RB * C;                                        // [P][RB][H]
+    const int tid = threadIdx.x, k = tid % HP, part = tid / HP;
+    const bool active = k < H;
+    const int b0 = blockIdx.x * RB;
+    for (int i = tid; i < CW * H; i += blockDim.x) {
+        const int cw = i / H, row = i - cw * H;
+        const int4 c4 = *reinterpret_cast<const int4 *>(ca.Rq + static_cast<size_t>(row) * C + 4 * cw);
+        const uint32_t word = (static_cast<uint32_t>(c4.x) & 0xffu) | ((static_cast<uint32_t>(c4.y) & 0xffu) << 8) |
+                              ((static_cast<uint32_t>(c4.z) & 0xffu) << 16) | ((static_cast<uint32_t>(c4.w) & 0xffu) << 24);
+        Rw[i] = word ^ 0x80808080u;
+    }
+    for (int i = tid; i < RB * C; i += blockDim.x) dqS[i] = 0.0f;
+    for (int i = tid; i < P * RB * H; i += blockDim.x) partS[i] = 0.0f;
+    const bool owner = active && part == 0;  // the pointwise derivative of (rows, k) runs in part 0
+    float scale[3] = {1.0f, 1.0f, 1.0f};
+    if (owner) {
+        scale[0] = a.scaleR[k]; scale[1] = a.scaleR[H + k]; scale[2] = a.scaleR[2 * H + k];
+    }
+    float dhBase[RB];
+    StepOperands cur[RB], nxt[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) dhBase[r] = 0.0f;
+    auto fetch = [&](int t, StepOperands (&dst)[RB]) {
+        if (!owner) return;
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            const int b = b0 + r;
+            if (b >= a.B) continue;
+            const size_t row = static_cast<size_t>(t) * a.B + b, hi = row * H + k;
+            const float *vRow = a.v + row * 4 * H;
+            StepOperands o;
+            o.z = vRow[k]; o.r = vRow[H + k]; o.g = vRow[2 * H + k]; o.qg = vRow[3 * H + k];
+            o.hOld = a.h[hi];
+            o.dhNew = a.dhNew[hi + static_cast<size_t>(a.B) * H];
+            o.keepBits = a.stepBits ? a.stepBits[hi] : 0x1fffu;
+            dst[r] = o;
+        }
+    };
+    fetch(a.T - 1, cur);
+    __syncthreads();
+
+    const int cwBegin = CW * part / P, cwEnd = CW * (part + 1) / P;
+    for (int t = a.T - 1; t >= 0; --t) {
+        if (t > 0) fetch(t - 1, nxt);
+        if (owner) {
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const int b = b0 + r;
+                if (b >= a.B) continue;
+                const size_t gi = (static_cast<size_t>(t) * a.B + b) * C + k;
+                const StepOperands o = cur[r];
+                auto keep = [&](int pos) { return static_cast<float>((o.keepBits >> pos) & 1u); };
+                float carried = dhBase[r];
+                for (int p2 = 0; p2 < P; ++p2) carried += partS[(p2 * RB + r) * H + k];
+                const float dhTotal = (o.dhNew + carried) * keep(12);
+                dhBase[r] = o.z * dhTotal;
+                const float dg = (1.0f - o.z) * dhTotal;
+                const float dz = (o.hOld - o.g) * dhTotal;
+                const float dpG = (1.0f - o.g * o.g) * dg * keep(2) * keep(5);
+                const float dqG = dpG * o.r;
+                const float dr = dpG * o.qg;
+                const float dpR = (o.r * (1.0f - o.r)) * dr;
+                const float dpZ = (o.z * (1.0f - o.z)) * dz;
+                const float kz = keep(0) * keep(3), kr = keep(1) * keep(4);
+                const float pz = dpZ * kz * keep(9), pr = dpR * kr * keep(10), pg = dpG * keep(11);
+                const float qz = dpZ * kz * keep(6), qr = dpR * kr * keep(7), qn = dqG * keep(8);
+                a.dp[gi] = pz; a.dp[gi + H] = pr; a.dp[gi + 2 * H] = pg;
+                a.dq[gi] = qz; a.dq[gi + H] = qr; a.dq[gi + 2 * H] = qn;
+                float *dqRow = dqS + r * C;
+                dqRow[k] = qz * scale[0]; dqRow[H + k] = qr * scale[1]; dqRow[2 * H + k] = qn * scale[2];
+            }
+        }
+        __syncthreads();
+        if (active) {
+            float acc[RB];
+#pragma unroll
+            for (int r = 0; r < RB; ++r) acc[r] = 0.0f;
+            const float bias = 8388736.0f;  // 2^23 + 128
+#pragma unroll 4
+            for (int cw = cwBegin; cw < cwEnd; ++cw) {
+                const uint32_t w = Rw[static_cast<size_t>(cw) * H + k];
+                const float w0 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)) - bias;
+                const float w1 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)) - bias;
+                const float w2 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)) - bias;
+                const float w3 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)) - bias;
+#pragma unroll
+                for (int r = 0; r < RB; ++r) {
+                    const float4 d = *reinterpret_cast<const float4 *>(dqS + r * C + 4 * cw);
+                    acc[r] = fmaf(w0, d.x, acc[r]);
+                    acc[r] = fmaf(w1, d.y, acc[r]);
+                    acc[r] = fmaf(w2, d.z, acc[r]);
+                    acc[r] = fmaf(w3, d.w, acc[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RB; ++r) partS[(part * RB + r) * H + k] = acc[r];
+        }
+#pragma unroll
+        for (int r = 0; r < RB; ++r) cur[r] = nxt[r];
+        __syncthreads();
+    }
+    if (owner) {
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            if (b0 + r >= a.B) continue;
+            const size_t o = static_cast<size_t>(b0 + r) * H + k;
+            float carried = dhBase[r];
+            for (int p2 = 0; p2 < P; ++p2) carried += partS[(p2 * RB + r) * H + k];
+            a.dh0[o] = carried * keepOf(a.mH0, o);
+        }
+    }
+}
+
 // ---- dh += R dq on tensor cores -------------------------------------------------
 //
 // Same data flow as recurrentBackwardQ, but the per-step product runs as mma.sync m16n8k16:
@@ -1001,7 +1137,54 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         chanScaleW = chan;
     }
 
-    if (registerPath) {
+    // H > 128 with 8-bit weight codes: the codes stay in shared memory for the whole sequence
+    const int hpCodes = (H + 31) / 32 * 32;
+    const int partsCodes = std::max(1, std::min(4, 512 / hpCodes));
+    auto codesSmem = [&](int rb) {
+        return static_cast<size_t>(C) * H + sizeof(float) * (static_cast<size_t>(rb) * C + static_cast<size_t>(partsCodes) * rb * H);
+    };
+    const bool codesPath = qat && !registerPath && call.exec->weightClass == CodeClass::I8 && C % 4 == 0 && hpCodes <= 512 &&
+                           codesSmem(1) + 1024 <= static_cast<size_t>(smemMax) && alignedTo(call.R_q, 16) &&
+                           std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
+    if (codesPath) {
+        BackwardCodesArgs ca{};
+        BackwardQArgs &q = ca.q;
+        if (mk.weight_ih_linear || mk.weight_hh_linear || mk.gate_input || mk.gate_output || mk.h) {
+            uint16_t *bits = ws.take<uint16_t>(rows * H);
+            {
+                KernelTimer timer__("packStepMasks", st);
+                auto aligned4 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0; };
+                if (H % 4 == 0 && aligned4(mk.weight_ih_linear) && aligned4(mk.weight_hh_linear) && aligned4(mk.gate_input) &&
+                    aligned4(mk.gate_output) && aligned4(mk.h))
+                    packStepMasks4<<<gridFor(rows * H / 4, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear, mk.gate_input,
+                                                                              mk.gate_output, mk.h, rows * H / 4, H,
+                                                                              reinterpret_cast<uint2 *>(bits));
+                else
+                    packStepMasks<<<gridFor(rows * H, 256), 256, 0, st>>>(mk.weight_ih_linear, mk.weight_hh_linear,
+                                                                          mk.gate_input, mk.gate_output, mk.h, rows, H, bits);
+            }
+            afterLaunch("packStepMasks");
+            q.stepBits = bits;
+        }
+        q.T = T; q.B = B; q.H = H; q.scaleR = chanScaleR;
+        q.h = call.h; q.v = call.v; q.dhNew = call.dh_new; q.dp = dp; q.dq = dq; q.dh0 = call.dh0;
+        q.mIh = mk.weight_ih_linear; q.mHh = mk.weight_hh_linear; q.mGateIn = mk.gate_input;
+        q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
+        ca.Rq = call.R_q; ca.HP = hpCodes; ca.parts = partsCodes;
+        int rb = 1;
+        const int want = std::max(1, (B + sms - 1) / sms);
+        while (rb < 4 && rb < want && codesSmem(rb * 2) + 1024 <= static_cast<size_t>(smemMax)) rb *= 2;
+        auto launchCodes = [&](auto kernel) {
+            const size_t smem = codesSmem(rb);
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("recurrentBackward", st);
+            kernel<<<(B + rb - 1) / rb, hpCodes * partsCodes, smem, st>>>(ca);
+        };
+        if (rb == 1) launchCodes(recurrentBackwardCodes<1>);
+        else if (rb == 2) launchCodes(recurrentBackwardCodes<2>);
+        else launchCodes(recurrentBackwardCodes<4>);
+        afterLaunch("recurrentBackward");
+    } else if (registerPath) {
         const int CW = H <= 32 ? 16 : (H <= 64 ? 32 : 64);
         // The tensor-core kernel takes its fragments from the integer codes themselves; only the
         // register kernel reads the packed pairs.

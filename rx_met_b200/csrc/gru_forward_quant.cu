@@ -30,6 +30,7 @@
 #include "common.h"
 #include "gru_device.cuh"
 #include "gru_forward_quant.h"
+#include "gru_forward_wide.h"
 #include "input_proj_umma.h"
 
 namespace rxmet {
@@ -1009,6 +1010,27 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
         afterLaunch("channelPrep");
     }
 
+    // W8 / A16: byte-plane dp4a kernels instead of the 64-bit generic ones
+    if constexpr (std::is_same<WT, int8_t>::value && std::is_same<AT, int16_t>::value && std::is_same<LT, int16_t>::value) {
+        if (forwardWideTakes(e, I, H)) {
+            WideCall wc{};
+            wc.T = T; wc.B = B; wc.I = I; wc.H = H;
+            wc.wCodes = reinterpret_cast<const int8_t *>(wCodes); wc.rCodes = reinterpret_cast<const int8_t *>(rCodes);
+            wc.iPad = iPad; wc.hPad = hPad;
+            wc.xCodes = reinterpret_cast<const int16_t *>(xCodes); wc.h0Codes = reinterpret_cast<const int16_t *>(h0Codes);
+            wc.compX = compX; wc.biasX = biasX; wc.compH = compH; wc.biasH = biasH;
+            wc.gemmX = ch.gemmX; wc.gemmH = ch.gemmH;
+            wc.ihCodes = reinterpret_cast<int16_t *>(ihCodes);
+            wc.h = call.h; wc.v = call.v; wc.hq = call.h_q; wc.vq = call.v_q;
+            wc.maskIh = mk.weight_ih_linear; wc.maskHh = mk.weight_hh_linear; wc.maskGateIn = mk.gate_input;
+            wc.maskGateOut = mk.gate_output; wc.maskH = mk.h;
+            if (mk.gate_input || mk.gate_output || mk.h)
+                RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
+            forwardWide(wc, e, ws, st);
+            return;
+        }
+    }
+
     // Which recurrence runs decides what the input projection stores.
     const int smemMax = currentDevice().smemMax, sms = currentDevice().sms;
     constexpr bool kI8 = std::is_same<WT, int8_t>::value && std::is_same<AT, int8_t>::value &&
@@ -1163,10 +1185,10 @@ void sizeTyped(WorkspaceSizer &ws, int T, int B, int I, int H) {
 }  // namespace
 
 size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
-    // The widest storage classes bound every configuration.
+    // The widest storage classes bound every configuration; the byte-plane kernels add their operands.
     WorkspaceSizer ws;
     sizeTyped<int32_t, int32_t, int32_t>(ws, T, B, I, H);
-    return ws.used() + 4096;
+    return ws.used() + 4096 + forwardWideExtraBytes(T, B, I, H);
 }
 
 void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes,

@@ -251,6 +251,7 @@ __global__ void __launch_bounds__(kWideThreads) inputLinearWide(const __grid_con
 
 struct WideRecurrentArgs {
     int T, B, H, HP, kWords;
+    int weightBytesInSmem;   // size of the shared-memory copy of `words` (the kernel's WS variant), else 0
     const uint2 *words;      // [2 gate pairs][kWords][H]: (x, y) = gates (2 * pair, 2 * pair + 1)
     const int64_t *addend;   // [4H]
     const float *channel;
@@ -265,9 +266,17 @@ struct WideRecurrentArgs {
     rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearWide)
 };
 
-template <int PLANES, int RB>
+// WS: weight_hh (4H x H bytes) fits shared memory beside the code rows and is copied there once, which
+// takes the L2 round trip out of every step of the serial chain (H up to about 200).
+template <int PLANES, int RB, bool WS>
 __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_constant__ WideRecurrentArgs a) {
-    extern __shared__ __align__(16) uint32_t wideSmem[];  // [2][BT][PLANES][kWords]
+    extern __shared__ __align__(16) uint32_t wideSmemRaw[];  // [weights when WS] [2][BT][PLANES][kWords]
+    uint32_t *wideSmem = wideSmemRaw + (WS ? a.weightBytesInSmem / 4 : 0);
+    if (WS) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.words);
+        uint4 *dst = reinterpret_cast<uint4 *>(wideSmemRaw);
+        for (int i = threadIdx.x; i < a.weightBytesInSmem / 16; i += blockDim.x) dst[i] = src[i];
+    }
     const int H = a.H, C = 4 * a.H, kWords = a.kWords;
     const int tid = threadIdx.x, j = tid % a.HP, sg = tid / a.HP;
     const int BT = (blockDim.x / a.HP) * RB;
@@ -325,13 +334,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_co
                     for (int r = 0; r < RB; ++r)
 #pragma unroll
                         for (int p = 0; p < PLANES; ++p) acc[gg][r][p] = 0;
-                const uint2 *wp = a.words + static_cast<size_t>(pair) * kWords * H + j;
+                const uint2 *wp = (WS ? reinterpret_cast<const uint2 *>(wideSmemRaw) : a.words) + static_cast<size_t>(pair) * kWords * H + j;
                 const uint4 *hRows = reinterpret_cast<const uint4 *>(cur + sg * RB * rowWords);
 #pragma unroll 2
                 for (int k4 = 0; k4 < kWords / 4; ++k4) {
                     uint2 w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) w[i] = __ldg(wp + static_cast<size_t>(4 * k4 + i) * H);
+                    for (int i = 0; i < 4; ++i) w[i] = WS ? wp[static_cast<size_t>(4 * k4 + i) * H] : __ldg(wp + static_cast<size_t>(4 * k4 + i) * H);
 #pragma unroll
                     for (int r = 0; r < RB; ++r)
 #pragma unroll
@@ -584,16 +593,22 @@ void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspa
         const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));
         const int bt = groups * rb;
         const int block = groups * a.HP;
-        const size_t smem = sizeof(uint32_t) * 2 * bt * planes * kHh;
+        const size_t planeBytes = sizeof(uint32_t) * 2 * bt * planes * kHh;
+        const size_t weightBytes = sizeof(uint32_t) * static_cast<size_t>(kHh) * C;  // a multiple of 16
+        const bool weightsInSmem = planeBytes + weightBytes + 1024 <= static_cast<size_t>(currentDevice().smemMax);
+        a.weightBytesInSmem = weightsInSmem ? static_cast<int>(weightBytes) : 0;
+        const size_t smem = planeBytes + (weightsInSmem ? weightBytes : 0);
         auto launch = [&](auto kernel) {
             ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
             KernelTimer timer__("lstmRecurrentWide", st);
             kernel<<<(B + bt - 1) / bt, block, smem, st>>>(a);
         };
-#define RXMET_WIDE_REC(RBV)                                   \
-    do {                                                       \
-        if (planes == 2) launch(recurrentWide<2, RBV>);        \
-        else launch(recurrentWide<1, RBV>);                    \
+#define RXMET_WIDE_REC(RBV)                                                        \
+    do {                                                                            \
+        if (planes == 2 && weightsInSmem) launch(recurrentWide<2, RBV, true>);      \
+        else if (planes == 2) launch(recurrentWide<2, RBV, false>);                 \
+        else if (weightsInSmem) launch(recurrentWide<1, RBV, true>);                \
+        else launch(recurrentWide<1, RBV, false>);                                  \
     } while (0)
         if (rb == 1) RXMET_WIDE_REC(1);
         else if (rb == 2) RXMET_WIDE_REC(2);
