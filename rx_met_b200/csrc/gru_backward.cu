@@ -1072,8 +1072,11 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(splitR * H * C);
     ws.take<float>(2 * kBiasSplits * C);
     // tensor-core path: split-K partials of (I+1) and (H+1) rows and the status word
-    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C))) * (I + 1) * C);
-    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
+    // (the slab form of the same kernel, for more than 128 rows or 16-bit codes, asks for fewer splits)
+    ws.take<float>(static_cast<size_t>(std::max(wgrad::slabSplitBound(I, H, static_cast<int>(C)),
+                                                I <= 143 ? wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C)) : 1)) * (I + 1) * C);
+    ws.take<float>(static_cast<size_t>(std::max(wgrad::slabSplitBound(I, H, static_cast<int>(C)),
+                                                H <= 143 ? wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C)) : 1)) * (H + 1) * C);
     ws.take<int>(64);
     return ws.used() + 4096;
 }
@@ -1105,6 +1108,11 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
                                  alignedTo(call.dx, 16) && alignedTo(mk.x, 8) && alignedTo(call.W_q, 16);
     const bool tensorGrads = qat && call.exec->actClass == CodeClass::I8 && I + 1 <= 144 && H + 1 <= 144 && I % 4 == 0 &&
                              H % 4 == 0 && !simtGrads && alignedTo(call.x_q, 16) && alignedTo(call.h, 16);
+    // More than 128 rows or 16-bit activation codes: the same tcgen05 kernel over 128-row slabs, two exact
+    // bf16 terms per code when the grid is wider than 8 bits.
+    const bool wideCodes = qat && call.exec->actClass != CodeClass::I8;
+    const bool slabGrads = qat && !tensorGrads && !simtGrads && call.exec->actClass != CodeClass::I32 && I % 4 == 0 && H % 4 == 0 &&
+                           alignedTo(call.x_q, 16) && alignedTo(call.h, 16) && wgrad::slabPathTakes(I, H, C);
 
     const float *W = call.W, *R = call.R, *x = call.x;
     const float *chanScaleR = nullptr, *chanScaleW = nullptr;
@@ -1126,7 +1134,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             dequantCodes<<<gridFor(static_cast<size_t>(H) * C, 256), 256, 0, st>>>(call.R_q, static_cast<size_t>(H) * C, C, chan + C, 0.f, 0, Rf);
             afterLaunch("dequantCodes");
         }
-        if (!tensorGrads) {
+        if (!tensorGrads && !slabGrads) {
             KernelTimer timer__("dequantCodes", st);
             dequantCodes<<<gridFor(rows * I, 256), 256, 0, st>>>(call.x_q, rows * I, I, nullptr, e.gate.eff[RXMET_GRU_X],
                                                                 e.gate.zp[RXMET_GRU_X], xf);
@@ -1303,6 +1311,30 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         {
             const ReduceJob jobX{px.partial, planX.splits, I, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw};
             const ReduceJob jobH{ph.partial, planH.splits, H, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr};
+            const size_t largest = static_cast<size_t>(std::max(I, H) + 1) * C;
+            KernelTimer timer__("reduceWeightGrad", st);
+            reduceWeightGrad<<<dim3(static_cast<unsigned>((largest + kReduceWidth - 1) / kReduceWidth), 2),
+                               dim3(kReduceWidth, kReduceLayers), 0, st>>>(jobX, jobH, C, status);
+        }
+        afterLaunch("reduceWeightGrad");
+        return;
+    }
+    if (slabGrads) {
+        const Exec &e = *call.exec;
+        const int K = static_cast<int>(rows);
+        int chunkK = 0;
+        const int splits = wgrad::slabSplits(K, I, H, C, sms, &chunkK);
+        WeightGradProblem px{}, ph{};
+        px.aCodes = call.x_q; px.aZero = e.gate.zp[RXMET_GRU_X]; px.M = I; px.B = dp;
+        px.partial = ws.take<float>(static_cast<size_t>(splits) * (I + 1) * C);
+        ph.aFloat = call.h; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq;
+        ph.partial = ws.take<float>(static_cast<size_t>(splits) * (H + 1) * C);
+        px.status = ph.status = status;
+        wgrad::launchSlabs(px, ph, K, C, chunkK, splits, wideCodes, st);
+        afterLaunch("weightGrad");
+        {
+            const ReduceJob jobX{px.partial, splits, I, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw};
+            const ReduceJob jobH{ph.partial, splits, H, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr};
             const size_t largest = static_cast<size_t>(std::max(I, H) + 1) * C;
             KernelTimer timer__("reduceWeightGrad", st);
             reduceWeightGrad<<<dim3(static_cast<unsigned>((largest + kReduceWidth - 1) / kReduceWidth), 2),

@@ -37,14 +37,29 @@ constexpr uint32_t kTermBytes = kTileM * kChunkK * 2;        // 8 KB: one bf16 t
 constexpr uint32_t kStageBytes = 3 * kTermBytes;
 constexpr uint32_t kAKStride = kCore;                        // next k-group of the same 8 rows
 constexpr uint32_t kAMStride = (kChunkK / 8) * kCore;        // next 8 rows
-constexpr int kMaxK = 512;
+constexpr int kMaxK = 768;
 
 size_t sharedBytes(int K, int NP) {
     return kStages * kStageBytes + kRing * kRawBytes + static_cast<size_t>(NP) * K * 2 + sizeof(float) * K;
 }
 
+// gridDim.y = column slabs of the output: slab s works on columns [NP s, NP s + NP) with its own copy of the
+// weight operand; every slab walks all rows (the gradient rows are re-read from L2 once per slab).
 template <int NP>
-__global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, int rowsPerCta) {
+__global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem whole, int rowsPerCta) {
+    Problem p = whole;
+    {
+        const int n0 = static_cast<int>(blockIdx.y) * NP;
+        if (p.ldN == 0) p.ldN = p.N;
+        if (p.ldCodesKN == 0) p.ldCodesKN = p.N;
+        if (gridDim.y > 1) {
+            p.N = min(NP, whole.N - n0);
+            if (p.codesNK) p.codesNK += static_cast<size_t>(n0) * p.K;
+            if (p.codesKN) p.codesKN += n0;
+            if (p.mask) p.mask += n0;
+            p.out += n0;
+        }
+    }
     constexpr uint32_t kTmemCols = NP <= 32 ? 32 : 64;
     constexpr uint32_t kIdesc = instructionDescriptor(NP, false, false);
     extern __shared__ __align__(128) uint8_t smem[];
@@ -109,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
             const int k = 8 * k8 + j;
             c[j] = n >= N ? 0.0f
                           : (p.codesNK ? static_cast<float>(p.codesNK[static_cast<size_t>(n) * K + k])
-                                       : p.codesKN[static_cast<size_t>(k) * N + n]);
+                                       : p.codesKN[static_cast<size_t>(k) * p.ldCodesKN + n]);
         }
         *reinterpret_cast<uint4 *>(weights + (n / 8) * kBNStride + k8 * kCore + (n % 8) * 16) =
             make_uint4(packBf16(c[0], c[1]), packBf16(c[2], c[3]), packBf16(c[4], c[5]), packBf16(c[6], c[7]));
@@ -183,10 +198,10 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
             const int row = rowBegin + tile * kTileM + 32 * q + lane;
             const bool poison = *reinterpret_cast<volatile int *>(&failed) != 0;
             if (row < rowEnd) {
-                const size_t o = static_cast<size_t>(row) * N + col0;
+                const size_t o = static_cast<size_t>(row) * p.ldN + col0;
                 float v[16];
                 uint8_t m[16];
-                const bool wide = (N % 8) == 0 && col0 + 8 <= N;  // whole 8-column groups, aligned
+                const bool wide = (N % 8) == 0 && (p.ldN % 8) == 0 && col0 + 8 <= N;  // whole 8-column groups, aligned
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (p.mask && wide && col0 + 8 * h + 8 <= N) {
@@ -209,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) inputGradUmma(const Problem p, in
                 }
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
-                    if ((N % 4) == 0 && col0 + 4 * h + 4 <= N) {
+                    if ((N % 4) == 0 && (p.ldN % 4) == 0 && col0 + 4 * h + 4 <= N) {
                         *reinterpret_cast<float4 *>(p.out + o + 4 * h) = make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
                     } else {
 #pragma unroll
@@ -235,22 +250,25 @@ template <int NP>
 void launchPadded(const Problem &prob, int sms, cudaStream_t st) {
     const size_t smem = sharedBytes(prob.K, NP);
     ensureDynamicSmem(reinterpret_cast<const void *>(inputGradUmma<NP>), smem);  // per device
+    const int slabs = (prob.N + NP - 1) / NP;
     const int groups = (prob.rows + 7) / 8;
-    const int grid = std::max(1, std::min(sms, groups));
+    const int grid = std::max(1, std::min(std::max(1, sms / slabs), groups));
     const int rowsPerCta = (groups + grid - 1) / grid * 8;
     KernelTimer timer__("inputGradUmma", st);
-    inputGradUmma<NP><<<grid, kThreads, smem, st>>>(prob, rowsPerCta);
+    inputGradUmma<NP><<<dim3(grid, slabs), kThreads, smem, st>>>(prob, rowsPerCta);
 }
 
 }  // namespace
 
 bool eligible(int K, int N) {
     static const bool disabled = std::getenv("RXMET_IGRAD_SIMT") != nullptr;
-    return !disabled && K >= kChunkK && K % kChunkK == 0 && K <= kMaxK && N >= 1 && N <= 64;
+    return !disabled && K >= kChunkK && K % kChunkK == 0 && K <= kMaxK && N >= 1;
 }
 
 void launch(const Problem &prob, int sms, cudaStream_t st) {
-    const int np = (prob.N + 15) / 16 * 16;
+    // widest slab whose weight operand fits shared memory beside the stages and the ring
+    const int widest = prob.K <= 512 ? 64 : 32;
+    const int np = prob.N > widest ? widest : (prob.N + 15) / 16 * 16;
     switch (np) {
         case 16: launchPadded<16>(prob, sms, st); break;
         case 32: launchPadded<32>(prob, sms, st); break;

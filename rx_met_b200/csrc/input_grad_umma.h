@@ -25,9 +25,13 @@ struct Problem {
     int maskKeeps = 1;                  // 1: a nonzero byte keeps the gradient; 0: a nonzero byte drops it
     float *out = nullptr;               // [rows][N]
     int *status = nullptr;              // device word, set to 1 when a bounded wait of the kernel gave up
+    int ldN = 0;                        // elements between rows of `out` and `mask` (0 = N); wider than N when the
+                                        // problem is one 64-column slab of a larger output
+    int ldCodesKN = 0;                  // elements between k rows of codesKN (0 = N)
 };
 
-// K a multiple of 32 up to 512, N up to 64.  RXMET_IGRAD_SIMT in the environment turns the path off.
+// K a multiple of 64 up to 768; any N: more than 64 columns (32 when K > 512, where the weight operand of a
+// wider slab no longer fits shared memory) run as column slabs that share one launch.  RXMET_IGRAD_SIMT in the environment turns the path off.
 bool eligible(int K, int N);
 void launch(const Problem &problem, int sms, cudaStream_t stream);
 

@@ -59,7 +59,7 @@ constexpr int kRows = 128;  // rows of the batch per work item = accumulator col
 
 size_t sharedBytes(int C, int kPad) { return static_cast<size_t>(C) * kPad + 2 * static_cast<size_t>(kRows) * kPad; }
 
-__global__ void __launch_bounds__(kThreads, 1) inputProjUmma(const Problem p) {
+__global__ void __launch_bounds__(kThreads, 2) inputProjUmma(const Problem p) {
     constexpr uint32_t kTmemCols = 2 * kRows;
     constexpr uint32_t kIdesc = instructionDescriptorI8(kRows);
     extern __shared__ __align__(128) uint8_t smem[];
@@ -226,7 +226,7 @@ void launch(const Problem &problem, int sms, cudaStream_t st) {
     ensureDynamicSmem(reinterpret_cast<const void *>(inputProjUmma), smem);
     const int items = ((prob.rows + kRows - 1) / kRows) * (prob.C / kTileM);
     KernelTimer timer__("inputLinear", st);
-    inputProjUmma<<<std::max(1, std::min(items, sms)), kThreads, smem, st>>>(prob);
+    inputProjUmma<<<std::max(1, std::min(items, 2 * sms)), kThreads, smem, st>>>(prob);
 }
 
 }  // namespace iproj

@@ -42,7 +42,7 @@ constexpr int kStageRows = 32;          // K rows per stage: two MMA k-steps of 
 
 // Depth of the ring of raw (unconverted) chunks, chosen so that ring + operand stages fill the
 // shared memory of an SM.
-template <int NT>
+template <int NT, int ATERMS = 1>
 struct Geometry {
     static constexpr int kThreads = 2 * NT;                      // two thread halves, two k-groups of B each
     static constexpr int kWarps = kThreads / 32;
@@ -51,10 +51,10 @@ struct Geometry {
     static constexpr uint32_t kBKStride = (NT / 8) * kCore;
     static constexpr uint32_t kABytes = (kStageRows / 8) * kAKStride;
     static constexpr uint32_t kBBytes = (kStageRows / 8) * kBKStride;
-    static constexpr uint32_t kStageBytes = kABytes + 3 * kBBytes;
+    static constexpr uint32_t kStageBytes = ATERMS * kABytes + 3 * kBBytes;
     static constexpr uint32_t kRawPieces = 2 * kWarps + 16;      // 1 KB pieces of a raw chunk: B per warp, then A
     static constexpr uint32_t kRawBytes = kRawPieces * 1024;
-    static constexpr int kRing = NT <= 128 ? 4 : (NT <= 192 ? 3 : 2);
+    static constexpr int kRing = NT <= 128 ? 4 : (NT <= 192 ? (ATERMS == 1 ? 3 : 2) : 2);
     static_assert(2 * kStageBytes + kRing * kRawBytes <= 227 * 1024, "shared memory of one SM");
     static constexpr size_t kSmem = 2 * kStageBytes + static_cast<size_t>(kRing) * kRawBytes;
 };
@@ -65,11 +65,11 @@ struct Geometry {
 // four whole core matrices (512 contiguous bytes) and its loads cover 8 rows x 128 contiguous bytes.  Each thread copies its own pieces of the next chunks into a
 // ring of raw buffers with cp.async, kRing chunks ahead; a warp later converts exactly the pieces
 // it copied, so the ring needs no CTA-wide barrier of its own.
-template <int NT>
+template <int NT, int ATERMS>
 __global__ void __launch_bounds__(2 * NT, 1)
-weightGradUmma(const Problem first, const Problem second, int K, int N, int chunkK, int *status) {
-    const Problem p = blockIdx.z == 0 ? first : second;  // gridDim.z problems share one launch
-    using G = Geometry<NT>;
+weightGradUmma(const __grid_constant__ ProblemSet set, int K, int N, int chunkK, int *status) {
+    const Problem &p = set.slab[blockIdx.z];  // gridDim.z problems / slabs share one launch
+    using G = Geometry<NT, ATERMS>;
     constexpr int NW = G::kWarps, CW = NT / 32, AT = G::kAPieces, R = G::kRing, TH = G::kThreads;
     constexpr uint32_t kAKStride = G::kAKStride, kBKStride = G::kBKStride, kABytes = G::kABytes, kBBytes = G::kBBytes;
     constexpr uint32_t kStageBytes = G::kStageBytes;
@@ -97,10 +97,12 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // rows of A beyond M stay zero for the whole kernel
-    for (uint32_t i = tid; i < 2 * kABytes / 16; i += TH) {
-        const uint32_t stage = i / (kABytes / 16), off = i % (kABytes / 16);
+    for (uint32_t i = tid; i < 2 * ATERMS * kABytes / 16; i += TH) {
+        const uint32_t stage = i / (ATERMS * kABytes / 16), off = i % (ATERMS * kABytes / 16);
         *reinterpret_cast<uint4 *>(stages + stage * kStageBytes + off * 16) = make_uint4(0u, 0u, 0u, 0u);
     }
+    const int lda = p.lda ? p.lda : M;
+    const int totalRows = p.totalRows ? p.totalRows : M + 1;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemSlot)), "r"(kTmemCols)
                      : "memory");
@@ -133,7 +135,7 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
                 const int k = k0 + 8 * (task & 3) + wrow;
                 if (task >= 16) continue;
                 const bool ok = task < 4 * quads && k < kEnd && m < M;
-                const size_t at = ok ? static_cast<size_t>(k) * M + m : 0;
+                const size_t at = ok ? static_cast<size_t>(k) * lda + m : 0;
                 copyAsync16(dstA + task * 64 + pos, static_cast<const uint32_t *>(aBase) + at, ok);
             }
         }
@@ -165,7 +167,7 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
             csum[0] += u.x; csum[1] += u.y; csum[2] += u.z; csum[3] += u.w;
             csum[4] += v.x; csum[5] += v.y; csum[6] += v.z; csum[7] += v.w;
             const Converted c = splitThree(u, v);
-            uint8_t *dst = stage + kABytes + (4 * cw + cq) * kCore + rk * 16 + g * kBKStride;
+            uint8_t *dst = stage + ATERMS * kABytes + (4 * cw + cq) * kCore + rk * 16 + g * kBKStride;
             *reinterpret_cast<uint4 *>(dst) = c.hi;
             *reinterpret_cast<uint4 *>(dst + kBBytes) = c.mid;
             *reinterpret_cast<uint4 *>(dst + 2 * kBBytes) = c.lo;
@@ -187,8 +189,23 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
 #pragma unroll
                 for (int i = 0; i < 8; ++i) x[i] = rintf(__uint_as_float(q[i]) * p.aInvScale) - p.aFloatZero;
             }
-            *reinterpret_cast<uint4 *>(stage + (4 * quad + cq) * kCore + rk * 16 + g * kAKStride) =
-                make_uint4(packBf16(x[0], x[1]), packBf16(x[2], x[3]), packBf16(x[4], x[5]), packBf16(x[6], x[7]));
+            uint8_t *dstA = stage + (4 * quad + cq) * kCore + rk * 16 + g * kAKStride;
+            if (ATERMS == 2) {
+                // a = 256 * floor(a / 256) + (a mod 256): both terms are exact in bf16 for |a| < 2^17
+                float hi[8], lo[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    hi[i] = floorf(x[i] * (1.0f / 256.0f)) * 256.0f;
+                    lo[i] = x[i] - hi[i];
+                }
+                *reinterpret_cast<uint4 *>(dstA) =
+                    make_uint4(packBf16(hi[0], hi[1]), packBf16(hi[2], hi[3]), packBf16(hi[4], hi[5]), packBf16(hi[6], hi[7]));
+                *reinterpret_cast<uint4 *>(dstA + kABytes) =
+                    make_uint4(packBf16(lo[0], lo[1]), packBf16(lo[2], lo[3]), packBf16(lo[4], lo[5]), packBf16(lo[6], lo[7]));
+            } else {
+                *reinterpret_cast<uint4 *>(dstA) =
+                    make_uint4(packBf16(x[0], x[1]), packBf16(x[2], x[3]), packBf16(x[4], x[5]), packBf16(x[6], x[7]));
+            }
         }
     };
 
@@ -209,12 +226,15 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
             const uint32_t base = smemAddr(stage);
 #pragma unroll
             for (int ks = 0; ks < kStageRows / 16; ++ks) {
-                const uint64_t descA = operandDescriptor(base + ks * 2 * kAKStride, kAKStride, kCore);
 #pragma unroll
-                for (int sp = 0; sp < 3; ++sp) {
-                    const uint64_t descB =
-                        operandDescriptor(base + kABytes + sp * kBBytes + ks * 2 * kBKStride, kBKStride, kCore);
-                    mmaBf16(tmem, descA, descB, kIdesc, (c > 0 || ks > 0 || sp > 0) ? 1u : 0u);
+                for (int at = 0; at < ATERMS; ++at) {
+                    const uint64_t descA = operandDescriptor(base + at * kABytes + ks * 2 * kAKStride, kAKStride, kCore);
+#pragma unroll
+                    for (int sp = 0; sp < 3; ++sp) {
+                        const uint64_t descB =
+                            operandDescriptor(base + ATERMS * kABytes + sp * kBBytes + ks * 2 * kBKStride, kBKStride, kCore);
+                        mmaBf16(tmem, descA, descB, kIdesc, (c > 0 || ks > 0 || sp > 0 || at > 0) ? 1u : 0u);
+                    }
                 }
             }
             commitTo(smemAddr(&bars[s]));
@@ -225,7 +245,8 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
     if (chunks > 0 && !waitPhase(smemAddr(&bars[2]), 0)) failed = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    float *out = p.partial + static_cast<size_t>(blockIdx.y) * (M + 1) * N;
+    float *slice = p.partial + static_cast<size_t>(blockIdx.y) * totalRows * N;
+    float *out = slice + static_cast<size_t>(p.rowBase) * N;
     // accumulator rows: warp w may read the tensor-memory lanes [32 (w % 4), 32 (w % 4) + 32)
     {
         const int q = warp & 3, sharing = (NW - q + 3) / 4;
@@ -268,10 +289,10 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
         for (int j = 0; j < 8; ++j) scratch[32 * cw + 8 * cq + j] = csum[j];
     }
     __syncthreads();
-    if (half == 0 && rk == 0) {
+    if (half == 0 && rk == 0 && p.writeBias) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) csum[j] += scratch[32 * cw + 8 * cq + j];
-        float4 *dst = reinterpret_cast<float4 *>(out + static_cast<size_t>(M) * N + n0 + 32 * cw + 8 * cq);
+        float4 *dst = reinterpret_cast<float4 *>(slice + static_cast<size_t>(totalRows - 1) * N + n0 + 32 * cw + 8 * cq);
         dst[0] = make_float4(csum[0], csum[1], csum[2], csum[3]);
         dst[1] = make_float4(csum[4], csum[5], csum[6], csum[7]);
     }
@@ -284,13 +305,22 @@ weightGradUmma(const Problem first, const Problem second, int K, int N, int chun
     if (tid == 0 && failed && status) atomicExch(status, 1);
 }
 
+template <int NT, int ATERMS>
+void launchSet(const ProblemSet &set, int K, int N, int chunkK, int splits, cudaStream_t st) {
+    constexpr size_t smem = Geometry<NT, ATERMS>::kSmem;
+    ensureDynamicSmem(reinterpret_cast<const void *>(weightGradUmma<NT, ATERMS>), smem);  // per device
+    KernelTimer timer__("weightGradUmma", st);
+    weightGradUmma<NT, ATERMS><<<dim3(N / NT, splits, set.count), Geometry<NT, ATERMS>::kThreads, smem, st>>>(
+        set, K, N, chunkK, set.slab[0].status);
+}
+
 template <int NT>
 void launchTile(const Problem &prob, const Problem *other, int K, int N, int chunkK, int splits, cudaStream_t st) {
-    constexpr size_t smem = Geometry<NT>::kSmem;
-    ensureDynamicSmem(reinterpret_cast<const void *>(weightGradUmma<NT>), smem);  // per device
-    KernelTimer timer__("weightGradUmma", st);
-    weightGradUmma<NT><<<dim3(N / NT, splits, other ? 2 : 1), Geometry<NT>::kThreads, smem, st>>>(
-        prob, other ? *other : prob, K, N, chunkK, prob.status);
+    ProblemSet set;
+    set.slab[0] = prob;
+    set.count = 1;
+    if (other) set.slab[set.count++] = *other;
+    launchSet<NT, 1>(set, K, N, chunkK, splits, st);
 }
 
 int tileColumns(int N) {
@@ -306,8 +336,8 @@ bool tensorMemoryPath(int M, int N) {
     return !disabled && M >= 4 && M <= kTileM && M % 4 == 0 && N % 4 == 0 && tileColumns(N) != 0;
 }
 
-int planTensorMemory(int K, int N, int sms, int *chunkK) {
-    const int tiles = N / tileColumns(N);
+int planTensorMemory(int K, int N, int sms, int *chunkK, int slabs) {
+    const int tiles = (N / tileColumns(N)) * std::max(1, slabs);
     const int want = std::max(1, sms / tiles);  // one CTA per SM
     *chunkK = ((K + want - 1) / want + kStageRows - 1) / kStageRows * kStageRows;
     return (K + *chunkK - 1) / *chunkK;
@@ -318,6 +348,49 @@ void launchTensorMemory(const Problem &prob, const Problem *other, int K, int N,
         case 256: launchTile<256>(prob, other, K, N, chunkK, splits, st); break;
         case 192: launchTile<192>(prob, other, K, N, chunkK, splits, st); break;
         case 128: launchTile<128>(prob, other, K, N, chunkK, splits, st); break;
+        default: fail(RXMET_ERR_UNSUPPORTED, "no tensor-memory tile for %d columns", N);
+    }
+}
+
+int slabsOf(int M) { return (M + kTileM - 1) / kTileM; }
+
+bool slabPathTakes(int Ma, int Mb, int N) {
+    static const bool disabled = std::getenv("RXMET_WGRAD_MMA_SYNC") != nullptr;
+    if (disabled || tileColumns(N) == 0 || Ma % 4 != 0 || Mb % 4 != 0 || Ma < 0 || Mb < 0) return false;
+    return slabsOf(Ma) + slabsOf(Mb) >= 1 && slabsOf(Ma) + slabsOf(Mb) <= kMaxSlabs;
+}
+
+int slabSplits(int K, int Ma, int Mb, int N, int sms, int *chunkK) {
+    return planTensorMemory(K, N, sms, chunkK, slabsOf(Ma) + slabsOf(Mb));
+}
+
+int slabSplitBound(int Ma, int Mb, int N) {
+    const int nt = tileColumns(N);
+    if (nt == 0) return 1;
+    return std::max(1, 160 / ((N / nt) * std::max(1, slabsOf(Ma) + slabsOf(Mb))));
+}
+
+void launchSlabs(const Problem &a, const Problem &b, int K, int N, int chunkK, int splits, bool wide, cudaStream_t st) {
+    ProblemSet set;
+    for (const Problem *prob : {&a, &b}) {
+        for (int m0 = 0; m0 < prob->M; m0 += kTileM) {
+            Problem s = *prob;
+            s.M = std::min(kTileM, prob->M - m0);
+            s.lda = prob->M;
+            s.rowBase = m0;
+            s.totalRows = prob->M + 1;
+            s.writeBias = m0 == 0 ? 1 : 0;
+            s.wideCodes = wide ? 1 : 0;
+            if (s.aCodes) s.aCodes += m0;
+            if (s.aFloat) s.aFloat += m0;
+            set.slab[set.count++] = s;
+        }
+    }
+    RXMET_REQUIRE(set.count >= 1 && set.count <= kMaxSlabs, "weight gradient: %d slabs", set.count);
+    switch (tileColumns(N)) {
+        case 256: wide ? launchSet<256, 2>(set, K, N, chunkK, splits, st) : launchSet<256, 1>(set, K, N, chunkK, splits, st); break;
+        case 192: wide ? launchSet<192, 2>(set, K, N, chunkK, splits, st) : launchSet<192, 1>(set, K, N, chunkK, splits, st); break;
+        case 128: wide ? launchSet<128, 2>(set, K, N, chunkK, splits, st) : launchSet<128, 1>(set, K, N, chunkK, splits, st); break;
         default: fail(RXMET_ERR_UNSUPPORTED, "no tensor-memory tile for %d columns", N);
     }
 }
