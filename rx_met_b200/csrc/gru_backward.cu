@@ -1078,6 +1078,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(static_cast<size_t>(std::max(wgrad::slabSplitBound(I, H, static_cast<int>(C)),
                                                 H <= 143 ? wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C)) : 1)) * (H + 1) * C);
     ws.take<int>(64);
+    ws.take<uint8_t>(igrad::widePackedBytes(static_cast<int>(C), I) + 256);   // weight operand of the streaming input-gradient kernel
     return ws.used() + 4096;
 }
 
@@ -1287,6 +1288,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         igrad::Problem pg{};
         pg.G = dp; pg.kScale = chanScaleW; pg.codesNK = call.W_q; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
         pg.mask = mk.x; pg.maskKeeps = 1; pg.out = call.dx; pg.status = status;
+        if (const size_t bytes = igrad::widePackedBytes(C, I)) pg.packed = ws.take<uint8_t>(bytes);
         igrad::launch(pg, sms, st);
         afterLaunch("inputGradUmma");
     } else {

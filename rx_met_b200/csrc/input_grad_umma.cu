@@ -260,12 +260,26 @@ void launchPadded(const Problem &prob, int sms, cudaStream_t st) {
 
 }  // namespace
 
+bool wideTakes(int K, int N);
+
 bool eligible(int K, int N) {
     static const bool disabled = std::getenv("RXMET_IGRAD_SIMT") != nullptr;
-    return !disabled && K >= kChunkK && K % kChunkK == 0 && K <= kMaxK && N >= 1;
+    if (disabled || N < 1) return false;
+    if (K >= kChunkK && K % kChunkK == 0 && K <= kMaxK) return true;
+    return wideTakes(K, N);   // only with Problem::packed
 }
 
+bool wideTakes(int K, int N);
+bool wideEligible(const Problem &p);
+void launchWide(const Problem &prob, cudaStream_t st);
+
 void launch(const Problem &prob, int sms, cudaStream_t st) {
+    if (wideEligible(prob)) {
+        launchWide(prob, st);
+        return;
+    }
+    if (prob.K > kMaxK || prob.K % kChunkK != 0)
+        fail(RXMET_ERR_UNSUPPORTED, "input gradient: %d channels need the streaming kernel (scratch, 16-byte aligned operands)", prob.K);
     // widest slab whose weight operand fits shared memory beside the stages and the ring
     const int widest = prob.K <= 512 ? 64 : 32;
     const int np = prob.N > widest ? widest : (prob.N + 15) / 16 * 16;

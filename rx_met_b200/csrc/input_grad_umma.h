@@ -28,11 +28,17 @@ struct Problem {
     int ldN = 0;                        // elements between rows of `out` and `mask` (0 = N); wider than N when the
                                         // problem is one 64-column slab of a larger output
     int ldCodesKN = 0;                  // elements between k rows of codesKN (0 = N)
+    void *packed = nullptr;             // scratch of widePackedBytes(K, N) bytes, 16-byte aligned: with it, outputs wider
+                                        // than 64 columns (up to 512) take the warp-specialised kernel that streams
+                                        // both operands and keeps the whole [128][N] accumulator in tensor memory
 };
 
-// K a multiple of 64 up to 768; any N: more than 64 columns (32 when K > 512, where the weight operand of a
-// wider slab no longer fits shared memory) run as column slabs that share one launch.  RXMET_IGRAD_SIMT in the environment turns the path off.
+// Resident-weight kernel: K a multiple of 64 up to 768; any N: more than 64 columns (32 when K > 512, where the
+// weight operand of a wider slab no longer fits shared memory) run as column slabs that share one launch.
+// Streaming kernel (Problem::packed given, 64 < N <= 512): any K that is a multiple of 32.
+// RXMET_IGRAD_SIMT in the environment turns both off, RXMET_IGRAD_NARROW the streaming kernel.
 bool eligible(int K, int N);
+size_t widePackedBytes(int K, int N);   // 0 when the streaming kernel does not take N
 void launch(const Problem &problem, int sms, cudaStream_t stream);
 
 }  // namespace igrad

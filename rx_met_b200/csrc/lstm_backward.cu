@@ -761,6 +761,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
     ws.take<int>(1);              // status word of the tensor-memory weight-gradient kernel
     ws.take<uint32_t>(rows * H);  // packed per-step clamp flags
+    ws.take<uint8_t>(igrad::widePackedBytes(static_cast<int>(C), I) + 256);   // weight operand of the streaming input-gradient kernel
     return ws.used() + 1024;
 }
 
@@ -919,6 +920,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         igrad::Problem pg{};
         pg.G = gIh; pg.kScale = channelScales; pg.codesKN = call.weightIh; pg.rows = static_cast<int>(rows); pg.K = C; pg.N = I;
         pg.mask = static_cast<const uint8_t *>(mk.input); pg.maskKeeps = 0; pg.out = call.grads.input; pg.status = tensorStatus;
+        if (const size_t bytes = igrad::widePackedBytes(C, I)) pg.packed = ws.take<uint8_t>(bytes);
         igrad::launch(pg, sms, st);
         afterLaunch("inputGradUmma");
     } else if (I <= 128 && C % 4 == 0) {
