@@ -229,6 +229,72 @@ def run_reference_arm(args):
 # GPU arm
 # --------------------------------------------------------------------------
 
+def reference_cuda_step(torch, device, eng, x, reps=5):
+    """The reference's OWN CUDA kernels for the same step (its integer-carrier training forward and its QAT
+    backward, compiled for sm_100a into oracle/_ref/libgru_ref_cuda.so by oracle/Makefile), timed on this GPU with
+    the product's weights and quantization parameters: the kernel-to-beat beside the CPU baseline.  Follows the
+    reference binding's order of work: forward; float copies of the saved codes, its dequantization, transposes,
+    zeroed weight gradients; backward.  The loss and the optimizer step are not included."""
+    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libgru_ref_cuda.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/libgru_ref_cuda.so not built"}
+    ref = C.CDLL(so)
+    ref.refcuda_last_error.restype = C.c_char_p
+    from rx_met_b200 import _cabi as cabi
+    T, B, I, H = eng.T, eng.B, eng.I, eng.H
+    f32, i32 = dict(dtype=torch.float32, device=device), dict(dtype=torch.int32, device=device)
+    h, v = torch.zeros((T + 1, B, H), **f32), torch.zeros((T, B, 4 * H), **f32)
+    W_q, R_q = torch.zeros((I, 3 * H), **i32), torch.zeros((H, 3 * H), **i32)
+    bw_q, br_q, x_q = torch.zeros(3 * H, **i32), torch.zeros(3 * H, **i32), torch.zeros((T, B, I), **i32)
+    shapes = {"x": (T, B, I), "W": (I, 3 * H), "R": (H, 3 * H), "bw": (3 * H,), "br": (3 * H,),
+              "weight_ih_linear": (T, B, 3 * H), "weight_hh_linear": (T, B, 3 * H), "gate_input": (T, B, 3 * H),
+              "gate_output": (T, B, 3 * H), "h": (T, B, H)}
+    masks, ms = {}, cabi.Masks()
+    for name, shape in shapes.items():
+        masks[name] = torch.zeros(shape, dtype=torch.uint8, device=device)
+        setattr(ms, name, masks[name].data_ptr())
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    dh_new = torch.randn((T + 1, B, H), generator=torch.Generator(device="cpu").manual_seed(3)).to(device) * 1e-3
+
+    def check(rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what}: {ref.refcuda_last_error().decode(errors='replace')}")
+
+    def forward():
+        check(ref.refcuda_gru_forward_quant_int(1, T, B, I, H, P(eng.W), P(eng.R), P(eng.bw), P(eng.br), P(x), None,
+                                                C.byref(eng._c_params), P(h), P(v), C.byref(ms), P(W_q), P(R_q), P(bw_q),
+                                                P(br_q), P(x_q)), "reference CUDA forward")
+
+    def backward():
+        Wf, Rf, bwf, brf, xf = [t.to(torch.float32) for t in (W_q, R_q, bw_q, br_q, x_q)]
+        check(ref.refcuda_gru_dequantize_saved(I, H, C.c_longlong(xf.numel()), P(Wf), P(Rf), P(bwf), P(brf), P(xf),
+                                               C.byref(eng._c_params)), "reference CUDA dequantize")
+        x_t, W_t, R_t = xf.permute(2, 0, 1).contiguous(), Wf.t().contiguous(), Rf.t().contiguous()
+        dx, dW, dR = torch.empty((T, B, I), **f32), torch.zeros((I, 3 * H), **f32), torch.zeros((H, 3 * H), **f32)
+        dbw, dbr, dh0 = torch.zeros(3 * H, **f32), torch.zeros(3 * H, **f32), torch.zeros((B, H), **f32)
+        check(ref.refcuda_gru_backward_quant(T, B, I, H, P(W_t), P(R_t), P(bwf), P(brf), P(x_t), P(dh_new), P(h), P(v),
+                                             C.byref(eng._c_params), C.byref(ms), P(dx), P(dW), P(dR), P(dbw), P(dbr), P(dh0)),
+              "reference CUDA backward")
+
+    try:
+        times = {"forward": [], "backward": []}
+        for i in range(reps + 2):
+            for name, fn in (("forward", forward), ("backward", backward)):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                torch.cuda.synchronize()   # the adapter synchronises the device itself before it returns
+                if i >= 2:
+                    times[name].append((time.perf_counter() - t0) * 1e3)
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": str(e)[:200]}
+    fwd, bwd = statistics.median(times["forward"]), statistics.median(times["backward"])
+    return {"forward_ms": fwd, "backward_ms": bwd, "step_ms": fwd + bwd, "value": T * B / ((fwd + bwd) * 1e-3), "unit": UNIT,
+            "what": "the reference's own CUDA kernels (integer carrier, training forward + QAT backward) compiled for "
+                    "sm_100a, same weights, inputs and quantization parameters; host clock around synchronous calls; "
+                    "loss and optimizer step not included"}
+
+
 def serial_chain_bound(lib, torch, device, cfg, T, I, H, full_kernel_ms, rows=2):
     """T x the minimal per-step latency of each recurrent kernel: the same two kernels timed on a batch that is ONE
     CTA's rows, where nothing but the dependent chain of a time step (barrier, shared-memory exchange of h, the dot
@@ -284,6 +350,8 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     group = None
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"   # keeps the library's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
     lib = cabi.load_library()
@@ -460,14 +528,11 @@ def run_ours(args):
         consumed[slot].record()
         grads = [dW, dR, dbw, dbr]
         if world > 1:
-            flat = torch.cat([g.reshape(-1) for g in grads])
-            dist.all_reduce(flat)
-            flat.div_(world)
-            o = 0
-            for g in grads:
-                g.copy_(flat[o:o + g.numel()].view_as(g)); o += g.numel()
-        for p_, g in zip((W, R, bw, br), grads):
-            p_.add_(g, alpha=-lr)
+            # one NCCL group call for the four gradient tensors the module returned (no packing copy)
+            with coalesced(group=group, device=device, async_ops=False):
+                for g in grads:
+                    dist.all_reduce(g)
+        torch._foreach_add_([W, R, bw, br], grads, alpha=-lr / world)   # mean over ranks and SGD in one multi-tensor kernel
         # device -> host read of the step's result: asynchronous copy into pinned memory, collected one
         # step later so that the host never stalls the queue
         loss_host[slot:slot + 1].copy_(loss.reshape(1), non_blocking=True)
@@ -476,6 +541,8 @@ def run_ours(args):
             loss_ready[1 - slot].synchronize()
             losses.append(float(loss_host[1 - slot]))
 
+    if world > 1:
+        from torch.distributed.distributed_c10d import _coalescing_manager as coalesced
     e2e_steps = min(args.steps, 20)
     for ev in consumed:
         ev.record()
@@ -488,6 +555,7 @@ def run_ours(args):
     if rank == 0:
         cpu = None
         secondary = None
+        reference_cuda = None
         if world == 1:
             secondary = {"aimet_native_kernels": aimet_kernel_bandwidth(lib, torch, device, peak),
                          "affine_qdq": affine_qdq_bandwidth(torch, device, peak),
@@ -497,6 +565,7 @@ def run_ours(args):
                          "kws_body_qat": kws_body_secondary(torch, device, flush, peak)}
             v_cpu, cores, kind, desc, _ = cpu_forward_throughput()
             cpu = {"value": v_cpu, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc}
+            reference_cuda = reference_cuda_step(torch, device, eng, xs[0])
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
@@ -506,7 +575,7 @@ def run_ours(args):
                        "quant": "W8 symmetric per-channel, A8 asymmetric, integer carrier", "l2": "flushed between steps",
                        "kernel_timing": "second pass of the same step with CUDA events around every kernel",
                        "launch": "cuda graph replay" if args.graph == "on" else "eager launches"},
-            "roofline": roofline, "cpu_baseline": cpu,
+            "roofline": roofline, "cpu_baseline": cpu, "reference_cuda": reference_cuda,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * T * B * (I + H) * world, "d2h_bytes_per_step": 4 * world,
                     "final_loss": losses[-1] if losses else None, "ms_per_step": e2e_ms / e2e_steps,
@@ -860,14 +929,15 @@ def run_kws_body(args, torch, dist, lib, device, group, rank, world, local_rank)
     e2e_steps = min(args.steps, 10)
     e2e_ms = timed(e2e, e2e_steps, 3)
     torch.cuda.synchronize()
-    if rank != 0:
-        return
-    peak, peak_kind = _peaks()
+    # per-kernel durations of one more step; every rank runs it (the step holds the gradient all-reduce)
     lib.rxmet_reset_kernel_timing(); lib.rxmet_set_kernel_timing(1)
     eng.step(xs[0], ys[0], 0.0)
     torch.cuda.synchronize()
     kernels = _kernel_ms(lib, _GRU_KERNELS)
     lib.rxmet_set_kernel_timing(0)
+    if rank != 0:
+        return
+    peak, peak_kind = _peaks()
     roof = _roofline_frac(value / world, KWS_FLOPS_PER_ST, KWS_BYTES_PER_ST, peak)
     top = max(kernels, key=kernels.get)
     line = {
@@ -1008,7 +1078,7 @@ def main():
                          "kernel (rxmet_stage_from_pinned_host) or copy-engine transfers")
     ap.add_argument("--affine-log2", type=int, default=26,
                     help="log2 of the element count of the --profile-only affine tensors (26: a small case for captures)")
-    ap.add_argument("--graph", choices=["on", "off"], default="off",
+    ap.add_argument("--graph", choices=["on", "off"], default="on",
                     help="device-resident leg: replay the step as one captured CUDA graph per input set")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only the device-resident leg (for captures under a profiler); prints no bench line")

@@ -43,6 +43,13 @@ RXMET_API const char *rxmet_version(void);
 /* Number of kernels this library has launched in this process so far. */
 RXMET_API uint64_t rxmet_kernel_launch_count(void);
 
+/* How many recurrent passes the caller keeps in flight at once on one GPU (the two directions of a
+ * bidirectional layer on two streams: 2).  The recurrent kernels of wide layers, which hold one CTA per
+ * SM, size their batch tiles so that the CTAs of all those launches are resident together instead of
+ * queueing behind each other.  Default 1; values below 1 are taken as 1.  Results do not depend on
+ * it.  No counterpart in the reference. */
+RXMET_API int rxmet_set_concurrent_passes(int passes);
+
 /* Per-kernel timing, off by default.  While enabled every kernel launch of the
  * library is bracketed by CUDA events on its stream;
  * rxmet_get_kernel_timing waits for the recorded events and returns the summed

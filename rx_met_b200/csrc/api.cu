@@ -143,6 +143,14 @@ void foldStats(rxmet_gru_ranges *r, const float *stats) {
 }  // namespace
 }  // namespace rxmet
 
+namespace rxmet {
+std::atomic<int> &concurrentPassesSetting() {
+    static std::atomic<int> passes{1};
+    return passes;
+}
+int concurrentPasses() { return concurrentPassesSetting().load(); }
+}  // namespace rxmet
+
 using namespace rxmet;
 
 extern "C" {
@@ -150,6 +158,11 @@ extern "C" {
 const char *rxmet_last_error(void) { return lastError().c_str(); }
 const char *rxmet_version(void) { return "rxmet_b200 0.1.0 (sm_100a)"; }
 uint64_t rxmet_kernel_launch_count(void) { return launchCounter().load(); }
+
+int rxmet_set_concurrent_passes(int passes) {
+    concurrentPassesSetting().store(passes < 1 ? 1 : passes);
+    return RXMET_OK;
+}
 
 int rxmet_set_kernel_timing(int enabled) {
     return guarded([&] {

@@ -97,6 +97,10 @@ struct DeviceInfo {
     int device = 0, sms = 0, smemMax = 0;
 };
 const DeviceInfo &currentDevice();
+// Recurrent passes the caller runs side by side on one GPU (rxmet_set_concurrent_passes); at least 1.
+int concurrentPasses();
+// SMs one of those passes can count on.
+inline int smsPerPass() { return std::max(1, currentDevice().sms / concurrentPasses()); }
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when `bytes` exceeds what the kernel
 // was last given.
 void ensureDynamicSmem(const void *kernel, size_t bytes);

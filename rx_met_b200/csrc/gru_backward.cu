@@ -1181,7 +1181,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
         ca.Rq = call.R_q; ca.HP = hpCodes; ca.parts = partsCodes;
         int rb = 1;
-        const int want = std::max(1, (B + sms - 1) / sms);
+        const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
         while (rb < 4 && rb < want && codesSmem(rb * 2) + 1024 <= static_cast<size_t>(smemMax)) rb *= 2;
         auto launchCodes = [&](auto kernel) {
             const size_t smem = codesSmem(rb);

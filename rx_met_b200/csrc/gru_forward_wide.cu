@@ -438,7 +438,7 @@ void forwardWide(const WideCall &call, const Exec &e, Workspace &ws, cudaStream_
         a.h = call.h; a.v = call.v; a.hq = call.hq; a.vq = call.vq;
         a.maskHh = call.maskHh; a.maskGateIn = call.maskGateIn; a.maskGateOut = call.maskGateOut; a.maskH = call.maskH;
         const int groupsMax = std::max(1, kThreads / a.HP);
-        const int want = std::max(1, (B + sms - 1) / sms);
+        const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
         int rb = 1;
         while (rb < 4 && rb * groupsMax < want) rb *= 2;
         const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));

@@ -334,11 +334,12 @@ WideShape shapeFor(int N) {
 
 }  // namespace
 
-size_t widePackedBytes(int K, int N) { return N > kMaxColumns ? 0 : static_cast<size_t>(shapeFor(N).NP) * K * 2; }
+size_t widePackedBytes(int K, int N) { return (N > kMaxColumns || K % kChunk != 0) ? 0 : static_cast<size_t>(shapeFor(N).NP) * K * 2; }
 
 bool wideTakes(int K, int N) {
     static const bool disabled = std::getenv("RXMET_IGRAD_SIMT") != nullptr || std::getenv("RXMET_IGRAD_NARROW") != nullptr;
-    return !disabled && N > 64 && N <= kMaxColumns && K >= kChunk && K % kChunk == 0 && encodeTiled() != nullptr;
+    static const int least = std::getenv("RXMET_IGRAD_STREAM_ALL") != nullptr ? 1 : 65;
+    return !disabled && N >= least && N <= kMaxColumns && K >= kChunk && K % kChunk == 0 && encodeTiled() != nullptr;
 }
 
 bool wideEligible(const Problem &p) {

@@ -206,6 +206,7 @@ int rxmet_lstm_backward_qat(int T, int B, int I, int H, const rxmet_lstm_quant_p
         call.weightIhScale = params->weight_ih_scale;
         call.weightHhScale = params->weight_hh_scale;
         call.codesFitTensorPath = params->config.bitwidth[RXMET_LSTM_INPUT] <= 8 && params->config.bitwidth[RXMET_LSTM_OUTPUT] <= 8;
+        call.codesFitTwoTerms = params->config.bitwidth[RXMET_LSTM_INPUT] <= 16 && params->config.bitwidth[RXMET_LSTM_OUTPUT] <= 16;
         call.weightCodesFitBf16 = params->config.bitwidth[RXMET_LSTM_WEIGHT_HH] <= 8;
         call.weightIhCodesFitBf16 = params->config.bitwidth[RXMET_LSTM_WEIGHT_IH] <= 8;
         lstm::backward(call, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));

@@ -745,6 +745,13 @@ constexpr int kMaxTensorSplits = 40;
 
 }  // namespace
 
+// Splits of the tensor-core weight-gradient partial arrays: the one-tile plan for at most 128 rows, the slab plan
+// (128-row slabs of both problems in one launch) beyond.
+int tensorSplitBound(int rows, int I, int H, int M, int C) {
+    const int single = M <= 143 ? wgrad::splitBound(rows, M, C) : 1;
+    return std::max(single, wgrad::slabPathTakes(I, H, C) ? wgrad::slabSplitBound(I, H, C) : 1);
+}
+
 size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     const size_t rows = static_cast<size_t>(T) * B, C = 4 * static_cast<size_t>(H);
     WorkspaceSizer ws;
@@ -757,8 +764,8 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(2 * kBiasSplits * C);
     ws.take<float>(2 * C);     // per-channel weight scales (QAT)
     ws.take<float>(rows * H);  // h_prev codes for the tensor-core weight gradient (QAT)
-    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, static_cast<int>(C))) * (I + 1) * C);
-    ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C))) * (H + 1) * C);
+    ws.take<float>(static_cast<size_t>(tensorSplitBound(static_cast<int>(rows), I, H, I, static_cast<int>(C))) * (I + 1) * C);
+    ws.take<float>(static_cast<size_t>(tensorSplitBound(static_cast<int>(rows), I, H, H, static_cast<int>(C))) * (H + 1) * C);
     ws.take<int>(1);              // status word of the tensor-memory weight-gradient kernel
     ws.take<uint32_t>(rows * H);  // packed per-step clamp flags
     ws.take<uint8_t>(igrad::widePackedBytes(static_cast<int>(C), I) + 256);   // weight operand of the streaming input-gradient kernel
@@ -782,8 +789,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     float *partBias = ws.take<float>(2 * kBiasSplits * static_cast<size_t>(C));
     float *channelScales = ws.take<float>(2 * static_cast<size_t>(C));
     float *hPrev = ws.take<float>(rows * H);
-    float *tensorIh = ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), I, C)) * (I + 1) * C);
-    float *tensorHh = ws.take<float>(static_cast<size_t>(wgrad::splitBound(static_cast<int>(rows), H, C)) * (H + 1) * C);
+    float *tensorIh = ws.take<float>(static_cast<size_t>(tensorSplitBound(static_cast<int>(rows), I, H, I, C)) * (I + 1) * C);
+    float *tensorHh = ws.take<float>(static_cast<size_t>(tensorSplitBound(static_cast<int>(rows), I, H, H, C)) * (H + 1) * C);
     int *tensorStatus = ws.take<int>(1);
     uint32_t *stepMasks = ws.take<uint32_t>(rows * H);
 
@@ -865,7 +872,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         if (wide) {
             const int HP = (H + 31) / 32 * 32;
             const int groupsMax = std::max(1, 512 / HP);
-            const int want = std::max(1, (B + sms - 1) / sms);
+            const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
             int rb = 1;
             while (rb < 8 && rb * groupsMax < want) rb *= 2;
             const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));
@@ -979,6 +986,37 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             const ReduceJob jobIh{tensorIh, planX.splits, I, call.dqX.scale, static_cast<const uint8_t *>(mk.weight_ih),
                                   static_cast<const uint8_t *>(mk.bias_ih), call.grads.weight_ih, call.grads.bias_ih};
             const ReduceJob jobHh{tensorHh, planH.splits, H, call.dqH.scale, static_cast<const uint8_t *>(mk.weight_hh),
+                                  static_cast<const uint8_t *>(mk.bias_hh), call.grads.weight_hh, call.grads.bias_hh};
+            const int rowBlocks = (std::max(I, H) + 1 + kReduceRows - 1) / kReduceRows;
+            KernelTimer timer__("lstmReduceWeightGradT", st);
+            reduceWeightGradT<<<dim3((C + 31) / 32, rowBlocks, 2), dim3(32, kReduceRows, kReduceLayers), 0, st>>>(jobIh, jobHh, C,
+                                                                                                                  tensorStatus);
+        }
+        afterLaunch("lstmReduceWeightGradT");
+        return;
+    }
+    // Larger layers or 16-bit activation grids: the same tcgen05 kernel over 128-row slabs of both problems in one
+    // launch, a code as two exact bf16 terms when its grid is wider than 8 bits.
+    if (call.quantized && call.codesFitTwoTerms && I % 4 == 0 && H % 4 == 0 && alignedTo(call.x, 16) && (call.h0 || call.dqH.zeroPoint == 0.0f) &&
+        wgrad::slabPathTakes(I, H, C) && std::getenv("RXMET_LSTM_WGRAD_SIMT") == nullptr) {
+        const size_t stateBytes = sizeof(float) * static_cast<size_t>(B) * H;
+        if (call.h0) RXMET_CUDA(cudaMemcpyAsync(hPrev, call.h0, stateBytes, cudaMemcpyDeviceToDevice, st));
+        else RXMET_CUDA(cudaMemsetAsync(hPrev, 0, stateBytes, st));
+        if (T > 1)
+            RXMET_CUDA(cudaMemcpyAsync(hPrev + static_cast<size_t>(B) * H, call.hiddenOutputs, stateBytes * (T - 1),
+                                       cudaMemcpyDeviceToDevice, st));
+        int chunkK = 0;
+        const int splits = wgrad::slabSplits(static_cast<int>(rows), I, H, C, currentDevice().sms, &chunkK);
+        wgrad::Problem px{}, ph{};
+        px.aFloat = call.x; px.aFloatZero = call.dqX.zeroPoint; px.M = I; px.B = gIh; px.partial = tensorIh;
+        ph.aFloat = hPrev; ph.aFloatZero = call.h0 ? call.dqH.zeroPoint : 0.0f; ph.M = H; ph.B = gHh; ph.partial = tensorHh;
+        px.status = ph.status = tensorStatus;
+        wgrad::launchSlabs(px, ph, static_cast<int>(rows), C, chunkK, splits, !call.codesFitTensorPath, st);
+        afterLaunch("weightGrad");
+        {
+            const ReduceJob jobIh{tensorIh, splits, I, call.dqX.scale, static_cast<const uint8_t *>(mk.weight_ih),
+                                  static_cast<const uint8_t *>(mk.bias_ih), call.grads.weight_ih, call.grads.bias_ih};
+            const ReduceJob jobHh{tensorHh, splits, H, call.dqH.scale, static_cast<const uint8_t *>(mk.weight_hh),
                                   static_cast<const uint8_t *>(mk.bias_hh), call.grads.weight_hh, call.grads.bias_hh};
             const int rowBlocks = (std::max(I, H) + 1 + kReduceRows - 1) / kReduceRows;
             KernelTimer timer__("lstmReduceWeightGradT", st);

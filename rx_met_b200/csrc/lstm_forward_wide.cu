@@ -587,7 +587,7 @@ void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspa
         // rows per CTA: enough CTAs to occupy the SMs first, then more rows per thread so that a weight
         // word fetched from L2 serves several rows
         const int groupsMax = std::max(1, kWideThreads / a.HP);
-        const int want = std::max(1, (B + sms - 1) / sms);
+        const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
         int rb = 1;
         while (rb < 8 && rb * groupsMax < want) rb *= 2;
         const int groups = std::max(1, std::min(groupsMax, (want + rb - 1) / rb));

@@ -69,6 +69,7 @@ struct BackwardCall {
     Dequant dqX, dqH, dqC, dqGate[4], dqTanh;
     const float *weightIhScale = nullptr, *weightHhScale = nullptr;
     bool codesFitTensorPath = false;  // x and hidden grids span at most 256 codes around their zero points
+    bool codesFitTwoTerms = false;    // x and hidden grids of at most 16 bits: a code is two exact bf16 terms
     bool weightCodesFitBf16 = false;  // weight_hh grid of at most 8 bits: codes are exact in bf16
     bool weightIhCodesFitBf16 = false;  // the same for weight_ih
 };

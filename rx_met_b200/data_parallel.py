@@ -44,9 +44,15 @@ def make_exchange(group, device) -> Exchange:
             typestr, op = _KINDS[kind]
             if count == 0:
                 return 0
-            t = torch.as_tensor(_DeviceArray(ptr, int(count), typestr), device=device)
-            with torch.cuda.stream(torch.cuda.ExternalStream(stream or 0, device=device)):
+            with torch.cuda.device(device):
+                t = torch.as_tensor(_DeviceArray(ptr, int(count), typestr), device=device)
+                if t.data_ptr() != ptr:
+                    raise RuntimeError("the exchange buffer was copied instead of aliased")
+                # Calibration is not a hot path: the exchange is fenced by device-wide synchronisation on both
+                # sides, so it does not rely on how the process group orders its kernels against foreign streams.
+                torch.cuda.synchronize(device)
                 dist.all_reduce(t, op=ops[op], group=group)
+                torch.cuda.synchronize(device)
             return 0
         except Exception:  # the C caller turns a non-zero return into an error status
             import traceback

@@ -177,8 +177,7 @@ class GruQatStep:
         self.backward()
         if self.group is not None:
             torch.distributed.all_reduce(self.flat_g, group=self.group)
-            self.flat_g.div_(self.world)
-        self.flat_w.add_(self.flat_g, alpha=-lr)
+        self.flat_w.add_(self.flat_g, alpha=-lr / self.world)   # mean over ranks folded into the update
         return loss
 
     # ---- the same step as one graph launch ----------------------------------
@@ -219,8 +218,7 @@ class GruQatStep:
             graph.replay()
             if not local:
                 torch.distributed.all_reduce(self.flat_g, group=self.group)
-                self.flat_g.div_(self.world)
-                self.flat_w.add_(self.flat_g, alpha=-lr)
+                self.flat_w.add_(self.flat_g, alpha=-lr / self.world)   # mean over ranks folded into the update
             return loss
 
         self._graph = graph   # keeps the captured buffers alive with the object

@@ -44,6 +44,8 @@ class StackedGruQat:
         self.group = process_group
         self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
         self.config = config or a16_config()
+        from . import _cabi as cabi
+        self._lib = cabi.load_library()
         f32 = dict(dtype=torch.float32, device=self.device)
         inputs = [I] + [2 * H] * (layers - 1)
         counts = [GruQatStep.parameter_count(i, H) for i in inputs for _ in range(2)]
@@ -88,6 +90,7 @@ class StackedGruQat:
         """Runs the two callables on the current and the side stream and joins them."""
         main = torch.cuda.current_stream(self.device)
         self.side.wait_stream(main)
+        self._lib.rxmet_set_concurrent_passes(2)   # the two directions share the SMs: their CTAs are resident together
         fn_forward()
         with torch.cuda.stream(self.side):
             fn_reverse()

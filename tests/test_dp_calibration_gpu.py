@@ -84,6 +84,23 @@ def test_sharded_histogram_calibration_equals_single_process(tmp_path):
     r0, r1 = np.load(tmp_path / "dp0.npz"), np.load(tmp_path / "dp1.npz")
     torch.cuda.set_device(0)
     single = _calibrate(0, 1, None)
+    problems = []
+
+    def differs(a, b):
+        if a.shape != b.shape:
+            n = min(a.size, b.size)
+            first = int(np.argmax(a[:n] != b[:n])) if np.any(a[:n] != b[:n]) else n
+            return f"shapes {a.shape} / {b.shape}, first difference at {first}"
+        return None if np.array_equal(a, b) else f"{int(np.sum(a != b))} of {a.size} entries"
+
     for k, v in single.items():
-        assert np.array_equal(r0[k], r1[k]), f"ranks disagree on {k}"
-        assert np.array_equal(r0[k], v), f"sharded calibration differs from one process on {k}"
+        between, against = differs(r0[k], r1[k]), differs(r0[k], v)
+        if between:
+            problems.append(f"ranks disagree on {k}: {between}")
+        if against:
+            problems.append(f"sharded calibration differs from one process on {k}: {against}")
+        if k == "l_bundle" and (between or against):
+            text = [bytes(a).decode() for a in (r0[k], r1[k], v)]
+            at = next((i for i, (x, y, z) in enumerate(zip(*text)) if not (x == y == z)), 0)
+            problems.append(" | ".join(t[max(0, at - 120):at + 60] for t in text))
+    assert not problems, "; ".join(problems)
