@@ -17,6 +17,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 
 #include "common.h"
@@ -489,6 +490,153 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardCodes(const __grid_co
             for (int p2 = 0; p2 < P; ++p2) carried += partS[(p2 * RB + r) * H + k];
             a.dh0[o] = carried * keepOf(a.mH0, o);
         }
+    }
+}
+
+// ---- the same recurrence over a cluster of eight CTAs ------------------------------------------
+//
+// For hidden sizes whose recurrent weights fit no single SM as fp32, the eight CTAs of a cluster share a tile
+// of RB batch rows: CTA c owns the hidden units [c H/8, (c+1) H/8) and keeps ITS rows of R (H/8 x 3H values,
+// exact integer codes as fp32) in registers for the whole sequence — thread (unit, part) holds the 3H/8
+// columns of part `part` — so the per-step product needs no weight traffic and no widening of codes at all.
+// Per step every CTA computes the pointwise derivative of its units, stores the scaled gate gradients of its
+// 3 H/8 columns into the dq tile of ALL eight CTAs through distributed shared memory, and after one hardware
+// cluster barrier (release / acquire; every CTA runs the same T iterations) multiplies the complete tile with
+// its register-resident weights.  The dq tile is double-buffered: a CTA can only write the tile of step t-2
+// after every CTA of the cluster has arrived at the barrier of step t-1, that is after it has finished
+// reading the tile of step t.
+struct BackwardClusterArgs {
+    BackwardQArgs q;
+    const int32_t *Rq;  // [H][3H] integer codes as saved by the forward
+};
+
+constexpr int kClusterCtas = 8, kClusterParts = 8;
+
+__device__ __forceinline__ void clusterBarrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int WPT, int RB>  // WPT = 3H / 8 weights per thread, RB batch rows per cluster (a multiple of 8)
+__global__ void __launch_bounds__(256, 1)   // launched with a cluster dimension of kClusterCtas
+recurrentBackwardCluster(const __grid_constant__ BackwardClusterArgs ca) {
+    constexpr int NC = kClusterCtas, P = kClusterParts, RPT = RB / P;
+    const BackwardQArgs &a = ca.q;
+    const int H = a.H, C = 3 * a.H, HS = H / NC;
+    extern __shared__ __align__(16) unsigned char smemRawC[];
+    float *dqS = reinterpret_cast<float *>(smemRawC);       // [2][RB][C]: scaled gate gradients of the whole tile
+    float *partS = dqS + 2 * RB * C;                        // [P][RB][HS]
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int tid = threadIdx.x, jl = tid % HS, part = tid / HS;
+    const int j = static_cast<int>(rank) * HS + jl;
+    const int b0 = static_cast<int>(blockIdx.x / NC) * RB;
+
+    float w[WPT];
+#pragma unroll
+    for (int i = 0; i < WPT; ++i) w[i] = static_cast<float>(ca.Rq[static_cast<size_t>(j) * C + part * WPT + i]);
+    for (int i = tid; i < 2 * RB * C; i += blockDim.x) dqS[i] = 0.0f;
+    for (int i = tid; i < P * RB * HS; i += blockDim.x) partS[i] = 0.0f;
+    const float scale[3] = {a.scaleR[j], a.scaleR[H + j], a.scaleR[2 * H + j]};
+    // this CTA's view of the same dq element in every CTA of the cluster
+    uint32_t tile[NC];
+    {
+        const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(dqS));
+#pragma unroll
+        for (int d = 0; d < NC; ++d) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(tile[d]) : "r"(local), "r"(d));
+    }
+
+    float dhBase[RPT];
+    StepOperands cur[RPT], nxt[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) dhBase[i] = 0.0f;
+    auto fetch = [&](int t, StepOperands (&dst)[RPT]) {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int b = b0 + part + P * i;
+            if (b >= a.B) continue;
+            const size_t row = static_cast<size_t>(t) * a.B + b, hi = row * H + j;
+            const float *vRow = a.v + row * 4 * H;
+            StepOperands o;
+            o.z = vRow[j]; o.r = vRow[H + j]; o.g = vRow[2 * H + j]; o.qg = vRow[3 * H + j];
+            o.hOld = a.h[hi];
+            o.dhNew = a.dhNew[hi + static_cast<size_t>(a.B) * H];
+            o.keepBits = a.stepBits ? a.stepBits[hi] : 0x1fffu;
+            dst[i] = o;
+        }
+    };
+    fetch(a.T - 1, cur);
+    clusterBarrier();  // every CTA has cleared its tiles before anyone stores into them
+
+    for (int t = a.T - 1; t >= 0; --t) {
+        const int buf = t & 1;
+        if (t > 0) fetch(t - 1, nxt);
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int r = part + P * i, b = b0 + r;
+            float q3[3] = {0.0f, 0.0f, 0.0f};
+            if (b < a.B) {
+                const size_t gi = (static_cast<size_t>(t) * a.B + b) * C + j;
+                const StepOperands o = cur[i];
+                auto keep = [&](int pos) { return static_cast<float>((o.keepBits >> pos) & 1u); };
+                float carried = dhBase[i];
+#pragma unroll
+                for (int p2 = 0; p2 < P; ++p2) carried += partS[(p2 * RB + r) * HS + jl];
+                const float dhTotal = (o.dhNew + carried) * keep(12);
+                dhBase[i] = o.z * dhTotal;
+                const float dg = (1.0f - o.z) * dhTotal;
+                const float dz = (o.hOld - o.g) * dhTotal;
+                const float dpG = (1.0f - o.g * o.g) * dg * keep(2) * keep(5);
+                const float dqG = dpG * o.r;
+                const float dr = dpG * o.qg;
+                const float dpR = (o.r * (1.0f - o.r)) * dr;
+                const float dpZ = (o.z * (1.0f - o.z)) * dz;
+                const float kz = keep(0) * keep(3), kr = keep(1) * keep(4);
+                const float pz = dpZ * kz * keep(9), pr = dpR * kr * keep(10), pg = dpG * keep(11);
+                const float qz = dpZ * kz * keep(6), qr = dpR * kr * keep(7), qn = dqG * keep(8);
+                a.dp[gi] = pz; a.dp[gi + H] = pr; a.dp[gi + 2 * H] = pg;
+                a.dq[gi] = qz; a.dq[gi + H] = qr; a.dq[gi + 2 * H] = qn;
+                q3[0] = qz * scale[0]; q3[1] = qr * scale[1]; q3[2] = qn * scale[2];
+            }
+            const uint32_t at = static_cast<uint32_t>(sizeof(float)) * static_cast<uint32_t>((buf * RB + r) * C + j);
+#pragma unroll
+            for (int d = 0; d < NC; ++d)
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(tile[d] + at + static_cast<uint32_t>(sizeof(float)) * g * H), "f"(q3[g])
+                                 : "memory");
+        }
+        clusterBarrier();  // the tile of step t is complete in every CTA
+
+        float acc[RB];
+#pragma unroll
+        for (int r = 0; r < RB; ++r) acc[r] = 0.0f;
+        const float *tileRow = dqS + static_cast<size_t>(buf) * RB * C + part * WPT;
+#pragma unroll
+        for (int i4 = 0; i4 < WPT / 4; ++i4) {
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const float4 d = *reinterpret_cast<const float4 *>(tileRow + r * C + 4 * i4);
+                acc[r] = fmaf(w[4 * i4], d.x, acc[r]);
+                acc[r] = fmaf(w[4 * i4 + 1], d.y, acc[r]);
+                acc[r] = fmaf(w[4 * i4 + 2], d.z, acc[r]);
+                acc[r] = fmaf(w[4 * i4 + 3], d.w, acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RB; ++r) partS[(part * RB + r) * HS + jl] = acc[r];
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) cur[i] = nxt[i];
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int r = part + P * i, b = b0 + r;
+        if (b >= a.B) continue;
+        const size_t o = static_cast<size_t>(b) * H + j;
+        float carried = dhBase[i];
+#pragma unroll
+        for (int p2 = 0; p2 < P; ++p2) carried += partS[(p2 * RB + r) * HS + jl];
+        a.dh0[o] = carried * keepOf(a.mH0, o);
     }
 }
 
@@ -1180,19 +1328,58 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         q.mIh = mk.weight_ih_linear; q.mHh = mk.weight_hh_linear; q.mGateIn = mk.gate_input;
         q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
         ca.Rq = call.R_q; ca.HP = hpCodes; ca.parts = partsCodes;
-        int rb = 1;
-        const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
-        while (rb < 4 && rb < want && codesSmem(rb * 2) + 1024 <= static_cast<size_t>(smemMax)) rb *= 2;
-        auto launchCodes = [&](auto kernel) {
-            const size_t smem = codesSmem(rb);
-            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
-            KernelTimer timer__("recurrentBackward", st);
-            kernel<<<(B + rb - 1) / rb, hpCodes * partsCodes, smem, st>>>(ca);
-        };
-        if (rb == 1) launchCodes(recurrentBackwardCodes<1>);
-        else if (rb == 2) launchCodes(recurrentBackwardCodes<2>);
-        else launchCodes(recurrentBackwardCodes<4>);
-        afterLaunch("recurrentBackward");
+        // H = 256, opt-in (RXMET_GRU_BWD_CLUSTER): the cluster kernel, weights as fp32 in the registers of eight CTAs.
+        // Correct, but measured slower than the kernel below at T = 100, B = 128 (0.59 against 0.51 ms): eight
+        // warps per SM issue at 40 %, and only 15 clusters of eight are resident on this part.
+        bool clusterRan = false;
+        if (H == 256 && std::getenv("RXMET_GRU_BWD_CLUSTER") != nullptr) {
+            BackwardClusterArgs cl{};
+            cl.q = q; cl.Rq = call.R_q;
+            const int rbCluster = B * concurrentPasses() * kClusterCtas > 8 * sms ? 16 : 8;
+            const size_t smem = sizeof(float) * (2 * static_cast<size_t>(rbCluster) * C + static_cast<size_t>(kClusterParts) * rbCluster * (H / kClusterCtas));
+            const int clusters = (B + rbCluster - 1) / rbCluster;
+            auto launchCluster = [&](auto kernel) -> bool {
+                ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3(static_cast<unsigned>(clusters * kClusterCtas));
+                cfg.blockDim = dim3((H / kClusterCtas) * kClusterParts);
+                cfg.dynamicSmemBytes = smem;
+                cfg.stream = st;
+                cudaLaunchAttribute clusterDim{};
+                clusterDim.id = cudaLaunchAttributeClusterDimension;
+                clusterDim.val.clusterDim.x = kClusterCtas;
+                clusterDim.val.clusterDim.y = 1;
+                clusterDim.val.clusterDim.z = 1;
+                cfg.attrs = &clusterDim;
+                cfg.numAttrs = 1;
+                int resident = 0;
+                if (cudaOccupancyMaxActiveClusters(&resident, kernel, &cfg) != cudaSuccess || resident < 1) {
+                    cudaGetLastError();
+                    return false;
+                }
+                if (std::getenv("RXMET_DEBUG_CLUSTER")) std::fprintf(stderr, "cluster backward: %d clusters of %d rows, %d resident at most\n", clusters, rbCluster, resident);
+                KernelTimer timer__("recurrentBackward", st);
+                RXMET_CUDA(cudaLaunchKernelEx(&cfg, kernel, cl));
+                return true;
+            };
+            clusterRan = rbCluster == 16 ? launchCluster(recurrentBackwardCluster<96, 16>) : launchCluster(recurrentBackwardCluster<96, 8>);
+            if (clusterRan) afterLaunch("recurrentBackwardCluster");
+        }
+        if (!clusterRan) {
+            int rb = 1;
+            const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
+            while (rb < 4 && rb < want && codesSmem(rb * 2) + 1024 <= static_cast<size_t>(smemMax)) rb *= 2;
+            auto launchCodes = [&](auto kernel) {
+                const size_t smem = codesSmem(rb);
+                ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+                KernelTimer timer__("recurrentBackward", st);
+                kernel<<<(B + rb - 1) / rb, hpCodes * partsCodes, smem, st>>>(ca);
+            };
+            if (rb == 1) launchCodes(recurrentBackwardCodes<1>);
+            else if (rb == 2) launchCodes(recurrentBackwardCodes<2>);
+            else launchCodes(recurrentBackwardCodes<4>);
+            afterLaunch("recurrentBackward");
+        }
     } else if (registerPath) {
         const int CW = H <= 32 ? 16 : (H <= 64 ? 32 : 64);
         // The tensor-core kernel takes its fragments from the integer codes themselves; only the

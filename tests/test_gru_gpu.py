@@ -335,6 +335,23 @@ def test_kws_body_layer_shapes(gl, cfg_name, shape):
         close(gb[k], wb[k], what=k)
 
 
+def test_cluster_backward_kernel_agrees(gl, monkeypatch):
+    """The opt-in backward recurrence over clusters of eight CTAs (weights in registers, gate gradients exchanged
+    through distributed shared memory) gives the gradients of the default kernel; a batch that leaves rows of
+    the last cluster empty."""
+    T, B, I, H = 5, 19, 40, 256
+    cfg = ol.make_config(**CONFIGS["a16"])
+    prob, params = calibrated((T, B, I, H), seed=77, cfg=cfg, with_h0=True, x_scale=1.2)
+    want = ol.forward_quant("orc", *prob, params, training=True)
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = np.random.default_rng(5).standard_normal((T, B, H)).astype(np.float32)
+    wb = ol.backward_quant(want, dh_new, want["h"], want["v"], params, want["masks"])
+    monkeypatch.setenv("RXMET_GRU_BWD_CLUSTER", "1")
+    gb = gl.backward_quant(want, dh_new, want["h"], want["v"], params, want["masks"].arr)
+    for k in wb:
+        close(gb[k], wb[k], what=k)
+
+
 def test_bounded_device_wait_gives_up_with_a_status(gl):
     """The poll loop of the tcgen05 kernels on a barrier nothing completes: the kernel returns after its
     limit, the status word is set, the call reports RXMET_ERR_DEVICE_TIMEOUT and the context keeps working."""
