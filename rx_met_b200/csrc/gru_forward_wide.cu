@@ -23,10 +23,12 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.h"
 #include "gru_device.cuh"
 #include "gru_forward_wide.h"
+#include "plane_proj_umma.cuh"
 
 namespace rxmet {
 namespace gru {
@@ -206,6 +208,7 @@ struct RecurrentArgs {
     float *v;                // [T][B][4H] dequantized
     int32_t *hq, *vq;        // optional codes
     uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;
+    const int *poison;       // status word of the tensor-core projection: non-zero turns the hidden outputs into NaN
 };
 
 template <int RB, bool WS>
@@ -238,7 +241,8 @@ recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__
         rs[gate] = active ? a.rescale[gate * H + j] : Rescale{1, 0};
     }
     const int32_t zpH = g.zp[RXMET_GRU_H], loH = g.qlo[RXMET_GRU_H];
-    const float scaleH = g.eff[RXMET_GRU_H];
+    // a projection whose bounded wait gave up left unusable codes: make that loud
+    const float scaleH = (a.poison && *a.poison) ? __int_as_float(0x7fc00000) : g.eff[RXMET_GRU_H];
     int32_t hOld[RB];
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
@@ -343,6 +347,31 @@ recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__
 struct Layout {
     uint32_t *xPlanes, *h0Planes, *wWords, *rWords;
     int64_t *addX, *addH;
+    uint4 *wTiles;     // input weights as canonical tensor-core tiles (plane_proj_umma.cuh)
+    int *projStatus;
+};
+
+// Epilogue of the tensor-core input projection: exact 64-bit sum of the two planes and the addend, the
+// rounding rescale onto the linear-output grid, clamp, code and keep flag.
+struct PlaneEpilogue {
+    const int64_t *addend;
+    const Rescale *rescale;
+    int32_t zpOut, lo, hi;
+    int16_t *out;
+    uint8_t *mask;
+    int C;
+    struct Channel {
+        int64_t addend;
+        Rescale rs;
+    };
+    __device__ Channel channel(int c) const { return Channel{addend[c], rescale[c]}; }
+    __device__ void store(const Channel &ch, size_t row, int c, const int32_t (&acc)[2]) const {
+        uint8_t keep;
+        const int32_t q = clampCode(static_cast<int32_t>(applyRescale(combine(acc[0], acc[1], ch.addend), ch.rs)) + zpOut, lo, hi, keep);
+        const size_t o = row * C + c;
+        out[o] = static_cast<int16_t>(q);
+        if (mask) mask[o] = keep;
+    }
 };
 
 template <class W>
@@ -356,6 +385,8 @@ Layout layoutWide(W &ws, int T, int B, int I, int H) {
     l.rWords = ws.template take<uint32_t>(kH * C);
     l.addX = ws.template take<int64_t>(C);
     l.addH = ws.template take<int64_t>(C);
+    l.wTiles = ws.template take<uint4>(C * planeproj::paddedK(static_cast<int>(kI)) / 16);
+    l.projStatus = ws.template take<int>(1);
     return l;
 }
 
@@ -408,7 +439,37 @@ void forwardWide(const WideCall &call, const Exec &e, Workspace &ws, cudaStream_
                                                                                    g.qlo[RXMET_GRU_H], l.h0Planes);
         afterLaunch("planesFromCodes");
     }
-    {
+    // Input projection: the tcgen05 kind::i8 kernel when the channel count tiles by 128 and the operands fit
+    // shared memory (RXMET_IPROJ_SIMT turns it off), else the dp4a kernel.
+    const int kPadI = planeproj::paddedK(kI);
+    const int rowsPerTile = planeproj::sharedBytes(kPadI, 2, 128) <= 200 * 1024 ? 128 : 64;
+    const bool tensorProjection = C % planeproj::kChannelTile == 0 && planeproj::sharedBytes(kPadI, 2, rowsPerTile) <= 200 * 1024 &&
+                                  std::getenv("RXMET_IPROJ_SIMT") == nullptr;
+    if (tensorProjection) {
+        RXMET_CUDA(cudaMemsetAsync(l.projStatus, 0, sizeof(int), st));
+        {
+            KernelTimer timer__("packWeightWords", st);
+            planeproj::packTiles<<<gridFor(static_cast<size_t>(C) * kPadI / 16, 256), 256, 0, st>>>(l.wWords, kI, C, kPadI, l.wTiles);
+            afterLaunch("packTiles");
+        }
+        planeproj::Problem pp{};
+        pp.planes = l.xPlanes; pp.rows = static_cast<int>(rows); pp.kWords = kI; pp.tiles = l.wTiles; pp.C = C; pp.status = l.projStatus;
+        PlaneEpilogue epi{};
+        epi.addend = l.addX; epi.rescale = call.gemmX;
+        epi.zpOut = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR]; epi.lo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR]; epi.hi = g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR];
+        epi.out = call.ihCodes; epi.mask = call.maskIh; epi.C = C;
+        const size_t smem = planeproj::sharedBytes(kPadI, 2, rowsPerTile);
+        const int rowTiles = static_cast<int>((rows + rowsPerTile - 1) / rowsPerTile);
+        const int grid = std::max(1, std::min(rowTiles, smsPerPass()));
+        auto launchTensor = [&](auto kernel) {
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("inputLinear", st);
+            kernel<<<grid, planeproj::kThreads, smem, st>>>(pp, epi);
+        };
+        if (rowsPerTile == 128) launchTensor(planeproj::planeProjUmma<PlaneEpilogue, 2, 128>);
+        else launchTensor(planeproj::planeProjUmma<PlaneEpilogue, 2, 64>);
+        afterLaunch("inputLinear");
+    } else {
         InputArgs a{};
         a.rows = static_cast<int>(rows); a.C = C; a.kWords = kI;
         a.x = l.xPlanes; a.words = l.wWords; a.addend = l.addX; a.rescale = call.gemmX;
@@ -437,6 +498,7 @@ void forwardWide(const WideCall &call, const Exec &e, Workspace &ws, cudaStream_
         a.h0 = call.h0Codes; a.hPad = call.hPad; a.h0Planes = l.h0Planes;
         a.h = call.h; a.v = call.v; a.hq = call.hq; a.vq = call.vq;
         a.maskHh = call.maskHh; a.maskGateIn = call.maskGateIn; a.maskGateOut = call.maskGateOut; a.maskH = call.maskH;
+        a.poison = tensorProjection ? l.projStatus : nullptr;
         const int groupsMax = std::max(1, kThreads / a.HP);
         const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
         int rb = 1;
