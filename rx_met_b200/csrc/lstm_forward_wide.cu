@@ -31,9 +31,11 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.h"
 #include "lstm_device.cuh"
+#include "plane_proj_umma.cuh"
 #include "lstm_kernels.h"
 
 namespace rxmet {
@@ -264,6 +266,7 @@ struct WideRecurrentArgs {
     float *output;           // [T][B][H] dequantized
     float *finalHidden, *finalCell;
     rxmet_lstm_trace ck;     // optional checkpoints (weight_ih_linear is written by inputLinearWide)
+    const int *poison;       // status word of the tensor-core projection: non-zero turns the outputs into NaN
 };
 
 // WS: weight_hh (4H x H bytes) fits shared memory beside the code rows and is copied there once, which
@@ -314,7 +317,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_co
     const float cLo = static_cast<float>(s.lo[opC] - s.zp[opC]), cHi = static_cast<float>(s.hi[opC] - s.zp[opC]);
     const float oLo = static_cast<float>(s.lo[opO] - s.zp[opO]), oHi = static_cast<float>(s.hi[opO] - s.zp[opO]);
     const int32_t cBase = s.zp[opC] - s.lo[opC], hBase = s.zp[opO] - s.lo[opO];
-    const float scaleH = s.scale[opO];
+    const float scaleH = (a.poison && *a.poison) ? __int_as_float(0x7fc00000) : s.scale[opO];
     const size_t stepC = static_cast<size_t>(a.B) * C, stepH = static_cast<size_t>(a.B) * H;
     __syncthreads();
 
@@ -442,6 +445,39 @@ struct WideLayout {
     uint32_t *x, *h0, *wIh, *wHh;
     float *c0, *channel, *lhs;
     int64_t *addIh, *addHh;
+    uint4 *ihTiles;    // weight_ih as canonical tensor-core tiles (plane_proj_umma.cuh)
+    int *projStatus;
+};
+
+// Epilogue of the tensor-core input projection: the exact sum of the planes and the addend rounded once to
+// float, then the reference's float rescale, clamp and gate-grid rescale (the same lines as inputLinearWide).
+template <int PLANES>
+struct WidePlaneEpilogue {
+    const int64_t *addend;
+    const float *fields;     // the per-channel float block (kChannelFields x 4H)
+    ScalarExec s;
+    int H;
+    float *lhs, *linear;
+    uint8_t *linearClamped;
+    struct Channel {
+        int64_t addend;
+        DevRescale out, toGate;
+    };
+    __device__ Channel channel(int c) const {
+        const size_t C = 4 * static_cast<size_t>(H);
+        return Channel{addend[c], DevRescale{fields[static_cast<size_t>(kIhOutMult) * C + c], fields[static_cast<size_t>(kIhOutPow2) * C + c]},
+                       s.ihToGate[c / H]};
+    }
+    __device__ void store(const Channel &ch, size_t row, int c, const int32_t (&acc)[PLANES]) const {
+        const int op = RXMET_LSTM_WEIGHT_IH_LINEAR;
+        const float cLo = static_cast<float>(s.lo[op] - s.zp[op]), cHi = static_cast<float>(s.hi[op] - s.zp[op]);
+        uint8_t m;
+        const float cen = linearCentredF(combine<PLANES>(acc, ch.addend), ch.out, cLo, cHi, m);
+        const size_t o = row * (4 * static_cast<size_t>(H)) + c;
+        lhs[o] = rescaleF(cen, ch.toGate);
+        if (linear) linear[o] = cen + s.zpF[op];
+        if (linearClamped) linearClamped[o] = m;
+    }
 };
 
 template <class W>
@@ -458,6 +494,8 @@ WideLayout layoutWide(W &ws, int T, int B, int I, int H, int planes) {
     l.addHh = ws.template take<int64_t>(C);
     l.channel = ws.template take<float>(kChannelFields * C);
     l.lhs = ws.template take<float>(rows * C);
+    l.ihTiles = ws.template take<uint4>(C * planeproj::paddedK(static_cast<int>(kIh)) / 16);
+    l.projStatus = ws.template take<int>(1);
     return l;
 }
 
@@ -550,7 +588,37 @@ void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspa
     const rxmet_lstm_trace noTrace{};
     const rxmet_lstm_trace &ck = call.checkpoints ? *call.checkpoints : noTrace;
     const int sms = currentDevice().sms;
-    {
+    // Input projection: the tcgen05 kind::i8 kernel when 4H tiles by 128 and the operands fit shared memory
+    // (RXMET_IPROJ_SIMT turns it off), else the dp4a kernel.
+    const int kPadIh = planeproj::paddedK(kIh);
+    const int rowsPerTile = planeproj::sharedBytes(kPadIh, planes, 128) <= 200 * 1024 ? 128 : 64;
+    const bool tensorProjection = C % planeproj::kChannelTile == 0 && planeproj::sharedBytes(kPadIh, planes, rowsPerTile) <= 200 * 1024 &&
+                                  std::getenv("RXMET_IPROJ_SIMT") == nullptr;
+    if (tensorProjection) {
+        RXMET_CUDA(cudaMemsetAsync(l.projStatus, 0, sizeof(int), st));
+        {
+            KernelTimer timer__("lstmPrepChannelsWide", st);
+            planeproj::packTiles<<<gridFor(static_cast<size_t>(C) * kPadIh / 16, 256), 256, 0, st>>>(l.wIh, kIh, C, kPadIh, l.ihTiles);
+        }
+        afterLaunch("packTiles");
+        planeproj::Problem pp{};
+        pp.planes = l.x; pp.rows = static_cast<int>(rows); pp.kWords = kIh; pp.tiles = l.ihTiles; pp.C = C; pp.status = l.projStatus;
+        const size_t smem = planeproj::sharedBytes(kPadIh, planes, rowsPerTile);
+        const int rowTiles = static_cast<int>((rows + rowsPerTile - 1) / rowsPerTile);
+        const int grid = std::max(1, std::min(rowTiles, smsPerPass()));
+        auto launchTensor = [&](auto kernel, auto epi) {
+            epi.addend = l.addIh; epi.fields = l.channel; epi.s = s; epi.H = H; epi.lhs = l.lhs;
+            epi.linear = ck.weight_ih_linear; epi.linearClamped = ck.weight_ih_linear_clamped;
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("lstmInputLinearWide", st);
+            kernel<<<grid, planeproj::kThreads, smem, st>>>(pp, epi);
+        };
+        if (planes == 2 && rowsPerTile == 128) launchTensor(planeproj::planeProjUmma<WidePlaneEpilogue<2>, 2, 128>, WidePlaneEpilogue<2>{});
+        else if (planes == 2) launchTensor(planeproj::planeProjUmma<WidePlaneEpilogue<2>, 2, 64>, WidePlaneEpilogue<2>{});
+        else if (rowsPerTile == 128) launchTensor(planeproj::planeProjUmma<WidePlaneEpilogue<1>, 1, 128>, WidePlaneEpilogue<1>{});
+        else launchTensor(planeproj::planeProjUmma<WidePlaneEpilogue<1>, 1, 64>, WidePlaneEpilogue<1>{});
+        afterLaunch("lstmInputLinearWide");
+    } else {
         WideInputArgs a{};
         a.rows = static_cast<int>(rows); a.H = H; a.kWords = kIh;
         a.x = l.x; a.words = l.wIh; a.addend = l.addIh; a.channel = l.channel; a.s = s; a.lhs = l.lhs;
@@ -584,6 +652,7 @@ void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspa
         for (int t = 0; t < kTables; ++t) a.tableOffset[t] = e.wide.offset[t];
         a.lhs = l.lhs; a.h0 = l.h0; a.c0 = l.c0; a.s = s;
         a.output = call.output; a.finalHidden = call.finalHidden; a.finalCell = call.finalCell; a.ck = ck;
+        a.poison = tensorProjection ? l.projStatus : nullptr;
         // rows per CTA: enough CTAs to occupy the SMs first, then more rows per thread so that a weight
         // word fetched from L2 serves several rows
         const int groupsMax = std::max(1, kWideThreads / a.HP);

@@ -66,7 +66,7 @@ inline size_t sharedBytes(int kPad, int planes, int rowsPerTile) {
 // words [kWords][C] (four signed codes along k per word) -> per channel tile of 128 the canonical K-major A
 // operand: byte (c, k) of tile c / 128 at ((c % 128) / 8) * (kPad / 16) * 128 + (k / 16) * 128 + (c % 8) * 16 + k % 16;
 // k beyond 4 kWords is zero.  One thread per 16-byte row of a core matrix.
-__global__ void packTiles(const uint32_t *__restrict__ words, int kWords, int C, int kPad, uint4 *__restrict__ tiles) {
+static __global__ void packTiles(const uint32_t *__restrict__ words, int kWords, int C, int kPad, uint4 *__restrict__ tiles) {
     const int groups = kPad / 16;
     const size_t total = static_cast<size_t>(C) * groups;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
