@@ -377,6 +377,22 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
+    if args.profile_only and args.workload == "lstm_sweep":
+        # one small inference forward of the configs[4] layer (T = --lstm-T or 50, B = 256) for captures under a profiler
+        from rx_met_b200 import _cabi_lstm as L
+        from rx_met_b200 import _quant_lstm as m
+        T, B, I, H = args.lstm_T or 50, 256, 256, 512
+        w = _lstm_weights(torch, device, I, H, 200)
+        gen = torch.Generator(device="cpu").manual_seed(78)
+        session = m.CalibrationSession(m._config_to_json(L.mixed_config(4, 16)), I, H, True, "minmax")
+        session.collect(torch.randn((50, 64, I), generator=gen).to(device), *w)
+        bundle = session.finalize(False)["bundle_json"]
+        x = torch.randn((T, B, I), generator=gen).to(device)
+        for _ in range(max(args.steps, 1) + args.warmup):
+            m.lstm_forward_quantized(x, *w, None, None, False, bundle)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_only": True, "workload": "lstm_sweep", "T": T, "B": B}), flush=True)
+        return
     if args.workload in ("lstm_sweep", "lstm_bi"):
         flush_ = torch.empty(256 << 20, dtype=torch.uint8, device=device)
         fn = lstm_w4a16_sweep if args.workload == "lstm_sweep" else lstm_bidirectional_a16

@@ -436,6 +436,337 @@ __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_co
     }
 }
 
+// ---- the recurrence with the per-step product on the tensor cores --------------------------------------------
+//
+// For hidden sizes whose weight_hh fits no single SM (and for large batches, where dp4a is the bound), the
+// 4H x H product of every step runs as tcgen05.mma kind::i8.  The hidden units are cut into tiles of 32: a
+// CTA owns one unit tile - its 128 gate channels (lane 32 g + u of tensor memory = gate g of unit u) with their
+// 128 x H weight bytes resident in shared memory as the canonical K-major A operand - for the rows of one ROW
+// GROUP, and the H / 32 CTAs of a row group together advance those rows one step at a time:
+//
+//   * the hidden codes of step t - 1 (byte planes, [rows][planes][K]) lie in a global exchange buffer; a CTA
+//     stages them 64 rows at a time into shared memory (cp.async straight into the canonical B layout, next
+//     sub-block in flight), one thread issues PLANES x K / 32 MMAs into one of two accumulator buffers, and
+//     the epilogue of the previous sub-block runs meanwhile;
+//   * epilogue, phase A (warp = gate, lane = unit): accumulators -> exact sum -> the reference's float rescale,
+//     clamp, gate-grid rescale, + the input projection's term, clamp, activation table -> gate output, kept
+//     in shared memory; phase B (after a barrier of the four warps of a row chunk; warp = four rows, lane =
+//     unit): cell update, tanh table, hidden code; the new hidden bytes go to the other half of the exchange
+//     buffer, 32 neighbouring units per store;
+//   * after its last sub-block a CTA publishes the step (fence, one atomic increment of the group's counter)
+//     and waits until all CTAs of its group have published it.  The launch is cooperative (all CTAs are
+//     resident); the wait is bounded and, when it gives up, sets the status word, stops all further waiting
+//     of the CTA and poisons its outputs with NaN.
+constexpr int kUnitTile = 32, kSubRows = 64, kGroupSpinLimit = 1 << 22;
+
+struct UmmaRecurrentArgs {
+    int T, B, H, kWords;
+    int groups, rowsPerGroup;     // row groups and rows of each (a multiple of 16)
+    const uint4 *tiles;           // [H / 32][128 x kPad bytes]: weight_hh tiles, canonical K-major
+    const int64_t *addend;        // [4H]
+    const float *channel;
+    const int32_t *tables;
+    int tableOffset[kTables];
+    const float *lhs;             // [T][B][4H]
+    uint32_t *exchange[2];        // 2 x [B][PLANES][kWords] hidden byte planes; [0] holds h0 at launch
+    float *cell;                  // [B][H] centred cell codes, c0 at launch, updated in place
+    ScalarExec s;
+    float *output, *finalHidden, *finalCell;
+    rxmet_lstm_trace ck;
+    unsigned int *counters;       // [groups], zero at launch
+    int *status;                  // set to 1 when a bounded wait gave up
+    const int *poison;
+};
+
+static __global__ void packHhTiles(const uint2 *__restrict__ words, int kWords, int H, int kPad, uint4 *__restrict__ tiles) {
+    const int groups = kPad / 16, C = 4 * H;
+    const size_t total = static_cast<size_t>(C) * groups;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int kg = static_cast<int>(i / C), c = static_cast<int>(i % C);
+        const int g = c / H, j = c % H;   // consecutive threads -> consecutive units of one gate
+        uint32_t v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kw = 4 * kg + e;
+            uint32_t word = 0u;
+            if (kw < kWords) {
+                const uint2 pair = words[(static_cast<size_t>(g >> 1) * kWords + kw) * H + j];
+                word = (g & 1) ? pair.y : pair.x;
+            }
+            v[e] = word;
+        }
+        const int tile = j / kUnitTile, lane = 32 * g + j % kUnitTile;
+        const size_t at = static_cast<size_t>(tile) * (128 * static_cast<size_t>(kPad) / 16) + static_cast<size_t>(lane / 8) * (groups * 8) +
+                          static_cast<size_t>(kg) * 8 + lane % 8;
+        tiles[at] = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+template <int PLANES>
+__global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constant__ UmmaRecurrentArgs a) {
+    using namespace umma;
+    constexpr uint32_t kBufCols = PLANES * kSubRows;
+    constexpr uint32_t kTmemCols = 2 * kBufCols;
+    constexpr uint32_t kIdesc = planeproj::instructionDescriptor(kSubRows);
+    extern __shared__ __align__(128) uint8_t smemU[];
+    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ uint32_t tmemSlot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = a.H, C = 4 * H, kWords = a.kWords, kPad = planeproj::paddedK(kWords);
+    const int tilesPerGroup = H / kUnitTile;
+    const int ut = blockIdx.x % tilesPerGroup, group = blockIdx.x / tilesPerGroup;
+    const int rowBegin = group * a.rowsPerGroup, rowEnd = min(a.B, rowBegin + a.rowsPerGroup);
+    const int subBlocks = (max(rowEnd - rowBegin, 0) + kSubRows - 1) / kSubRows;
+    const uint32_t groupStride = static_cast<uint32_t>(kPad / 16) * kCore;
+    const uint32_t tileBytes = 128u * kPad, planeBytes = static_cast<uint32_t>(kSubRows) * kPad;
+    uint8_t *aTile = smemU;                                   // [16][kPad / 16][8][16]
+    uint8_t *bPlanes = smemU + tileBytes;                     // 2 x PLANES x [8][kPad / 16][8][16]
+    float *gateS = reinterpret_cast<float *>(bPlanes + 2 * PLANES * planeBytes);   // [4 chunks][4 gates][16 rows][32 units]
+    const ScalarExec &s = a.s;
+    volatile int *failFlag = &failed;
+
+    if (tid == 0) {
+        failed = 0;
+        for (int i = 0; i < 2; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smemAddr(&bars[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemSlot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    {
+        const uint4 *src = a.tiles + static_cast<size_t>(ut) * (tileBytes / 16);
+        for (uint32_t i = tid; i < tileBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(aTile)[i] = __ldg(src + i);
+        for (uint32_t i = tid; i < 2 * PLANES * planeBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(bPlanes)[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmemSlot;
+
+    // phase A role: gate `gate` of unit j for the 16 rows of chunk `chunk`; phase B role: rows 4 gate .. + 3 of the chunk
+    const int gate = warp & 3, chunk = warp >> 2;
+    const int j = ut * kUnitTile + lane, c = gate * H + j;
+    const int64_t addend = a.addend[c];
+    const DevRescale outR{a.channel[static_cast<size_t>(kHhOutMult) * C + c], a.channel[static_cast<size_t>(kHhOutPow2) * C + c]};
+    const DevRescale toGate = s.hhToGate[gate];
+    const int opHh = RXMET_LSTM_WEIGHT_HH_LINEAR, opC = RXMET_LSTM_CELL_STATE, opO = RXMET_LSTM_OUTPUT, opIn = RXMET_LSTM_INPUT_GATE_INPUT + gate;
+    const float hhLo = static_cast<float>(s.lo[opHh] - s.zp[opHh]), hhHi = static_cast<float>(s.hi[opHh] - s.zp[opHh]);
+    const float giLo = static_cast<float>(s.lo[opIn] - s.zp[opIn]), giHi = static_cast<float>(s.hi[opIn] - s.zp[opIn]);
+    const float cLo = static_cast<float>(s.lo[opC] - s.zp[opC]), cHi = static_cast<float>(s.hi[opC] - s.zp[opC]);
+    const float oLo = static_cast<float>(s.lo[opO] - s.zp[opO]), oHi = static_cast<float>(s.hi[opO] - s.zp[opO]);
+    const int32_t cBase = s.zp[opC] - s.lo[opC], hBase = s.zp[opO] - s.lo[opO], giBase = s.zp[opIn] - s.lo[opIn];
+    const float scaleH = (a.poison && *a.poison) ? __int_as_float(0x7fc00000) : s.scale[opO];
+    const size_t stepC = static_cast<size_t>(a.B) * C, stepH = static_cast<size_t>(a.B) * H;
+    const int rowWords = PLANES * kWords;
+
+    // hidden planes of sub-block `sb` of the exchange half `src` -> plane buffer `buf`
+    auto stage = [&](const uint32_t *src, int sb, int buf) {
+        const int row0 = rowBegin + sb * kSubRows;
+        const int pieces = kSubRows * PLANES * (kWords / 4);
+        for (int i = tid; i < pieces; i += blockDim.x) {
+            const int r = i / (PLANES * (kWords / 4)), rest = i - r * (PLANES * (kWords / 4));
+            const int pl = rest / (kWords / 4), kg = rest - pl * (kWords / 4);
+            const bool valid = row0 + r < rowEnd;
+            const uint32_t *from = src + (valid ? (static_cast<size_t>(row0 + r) * rowWords + pl * kWords + 4 * kg) : 0);
+            copyAsync16(bPlanes + (buf * PLANES + pl) * planeBytes + (r >> 3) * groupStride + kg * kCore + (r & 7) * 16, from, valid);
+        }
+        commitCopies();
+    };
+
+    // one sub-block per step: this thread meets the same four (row, unit) cells every step and keeps them in registers
+    const bool cellInRegisters = subBlocks == 1;
+    float cellReg[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int b = rowBegin + 16 * chunk + 4 * gate + i;
+        cellReg[i] = (cellInRegisters && b < rowEnd) ? a.cell[static_cast<size_t>(b) * H + j] : 0.0f;
+    }
+    uint32_t batch = 0;   // MMA batches issued so far: accumulator / plane buffer = batch & 1
+    auto epilogue = [&](int t, int sb, uint32_t m) {
+        const int buf = m & 1;
+        const int row0 = rowBegin + sb * kSubRows + 16 * chunk;
+        const size_t baseC = t * stepC, baseH = t * stepH;
+        // the input projection's terms do not depend on the product: their loads fly while the MMAs finish
+        const bool chunkHasRows = row0 < rowEnd;   // uniform over the four warps of a chunk
+        float lhsV[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) lhsV[r] = row0 + r < rowEnd ? __ldg(a.lhs + baseC + static_cast<size_t>(row0 + r) * C + c) : 0.0f;
+        if (!*failFlag && !waitPhase(smemAddr(&bars[buf]), (m >> 1) & 1)) *failFlag = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!chunkHasRows) {   // nothing to do for this chunk; the accumulator buffer is not read
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            return;
+        }
+        // ---- phase A: all loads of the 16 rows before any store, so that their latencies overlap
+        uint32_t acc[PLANES][16];
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                : "=r"(acc[pl][0]), "=r"(acc[pl][1]), "=r"(acc[pl][2]), "=r"(acc[pl][3]), "=r"(acc[pl][4]), "=r"(acc[pl][5]),
+                  "=r"(acc[pl][6]), "=r"(acc[pl][7]), "=r"(acc[pl][8]), "=r"(acc[pl][9]), "=r"(acc[pl][10]), "=r"(acc[pl][11]),
+                  "=r"(acc[pl][12]), "=r"(acc[pl][13]), "=r"(acc[pl][14]), "=r"(acc[pl][15])
+                : "r"(tmem + (static_cast<uint32_t>(32 * gate) << 16) + static_cast<uint32_t>(buf * kBufCols + pl * kSubRows + 16 * chunk)));
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        float hhCen[16], gi[16];
+        int32_t entry[16];
+        uint32_t flags = 0;   // bit r: hh clamp, bit 16 + r: gate-input clamp
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            int32_t v[PLANES];
+#pragma unroll
+            for (int pl = 0; pl < PLANES; ++pl) v[pl] = static_cast<int32_t>(acc[pl][r]);
+            uint8_t m8;
+            hhCen[r] = linearCentredF(combine<PLANES>(v, addend), outR, hhLo, hhHi, m8);
+            const float sum = lhsV[r] + rescaleF(hhCen[r], toGate);
+            gi[r] = fminf(fmaxf(sum, giLo), giHi);
+            flags |= (static_cast<uint32_t>(m8) << r) | (static_cast<uint32_t>((sum < giLo) || (sum > giHi)) << (16 + r));
+        }
+#pragma unroll
+        for (int r = 0; r < 16; ++r) entry[r] = __ldg(a.tables + a.tableOffset[gate] + static_cast<int32_t>(gi[r]) + giBase);
+        float *mine = gateS + ((chunk * 4 + gate) * 16) * 32 + lane;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int b = row0 + r;
+            const float outCen = static_cast<float>(entry[r] >> 1);
+            mine[r * 32] = b < rowEnd ? outCen : 0.0f;
+            if (b < rowEnd) {
+                const size_t o = baseC + static_cast<size_t>(b) * C + c;
+                if (a.ck.weight_hh_linear) a.ck.weight_hh_linear[o] = hhCen[r] + s.zpF[opHh];
+                if (a.ck.weight_hh_linear_clamped) a.ck.weight_hh_linear_clamped[o] = static_cast<uint8_t>((flags >> r) & 1u);
+                if (a.ck.gate_inputs) a.ck.gate_inputs[o] = gi[r] + s.zpF[opIn];
+                if (a.ck.gate_inputs_clamped) a.ck.gate_inputs_clamped[o] = static_cast<uint8_t>((flags >> (16 + r)) & 1u);
+                if (a.ck.gate_outputs) a.ck.gate_outputs[o] = outCen + s.zpF[RXMET_LSTM_INPUT_GATE_OUTPUT + gate];
+                if (a.ck.gate_outputs_clamped) a.ck.gate_outputs_clamped[o] = static_cast<uint8_t>(entry[r] & 1);
+            }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + chunk) : "memory");   // the four warps of this row chunk
+        // ---- phase B: the same discipline for this warp's four rows
+        uint32_t *next = a.exchange[(t + 1) & 1];
+        float cOld[4], cNew[4], rounded[4], gO[4];
+        int32_t te[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int b = row0 + 4 * gate + i;
+            cOld[i] = cellInRegisters ? cellReg[i] : (b < rowEnd ? a.cell[static_cast<size_t>(b) * H + j] : 0.0f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float *g4 = gateS + (chunk * 4 * 16 + 4 * gate + i) * 32 + lane;
+            const float gI = g4[0], gF = g4[16 * 32], gG = g4[2 * 16 * 32];
+            gO[i] = g4[3 * 16 * 32];
+            const float pf = __fmul_rn(gF, cOld[i]), pi = __fmul_rn(gI, gG);
+            const float sf = scaleCell(pf, s.forgetRatio, s.forgetMantissa, s.forgetExponent, s.forgetUsesFp);
+            const float si = scaleCell(pi, s.inputRatio, s.inputMantissa, s.inputExponent, s.inputUsesFp);
+            rounded[i] = rintf(__fadd_rn(sf, si));
+            cNew[i] = fminf(fmaxf(rounded[i], cLo), cHi);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) te[i] = __ldg(a.tables + a.tableOffset[4] + static_cast<int32_t>(cNew[i]) + cBase);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int b = row0 + 4 * gate + i;
+            if (b >= rowEnd) continue;
+            const size_t so = baseH + static_cast<size_t>(b) * H + j, cell = static_cast<size_t>(b) * H + j;
+            if (cellInRegisters) cellReg[i] = cNew[i];
+            else a.cell[cell] = cNew[i];
+            const float tanhCen = static_cast<float>(te[i] >> 1);
+            const float raw = __fmul_rn(gO[i], tanhCen);
+            const float hr = rescaleF(raw, s.productToOutput);
+            const float hCen = fminf(fmaxf(hr, oLo), oHi);
+            const uint32_t u = static_cast<uint32_t>(static_cast<int32_t>(hCen) + hBase);
+            uint8_t *rowBytes = reinterpret_cast<uint8_t *>(next + static_cast<size_t>(b) * rowWords);
+            if (PLANES == 2) {
+                rowBytes[j] = static_cast<uint8_t>(u >> 8);
+                rowBytes[kWords * 4 + j] = static_cast<uint8_t>(u & 0xffu);
+            } else {
+                rowBytes[j] = static_cast<uint8_t>(u);
+            }
+            const float hOut = __fmul_rn(hCen, scaleH);
+            a.output[so] = hOut;
+            if (a.ck.cell_states) a.ck.cell_states[so] = cNew[i] + s.zpF[opC];
+            if (a.ck.cell_states_clamped) a.ck.cell_states_clamped[so] = (rounded[i] < cLo) || (rounded[i] > cHi);
+            if (a.ck.cell_tanh_outputs) a.ck.cell_tanh_outputs[so] = tanhCen + s.zpF[RXMET_LSTM_CELL_TANH_OUTPUT];
+            if (a.ck.cell_tanh_outputs_clamped) a.ck.cell_tanh_outputs_clamped[so] = static_cast<uint8_t>(te[i] & 1);
+            if (a.ck.hidden_outputs) a.ck.hidden_outputs[so] = hCen + s.zpF[opO];
+            if (a.ck.hidden_outputs_clamped) a.ck.hidden_outputs_clamped[so] = (hr < oLo) || (hr > oHi);
+            if (t == a.T - 1) {
+                a.finalHidden[cell] = hOut;
+                a.finalCell[cell] = __fmul_rn(cNew[i], s.scale[opC]);
+            }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + chunk) : "memory");   // gateS of this chunk is free again
+    };
+
+    for (int t = 0; t < a.T; ++t) {
+        const uint32_t *current = a.exchange[t & 1];
+        if (subBlocks > 0) stage(current, 0, batch & 1);
+        int pendingSb = -1;
+        uint32_t pendingBatch = 0;
+        for (int sb = 0; sb < subBlocks; ++sb, ++batch) {
+            waitCopies<0>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int buf = batch & 1;
+                const uint32_t aBase = smemAddr(aTile);
+#pragma unroll
+                for (int pl = 0; pl < PLANES; ++pl) {
+                    const uint32_t bBase = smemAddr(bPlanes + (buf * PLANES + pl) * planeBytes);
+                    for (int ks = 0; ks < kPad / 32; ++ks)
+                        planeproj::mmaI8(tmem + buf * kBufCols + pl * kSubRows, operandDescriptor(aBase + ks * 2 * kCore, kCore, groupStride),
+                                         operandDescriptor(bBase + ks * 2 * kCore, kCore, groupStride), kIdesc, ks > 0 ? 1u : 0u);
+                }
+                commitTo(smemAddr(&bars[buf]));
+            }
+            if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch);
+            // the plane buffer of the next batch was read by the MMAs of the batch whose epilogue has just run
+            if (sb + 1 < subBlocks) stage(current, sb + 1, (batch + 1) & 1);
+            pendingSb = sb;
+            pendingBatch = batch;
+        }
+        if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch);
+
+        // ---- publish step t and wait for the other unit tiles of this row group
+        if (t + 1 < a.T) {
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                atomicAdd(a.counters + group, 1u);
+                const unsigned int want = static_cast<unsigned int>(tilesPerGroup) * (t + 1);
+                bool arrived = *failFlag != 0;
+                for (int spin = 0; !arrived && spin < kGroupSpinLimit; ++spin) {
+                    unsigned int seen;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.counters + group) : "memory");
+                    arrived = seen >= want;
+                }
+                if (!arrived) *failFlag = 1;
+            }
+            __syncthreads();
+            __threadfence();
+        }
+    }
+    if (*failFlag) {   // loud: the last outputs of this CTA's units become NaN
+        for (int i = tid; i < (rowEnd - rowBegin) * kUnitTile; i += blockDim.x) {
+            const int b = rowBegin + i / kUnitTile, jj = ut * kUnitTile + i % kUnitTile;
+            a.finalHidden[static_cast<size_t>(b) * H + jj] = __int_as_float(0x7fc00000);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    if (tid == 0 && failed && a.status) atomicExch(a.status, 1);
+}
+
 int gridFor(size_t n, int block) { return static_cast<int>(std::min<size_t>((n + block - 1) / block, 148 * 8)); }
 
 // words per code row: K padded to a multiple of 16 bytes so that rows are read as 16-byte pieces
@@ -447,6 +778,9 @@ struct WideLayout {
     int64_t *addIh, *addHh;
     uint4 *ihTiles;    // weight_ih as canonical tensor-core tiles (plane_proj_umma.cuh)
     int *projStatus;
+    uint4 *hhTiles;    // weight_hh as unit tiles for the tensor-core recurrence
+    uint32_t *exchange;      // second half of the hidden-plane exchange buffer (the first is h0)
+    unsigned int *counters;  // step counters of the row groups, then the status word of the recurrence
 };
 
 // Epilogue of the tensor-core input projection: the exact sum of the planes and the addend rounded once to
@@ -496,6 +830,9 @@ WideLayout layoutWide(W &ws, int T, int B, int I, int H, int planes) {
     l.lhs = ws.template take<float>(rows * C);
     l.ihTiles = ws.template take<uint4>(C * planeproj::paddedK(static_cast<int>(kIh)) / 16);
     l.projStatus = ws.template take<int>(1);
+    l.hhTiles = ws.template take<uint4>(C * planeproj::paddedK(static_cast<int>(kHh)) / 16);
+    l.exchange = ws.template take<uint32_t>(static_cast<size_t>(B) * planes * kHh);
+    l.counters = ws.template take<unsigned int>(256);
     return l;
 }
 
@@ -644,6 +981,47 @@ void forwardQuantWide(const ForwardQuantCall &call, const Exec &e, void *workspa
         else RXMET_WIDE_IH(64);
 #undef RXMET_WIDE_IH
         afterLaunch("lstmInputLinearWide");
+    }
+    // Recurrence: per-step product on the tensor cores for hidden sizes whose weights fit no single SM
+    // (RXMET_LSTM_REC_SIMT turns it off, RXMET_LSTM_REC_UMMA forces it for every eligible shape).
+    {
+        const int kPadHh = planeproj::paddedK(kHh);
+        const int tilesPerGroup = H / kUnitTile;
+        const size_t smemU = 128 * static_cast<size_t>(kPadHh) + 2 * static_cast<size_t>(planes) * kSubRows * kPadHh + sizeof(float) * 4 * 4 * 16 * 32;
+        int cooperative = 0;
+        RXMET_CUDA(cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, currentDevice().device));
+        const bool eligible = H % kUnitTile == 0 && tilesPerGroup <= smsPerPass() && smemU <= static_cast<size_t>(currentDevice().smemMax) &&
+                              cooperative != 0 && std::getenv("RXMET_LSTM_REC_SIMT") == nullptr;
+        if (eligible && (H >= 256 || std::getenv("RXMET_LSTM_REC_UMMA") != nullptr)) {
+            int groups = std::max(1, std::min(smsPerPass() / tilesPerGroup, (B + 15) / 16));
+            const int rowsPerGroup = ((B + groups - 1) / groups + 15) / 16 * 16;
+            groups = (B + rowsPerGroup - 1) / rowsPerGroup;
+            {
+                KernelTimer timer__("lstmPrepChannelsWide", st);
+                packHhTiles<<<gridFor(static_cast<size_t>(C) * kPadHh / 16, 256), 256, 0, st>>>(reinterpret_cast<const uint2 *>(l.wHh), kHh, H, kPadHh,
+                                                                                                l.hhTiles);
+            }
+            afterLaunch("packHhTiles");
+            RXMET_CUDA(cudaMemsetAsync(l.counters, 0, sizeof(unsigned int) * 256, st));
+            UmmaRecurrentArgs u{};
+            u.T = T; u.B = B; u.H = H; u.kWords = kHh; u.groups = groups; u.rowsPerGroup = rowsPerGroup;
+            u.tiles = l.hhTiles; u.addend = l.addHh; u.channel = l.channel; u.tables = tables;
+            for (int t = 0; t < kTables; ++t) u.tableOffset[t] = e.wide.offset[t];
+            u.lhs = l.lhs; u.exchange[0] = l.h0; u.exchange[1] = l.exchange; u.cell = l.c0; u.s = s;
+            u.output = call.output; u.finalHidden = call.finalHidden; u.finalCell = call.finalCell; u.ck = ck;
+            u.counters = l.counters; u.status = reinterpret_cast<int *>(l.counters + 255);
+            u.poison = tensorProjection ? l.projStatus : nullptr;
+            auto launchU = [&](auto kernel) {
+                ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smemU);
+                void *params[] = {&u};
+                KernelTimer timer__("lstmRecurrentWide", st);
+                RXMET_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), dim3(groups * tilesPerGroup), dim3(512), params, smemU, st));
+            };
+            if (planes == 2) launchU(recurrentWideUmma<2>);
+            else launchU(recurrentWideUmma<1>);
+            afterLaunch("lstmRecurrentWideUmma");
+            return;
+        }
     }
     {
         WideRecurrentArgs a{};
