@@ -327,6 +327,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_co
         const size_t baseC = t * stepC, baseH = t * stepH;
         if (active) {
             float rhs[4][RB];
+            // the input projection's terms of this step: loaded first, so that they arrive during the dot products
+            float lhsV[4][RB];
+#pragma unroll
+            for (int r = 0; r < RB; ++r)
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    lhsV[g][r] = b0 + r < a.B ? __ldg(a.lhs + baseC + static_cast<size_t>(b0 + r) * C + g * H + j) : 0.0f;
             // ---- hh linear stage, two gates at a time ----
 #pragma unroll
             for (int pair = 0; pair < 2; ++pair) {
@@ -386,7 +393,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) recurrentWide(const __grid_co
                 for (int g = 0; g < 4; ++g) {
                     const int opIn = RXMET_LSTM_INPUT_GATE_INPUT + g;
                     const float giLo = static_cast<float>(s.lo[opIn] - s.zp[opIn]), giHi = static_cast<float>(s.hi[opIn] - s.zp[opIn]);
-                    const float sum = a.lhs[rowC + g * H] + rhs[g][r];
+                    const float sum = lhsV[g][r] + rhs[g][r];
                     const float cen = fminf(fmaxf(sum, giLo), giHi);
                     const int32_t e = __ldg(a.tables + a.tableOffset[g] + static_cast<int32_t>(cen) + (s.zp[opIn] - s.lo[opIn]));
                     outCen[g] = static_cast<float>(e >> 1);
