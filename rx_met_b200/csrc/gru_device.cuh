@@ -26,12 +26,12 @@ struct PreRescale {
 // shifts left (quantize_ops_helper.h:201-224).
 __device__ __forceinline__ int64_t rshiftRound(int64_t x, int n) {
     if (n <= 0) return x << (-n);
-    // floor quotient + non-negative remainder: round-half-even is symmetric, so this equals the
-    // reference's round-the-magnitude-then-negate formulation for every x
-    const int64_t q = x >> n;
-    const uint64_t r = static_cast<uint64_t>(x) & ((1ull << n) - 1ull);
-    const uint64_t half = 1ull << (n - 1);
-    return q + static_cast<int64_t>((r > half) || (r == half && (q & 1)));
+    // floor quotient q = x >> n and non-negative remainder r: the result is q + (r > half || (r == half && q odd)).
+    // Adding half - 1 + (q & 1) before the shift carries in exactly those cases (a remainder above half always,
+    // one equal to half only into an odd quotient, a smaller one never), which equals the reference's
+    // round-the-magnitude-then-negate formulation for every x (round-half-even is symmetric).  |x| < 2^62.
+    const int64_t roundAdd = (static_cast<int64_t>(1) << (n - 1)) - 1;
+    return (x + roundAdd + ((x >> n) & 1)) >> n;
 }
 
 // The same rounding shift for 1 <= n <= 62 as one add and one shift:

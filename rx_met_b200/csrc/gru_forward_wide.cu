@@ -263,6 +263,15 @@ recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__
         const uint32_t *cur = planeSmem + (t & 1) * bufWords;
         uint8_t *nxt = reinterpret_cast<uint8_t *>(planeSmem + ((t + 1) & 1) * bufWords);
         if (active) {
+            // the input projection's codes of this step: loaded first, so that they arrive during the dot products
+            int32_t ihV[RB][3];
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                const int b = b0 + r;
+                const int16_t *ihRow = a.ih + (static_cast<size_t>(t) * a.B + (b < a.B ? b : 0)) * C;
+#pragma unroll
+                for (int gate = 0; gate < 3; ++gate) ihV[r][gate] = __ldg(ihRow + gate * H + j);
+            }
             int32_t acc[3][RB][2];
 #pragma unroll
             for (int gate = 0; gate < 3; ++gate)
@@ -305,9 +314,8 @@ recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__
                 for (int gate = 0; gate < 3; ++gate)
                     hh[gate] = clampCode(static_cast<int32_t>(applyRescale(combine(acc[gate][r][0], acc[gate][r][1], addend[gate]), rs[gate])) + zpOut,
                                          loOut, hiOut, keepHh[gate]);
-                const int16_t *ihRow = a.ih + row * C;
                 GateMasks m;
-                const GateCodes q = gruCell(ihRow[j], ihRow[H + j], ihRow[2 * H + j], hh[0], hh[1], hh[2], hOld[r], g, m);
+                const GateCodes q = gruCell(ihV[r][0], ihV[r][1], ihV[r][2], hh[0], hh[1], hh[2], hOld[r], g, m);
                 hOld[r] = q.h;
                 const uint32_t u = static_cast<uint32_t>(q.h - loH);
                 uint8_t *rowBytes = nxt + static_cast<size_t>(sg * RB + r) * rowWords * 4;
