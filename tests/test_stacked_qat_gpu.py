@@ -106,3 +106,28 @@ def test_step_trains():
     model.calibrate([x])
     losses = [float(model.step(x, labels, lr=0.5)) for _ in range(12)]
     assert losses[-1] < losses[0]
+
+
+def test_captured_step_replays_the_eager_step():
+    """One CUDA graph for the whole stacked step: after the same number of steps on the same inputs the weights
+    and the loss equal those of the eager engine bit for bit."""
+    from rx_met_b200.stacked_qat import StackedGruQat, a16_config
+    T, B, I, H, layers, classes = 6, 8, 12, 64, 2, 5
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn((T, B, I), generator=gen).to(dev)
+    labels = torch.randint(0, classes, (B,), generator=gen).to(dev)
+    engines = [StackedGruQat(T, B, I, H, layers, classes, dev, a16_config(8, 16), seed=11) for _ in range(2)]
+    for e in engines:
+        e.calibrate([x])
+    eager, captured = engines
+    replay, loss_c = captured.capture_step(x, labels, 1e-2, warmup=2)
+    for _ in range(2):
+        eager.step(x, labels, 1e-2)
+    for _ in range(3):
+        loss_e = eager.step(x, labels, 1e-2)
+        loss_c = replay()
+    torch.cuda.synchronize()
+    assert captured.captured_launches > 50
+    assert torch.equal(eager.flat_w, captured.flat_w)
+    assert torch.equal(loss_e, loss_c)
