@@ -1072,6 +1072,18 @@ def lstm_secondary(lib, torch, device, flush, profile_steps=0, T_override=None):
             per[n] = ms.value / 3
     lib.rxmet_set_kernel_timing(0)
     out["kernel_ms_per_step"] = per
+    # per-kernel HBM roofline of the training step: algorithmic bytes per sequence-step (C = 4H gate channels; the
+    # training forward writes 7 float checkpoints and 14 byte masks, the backward reads them once)
+    C4 = 4 * H
+    algorithmic = {"lstmQuantizeCodes": 5 * I, "lstmInputLinearQ": I + C4 * 4 + C4 * 5,
+                   "lstmRecurrentQ": C4 * 4 + H + (4 * C4 + 3 * H) * 5 - C4 * 5, "lstmPackStepMasks": (4 * C4 + 3 * H) + 4 * H,
+                   "lstmRecurrentBackwardMma": (C4 + 3 * H + H) * 4 + 4 * H + 2 * C4 * 4,
+                   "lstmRecurrentBackward": (C4 + 3 * H + H) * 4 + 4 * H + 2 * C4 * 4,
+                   "inputGradUmma": C4 * 4 + I * 5, "weightGradUmma": 2 * C4 * 4 + (I + H) * 4}
+    peak, peak_kind = _peaks()
+    out["kernel_roofline"] = {n: {"bytes_per_st": algorithmic[n], "GB/s": algorithmic[n] * st / (ms * 1e-3) / 1e9,
+                                  "frac": algorithmic[n] * st / (ms * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}"}
+                              for n, ms in per.items() if n in algorithmic}
     # the reference's CPU quantized forward (its only CPU path) on all host cores, bounded sample
     prefix = "ref" if ll.have_ref() else "orc"
     q = ll.quantize_masters("orc", p, box)
