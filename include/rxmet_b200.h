@@ -430,6 +430,38 @@ RXMET_API int rxmet_gru_backward_quant(int T, int B, int I, int H,
                                        void *workspace_dev, size_t workspace_bytes,
                                        void *stream);
 
+/* The training forward / QAT backward pair with the per-step clamp flags in a compact form: instead of the
+ * five byte masks weight_ih_linear, weight_hh_linear, gate_input, gate_output and h ([T,B,3H] x 4 + [T,B,H] =
+ * 13 bytes per element and step) the forward writes ONE 16-bit word per (t, b, j) into step_flags_dev
+ * ([T,B,H] uint16): bit 0..2 = gate_output z, r, n; 3..5 = gate_input; 6..8 = weight_hh_linear; 9..11 =
+ * weight_ih_linear; 12 = h (1 = kept), and the backward reads that word.  `masks` still carries the six
+ * parameter / input masks (x, h0, W, R, bw, br) and weight_ih_linear, which the input projection fills and the
+ * recurrence folds into the word; its other four per-step members may be NULL and are not written then.
+ * Results are identical to the byte-mask pair.  For training engines that own their save-for-backward
+ * buffers (rx_met_b200.qat.GruQatStep); the reference's binding hands byte masks to Python and has no
+ * counterpart.  Supported where rxmet_gru_packed_flags_supported returns 1 (8-bit grids, H <= 128);
+ * RXMET_ERR_UNSUPPORTED otherwise. */
+RXMET_API int rxmet_gru_packed_flags_supported(const rxmet_gru_quant_params *params, int B, int I, int H);
+RXMET_API int rxmet_gru_forward_quant_packed(int T, int B, int I, int H,
+                                             const float *W_dev, const float *R_dev,
+                                             const float *bw_dev, const float *br_dev,
+                                             const float *x_dev, const float *h0_dev,
+                                             const rxmet_gru_quant_params *params,
+                                             float *h_dev, float *v_dev,
+                                             int32_t *W_q_dev, int32_t *R_q_dev,
+                                             int32_t *bw_q_dev, int32_t *br_q_dev, int32_t *x_q_dev,
+                                             const rxmet_gru_masks *masks, uint16_t *step_flags_dev,
+                                             void *workspace_dev, size_t workspace_bytes, void *stream);
+RXMET_API int rxmet_gru_backward_quant_packed(int T, int B, int I, int H,
+                                              const int32_t *W_q_dev, const int32_t *R_q_dev,
+                                              const int32_t *x_q_dev,
+                                              const float *dh_new_dev, const float *h_dev, const float *v_dev,
+                                              const rxmet_gru_quant_params *params,
+                                              const rxmet_gru_masks *masks, const uint16_t *step_flags_dev,
+                                              float *dx_dev, float *dW_dev, float *dR_dev,
+                                              float *dbw_dev, float *dbr_dev, float *dh0_dev,
+                                              void *workspace_dev, size_t workspace_bytes, void *stream);
+
 /* Float backward.  Replaces backward_fp -> gru::BackwardPass<float>::Run
  * (gru_interface_binding.cc:975-1046, operators/quant-gru/src/
  * gru_backward_gpu.cu). */

@@ -422,6 +422,56 @@ int rxmet_gru_backward_quant(int T, int B, int I, int H, const int32_t *W_q_dev,
     });
 }
 
+int rxmet_gru_packed_flags_supported(const rxmet_gru_quant_params *params, int B, int I, int H) {
+    int supported = 0;
+    const int rc = guarded([&] {
+        RXMET_PTR(params);
+        RXMET_REQUIRE(params->hidden == H, "quant params were made for hidden=%d, call has H=%d", params->hidden, H);
+        supported = gru::packedFlagsSupported(*gru::deriveExec(*params), B, I, H) ? 1 : 0;
+    });
+    return rc == RXMET_OK ? supported : 0;
+}
+
+int rxmet_gru_forward_quant_packed(int T, int B, int I, int H, const float *W_dev, const float *R_dev, const float *bw_dev,
+                                   const float *br_dev, const float *x_dev, const float *h0_dev,
+                                   const rxmet_gru_quant_params *params, float *h_dev, float *v_dev, int32_t *W_q_dev,
+                                   int32_t *R_q_dev, int32_t *bw_q_dev, int32_t *br_q_dev, int32_t *x_q_dev,
+                                   const rxmet_gru_masks *masks, uint16_t *step_flags_dev, void *workspace_dev,
+                                   size_t workspace_bytes, void *stream) {
+    return guarded([&] {
+        RXMET_PTR(x_dev); RXMET_PTR(h_dev); RXMET_PTR(v_dev); RXMET_PTR(masks); RXMET_PTR(step_flags_dev);
+        gru::ForwardQuantCall call;
+        call.isTraining = 1;
+        call.T = T; call.B = B; call.I = I; call.H = H;
+        call.W = W_dev; call.R = R_dev; call.bw = bw_dev; call.br = br_dev; call.x = x_dev; call.h0 = h0_dev;
+        call.h = h_dev; call.v = v_dev;
+        call.W_q = W_q_dev; call.R_q = R_q_dev; call.bw_q = bw_q_dev; call.br_q = br_q_dev; call.x_q = x_q_dev;
+        call.masks = masks;
+        call.stepFlags = step_flags_dev;
+        runQuant(call, params, workspace_dev, workspace_bytes, stream);
+    });
+}
+
+int rxmet_gru_backward_quant_packed(int T, int B, int I, int H, const int32_t *W_q_dev, const int32_t *R_q_dev,
+                                    const int32_t *x_q_dev, const float *dh_new_dev, const float *h_dev, const float *v_dev,
+                                    const rxmet_gru_quant_params *params, const rxmet_gru_masks *masks,
+                                    const uint16_t *step_flags_dev, float *dx_dev, float *dW_dev, float *dR_dev,
+                                    float *dbw_dev, float *dbr_dev, float *dh0_dev, void *workspace_dev,
+                                    size_t workspace_bytes, void *stream) {
+    return guarded([&] {
+        RXMET_PTR(params); RXMET_PTR(W_q_dev); RXMET_PTR(R_q_dev); RXMET_PTR(x_q_dev); RXMET_PTR(step_flags_dev);
+        RXMET_REQUIRE(params->hidden == H, "quant params were made for hidden=%d, call has H=%d", params->hidden, H);
+        const auto exec = gru::deriveExec(*params);
+        gru::BackwardCall call;
+        call.T = T; call.B = B; call.I = I; call.H = H;
+        call.W_q = W_q_dev; call.R_q = R_q_dev; call.x_q = x_q_dev; call.exec = exec.get();
+        call.dh_new = dh_new_dev; call.h = h_dev; call.v = v_dev; call.masks = masks;
+        call.stepFlags = step_flags_dev;
+        call.dx = dx_dev; call.dW = dW_dev; call.dR = dR_dev; call.dbw = dbw_dev; call.dbr = dbr_dev; call.dh0 = dh0_dev;
+        runBackward(call, workspace_dev, workspace_bytes, stream);
+    });
+}
+
 int rxmet_gru_backward_fp(int T, int B, int I, int H, const float *W_dev, const float *R_dev, const float *bw_dev,
                           const float *br_dev, const float *x_dev, const float *dh_new_dev, const float *h_dev,
                           const float *v_dev, float *dx_dev, float *dW_dev, float *dR_dev, float *dbw_dev,

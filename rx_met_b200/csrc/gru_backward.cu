@@ -1248,6 +1248,8 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     // Which kernels take the saved integer codes directly (QAT on 8-bit grids).
     const bool qat = call.W_q != nullptr;
     if (qat) RXMET_REQUIRE(call.exec != nullptr, "backward: quantized operands need execution parameters");
+    if (call.stepFlags && !(qat && call.exec->weightClass == CodeClass::I8 && H <= 128 && std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr))
+        fail(RXMET_ERR_UNSUPPORTED, "packed step flags are read by the 8-bit register path of the backward only");
     const bool simtGrads = std::getenv("RXMET_GRU_GRAD_SIMT") != nullptr;
     const bool registerPath = qat && call.exec->weightClass == CodeClass::I8 && H <= 128 &&
                               std::getenv("RXMET_GRU_BWD_GENERIC") == nullptr;
@@ -1393,7 +1395,9 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             afterLaunch("packRecurrentBf16");
         }
         BackwardQArgs q{};
-        if (mk.weight_ih_linear || mk.weight_hh_linear || mk.gate_input || mk.gate_output || mk.h) {
+        if (call.stepFlags) {
+            q.stepBits = call.stepFlags;   // packed by the forward itself
+        } else if (mk.weight_ih_linear || mk.weight_hh_linear || mk.gate_input || mk.gate_output || mk.h) {
             uint16_t *bits = ws.take<uint16_t>(rows * H);
             {
                 KernelTimer timer__("packStepMasks", st);

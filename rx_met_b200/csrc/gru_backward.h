@@ -21,6 +21,7 @@ struct BackwardCall {
     const Exec *exec = nullptr;
     const float *dh_new = nullptr, *h = nullptr, *v = nullptr;
     const rxmet_gru_masks *masks = nullptr;
+    const uint16_t *stepFlags = nullptr;    // optional [T,B,H]: packed per-step keep flags as the forward wrote them
     float *dx = nullptr, *dW = nullptr, *dR = nullptr, *dbw = nullptr, *dbr = nullptr, *dh0 = nullptr;
 };
 

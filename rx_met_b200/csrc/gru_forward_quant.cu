@@ -467,6 +467,10 @@ struct RecurrentArgs {
     int32_t *vq;          // optional [T][B][4H]
     uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;
     const int *poison;    // optional device word: non-zero = the ih codes are not valid, write NaN
+    // packed keep flags (recurrentForwardI8 only): bit 0..2 gate output z, r, n; 3..5 gate input; 6..8 hh linear;
+    // 9..11 ih linear (read from maskIh, the input projection's flags); 12 hidden state
+    uint16_t *stepBits;
+    const uint8_t *maskIh;
 };
 
 template <class WT, class AT, class LT, int BT>
@@ -600,7 +604,7 @@ recurrentForward(const __grid_constant__ RecurrentArgs a, const __grid_constant_
 // serial chain.  Requires 3H <= blockDim and H <= 4*KW.
 // Mode 0: 64-bit gate arithmetic; 1: 32-bit where provably exact; 2: additionally direct
 // activation tables in shared memory and ih contributions pre-rescaled by the input projection.
-template <int KW, int BT, int Mode>
+template <int KW, int BT, int Mode, bool Packed = false>
 __global__ void __launch_bounds__(KW * 12)
 recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec gateParam) {
     const int H = a.H, C = 3 * a.H;
@@ -689,6 +693,8 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
     constexpr int kSlots = 2;
     const int elems = nb * H;
     int16_t ihCur[kSlots][3], ihNext[kSlots][3];
+    constexpr bool packed = Packed;   // the keep flags leave as one 16-bit word per element; no byte masks are written
+    uint8_t ihKeepCur[kSlots][3] = {}, ihKeepNext[kSlots][3] = {};   // combined only where they are used: no wait at the loads
 
     // hh epilogue of this thread's channel: with |acc + bias - comp| < 2^31, a multiplier that
     // shrinks and a shift in [1, 31] the rounding rescale is one widening multiply-add and a
@@ -726,11 +732,24 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
             }
         }
     };
+    auto fetchKeep = [&](size_t stepBase, uint8_t (&dst)[kSlots][3]) {
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2) {
+            if (tid + s2 * nthreads < elems) {
+                const uint8_t *row = a.maskIh + stepBase + offC[s2];
+                dst[s2][0] = row[0]; dst[s2][1] = row[H]; dst[s2][2] = row[2 * H];
+            }
+        }
+    };
     fetch(0, ihCur);
+    if (packed) fetchKeep(0, ihKeepCur);
 
     const int4 *hS4 = reinterpret_cast<const int4 *>(hS);
     for (int t = 0; t < a.T; ++t, baseH += stepH, baseC += stepC, baseV += stepV) {
-        if (t + 1 < a.T) fetch(baseC + stepC, ihNext);
+        if (t + 1 < a.T) {
+            fetch(baseC + stepC, ihNext);
+            if (packed) fetchKeep(baseC + stepC, ihKeepNext);
+        }
 
         if (hasColumn) {
             int32_t acc[BT];
@@ -758,8 +777,8 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
                     const int64_t prod = (static_cast<int64_t>(acc[b]) - cmp + bias) * static_cast<int64_t>(rs.mult);
                     code = clampCode(rshiftRoundCalled(prod, rs.shift) + zpOut, loOut, hiOut, keep);
                 }
-                hhS[b * C + tid] = code;
-                if (a.maskHh && b < nb) a.maskHh[baseC + static_cast<size_t>(b0 + b) * C + tid] = keep;
+                hhS[b * C + tid] = packed ? code * 2 + keep : code;   // the flag rides with the code to the cell thread
+                if (!packed && a.maskHh && b < nb) a.maskHh[baseC + static_cast<size_t>(b0 + b) * C + tid] = keep;
             }
         }
         __syncthreads();
@@ -772,12 +791,21 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
                 const int32_t *hhRow = hhS + b * C;
                 GateMasks m;
                 const int32_t hOld = hS[b * kPadded + j];
-                const int32_t hhn = hhRow[2 * H + j];
+                int32_t hhz = hhRow[j], hhr = hhRow[H + j], hhn = hhRow[2 * H + j];
+                uint32_t hhKeep = 0;
+                if (packed) {
+                    hhKeep = static_cast<uint32_t>(hhz & 1) | (static_cast<uint32_t>(hhr & 1) << 1) | (static_cast<uint32_t>(hhn & 1) << 2);
+                    hhz >>= 1; hhr >>= 1; hhn >>= 1;
+                }
                 GateCodes q;
                 if constexpr (Mode == 2)
-                    q = gruCellPrepared(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, fast, tab, m);
+                    q = gruCellPrepared(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhz, hhr, hhn, hOld, fast, tab, m);
                 else
-                    q = gruCell<Mode == 1>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhRow[j], hhRow[H + j], hhn, hOld, g, m);
+                    q = gruCell<Mode == 1>(ihCur[s2][0], ihCur[s2][1], ihCur[s2][2], hhz, hhr, hhn, hOld, g, m);
+                if (packed)
+                    a.stepBits[baseH + offH[s2]] = static_cast<uint16_t>(
+                        m.out[0] | (m.out[1] << 1) | (m.out[2] << 2) | (m.in[0] << 3) | (m.in[1] << 4) | (m.in[2] << 5) | (hhKeep << 6) |
+                        (ihKeepCur[s2][0] << 9) | (ihKeepCur[s2][1] << 10) | (ihKeepCur[s2][2] << 11) | (static_cast<uint32_t>(m.h) << 12));
                 hS[b * kPadded + j] = static_cast<int8_t>(q.h);
                 const size_t ho = baseH + stepH + offH[s2];  // row t + 1 of h
                 a.h[ho] = static_cast<float>(q.h - zpH) * scaleH;
@@ -791,7 +819,7 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
                     int32_t *vq = a.vq + baseV + offV[s2];
                     vq[0] = q.z; vq[H] = q.r; vq[2 * H] = q.n; vq[3 * H] = hhn;
                 }
-                if (a.maskGateIn) {
+                if (!packed && a.maskGateIn) {
                     uint8_t *mi = a.maskGateIn + baseC + offC[s2], *mo = a.maskGateOut + baseC + offC[s2];
                     mi[0] = m.in[0]; mi[H] = m.in[1]; mi[2 * H] = m.in[2];
                     mo[0] = m.out[0]; mo[H] = m.out[1]; mo[2 * H] = m.out[2];
@@ -803,6 +831,10 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
         for (int s2 = 0; s2 < kSlots; ++s2)
 #pragma unroll
             for (int q3 = 0; q3 < 3; ++q3) ihCur[s2][q3] = ihNext[s2][q3];
+#pragma unroll
+        for (int s2 = 0; s2 < kSlots; ++s2)
+#pragma unroll
+            for (int q3 = 0; q3 < 3; ++q3) ihKeepCur[s2][q3] = ihKeepNext[s2][q3];
         __syncthreads();
     }
 }
@@ -1113,6 +1145,12 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
     a.h = call.h; a.v = call.v; a.hq = call.h_q; a.vq = call.v_q;
     a.maskHh = mk.weight_hh_linear; a.maskGateIn = mk.gate_input; a.maskGateOut = mk.gate_output; a.maskH = mk.h;
     a.poison = tensorProjection ? projStatus : nullptr;
+    a.stepBits = call.stepFlags; a.maskIh = mk.weight_ih_linear;
+    if (call.stepFlags) {
+        RXMET_REQUIRE(training && mk.weight_ih_linear, "packed step flags need a training forward with the weight_ih_linear mask");
+        if (!registerPath || mode != 2)
+            fail(RXMET_ERR_UNSUPPORTED, "packed step flags are written by the 8-bit register path with direct activation tables only");
+    }
     if (mk.gate_input || mk.gate_output || mk.h)
         RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
 
@@ -1146,7 +1184,8 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                 bool done = false;
 #define RXMET_I8_CASE(KW, BT)                                                 \
     if (!done && hWords <= KW && btI8 == BT) {                                 \
-        if (mode == 2) launchI8(recurrentForwardI8<KW, BT, 2>);                \
+        if (mode == 2 && a.stepBits) launchI8(recurrentForwardI8<KW, BT, 2, true>); \
+        else if (mode == 2) launchI8(recurrentForwardI8<KW, BT, 2>);           \
         else if (mode == 1) launchI8(recurrentForwardI8<KW, BT, 1>);           \
         else launchI8(recurrentForwardI8<KW, BT, 0>);                          \
         done = true;                                                           \
@@ -1191,8 +1230,21 @@ size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
     return ws.used() + 4096 + forwardWideExtraBytes(T, B, I, H);
 }
 
+bool packedFlagsSupported(const Exec &e, int B, int I, int H) {
+    (void)I;
+    if (e.weightClass != CodeClass::I8 || e.actClass != CodeClass::I8 || e.linearClass == CodeClass::I32) return false;
+    if (std::getenv("RXMET_GRU_FWD_GENERIC") != nullptr || std::getenv("RXMET_GRU_FWD_BT") != nullptr) return false;
+    const int sms = currentDevice().sms, C = 3 * H;
+    const int block = (C + 31) / 32 * 32, hWords = (H + 3) / 4;
+    const int bt = (B > 2 * sms) ? 4 : ((B > sms) ? 2 : 1);
+    return block <= 768 && hWords <= 64 && bt * H <= 2 * block && H <= 128 &&   // H <= 128: the backward's register path
+           fastGateMath(e.gate) && std::getenv("RXMET_GRU_FWD_MODE") == nullptr;
+}
+
 void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, size_t workspaceBytes,
                   cudaStream_t st) {
+    if (call.stepFlags && !packedFlagsSupported(e, call.B, call.I, call.H))
+        fail(RXMET_ERR_UNSUPPORTED, "packed step flags: these grids or sizes do not take the 8-bit register path");
     Workspace ws(workspace, workspaceBytes);
     const CodeClass w = e.weightClass, a = e.actClass, l = e.linearClass;
     if (l == CodeClass::I32 || w == CodeClass::I32 || a == CodeClass::I32) {

@@ -26,7 +26,11 @@ struct ForwardQuantCall {
     int32_t *W_q = nullptr, *R_q = nullptr, *bw_q = nullptr, *br_q = nullptr, *x_q = nullptr;
     int32_t *h_q = nullptr, *v_q = nullptr;
     const rxmet_gru_masks *masks = nullptr;
+    uint16_t *stepFlags = nullptr;          // optional [T,B,H]: the 13 per-step keep flags of an element packed into 16 bits
 };
+
+// Whether forwardQuant can write stepFlags for these parameters and sizes (the register-resident 8-bit path).
+bool packedFlagsSupported(const Exec &exec, int B, int I, int H);
 
 // Page-locked host copy of the per-channel block of `exec`, 12 arrays of 3H 32-bit words: effective
 // scales of W, R, bw, br (floats), then the Rescale pairs gemm_x, bias_x, gemm_h, bias_h.  Built on

@@ -10,6 +10,7 @@ are the calibration min/max all-reduce and the gradient all-reduce.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -72,6 +73,13 @@ class GruQatStep:
         self.mask_struct = cabi.Masks()
         for k_, t in self.masks.items():
             setattr(self.mask_struct, k_, t.data_ptr())
+        # compact save-for-backward of the clamp flags: one 16-bit word per element and step instead of 13 mask bytes,
+        # written by the forward itself (used when the library supports it for the parameters in force)
+        self.step_flags = torch.empty((T, B, H), dtype=torch.int16, device=self.device)
+        self.packed_mask_struct = cabi.Masks()
+        for k_ in ("x", "W", "R", "bw", "br", "weight_ih_linear"):
+            setattr(self.packed_mask_struct, k_, self.masks[k_].data_ptr())
+        self._packed = False
         self.dh_new = torch.zeros((T + 1, B, H), **f32)
         self.dx = torch.empty((T, B, I), **f32)
         self.dh0 = torch.empty((B, H), **f32)
@@ -134,6 +142,8 @@ class GruQatStep:
     def set_params(self, params: GRUQuantParams) -> None:
         self.params = params
         self._c_params, self._keep = params._to_c()
+        self._packed = (os.environ.get("RXMET_QAT_BYTE_MASKS") is None and
+                        bool(self.lib.rxmet_gru_packed_flags_supported(C.byref(self._c_params), self.B, self.I, self.H)))
 
     # ---- one training step -------------------------------------------------
     def _stream(self):
@@ -142,6 +152,13 @@ class GruQatStep:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Quantized training forward; returns the output sequence h[1:] (a view)."""
         with torch.cuda.device(self.device):
+            if self._packed:
+                cabi.check(self.lib.rxmet_gru_forward_quant_packed(
+                    self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
+                    C.byref(self._c_params), _p(self.h), _p(self.v), _p(self.W_q), _p(self.R_q), _p(self.bw_q),
+                    _p(self.br_q), _p(self.x_q), C.byref(self.packed_mask_struct), _p(self.step_flags), _p(self.ws),
+                    C.c_size_t(self.ws.numel()), self._stream()), "forward_quant_packed")
+                return self.h[1:]
             cabi.check(self.lib.rxmet_gru_forward_quant(
                 1, self.T, self.B, self.I, self.H, _p(self.W), _p(self.R), _p(self.bw), _p(self.br), _p(x), None,
                 C.byref(self._c_params), _p(self.h), _p(self.v), _p(self.W_q), _p(self.R_q), _p(self.bw_q),
@@ -152,6 +169,13 @@ class GruQatStep:
     def backward(self) -> None:
         """BPTT from self.dh_new ([T+1,B,H], row 0 unused) into the flat gradient buffer."""
         with torch.cuda.device(self.device):
+            if self._packed:
+                cabi.check(self.lib.rxmet_gru_backward_quant_packed(
+                    self.T, self.B, self.I, self.H, _p(self.W_q), _p(self.R_q), _p(self.x_q), _p(self.dh_new), _p(self.h),
+                    _p(self.v), C.byref(self._c_params), C.byref(self.packed_mask_struct), _p(self.step_flags),
+                    _p(self.dx), _p(self.dW), _p(self.dR), _p(self.dbw), _p(self.dbr), _p(self.dh0), _p(self.ws),
+                    C.c_size_t(self.ws.numel()), self._stream()), "backward_quant_packed")
+                return
             cabi.check(self.lib.rxmet_gru_backward_quant(
                 self.T, self.B, self.I, self.H, _p(self.W_q), _p(self.R_q), _p(self.bw_q), _p(self.br_q), _p(self.x_q),
                 _p(self.dh_new), _p(self.h), _p(self.v), C.byref(self._c_params), C.byref(self.mask_struct),

@@ -453,6 +453,46 @@ def test_captured_step_replays_the_eager_step():
     assert torch.equal(w_eager, w_graph)
 
 
+@pytest.mark.parametrize("shape", [(7, 5, 12, 32), (6, 9, 40, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_packed_step_flags_equal_the_byte_masks(monkeypatch, shape):
+    """The compact save-for-backward of the training engine: the 16-bit word the forward writes per element and
+    step holds exactly the 13 byte flags of the reference-shaped masks, and a training step through the packed
+    pair leaves the same weights, bit for bit, as the step through the byte masks."""
+    import torch
+    from rx_met_b200 import gru_interface_binding as ops
+    from rx_met_b200.qat import GruQatStep
+    T, B, I, H = shape
+    dev = torch.device("cuda", 0)
+    cfg = ops.OperatorQuantConfig()
+    for name in cabi.OP_NAMES:
+        if name not in ("W", "R", "bw", "br"):
+            setattr(cfg, f"{name}_symmetric_", False)
+    gen = torch.Generator().manual_seed(17)
+    x = torch.randn((T, B, I), generator=gen).to(dev)
+    y = torch.randn((T, B, H), generator=gen).to(dev)
+    packed = GruQatStep(T, B, I, H, dev, cfg, seed=5)
+    packed.calibrate([x * 0.6])            # narrower calibration input: the step clamps
+    assert packed._packed
+    monkeypatch.setenv("RXMET_QAT_BYTE_MASKS", "1")
+    plain = GruQatStep(T, B, I, H, dev, cfg, seed=5)
+    plain.calibrate([x * 0.6])
+    assert not plain._packed
+    packed.forward(x)
+    plain.forward(x)
+    m = plain.masks
+    C3 = 3 * H
+    word = torch.zeros((T, B, H), dtype=torch.int32, device=dev)
+    for bit, name in ((0, "gate_output"), (3, "gate_input"), (6, "weight_hh_linear"), (9, "weight_ih_linear")):
+        for g in range(3):
+            word |= m[name][..., g * H:(g + 1) * H].to(torch.int32) << (bit + g)
+    word |= m["h"].to(torch.int32) << 12
+    assert torch.equal(packed.step_flags.to(torch.int32) & 0xffff, word)
+    assert (word != 0x1fff).any(), "the case should clamp somewhere"
+    for _ in range(3):
+        lp, lb = packed.step(x, y, 1e-2), plain.step(x, y, 1e-2)
+    assert torch.equal(packed.flat_w, plain.flat_w) and torch.equal(lp, lb)
+
+
 def test_fused_mse_loss_and_gradient():
     """The step's loss kernel: gradient bit-identical to the eager float32 expressions, loss within 1e-6 relative."""
     import torch
