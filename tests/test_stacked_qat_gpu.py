@@ -29,6 +29,9 @@ def _close(got, want, tol, name):
     assert err <= tol, f"{name}: max error {err:.3e} of the largest magnitude"
 
 
+_FLAG_BITS = {"gate_output": 0, "gate_input": 3, "weight_hh_linear": 6, "h": 12}   # weight_ih_linear stays a byte mask
+
+
 @pytest.mark.parametrize("T,B,I,H,layers,bits", [(5, 6, 10, 32, 2, 16), (4, 5, 40, 256, 3, 16), (6, 4, 12, 64, 2, 8)])
 def test_stacked_step_matches_the_checker(T, B, I, H, layers, bits):
     from rx_met_b200.stacked_qat import StackedGruQat, a16_config
@@ -54,7 +57,13 @@ def test_stacked_step_matches_the_checker(T, B, I, H, layers, bits):
             np.testing.assert_array_equal(_np(d.x_q), want["x_q"], err_msg=f"layer {li} x codes")
             np.testing.assert_array_equal(_np(d.h), want["h"], err_msg=f"layer {li} h")
             np.testing.assert_array_equal(_np(d.v), want["v"], err_msg=f"layer {li} v")
+            flags = _np(d.step_flags).astype(np.int32) & 0xffff if d._packed else None
             for k, m in want["masks"].arr.items():
+                if flags is not None and k in _FLAG_BITS:   # the engine kept these as one 16-bit word per element and step
+                    first = _FLAG_BITS[k]
+                    got = (flags >> first) & 1 if k == "h" else np.concatenate([(flags >> (first + g)) & 1 for g in range(3)], -1)
+                    np.testing.assert_array_equal(got.astype(np.uint8), m, err_msg=f"layer {li} packed flags {k}")
+                    continue
                 np.testing.assert_array_equal(_np(d.masks[k]), m, err_msg=f"layer {li} mask {k}")
             saved.append((d, want, flip))
             outs.append(want["h"][1:][::-1] if flip else want["h"][1:])
