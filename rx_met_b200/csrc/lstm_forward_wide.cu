@@ -594,7 +594,9 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
         cellReg[i] = (cellInRegisters && b < rowEnd) ? a.cell[static_cast<size_t>(b) * H + j] : 0.0f;
     }
     uint32_t batch = 0;   // MMA batches issued so far: accumulator / plane buffer = batch & 1
-    auto epilogue = [&](int t, int sb, uint32_t m) {
+    // nextSb >= 0: once the batch's MMAs are known to be complete, the planes of sub-block nextSb are staged into
+    // the buffer those MMAs read (they then fly during this epilogue)
+    auto epilogue = [&](int t, int sb, uint32_t m, const uint32_t *current, int nextSb) {
         const int buf = m & 1;
         const int row0 = rowBegin + sb * kSubRows + 16 * chunk;
         const size_t baseC = t * stepC, baseH = t * stepH;
@@ -605,6 +607,7 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
         for (int r = 0; r < 16; ++r) lhsV[r] = row0 + r < rowEnd ? __ldg(a.lhs + baseC + static_cast<size_t>(row0 + r) * C + c) : 0.0f;
         if (!*failFlag && !waitPhase(smemAddr(&bars[buf]), (m >> 1) & 1)) *failFlag = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (nextSb >= 0) stage(current, nextSb, buf);
         if (!chunkHasRows) {   // nothing to do for this chunk; the accumulator buffer is not read
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             return;
@@ -713,6 +716,14 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
         asm volatile("bar.sync %0, 128;" ::"r"(1 + chunk) : "memory");   // gateS of this chunk is free again
     };
 
+    // operand descriptors of the resident weight tile and of the two plane buffers, without the k-step offset
+    const uint64_t descA0 = operandDescriptor(smemAddr(aTile), kCore, groupStride);
+    uint64_t descB0[2][PLANES];
+#pragma unroll
+    for (int bufI = 0; bufI < 2; ++bufI)
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) descB0[bufI][pl] = operandDescriptor(smemAddr(bPlanes + (bufI * PLANES + pl) * planeBytes), kCore, groupStride);
+
     for (int t = 0; t < a.T; ++t) {
         const uint32_t *current = a.exchange[t & 1];
         if (subBlocks > 0) stage(current, 0, batch & 1);
@@ -725,23 +736,22 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
             if (tid == 0) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int buf = batch & 1;
-                const uint32_t aBase = smemAddr(aTile);
+                const uint64_t kStep = static_cast<uint64_t>((2 * kCore) >> 4);   // start-address field advances by two k-groups
 #pragma unroll
-                for (int pl = 0; pl < PLANES; ++pl) {
-                    const uint32_t bBase = smemAddr(bPlanes + (buf * PLANES + pl) * planeBytes);
+                for (int pl = 0; pl < PLANES; ++pl)
                     for (int ks = 0; ks < kPad / 32; ++ks)
-                        planeproj::mmaI8(tmem + buf * kBufCols + pl * kSubRows, operandDescriptor(aBase + ks * 2 * kCore, kCore, groupStride),
-                                         operandDescriptor(bBase + ks * 2 * kCore, kCore, groupStride), kIdesc, ks > 0 ? 1u : 0u);
-                }
+                        planeproj::mmaI8(tmem + buf * kBufCols + pl * kSubRows, descA0 + ks * kStep, descB0[buf][pl] + ks * kStep, kIdesc,
+                                         ks > 0 ? 1u : 0u);
                 commitTo(smemAddr(&bars[buf]));
             }
-            if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch);
-            // the plane buffer of the next batch was read by the MMAs of the batch whose epilogue has just run
-            if (sb + 1 < subBlocks) stage(current, sb + 1, (batch + 1) & 1);
+            // The plane buffer of the next batch was read by the MMAs of the previous one: once those are known to be
+            // complete the next sub-block's copies start, and they fly during the previous sub-block's epilogue.
+            if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch, current, sb + 1 < subBlocks ? sb + 1 : -1);
+            else if (sb + 1 < subBlocks) stage(current, sb + 1, (batch + 1) & 1);
             pendingSb = sb;
             pendingBatch = batch;
         }
-        if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch);
+        if (pendingSb >= 0) epilogue(t, pendingSb, pendingBatch, current, -1);
 
         // ---- publish step t and wait for the other unit tiles of this row group
         if (t + 1 < a.T) {
