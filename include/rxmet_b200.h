@@ -430,6 +430,28 @@ RXMET_API int rxmet_gru_backward_quant(int T, int B, int I, int H,
                                        void *workspace_dev, size_t workspace_bytes,
                                        void *stream);
 
+/* The same forward on the reference's FP32 carrier: codes held in floats, every rescale = rint(x * ratio)
+ * with ratio = source scale / destination scale in float, the 16-segment tables evaluated in float.
+ * Replaces forward_quant_float_storage -> quantGRUForwardFP -> ForwardPassQuantFP::Run as the reference's
+ * CUDA build runs it (gru_interface_binding.cc:599-719, operators/quant-gru/src/gru_interface.cc:636-716,
+ * src/gru_forward_gpu_quant_fp.cu).  Arguments and outputs as rxmet_gru_forward_quant (the code outputs
+ * stay int32; the reference stores the same integers in float tensors).  The matrix products are formed
+ * exactly on the integer codes, which equals the reference's float GEMM while the sums stay below 2^24
+ * (every 8-bit configuration with input and hidden sizes up to 512); beyond that the reference's own result
+ * depends on its GEMM's summation order and this entry returns the exactly summed one. */
+RXMET_API int rxmet_gru_forward_quant_fp_carrier(int is_training, int T, int B, int I, int H,
+                                                 const float *W_dev, const float *R_dev,
+                                                 const float *bw_dev, const float *br_dev,
+                                                 const float *x_dev, const float *h0_dev,
+                                                 const rxmet_gru_quant_params *params,
+                                                 float *h_dev, float *v_dev,
+                                                 int32_t *W_q_dev, int32_t *R_q_dev,
+                                                 int32_t *bw_q_dev, int32_t *br_q_dev,
+                                                 int32_t *x_q_dev, int32_t *h_q_dev, int32_t *v_q_dev,
+                                                 const rxmet_gru_masks *masks,
+                                                 void *workspace_dev, size_t workspace_bytes,
+                                                 void *stream);
+
 /* The training forward / QAT backward pair with the per-step clamp flags in a compact form: instead of the
  * five byte masks weight_ih_linear, weight_hh_linear, gate_input, gate_output and h ([T,B,3H] x 4 + [T,B,H] =
  * 13 bytes per element and step) the forward writes ONE 16-bit word per (t, b, j) into step_flags_dev

@@ -422,6 +422,27 @@ int rxmet_gru_backward_quant(int T, int B, int I, int H, const int32_t *W_q_dev,
     });
 }
 
+int rxmet_gru_forward_quant_fp_carrier(int is_training, int T, int B, int I, int H, const float *W_dev, const float *R_dev,
+                                       const float *bw_dev, const float *br_dev, const float *x_dev, const float *h0_dev,
+                                       const rxmet_gru_quant_params *params, float *h_dev, float *v_dev, int32_t *W_q_dev,
+                                       int32_t *R_q_dev, int32_t *bw_q_dev, int32_t *br_q_dev, int32_t *x_q_dev,
+                                       int32_t *h_q_dev, int32_t *v_q_dev, const rxmet_gru_masks *masks, void *workspace_dev,
+                                       size_t workspace_bytes, void *stream) {
+    return guarded([&] {
+        RXMET_PTR(x_dev); RXMET_PTR(h_dev); RXMET_PTR(v_dev); RXMET_PTR(params);
+        gru::ForwardQuantCall call;
+        call.isTraining = is_training;
+        call.T = T; call.B = B; call.I = I; call.H = H;
+        call.W = W_dev; call.R = R_dev; call.bw = bw_dev; call.br = br_dev; call.x = x_dev; call.h0 = h0_dev;
+        call.h = h_dev; call.v = v_dev;
+        call.W_q = W_q_dev; call.R_q = R_q_dev; call.bw_q = bw_q_dev; call.br_q = br_q_dev; call.x_q = x_q_dev;
+        call.h_q = h_q_dev; call.v_q = v_q_dev;
+        call.masks = masks;
+        call.fpCarrier = params;
+        runQuant(call, params, workspace_dev, workspace_bytes, stream);
+    });
+}
+
 int rxmet_gru_packed_flags_supported(const rxmet_gru_quant_params *params, int B, int I, int H) {
     int supported = 0;
     const int rc = guarded([&] {

@@ -1223,11 +1223,271 @@ void sizeTyped(WorkspaceSizer &ws, int T, int B, int I, int H) {
 
 }  // namespace
 
+size_t fpCarrierBytes(int T, int B, int I, int H);
+
 size_t forwardQuantWorkspaceBytes(int T, int B, int I, int H) {
     // The widest storage classes bound every configuration; the byte-plane kernels add their operands.
     WorkspaceSizer ws;
     sizeTyped<int32_t, int32_t, int32_t>(ws, T, B, I, H);
-    return ws.used() + 4096 + forwardWideExtraBytes(T, B, I, H);
+    return std::max(ws.used() + 4096 + forwardWideExtraBytes(T, B, I, H), fpCarrierBytes(T, B, I, H));
+}
+
+// ---- FP32 carrier -------------------------------------------------------------------------------------------
+//
+// The reference's second quantized carrier (its CUDA default for float code storage): codes held in floats,
+// rescale = rint(x * ratio) in float, the 16-segment tables evaluated in float
+// (operators/quant-gru/src/gru_forward_gpu_quant_fp.cu).  The matrix products are formed exactly on the integer
+// codes and converted to float once, which equals the reference's float GEMM whenever the sums stay below 2^24
+// (always for 8-bit grids up to K = 512; beyond, the reference's own result depends on its GEMM's summation
+// order).  Everything behind the product follows the reference's float operations one by one.
+__device__ __forceinline__ float fpClamp(float v, float lo, float hi, uint8_t &keep) {
+    keep = (v < lo || v > hi) ? 0 : 1;
+    return fmaxf(lo, fminf(v, hi));
+}
+// biasRescaleInline, gru_forward_gpu_quant_fp.cu:138-163
+__device__ __forceinline__ float fpLinear(float gemm, float bias, float sumZp, float invGemm, float invBias, float zpOut, float lo,
+                                          float hi, uint8_t &keep) {
+    const float biasTerm = rintf(__fmul_rn(bias, invBias));
+    const float combined = __fadd_rn(__fsub_rn(gemm, sumZp), biasTerm);
+    return fpClamp(__fadd_rn(rintf(__fmul_rn(combined, invGemm)), zpOut), lo, hi, keep);
+}
+// piecewiseLinearFP, gru_forward_gpu_quant_fp.cu:91-108
+__device__ __forceinline__ float fpTable(float qx, const Lut &lut, float lo, float hi, uint8_t &keep) {
+    int seg = kSegments - 1;
+#pragma unroll
+    for (int i = kSegments - 2; i >= 0; --i) seg = (qx < static_cast<float>(lut.threshold[i])) ? i : seg;
+    const float product = __fmul_rn(static_cast<float>(lut.q_b[seg]), __fsub_rn(qx, static_cast<float>(lut.zp_x)));
+    const float value = __fadd_rn(rintf(ldexpf(product, -lut.n_bx[seg])), static_cast<float>(lut.term_c[seg]));
+    return fpClamp(value, lo, hi, keep);
+}
+
+// sums[c] = float(sum_k codes[k][c]) * zp: the zero-point compensation term (computeWeightSumKernel)
+__global__ void fpWeightSums(const int32_t *__restrict__ codes, int K, int C, float zp, float *__restrict__ sums) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    int32_t sum = 0;
+    for (int k = 0; k < K; ++k) sum += codes[static_cast<size_t>(k) * C + c];
+    sums[c] = __fmul_rn(static_cast<float>(sum), zp);
+}
+
+struct FpLinearArgs {
+    const int32_t *x;       // [rows][I]
+    const int32_t *W;       // [I][C]
+    const int32_t *bias;    // [C]
+    const float *sumZp, *invGemm, *invBias;
+    int rows, I, C;
+    float zpOut, lo, hi;
+    float *out;             // [rows][C] float codes
+    uint8_t *mask;          // optional
+};
+__global__ void fpInputLinear(const FpLinearArgs a) {
+    const size_t total = static_cast<size_t>(a.rows) * a.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t row = i / a.C;
+        const int c = static_cast<int>(i % a.C);
+        const int32_t *xr = a.x + row * a.I;
+        int64_t acc = 0;
+        for (int k = 0; k < a.I; ++k) acc += static_cast<int64_t>(xr[k]) * a.W[static_cast<size_t>(k) * a.C + c];
+        uint8_t keep;
+        a.out[i] = fpLinear(static_cast<float>(acc), static_cast<float>(a.bias[c]), a.sumZp[c], a.invGemm[c], a.invBias[c], a.zpOut, a.lo,
+                            a.hi, keep);
+        if (a.mask) a.mask[i] = keep;
+    }
+}
+
+struct FpRecurrentArgs {
+    int T, B, H;
+    const int32_t *R;       // [H][3H]
+    const int32_t *bias;    // [3H] br codes
+    const float *sumZp, *invGemm, *invBias;
+    const float *ih;        // [T][B][3H] float codes of the ih linear stage
+    const int32_t *h0;      // [B][H] codes (the zero point when no initial state was given)
+    FpCarrierScalars s;
+    float *h, *v;           // dequantized outputs
+    int32_t *hq, *vq;       // optional codes
+    uint8_t *maskHh, *maskGateIn, *maskGateOut, *maskH;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(768) fpRecurrent(const __grid_constant__ FpRecurrentArgs a, const __grid_constant__ GateExec g) {
+    extern __shared__ __align__(16) unsigned char fpSmem[];
+    int32_t *hS = reinterpret_cast<int32_t *>(fpSmem);          // [BT][H] hidden codes
+    float *hhS = reinterpret_cast<float *>(hS + BT * a.H);       // [BT][3H] hh linear codes
+    const int H = a.H, C = 3 * a.H, tid = threadIdx.x, nthreads = blockDim.x;
+    const int b0 = blockIdx.x * BT, nb = min(BT, a.B - b0);
+    const FpCarrierScalars &s = a.s;
+    const float zpH = s.zp[RXMET_GRU_H], zpHh = s.zp[RXMET_GRU_WEIGHT_HH_LINEAR], zpIh = s.zp[RXMET_GRU_WEIGHT_IH_LINEAR];
+    for (int i = tid; i < BT * H; i += nthreads) {
+        const int b = i / H, j = i % H;
+        const int32_t q = b < nb ? a.h0[static_cast<size_t>(b0 + b) * H + j] : g.zp[RXMET_GRU_H];
+        hS[i] = q;
+        if (b < nb) {
+            const size_t o = static_cast<size_t>(b0 + b) * H + j;
+            a.h[o] = static_cast<float>(q - g.zp[RXMET_GRU_H]) * g.eff[RXMET_GRU_H];
+            if (a.hq) a.hq[o] = q;
+        }
+    }
+    __syncthreads();
+    for (int t = 0; t < a.T; ++t) {
+        // hh linear stage of this step: exact integer product, then the reference's float bias-and-rescale
+        for (int c = tid; c < C; c += nthreads) {
+            int64_t acc[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[b] = 0;
+            for (int k = 0; k < H; ++k) {
+                const int64_t w = a.R[static_cast<size_t>(k) * C + c];
+#pragma unroll
+                for (int b = 0; b < BT; ++b) acc[b] += w * hS[b * H + k];
+            }
+            const float bias = static_cast<float>(a.bias[c]);
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                uint8_t keep;
+                hhS[b * C + c] = fpLinear(static_cast<float>(acc[b]), bias, a.sumZp[c], a.invGemm[c], a.invBias[c], zpHh,
+                                          s.lo[RXMET_GRU_WEIGHT_HH_LINEAR], s.hi[RXMET_GRU_WEIGHT_HH_LINEAR], keep);
+                if (a.maskHh && b < nb) a.maskHh[(static_cast<size_t>(t) * a.B + b0 + b) * C + c] = keep;
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < nb * H; e += nthreads) {
+            const int b = e / H, j = e % H;
+            const size_t row = static_cast<size_t>(t) * a.B + b0 + b;
+            const float *ih = a.ih + row * C + j;
+            const float *hh = hhS + b * C + j;
+            uint8_t kin[3], kout[3], kh;
+            // update and reset gates (computeUpdateGateFP / computeResetGateFP)
+            const float zin = __fadd_rn(__fadd_rn(rintf(__fmul_rn(__fsub_rn(ih[0], zpIh), s.ihToUpdate)),
+                                                  rintf(__fmul_rn(__fsub_rn(hh[0], zpHh), s.hhToUpdate))),
+                                        s.zp[RXMET_GRU_UPDATE_GATE_INPUT]);
+            const float z = fpTable(fpClamp(zin, s.lo[RXMET_GRU_UPDATE_GATE_INPUT], s.hi[RXMET_GRU_UPDATE_GATE_INPUT], kin[0]), g.lut_update,
+                                    s.lo[RXMET_GRU_UPDATE_GATE_OUTPUT], s.hi[RXMET_GRU_UPDATE_GATE_OUTPUT], kout[0]);
+            const float rin = __fadd_rn(__fadd_rn(rintf(__fmul_rn(__fsub_rn(ih[H], zpIh), s.ihToReset)),
+                                                  rintf(__fmul_rn(__fsub_rn(hh[H], zpHh), s.hhToReset))),
+                                        s.zp[RXMET_GRU_RESET_GATE_INPUT]);
+            const float r = fpTable(fpClamp(rin, s.lo[RXMET_GRU_RESET_GATE_INPUT], s.hi[RXMET_GRU_RESET_GATE_INPUT], kin[1]), g.lut_reset,
+                                    s.lo[RXMET_GRU_RESET_GATE_OUTPUT], s.hi[RXMET_GRU_RESET_GATE_OUTPUT], kout[1]);
+            // candidate (computeNewGateFP)
+            const float hhn = hh[2 * H];
+            const float rh = rintf(__fmul_rn(__fmul_rn(__fsub_rn(r, s.zp[RXMET_GRU_RESET_GATE_OUTPUT]), __fsub_rn(hhn, zpHh)), s.rhToNew));
+            const float nin = __fadd_rn(__fadd_rn(rintf(__fmul_rn(__fsub_rn(ih[2 * H], zpIh), s.ihToNew)), rh), s.zp[RXMET_GRU_NEW_GATE_INPUT]);
+            const float n = fpTable(fpClamp(nin, s.lo[RXMET_GRU_NEW_GATE_INPUT], s.hi[RXMET_GRU_NEW_GATE_INPUT], kin[2]), g.lut_new,
+                                    s.lo[RXMET_GRU_NEW_GATE_OUTPUT], s.hi[RXMET_GRU_NEW_GATE_OUTPUT], kout[2]);
+            // new hidden code (computeHiddenStateFP): the two products are summed with one fused multiply-add, as the
+            // reference's device code is compiled; both are exact below 2^24, so the order is immaterial there
+            const float hOld = static_cast<float>(hS[b * H + j]);
+            const float nAligned = __fadd_rn(rintf(__fmul_rn(__fsub_rn(n, s.zp[RXMET_GRU_NEW_GATE_OUTPUT]), s.newToH)), zpH);
+            const float oldMul = __fmul_rn(__fsub_rn(z, s.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]), __fsub_rn(hOld, zpH));
+            const float sum = __fmaf_rn(__fsub_rn(s.quantOne, z), __fsub_rn(nAligned, zpH), oldMul);
+            const float hNew = fpClamp(__fadd_rn(rintf(__fmul_rn(sum, s.updateOldToH)), zpH), s.lo[RXMET_GRU_H], s.hi[RXMET_GRU_H], kh);
+            const int32_t hCode = static_cast<int32_t>(hNew);
+            hS[b * H + j] = hCode;
+            const size_t ho = (row + a.B) * H + j;
+            a.h[ho] = static_cast<float>(hCode - g.zp[RXMET_GRU_H]) * g.eff[RXMET_GRU_H];
+            float *vRow = a.v + row * 4 * H + j;
+            const int32_t zc = static_cast<int32_t>(z), rc = static_cast<int32_t>(r), nc = static_cast<int32_t>(n), hc = static_cast<int32_t>(hhn);
+            vRow[0] = static_cast<float>(zc - g.zp[RXMET_GRU_UPDATE_GATE_OUTPUT]) * g.eff[RXMET_GRU_UPDATE_GATE_OUTPUT];
+            vRow[H] = static_cast<float>(rc - g.zp[RXMET_GRU_RESET_GATE_OUTPUT]) * g.eff[RXMET_GRU_RESET_GATE_OUTPUT];
+            vRow[2 * H] = static_cast<float>(nc - g.zp[RXMET_GRU_NEW_GATE_OUTPUT]) * g.eff[RXMET_GRU_NEW_GATE_OUTPUT];
+            vRow[3 * H] = static_cast<float>(hc - g.zp[RXMET_GRU_WEIGHT_HH_LINEAR]) * g.eff[RXMET_GRU_WEIGHT_HH_LINEAR];
+            if (a.hq) a.hq[ho] = hCode;
+            if (a.vq) {
+                int32_t *vq = a.vq + row * 4 * H + j;
+                vq[0] = zc; vq[H] = rc; vq[2 * H] = nc; vq[3 * H] = hc;
+            }
+            if (a.maskGateIn) {
+                uint8_t *mi = a.maskGateIn + row * C + j, *mo = a.maskGateOut + row * C + j;
+                mi[0] = kin[0]; mi[H] = kin[1]; mi[2 * H] = kin[2];
+                mo[0] = kout[0]; mo[H] = kout[1]; mo[2 * H] = kout[2];
+                a.maskH[row * H + j] = kh;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+size_t fpCarrierBytes(int T, int B, int I, int H) {
+    const size_t rows = static_cast<size_t>(T) * B, C = 3 * static_cast<size_t>(H);
+    WorkspaceSizer ws;
+    ws.take<float>(12 * C);
+    ws.take<int32_t>(static_cast<size_t>(I) * C);
+    ws.take<int32_t>(static_cast<size_t>(H) * C);
+    ws.take<int32_t>(2 * C);
+    ws.take<int32_t>(rows * I);
+    ws.take<int32_t>(static_cast<size_t>(B) * H);
+    ws.take<float>(rows * C);
+    ws.take<float>(6 * C);
+    return ws.used() + 4096;
+}
+
+void forwardFpCarrier(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaStream_t st) {
+    const int T = call.T, B = call.B, I = call.I, H = call.H, C = 3 * H;
+    const GateExec &g = e.gate;
+    const size_t rows = static_cast<size_t>(T) * B;
+    RXMET_REQUIRE(call.x != nullptr && call.x_codes_in == nullptr && call.h0_codes_in == nullptr, "the FP32 carrier takes float inputs");
+    RXMET_REQUIRE(call.stepFlags == nullptr, "the FP32 carrier writes byte masks");
+    const bool training = call.isTraining != 0;
+    const rxmet_gru_masks none{};
+    const rxmet_gru_masks &mk = (training && call.masks) ? *call.masks : none;
+    const FpCarrierParams fp = deriveFpCarrier(*call.fpCarrier);
+
+    const ChannelDevice ch = uploadChannels(e, ws, st);
+    int32_t *wq = ws.take<int32_t>(static_cast<size_t>(I) * C), *rq = ws.take<int32_t>(static_cast<size_t>(H) * C);
+    int32_t *biasQ = ws.take<int32_t>(2 * static_cast<size_t>(C));
+    int32_t *xq = ws.take<int32_t>(rows * I), *h0q = ws.take<int32_t>(static_cast<size_t>(B) * H);
+    float *ih = ws.take<float>(rows * C);
+    float *chan = ws.take<float>(6 * static_cast<size_t>(C));   // four ratio arrays, two zero-point compensation arrays
+    launchQuantize<int32_t>(st, call.W, I, C, I, C, ch.effW, 0.f, 0, g.qlo[RXMET_GRU_W], g.qhi[RXMET_GRU_W], 1, wq, call.W_q, mk.W);
+    launchQuantize<int32_t>(st, call.R, H, C, H, C, ch.effR, 0.f, 0, g.qlo[RXMET_GRU_R], g.qhi[RXMET_GRU_R], 1, rq, call.R_q, mk.R);
+    launchQuantize<int32_t>(st, call.bw, 1, C, 1, C, ch.effBw, 0.f, 0, g.qlo[RXMET_GRU_BW], g.qhi[RXMET_GRU_BW], 1, biasQ, call.bw_q, mk.bw);
+    launchQuantize<int32_t>(st, call.br, 1, C, 1, C, ch.effBr, 0.f, 0, g.qlo[RXMET_GRU_BR], g.qhi[RXMET_GRU_BR], 1, biasQ + C, call.br_q, mk.br);
+    launchQuantize<int32_t>(st, call.x, static_cast<int>(rows), I, static_cast<int>(rows), I, nullptr, g.eff[RXMET_GRU_X], g.zp[RXMET_GRU_X],
+                            g.qlo[RXMET_GRU_X], g.qhi[RXMET_GRU_X], 1, xq, call.x_q, mk.x);
+    if (call.h0) {
+        launchQuantize<int32_t>(st, call.h0, B, H, B, H, nullptr, g.eff[RXMET_GRU_H], g.zp[RXMET_GRU_H], g.qlo[RXMET_GRU_H],
+                                g.qhi[RXMET_GRU_H], 1, h0q, nullptr, mk.h0);
+    } else {
+        fillCodes<int32_t><<<gridFor(static_cast<size_t>(B) * H, 256), 256, 0, st>>>(h0q, static_cast<size_t>(B) * H, g.zp[RXMET_GRU_H]);
+        afterLaunch("fillCodes");
+    }
+    // pageable source: the runtime stages it before the call returns
+    RXMET_CUDA(cudaMemcpyAsync(chan, fp.channel.data(), sizeof(float) * 4 * C, cudaMemcpyHostToDevice, st));
+    float *sumX = chan + 4 * static_cast<size_t>(C), *sumH = chan + 5 * static_cast<size_t>(C);
+    fpWeightSums<<<(C + 127) / 128, 128, 0, st>>>(wq, I, C, fp.s.zp[RXMET_GRU_X], sumX);
+    afterLaunch("fpWeightSums");
+    fpWeightSums<<<(C + 127) / 128, 128, 0, st>>>(rq, H, C, fp.s.zp[RXMET_GRU_H], sumH);
+    afterLaunch("fpWeightSums");
+    {
+        FpLinearArgs a{};
+        a.x = xq; a.W = wq; a.bias = biasQ; a.sumZp = sumX; a.invGemm = chan; a.invBias = chan + C;
+        a.rows = static_cast<int>(rows); a.I = I; a.C = C;
+        a.zpOut = fp.s.zp[RXMET_GRU_WEIGHT_IH_LINEAR]; a.lo = fp.s.lo[RXMET_GRU_WEIGHT_IH_LINEAR]; a.hi = fp.s.hi[RXMET_GRU_WEIGHT_IH_LINEAR];
+        a.out = ih; a.mask = mk.weight_ih_linear;
+        KernelTimer timer__("inputLinear", st);
+        fpInputLinear<<<gridFor(rows * C, 256), 256, 0, st>>>(a);
+        afterLaunch("inputLinear");
+    }
+    {
+        FpRecurrentArgs a{};
+        a.T = T; a.B = B; a.H = H; a.R = rq; a.bias = biasQ + C; a.sumZp = sumH; a.invGemm = chan + 2 * static_cast<size_t>(C);
+        a.invBias = chan + 3 * static_cast<size_t>(C); a.ih = ih; a.h0 = h0q; a.s = fp.s;
+        a.h = call.h; a.v = call.v; a.hq = call.h_q; a.vq = call.v_q;
+        a.maskHh = mk.weight_hh_linear; a.maskGateIn = mk.gate_input; a.maskGateOut = mk.gate_output; a.maskH = mk.h;
+        if (mk.gate_input || mk.gate_output || mk.h)
+            RXMET_REQUIRE(mk.gate_input && mk.gate_output && mk.h, "gate_input, gate_output and h masks come together");
+        const int sms = currentDevice().sms;
+        const int bt = B >= 4 * sms ? 4 : (B >= 2 * sms ? 2 : 1);
+        const int block = std::min((C + 31) / 32 * 32, 768);
+        auto launch = [&](auto kernel, int BT) {
+            const size_t smem = sizeof(int32_t) * BT * H + sizeof(float) * BT * C;
+            ensureDynamicSmem(reinterpret_cast<const void *>(kernel), smem);
+            KernelTimer timer__("recurrentForward", st);
+            kernel<<<(B + BT - 1) / BT, block, smem, st>>>(a, g);
+        };
+        if (bt == 4) launch(fpRecurrent<4>, 4);
+        else if (bt == 2) launch(fpRecurrent<2>, 2);
+        else launch(fpRecurrent<1>, 1);
+        afterLaunch("recurrentForward");
+    }
 }
 
 bool packedFlagsSupported(const Exec &e, int B, int I, int H) {
@@ -1246,6 +1506,10 @@ void forwardQuant(const ForwardQuantCall &call, const Exec &e, void *workspace, 
     if (call.stepFlags && !packedFlagsSupported(e, call.B, call.I, call.H))
         fail(RXMET_ERR_UNSUPPORTED, "packed step flags: these grids or sizes do not take the 8-bit register path");
     Workspace ws(workspace, workspaceBytes);
+    if (call.fpCarrier) {
+        forwardFpCarrier(call, e, ws, st);
+        return;
+    }
     const CodeClass w = e.weightClass, a = e.actClass, l = e.linearClass;
     if (l == CodeClass::I32 || w == CodeClass::I32 || a == CodeClass::I32) {
         runTyped<int32_t, int32_t, int32_t>(call, e, ws, st);

@@ -27,6 +27,7 @@ struct ForwardQuantCall {
     int32_t *h_q = nullptr, *v_q = nullptr;
     const rxmet_gru_masks *masks = nullptr;
     uint16_t *stepFlags = nullptr;          // optional [T,B,H]: the 13 per-step keep flags of an element packed into 16 bits
+    const rxmet_gru_quant_params *fpCarrier = nullptr;   // set: run the FP32 carrier with these (raw) scales
 };
 
 // Whether forwardQuant can write stepFlags for these parameters and sizes (the register-resident 8-bit path).

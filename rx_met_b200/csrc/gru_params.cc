@@ -566,5 +566,51 @@ std::shared_ptr<const Exec> deriveExec(const rxmet_gru_quant_params &p) {
     return exec;
 }
 
+// Every ratio is ONE float division of float scales (products of two scales are rounded to float first), as the
+// reference computes them on the host; this file is compiled without FMA contraction.
+FpCarrierParams deriveFpCarrier(const rxmet_gru_quant_params &p) {
+    FpCarrierParams out;
+    FpCarrierScalars &s = out.s;
+    for (int op = 0; op < kOps; ++op) {
+        s.zp[op] = static_cast<float>(p.zero_point[op]);
+        const int bits = p.config.bits[op];
+        const int64_t qmin = p.config.is_unsigned[op] ? 0 : -(int64_t{1} << (bits - 1));
+        const int64_t qmax = p.config.is_unsigned[op] ? (int64_t{1} << bits) - 1 : (int64_t{1} << (bits - 1)) - 1;
+        float lo = static_cast<float>(qmin), hi = static_cast<float>(qmax);
+        if (static_cast<double>(lo) < static_cast<double>(qmin)) lo = std::nextafterf(lo, INFINITY);
+        if (static_cast<double>(hi) > static_cast<double>(qmax)) hi = std::nextafterf(hi, -INFINITY);
+        s.lo[op] = lo;
+        s.hi[op] = hi;
+    }
+    auto ratio = [](float src, float dst) { return src / dst; };
+    const float *sc = p.scale;
+    s.ihToUpdate = ratio(sc[RXMET_GRU_WEIGHT_IH_LINEAR], sc[RXMET_GRU_UPDATE_GATE_INPUT]);
+    s.hhToUpdate = ratio(sc[RXMET_GRU_WEIGHT_HH_LINEAR], sc[RXMET_GRU_UPDATE_GATE_INPUT]);
+    s.ihToReset = ratio(sc[RXMET_GRU_WEIGHT_IH_LINEAR], sc[RXMET_GRU_RESET_GATE_INPUT]);
+    s.hhToReset = ratio(sc[RXMET_GRU_WEIGHT_HH_LINEAR], sc[RXMET_GRU_RESET_GATE_INPUT]);
+    s.ihToNew = ratio(sc[RXMET_GRU_WEIGHT_IH_LINEAR], sc[RXMET_GRU_NEW_GATE_INPUT]);
+    {
+        const float product = sc[RXMET_GRU_RESET_GATE_OUTPUT] * sc[RXMET_GRU_WEIGHT_HH_LINEAR];
+        s.rhToNew = ratio(product, sc[RXMET_GRU_NEW_GATE_INPUT]);
+    }
+    s.quantOne = rintf(1.0f / sc[RXMET_GRU_UPDATE_GATE_OUTPUT]) + static_cast<float>(p.zero_point[RXMET_GRU_UPDATE_GATE_OUTPUT]);
+    {
+        const float product = sc[RXMET_GRU_UPDATE_GATE_OUTPUT] * sc[RXMET_GRU_H];
+        s.updateOldToH = ratio(product, sc[RXMET_GRU_H]);
+    }
+    s.newToH = ratio(sc[RXMET_GRU_NEW_GATE_OUTPUT], sc[RXMET_GRU_H]);
+    const size_t C = 3 * static_cast<size_t>(p.hidden);
+    out.channel.resize(4 * C);
+    for (size_t c = 0; c < C; ++c) {
+        const float wx = p.scale_W[c] * sc[RXMET_GRU_X];
+        out.channel[c] = ratio(wx, sc[RXMET_GRU_WEIGHT_IH_LINEAR]);
+        out.channel[C + c] = ratio(p.scale_bw[c], wx);
+        const float rh = p.scale_R[c] * sc[RXMET_GRU_H];
+        out.channel[2 * C + c] = ratio(rh, sc[RXMET_GRU_WEIGHT_HH_LINEAR]);
+        out.channel[3 * C + c] = ratio(p.scale_br[c], rh);
+    }
+    return out;
+}
+
 }  // namespace gru
 }  // namespace rxmet

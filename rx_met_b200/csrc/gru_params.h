@@ -92,5 +92,21 @@ float decodeEffectiveScale(float scale, bool usePot2);
 // step and the table generation costs tens of microseconds.
 std::shared_ptr<const Exec> deriveExec(const rxmet_gru_quant_params &params);
 
+// Parameters of the FP32 carrier (floats holding integer codes, rescales = rint(x * ratio) with ratio = source
+// scale / destination scale as one float division; reference: ForwardPassQuantFP::setRescaleParam,
+// operators/quant-gru/src/gru_forward_gpu_quant_fp.cu:853-1044).  Scalars travel to kernels by value, the four
+// per-channel arrays (3 * hidden floats each) are uploaded per call.
+struct FpCarrierScalars {
+    float zp[kOps];
+    float lo[kOps], hi[kOps];            // clamp bounds of every point (clamp_f, quantize_ops_helper.h:334-354)
+    float ihToUpdate, hhToUpdate, ihToReset, hhToReset, ihToNew, rhToNew, newToH, updateOldToH;
+    float quantOne;                      // rint(1 / scale_update_gate_output) + its zero point
+};
+struct FpCarrierParams {
+    FpCarrierScalars s{};
+    std::vector<float> channel;          // [4][3 hidden]: gemm_x -> ih linear, bw -> gemm_x, gemm_h -> hh linear, br -> gemm_h
+};
+FpCarrierParams deriveFpCarrier(const rxmet_gru_quant_params &params);
+
 }  // namespace gru
 }  // namespace rxmet

@@ -471,7 +471,30 @@ def _carve(device, dtype, shapes):
     return [pool[o:o + n].view(shape) for o, n, shape in zip(offsets, counts, shapes)]
 
 
-def _forward_quant(is_training, T, B, I, H, W, R, bw, br, x, h0, quant_params, code_dtype):
+_FLOAT_STORAGE_CARRIERS = ("integer", "fp32")
+_float_storage_carrier = "integer"
+
+
+def set_float_storage_carrier(carrier):
+    """Choose what forward_quant_float_storage computes with; returns the previous choice.
+
+    "integer" (default): the integer carrier, the same arithmetic as forward_quant_int_storage and as the
+    reference's CPU build (src/quantize_ops_helper.h: multiply, add, rounding right shift), so the two storage
+    modes return the same codes.  "fp32": the reference's CUDA float-code arithmetic
+    (src/gru_forward_gpu_quant_fp.cu: codes held in float, rescales as rintf(x * ratio), float tables), bit
+    for bit what the reference's CUDA kernels return while the integer matrix sums stay below 2^24."""
+    global _float_storage_carrier
+    if carrier not in _FLOAT_STORAGE_CARRIERS:
+        raise ValueError(f"carrier must be one of {_FLOAT_STORAGE_CARRIERS}, got {carrier!r}")
+    previous, _float_storage_carrier = _float_storage_carrier, carrier
+    return previous
+
+
+def float_storage_carrier():
+    return _float_storage_carrier
+
+
+def _forward_quant(is_training, T, B, I, H, W, R, bw, br, x, h0, quant_params, code_dtype, fp_carrier=False):
     lib = cabi.load_library()
     W, R, bw, br, x, h0v = _common_inputs(T, B, I, H, W, R, bw, br, x, h0)
     dev = x.device
@@ -494,7 +517,8 @@ def _forward_quant(is_training, T, B, I, H, W, R, bw, br, x, h0, quant_params, c
             masks[name] = empty
     ws = _workspace(dev, lib.rxmet_gru_workspace_bytes(1, T, B, I, H))
     with torch.cuda.device(dev):
-        cabi.check(lib.rxmet_gru_forward_quant(
+        entry = lib.rxmet_gru_forward_quant_fp_carrier if fp_carrier else lib.rxmet_gru_forward_quant
+        cabi.check(entry(
             int(bool(is_training)), T, B, I, H, _ptr(W), _ptr(R), _ptr(bw), _ptr(br), _ptr(x), _ptr(h0v),
             C.byref(params), _ptr(h), _ptr(v), _ptr(codes["W_q"]), _ptr(codes["R_q"]), _ptr(codes["bw_q"]),
             _ptr(codes["br_q"]), _ptr(codes["x_q"]), None, None,
@@ -518,9 +542,11 @@ def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, h
 
 def forward_quant_float_storage(is_training, time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, h0,
                                 quant_params):
-    """Same tuple with the code caches stored as float32 (values are still integers)."""
+    """Same tuple with the code caches stored as float32 (values are still integers); computed with the
+    carrier set_float_storage_carrier selected."""
     return _forward_quant(is_training, int(time_steps), int(batch_size), int(input_size), int(hidden_size),
-                          W, R, bw, br, x, h0, quant_params, torch.float32)
+                          W, R, bw, br, x, h0, quant_params, torch.float32,
+                          fp_carrier=_float_storage_carrier == "fp32")
 
 
 def forward_quantized_int_io(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x_q, h0_q, quant_params):

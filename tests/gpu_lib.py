@@ -31,8 +31,9 @@ def workspace(op, T, B, I, H, extra=0):
     return torch.empty(n, dtype=torch.uint8, device="cuda"), n
 
 
-def forward_quant(W, R, bw, br, x, h0, params, training=True, workspace_bytes=None):
-    """params: oracle_lib.ParamsBox.  Returns dict of numpy arrays (codes, masks, h, v)."""
+def forward_quant(W, R, bw, br, x, h0, params, training=True, workspace_bytes=None, fp_carrier=False):
+    """params: oracle_lib.ParamsBox.  Returns dict of numpy arrays (codes, masks, h, v).  fp_carrier: the reference's
+    FP32 carrier (rxmet_gru_forward_quant_fp_carrier) instead of the integer carrier."""
     lib = cabi.load_library()
     T, B, I = x.shape
     H = R.shape[0]
@@ -54,7 +55,8 @@ def forward_quant(W, R, bw, br, x, h0, params, training=True, workspace_bytes=No
     ws, n = workspace(1, T, B, I, H)
     if workspace_bytes is not None:
         n = workspace_bytes
-    rc = lib.rxmet_gru_forward_quant(
+    entry = lib.rxmet_gru_forward_quant_fp_carrier if fp_carrier else lib.rxmet_gru_forward_quant
+    rc = entry(
         int(training), T, B, I, H, ptr(d["W"]), ptr(d["R"]), ptr(d["bw"]), ptr(d["br"]), ptr(d["x"]), ptr(d["h0"]),
         C.byref(params.c), ptr(out["h"]), ptr(out["v"]), ptr(out["W_q"]), ptr(out["R_q"]), ptr(out["bw_q"]),
         ptr(out["br_q"]), ptr(out["x_q"]), ptr(out["h_q"]), ptr(out["v_q"]),

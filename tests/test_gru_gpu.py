@@ -368,6 +368,47 @@ def test_python_module_mirrors_reference_binding(gl):
     assert out_q.dtype == torch.int32 and tuple(out_q.shape) == (T, B, H) and tuple(hn_q.shape) == (1, B, H)
 
 
+def test_float_storage_carrier_switch(gl):
+    """forward_quant_float_storage with the carrier set to "fp32" returns what the FP32-carrier entry point
+    returns (the reference's CUDA float-code arithmetic); the default stays the integer carrier; the backward
+    accepts either forward's caches."""
+    import types
+    import torch
+    from rx_met_b200 import gru_interface_binding as ops
+    T, B, I, H = 7, 5, 12, 32
+    prob = ol.gru_problem(29, T, B, I, H, with_h0=True)
+    t = [torch.from_numpy(a).cuda() for a in prob]
+    cfg = ops.OperatorQuantConfig()
+    for name in cabi.OP_NAMES:
+        if name not in ("W", "R", "bw", "br"):
+            setattr(cfg, f"{name}_symmetric_", False)
+    ranges = ops.GRUQuantizationRanges(H)
+    ops.forward_calibrate(False, T, B, I, H, *t, "minmax", cfg, quant_ranges=ranges)
+    qp = ops.calculate_gru_quantitative_parameters(ranges, cfg)
+    params_c, keep = qp._to_c()
+    rc, want = gl.forward_quant(*prob, types.SimpleNamespace(c=params_c), training=True, fp_carrier=True)
+    assert rc == 0, want
+    assert ops.float_storage_carrier() == "integer"
+    previous = ops.set_float_storage_carrier("fp32")
+    try:
+        out = ops.forward_quant_float_storage(True, T, B, I, H, *t, qp)
+    finally:
+        ops.set_float_storage_carrier(previous)
+    assert ops.float_storage_carrier() == "integer"
+    np.testing.assert_array_equal(out[0].cpu().numpy(), want["h"])
+    np.testing.assert_array_equal(out[1].cpu().numpy(), want["v"])
+    for k, got in zip(("W_q", "R_q", "bw_q", "br_q", "x_q"), out[2:7]):
+        assert got.dtype == torch.float32
+        np.testing.assert_array_equal(got.cpu().numpy().astype(np.int32), want[k], err_msg=k)
+    with pytest.raises(ValueError):
+        ops.set_float_storage_carrier("bf16")
+    dh_new = torch.zeros((T + 1, B, H), device="cuda")
+    dh_new[1:] = torch.randn((T, B, H), generator=torch.Generator().manual_seed(1)).cuda()
+    grads = ops.backward_quant_float_storage(T, B, I, H, *out[2:7], dh_new, out[0], out[1], qp, *out[7:])
+    assert len(grads) == 6 and all(bool(torch.isfinite(g).all()) for g in grads)
+    del keep
+
+
 @pytest.mark.parametrize("cfg_name", ["a16", "w8a8"])
 @pytest.mark.parametrize("shape", [(4, 3, 40, 256), (3, 2, 512, 256)], ids=lambda s: "x".join(map(str, s)))
 def test_kws_body_layer_shapes(gl, cfg_name, shape):

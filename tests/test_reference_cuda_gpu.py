@@ -107,3 +107,52 @@ def test_forward_and_backward_against_the_reference_cuda_build(T, B, I, H, bits,
     for k in ("dx", "dW", "dR", "dbw", "dbr", "dh0"):
         err = np.abs(mine[k].astype(np.float64) - want[k]).max()
         assert err <= 2e-5 * max(np.abs(want[k]).max(), 1e-30), f"{k}: {err:.3e} against {np.abs(want[k]).max():.3e}"
+
+
+def reference_forward_fp(problem, params, T, B, I, H):
+    """quantGRUForwardFP of the reference's CUDA build: float code caches, dequantized h and v, byte masks."""
+    W, R, bw, br, x, h0 = [gpu_lib.dev(a) for a in problem]
+    f32 = dict(dtype=torch.float32, device="cuda")
+    out = {"h": torch.zeros((T + 1, B, H), **f32), "v": torch.zeros((T, B, 4 * H), **f32),
+           "W_q": torch.zeros((I, 3 * H), **f32), "R_q": torch.zeros((H, 3 * H), **f32), "bw_q": torch.zeros(3 * H, **f32),
+           "br_q": torch.zeros(3 * H, **f32), "x_q": torch.zeros((T, B, I), **f32)}
+    masks, ms = {}, cabi.Masks()
+    for name, shape in gpu_lib.MASK_SHAPES(T, B, I, H).items():
+        if name == "h0" and h0 is None:
+            continue
+        masks[name] = torch.full(shape, 255, dtype=torch.uint8, device="cuda")
+        setattr(ms, name, masks[name].data_ptr())
+    rc.call("refcuda_gru_forward_quant_fp", 1, T, B, I, H, P(W), P(R), P(bw), P(br), P(x), P(h0), C.byref(params.c),
+            P(out["h"]), P(out["v"]), C.byref(ms), P(out["W_q"]), P(out["R_q"]), P(out["bw_q"]), P(out["br_q"]), P(out["x_q"]))
+    return out, masks
+
+
+FP_CASES = [
+    # T, B, I, H, symmetric activations, h0, power-of-two scales
+    (6, 5, 12, 16, False, True, False),
+    (12, 16, 40, 128, False, False, False),
+    (8, 40, 40, 64, True, True, False),
+    (7, 9, 24, 96, False, True, True),
+]
+
+
+@pytest.mark.parametrize("T,B,I,H,sym,with_h0,pot2", FP_CASES)
+def test_fp32_carrier_forward_against_the_reference_cuda_build(T, B, I, H, sym, with_h0, pot2):
+    """The FP32 carrier (the reference's CUDA default behind forward_quant_float_storage) on 8-bit grids: h, v, all
+    saved codes and all eleven clamp masks equal the reference's own CUDA kernels bit for bit."""
+    cfg = ol.make_config(bits=8, symmetric=sym, use_pot2=pot2)
+    problem, params = calibrated(31 + T, T, B, I, H, cfg, with_h0)
+    want, want_masks = reference_forward_fp(problem, params, T, B, I, H)
+    rc_, got = gpu_lib.forward_quant(*problem, params, training=True, fp_carrier=True)
+    assert rc_ == 0, got
+    for k in ("W_q", "R_q", "bw_q", "br_q", "x_q"):
+        np.testing.assert_array_equal(got[k], want[k].cpu().numpy().astype(np.int32), err_msg=k)
+    for k in ("h", "v"):
+        np.testing.assert_array_equal(got[k], want[k].cpu().numpy(), err_msg=k)
+    for k, m in want_masks.items():
+        np.testing.assert_array_equal(got["masks"][k], m.cpu().numpy(), err_msg=f"mask {k}")
+    # the two carriers are different contracts: they need not agree with each other
+    rc_, integer = gpu_lib.forward_quant(*problem, params, training=True)
+    assert rc_ == 0
+    differing = float((integer["h_q"] != got["h_q"]).mean())
+    print(f"FP32 carrier against integer carrier: {100 * differing:.2f} % of the hidden codes differ")
