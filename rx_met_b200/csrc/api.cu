@@ -87,6 +87,55 @@ int residentPerSm(const void *kernel, int block, size_t smem) {
     return n;
 }
 
+OverlapLane &overlapLane() {
+    constexpr int kMaxDevices = 64;
+    static thread_local OverlapLane lanes[kMaxDevices];
+    const int device = currentDevice().device;
+    OverlapLane &lane = lanes[device];
+    if (lane.stream == nullptr) {
+        RXMET_CUDA(cudaStreamCreateWithFlags(&lane.stream, cudaStreamNonBlocking));
+        for (int i = 0; i < kLaneEvents; ++i) {
+            RXMET_CUDA(cudaEventCreateWithFlags(&lane.fork[i], cudaEventDisableTiming));
+            RXMET_CUDA(cudaEventCreateWithFlags(&lane.done[i], cudaEventDisableTiming));
+        }
+    }
+    return lane;
+}
+
+std::vector<int> overlapChunks(int T, size_t rows, bool backward) {
+    std::vector<int> percent;
+    if (const char *env = std::getenv(backward ? "RXMET_GRU_BWD_CHUNKS" : "RXMET_GRU_FWD_CHUNKS")) {
+        for (const char *p = env; *p;) {
+            char *end = nullptr;
+            const long v = std::strtol(p, &end, 10);
+            if (end == p) break;
+            if (v > 0) percent.push_back(static_cast<int>(v));
+            p = (*end == ',') ? end + 1 : end;
+            if (*end != ',') break;
+        }
+    }
+    // No cut by default: on a B200 at T = 100, B = 256, I = 40, H = 128 every cut measured slower than the
+    // single launches (the GEMM CTAs sharing the SMs slow the recurrence's serial chain by more than they hide).
+    (void)rows;
+    if (percent.size() < 2 || percent.size() > static_cast<size_t>(kLaneEvents)) return {T};
+    if (backward) {
+        // the backward runs the time axis downwards and its batched work FOLLOWS each chunk: the short chunk last
+        std::reverse(percent.begin(), percent.end());
+    }
+    int total = 0;
+    for (int v : percent) total += v;
+    std::vector<int> steps;
+    int used = 0;
+    for (size_t i = 0; i < percent.size(); ++i) {
+        int n = (i + 1 == percent.size()) ? T - used : static_cast<int>(static_cast<long long>(T) * percent[i] / total);
+        n = std::max(0, std::min(n, T - used));
+        if (n > 0) steps.push_back(n);
+        used += n;
+    }
+    if (steps.empty()) steps.push_back(T);
+    return steps;
+}
+
 void kernelTimingBegin(const char *, cudaStream_t stream, cudaEvent_t *start, cudaEvent_t *stop) {
     if (cudaEventCreate(start) != cudaSuccess || cudaEventCreate(stop) != cudaSuccess) {
         *start = *stop = nullptr;

@@ -4,12 +4,14 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "rxmet_b200.h"
 
@@ -101,6 +103,24 @@ const DeviceInfo &currentDevice();
 int concurrentPasses();
 // SMs one of those passes can count on.
 inline int smsPerPass() { return std::max(1, currentDevice().sms / concurrentPasses()); }
+// A second stream of this thread on the current device, for work the library runs beside a recurrence that
+// occupies the caller's stream, and the events that order the two.  Every user forks from the caller's stream
+// (record fork[i] there, make the lane wait for it) and joins back (record done[i] on the lane, make the caller's
+// stream wait for it) before it returns, so the pattern is legal inside a stream capture and the caller never
+// sees the lane.
+constexpr int kLaneEvents = 8;
+struct OverlapLane {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork[kLaneEvents] = {};
+    cudaEvent_t done[kLaneEvents] = {};
+};
+OverlapLane &overlapLane();
+// Time chunks, in processing order, that a forward (ascending time) or a backward (descending time) over T
+// steps is cut into so that the batched GEMM work of one chunk runs under the recurrence of its neighbour;
+// one chunk = no overlap.  RXMET_GRU_FWD_CHUNKS / RXMET_GRU_BWD_CHUNKS = "15,35,50" (per cent of the steps, in the
+// order of ascending time for the forward; the backward walks the mirror image, short chunk last) override the
+// default; a single number switches the cut off.
+std::vector<int> overlapChunks(int T, size_t rows, bool backward);
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when `bytes` exceeds what the kernel
 // was last given.
 void ensureDynamicSmem(const void *kernel, size_t bytes);

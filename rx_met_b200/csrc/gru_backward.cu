@@ -228,6 +228,11 @@ struct BackwardQArgs {
     float *dp, *dq, *dh0;
     const uint8_t *mIh, *mHh, *mGateIn, *mGateOut, *mH, *mH0;
     const uint16_t *stepBits;  // packed keep flags, see packStepMasks; null = nothing was clamped
+    // a sequence cut into time chunks (recurrentBackwardMma only): the gradient that flows into the chunk's last
+    // step from the later chunk, and whether dh0 receives this chunk's outgoing gradient as it is (1) or, at
+    // the start of the sequence, under the h0 mask (0)
+    const float *dhIn;
+    int carryOut;
 };
 
 struct StepOperands {
@@ -683,8 +688,9 @@ __global__ void __launch_bounds__(96 * HT) recurrentBackwardMma(const __grid_con
     StepOperands cur[kSlots], nxt[kSlots];
 #pragma unroll
     for (int s2 = 0; s2 < kSlots; ++s2) {
-        dhBase[s2] = 0.0f;
-        const int j = (tid + s2 * nthreads) % H;
+        const int e = tid + s2 * nthreads;
+        const int j = e % H;
+        dhBase[s2] = (a.dhIn != nullptr && e < elems) ? a.dhIn[static_cast<size_t>(b0 + e / H) * H + j] : 0.0f;
         scale[s2][0] = a.scaleR[j]; scale[s2][1] = a.scaleR[H + j]; scale[s2][2] = a.scaleR[2 * H + j];
     }
     auto fetch = [&](int t, StepOperands (&dst)[kSlots]) {
@@ -814,7 +820,8 @@ __global__ void __launch_bounds__(96 * HT) recurrentBackwardMma(const __grid_con
         if (e < elems) {
             const int b = e / H, j = e % H;
             const size_t o = static_cast<size_t>(b0 + b) * H + j;
-            a.dh0[o] = (dhBase[s2] + partS[0][b][j] + partS[1][b][j] + partS[2][b][j]) * keepOf(a.mH0, o);
+            const float carried = dhBase[s2] + partS[0][b][j] + partS[1][b][j] + partS[2][b][j];
+            a.dh0[o] = a.carryOut ? carried : carried * keepOf(a.mH0, o);
         }
     }
 }
@@ -1226,6 +1233,7 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<float>(static_cast<size_t>(std::max(wgrad::slabSplitBound(I, H, static_cast<int>(C)),
                                                 H <= 143 ? wgrad::splitBound(static_cast<int>(rows), H, static_cast<int>(C)) : 1)) * (H + 1) * C);
     ws.take<int>(64);
+    ws.take<float>(static_cast<size_t>(B) * H);   // gradient carried between time chunks
     ws.take<uint8_t>(igrad::widePackedBytes(static_cast<int>(C), I) + 256);   // weight operand of the streaming input-gradient kernel
     return ws.used() + 4096;
 }
@@ -1420,15 +1428,98 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
         q.mGateOut = mk.gate_output; q.mH = mk.h; q.mH0 = mk.h0;
         const size_t smem = sizeof(float) * (static_cast<size_t>(bt) * 3 * 2 * CW + 3 * static_cast<size_t>(bt) * H);
         const int grid = (B + bt - 1) / bt;
-        if (mmaPath) {
+        auto launchMma = [&](const BackwardQArgs &qa) {
             KernelTimer timer__("recurrentBackward", st);
 #define RXMET_BWD_CASE(HTV, BTV) \
-    if (H == 32 * HTV && bt == BTV) recurrentBackwardMma<HTV, BTV><<<grid, 96 * HTV, 0, st>>>(q, call.R_q);
+    if (H == 32 * HTV && bt == BTV) recurrentBackwardMma<HTV, BTV><<<grid, 96 * HTV, 0, st>>>(qa, call.R_q);
             RXMET_BWD_CASE(1, 1) RXMET_BWD_CASE(1, 2) RXMET_BWD_CASE(1, 4)
             RXMET_BWD_CASE(2, 1) RXMET_BWD_CASE(2, 2) RXMET_BWD_CASE(2, 4)
             RXMET_BWD_CASE(3, 1) RXMET_BWD_CASE(3, 2) RXMET_BWD_CASE(3, 4)
             RXMET_BWD_CASE(4, 1) RXMET_BWD_CASE(4, 2) RXMET_BWD_CASE(4, 4)
 #undef RXMET_BWD_CASE
+        };
+        // Time chunks, latest first: while the recurrence of chunk i + 1 occupies the caller's stream, the
+        // gradient GEMMs of chunk i (dx rows, dW / dR partial sums) run on the library's second stream; only the
+        // last (short) chunk's GEMMs and the reduction of the partial sums stay behind the recurrence.
+        std::vector<int> chunks{T};
+        if (mmaPath && tensorInputGrad && tensorGrads && (static_cast<size_t>(B) * I) % 8 == 0)
+            chunks = overlapChunks(T, rows, true);
+        std::vector<wgrad::Plan> plans;
+        int totalSplits = 0;
+        if (chunks.size() > 1) {
+            int share = 100;
+            if (const char *env = std::getenv("RXMET_GRU_CHUNK_SMS")) share = std::max(5, std::min(100, std::atoi(env)));
+            for (size_t i = 0; i < chunks.size(); ++i) {
+                const int K = chunks[i] * B;
+                const int use = (i + 1 == chunks.size()) ? sms : std::max(4, sms * share / 100);
+                const wgrad::Plan px = wgrad::plan(K, I, C, use), ph = wgrad::plan(K, H, C, use);
+                if (!px.tensorMemory || !ph.tensorMemory || px.splits != ph.splits || px.chunkK != ph.chunkK) { plans.clear(); break; }
+                plans.push_back(px);
+                totalSplits += px.splits;
+            }
+            const int bound = std::min(wgrad::splitBound(static_cast<int>(rows), I, C), wgrad::splitBound(static_cast<int>(rows), H, C));
+            if (plans.size() != chunks.size() || totalSplits > bound) chunks.assign(1, T);
+        }
+        if (chunks.size() > 1) {
+            const Exec &e = *call.exec;
+            OverlapLane &lane = overlapLane();
+            float *carry = ws.take<float>(static_cast<size_t>(B) * H);
+            int *status = ws.take<int>(1);
+            RXMET_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+            float *partialX = ws.take<float>(static_cast<size_t>(totalSplits) * (I + 1) * C);
+            float *partialH = ws.take<float>(static_cast<size_t>(totalSplits) * (H + 1) * C);
+            uint8_t *packedW = nullptr;
+            if (const size_t bytes = igrad::widePackedBytes(C, I)) packedW = ws.take<uint8_t>(bytes);
+            int tEnd = T, splitBase = 0;
+            for (size_t i = 0; i < chunks.size(); ++i) {
+                const int n = chunks[i], t0 = tEnd - n;
+                const size_t r0 = static_cast<size_t>(t0) * B;
+                const bool more = i + 1 < chunks.size();
+                BackwardQArgs qa = q;
+                qa.T = n;
+                qa.h = q.h + r0 * H; qa.v = q.v + r0 * 4 * H; qa.dhNew = q.dhNew + r0 * H;
+                qa.dp = dp + r0 * C; qa.dq = dq + r0 * C;
+                if (q.stepBits) qa.stepBits = q.stepBits + r0 * H;
+                qa.dhIn = i > 0 ? carry : nullptr;
+                qa.carryOut = more ? 1 : 0;
+                qa.dh0 = more ? carry : call.dh0;
+                launchMma(qa);
+                afterLaunch("recurrentBackwardMma");
+                RXMET_CUDA(cudaEventRecord(lane.fork[i], st));
+                RXMET_CUDA(cudaStreamWaitEvent(lane.stream, lane.fork[i], 0));
+                const int K = n * B;
+                igrad::Problem pg{};
+                pg.G = dp + r0 * C; pg.kScale = chanScaleW; pg.codesNK = call.W_q; pg.rows = K; pg.K = C; pg.N = I;
+                pg.mask = mk.x ? mk.x + r0 * I : nullptr; pg.maskKeeps = 1; pg.out = call.dx + r0 * I; pg.status = status;
+                pg.packed = packedW;
+                igrad::launch(pg, sms, lane.stream);
+                afterLaunch("inputGradUmma");
+                WeightGradProblem px{}, ph{};
+                px.aCodes = call.x_q + r0 * I; px.aZero = e.gate.zp[RXMET_GRU_X]; px.M = I; px.B = dp + r0 * C;
+                px.partial = partialX + static_cast<size_t>(splitBase) * (I + 1) * C;
+                ph.aFloat = call.h + r0 * H; ph.aInvScale = 1.0f / e.gate.eff[RXMET_GRU_H]; ph.M = H; ph.B = dq + r0 * C;
+                ph.partial = partialH + static_cast<size_t>(splitBase) * (H + 1) * C;
+                px.status = ph.status = status;
+                wgrad::launchPair(px, plans[i], ph, plans[i], K, C, lane.stream);
+                afterLaunch("weightGrad");
+                splitBase += plans[i].splits;
+                tEnd = t0;
+            }
+            RXMET_CUDA(cudaEventRecord(lane.done[0], lane.stream));
+            RXMET_CUDA(cudaStreamWaitEvent(st, lane.done[0], 0));
+            {
+                const ReduceJob jobX{partialX, totalSplits, I, e.gate.eff[RXMET_GRU_X], mk.W, mk.bw, call.dW, call.dbw};
+                const ReduceJob jobH{partialH, totalSplits, H, e.gate.eff[RXMET_GRU_H], mk.R, mk.br, call.dR, call.dbr};
+                const size_t largest = static_cast<size_t>(std::max(I, H) + 1) * C;
+                KernelTimer timer__("reduceWeightGrad", st);
+                reduceWeightGrad<<<dim3(static_cast<unsigned>((largest + kReduceWidth - 1) / kReduceWidth), 2),
+                                   dim3(kReduceWidth, kReduceLayers), 0, st>>>(jobX, jobH, C, status);
+            }
+            afterLaunch("reduceWeightGrad");
+            return;
+        }
+        if (mmaPath) {
+            launchMma(q);
         } else {
             KernelTimer timer__("recurrentBackward", st);
 #define RXMET_BWD_CASE(CWV, BTV) \

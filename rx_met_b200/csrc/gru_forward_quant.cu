@@ -471,6 +471,9 @@ struct RecurrentArgs {
     // 9..11 ih linear (read from maskIh, the input projection's flags); 12 hidden state
     uint16_t *stepBits;
     const uint8_t *maskIh;
+    // optional (recurrentForwardI8 only): the hidden codes after the last step, in the layout of h0, so that the
+    // next launch can carry on from there (a sequence cut into time chunks)
+    void *hFinal;
 };
 
 template <class WT, class AT, class LT, int BT>
@@ -837,6 +840,13 @@ recurrentForwardI8(const __grid_constant__ RecurrentArgs a, const __grid_constan
             for (int q3 = 0; q3 < 3; ++q3) ihKeepCur[s2][q3] = ihKeepNext[s2][q3];
         __syncthreads();
     }
+    if (a.hFinal != nullptr) {
+        int8_t *out = static_cast<int8_t *>(a.hFinal);
+        for (int i = tid; i < BT * kPadded; i += nthreads) {
+            const int b = i / kPadded, k = i % kPadded;
+            if (b < nb && k < srcPadded) out[static_cast<size_t>(b0 + b) * srcPadded + k] = hS[i];
+        }
+    }
 }
 
 size_t recurrentSmemBytes(int H, int kWords, int pack, size_t wordBytes, size_t actBytes, int BT, bool weights) {
@@ -1084,6 +1094,7 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
 
     // 3. input projection, all steps
     bool tensorProjection = false;
+    std::vector<int> chunks{T};   // time chunks of the overlapped pipeline (one = none)
     {
         const int block = std::min(padTo(C, 32), 512);
         const int kw4 = (iWords + 3) / 4;
@@ -1094,14 +1105,37 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                 specialised = true;
                 tensorProjection = true;
                 RXMET_CUDA(cudaMemsetAsync(projStatus, 0, sizeof(int), st));
-                iproj::Problem pj{};
-                pj.x = reinterpret_cast<const int32_t *>(xCodes); pj.rows = static_cast<int>(rows); pj.kWords = iWords;
-                pj.w = reinterpret_cast<const int32_t *>(wCodes); pj.C = C;
-                pj.comp = compX; pj.biasAcc = biasX; pj.rescale = ch.gemmX;
-                pj.zpOut = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR]; pj.lo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR];
-                pj.hi = g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR];
-                pj.pre = pre; pj.out = reinterpret_cast<int16_t *>(ihCodes); pj.mask = mk.weight_ih_linear; pj.status = projStatus;
-                iproj::launch(pj, sms, st);
+                // rows [r0, r0 + n) on stream `s`
+                auto projectRows = [&](size_t r0, size_t n, cudaStream_t s) {
+                    iproj::Problem pj{};
+                    pj.x = reinterpret_cast<const int32_t *>(xCodes) + r0 * iWords; pj.rows = static_cast<int>(n); pj.kWords = iWords;
+                    pj.w = reinterpret_cast<const int32_t *>(wCodes); pj.C = C;
+                    pj.comp = compX; pj.biasAcc = biasX; pj.rescale = ch.gemmX;
+                    pj.zpOut = g.zp[RXMET_GRU_WEIGHT_IH_LINEAR]; pj.lo = g.qlo[RXMET_GRU_WEIGHT_IH_LINEAR];
+                    pj.hi = g.qhi[RXMET_GRU_WEIGHT_IH_LINEAR];
+                    pj.pre = pre; pj.out = reinterpret_cast<int16_t *>(ihCodes) + r0 * C;
+                    pj.mask = mk.weight_ih_linear ? mk.weight_ih_linear + r0 * C : nullptr; pj.status = projStatus;
+                    iproj::launch(pj, sms, s);
+                };
+                // Cut into time chunks, the projection of chunk i + 1 runs on the library's second stream under the
+                // recurrence of chunk i; only the first (short) chunk's projection stays in front of the recurrence.
+                // Chunk borders must keep the 16-byte alignment of the operand rows.
+                if (registerPath && (static_cast<size_t>(B) * iPad) % 16 == 0 && (static_cast<size_t>(B) * C) % 16 == 0)
+                    chunks = overlapChunks(T, rows, false);
+                if (chunks.size() > 1) {
+                    OverlapLane &lane = overlapLane();
+                    projectRows(0, static_cast<size_t>(chunks[0]) * B, st);
+                    RXMET_CUDA(cudaEventRecord(lane.fork[0], st));
+                    RXMET_CUDA(cudaStreamWaitEvent(lane.stream, lane.fork[0], 0));
+                    int t0 = chunks[0];
+                    for (size_t i = 1; i < chunks.size(); ++i) {
+                        projectRows(static_cast<size_t>(t0) * B, static_cast<size_t>(chunks[i]) * B, lane.stream);
+                        RXMET_CUDA(cudaEventRecord(lane.done[i], lane.stream));
+                        t0 += chunks[i];
+                    }
+                } else {
+                    projectRows(0, rows, st);
+                }
             }
         }
         if constexpr (kI8) {
@@ -1178,24 +1212,53 @@ void runTyped(const ForwardQuantCall &call, const Exec &e, Workspace &ws, cudaSt
                 for (int op : {RXMET_GRU_UPDATE_GATE_INPUT, RXMET_GRU_RESET_GATE_INPUT, RXMET_GRU_NEW_GATE_INPUT})
                     smem += sizeof(int32_t) * (g.qhi[op] - g.qlo[op] + 1);
             }
-            auto launchI8 = [&](auto kernel) { kernel<<<(B + btI8 - 1) / btI8, blockI8, smem, st>>>(a, g); };
-            {
-                KernelTimer timer__("recurrentForward", st);
-                bool done = false;
+            auto launchSteps = [&](const RecurrentArgs &ra) {
+                auto launchI8 = [&](auto kernel) { kernel<<<(B + btI8 - 1) / btI8, blockI8, smem, st>>>(ra, g); };
+                {
+                    KernelTimer timer__("recurrentForward", st);
+                    bool done = false;
 #define RXMET_I8_CASE(KW, BT)                                                 \
     if (!done && hWords <= KW && btI8 == BT) {                                 \
-        if (mode == 2 && a.stepBits) launchI8(recurrentForwardI8<KW, BT, 2, true>); \
+        if (mode == 2 && ra.stepBits) launchI8(recurrentForwardI8<KW, BT, 2, true>); \
         else if (mode == 2) launchI8(recurrentForwardI8<KW, BT, 2>);           \
         else if (mode == 1) launchI8(recurrentForwardI8<KW, BT, 1>);           \
         else launchI8(recurrentForwardI8<KW, BT, 0>);                          \
         done = true;                                                           \
     }
-                RXMET_I8_CASE(16, 1) RXMET_I8_CASE(16, 2) RXMET_I8_CASE(16, 4)
-                RXMET_I8_CASE(32, 1) RXMET_I8_CASE(32, 2) RXMET_I8_CASE(32, 4)
-                RXMET_I8_CASE(64, 1) RXMET_I8_CASE(64, 2) RXMET_I8_CASE(64, 4)
+                    RXMET_I8_CASE(16, 1) RXMET_I8_CASE(16, 2) RXMET_I8_CASE(16, 4)
+                    RXMET_I8_CASE(32, 1) RXMET_I8_CASE(32, 2) RXMET_I8_CASE(32, 4)
+                    RXMET_I8_CASE(64, 1) RXMET_I8_CASE(64, 2) RXMET_I8_CASE(64, 4)
 #undef RXMET_I8_CASE
+                }
+                afterLaunch("recurrentForwardI8");
+            };
+            if (chunks.size() == 1) {
+                launchSteps(a);
+                return;
             }
-            afterLaunch("recurrentForwardI8");
+            // one launch per time chunk: the hidden codes travel from launch to launch in the h0 buffer, every other
+            // operand is the whole-sequence array moved to the chunk's first step
+            OverlapLane &lane = overlapLane();
+            int t0 = 0;
+            for (size_t i = 0; i < chunks.size(); ++i) {
+                if (i > 0) RXMET_CUDA(cudaStreamWaitEvent(st, lane.done[i], 0));
+                const size_t r0 = static_cast<size_t>(t0) * B;
+                RecurrentArgs ra = a;
+                ra.T = chunks[i];
+                ra.hFinal = (i + 1 < chunks.size()) ? h0Codes : nullptr;
+                ra.ih = reinterpret_cast<const int16_t *>(ihCodes) + r0 * C;
+                ra.h = a.h + r0 * H; ra.v = a.v + r0 * 4 * H;
+                if (a.hq) ra.hq = a.hq + r0 * H;
+                if (a.vq) ra.vq = a.vq + r0 * 4 * H;
+                if (a.maskHh) ra.maskHh = a.maskHh + r0 * C;
+                if (a.maskGateIn) ra.maskGateIn = a.maskGateIn + r0 * C;
+                if (a.maskGateOut) ra.maskGateOut = a.maskGateOut + r0 * C;
+                if (a.maskH) ra.maskH = a.maskH + r0 * H;
+                if (a.stepBits) ra.stepBits = a.stepBits + r0 * H;
+                if (a.maskIh) ra.maskIh = a.maskIh + r0 * C;
+                launchSteps(ra);
+                t0 += chunks[i];
+            }
             return;
         }
     }

@@ -534,6 +534,66 @@ def test_packed_step_flags_equal_the_byte_masks(monkeypatch, shape):
     assert torch.equal(packed.flat_w, plain.flat_w) and torch.equal(lp, lb)
 
 
+@pytest.mark.parametrize("byte_masks", [False, True], ids=["packed", "bytes"])
+def test_time_chunked_step_equals_the_single_launch_step(monkeypatch, byte_masks):
+    """The overlapped pipeline cuts the sequence into time chunks (projection / gradient GEMMs of one chunk under the
+    recurrence of its neighbour).  Codes, h, v, flags, dx and dh0 are bit-identical to the one-launch path; the
+    weight gradients sum the same products in another order (1e-5); a graph of the chunked step replays it."""
+    import torch
+    from rx_met_b200 import gru_interface_binding as ops
+    from rx_met_b200.qat import GruQatStep
+    lib = cabi.load_library()
+    T, B, I, H = 24, 64, 40, 128
+    dev = torch.device("cuda", 0)
+    cfg = ops.OperatorQuantConfig()
+    for name in cabi.OP_NAMES:
+        if name not in ("W", "R", "bw", "br"):
+            setattr(cfg, f"{name}_symmetric_", False)
+    if byte_masks:
+        monkeypatch.setenv("RXMET_QAT_BYTE_MASKS", "1")
+    gen = torch.Generator().manual_seed(23)
+    x = torch.randn((T, B, I), generator=gen).to(dev)
+    y = torch.randn((T, B, H), generator=gen).to(dev)
+
+    def run(chunks):
+        monkeypatch.setenv("RXMET_GRU_FWD_CHUNKS", chunks)
+        monkeypatch.setenv("RXMET_GRU_BWD_CHUNKS", chunks)
+        eng = GruQatStep(T, B, I, H, dev, cfg, seed=9)
+        eng.calibrate([x * 0.7])
+        before = lib.rxmet_kernel_launch_count()
+        eng.forward(x)
+        middle = lib.rxmet_kernel_launch_count()
+        eng.mse_loss(y)
+        eng.backward()
+        torch.cuda.synchronize()
+        return eng, (middle - before, lib.rxmet_kernel_launch_count() - middle)
+
+    one, launches_one = run("100")
+    cut, launches_cut = run("20,30,50")
+    assert launches_cut[0] > launches_one[0], "the chunked forward did not run"
+    assert launches_cut[1] > launches_one[1], "the chunked backward did not run"
+    assert torch.equal(one.h, cut.h) and torch.equal(one.v, cut.v)
+    if byte_masks:
+        for k in one.masks:
+            assert torch.equal(one.masks[k], cut.masks[k]), k
+    else:
+        assert torch.equal(one.step_flags, cut.step_flags)
+    assert torch.equal(one.dx, cut.dx) and torch.equal(one.dh0, cut.dh0)
+    scale = float(one.flat_g.abs().max())
+    assert float((one.flat_g - cut.flat_g).abs().max()) <= 1e-5 * scale
+    # the chunked step inside a captured graph
+    eager = [float(cut.step(x, y, 1e-2)) for _ in range(3)]
+    graphed = GruQatStep(T, B, I, H, dev, cfg, seed=9)
+    graphed.calibrate([x * 0.7])
+    replay, loss = graphed.capture_step(x, y, 1e-2, warmup=1)   # one eager step, then the capture
+    got = []
+    for _ in range(2):
+        replay()
+        got.append(float(loss))
+    assert got == eager[1:]
+    assert torch.equal(graphed.flat_w, cut.flat_w)
+
+
 def test_fused_mse_loss_and_gradient():
     """The step's loss kernel: gradient bit-identical to the eager float32 expressions, loss within 1e-6 relative."""
     import torch
