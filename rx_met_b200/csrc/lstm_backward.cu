@@ -21,6 +21,7 @@
 #include "common.h"
 #include "input_grad_umma.h"
 #include "lstm_kernels.h"
+#include "umma_device.cuh"
 #include "weight_grad_mma.h"
 
 namespace rxmet {
@@ -515,6 +516,288 @@ __global__ void __launch_bounds__(128 * HT) recurrentBackwardMma(const __grid_co
     }
 }
 
+// ---- hidden sizes above 128 on the tcgen05 tensor cores (QAT with weight grids of at most 8 bits) ---------
+//
+// dh[b][j] = sum_c G_hh[b][c] * code[c][j] * scale[c] needs every channel of a row for every hidden unit, and
+// weight_hh (4H x H) fits no single SM.  The contraction is therefore split over the CTAs of a row tile:
+//   * CTA (row tile of 128 batch rows, unit tile of 32 hidden units) owns the pointwise derivative of its
+//     128 x 32 elements - which yields exactly the 128 channels (4 gates x 32 units) of G_hh that form ITS
+//     K slice - and keeps rows [its 128 channels] x [all H units] of the weight codes in shared memory as an
+//     exact bf16 operand (K-major canonical layout, loaded once);
+//   * per step it writes the slice of G_hh, multiplied by the channel scale and split into three bf16 terms
+//     (products exact, only the fp32 accumulation rounds), straight into the A operand tiles in shared memory
+//     (nothing is exchanged for the product), one thread issues 3 x 8 MMAs (M 128, N H or 2 x H/2, K 16) per
+//     accumulator half into tensor memory, and all warps move the [128][H] partial sums to a global array;
+//   * the CTAs of a row tile then meet at a counter (cooperative launch, bounded polling) and the next step's
+//     pointwise stage adds the H/32 partial sums of its elements in a fixed order (bit-reproducible).
+// dc never leaves the registers of the thread that owns the element.  A wait that runs out sets the status
+// word, ends all further waiting of the CTA and turns its dh0 into NaN.
+constexpr int kBwdUnits = 32, kBwdRows = 128, kBwdSlice = 4 * kBwdUnits;
+constexpr int kBwdSpinLimit = 1 << 22;
+constexpr uint32_t kBwdSplitBytes = kBwdRows * kBwdSlice * 2;   // one bf16 term of the A operand
+
+struct RecurrentUmmaArgs {
+    RecurrentArgs base;
+    const uint4 *tiles;          // [H / 32] weight tiles: [H / 8][16][8 units][8 channels] bf16
+    const float *channelScale;   // [4H] scale of weight_hh per channel
+    float *partial;              // [2][rowTiles][H / 32][128][H]
+    unsigned int *counters;      // [rowTiles], zero at launch
+    int *status;                 // set to 1 when a bounded wait gave up
+    int rowBase, rowTiles;       // this launch covers batch rows [rowBase, rowBase + 128 * rowTiles)
+};
+
+__global__ void packBackwardTiles(const float *__restrict__ codes, int H, uint4 *__restrict__ tiles) {
+    const size_t total = static_cast<size_t>(H / kBwdUnits) * 16 * H;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int n = static_cast<int>(i % H), kg = static_cast<int>((i / H) % 16), ut = static_cast<int>(i / (static_cast<size_t>(16) * H));
+        const int c0 = (kg / 4) * H + ut * kBwdUnits + (kg % 4) * 8;   // first of eight consecutive channels of one gate
+        uint32_t v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            v[e] = umma::packBf16(codes[static_cast<size_t>(c0 + 2 * e) * H + n], codes[static_cast<size_t>(c0 + 2 * e + 1) * H + n]);
+        tiles[static_cast<size_t>(ut) * (static_cast<size_t>(H) * 16) + static_cast<size_t>(n / 8) * 128 + kg * 8 + n % 8] =
+            make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+__global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_constant__ RecurrentUmmaArgs args) {
+    const RecurrentArgs &a = args.base;
+    extern __shared__ __align__(128) uint8_t smemBwd[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmemSlot;
+    __shared__ int failed;
+    __shared__ __align__(16) float scaleS[kBwdSlice];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = a.H, C = 4 * H;
+    const int tilesPerRow = H / kBwdUnits;
+    const int ut = blockIdx.x % tilesPerRow, rt = blockIdx.x / tilesPerRow;
+    const int halves = H > 256 ? 2 : 1, nHalf = H / halves;
+    const uint32_t tmemCols = H > 256 ? 512u : (H > 128 ? 256u : 128u);
+    uint8_t *wTile = smemBwd;                                   // H x 128 bf16
+    uint8_t *gTiles = smemBwd + static_cast<size_t>(H) * 256;   // 3 x [128 rows][128 channels] bf16
+    volatile int *failFlag = &failed;
+
+    if (tid == 0) {
+        failed = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smemAddr(&bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(umma::smemAddr(&tmemSlot)), "r"(tmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    {
+        const uint4 *src = args.tiles + static_cast<size_t>(ut) * (static_cast<size_t>(H) * 16);
+        for (int i = tid; i < H * 16; i += blockDim.x) reinterpret_cast<uint4 *>(wTile)[i] = __ldg(src + i);
+        for (uint32_t i = tid; i < 3 * kBwdSplitBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(gTiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (tid < kBwdSlice) scaleS[tid] = args.channelScale[(tid / kBwdUnits) * H + ut * kBwdUnits + tid % kBwdUnits];
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmemSlot;
+
+    // pointwise role: warp = four neighbouring batch rows (twice: rows 4 warp + {0, 64}), eight lanes per row, four
+    // neighbouring units per lane, so that a warp's 16-byte loads cover whole 128-byte lines
+    const int rowInPass = warp * 4 + (lane >> 3), j0 = ut * kBwdUnits + (lane & 7) * 4;
+    const int ug = (lane & 7) >> 1, sub = lane & 1;   // eight-channel group of a gate, and which half of it
+    int bRow[2];
+    bool valid[2];
+    size_t stateIdx[2];
+    uint32_t aRowOffset[2];
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+        const int r = ps * 64 + rowInPass;
+        bRow[ps] = args.rowBase + rt * kBwdRows + r;
+        valid[ps] = bRow[ps] < a.B;
+        stateIdx[ps] = static_cast<size_t>(valid[ps] ? bRow[ps] : 0) * H + j0;
+        aRowOffset[ps] = static_cast<uint32_t>(r / 8) * 2048u + static_cast<uint32_t>(r % 8) * 16u;
+    }
+    // epilogue role: tensor-memory lanes 32 * (warp % 4) .. + 31, columns [colBegin, colBegin + H / 4)
+    const int quarter = warp & 3, colBegin = (warp >> 2) * (H / 4);
+    const size_t partialTile = static_cast<size_t>(kBwdRows) * H;                 // floats of one CTA's partial sums
+    const size_t partialStep = static_cast<size_t>(args.rowTiles) * tilesPerRow * partialTile;
+    const uint32_t idesc = umma::instructionDescriptor(nHalf, false, false);
+    uint64_t descA[3], descB[2];
+#pragma unroll
+    for (int sp = 0; sp < 3; ++sp) descA[sp] = umma::operandDescriptor(umma::smemAddr(gTiles) + sp * kBwdSplitBytes, umma::kCore, 2048u);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) descB[hf] = umma::operandDescriptor(umma::smemAddr(wTile) + static_cast<uint32_t>(hf * (nHalf / 8)) * 2048u, umma::kCore, 2048u);
+
+    float dc[8];
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+        const float4 v = valid[ps] ? *reinterpret_cast<const float4 *>(a.gradFinalCell + stateIdx[ps]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        dc[4 * ps] = v.x; dc[4 * ps + 1] = v.y; dc[4 * ps + 2] = v.z; dc[4 * ps + 3] = v.w;
+    }
+    // the carried gradient of four units: the final-state gradient before the last step, afterwards the sum of
+    // the row tile's partial products of the step above
+    auto carried = [&](int t, int ps) -> float4 {
+        if (t == a.T - 1) return *reinterpret_cast<const float4 *>(a.gradFinalHidden + stateIdx[ps]);
+        const float *p = args.partial + static_cast<size_t>((t + 1) & 1) * partialStep + static_cast<size_t>(rt) * tilesPerRow * partialTile +
+                         static_cast<size_t>(ps * 64 + rowInPass) * H + j0;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s2 = 0; s2 < tilesPerRow; ++s2) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(p + static_cast<size_t>(s2) * partialTile));
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        return sum;
+    };
+    auto groupBarrier = [&](int stepsDone) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            atomicAdd(args.counters + rt, 1u);
+            const unsigned int want = static_cast<unsigned int>(tilesPerRow) * stepsDone;
+            bool arrived = *failFlag != 0;
+            for (int spin = 0; !arrived && spin < kBwdSpinLimit; ++spin) {
+                unsigned int seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(args.counters + rt) : "memory");
+                arrived = seen >= want;
+            }
+            if (!arrived) *failFlag = 1;
+        }
+        __syncthreads();
+        __threadfence();
+    };
+
+    uint32_t parity = 0;
+    int stepsDone = 0;
+    for (int t = a.T - 1; t >= 0; --t) {
+        // ---- pointwise derivative of this thread's eight elements, four at a time
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) {
+            if (valid[ps]) {
+                const size_t row = static_cast<size_t>(t) * a.B + bRow[ps];
+                const size_t so = row * H + j0, go = row * C + j0;
+                const float4 dhIn = carried(t, ps);
+                const uint4 bits4 = a.stepMasks ? *reinterpret_cast<const uint4 *>(a.stepMasks + so) : make_uint4(0u, 0u, 0u, 0u);
+                const float4 gi = *reinterpret_cast<const float4 *>(a.gateOutputs + go);
+                const float4 gf = *reinterpret_cast<const float4 *>(a.gateOutputs + go + static_cast<size_t>(H));
+                const float4 gc = *reinterpret_cast<const float4 *>(a.gateOutputs + go + 2 * static_cast<size_t>(H));
+                const float4 gq = *reinterpret_cast<const float4 *>(a.gateOutputs + go + 3 * static_cast<size_t>(H));
+                const float4 ct4 = *reinterpret_cast<const float4 *>(a.cellTanh + so);
+                const float4 gradOut = *reinterpret_cast<const float4 *>(a.gradOutput + so);
+                float4 cp4;
+                if (t > 0) cp4 = *reinterpret_cast<const float4 *>(a.cellStates + so - static_cast<size_t>(a.B) * H);
+                else if (a.c0) cp4 = *reinterpret_cast<const float4 *>(a.c0 + stateIdx[ps]);
+                else cp4 = make_float4(a.dqC.zeroPoint, a.dqC.zeroPoint, a.dqC.zeroPoint, a.dqC.zeroPoint);
+                const float dhv[4] = {dhIn.x, dhIn.y, dhIn.z, dhIn.w};
+                const uint32_t bitv[4] = {bits4.x, bits4.y, bits4.z, bits4.w};
+                const float igv[4] = {gi.x, gi.y, gi.z, gi.w}, fgv[4] = {gf.x, gf.y, gf.z, gf.w};
+                const float cgv[4] = {gc.x, gc.y, gc.z, gc.w}, ogv[4] = {gq.x, gq.y, gq.z, gq.w};
+                const float ctv[4] = {ct4.x, ct4.y, ct4.z, ct4.w}, gov[4] = {gradOut.x, gradOut.y, gradOut.z, gradOut.w};
+                const float cpv[4] = {cp4.x, cp4.y, cp4.z, cp4.w};
+                float outIh[4][4], outHh[4][4];   // [gate][unit]
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t bits = bitv[e];
+                    auto keepBit = [&](int bit) { return (bits >> bit) & 1u ? 0.0f : 1.0f; };
+                    const float ig = realOf(igv[e], a.dqGate[0]), fg = realOf(fgv[e], a.dqGate[1]);
+                    const float cg = realOf(cgv[e], a.dqGate[2]), og = realOf(ogv[e], a.dqGate[3]);
+                    const float ct = realOf(ctv[e], a.dqTanh), cPrev = realOf(cpv[e], a.dqC);
+                    const float dh = (dhv[e] + gov[e]) * keepBit(0);
+                    const float gOut = dh * ct;
+                    const float gTanh = dh * og * keepBit(1);
+                    const float dcAll = dc[4 * ps + e] + gTanh * (1.0f - ct * ct);
+                    const float mdc = dcAll * keepBit(2);
+                    const float go4[4] = {mdc * cg * keepBit(3), mdc * cPrev * keepBit(4), mdc * ig * keepBit(5), gOut * keepBit(6)};
+                    const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
+                                          go4[3] * og * (1.0f - og)};
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float grad = gi4[g] * keepBit(7 + g);
+                        outIh[g][e] = grad * keepBit(11 + g);
+                        outHh[g][e] = grad * keepBit(15 + g);
+                    }
+                    dc[4 * ps + e] = mdc * fg;
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const size_t o = go + static_cast<size_t>(g) * H;
+                    *reinterpret_cast<float4 *>(a.gIh + o) = make_float4(outIh[g][0], outIh[g][1], outIh[g][2], outIh[g][3]);
+                    *reinterpret_cast<float4 *>(a.gHh + o) = make_float4(outHh[g][0], outHh[g][1], outHh[g][2], outHh[g][3]);
+                    // scaled by the channel's weight scale and split into three bf16 terms: channels g*32 + 4*(lane%8) ..
+                    const float4 sc = *reinterpret_cast<const float4 *>(scaleS + g * kBwdUnits + (lane & 7) * 4);
+                    const float v[4] = {outHh[g][0] * sc.x, outHh[g][1] * sc.y, outHh[g][2] * sc.z, outHh[g][3] * sc.w};
+                    uint32_t hi2[2], mid2[2], lo2[2];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        hi2[i] = packBf16(v[2 * i], v[2 * i + 1]);
+                        const float r0 = v[2 * i] - bf16Lo(hi2[i]), r1 = v[2 * i + 1] - umma::bf16Hi(hi2[i]);
+                        mid2[i] = packBf16(r0, r1);
+                        lo2[i] = packBf16(r0 - bf16Lo(mid2[i]), r1 - umma::bf16Hi(mid2[i]));
+                    }
+                    uint8_t *dst = gTiles + aRowOffset[ps] + static_cast<uint32_t>(g * 4 + ug) * umma::kCore + 8u * sub;
+                    *reinterpret_cast<uint2 *>(dst) = make_uint2(hi2[0], hi2[1]);
+                    *reinterpret_cast<uint2 *>(dst + kBwdSplitBytes) = make_uint2(mid2[0], mid2[1]);
+                    *reinterpret_cast<uint2 *>(dst + 2 * kBwdSplitBytes) = make_uint2(lo2[0], lo2[1]);
+                }
+            }
+        }
+        // ---- dh partial sums of this K slice: [128 rows][H units] into tensor memory
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 0) {   // lane 0 issues; its siblings wait here instead of polling the barrier beside it
+          if (lane == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int hf = 0; hf < halves; ++hf)
+#pragma unroll
+                for (int sp = 0; sp < 3; ++sp)
+#pragma unroll
+                    for (int ks = 0; ks < kBwdSlice / 16; ++ks)
+                        umma::mmaBf16(tmem + static_cast<uint32_t>(hf * nHalf), descA[sp] + static_cast<uint64_t>(ks) * 16u,
+                                descB[hf] + static_cast<uint64_t>(ks) * 16u, idesc, (sp | ks) ? 1u : 0u);
+            umma::commitTo(umma::smemAddr(&bar));
+          }
+          __syncwarp();
+        }
+        if (!*failFlag && !umma::waitPhase(umma::smemAddr(&bar), parity)) *failFlag = 1;
+        parity ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
+            float *dst = args.partial + static_cast<size_t>(t & 1) * partialStep +
+                         (static_cast<size_t>(rt) * tilesPerRow + ut) * partialTile + static_cast<size_t>(quarter * 32 + lane) * H;
+            for (int c = colBegin; c < colBegin + H / 4; c += 32) {
+                uint32_t v[32];
+                umma::tmemLoad32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c), v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)   // 32-byte stores: whole sectors
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + c + 8 * i), "r"(v[8 * i]),
+                                 "r"(v[8 * i + 1]), "r"(v[8 * i + 2]), "r"(v[8 * i + 3]), "r"(v[8 * i + 4]), "r"(v[8 * i + 5]),
+                                 "r"(v[8 * i + 6]), "r"(v[8 * i + 7])
+                                 : "memory");
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        // ---- publish the step and wait for the other K slices of this row tile
+        ++stepsDone;
+        groupBarrier(stepsDone);
+    }
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+        if (!valid[ps]) continue;
+        const float nan = __int_as_float(0x7fc00000);
+        const float4 dh0 = *failFlag ? make_float4(nan, nan, nan, nan) : carried(-1, ps);
+        const float out[4] = {dh0.x, dh0.y, dh0.z, dh0.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const size_t o = stateIdx[ps] + e;
+            a.dh0[o] = out[e] * keepOf(a.mk.initial_hidden, o);
+            a.dc0[o] = dc[4 * ps + e] * keepOf(a.mk.initial_cell, o);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmemCols) : "memory");
+    if (tid == 0 && failed && args.status) atomicExch(args.status, 1);
+}
+
 // Rows of a [rows, cols] operand that switches source after `split` rows (h_prev = [h0 ; hidden[0..T-2]]).
 struct RowSource {
     const float *first;  // rows [0, split) ; null = zeros
@@ -745,6 +1028,14 @@ constexpr int kMaxTensorSplits = 40;
 
 }  // namespace
 
+// The tcgen05 recurrence of wide layers takes hidden sizes whose accumulator quarters are whole 32-column pieces.
+bool wideTensorShape(int H) { return H > 128 && H <= 512 && H % 128 == 0; }
+// Row tiles (128 batch rows) one cooperative launch holds: every CTA must be resident, one per SM.
+int wideTensorRowTiles(int B, int H) {
+    const int tilesPerRow = H / kBwdUnits;
+    return std::max(1, std::min((B + kBwdRows - 1) / kBwdRows, std::max(1, 148 / tilesPerRow)));
+}
+
 // Splits of the tensor-core weight-gradient partial arrays: the one-tile plan for at most 128 rows, the slab plan
 // (128-row slabs of both problems in one launch) beyond.
 int tensorSplitBound(int rows, int I, int H, int M, int C) {
@@ -769,6 +1060,11 @@ size_t backwardWorkspaceBytes(int T, int B, int I, int H) {
     ws.take<int>(1);              // status word of the tensor-memory weight-gradient kernel
     ws.take<uint32_t>(rows * H);  // packed per-step clamp flags
     ws.take<uint8_t>(igrad::widePackedBytes(static_cast<int>(C), I) + 256);   // weight operand of the streaming input-gradient kernel
+    if (wideTensorShape(H)) {   // tensor-core recurrence of wide layers: weight tiles, partial sums, counters
+        ws.take<uint4>(C * H / 8);
+        ws.take<float>(2 * static_cast<size_t>(wideTensorRowTiles(B, H)) * (H / kBwdUnits) * kBwdRows * H);
+        ws.take<unsigned int>(256);
+    }
     return ws.used() + 1024;
 }
 
@@ -798,6 +1094,23 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     // others read real-valued weights rebuilt here.
     const bool tensorPath = !wide && call.quantized && call.weightCodesFitBf16 && H % 32 == 0 && H <= 128 &&
                             std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
+    // Wide layers: the tcgen05 recurrence (float4 loads of the saved tensors and of the incoming gradients)
+    uint4 *wideTiles = nullptr;
+    float *widePartial = nullptr;
+    unsigned int *wideCounters = nullptr;
+    if (wideTensorShape(H)) {
+        wideTiles = ws.take<uint4>(static_cast<size_t>(C) * H / 8);
+        widePartial = ws.take<float>(2 * static_cast<size_t>(wideTensorRowTiles(B, H)) * (H / kBwdUnits) * kBwdRows * H);
+        wideCounters = ws.take<unsigned int>(256);
+    }
+    const size_t wideSmem = static_cast<size_t>(H) * 256 + 3 * kBwdSplitBytes;
+    int cooperative = 0;
+    RXMET_CUDA(cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, currentDevice().device));
+    const bool wideTensor = wide && wideTensorShape(H) && call.quantized && call.weightCodesFitBf16 && cooperative != 0 &&
+                            H / kBwdUnits <= smsPerPass() && wideSmem <= static_cast<size_t>(currentDevice().smemMax) &&
+                            alignedTo(call.gateOutputs, 16) && alignedTo(call.cellStates, 16) && alignedTo(call.cellTanhOutputs, 16) &&
+                            alignedTo(call.gradOutput, 16) && alignedTo(call.gradFinalHidden, 16) && alignedTo(call.gradFinalCell, 16) &&
+                            alignedTo(call.c0, 16) && std::getenv("RXMET_LSTM_BWD_SIMT") == nullptr;
     // 16-byte copies of the caller's weight codes, float4 stores of dx and 8-byte loads of the input mask
     const bool tensorInputGrad = call.quantized && call.weightIhCodesFitBf16 && igrad::eligible(C, I) &&
                                  alignedTo(call.grads.input, 16) && alignedTo(call.weightIh, 16) &&
@@ -812,7 +1125,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             dequantWeights<<<gridFor(static_cast<size_t>(C) * I, 256), 256, 0, st>>>(call.weightIh, channelScales, C, I, wIhReal);
             afterLaunch("lstmDequantWeights");
         }
-        if (!tensorPath) {
+        if (!tensorPath && !wideTensor) {
             KernelTimer timer__("lstmDequantWeights", st);
             dequantWeights<<<gridFor(static_cast<size_t>(C) * H, 256), 256, 0, st>>>(call.weightHh, channelScales + C, C, H, wHhReal);
             afterLaunch("lstmDequantWeights");
@@ -869,7 +1182,31 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
 #undef RXMET_LSTM_MMA
             afterLaunch("lstmRecurrentBackwardMma");
         }
-        if (wide) {
+        if (wideTensor) {
+            {
+                KernelTimer timer__("lstmPackBackwardTiles", st);
+                packBackwardTiles<<<gridFor(static_cast<size_t>(H / kBwdUnits) * 16 * H, 256), 256, 0, st>>>(call.weightHh, H, wideTiles);
+            }
+            afterLaunch("lstmPackBackwardTiles");
+            const int tilesPerRow = H / kBwdUnits;
+            const int rowTilesAll = (B + kBwdRows - 1) / kBwdRows;
+            const int perLaunch = std::max(1, std::min(wideTensorRowTiles(B, H), smsPerPass() / tilesPerRow));
+            ensureDynamicSmem(reinterpret_cast<const void *>(recurrentBackwardUmma), wideSmem);
+            RXMET_CUDA(cudaMemsetAsync(wideCounters + 255, 0, sizeof(unsigned int), st));
+            for (int first = 0; first < rowTilesAll; first += perLaunch) {
+                RecurrentUmmaArgs u{};
+                u.base = a;
+                u.tiles = wideTiles; u.channelScale = channelScales + C; u.partial = widePartial;
+                u.counters = wideCounters; u.status = reinterpret_cast<int *>(wideCounters + 255);
+                u.rowBase = first * kBwdRows; u.rowTiles = std::min(perLaunch, rowTilesAll - first);
+                RXMET_CUDA(cudaMemsetAsync(wideCounters, 0, sizeof(unsigned int) * 255, st));
+                void *params[] = {&u};
+                KernelTimer timer__("lstmRecurrentBackwardWide", st);
+                RXMET_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(recurrentBackwardUmma), dim3(u.rowTiles * tilesPerRow),
+                                                       dim3(512), params, wideSmem, st));
+            }
+            afterLaunch("lstmRecurrentBackwardUmma");
+        } else if (wide) {
             const int HP = (H + 31) / 32 * 32;
             const int groupsMax = std::max(1, 512 / HP);
             const int want = std::max(1, (B + smsPerPass() - 1) / smsPerPass());
