@@ -28,6 +28,7 @@ namespace rxmet {
 namespace lstm {
 namespace {
 
+__device__ __forceinline__ void prefetchL2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float keepOf(const uint8_t *mask, size_t i) { return (mask == nullptr || mask[i] == 0) ? 1.0f : 0.0f; }
 __device__ __forceinline__ float realOf(float v, Dequant d) { return (v - d.zeroPoint) * d.scale; }
 
@@ -543,7 +544,8 @@ struct RecurrentUmmaArgs {
     float *partial;              // [2][rowTiles][H / 32][128][H]
     unsigned int *counters;      // [rowTiles], zero at launch
     int *status;                 // set to 1 when a bounded wait gave up
-    int rowBase, rowTiles;       // this launch covers batch rows [rowBase, rowBase + 128 * rowTiles)
+    int rowBase, rowTiles;       // this launch covers batch rows [rowBase, rowBase + tileRows * rowTiles)
+    int tileRows;                // batch rows of a row tile: 32, 64 or 128 (the accumulator tile always has 128 rows)
 };
 
 __global__ void packBackwardTiles(const float *__restrict__ codes, int H, uint4 *__restrict__ tiles) {
@@ -572,10 +574,15 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
     const int H = a.H, C = 4 * H;
     const int tilesPerRow = H / kBwdUnits;
     const int ut = blockIdx.x % tilesPerRow, rt = blockIdx.x / tilesPerRow;
-    const int halves = H > 256 ? 2 : 1, nHalf = H / halves;
-    const uint32_t tmemCols = H > 256 ? 512u : (H > 128 ? 256u : 128u);
+    // The product runs transposed: M = 128 hidden units per accumulator tile (weights as the A operand), N = the row
+    // tile's batch rows (gate gradients as the B operand).  A row tile of 32 batch rows then costs an eighth of the
+    // tensor time of 128-row accumulators, and an accumulator lane holds ONE unit's sums for neighbouring batch
+    // rows, so that a warp's stores of a batch row are 128 contiguous bytes.
+    const int unitTiles = H / 128, N = args.tileRows;
+    uint32_t tmemCols = 32;
+    while (tmemCols < static_cast<uint32_t>(unitTiles * N)) tmemCols *= 2;
     uint8_t *wTile = smemBwd;                                   // H x 128 bf16
-    uint8_t *gTiles = smemBwd + static_cast<size_t>(H) * 256;   // 3 x [128 rows][128 channels] bf16
+    uint8_t *gTiles = smemBwd + static_cast<size_t>(H) * 256;   // 3 x [128 batch rows][128 channels] bf16 (the first N rows are used)
     volatile int *failFlag = &failed;
 
     if (tid == 0) {
@@ -591,7 +598,6 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
     {
         const uint4 *src = args.tiles + static_cast<size_t>(ut) * (static_cast<size_t>(H) * 16);
         for (int i = tid; i < H * 16; i += blockDim.x) reinterpret_cast<uint4 *>(wTile)[i] = __ldg(src + i);
-        for (uint32_t i = tid; i < 3 * kBwdSplitBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(gTiles)[i] = make_uint4(0u, 0u, 0u, 0u);
         if (tid < kBwdSlice) scaleS[tid] = args.channelScale[(tid / kBwdUnits) * H + ut * kBwdUnits + tid % kBwdUnits];
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -604,41 +610,48 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
     // neighbouring units per lane, so that a warp's 16-byte loads cover whole 128-byte lines
     const int rowInPass = warp * 4 + (lane >> 3), j0 = ut * kBwdUnits + (lane & 7) * 4;
     const int ug = (lane & 7) >> 1, sub = lane & 1;   // eight-channel group of a gate, and which half of it
-    int bRow[2];
-    bool valid[2];
-    size_t stateIdx[2];
-    uint32_t aRowOffset[2];
-#pragma unroll
-    for (int ps = 0; ps < 2; ++ps) {
-        const int r = ps * 64 + rowInPass;
-        bRow[ps] = args.rowBase + rt * kBwdRows + r;
-        valid[ps] = bRow[ps] < a.B;
-        stateIdx[ps] = static_cast<size_t>(valid[ps] ? bRow[ps] : 0) * H + j0;
-        aRowOffset[ps] = static_cast<uint32_t>(r / 8) * 2048u + static_cast<uint32_t>(r % 8) * 16u;
-    }
-    // epilogue role: tensor-memory lanes 32 * (warp % 4) .. + 31, columns [colBegin, colBegin + H / 4)
-    const int quarter = warp & 3, colBegin = (warp >> 2) * (H / 4);
-    const size_t partialTile = static_cast<size_t>(kBwdRows) * H;                 // floats of one CTA's partial sums
+    // operand rows of batch rows beyond the batch hold whatever was there: they only reach accumulator columns that
+    // nobody reads (column n of the product depends on row n of the B operand alone)
+    struct RowSlot {
+        int i, b;
+        bool valid;
+        size_t stateIdx;
+        uint32_t aOffset;
+    };
+    auto slotOf = [&](int ps) {
+        RowSlot rs;
+        rs.i = ps * 64 + rowInPass;
+        rs.b = args.rowBase + rt * args.tileRows + rs.i;
+        rs.valid = rs.i < args.tileRows && rs.b < a.B;
+        rs.stateIdx = static_cast<size_t>(rs.valid ? rs.b : 0) * H + j0;
+        rs.aOffset = static_cast<uint32_t>(rs.i / 8) * 2048u + static_cast<uint32_t>(rs.i % 8) * 16u;
+        return rs;
+    };
+    // epilogue role: accumulator tile warp / 4 (128 units), lanes 32 * (warp % 4) .. + 31: unit jOut
+    const int outTile = warp >> 2, quarter = warp & 3, jOut = outTile * 128 + quarter * 32 + lane;
+    const int rowsValid = max(0, min(N, a.B - (args.rowBase + rt * N)));   // batch rows of this row tile that exist
+    const size_t partialTile = static_cast<size_t>(N) * H;                      // floats of one CTA's partial sums
     const size_t partialStep = static_cast<size_t>(args.rowTiles) * tilesPerRow * partialTile;
-    const uint32_t idesc = umma::instructionDescriptor(nHalf, false, false);
-    uint64_t descA[3], descB[2];
-#pragma unroll
-    for (int sp = 0; sp < 3; ++sp) descA[sp] = umma::operandDescriptor(umma::smemAddr(gTiles) + sp * kBwdSplitBytes, umma::kCore, 2048u);
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) descB[hf] = umma::operandDescriptor(umma::smemAddr(wTile) + static_cast<uint32_t>(hf * (nHalf / 8)) * 2048u, umma::kCore, 2048u);
+    const uint32_t idesc = umma::instructionDescriptor(N, false, false);
+    const uint64_t descW0 = umma::operandDescriptor(umma::smemAddr(wTile), umma::kCore, 2048u);
+    const uint64_t descG0 = umma::operandDescriptor(umma::smemAddr(gTiles), umma::kCore, 2048u);
 
-    float dc[8];
-#pragma unroll
-    for (int ps = 0; ps < 2; ++ps) {
-        const float4 v = valid[ps] ? *reinterpret_cast<const float4 *>(a.gradFinalCell + stateIdx[ps]) : make_float4(0.f, 0.f, 0.f, 0.f);
-        dc[4 * ps] = v.x; dc[4 * ps + 1] = v.y; dc[4 * ps + 2] = v.z; dc[4 * ps + 3] = v.w;
+    // dc of the thread's elements: [pass][unit]; the pass loop stays rolled (the kernel's code must stay small
+    // enough for the instruction caches), so the two sets are picked by selects
+    float dcA[4], dcB[4];
+    {
+        const RowSlot s0 = slotOf(0), s1 = slotOf(1);
+        const float4 v0 = s0.valid ? *reinterpret_cast<const float4 *>(a.gradFinalCell + s0.stateIdx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 v1 = s1.valid ? *reinterpret_cast<const float4 *>(a.gradFinalCell + s1.stateIdx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        dcA[0] = v0.x; dcA[1] = v0.y; dcA[2] = v0.z; dcA[3] = v0.w;
+        dcB[0] = v1.x; dcB[1] = v1.y; dcB[2] = v1.z; dcB[3] = v1.w;
     }
     // the carried gradient of four units: the final-state gradient before the last step, afterwards the sum of
     // the row tile's partial products of the step above
-    auto carried = [&](int t, int ps) -> float4 {
-        if (t == a.T - 1) return *reinterpret_cast<const float4 *>(a.gradFinalHidden + stateIdx[ps]);
+    auto carried = [&](int t, const RowSlot &rs) -> float4 {
+        if (t == a.T - 1) return *reinterpret_cast<const float4 *>(a.gradFinalHidden + rs.stateIdx);
         const float *p = args.partial + static_cast<size_t>((t + 1) & 1) * partialStep + static_cast<size_t>(rt) * tilesPerRow * partialTile +
-                         static_cast<size_t>(ps * 64 + rowInPass) * H + j0;
+                         static_cast<size_t>(rs.i) * H + j0;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
         for (int s2 = 0; s2 < tilesPerRow; ++s2) {
@@ -669,12 +682,16 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
     int stepsDone = 0;
     for (int t = a.T - 1; t >= 0; --t) {
         // ---- pointwise derivative of this thread's eight elements, four at a time
-#pragma unroll
+#pragma unroll 1
         for (int ps = 0; ps < 2; ++ps) {
-            if (valid[ps]) {
-                const size_t row = static_cast<size_t>(t) * a.B + bRow[ps];
+            const RowSlot rs = slotOf(ps);
+            if (rs.valid) {
+                float dc[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dc[e] = ps ? dcB[e] : dcA[e];
+                const size_t row = static_cast<size_t>(t) * a.B + rs.b;
                 const size_t so = row * H + j0, go = row * C + j0;
-                const float4 dhIn = carried(t, ps);
+                const float4 dhIn = carried(t, rs);
                 const uint4 bits4 = a.stepMasks ? *reinterpret_cast<const uint4 *>(a.stepMasks + so) : make_uint4(0u, 0u, 0u, 0u);
                 const float4 gi = *reinterpret_cast<const float4 *>(a.gateOutputs + go);
                 const float4 gf = *reinterpret_cast<const float4 *>(a.gateOutputs + go + static_cast<size_t>(H));
@@ -684,7 +701,7 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
                 const float4 gradOut = *reinterpret_cast<const float4 *>(a.gradOutput + so);
                 float4 cp4;
                 if (t > 0) cp4 = *reinterpret_cast<const float4 *>(a.cellStates + so - static_cast<size_t>(a.B) * H);
-                else if (a.c0) cp4 = *reinterpret_cast<const float4 *>(a.c0 + stateIdx[ps]);
+                else if (a.c0) cp4 = *reinterpret_cast<const float4 *>(a.c0 + rs.stateIdx);
                 else cp4 = make_float4(a.dqC.zeroPoint, a.dqC.zeroPoint, a.dqC.zeroPoint, a.dqC.zeroPoint);
                 const float dhv[4] = {dhIn.x, dhIn.y, dhIn.z, dhIn.w};
                 const uint32_t bitv[4] = {bits4.x, bits4.y, bits4.z, bits4.w};
@@ -703,7 +720,7 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
                     const float dh = (dhv[e] + gov[e]) * keepBit(0);
                     const float gOut = dh * ct;
                     const float gTanh = dh * og * keepBit(1);
-                    const float dcAll = dc[4 * ps + e] + gTanh * (1.0f - ct * ct);
+                    const float dcAll = dc[e] + gTanh * (1.0f - ct * ct);
                     const float mdc = dcAll * keepBit(2);
                     const float go4[4] = {mdc * cg * keepBit(3), mdc * cPrev * keepBit(4), mdc * ig * keepBit(5), gOut * keepBit(6)};
                     const float gi4[4] = {go4[0] * ig * (1.0f - ig), go4[1] * fg * (1.0f - fg), go4[2] * (1.0f - cg * cg),
@@ -714,7 +731,7 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
                         outIh[g][e] = grad * keepBit(11 + g);
                         outHh[g][e] = grad * keepBit(15 + g);
                     }
-                    dc[4 * ps + e] = mdc * fg;
+                    dc[e] = mdc * fg;
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -732,11 +749,32 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
                         mid2[i] = packBf16(r0, r1);
                         lo2[i] = packBf16(r0 - bf16Lo(mid2[i]), r1 - umma::bf16Hi(mid2[i]));
                     }
-                    uint8_t *dst = gTiles + aRowOffset[ps] + static_cast<uint32_t>(g * 4 + ug) * umma::kCore + 8u * sub;
+                    uint8_t *dst = gTiles + rs.aOffset + static_cast<uint32_t>(g * 4 + ug) * umma::kCore + 8u * sub;
                     *reinterpret_cast<uint2 *>(dst) = make_uint2(hi2[0], hi2[1]);
                     *reinterpret_cast<uint2 *>(dst + kBwdSplitBytes) = make_uint2(mid2[0], mid2[1]);
                     *reinterpret_cast<uint2 *>(dst + 2 * kBwdSplitBytes) = make_uint2(lo2[0], lo2[1]);
                 }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    dcA[e] = ps ? dcA[e] : dc[e];
+                    dcB[e] = ps ? dc[e] : dcB[e];
+                }
+            }
+        }
+        // the saved tensors of the step below come from HBM: ask their lines into L2 now, one lane per 128-byte line
+        if (t > 0 && (lane & 7) == 0) {
+#pragma unroll 1
+            for (int ps = 0; ps < 2; ++ps) {
+                const RowSlot rs = slotOf(ps);
+                if (!rs.valid) continue;
+                const size_t row = static_cast<size_t>(t - 1) * a.B + rs.b;
+                const size_t so = row * H + ut * kBwdUnits, go = row * C + ut * kBwdUnits;
+                if (a.stepMasks) prefetchL2(a.stepMasks + so);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) prefetchL2(a.gateOutputs + go + static_cast<size_t>(g) * H);
+                prefetchL2(a.cellTanh + so);
+                prefetchL2(a.gradOutput + so);
+                if (t > 1) prefetchL2(a.cellStates + so - static_cast<size_t>(a.B) * H);
             }
         }
         // ---- dh partial sums of this K slice: [128 rows][H units] into tensor memory
@@ -746,13 +784,14 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         if (warp == 0) {   // lane 0 issues; its siblings wait here instead of polling the barrier beside it
           if (lane == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int hf = 0; hf < halves; ++hf)
-#pragma unroll
+            for (int mt = 0; mt < unitTiles; ++mt)
+#pragma unroll 1
                 for (int sp = 0; sp < 3; ++sp)
-#pragma unroll
+#pragma unroll 2
                     for (int ks = 0; ks < kBwdSlice / 16; ++ks)
-                        umma::mmaBf16(tmem + static_cast<uint32_t>(hf * nHalf), descA[sp] + static_cast<uint64_t>(ks) * 16u,
-                                descB[hf] + static_cast<uint64_t>(ks) * 16u, idesc, (sp | ks) ? 1u : 0u);
+                        umma::mmaBf16(tmem + static_cast<uint32_t>(mt * N), descW0 + static_cast<uint64_t>(mt) * ((16u * 2048u) >> 4) + static_cast<uint64_t>(ks) * 16u,
+                                      descG0 + static_cast<uint64_t>(sp) * (kBwdSplitBytes >> 4) + static_cast<uint64_t>(ks) * 16u, idesc,
+                                      (sp | ks) ? 1u : 0u);
             umma::commitTo(umma::smemAddr(&bar));
           }
           __syncwarp();
@@ -760,18 +799,14 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         if (!*failFlag && !umma::waitPhase(umma::smemAddr(&bar), parity)) *failFlag = 1;
         parity ^= 1u;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        {
-            float *dst = args.partial + static_cast<size_t>(t & 1) * partialStep +
-                         (static_cast<size_t>(rt) * tilesPerRow + ut) * partialTile + static_cast<size_t>(quarter * 32 + lane) * H;
-            for (int c = colBegin; c < colBegin + H / 4; c += 32) {
+        if (outTile < unitTiles) {
+            float *dst = args.partial + static_cast<size_t>(t & 1) * partialStep + (static_cast<size_t>(rt) * tilesPerRow + ut) * partialTile + jOut;
+            for (int c = 0; c < rowsValid; c += 32) {
                 uint32_t v[32];
-                umma::tmemLoad32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c), v);
+                umma::tmemLoad32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(outTile * N + c), v);
 #pragma unroll
-                for (int i = 0; i < 4; ++i)   // 32-byte stores: whole sectors
-                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + c + 8 * i), "r"(v[8 * i]),
-                                 "r"(v[8 * i + 1]), "r"(v[8 * i + 2]), "r"(v[8 * i + 3]), "r"(v[8 * i + 4]), "r"(v[8 * i + 5]),
-                                 "r"(v[8 * i + 6]), "r"(v[8 * i + 7])
-                                 : "memory");
+                for (int i = 0; i < 32; ++i)
+                    if (c + i < rowsValid) __stcg(dst + static_cast<size_t>(c + i) * H, __uint_as_float(v[i]));
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -779,17 +814,18 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         ++stepsDone;
         groupBarrier(stepsDone);
     }
-#pragma unroll
+#pragma unroll 1
     for (int ps = 0; ps < 2; ++ps) {
-        if (!valid[ps]) continue;
+        const RowSlot rs = slotOf(ps);
+        if (!rs.valid) continue;
         const float nan = __int_as_float(0x7fc00000);
-        const float4 dh0 = *failFlag ? make_float4(nan, nan, nan, nan) : carried(-1, ps);
+        const float4 dh0 = *failFlag ? make_float4(nan, nan, nan, nan) : carried(-1, rs);
         const float out[4] = {dh0.x, dh0.y, dh0.z, dh0.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const size_t o = stateIdx[ps] + e;
+            const size_t o = rs.stateIdx + e;
             a.dh0[o] = out[e] * keepOf(a.mk.initial_hidden, o);
-            a.dc0[o] = dc[4 * ps + e] * keepOf(a.mk.initial_cell, o);
+            a.dc0[o] = (ps ? dcB[e] : dcA[e]) * keepOf(a.mk.initial_cell, o);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1189,8 +1225,14 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
             }
             afterLaunch("lstmPackBackwardTiles");
             const int tilesPerRow = H / kBwdUnits;
-            const int rowTilesAll = (B + kBwdRows - 1) / kBwdRows;
-            const int perLaunch = std::max(1, std::min(wideTensorRowTiles(B, H), smsPerPass() / tilesPerRow));
+            // Rows per row tile: the per-step exchange of partial sums is bound by what one SM moves, so the batch is
+            // spread over as many SMs as one cooperative launch holds (smaller row tiles leave accumulator rows unused).
+            const int tilesHeld = std::max(1, smsPerPass() / tilesPerRow);
+            int tileRows = kBwdRows;
+            for (int rows : {64, 32})
+                if ((B + rows - 1) / rows <= tilesHeld) tileRows = rows;
+            const int rowTilesAll = (B + tileRows - 1) / tileRows;
+            const int perLaunch = std::max(1, std::min(rowTilesAll, tilesHeld));
             ensureDynamicSmem(reinterpret_cast<const void *>(recurrentBackwardUmma), wideSmem);
             RXMET_CUDA(cudaMemsetAsync(wideCounters + 255, 0, sizeof(unsigned int), st));
             for (int first = 0; first < rowTilesAll; first += perLaunch) {
@@ -1198,7 +1240,7 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
                 u.base = a;
                 u.tiles = wideTiles; u.channelScale = channelScales + C; u.partial = widePartial;
                 u.counters = wideCounters; u.status = reinterpret_cast<int *>(wideCounters + 255);
-                u.rowBase = first * kBwdRows; u.rowTiles = std::min(perLaunch, rowTilesAll - first);
+                u.tileRows = tileRows; u.rowBase = first * tileRows; u.rowTiles = std::min(perLaunch, rowTilesAll - first);
                 RXMET_CUDA(cudaMemsetAsync(wideCounters, 0, sizeof(unsigned int) * 255, st));
                 void *params[] = {&u};
                 KernelTimer timer__("lstmRecurrentBackwardWide", st);
