@@ -778,7 +778,7 @@ _LSTM_WIDE_KERNELS = ["lstmQuantizePlanes", "lstmQuantizeCodes", "lstmPrepChanne
                       "lstmRecurrentFloatWide", "lstmRecurrentFloat", "lstmInputLinearFloat", "lstmJobMinMax", "lstmJobHistogram",
                       "lstmRecurrentBackwardWide", "lstmRecurrentBackward", "lstmGemmNN", "lstmGemmRowsTN", "lstmReduceSplits",
                       "lstmColumnSums", "lstmDequantWeights", "lstmPackStepMasks", "inputGradUmma", "weightGradUmma",
-                      "lstmReduceWeightGradT", "lstmInputGradNarrow"]
+                      "lstmReduceWeightGradT", "lstmInputGradNarrow", "lstmPackBackwardTiles"]
 
 
 def lstm_bidirectional_a16(lib, torch, device, flush, peak_gbs, args):

@@ -587,7 +587,7 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
 
     if (tid == 0) {
         failed = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(umma::smemAddr(&bar)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(umma::smemAddr(&bar)), "r"(H / 128) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -652,11 +652,16 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         if (t == a.T - 1) return *reinterpret_cast<const float4 *>(a.gradFinalHidden + rs.stateIdx);
         const float *p = args.partial + static_cast<size_t>((t + 1) & 1) * partialStep + static_cast<size_t>(rt) * tilesPerRow * partialTile +
                          static_cast<size_t>(rs.i) * H + j0;
+        // eight loads in flight at a time: a rolled loop would pay one L2 round trip per slice
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s2 = 0; s2 < tilesPerRow; ++s2) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(p + static_cast<size_t>(s2) * partialTile));
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        for (int s0 = 0; s0 < tilesPerRow; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = s0 + i < tilesPerRow ? __ldcg(reinterpret_cast<const float4 *>(p + static_cast<size_t>(s0 + i) * partialTile))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { sum.x += v[i].x; sum.y += v[i].y; sum.z += v[i].z; sum.w += v[i].w; }
         }
         return sum;
     };
@@ -781,20 +786,23 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        if (warp == 0) {   // lane 0 issues; its siblings wait here instead of polling the barrier beside it
-          if (lane == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int mt = 0; mt < unitTiles; ++mt)
-#pragma unroll 1
+        // One thread per accumulator tile issues that tile's MMAs (a single issuer spends more time on descriptor
+        // arithmetic than the tensor pipe needs for N = 32); its lane siblings wait at the warp barrier instead of
+        // polling beside it.  Each issuer commits to the same barrier (initialised to the number of tiles).
+        if (warp < unitTiles) {
+            if (lane == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem + static_cast<uint32_t>(warp * N);
+                const uint64_t w0 = descW0 + static_cast<uint64_t>(warp) * ((16u * 2048u) >> 4);
+#pragma unroll
                 for (int sp = 0; sp < 3; ++sp)
-#pragma unroll 2
+#pragma unroll
                     for (int ks = 0; ks < kBwdSlice / 16; ++ks)
-                        umma::mmaBf16(tmem + static_cast<uint32_t>(mt * N), descW0 + static_cast<uint64_t>(mt) * ((16u * 2048u) >> 4) + static_cast<uint64_t>(ks) * 16u,
-                                      descG0 + static_cast<uint64_t>(sp) * (kBwdSplitBytes >> 4) + static_cast<uint64_t>(ks) * 16u, idesc,
+                        umma::mmaBf16(d, w0 + static_cast<uint64_t>(ks * 16), descG0 + static_cast<uint64_t>(sp * (kBwdSplitBytes >> 4) + ks * 16), idesc,
                                       (sp | ks) ? 1u : 0u);
-            umma::commitTo(umma::smemAddr(&bar));
-          }
-          __syncwarp();
+                umma::commitTo(umma::smemAddr(&bar));
+            }
+            __syncwarp();
         }
         if (!*failFlag && !umma::waitPhase(umma::smemAddr(&bar), parity)) *failFlag = 1;
         parity ^= 1u;
