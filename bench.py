@@ -388,10 +388,18 @@ def run_ours(args):
         session.collect(torch.randn((50, 64, I), generator=gen).to(device), *w)
         bundle = session.finalize(False)["bundle_json"]
         x = torch.randn((T, B, I), generator=gen).to(device)
+        order = ("input", "weight_ih", "weight_hh", "bias_ih", "bias_hh", "h_0", "c_0")
+        g = [torch.randn(s, generator=gen).to(device) for s in [(T, B, H), (B, H), (B, H)]]
         for _ in range(max(args.steps, 1) + args.warmup):
-            m.lstm_forward_quantized(x, *w, None, None, False, bundle)
+            if not args.lstm_qat:
+                m.lstm_forward_quantized(x, *w, None, None, False, bundle)
+                continue
+            ck = m.lstm_forward_quantized(x, *w, None, None, False, bundle, "pedantic", False, True)[3]
+            m.lstm_backward_qat([ck["quantized_master"][n] for n in order], False, bundle,
+                                [ck["values"][n] for n in ("gate_outputs", "cell_states", "cell_tanh_outputs", "hidden_outputs")],
+                                *g, [ck["master_clamp_masks"][n] for n in order], [ck["clamp_masks"][n] for n in L.TRACE_VALUES])
         torch.cuda.synchronize()
-        print(json.dumps({"profile_only": True, "workload": "lstm_sweep", "T": T, "B": B}), flush=True)
+        print(json.dumps({"profile_only": True, "workload": "lstm_sweep", "T": T, "B": B, "qat": bool(args.lstm_qat)}), flush=True)
         return
     if args.workload in ("lstm_sweep", "lstm_bi"):
         flush_ = torch.empty(256 << 20, dtype=torch.uint8, device=device)
@@ -1158,6 +1166,8 @@ def main():
                          "the bidirectional W8/A16 calibration + forward as a JSON object (1 GPU).  With --profile-only: "
                          "which loop to run under a profiler")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
+    ap.add_argument("--lstm-qat", action="store_true",
+                    help="--profile-only lstm_sweep loop: training forward + QAT backward instead of the inference forward")
     ap.add_argument("--e2e-copy", choices=["kernel", "dma"], default="kernel",
                     help="how the end-to-end leg moves a step's inputs from pinned host memory: the library's staging "
                          "kernel (rxmet_stage_from_pinned_host) or copy-engine transfers")

@@ -92,7 +92,7 @@ def test_float_forward_and_backward_beyond_128(T, B, I, H):
         close(t.cpu().numpy().reshape(wg[n].shape), wg[n], 2e-5, n)
 
 
-@pytest.mark.parametrize("T,B,I,H,wb,ab", [(4, 6, 80, 128, 8, 16), (3, 5, 256, 512, 4, 16), (5, 130, 32, 256, 4, 16)])
+@pytest.mark.parametrize("T,B,I,H,wb,ab", [(4, 6, 80, 128, 8, 16), (3, 5, 256, 512, 4, 16), (5, 130, 32, 256, 4, 16), (3, 40, 32, 384, 8, 16), (2, 2400, 16, 256, 4, 16)])
 def test_wide_qat_backward(T, B, I, H, wb, ab):
     """Quantized training forward on 16-bit grids, then the QAT backward on the saved tensors against the
     masked float backward of the checker on the dequantized tensors."""
