@@ -536,7 +536,7 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
 
     if (tid == 0) {
         failed = 0;
-        for (int i = 0; i < 2; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smemAddr(&bars[i])) : "memory");
+        for (int i = 0; i < 2; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(&bars[i])), "r"(PLANES) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -572,15 +572,29 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
     const int rowWords = PLANES * kWords;
 
     // hidden planes of sub-block `sb` of the exchange half `src` -> plane buffer `buf`
+    // Rows beyond the group's last row are not copied: their operand rows keep whatever they held, which only
+    // reaches accumulator columns that nobody reads (column n of the product depends on operand row n alone).
+    const int perRow = PLANES * (kWords / 4);                       // 16-byte pieces of one row
+    const int perRowShift = (perRow & (perRow - 1)) == 0 ? 31 - __clz(perRow) : -1;
+    const int perPlaneShift = 31 - __clz(kWords / 4);               // used with perRowShift only (both powers of two then)
     auto stage = [&](const uint32_t *src, int sb, int buf) {
         const int row0 = rowBegin + sb * kSubRows;
-        const int pieces = kSubRows * PLANES * (kWords / 4);
+        const int pieces = min(kSubRows, rowEnd - row0) * perRow;
         for (int i = tid; i < pieces; i += blockDim.x) {
-            const int r = i / (PLANES * (kWords / 4)), rest = i - r * (PLANES * (kWords / 4));
-            const int pl = rest / (kWords / 4), kg = rest - pl * (kWords / 4);
-            const bool valid = row0 + r < rowEnd;
-            const uint32_t *from = src + (valid ? (static_cast<size_t>(row0 + r) * rowWords + pl * kWords + 4 * kg) : 0);
-            copyAsync16(bPlanes + (buf * PLANES + pl) * planeBytes + (r >> 3) * groupStride + kg * kCore + (r & 7) * 16, from, valid);
+            int r, pl, kg;
+            if (perRowShift >= 0) {
+                r = i >> perRowShift;
+                const int rest = i & (perRow - 1);
+                pl = rest >> perPlaneShift;
+                kg = rest & ((kWords / 4) - 1);
+            } else {
+                r = i / perRow;
+                const int rest = i - r * perRow;
+                pl = rest / (kWords / 4);
+                kg = rest - pl * (kWords / 4);
+            }
+            const uint32_t *from = src + (static_cast<size_t>(row0 + r) * rowWords + pl * kWords + 4 * kg);
+            copyAsync16(bPlanes + (buf * PLANES + pl) * planeBytes + (r >> 3) * groupStride + kg * kCore + (r & 7) * 16, from, true);
         }
         commitCopies();
     };
@@ -733,16 +747,20 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
             waitCopies<0>();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncthreads();
-            if (tid == 0) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int buf = batch & 1;
-                const uint64_t kStep = static_cast<uint64_t>((2 * kCore) >> 4);   // start-address field advances by two k-groups
-#pragma unroll
-                for (int pl = 0; pl < PLANES; ++pl)
+            // One thread per byte plane issues that plane's MMAs (its accumulator columns are its own) and commits to
+            // the batch's barrier, which counts PLANES arrivals; the issuer's lane siblings wait at the warp barrier
+            // instead of polling the barrier beside it.
+            if (warp < PLANES) {
+                if (lane == 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int buf = batch & 1;
+                    const uint64_t kStep = static_cast<uint64_t>((2 * kCore) >> 4);   // start-address field advances by two k-groups
+                    const uint64_t descB = warp == 0 ? descB0[buf][0] : descB0[buf][PLANES - 1];
                     for (int ks = 0; ks < kPad / 32; ++ks)
-                        planeproj::mmaI8(tmem + buf * kBufCols + pl * kSubRows, descA0 + ks * kStep, descB0[buf][pl] + ks * kStep, kIdesc,
-                                         ks > 0 ? 1u : 0u);
-                commitTo(smemAddr(&bars[buf]));
+                        planeproj::mmaI8(tmem + buf * kBufCols + warp * kSubRows, descA0 + ks * kStep, descB + ks * kStep, kIdesc, ks > 0 ? 1u : 0u);
+                    commitTo(smemAddr(&bars[buf]));
+                }
+                __syncwarp();
             }
             // The plane buffer of the next batch was read by the MMAs of the previous one: once those are known to be
             // complete the next sub-block's copies start, and they fly during the previous sub-block's epilogue.
