@@ -528,8 +528,8 @@ def run_ours(args):
             copy_stream.wait_event(consumed[slot])
             if args.e2e_copy == "kernel":
                 # the library's staging kernel: a few CTAs read the pinned buffers over PCIe
-                stage_from_pinned_host(x_buf[slot], xs_host[i % n_sets], ctas=4, stream=copy_stream)
-                stage_from_pinned_host(y_buf[slot], ys_host[i % n_sets], ctas=4, stream=copy_stream)
+                stage_from_pinned_host(x_buf[slot], xs_host[i % n_sets], ctas=args.e2e_ctas, stream=copy_stream)
+                stage_from_pinned_host(y_buf[slot], ys_host[i % n_sets], ctas=args.e2e_ctas, stream=copy_stream)
             else:
                 x_buf[slot].copy_(xs_host[i % n_sets], non_blocking=True)
                 y_buf[slot].copy_(ys_host[i % n_sets], non_blocking=True)
@@ -1165,6 +1165,7 @@ def main():
                          "(its own bench line, any --gpus).  lstm_sweep / lstm_bi: print the QuantLSTM W4/A16 batch sweep or "
                          "the bidirectional W8/A16 calibration + forward as a JSON object (1 GPU).  With --profile-only: "
                          "which loop to run under a profiler")
+    ap.add_argument("--e2e-ctas", type=int, default=4, help="CTAs of the staging kernel in the end-to-end leg")
     ap.add_argument("--lstm-T", type=int, default=20, help="sequence length of the --profile-only lstm loop")
     ap.add_argument("--lstm-qat", action="store_true",
                     help="--profile-only lstm_sweep loop: training forward + QAT backward instead of the inference forward")

@@ -12,17 +12,19 @@ __global__ void __launch_bounds__(256) stageFromHost(const uint4 *__restrict__ s
                                                      const unsigned char *__restrict__ srcTail, unsigned char *__restrict__ dstTail,
                                                      int tailBytes) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    // four independent 16-byte loads per thread and pass keep enough PCIe reads in flight
+    // eight independent 16-byte loads per thread and pass: a PCIe read takes microseconds, and the bytes in flight
+    // (CTAs x 256 threads x 128 B) decide the rate
+    constexpr int kInFlight = 8;
     size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-    for (; i + 3 * stride < vectors; i += 4 * stride) {
-        uint4 v[4];
+    for (; i + (kInFlight - 1) * stride < vectors; i += kInFlight * stride) {
+        uint4 v[kInFlight];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < kInFlight; ++k)
             asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
                          : "l"(src + i + k * stride));
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < kInFlight; ++k)
             asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + i + k * stride), "r"(v[k].x), "r"(v[k].y),
                          "r"(v[k].z), "r"(v[k].w)
                          : "memory");
