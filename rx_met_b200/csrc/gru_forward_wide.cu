@@ -213,7 +213,12 @@ struct RecurrentArgs {
 
 template <int RB, bool WS>
 __global__ void __launch_bounds__(kThreads, 1)
-recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec g) {
+recurrentPlanes(const __grid_constant__ RecurrentArgs a, const __grid_constant__ GateExec gateParam) {
+    // The cell reads table entries at per-lane segment indices: from the constant bank such a read is replayed once
+    // per distinct index in the warp, from shared memory it is one banked access.
+    __shared__ GateExec g;
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(GateExec) / 4); i += blockDim.x)
+        reinterpret_cast<int32_t *>(&g)[i] = reinterpret_cast<const int32_t *>(&gateParam)[i];
     extern __shared__ __align__(16) uint32_t planeSmemRaw[];  // [weights when WS] [2][BT][2][kWords]
     uint32_t *planeSmem = planeSmemRaw + (WS ? a.weightBytesInSmem / 4 : 0);
     const int H = a.H, C = 3 * a.H, kWords = a.kWords;
@@ -515,7 +520,7 @@ void forwardWide(const WideCall &call, const Exec &e, Workspace &ws, cudaStream_
         const int bt = groups * rb, block = groups * a.HP;
         const size_t planeBytes = sizeof(uint32_t) * 2 * bt * 2 * kH;
         const size_t weightBytes = sizeof(uint32_t) * static_cast<size_t>(kH) * C;
-        const bool weightsInSmem = planeBytes + weightBytes + 1024 <= static_cast<size_t>(currentDevice().smemMax);
+        const bool weightsInSmem = planeBytes + weightBytes + 2048 <= static_cast<size_t>(currentDevice().smemMax);   // + the kernel's static copy of the gate parameters
         a.weightBytesInSmem = weightsInSmem ? static_cast<int>(weightBytes) : 0;
         const size_t smem = planeBytes + (weightsInSmem ? weightBytes : 0);
         auto launch = [&](auto kernel) {
