@@ -1197,6 +1197,7 @@ void launch(const Problem &prob, int K, int N, const Plan &pl, cudaStream_t st) 
 void launchPair(const Problem &a, const Plan &planA, const Problem &b, const Plan &planB, int K, int N, cudaStream_t st) {
     if (planA.tensorMemory && planB.tensorMemory && planA.splits == planB.splits && planA.chunkK == planB.chunkK &&
         a.status == b.status) {
+        if (launchPairStreamed(a, b, K, N, planA.chunkK, planA.splits, st)) return;
         const bool aFirst = a.M >= b.M;
         launchTensorMemory(aFirst ? a : b, aFirst ? &b : &a, K, N, planA.chunkK, planA.splits, st);
         return;
@@ -1583,7 +1584,10 @@ void backward(const BackwardCall &call, void *workspace, size_t workspaceBytes, 
     if (tensorGrads) {
         const Exec &e = *call.exec;
         const int K = static_cast<int>(rows);
-        const wgrad::Plan planX = wgrad::plan(K, I, C, sms), planH = wgrad::plan(K, H, C, sms);
+        // the two problems share one launch of one CTA per SM: each is planned for half of the SMs, so that the
+        // launch is a single wave (RXMET_WGRAD_FULL_SPLIT plans each for all SMs, two waves)
+        const int planSms = std::getenv("RXMET_WGRAD_FULL_SPLIT") ? sms : std::max(1, sms / 2);
+        const wgrad::Plan planX = wgrad::plan(K, I, C, planSms), planH = wgrad::plan(K, H, C, planSms);
         WeightGradProblem px{}, ph{};
         px.aCodes = call.x_q; px.aZero = e.gate.zp[RXMET_GRU_X]; px.M = I; px.B = dp;
         px.partial = ws.take<float>(static_cast<size_t>(planX.splits) * (I + 1) * C);

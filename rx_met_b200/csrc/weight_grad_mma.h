@@ -61,6 +61,11 @@ void launch(const Problem &problem, int K, int N, const Plan &plan, cudaStream_t
 // CTAs scheduled first; otherwise two launches.
 void launchPair(const Problem &a, const Plan &planA, const Problem &b, const Plan &planB, int K, int N, cudaStream_t stream);
 
+// The warp-specialised tcgen05 kernel (weight_grad_stream_umma.cu): both problems of a pair with at most 128 rows
+// (a multiple of 8) each, whole arrays (no slabs), 8-bit codes, N a multiple of 128 or 192 but not of 256.  Returns
+// false without launching when it does not take the pair.
+bool launchPairStreamed(const Problem &a, const Problem &b, int K, int N, int chunkK, int splits, cudaStream_t stream);
+
 // The tcgen05 kernel (weight_grad_umma.cu).
 bool tensorMemoryPath(int M, int N);
 int planTensorMemory(int K, int N, int sms, int *chunkK, int slabs = 1);
