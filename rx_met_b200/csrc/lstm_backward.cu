@@ -669,6 +669,7 @@ __global__ void __launch_bounds__(512, 1) recurrentBackwardUmma(const __grid_con
         __threadfence();
         __syncthreads();
         if (tid == 0) {
+            __threadfence();   // cumulative: what the other threads wrote before the barrier is ordered before the arrival
             atomicAdd(args.counters + rt, 1u);
             const unsigned int want = static_cast<unsigned int>(tilesPerRow) * stepsDone;
             bool arrived = *failFlag != 0;

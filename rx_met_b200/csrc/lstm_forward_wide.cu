@@ -776,6 +776,7 @@ __global__ void __launch_bounds__(512, 1) recurrentWideUmma(const __grid_constan
             __threadfence();
             __syncthreads();
             if (tid == 0) {
+                __threadfence();   // cumulative: what the other threads wrote before the barrier is ordered before the arrival
                 atomicAdd(a.counters + group, 1u);
                 const unsigned int want = static_cast<unsigned int>(tilesPerGroup) * (t + 1);
                 bool arrived = *failFlag != 0;
