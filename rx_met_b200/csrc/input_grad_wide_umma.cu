@@ -2,18 +2,18 @@
 // tcgen05.mma, warp-specialised: nothing of either operand stays resident, both stream through
 // shared memory once per 128-row tile while the whole [128][N] accumulator lives in tensor memory.
 //
-//   * warp 8, one lane: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) brings chunk after chunk of
-//     raw fp32 gradients ([128 rows][32 channels] = 16 KB) into a ring of four buffers;
-//   * warp 9, one lane: one bulk copy per chunk brings the 32-channel slice of the weight operand,
+//   * one lane of the warp behind the converters: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) brings chunk after
+//     chunk of raw fp32 gradients (boxes of [128 rows][32 channels] = 16 KB; one or two per chunk) into a ring;
+//   * one lane of the next warp: one bulk copy per chunk brings the chunk's slice of the weight operand,
 //     packed beforehand by packWideWeights into the canonical un-swizzled K-major layout, into a
 //     ring of three buffers that the MMAs read directly;
-//   * warps 0-7 convert: read a raw chunk (the swizzle makes the reads conflict-free), fold the
+//   * the converter warps (8, or 16 with 64-channel chunks): read a raw chunk (the swizzle makes the reads conflict-free), fold the
 //     per-channel scale in, split every value into three bf16 terms and store them as the A operand
 //     of one of two stages;
-//   * warp 10, one lane: issues the MMAs of a chunk (2 k-steps x 3 terms x column blocks of at most
+//   * one lane of the last warp: issues the MMAs of a chunk (2 or 4 k-steps x 3 terms x column blocks of at most
 //     256) and commits them to the barriers that free the A stage and the weight buffer.
 // Full / empty mbarriers connect the roles; the only CTA-wide barriers are at the start and the end.
-// After the last chunk warps 0-7 read the accumulators (lane = row), apply the mask and store.
+// After the last chunk the converter warps read the accumulators (lane = row), apply the mask and store.
 // Every wait is bounded: a wait that gives up sets a flag that ends all further waiting, poisons the
 // CTA's outputs with NaN and sets the status word; the CTA still waits for its copies in flight and
 // frees its tensor memory.
@@ -32,26 +32,33 @@ namespace {
 
 using namespace umma;
 
-constexpr int kConvWarps = 8;
-constexpr int kThreadsWide = (kConvWarps + 3) * 32;
-constexpr int kChunk = 32;                                   // channels per chunk = one 128-byte span of a raw row
-constexpr int kRawRing = 4, kAStages = 2, kBRing = 3;
-constexpr uint32_t kRawChunkBytes = kTileM * kChunk * 4;     // 16 KB
-constexpr uint32_t kTermChunkBytes = kTileM * kChunk * 2;    // 8 KB: one bf16 term of a chunk
-constexpr uint32_t kAStageBytes = 3 * kTermChunkBytes;
-constexpr uint32_t kRowGroupStride = (kChunk / 8) * kCore;   // next 8 rows (A) or 8 columns (B) inside a chunk
+// CH channels per chunk (32 or 64: one or two 128-byte spans of a raw row), CW converter warps.  The wider chunk halves
+// the number of hand-overs between the roles per tile; it fits beside the weight ring for up to 128 columns.
+template <int CH, int CW>
+struct WideGeometry {
+    static constexpr int kConvWarps = CW;
+    static constexpr int kThreads = (CW + 3) * 32;
+    static constexpr int kBoxes = CH / 32;                                  // TMA boxes (128 rows x 32 channels) per chunk
+    static constexpr int kRawRing = CH == 32 ? 4 : 3, kAStages = 2, kBRing = 3;
+    static constexpr uint32_t kBoxBytes = kTileM * 32 * 4;                  // 16 KB
+    static constexpr uint32_t kRawChunkBytes = kBoxes * kBoxBytes;
+    static constexpr uint32_t kTermChunkBytes = kTileM * CH * 2;            // one bf16 term of a chunk
+    static constexpr uint32_t kAStageBytes = 3 * kTermChunkBytes;
+    static constexpr uint32_t kRowGroupStride = (CH / 8) * kCore;           // next 8 rows (A) or 8 columns (B) inside a chunk
+    static size_t sharedBytes(int NP) {
+        return 1024 + kRawRing * kRawChunkBytes + kAStages * kAStageBytes + static_cast<size_t>(kBRing) * NP * CH * 2;
+    }
+};
+constexpr int kChunk = 32;          // granularity of K that every variant takes
 constexpr int kMaxColumns = 512;
 
-size_t wideSharedBytes(int NP) {
-    return 1024 + kRawRing * kRawChunkBytes + kAStages * kAStageBytes + static_cast<size_t>(kBRing) * NP * kChunk * 2;
-}
-
-// codes -> bf16, chunk by chunk: packed[chunk][n / 8][k-group of 8][n % 8][8 k]; one thread per 16-byte row.
-__global__ void packWideWeights(const int32_t *codesNK, const float *codesKN, int ldCodesKN, int K, int N, int NP, uint4 *packed) {
+// codes -> bf16, chunk by chunk of CH channels: packed[chunk][n / 8][k-group of 8][n % 8][8 k]; one thread per 16-byte row.
+__global__ void packWideWeights(const int32_t *codesNK, const float *codesKN, int ldCodesKN, int K, int N, int NP, int CH, uint4 *packed) {
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
     if (item >= (K / 8) * NP) return;
-    const int nr = item & 7, kg = (item >> 3) & 3, n8 = (item >> 5) % (NP / 8), kc = (item >> 5) / (NP / 8);
-    const int n = 8 * n8 + nr, k0 = kc * kChunk + 8 * kg;
+    const int groups = CH / 8;   // k-groups of a chunk
+    const int nr = item & 7, kg = (item >> 3) % groups, n8 = ((item >> 3) / groups) % (NP / 8), kc = ((item >> 3) / groups) / (NP / 8);
+    const int n = 8 * n8 + nr, k0 = kc * CH + 8 * kg;
     float c[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -68,8 +75,13 @@ struct WideShape {
     int tmemCols;  // power of two that holds NP columns
 };
 
-__global__ void __launch_bounds__(kThreadsWide, 1)
+template <int CH, int CW>
+__global__ void __launch_bounds__((CW + 3) * 32, 1)
 inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant__ CUtensorMap gradients) {
+    using G = WideGeometry<CH, CW>;
+    constexpr int kConvWarps = CW, kRawRing = G::kRawRing, kAStages = G::kAStages, kBRing = G::kBRing;
+    constexpr uint32_t kRawChunkBytes = G::kRawChunkBytes, kTermChunkBytes = G::kTermChunkBytes, kAStageBytes = G::kAStageBytes,
+                       kRowGroupStride = G::kRowGroupStride;
     extern __shared__ __align__(1024) uint8_t smemRaw[];
     __shared__ __align__(8) uint64_t rawFull[kRawRing], rawEmpty[kRawRing], aFull[kAStages], aEmpty[kAStages], bFull[kBRing],
         bEmpty[kBRing], accFull;
@@ -77,9 +89,9 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
     __shared__ int failed;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int K = p.K, N = p.N, NP = shape.NP, chunks = K / kChunk;
+    const int K = p.K, N = p.N, NP = shape.NP, chunks = K / CH;
     const int ldN = p.ldN ? p.ldN : N;
-    const uint32_t bBytes = static_cast<uint32_t>(NP) * kChunk * 2;
+    const uint32_t bBytes = static_cast<uint32_t>(NP) * CH * 2;
     uint8_t *base = smemRaw + ((1024u - (smemAddr(smemRaw) & 1023u)) & 1023u);   // the swizzled TMA boxes need 1024-byte alignment
     uint8_t *raw = base;
     uint8_t *aStages = raw + kRawRing * kRawChunkBytes;
@@ -131,10 +143,12 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
                 if (*failFlag) break;
                 const uint32_t bar = smemAddr(&rawFull[slot]);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kRawChunkBytes) : "memory");
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                    ::"r"(smemAddr(raw + slot * kRawChunkBytes)), "l"(&gradients), "r"(c * kChunk), "r"(row0), "r"(bar)
-                    : "memory");
+#pragma unroll
+                for (int b = 0; b < G::kBoxes; ++b)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(smemAddr(raw + slot * kRawChunkBytes + b * G::kBoxBytes)), "l"(&gradients), "r"(c * CH + 32 * b), "r"(row0), "r"(bar)
+                        : "memory");
                 issued = c + 1;
             }
             if (*failFlag)   // copies in flight must land before the CTA's shared memory is given up
@@ -171,7 +185,7 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t aBase = smemAddr(aStages + sa * kAStageBytes), bBase = smemAddr(bRing + static_cast<size_t>(sb) * bBytes);
 #pragma unroll
-                for (int ks = 0; ks < kChunk / 16; ++ks) {
+                for (int ks = 0; ks < CH / 16; ++ks) {
                     for (int nb = 0; nb < shape.blocks; ++nb) {
                         const uint64_t descB =
                             operandDescriptor(bBase + nb * (shape.NB / 8) * kRowGroupStride + ks * 2 * kCore, kCore, kRowGroupStride);
@@ -189,41 +203,51 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
             commitTo(smemAddr(&accFull));
         }
     } else {
-        // ---- converters: warp w owns row groups w and w + 8 of the tile (8 rows each); lane -> row lane % 8,
-        // channels [8 (lane / 8), + 8) of the chunk
+        // ---- converters: warp w owns the row groups w, w + CW, ... of the tile (8 rows each); lane -> row lane % 8,
+        // channels [8 (lane / 8), + 8) of each 32-channel box of the chunk
         const int rm = lane & 7, cq = lane >> 3;
+        constexpr int kGroupsPerWarp = 16 / CW, kPieces = kGroupsPerWarp * G::kBoxes;
         for (int c = 0; c < chunks; ++c) {
             const int slot = c % kRawRing, sa = c % kAStages;
             await(&rawFull[slot], (c / kRawRing) & 1);
             const uint8_t *src = raw + slot * kRawChunkBytes;
-            uint4 ru[2], rv[2];
+            uint4 ru[kPieces], rv[kPieces];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint8_t *row = src + (8 * (warp + kConvWarps * h) + rm) * 128;
-                ru[h] = *reinterpret_cast<const uint4 *>(row + (((2 * cq) ^ rm) << 4));
-                rv[h] = *reinterpret_cast<const uint4 *>(row + (((2 * cq + 1) ^ rm) << 4));
-            }
+            for (int h = 0; h < kGroupsPerWarp; ++h)
+#pragma unroll
+                for (int b = 0; b < G::kBoxes; ++b) {
+                    const uint8_t *row = src + b * G::kBoxBytes + (8 * (warp + kConvWarps * h) + rm) * 128;
+                    ru[h * G::kBoxes + b] = *reinterpret_cast<const uint4 *>(row + (((2 * cq) ^ rm) << 4));
+                    rv[h * G::kBoxes + b] = *reinterpret_cast<const uint4 *>(row + (((2 * cq + 1) ^ rm) << 4));
+                }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(&rawEmpty[slot])) : "memory");
-            float4 su = make_float4(1.0f, 1.0f, 1.0f, 1.0f), sv = su;
-            if (p.kScale) {
-                su = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * kChunk + 8 * cq));
-                sv = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * kChunk + 8 * cq + 4));
+            float4 su[G::kBoxes], sv[G::kBoxes];
+#pragma unroll
+            for (int b = 0; b < G::kBoxes; ++b) {
+                su[b] = sv[b] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                if (p.kScale) {
+                    su[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * CH + 32 * b + 8 * cq));
+                    sv[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * CH + 32 * b + 8 * cq + 4));
+                }
             }
             if (c >= kAStages) await(&aEmpty[sa], (c / kAStages - 1) & 1);
             uint8_t *stage = aStages + sa * kAStageBytes;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float4 u = make_float4(__uint_as_float(ru[h].x) * su.x, __uint_as_float(ru[h].y) * su.y,
-                                             __uint_as_float(ru[h].z) * su.z, __uint_as_float(ru[h].w) * su.w);
-                const float4 v = make_float4(__uint_as_float(rv[h].x) * sv.x, __uint_as_float(rv[h].y) * sv.y,
-                                             __uint_as_float(rv[h].z) * sv.z, __uint_as_float(rv[h].w) * sv.w);
-                const Converted cv = splitThree(u, v);
-                uint8_t *dst = stage + (warp + kConvWarps * h) * kRowGroupStride + cq * kCore + rm * 16;
-                *reinterpret_cast<uint4 *>(dst) = cv.hi;
-                *reinterpret_cast<uint4 *>(dst + kTermChunkBytes) = cv.mid;
-                *reinterpret_cast<uint4 *>(dst + 2 * kTermChunkBytes) = cv.lo;
-            }
+            for (int h = 0; h < kGroupsPerWarp; ++h)
+#pragma unroll
+                for (int b = 0; b < G::kBoxes; ++b) {
+                    const uint4 qu = ru[h * G::kBoxes + b], qv = rv[h * G::kBoxes + b];
+                    const float4 u = make_float4(__uint_as_float(qu.x) * su[b].x, __uint_as_float(qu.y) * su[b].y,
+                                                 __uint_as_float(qu.z) * su[b].z, __uint_as_float(qu.w) * su[b].w);
+                    const float4 v = make_float4(__uint_as_float(qv.x) * sv[b].x, __uint_as_float(qv.y) * sv[b].y,
+                                                 __uint_as_float(qv.z) * sv[b].z, __uint_as_float(qv.w) * sv[b].w);
+                    const Converted cv = splitThree(u, v);
+                    uint8_t *dst = stage + (warp + kConvWarps * h) * kRowGroupStride + (4 * b + cq) * kCore + rm * 16;
+                    *reinterpret_cast<uint4 *>(dst) = cv.hi;
+                    *reinterpret_cast<uint4 *>(dst + kTermChunkBytes) = cv.mid;
+                    *reinterpret_cast<uint4 *>(dst + 2 * kTermChunkBytes) = cv.lo;
+                }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(&aFull[sa])) : "memory");
@@ -233,8 +257,8 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
         await(&accFull, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool poison = *failFlag != 0;
-        const int q = warp & 3, half = (NP / 2 + 15) / 16 * 16;
-        const int colBegin = (warp >> 2) * half, colEnd = min(NP, colBegin + half);
+        const int q = warp & 3, part = ((NP + CW / 4 - 1) / (CW / 4) + 15) / 16 * 16;   // columns per warp of a lane quarter
+        const int colBegin = (warp >> 2) * part, colEnd = min(NP, colBegin + part);
         const int row = row0 + 32 * q + lane;
         const bool wideMask = (N % 8) == 0 && (ldN % 8) == 0;
         const bool wideOut = (N % 4) == 0 && (ldN % 4) == 0;
@@ -347,16 +371,26 @@ bool wideEligible(const Problem &p) {
            (p.kScale == nullptr || alignedTo(p.kScale, 16));
 }
 
-void launchWide(const Problem &prob, cudaStream_t st) {
-    const WideShape shape = shapeFor(prob.N);
-    const size_t smem = wideSharedBytes(shape.NP);
-    ensureDynamicSmem(reinterpret_cast<const void *>(inputGradWideUmma), smem);
+template <int CH, int CW>
+void launchWideAs(const Problem &prob, const WideShape &shape, cudaStream_t st) {
+    using G = WideGeometry<CH, CW>;
+    const size_t smem = G::sharedBytes(shape.NP);
+    ensureDynamicSmem(reinterpret_cast<const void *>(inputGradWideUmma<CH, CW>), smem);
     const CUtensorMap map = gradientMap(prob.G, prob.rows, prob.K);
     const int items = (prob.K / 8) * shape.NP;
     KernelTimer timer__("inputGradUmma", st);
     packWideWeights<<<(items + 255) / 256, 256, 0, st>>>(prob.codesNK, prob.codesKN, prob.ldCodesKN ? prob.ldCodesKN : prob.N, prob.K, prob.N,
-                                                         shape.NP, static_cast<uint4 *>(prob.packed));
-    inputGradWideUmma<<<(prob.rows + kTileM - 1) / kTileM, kThreadsWide, smem, st>>>(prob, shape, map);
+                                                         shape.NP, CH, static_cast<uint4 *>(prob.packed));
+    inputGradWideUmma<CH, CW><<<(prob.rows + kTileM - 1) / kTileM, G::kThreads, smem, st>>>(prob, shape, map);
+}
+
+void launchWide(const Problem &prob, cudaStream_t st) {
+    const WideShape shape = shapeFor(prob.N);
+    // up to 80 columns leave room for 64-channel chunks and sixteen converter warps (half as many hand-overs per tile)
+    static const bool narrowChunks = std::getenv("RXMET_IGRAD_CHUNK32") != nullptr;
+    if (prob.K % 64 == 0 && !narrowChunks && WideGeometry<64, 16>::sharedBytes(shape.NP) <= static_cast<size_t>(currentDevice().smemMax))
+        launchWideAs<64, 16>(prob, shape, st);
+    else launchWideAs<32, 8>(prob, shape, st);
 }
 
 }  // namespace igrad

@@ -151,7 +151,8 @@ def test_calibration_ignores_non_finite_values(gl):
 
 
 @pytest.mark.parametrize("cfg_name", ["w8a8", "a16", "w8a8_pot2"])
-@pytest.mark.parametrize("shape", [(5, 2, 3, 4), (7, 3, 31, 33), (8, 9, 40, 128)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("shape", [(5, 2, 3, 4), (7, 3, 31, 33), (8, 9, 40, 128), (6, 20, 72, 64), (6, 20, 72, 96)],
+                         ids=lambda s: "x".join(map(str, s)))   # 72 inputs: the streaming dx kernel, 64- and 32-channel chunks
 def test_backward_quant(gl, cfg_name, shape):
     T, B, I, H = shape
     cfg = ol.make_config(**CONFIGS[cfg_name])
