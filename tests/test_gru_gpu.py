@@ -179,10 +179,11 @@ def test_backward_quant(gl, cfg_name, shape):
         assert np.array_equal(a[k], b[k]), k
 
 
-def test_backward_quant_row_ranges_of_several_tiles(gl):
+@pytest.mark.parametrize("shape", [(80, 256, 40, 128), (80, 256, 72, 64)], ids=lambda s: "x".join(map(str, s)))
+def test_backward_quant_row_ranges_of_several_tiles(gl, shape):
     """Enough rows (T*B = 20480) that every CTA of the tcgen05 input-gradient kernel walks two 128-row
-    tiles and the split-K weight-gradient kernel runs many chunks per split."""
-    shape = (80, 256, 40, 128)
+    tiles and the split-K weight-gradient kernel runs many chunks per split.  72 inputs: the streaming
+    input-gradient kernel over more 128-row tiles than SMs."""
     T, B, I, H = shape
     cfg = ol.make_config(**CONFIGS["w8a8"])
     prob, params = calibrated(shape, seed=91, cfg=cfg, with_h0=True)
