@@ -207,6 +207,18 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
         // channels [8 (lane / 8), + 8) of each 32-channel box of the chunk
         const int rm = lane & 7, cq = lane >> 3;
         constexpr int kGroupsPerWarp = 16 / CW, kPieces = kGroupsPerWarp * G::kBoxes;
+        float4 suNext[G::kBoxes], svNext[G::kBoxes];
+        auto loadScales = [&](int chunk) {
+#pragma unroll
+            for (int b = 0; b < G::kBoxes; ++b) {
+                suNext[b] = svNext[b] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                if (p.kScale) {
+                    suNext[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + chunk * CH + 32 * b + 8 * cq));
+                    svNext[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + chunk * CH + 32 * b + 8 * cq + 4));
+                }
+            }
+        };
+        loadScales(0);
         for (int c = 0; c < chunks; ++c) {
             const int slot = c % kRawRing, sa = c % kAStages;
             await(&rawFull[slot], (c / kRawRing) & 1);
@@ -222,15 +234,15 @@ inputGradWideUmma(const Problem p, const WideShape shape, const __grid_constant_
                 }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(&rawEmpty[slot])) : "memory");
+            // this chunk's scales were asked for one chunk ago; the next chunk's go out now, so that their L2 round
+            // trip does not sit between the raw chunk and the operand stores
             float4 su[G::kBoxes], sv[G::kBoxes];
 #pragma unroll
             for (int b = 0; b < G::kBoxes; ++b) {
-                su[b] = sv[b] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-                if (p.kScale) {
-                    su[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * CH + 32 * b + 8 * cq));
-                    sv[b] = __ldg(reinterpret_cast<const float4 *>(p.kScale + c * CH + 32 * b + 8 * cq + 4));
-                }
+                su[b] = suNext[b];
+                sv[b] = svNext[b];
             }
+            if (c + 1 < chunks) loadScales(c + 1);
             if (c >= kAStages) await(&aEmpty[sa], (c / kAStages - 1) & 1);
             uint8_t *stage = aStages + sa * kAStageBytes;
 #pragma unroll
