@@ -258,3 +258,19 @@ def test_c_abi_exports_every_declared_symbol():
     lib = cabi.load_library()
     missing = [name for name in sorted(declared) if not hasattr(lib, name)]
     assert not missing, missing
+
+
+def test_float_storage_carrier_switch_is_host_state():
+    """The module-level switch behind forward_quant_float_storage: default "integer", returns the previous choice,
+    rejects anything but the two carriers (no GPU involved)."""
+    from rx_met_b200 import gru_interface_binding as ops
+    assert ops.float_storage_carrier() == "integer"
+    assert ops.set_float_storage_carrier("fp32") == "integer"
+    try:
+        assert ops.float_storage_carrier() == "fp32"
+        with pytest.raises(ValueError):
+            ops.set_float_storage_carrier("bf16")
+        assert ops.float_storage_carrier() == "fp32"
+    finally:
+        assert ops.set_float_storage_carrier("integer") == "fp32"
+    assert ops.float_storage_carrier() == "integer"
